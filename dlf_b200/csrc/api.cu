@@ -1,0 +1,520 @@
+// extern "C" boundary of the library (declared in include/dlf_b200.h): argument checks in the
+// reference's order, reduction of every call to the canonical problem of contraction.cuh,
+// tile / loader selection, TMA descriptor encoding and the launch. No call here allocates
+// device memory except the one-off 4-byte status word per device.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <climits>
+#include <cstdint>
+#include <cstring>
+#include <mutex>
+#include <vector>
+
+#include "../../include/dlf_b200.h"
+#include "contraction.cuh"
+
+using namespace dlfb200;
+
+namespace {
+
+// gpgpu::blas::StatusCode values used here (gpgpu/include/gblas.h:43-107)
+enum : int {
+    kSuccess = 0,
+    kInvalidValue = -30,
+    kNotImplemented = -1024,
+    kInvalidMatrixA = -1022,
+    kInvalidMatrixB = -1021,
+    kInvalidMatrixC = -1020,
+    kInvalidDimension = -1017,
+    kInvalidLeadDimA = -1016,
+    kInvalidLeadDimB = -1015,
+    kInvalidLeadDimC = -1014,
+    kInsufficientMemoryTemp = -2050,
+    kInvalidBatchCount = -2049,
+    kNoHalfPrecision = -2045,
+    kUnexpectedError = -2039,
+};
+
+constexpr int kMaxDevices = 64;
+constexpr int kSmemPerBlockOptin = 232448;  // 227 KB
+
+struct DeviceState {
+    bool ready = false;
+    int num_sms = 0;
+    int* status = nullptr;
+    int static_smem_tma = 0;
+    int static_smem_gen2 = 0;
+    int static_smem_gen4 = 0;
+    PFN_cuTensorMapEncodeTiled_v12000 encode = nullptr;
+};
+
+DeviceState g_dev[kMaxDevices];
+std::mutex g_mu;
+std::atomic<unsigned long long> g_launches{0};
+std::atomic<int> g_force_bn{0};
+std::atomic<int> g_force_generic{0};
+
+#define CUDA_TRY(expr)                                   \
+    do {                                                 \
+        cudaError_t e__ = (expr);                        \
+        if (e__ != cudaSuccess) return static_cast<int>(e__); \
+    } while (0)
+
+int ensure_device(DeviceState** out) {
+    int dev = 0;
+    CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return kInvalidValue;
+    std::lock_guard<std::mutex> lock(g_mu);
+    DeviceState& st = g_dev[dev];
+    if (!st.ready) {
+        CUDA_TRY(cudaDeviceGetAttribute(&st.num_sms, cudaDevAttrMultiProcessorCount, dev));
+        int major = 0;
+        CUDA_TRY(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+        if (major != 10) return kNotImplemented;  // tcgen05 kernels: sm_100a only
+        cudaFuncAttributes fa;
+        CUDA_TRY(cudaFuncGetAttributes(&fa, contraction_kernel<2, true>));
+        st.static_smem_tma = static_cast<int>(fa.sharedSizeBytes);
+        CUDA_TRY(cudaFuncGetAttributes(&fa, contraction_kernel<2, false>));
+        st.static_smem_gen2 = static_cast<int>(fa.sharedSizeBytes);
+        CUDA_TRY(cudaFuncGetAttributes(&fa, contraction_kernel<4, false>));
+        st.static_smem_gen4 = static_cast<int>(fa.sharedSizeBytes);
+        CUDA_TRY(cudaFuncSetAttribute(contraction_kernel<2, true>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      kSmemPerBlockOptin - st.static_smem_tma));
+        CUDA_TRY(cudaFuncSetAttribute(contraction_kernel<2, false>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      kSmemPerBlockOptin - st.static_smem_gen2));
+        CUDA_TRY(cudaFuncSetAttribute(contraction_kernel<4, false>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      kSmemPerBlockOptin - st.static_smem_gen4));
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+        if (qres != cudaDriverEntryPointSuccess || fn == nullptr) return kUnexpectedError;
+        st.encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+        CUDA_TRY(cudaMalloc(&st.status, sizeof(int)));
+        CUDA_TRY(cudaMemset(st.status, 0, sizeof(int)));
+        st.ready = true;
+    }
+    *out = &st;
+    return kSuccess;
+}
+
+bool dtype_info(int dtype, int& fmt, int& es) {
+    switch (dtype) {
+        case DLF_B200_HALF: fmt = FMT_F16; es = 2; return true;
+        case DLF_B200_BFLOAT16: fmt = FMT_BF16; es = 2; return true;
+        case DLF_B200_SINGLE: fmt = FMT_F32; es = 4; return true;
+        default: return false;
+    }
+}
+
+float scalar_to_float(int fmt, const void* p) {
+    if (fmt == FMT_F16) {
+        __half h;
+        std::memcpy(&h, p, 2);
+        return __half2float(h);
+    }
+    if (fmt == FMT_BF16) {
+        __nv_bfloat16 h;
+        std::memcpy(&h, p, 2);
+        return __bfloat162float(h);
+    }
+    float f;
+    std::memcpy(&f, p, 4);
+    return f;
+}
+
+struct Problem {
+    int fmt = 0, es = 0;
+    long long M = 0, N = 0, K = 0, batch = 1;
+    GenOperand a{}, b{};
+    char* d = nullptr;
+    long long ldd = 0, d_batch_stride = 0;
+    float alpha = 1.f, beta = 0.f;
+    const long long* a_offs = nullptr;
+    const long long* b_offs = nullptr;
+    const long long* d_offs = nullptr;
+    const float* alphas = nullptr;
+    const float* betas = nullptr;
+    const char* bias = nullptr;
+    Im2colGeom g{};
+};
+
+bool tma_ok(const GenOperand& op, int es, long long rows, long long K, long long batch) {
+    if (op.im2col) return false;
+    if (reinterpret_cast<uintptr_t>(op.base) & 15u) return false;
+    const long long lines = op.k_major ? rows : K;
+    if (lines > 1 && (op.ld * es) % 16 != 0) return false;
+    if (batch > 1 && op.batch_stride != 0 && (op.batch_stride * es) % 16 != 0) return false;
+    if (op.ld * es >= (1ll << 40) || op.batch_stride * es >= (1ll << 40)) return false;
+    return true;
+}
+
+// 3-D tiled tensor map {contiguous dim, line dim, batch} with 128-byte swizzle and zero fill.
+int encode_map(const DeviceState& st, CUtensorMap* map, const GenOperand& op, int es,
+               long long rows, long long K, long long batch, int box_rows) {
+    const int BK = 128 / es;
+    cuuint64_t dims[3];
+    cuuint64_t strides[2];
+    cuuint32_t box[3];
+    cuuint32_t estr[3] = {1, 1, 1};
+    const long long ld_bytes = (op.ld * es) % 16 == 0 && op.ld > 0 ? op.ld * es : 16;
+    if (op.k_major) {
+        dims[0] = static_cast<cuuint64_t>(K);
+        dims[1] = static_cast<cuuint64_t>(rows);
+        box[0] = BK;
+        box[1] = box_rows;
+    } else {
+        dims[0] = static_cast<cuuint64_t>(rows);
+        dims[1] = static_cast<cuuint64_t>(K);
+        box[0] = BK;  // E rows of the MN-major operand
+        box[1] = BK;
+    }
+    const bool batched = batch > 1 && op.batch_stride != 0;
+    dims[2] = batched ? static_cast<cuuint64_t>(batch) : 1;
+    strides[0] = static_cast<cuuint64_t>(ld_bytes);
+    strides[1] = batched ? static_cast<cuuint64_t>(op.batch_stride * es)
+                         : static_cast<cuuint64_t>(ld_bytes) * dims[1];
+    if (strides[1] >= (1ull << 40)) strides[1] = static_cast<cuuint64_t>(ld_bytes);
+    box[2] = 1;
+    const CUtensorMapDataType dt =
+        es == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT32;
+    CUresult r = st.encode(map, dt, 3, const_cast<char*>(op.base), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? kSuccess : kUnexpectedError;
+}
+
+int launch(const Problem& q, cudaStream_t stream) {
+    DeviceState* st = nullptr;
+    int rc = ensure_device(&st);
+    if (rc != kSuccess) return rc;
+    if (q.M > INT_MAX - 512 || q.N > INT_MAX - 512 || q.K > INT_MAX - 512 || q.batch > INT_MAX)
+        return kInvalidDimension;
+
+    const bool use_tma = q.es == 2 && !g_force_generic.load() && q.a_offs == nullptr &&
+                         tma_ok(q.a, q.es, q.M, q.K, q.batch) &&
+                         tma_ok(q.b, q.es, q.N, q.K, q.batch);
+
+    const long long tiles_m = (q.M + kBM - 1) / kBM;
+    int bn = q.N <= 64 ? 64 : (q.N <= 128 ? 128 : 256);
+    if (q.es == 4 && bn == 256) bn = 128;  // two (hi, lo) copies per stage: keep >= 3 stages
+    auto tiles_for = [&](int w) { return q.batch * tiles_m * ((q.N + w - 1) / w); };
+    while (bn > 64 && tiles_for(bn) < st->num_sms) bn /= 2;
+    const int forced = g_force_bn.load();
+    if (forced == 64 || forced == 128 || (forced == 256 && q.es == 2)) bn = forced;
+    const long long tiles_n = (q.N + bn - 1) / bn;
+    const long long total = q.batch * tiles_m * tiles_n;
+
+    const int static_smem =
+        use_tma ? st->static_smem_tma : (q.es == 2 ? st->static_smem_gen2 : st->static_smem_gen4);
+    const int stage_bytes = (kBM + bn) * 128 * (q.es == 4 ? 2 : 1);
+    int stages = (kSmemPerBlockOptin - static_smem - 1024) / stage_bytes;
+    if (stages > kMaxStages) stages = kMaxStages;
+    if (stages < 2) return kUnexpectedError;
+    const size_t dyn_smem = static_cast<size_t>(stages) * stage_bytes + 1024;
+
+    Params p{};
+    p.M = static_cast<int>(q.M);
+    p.N = static_cast<int>(q.N);
+    p.K = static_cast<int>(q.K);
+    p.batch = static_cast<int>(q.batch);
+    p.BN = bn;
+    p.stages = stages;
+    p.fmt = q.fmt;
+    p.tiles_m = static_cast<int>(tiles_m);
+    p.tiles_n = static_cast<int>(tiles_n);
+    p.total_tiles = total;
+    p.alpha = q.alpha;
+    p.beta = q.beta;
+    p.a = q.a;
+    p.b = q.b;
+    p.d = q.d;
+    p.ldd = q.ldd;
+    p.d_batch_stride = q.d_batch_stride;
+    p.a_offs = q.a_offs;
+    p.b_offs = q.b_offs;
+    p.d_offs = q.d_offs;
+    p.alphas = q.alphas;
+    p.betas = q.betas;
+    p.bias = q.bias;
+    p.g = q.g;
+    p.status = st->status;
+
+    CUtensorMap tm_a, tm_b;
+    std::memset(&tm_a, 0, sizeof(tm_a));
+    std::memset(&tm_b, 0, sizeof(tm_b));
+    if (use_tma) {
+        rc = encode_map(*st, &tm_a, q.a, q.es, q.M, q.K, q.batch, kBM);
+        if (rc != kSuccess) return rc;
+        rc = encode_map(*st, &tm_b, q.b, q.es, q.N, q.K, q.batch, bn);
+        if (rc != kSuccess) return rc;
+    }
+
+    const unsigned grid = static_cast<unsigned>(total < st->num_sms ? total : st->num_sms);
+    if (use_tma) {
+        contraction_kernel<2, true><<<grid, kThreadsTma, dyn_smem, stream>>>(p, tm_a, tm_b);
+    } else if (q.es == 2) {
+        contraction_kernel<2, false><<<grid, kThreadsGen, dyn_smem, stream>>>(p, tm_a, tm_b);
+    } else {
+        contraction_kernel<4, false><<<grid, kThreadsGen, dyn_smem, stream>>>(p, tm_a, tm_b);
+    }
+    g_launches.fetch_add(1);
+    CUDA_TRY(cudaGetLastError());
+    return kSuccess;
+}
+
+// Argument rules of Xgemm<T>::ProcessArguments (gpgpu/src/routines/level3/xgemm.hpp:54-91)
+// and TestMatrixA/B/C (gpgpu/src/utilities/buffer_test.hpp:24-55), then the mapping of the
+// user's (layout, transposes) onto the canonical problem whose output index i is contiguous.
+int setup_gemm(Problem& q, int dtype, int layout, int ta, int tb, size_t m, size_t n, size_t k,
+               const void* a, size_t a_ld, const void* b, size_t b_ld, void* c, size_t c_ld) {
+    if (!dtype_info(dtype, q.fmt, q.es)) return kNotImplemented;
+    if (layout != DLF_B200_ROW_MAJOR && layout != DLF_B200_COL_MAJOR) return kInvalidValue;
+    if (ta < DLF_B200_NO_TRANS || ta > DLF_B200_CONJ_TRANS) return kInvalidValue;
+    if (tb < DLF_B200_NO_TRANS || tb > DLF_B200_CONJ_TRANS) return kInvalidValue;
+    if (m == 0 || n == 0 || k == 0) return kInvalidDimension;
+    const bool row = layout == DLF_B200_ROW_MAJOR;
+    const bool a_rot = (!row && ta != DLF_B200_NO_TRANS) || (row && ta == DLF_B200_NO_TRANS);
+    const bool b_rot = (!row && tb != DLF_B200_NO_TRANS) || (row && tb == DLF_B200_NO_TRANS);
+    const size_t a_one = a_rot ? k : m;
+    const size_t b_one = b_rot ? n : k;
+    const size_t c_one = row ? n : m;
+    if (a_ld < a_one) return kInvalidLeadDimA;
+    if (b_ld < b_one) return kInvalidLeadDimB;
+    if (c_ld < c_one) return kInvalidLeadDimC;
+    if (a == nullptr) return kInvalidMatrixA;
+    if (b == nullptr) return kInvalidMatrixB;
+    if (c == nullptr) return kInvalidMatrixC;
+
+    GenOperand ua{}, ub{};
+    ua.base = static_cast<const char*>(a);
+    ua.ld = static_cast<long long>(a_ld);
+    ua.k_major = a_rot ? 1 : 0;  // a_rot: k is the contiguous index of A
+    ub.base = static_cast<const char*>(b);
+    ub.ld = static_cast<long long>(b_ld);
+    ub.k_major = b_rot ? 0 : 1;  // b_rot: n is the contiguous index of B
+    q.K = static_cast<long long>(k);
+    if (!row) {  // C(m x n) column-major: i = row of C
+        q.M = static_cast<long long>(m);
+        q.N = static_cast<long long>(n);
+        q.a = ua;
+        q.b = ub;
+    } else {  // C row-major: i = column of C, so B supplies the "A" side
+        q.M = static_cast<long long>(n);
+        q.N = static_cast<long long>(m);
+        q.a = ub;
+        q.b = ua;
+    }
+    q.d = static_cast<char*>(c);
+    q.ldd = static_cast<long long>(c_ld);
+    return kSuccess;
+}
+
+}  // namespace
+
+extern "C" {
+
+int dlf_b200_gemm(int dtype, int layout, int trans_a, int trans_b, size_t m, size_t n, size_t k,
+                  const void* alpha, const void* a, size_t a_ld, const void* b, size_t b_ld,
+                  const void* beta, void* c, size_t c_ld, void* stream) {
+    Problem q;
+    int rc = setup_gemm(q, dtype, layout, trans_a, trans_b, m, n, k, a, a_ld, b, b_ld, c, c_ld);
+    if (rc != kSuccess) return rc;
+    if (alpha == nullptr || beta == nullptr) return kInvalidValue;
+    q.alpha = scalar_to_float(q.fmt, alpha);
+    q.beta = scalar_to_float(q.fmt, beta);
+    return launch(q, static_cast<cudaStream_t>(stream));
+}
+
+int dlf_b200_gemm_strided_batched(int dtype, int layout, int trans_a, int trans_b, size_t m,
+                                  size_t n, size_t k, const void* alpha, const void* a,
+                                  size_t a_ld, size_t a_stride, const void* b, size_t b_ld,
+                                  size_t b_stride, const void* beta, void* c, size_t c_ld,
+                                  size_t c_stride, size_t batch_count, void* stream) {
+    if (batch_count < 1) return kInvalidBatchCount;
+    Problem q;
+    int rc = setup_gemm(q, dtype, layout, trans_a, trans_b, m, n, k, a, a_ld, b, b_ld, c, c_ld);
+    if (rc != kSuccess) return rc;
+    if (alpha == nullptr || beta == nullptr) return kInvalidValue;
+    q.alpha = scalar_to_float(q.fmt, alpha);
+    q.beta = scalar_to_float(q.fmt, beta);
+    q.batch = static_cast<long long>(batch_count);
+    const bool row = layout == DLF_B200_ROW_MAJOR;
+    (row ? q.b : q.a).batch_stride = static_cast<long long>(a_stride);
+    (row ? q.a : q.b).batch_stride = static_cast<long long>(b_stride);
+    q.d_batch_stride = static_cast<long long>(c_stride);
+    return launch(q, static_cast<cudaStream_t>(stream));
+}
+
+size_t dlf_b200_gemm_batched_workspace_bytes(size_t batch_count) {
+    // three int64 offset tables + two float scalar tables
+    return batch_count * (3 * sizeof(long long) + 2 * sizeof(float));
+}
+
+int dlf_b200_gemm_batched(int dtype, int layout, int trans_a, int trans_b, size_t m, size_t n,
+                          size_t k, const void* alphas, const void* a, const size_t* a_offsets,
+                          size_t a_ld, const void* b, const size_t* b_offsets, size_t b_ld,
+                          const void* betas, void* c, const size_t* c_offsets, size_t c_ld,
+                          size_t batch_count, void* workspace, size_t workspace_bytes,
+                          void* stream) {
+    if (batch_count < 1 || alphas == nullptr || betas == nullptr || a_offsets == nullptr ||
+        b_offsets == nullptr || c_offsets == nullptr)
+        return kInvalidBatchCount;
+    Problem q;
+    int rc = setup_gemm(q, dtype, layout, trans_a, trans_b, m, n, k, a, a_ld, b, b_ld, c, c_ld);
+    if (rc != kSuccess) return rc;
+    const size_t need = dlf_b200_gemm_batched_workspace_bytes(batch_count);
+    if (workspace == nullptr || workspace_bytes < need) return kInsufficientMemoryTemp;
+    if (reinterpret_cast<uintptr_t>(workspace) & 7u) return kInvalidValue;
+
+    const bool row = layout == DLF_B200_ROW_MAJOR;
+    std::vector<unsigned char> host(need);
+    long long* h_a = reinterpret_cast<long long*>(host.data());
+    long long* h_b = h_a + batch_count;
+    long long* h_d = h_b + batch_count;
+    float* h_alpha = reinterpret_cast<float*>(h_d + batch_count);
+    float* h_beta = h_alpha + batch_count;
+    for (size_t i = 0; i < batch_count; ++i) {
+        // the canonical "A" side is the user's B for row-major calls
+        h_a[i] = static_cast<long long>(row ? b_offsets[i] : a_offsets[i]);
+        h_b[i] = static_cast<long long>(row ? a_offsets[i] : b_offsets[i]);
+        h_d[i] = static_cast<long long>(c_offsets[i]);
+        h_alpha[i] = scalar_to_float(q.fmt, static_cast<const char*>(alphas) + i * q.es);
+        h_beta[i] = scalar_to_float(q.fmt, static_cast<const char*>(betas) + i * q.es);
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // pageable source: the runtime stages it before returning, so `host` may go out of scope
+    CUDA_TRY(cudaMemcpyAsync(workspace, host.data(), need, cudaMemcpyHostToDevice, s));
+    char* w = static_cast<char*>(workspace);
+    q.a_offs = reinterpret_cast<const long long*>(w);
+    q.b_offs = q.a_offs + batch_count;
+    q.d_offs = q.b_offs + batch_count;
+    q.alphas = reinterpret_cast<const float*>(q.d_offs + batch_count);
+    q.betas = q.alphas + batch_count;
+    q.batch = static_cast<long long>(batch_count);
+    return launch(q, s);
+}
+
+size_t dlf_b200_conv2d_workspace_bytes(int, size_t, size_t, size_t, size_t, size_t, size_t, size_t,
+                                       size_t, size_t, size_t) {
+    return 0;  // implicit GEMM: the im2col matrix only ever exists tile by tile in shared memory
+}
+
+int dlf_b200_conv2d(int dtype, size_t batches, size_t channels, size_t height, size_t width,
+                    size_t output_h, size_t output_w, size_t num_kernels, size_t group,
+                    size_t kernel_h, size_t kernel_w, size_t pad_top, size_t pad_left,
+                    size_t pad_bottom, size_t pad_right, size_t stride_h, size_t stride_w,
+                    size_t dilation_h, size_t dilation_w, const void* x, const void* w,
+                    const void* bias, void* y, void* workspace, size_t workspace_bytes,
+                    void* stream) {
+    (void)pad_bottom;
+    (void)pad_right;
+    (void)workspace;
+    (void)workspace_bytes;
+    Problem q;
+    if (!dtype_info(dtype, q.fmt, q.es)) return kNotImplemented;
+    if (batches == 0 || channels == 0 || height == 0 || width == 0 || output_h == 0 ||
+        output_w == 0 || num_kernels == 0 || kernel_h == 0 || kernel_w == 0)
+        return kInvalidDimension;
+    if (group == 0 || channels % group != 0 || num_kernels % group != 0) return kInvalidDimension;
+    if (stride_h == 0 || stride_w == 0 || dilation_h == 0 || dilation_w == 0) return kInvalidValue;
+    if (x == nullptr) return kInvalidMatrixA;
+    if (w == nullptr) return kInvalidMatrixB;
+    if (y == nullptr) return kInvalidMatrixC;
+    const long long P = static_cast<long long>(output_h) * output_w;
+    const long long cg = static_cast<long long>(channels / group);
+    const long long ng = static_cast<long long>(num_kernels / group);
+    const long long K = cg * kernel_h * kernel_w;
+    const size_t lim = 1u << 30;
+    if (height >= lim || width >= lim || kernel_h >= lim || kernel_w >= lim || pad_top >= lim ||
+        pad_left >= lim || stride_h >= lim || stride_w >= lim || dilation_h >= lim ||
+        dilation_w >= lim || static_cast<long long>(height) * width >= INT_MAX)
+        return kInvalidDimension;
+
+    q.M = static_cast<long long>(batches) * P;  // global output pixel index
+    q.N = ng;
+    q.K = K;
+    q.batch = static_cast<long long>(group);
+    q.a.base = static_cast<const char*>(x);
+    q.a.im2col = 1;
+    q.a.k_major = 0;
+    q.a.ld = 0;
+    q.a.batch_stride = cg * static_cast<long long>(height) * width;
+    q.b.base = static_cast<const char*>(w);
+    q.b.k_major = 1;
+    q.b.ld = K;
+    q.b.batch_stride = ng * K;
+    q.d = static_cast<char*>(y);
+    q.ldd = P;
+    q.d_batch_stride = ng * P;
+    q.alpha = 1.f;
+    q.beta = 0.f;
+    q.bias = static_cast<const char*>(bias);
+    q.g.H = static_cast<int>(height);
+    q.g.W = static_cast<int>(width);
+    q.g.OH = static_cast<int>(output_h);
+    q.g.OW = static_cast<int>(output_w);
+    q.g.KH = static_cast<int>(kernel_h);
+    q.g.KW = static_cast<int>(kernel_w);
+    q.g.pad_t = static_cast<int>(pad_top);
+    q.g.pad_l = static_cast<int>(pad_left);
+    q.g.sh = static_cast<int>(stride_h);
+    q.g.sw = static_cast<int>(stride_w);
+    q.g.dh = static_cast<int>(dilation_h);
+    q.g.dw = static_cast<int>(dilation_w);
+    q.g.P = static_cast<int>(P);
+    q.g.img_stride = static_cast<long long>(channels) * height * width;
+    q.g.out_img_stride = static_cast<long long>(num_kernels) * P;
+    if (P > INT_MAX) return kInvalidDimension;
+    return launch(q, static_cast<cudaStream_t>(stream));
+}
+
+const char* dlf_b200_status_string(int status) {
+    switch (status) {
+        case kSuccess: return "kSuccess";
+        case kInvalidValue: return "kInvalidValue";
+        case kNotImplemented: return "kNotImplemented";
+        case kInvalidMatrixA: return "kInvalidMatrixA";
+        case kInvalidMatrixB: return "kInvalidMatrixB";
+        case kInvalidMatrixC: return "kInvalidMatrixC";
+        case kInvalidDimension: return "kInvalidDimension";
+        case kInvalidLeadDimA: return "kInvalidLeadDimA";
+        case kInvalidLeadDimB: return "kInvalidLeadDimB";
+        case kInvalidLeadDimC: return "kInvalidLeadDimC";
+        case kInsufficientMemoryTemp: return "kInsufficientMemoryTemp";
+        case kInvalidBatchCount: return "kInvalidBatchCount";
+        case kNoHalfPrecision: return "kNoHalfPrecision";
+        case kUnexpectedError: return "kUnexpectedError";
+        default: break;
+    }
+    if (status > 0) return cudaGetErrorName(static_cast<cudaError_t>(status));
+    return "unknown status";
+}
+
+int dlf_b200_device_status(int* device_status) {
+    DeviceState* st = nullptr;
+    int rc = ensure_device(&st);
+    if (rc != kSuccess) return rc;
+    CUDA_TRY(cudaDeviceSynchronize());
+    int v = 0;
+    CUDA_TRY(cudaMemcpy(&v, st->status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (v != 0) CUDA_TRY(cudaMemset(st->status, 0, sizeof(int)));
+    if (device_status) *device_status = v;
+    return kSuccess;
+}
+
+void dlf_b200_set_tuning(int force_bn, int force_generic_loader) {
+    g_force_bn.store(force_bn);
+    g_force_generic.store(force_generic_loader);
+}
+
+unsigned long long dlf_b200_launch_count(void) { return g_launches.load(); }
+
+}  // extern "C"

@@ -1,0 +1,571 @@
+// Persistent, warp-specialised tcgen05 contraction kernel.
+//
+// One kernel body serves gemm / gemmStridedBatched / gemmBatched and conv2d. Every call is
+// first brought to one canonical problem on the host:
+//
+//     D[i + j*ldd] = alpha * sum_k Au(i,k) * Bu(j,k) + beta * D[i + j*ldd] (+ bias[j])
+//
+// with i the memory-contiguous index of the output. i maps to the 128 TMEM lanes of a
+// UMMA tile, so a warp of the epilogue stores 32 consecutive output elements per
+// instruction. Au (M x K) and Bu (N x K) are each either "K-major" (k contiguous in
+// memory) or "MN-major" (i resp. j contiguous); tcgen05.mma accepts both for f16, bf16
+// and tf32, which is why no transposition or padding pass exists.
+//
+// Shared-memory operand tiles use the 128-byte-swizzled canonical UMMA layouts. A tile
+// of R rows by BK = 128/sizeof(T) k-values is R "lines" of 128 bytes; 16-byte chunk c of
+// line L sits at  L*128 + ((c ^ (L & 7)) << 4).
+//   K-major : line L = row L, the 128 bytes run along k.
+//             descriptor: SBO = 1024 (8 rows), one UMMA k-step = +32 bytes.
+//   MN-major: line L = (row group g = L / BK, k = L % BK), the 128 bytes run along rows
+//             g*E .. g*E+E-1 (E = BK). descriptor: LBO = BK*128 (next row group),
+//             SBO = 1024 (next 8 k), one UMMA k-step = +(UMMA_K/8)*1024 bytes.
+// TMA boxes with CU_TENSOR_MAP_SWIZZLE_128B produce exactly these layouts; the generic
+// loader warps reproduce them with plain stores.
+//
+// Roles (warp index): 0-3 epilogue (TMEM lane quadrant = warp index), 4 UMMA issuer and
+// TMEM owner, 5 TMA producer, 6-13 generic loader warps (only launched for the generic
+// variant). fp32 inputs run as 3xTF32: the loader writes hi = tf32(x) and lo = tf32(x - hi)
+// tiles and the issuer accumulates lo*hi + hi*lo + hi*hi into one fp32 TMEM accumulator.
+//
+// All mbarrier waits are bounded (ptx::mbar_wait_bounded); a timeout raises a per-CTA
+// abort flag, every role drains, TMEM is freed and a status word in global memory is set.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "ptx.cuh"
+
+namespace dlfb200 {
+
+constexpr int kBM = 128;
+constexpr int kMmaWarp = 4;
+constexpr int kTmaWarp = 5;
+constexpr int kFirstLoaderWarp = 6;
+constexpr int kLoaderWarps = 8;
+constexpr int kLoaderThreads = kLoaderWarps * 32;
+constexpr int kThreadsTma = 6 * 32;
+constexpr int kThreadsGen = (kFirstLoaderWarp + kLoaderWarps) * 32;
+constexpr int kMaxStages = 8;
+constexpr int kGroupM = 8;  // tile rasterisation: kGroupM row-tiles share their column sweep
+
+enum : int { FMT_F16 = 0, FMT_BF16 = 1, FMT_F32 = 2 };
+
+enum : int {
+    DEV_STATUS_OK = 0,
+    DEV_STATUS_WAIT_TIMEOUT = 1,  // a bounded mbarrier wait gave up
+};
+
+struct GenOperand {
+    const char* base;        // element (0,0) of batch 0
+    long long ld;            // elements between consecutive 128-byte lines' origins
+    long long batch_stride;  // elements between batches (0 = shared by every batch)
+    int k_major;             // 1: k contiguous in memory; 0: row index contiguous
+    int im2col;              // operand is an implicit im2col view of an NCHW tensor (A only)
+};
+
+// Geometry of the implicit im2col operand. Row index i of the canonical problem is the
+// global output pixel  img * P + oh * OW + ow ; k = (c * KH + kh) * KW + kw.
+struct Im2colGeom {
+    int H, W, OH, OW, KH, KW, pad_t, pad_l, sh, sw, dh, dw;
+    int P;                     // OH*OW
+    long long img_stride;      // elements between images of X (C*H*W)
+    long long out_img_stride;  // elements between images of Y (Cout*P)
+};
+
+struct Params {
+    int M, N, K, batch;
+    int BN, stages, fmt;
+    int tiles_m, tiles_n;
+    long long total_tiles;
+    float alpha, beta;
+    GenOperand a, b;
+    char* d;
+    long long ldd, d_batch_stride;
+    // gemmBatched tables (device memory, entries per batch); null for the other calls
+    const long long* a_offs;
+    const long long* b_offs;
+    const long long* d_offs;
+    const float* alphas;
+    const float* betas;
+    const char* bias;  // bias[batch*N + j] in the storage type, or null
+    Im2colGeom g;
+    int* status;
+};
+
+struct PixelEntry {  // one output pixel of the current tile (implicit im2col operand)
+    long long base;  // img*img_stride + ih0*W + iw0 (may point before the image: guarded)
+    int ih0, iw0;    // oh*sh - pad_t, ow*sw - pad_l ; ih0 = INT_MIN/2 marks "no such pixel"
+};
+
+__device__ __forceinline__ void decode_tile(const Params& p, long long t, int& b, int& m0,
+                                            int& n0) {
+    const long long per = static_cast<long long>(p.tiles_m) * p.tiles_n;
+    b = static_cast<int>(t / per);
+    const int r = static_cast<int>(t - b * per);
+    const int group = kGroupM * p.tiles_n;
+    const int gi = r / group;
+    const int first = gi * kGroupM;
+    const int gm = min(p.tiles_m - first, kGroupM);
+    const int rr = r - gi * group;
+    m0 = (first + rr % gm) * kBM;
+    n0 = (rr / gm) * p.BN;
+}
+
+template <int ES>
+__device__ __forceinline__ uint4 load_chunk_dense(const GenOperand& op, long long boff,
+                                                  int line_coord, int line_lim, int cont0,
+                                                  int cont_lim) {
+    constexpr int CPE = 16 / ES;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (line_coord >= line_lim || cont0 >= cont_lim) return v;
+    const char* ptr =
+        op.base + (boff + static_cast<long long>(line_coord) * op.ld + cont0) * ES;
+    if (cont0 + CPE <= cont_lim && (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0u) {
+        return *reinterpret_cast<const uint4*>(ptr);
+    }
+    if constexpr (ES == 2) {
+        unsigned short e[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            e[i] = (cont0 + i < cont_lim) ? reinterpret_cast<const unsigned short*>(ptr)[i]
+                                          : static_cast<unsigned short>(0);
+        v.x = e[0] | (static_cast<uint32_t>(e[1]) << 16);
+        v.y = e[2] | (static_cast<uint32_t>(e[3]) << 16);
+        v.z = e[4] | (static_cast<uint32_t>(e[5]) << 16);
+        v.w = e[6] | (static_cast<uint32_t>(e[7]) << 16);
+    } else {
+        uint32_t e[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            e[i] = (cont0 + i < cont_lim) ? reinterpret_cast<const uint32_t*>(ptr)[i] : 0u;
+        v = make_uint4(e[0], e[1], e[2], e[3]);
+    }
+    return v;
+}
+
+template <int ES>
+__device__ __forceinline__ uint4 load_chunk_im2col(const Params& p, const PixelEntry* table,
+                                                   long long boff, int k, int pix0) {
+    constexpr int CPE = 16 / ES;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (k >= p.K) return v;
+    const int khw = p.g.KH * p.g.KW;
+    const int ch = k / khw;
+    const int rem = k - ch * khw;
+    const int kh = rem / p.g.KW;
+    const int kw = rem - kh * p.g.KW;
+    const int dy = kh * p.g.dh, dx = kw * p.g.dw;
+    const long long koff =
+        boff + (static_cast<long long>(ch) * p.g.H + dy) * p.g.W + dx;
+    if constexpr (ES == 2) {
+        unsigned short e[8];
+#pragma unroll
+        for (int i = 0; i < CPE; ++i) {
+            const PixelEntry pe = table[pix0 + i];
+            const bool ok = static_cast<unsigned>(pe.ih0 + dy) < static_cast<unsigned>(p.g.H) &&
+                            static_cast<unsigned>(pe.iw0 + dx) < static_cast<unsigned>(p.g.W);
+            e[i] = ok ? reinterpret_cast<const unsigned short*>(p.a.base)[pe.base + koff]
+                      : static_cast<unsigned short>(0);
+        }
+        v.x = e[0] | (static_cast<uint32_t>(e[1]) << 16);
+        v.y = e[2] | (static_cast<uint32_t>(e[3]) << 16);
+        v.z = e[4] | (static_cast<uint32_t>(e[5]) << 16);
+        v.w = e[6] | (static_cast<uint32_t>(e[7]) << 16);
+    } else {
+        uint32_t e[4];
+#pragma unroll
+        for (int i = 0; i < CPE; ++i) {
+            const PixelEntry pe = table[pix0 + i];
+            const bool ok = static_cast<unsigned>(pe.ih0 + dy) < static_cast<unsigned>(p.g.H) &&
+                            static_cast<unsigned>(pe.iw0 + dx) < static_cast<unsigned>(p.g.W);
+            e[i] = ok ? reinterpret_cast<const uint32_t*>(p.a.base)[pe.base + koff] : 0u;
+        }
+        v = make_uint4(e[0], e[1], e[2], e[3]);
+    }
+    return v;
+}
+
+// x = hi + lo with hi, lo both exactly representable in tf32 (10 explicit mantissa bits).
+__device__ __forceinline__ void split_tf32(uint32_t x, uint32_t& hi, uint32_t& lo) {
+    const float xf = __uint_as_float(x);
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(xf));
+    const float rest = xf - __uint_as_float(hi);
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo) : "f"(rest));
+}
+
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, const uint4& v) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y),
+                 "r"(v.z), "r"(v.w)
+                 : "memory");
+}
+
+template <int ES>
+__device__ __forceinline__ void store_chunk(uint32_t tile, uint32_t lo_tile, int L, int c,
+                                            const uint4& v) {
+    const uint32_t off = static_cast<uint32_t>(L) * 128u + (static_cast<uint32_t>(c ^ (L & 7)) << 4);
+    if constexpr (ES == 2) {
+        st_shared_v4(tile + off, v);
+    } else {
+        uint4 hi, lo;
+        split_tf32(v.x, hi.x, lo.x);
+        split_tf32(v.y, hi.y, lo.y);
+        split_tf32(v.z, hi.z, lo.z);
+        split_tf32(v.w, hi.w, lo.w);
+        st_shared_v4(tile + off, hi);
+        st_shared_v4(lo_tile + off, lo);
+    }
+}
+
+template <int ES>
+__device__ __forceinline__ void store_out(char* ptr, float v, int fmt) {
+    if constexpr (ES == 4) {
+        *reinterpret_cast<float*>(ptr) = v;
+    } else {
+        if (fmt == FMT_F16)
+            *reinterpret_cast<__half*>(ptr) = __float2half_rn(v);
+        else
+            *reinterpret_cast<__nv_bfloat16*>(ptr) = __float2bfloat16_rn(v);
+    }
+}
+template <int ES>
+__device__ __forceinline__ float load_out(const char* ptr, int fmt) {
+    if constexpr (ES == 4) {
+        return *reinterpret_cast<const float*>(ptr);
+    } else {
+        if (fmt == FMT_F16) return __half2float(*reinterpret_cast<const __half*>(ptr));
+        return __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(ptr));
+    }
+}
+
+template <int ES, bool USE_TMA>
+__global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
+    contraction_kernel(const __grid_constant__ Params p, const __grid_constant__ CUtensorMap tmA,
+                       const __grid_constant__ CUtensorMap tmB) {
+    static_assert(!(USE_TMA && ES == 4), "fp32 operands need the split done by loader warps");
+    constexpr int BK = 128 / ES;               // k-values per stage (one 128-byte line)
+    constexpr int E = BK;                      // rows per MN-major row group
+    constexpr int CPE = 16 / ES;               // elements per 16-byte chunk
+    constexpr int UMMA_K = 32 / ES;            // 16 (f16/bf16) or 8 (tf32)
+    constexpr uint32_t KSTEP_K = 32;           // bytes per UMMA k-step, K-major
+    constexpr uint32_t KSTEP_MN = (UMMA_K / 8) * 1024;  // bytes per UMMA k-step, MN-major
+    constexpr uint32_t A_TILE = kBM * 128;
+
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[kMaxStages];
+    __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
+    __shared__ __align__(8) uint64_t tfull_bar[2];
+    __shared__ __align__(8) uint64_t tempty_bar[2];
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+    __shared__ __align__(16) PixelEntry pix_table[USE_TMA ? 1 : kLoaderWarps * kBM];
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int BN = p.BN;
+    const int S = p.stages;
+    const uint32_t b_tile = static_cast<uint32_t>(BN) * 128u;
+    const uint32_t stage_bytes = (A_TILE + b_tile) * (ES == 4 ? 2u : 1u);
+    const uint32_t smem0 = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+    const int num_kb = (p.K + BK - 1) / BK;
+    const uint32_t tmem_cols = (2 * BN <= 128) ? 128u : (2 * BN <= 256 ? 256u : 512u);
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < S; ++s) {
+            ptx::mbar_init(ptx::smem_u32(&full_bar[s]), USE_TMA ? 1u : kLoaderThreads);
+            ptx::mbar_init(ptx::smem_u32(&empty_bar[s]), 1u);
+        }
+        for (int i = 0; i < 2; ++i) {
+            ptx::mbar_init(ptx::smem_u32(&tfull_bar[i]), 1u);
+            ptx::mbar_init(ptx::smem_u32(&tempty_bar[i]), 128u);
+        }
+        ptx::fence_mbar_init();
+    }
+    if (warp == kMmaWarp) {
+        __syncwarp();
+        ptx::tmem_alloc(ptx::smem_u32(&tmem_slot), tmem_cols);
+        ptx::tmem_relinquish();
+    }
+    if (USE_TMA && warp == kTmaWarp && lane == 0) {
+        ptx::tma_prefetch_desc(&tmA);
+        ptx::tma_prefetch_desc(&tmB);
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&tmem_slot);
+    volatile int* abort_p = &abort_flag;
+
+    if (warp < 4) {
+        // ------------------------------------------------------------ epilogue
+        long long it = 0;
+        for (long long t = blockIdx.x; t < p.total_tiles; t += gridDim.x, ++it) {
+            int b, m0, n0;
+            decode_tile(p, t, b, m0, n0);
+            const uint32_t buf = static_cast<uint32_t>(it & 1);
+            const uint32_t tphase = static_cast<uint32_t>((it >> 1) & 1);
+            // tcgen05.ld is warp-collective: the warp leaves together or not at all
+            const bool w = ptx::mbar_wait_bounded(ptx::smem_u32(&tfull_bar[buf]), tphase, abort_p);
+            if (!__all_sync(0xffffffffu, w)) break;
+            ptx::tc_fence_after();
+
+            const int i = m0 + warp * 32 + lane;
+            const bool row_ok = i < p.M;
+            long long rowbase;
+            long long colstride;
+            if (p.a.im2col) {
+                const int img = i / p.g.P;
+                const int pp = i - img * p.g.P;
+                rowbase = static_cast<long long>(img) * p.g.out_img_stride +
+                          static_cast<long long>(b) * p.d_batch_stride + pp;
+                colstride = p.g.P;
+            } else {
+                rowbase = (p.d_offs ? p.d_offs[b] : static_cast<long long>(b) * p.d_batch_stride) + i;
+                colstride = p.ldd;
+            }
+            const float alpha = p.alphas ? p.alphas[b] : p.alpha;
+            const float beta = p.betas ? p.betas[b] : p.beta;
+            const char* bias = p.bias ? p.bias + static_cast<long long>(b) * p.N * ES : nullptr;
+            const uint32_t trow = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + buf * BN;
+
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                if (n0 + c0 >= p.N) break;
+                uint32_t v[32];
+                ptx::tmem_ld_32x32(trow + c0, v);
+                ptx::tmem_ld_wait();
+                if (row_ok) {
+#pragma unroll
+                    for (int jj = 0; jj < 32; ++jj) {
+                        const int j = n0 + c0 + jj;
+                        if (j < p.N) {
+                            char* optr = p.d + (rowbase + static_cast<long long>(j) * colstride) * ES;
+                            float r = alpha * __uint_as_float(v[jj]);
+                            if (beta != 0.0f) r += beta * load_out<ES>(optr, p.fmt);
+                            if (bias) r += load_out<ES>(bias + static_cast<long long>(j) * ES, p.fmt);
+                            store_out<ES>(optr, r, p.fmt);
+                        }
+                    }
+                }
+            }
+            ptx::tc_fence_before();
+            ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));
+        }
+    } else if (warp == kMmaWarp) {
+        // ------------------------------------------------------------ UMMA issuer
+        if (lane == 0) {
+            const uint32_t idesc =
+                ptx::make_idesc(p.fmt == FMT_F32 ? 2u : static_cast<uint32_t>(p.fmt),
+                                p.a.k_major ? 0u : 1u, p.b.k_major ? 0u : 1u, kBM, BN);
+            const uint32_t a_step = p.a.k_major ? KSTEP_K : KSTEP_MN;
+            const uint32_t b_step = p.b.k_major ? KSTEP_K : KSTEP_MN;
+            const uint32_t a_lbo = p.a.k_major ? 16u : static_cast<uint32_t>(BK) * 128u;
+            const uint32_t b_lbo = p.b.k_major ? 16u : static_cast<uint32_t>(BK) * 128u;
+            uint32_t stage = 0, phase = 0;
+            long long it = 0;
+            bool ok = true;
+            for (long long t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x, ++it) {
+                const uint32_t buf = static_cast<uint32_t>(it & 1);
+                const uint32_t tphase = static_cast<uint32_t>((it >> 1) & 1);
+                if (!ptx::mbar_wait_bounded(ptx::smem_u32(&tempty_bar[buf]), tphase ^ 1u, abort_p)) {
+                    ok = false;
+                    break;
+                }
+                ptx::tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!ptx::mbar_wait_bounded(ptx::smem_u32(&full_bar[stage]), phase, abort_p)) {
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after();
+                    const uint32_t sA = smem0 + stage * stage_bytes;
+                    const uint32_t sB = sA + A_TILE;
+#pragma unroll
+                    for (int ks = 0; ks < BK / UMMA_K; ++ks) {
+                        const uint64_t da = ptx::make_smem_desc(sA + ks * a_step, a_lbo, 1024u);
+                        const uint64_t db = ptx::make_smem_desc(sB + ks * b_step, b_lbo, 1024u);
+                        const uint32_t acc = (kb | ks) ? 1u : 0u;
+                        if constexpr (ES == 2) {
+                            ptx::umma_f16(d_tmem, da, db, idesc, acc);
+                        } else {
+                            const uint32_t lo_off = A_TILE + b_tile;
+                            const uint64_t da_lo =
+                                ptx::make_smem_desc(sA + lo_off + ks * a_step, a_lbo, 1024u);
+                            const uint64_t db_lo =
+                                ptx::make_smem_desc(sB + lo_off + ks * b_step, b_lbo, 1024u);
+                            ptx::umma_tf32(d_tmem, da_lo, db, idesc, acc);
+                            ptx::umma_tf32(d_tmem, da, db_lo, idesc, 1u);
+                            ptx::umma_tf32(d_tmem, da, db, idesc, 1u);
+                        }
+                    }
+                    ptx::umma_commit(ptx::smem_u32(&empty_bar[stage]));
+                    if (++stage == static_cast<uint32_t>(S)) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (ok) ptx::umma_commit(ptx::smem_u32(&tfull_bar[buf]));
+            }
+        }
+    } else if (USE_TMA && warp == kTmaWarp) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (long long t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x) {
+                int b, m0, n0;
+                decode_tile(p, t, b, m0, n0);
+                const int ba = p.a.batch_stride ? b : 0;
+                const int bb = p.b.batch_stride ? b : 0;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!ptx::mbar_wait_bounded(ptx::smem_u32(&empty_bar[stage]), phase ^ 1u,
+                                                abort_p)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t bar = ptx::smem_u32(&full_bar[stage]);
+                    const uint32_t sA = smem0 + stage * stage_bytes;
+                    const uint32_t sB = sA + A_TILE;
+                    ptx::mbar_arrive_expect_tx(bar, A_TILE + b_tile);
+                    if (p.a.k_major) {
+                        ptx::tma_load_3d(sA, &tmA, bar, kb * BK, m0, ba);
+                    } else {
+                        for (int g = 0; g < kBM / E; ++g)
+                            ptx::tma_load_3d(sA + g * BK * 128, &tmA, bar, m0 + g * E, kb * BK, ba);
+                    }
+                    if (p.b.k_major) {
+                        ptx::tma_load_3d(sB, &tmB, bar, kb * BK, n0, bb);
+                    } else {
+                        for (int g = 0; g < BN / E; ++g)
+                            ptx::tma_load_3d(sB + g * BK * 128, &tmB, bar, n0 + g * E, kb * BK, bb);
+                    }
+                    if (++stage == static_cast<uint32_t>(S)) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+    } else if (!USE_TMA && warp >= kFirstLoaderWarp) {
+        // ------------------------------------------------------------ generic loader warps
+        const int lt = threadIdx.x - kFirstLoaderWarp * 32;
+        const int c = lt & 7;
+        const int l0 = lt >> 3;
+        uint32_t stage = 0, phase = 0;
+        long long it = 0;
+        bool ok = true;
+        for (long long t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x, ++it) {
+            int b, m0, n0;
+            decode_tile(p, t, b, m0, n0);
+            const long long a_boff =
+                p.a_offs ? p.a_offs[b] : static_cast<long long>(b) * p.a.batch_stride;
+            const long long b_boff =
+                p.b_offs ? p.b_offs[b] : static_cast<long long>(b) * p.b.batch_stride;
+            // Each loader warp keeps its own table of the tile's 128 output pixels, so no
+            // cross-warp barrier is needed when warps run ahead of one another.
+            PixelEntry* table = pix_table + (warp - kFirstLoaderWarp) * kBM;
+            if (p.a.im2col) {
+                __syncwarp();
+#pragma unroll
+                for (int q = 0; q < kBM / 32; ++q) {
+                    PixelEntry pe;
+                    const int gp = m0 + lane + 32 * q;
+                    if (gp < p.M) {
+                        const int img = gp / p.g.P;
+                        const int pp = gp - img * p.g.P;
+                        const int oh = pp / p.g.OW;
+                        const int ow = pp - oh * p.g.OW;
+                        pe.ih0 = oh * p.g.sh - p.g.pad_t;
+                        pe.iw0 = ow * p.g.sw - p.g.pad_l;
+                        pe.base = static_cast<long long>(img) * p.g.img_stride +
+                                  static_cast<long long>(pe.ih0) * p.g.W + pe.iw0;
+                    } else {
+                        pe.ih0 = -(1 << 30);
+                        pe.iw0 = -(1 << 30);
+                        pe.base = 0;
+                    }
+                    table[lane + 32 * q] = pe;
+                }
+                __syncwarp();
+            }
+            for (int kb = 0; kb < num_kb; ++kb) {
+                // the whole warp leaves together: later __syncwarp()s need every lane
+                const bool w =
+                    ptx::mbar_wait_bounded(ptx::smem_u32(&empty_bar[stage]), phase ^ 1u, abort_p);
+                if (!__all_sync(0xffffffffu, w)) {
+                    ok = false;
+                    break;
+                }
+                const uint32_t sA = smem0 + stage * stage_bytes;
+                const uint32_t sB = sA + A_TILE;
+                const uint32_t lo_off = A_TILE + b_tile;
+                // A tile: kBM lines
+                {
+                    uint4 v[kBM / 32];
+#pragma unroll
+                    for (int q = 0; q < kBM / 32; ++q) {
+                        const int L = l0 + 32 * q;
+                        if (p.a.im2col) {
+                            v[q] = load_chunk_im2col<ES>(p, table, a_boff, kb * BK + (L % BK),
+                                                         (L / BK) * E + c * CPE);
+                        } else if (p.a.k_major) {
+                            v[q] = load_chunk_dense<ES>(p.a, a_boff, m0 + L, p.M, kb * BK + c * CPE,
+                                                        p.K);
+                        } else {
+                            v[q] = load_chunk_dense<ES>(p.a, a_boff, kb * BK + (L % BK), p.K,
+                                                        m0 + (L / BK) * E + c * CPE, p.M);
+                        }
+                    }
+#pragma unroll
+                    for (int q = 0; q < kBM / 32; ++q)
+                        store_chunk<ES>(sA, sA + lo_off, l0 + 32 * q, c, v[q]);
+                }
+                // B tile: BN lines, four at a time
+                for (int q0 = 0; q0 < BN / 32; q0 += 4) {
+                    uint4 v[4];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const int L = l0 + 32 * (q0 + q);
+                        if (q0 + q >= BN / 32) {
+                            v[q] = make_uint4(0u, 0u, 0u, 0u);
+                        } else if (p.b.k_major) {
+                            v[q] = load_chunk_dense<ES>(p.b, b_boff, n0 + L, p.N, kb * BK + c * CPE,
+                                                        p.K);
+                        } else {
+                            v[q] = load_chunk_dense<ES>(p.b, b_boff, kb * BK + (L % BK), p.K,
+                                                        n0 + (L / BK) * E + c * CPE, p.N);
+                        }
+                    }
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        if (q0 + q < BN / 32)
+                            store_chunk<ES>(sB, sB + lo_off, l0 + 32 * (q0 + q), c, v[q]);
+                }
+                ptx::fence_proxy_async_smem();
+                ptx::mbar_arrive(ptx::smem_u32(&full_bar[stage]));
+                if (++stage == static_cast<uint32_t>(S)) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (*abort_p) {
+        // Give copies and UMMAs still in flight time to land before shared memory and
+        // TMEM are released.
+        for (int i = 0; i < 200; ++i) __nanosleep(1000);
+        if (threadIdx.x == 0) atomicOr(p.status, DEV_STATUS_WAIT_TIMEOUT);
+        __syncthreads();
+    }
+    if (warp == kMmaWarp) {
+        __syncwarp();
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc(tmem_base, tmem_cols);
+    }
+}
+
+}  // namespace dlfb200

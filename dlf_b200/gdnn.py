@@ -1,0 +1,98 @@
+"""Host-side mirror of ``gpgpu::dnn::conv2d`` (gpgpu/include/gdnn.h:201-213) plus the
+``Filter2D`` geometry of dlf/include/tensor/dnn.h:9-122 that its callers use.
+
+``conv2d`` keeps the reference's argument order. One argument is added at the end: ``bias``
+(``num_kernels`` values), which the reference applies as a separate pass over Y
+(``ConvOp::evaluate``, dlf/include/predict.h:1272-1281) and this backend folds into the
+convolution's epilogue.
+"""
+import ctypes
+
+from . import lib
+from .gblas import BLASError, StatusCode, _check, _ptr, _stream, precision_of
+
+
+class Filter2D:
+    """Geometry of a 2-D filter: NCHW input, OIHW kernel (dnn.h:9-122)."""
+
+    def __init__(self, input_shape, kernel_shape, group=1):
+        self.batches, self.channels, self.height, self.width = map(int, input_shape)
+        self.num_kernels, cpg, self.kernel_h, self.kernel_w = map(int, kernel_shape)
+        self.group = int(group)
+        if cpg * self.group != self.channels:
+            raise ValueError("kernel channels * group != input channels")
+        self.pad_top = self.pad_left = self.pad_bottom = self.pad_right = 0
+        self.stride_h = self.stride_w = 1
+        self.dilation_h = self.dilation_w = 1
+
+    def pads(self, *p):
+        if len(p) == 2:
+            self.pad_top = self.pad_bottom = int(p[0])
+            self.pad_left = self.pad_right = int(p[1])
+        else:
+            self.pad_top, self.pad_left, self.pad_bottom, self.pad_right = map(int, p)
+        return self
+
+    def strides(self, h, w):
+        self.stride_h, self.stride_w = int(h), int(w)
+        return self
+
+    def dilations(self, h, w):
+        self.dilation_h, self.dilation_w = int(h), int(w)
+        return self
+
+    @property
+    def output_h(self):  # dnn.h:99-103
+        size = self.height + self.pad_top + self.pad_bottom
+        ext = self.dilation_h * (self.kernel_h - 1) + 1
+        return (size - ext) // self.stride_h + 1 if size >= ext else 1
+
+    @property
+    def output_w(self):  # dnn.h:105-109
+        size = self.width + self.pad_left + self.pad_right
+        ext = self.dilation_w * (self.kernel_w - 1) + 1
+        return (size - ext) // self.stride_w + 1 if size >= ext else 1
+
+    def output_shape(self):
+        return (self.batches, self.num_kernels, self.output_h, self.output_w)
+
+
+def conv2d(batches, channels, height, width, output_h, output_w, num_kernels, group, kernel_h,
+           kernel_w, pad_top, pad_left, pad_bottom, pad_right, stride_h, stride_w, dilation_h,
+           dilation_w, im_buffer, kernel_buffer, result_buffer, queue=None, event=None, bias=None):
+    """NCHW cross-correlation into result_buffer (gpgpu::dnn::conv2d, gdnn.h:201-213)."""
+    prec = precision_of(result_buffer)
+    if im_buffer.dtype != result_buffer.dtype or kernel_buffer.dtype != result_buffer.dtype:
+        raise BLASError(StatusCode.kInvalidValue)
+    if bias is not None and bias.dtype != result_buffer.dtype:
+        raise BLASError(StatusCode.kInvalidValue)
+    if group < 1 or channels % group or num_kernels % group:
+        raise BLASError(StatusCode.kInvalidDimension)
+    if im_buffer.numel() < batches * channels * height * width:
+        raise BLASError(StatusCode.kInsufficientMemoryA)
+    if kernel_buffer.numel() < num_kernels * (channels // group) * kernel_h * kernel_w:
+        raise BLASError(StatusCode.kInsufficientMemoryB)
+    if result_buffer.numel() < batches * num_kernels * output_h * output_w:
+        raise BLASError(StatusCode.kInsufficientMemoryC)
+    if bias is not None and bias.numel() < num_kernels:
+        raise BLASError(StatusCode.kInvalidValue)
+    s, sp = _stream(queue)
+    if event is not None:
+        event.start.record(s)
+    rc = lib().dlf_b200_conv2d(
+        int(prec), batches, channels, height, width, output_h, output_w, num_kernels, group,
+        kernel_h, kernel_w, pad_top, pad_left, pad_bottom, pad_right, stride_h, stride_w,
+        dilation_h, dilation_w, _ptr(im_buffer), _ptr(kernel_buffer),
+        _ptr(bias) if bias is not None else ctypes.c_void_p(0), _ptr(result_buffer),
+        ctypes.c_void_p(0), 0, sp)
+    if event is not None:
+        event.end.record(s)
+    _check(rc)
+
+
+def conv2d_filter(X, W, Y, filt, bias=None, queue=None, event=None):
+    """dlf::dnn::conv2d(X, W, Y, filter) for device tensors (dlf/include/tensor/dnn_detail.h:154-166)."""
+    conv2d(filt.batches, filt.channels, filt.height, filt.width, filt.output_h, filt.output_w,
+           filt.num_kernels, filt.group, filt.kernel_h, filt.kernel_w, filt.pad_top,
+           filt.pad_left, filt.pad_bottom, filt.pad_right, filt.stride_h, filt.stride_w,
+           filt.dilation_h, filt.dilation_w, X, W, Y, queue=queue, event=event, bias=bias)

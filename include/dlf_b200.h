@@ -1,0 +1,112 @@
+/* dlf_b200.h - C ABI of the B200 (sm_100a) dense-contraction backend for dlf's gpgpu layer.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream (as void*), launches
+ * asynchronously on that stream and returns an int:
+ *     0                      success (gpgpu::blas::StatusCode::kSuccess)
+ *     negative               a gpgpu::blas::StatusCode value (gpgpu/include/gblas.h:43-107)
+ *     positive               a cudaError_t from the CUDA runtime
+ * Nothing throws. The C++ shim in dlf_b200_gpgpu.hpp turns a non-zero return into the
+ * exception the reference raises for the same mistake.
+ *
+ * Enumerations reuse the reference's integer values:
+ *     layout     101 RowMajor, 102 ColMajor              (gblas.h:110)
+ *     transpose  111 NoTrans, 112 Trans, 113 ConjTrans   (gblas.h:111)
+ *     dtype      16 Half, 32 Single                      (Precision, gblas.h:118-123)
+ *                1600 bfloat16 (an addition: the reference has no bf16 type)
+ * Matrix pointers are "buffer + offset" already resolved by the caller, exactly what the
+ * reference passes to its cuBLAS calls (gpgpu/src/gblas.cpp:1928-1930). Leading dimensions,
+ * strides and offsets are counted in elements. alpha / beta are passed by pointer in the
+ * storage type of the matrices (host memory).
+ */
+#ifndef DLF_B200_H_
+#define DLF_B200_H_
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+    DLF_B200_ROW_MAJOR = 101,
+    DLF_B200_COL_MAJOR = 102,
+    DLF_B200_NO_TRANS = 111,
+    DLF_B200_TRANS = 112,
+    DLF_B200_CONJ_TRANS = 113,
+    DLF_B200_HALF = 16,
+    DLF_B200_SINGLE = 32,
+    DLF_B200_BFLOAT16 = 1600
+};
+
+/* C = alpha * op(A) * op(B) + beta * C.
+ * Replaces gpgpu::blas::gemm<T> (gpgpu/include/gblas.h:496-504; cuBLAS call site
+ * gpgpu/src/gblas.cpp:1926-1951; OpenCL routine gpgpu/src/routines/level3/xgemm.cpp:53-99).
+ * beta == 0 never reads C. */
+int dlf_b200_gemm(int dtype, int layout, int trans_a, int trans_b, size_t m, size_t n, size_t k,
+                  const void* alpha, const void* a, size_t a_ld, const void* b, size_t b_ld,
+                  const void* beta, void* c, size_t c_ld, void* stream);
+
+/* Same product for batch_count matrices spaced by fixed strides; a stride of 0 shares one
+ * operand between all batches. Replaces gpgpu::blas::gemmStridedBatched<T>
+ * (gblas.h:673-683; gblas.cpp:3090-3141; routines/levelx/xgemmstridedbatched.cpp:53-95). */
+int dlf_b200_gemm_strided_batched(int dtype, int layout, int trans_a, int trans_b, size_t m,
+                                  size_t n, size_t k, const void* alpha, const void* a,
+                                  size_t a_ld, size_t a_stride, const void* b, size_t b_ld,
+                                  size_t b_stride, const void* beta, void* c, size_t c_ld,
+                                  size_t c_stride, size_t batch_count, void* stream);
+
+/* Batched product with per-batch alpha / beta and per-batch element offsets, all given as host
+ * arrays of batch_count entries, as in gpgpu::blas::gemmBatched<T> (gblas.h:661-671;
+ * gblas.cpp:2928-3012; routines/levelx/xgemmbatched.cpp:51-118). a, b, c are the buffer bases.
+ * The tables are copied into `workspace` (device memory, at least
+ * dlf_b200_gemm_batched_workspace_bytes(batch_count) bytes, owned by the caller, e.g. taken from
+ * gpgpu's TemporaryBuffer pool) on the given stream before the kernel runs. */
+int dlf_b200_gemm_batched(int dtype, int layout, int trans_a, int trans_b, size_t m, size_t n,
+                          size_t k, const void* alphas, const void* a, const size_t* a_offsets,
+                          size_t a_ld, const void* b, const size_t* b_offsets, size_t b_ld,
+                          const void* betas, void* c, const size_t* c_offsets, size_t c_ld,
+                          size_t batch_count, void* workspace, size_t workspace_bytes,
+                          void* stream);
+size_t dlf_b200_gemm_batched_workspace_bytes(size_t batch_count);
+
+/* NCHW cross-correlation Y = conv2d(X, W) (+ bias), computed as an implicit GEMM: no im2col
+ * buffer is materialised. X is {batches, channels, height, width}, W is
+ * {num_kernels, channels/group, kernel_h, kernel_w}, Y is {batches, num_kernels, output_h,
+ * output_w}; (pad_top, pad_left) is the origin shift, pad_bottom / pad_right only enter through
+ * output_h / output_w, as in dlf (dlf/include/tensor/dnn.h:92-109).
+ * Replaces gpgpu::dnn::conv2d<T> (gpgpu/include/gdnn.h:201-213; gpgpu/src/gdnn.cpp:1577-1630).
+ * `bias` (num_kernels entries, storage type) may be NULL; when given it is added in the
+ * epilogue, replacing the separate transformChannel pass of ConvOp
+ * (dlf/include/predict.h:1272-1281). workspace may be NULL: the kernel needs none. */
+int dlf_b200_conv2d(int dtype, size_t batches, size_t channels, size_t height, size_t width,
+                    size_t output_h, size_t output_w, size_t num_kernels, size_t group,
+                    size_t kernel_h, size_t kernel_w, size_t pad_top, size_t pad_left,
+                    size_t pad_bottom, size_t pad_right, size_t stride_h, size_t stride_w,
+                    size_t dilation_h, size_t dilation_w, const void* x, const void* w,
+                    const void* bias, void* y, void* workspace, size_t workspace_bytes,
+                    void* stream);
+size_t dlf_b200_conv2d_workspace_bytes(int dtype, size_t batches, size_t channels, size_t height,
+                                       size_t width, size_t output_h, size_t output_w,
+                                       size_t num_kernels, size_t group, size_t kernel_h,
+                                       size_t kernel_w);
+
+/* Name of a status code returned by the functions above (static storage). Mirrors the
+ * StatusCode enumerators of gblas.h:43-107. */
+const char* dlf_b200_status_string(int status);
+
+/* Synchronises the current device and reads-and-clears its kernel status word: 0 when every
+ * kernel since the last call ran to completion, non-zero when a bounded device-side wait gave
+ * up (bit 0). Kernels never trap or spin forever; this is how such a failure is reported. */
+int dlf_b200_device_status(int* device_status);
+
+/* Tuning overrides for experiments: force the N-tile width (64, 128 or 256; 0 = automatic) and
+ * force the generic (non-TMA) operand loader (1) for every following call of this process. */
+void dlf_b200_set_tuning(int force_bn, int force_generic_loader);
+
+/* Counts kernel launches made by this library in this process (all threads). */
+unsigned long long dlf_b200_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DLF_B200_H_ */
