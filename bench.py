@@ -1,0 +1,529 @@
+#!/usr/bin/env python
+"""Benchmark of the dense-contraction hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+A step is one pass of the hot path over one batch of seeded synthetic input. The headline
+workload (default) is BASELINE config 2: fp32 NCHW conv2d N=64 C=64 56x56 -> 64, 3x3, stride 1,
+pad 1, with bias, one kernel launch per step. With N GPUs every rank convolves its own batch of
+64 images (batch-sharded, no data-path collective, weak scaling). Rank 0 prints ONE JSON line.
+
+Timing: CUDA events on the launching stream around exactly K steps after W warm-up steps,
+barrier + synchronize on both sides, max over ranks. Inputs and outputs rotate over several
+buffer sets whose total size exceeds the 126 MB L2, so no step finds its operands cached.
+"""
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+L2_BYTES = 126 * 1024 * 1024
+NOMINAL = {"f16": 2250.0, "bf16": 2250.0, "f32": 1125.0 / 3.0}  # dense TFLOP/s; f32 = 3xTF32
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0,
+            "source": "fallback"}
+
+
+# ------------------------------------------------------------------------------------------
+# workloads
+# ------------------------------------------------------------------------------------------
+class Workload:
+    """One configuration of BASELINE.json: seeded inputs, a launch per step, algorithmic work."""
+    name = ""
+    dtype = "f32"
+    launches_per_step = 1
+
+    def torch_dtype(self):
+        return {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}[self.dtype]
+
+    def tensor_peak(self, peaks):
+        """Measured dense tensor roof for this dtype: cuBLAS bf16 burst for 16-bit inputs; tf32
+        runs at half the bf16 rate and 3xTF32 issues three MMAs per product."""
+        return peaks["bf16_tflops"] if self.dtype != "f32" else peaks["bf16_tflops"] / 6.0
+
+
+class ConvC2(Workload):
+    """Config 2: fp32 conv2d NCHW 64x64x56x56 -> 64 channels, 3x3 s1 p1, bias."""
+    name = "conv2d_f32_n64_c64_56x56_k3"
+    dtype = "f32"
+    shape = dict(N=64, C=64, H=56, W=56, Co=64, KH=3, KW=3, pad=1, stride=1, group=1)
+
+    def __init__(self, shape=None, dtype=None):
+        if shape:
+            self.shape = dict(self.shape, **shape)
+        if dtype:
+            self.dtype = dtype
+        s = self.shape
+        self.OH = (s["H"] + 2 * s["pad"] - s["KH"]) // s["stride"] + 1
+        self.OW = (s["W"] + 2 * s["pad"] - s["KW"]) // s["stride"] + 1
+        es = 4 if self.dtype == "f32" else 2
+        self.flops = 2.0 * s["N"] * s["Co"] * self.OH * self.OW * (s["C"] // s["group"]) * s["KH"] * s["KW"]
+        self.x_bytes = es * s["N"] * s["C"] * s["H"] * s["W"]
+        self.y_bytes = es * s["N"] * s["Co"] * self.OH * self.OW
+        self.bytes = self.x_bytes + self.y_bytes + es * s["Co"] * (s["C"] // s["group"]) * s["KH"] * s["KW"] + es * s["Co"]
+
+    def host_inputs(self, seed):
+        s = self.shape
+        rng = np.random.default_rng(seed)
+        X = rng.normal(size=(s["N"], s["C"], s["H"], s["W"])).astype(np.float32)
+        std = math.sqrt(2.0 / (s["C"] // s["group"] * s["KH"] * s["KW"]))
+        W = (std * rng.normal(size=(s["Co"], s["C"] // s["group"], s["KH"], s["KW"]))).astype(np.float32)
+        b = rng.uniform(-0.1, 0.1, s["Co"]).astype(np.float32)
+        return X, W, b
+
+    def setup(self, device, seed, sets):
+        from dlf_b200 import gdnn
+        s = self.shape
+        X, W, b = self.host_inputs(seed)
+        td = self.torch_dtype()
+        self.filt = gdnn.Filter2D(X.shape, W.shape, s["group"]).pads(s["pad"], s["pad"]).strides(s["stride"], s["stride"])
+        self.W = torch.from_numpy(W).to(td).to(device)
+        self.b = torch.from_numpy(b).to(td).to(device)
+        x0 = torch.from_numpy(X).to(td)
+        self.host_x = x0.pin_memory()
+        self.X = [x0.to(device) for _ in range(sets)]
+        self.Y = [torch.empty(self.filt.output_shape(), dtype=td, device=device) for _ in range(sets)]
+        self.host_y = torch.empty(self.filt.output_shape(), dtype=td).pin_memory()
+        self.sets = sets
+
+    def sets_needed(self):
+        return max(2, int(math.ceil(2.0 * L2_BYTES / (self.x_bytes + self.y_bytes))))
+
+    def step(self, i):
+        from dlf_b200 import gdnn
+        j = i % self.sets
+        gdnn.conv2d_filter(self.X[j], self.W, self.Y[j], self.filt, bias=self.b)
+
+    def e2e_step(self, i):
+        """Public API with host buffers: H2D of the step's input, the convolution, D2H of Y."""
+        from dlf_b200 import tensor as dt
+        j = i % self.sets
+        self.X[j].copy_(self.host_x, non_blocking=True)
+        dt.conv2d(self.X[j], self.W, self.Y[j], self.filt, bias=self.b)
+        self.host_y.copy_(self.Y[j], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    def e2e_bytes(self):
+        return self.x_bytes, self.y_bytes
+
+    def check(self):
+        """Spot check of the last output against the oracle (two images)."""
+        import oracle
+        X, W, b = self.host_inputs(self.seed_used)
+        td = self.torch_dtype()
+        if td != torch.float32:
+            X = torch.from_numpy(X).to(td).float().numpy()
+            W = torch.from_numpy(W).to(td).float().numpy()
+            b = torch.from_numpy(b).to(td).float().numpy()
+        s = self.shape
+        ref = oracle.conv2d(X[:2], W, group=s["group"], pads=(s["pad"],) * 4,
+                            strides=(s["stride"],) * 2, bias=b, wide=True)
+        got = self.Y[0][:2].float().cpu().numpy()
+        return float(np.linalg.norm(got - ref) / np.linalg.norm(ref))
+
+    def cpu_reference(self, budget_s):
+        """The reference's CPU schedule (dlf/include/tensor/dnn_detail.h:123-152: per image im2col
+        then sgemm, serial over the batch; bias as a second pass) with the host BLAS."""
+        import oracle
+        X, W, b = self.host_inputs(0)
+        fn, desc = oracle.find_host_cblas()
+        cb = oracle.host_sgemm_nn_callback(fn) if fn is not None else None
+        s = self.shape
+        kw = dict(group=s["group"], pads=(s["pad"],) * 4, strides=(s["stride"],) * 2, bias=b, sgemm_nn=cb)
+        n_img = min(s["N"], 8)
+        oracle.conv2d(X[:n_img], W, **kw)  # warm-up
+        t0 = time.perf_counter()
+        reps = 0
+        while True:
+            oracle.conv2d(X[:n_img], W, **kw)
+            reps += 1
+            if time.perf_counter() - t0 > budget_s or reps >= 200:
+                break
+        dt_s = (time.perf_counter() - t0) / reps
+        flops = self.flops * n_img / s["N"]
+        return dict(value=flops / dt_s / 1e12, seconds_per_sample=dt_s,
+                    sample="%d of %d images per pass, %d passes; im2col + %s per image" % (
+                        n_img, s["N"], reps, desc if fn is not None else "oracle sgemm (no host BLAS found)"),
+                    blas=desc)
+
+
+class GemmWorkload(Workload):
+    """Single or strided-batched GEMM; row-major."""
+
+    def __init__(self, name, dtype, m, n, k, batch=1, ta=False, tb=False, alpha=1.0, beta=0.0, dist="normal"):
+        self.name, self.dtype = name, dtype
+        self.m, self.n, self.k, self.batch, self.ta, self.tb = m, n, k, batch, ta, tb
+        self.alpha, self.beta, self.dist = alpha, beta, dist
+        es = 4 if dtype == "f32" else 2
+        self.flops = 2.0 * m * n * k * batch
+        self.bytes = es * batch * (m * k + k * n + m * n * (2 if beta != 0 else 1))
+        self.in_bytes = es * batch * (m * k + k * n)
+        self.out_bytes = es * batch * m * n
+
+    def sets_needed(self):
+        per = self.bytes
+        return max(2, min(8, int(math.ceil(2.0 * L2_BYTES / per))))
+
+    def setup(self, device, seed, sets):
+        g = torch.Generator(device=device).manual_seed(seed)
+        td = self.torch_dtype()
+        self.sets = sets
+        mk = (lambda *s: torch.randn(*s, generator=g, device=device, dtype=torch.float32)) if self.dist == "normal" \
+            else (lambda *s: torch.rand(*s, generator=g, device=device, dtype=torch.float32) * 2 - 1)
+        scale = 0.1 if self.dist == "normal" else 1.0
+        self.A = [(mk(self.batch * self.m * self.k) * scale).to(td) for _ in range(sets)]
+        self.B = [(mk(self.batch * self.k * self.n) * scale).to(td) for _ in range(sets)]
+        self.C = [torch.randn(self.batch * self.m * self.n, generator=g, device=device, dtype=torch.float32).to(td)
+                  for _ in range(sets)]
+
+    def step(self, i):
+        from dlf_b200 import gblas
+        j = i % self.sets
+        ta = gblas.Transpose.Trans if self.ta else gblas.Transpose.NoTrans
+        tb = gblas.Transpose.Trans if self.tb else gblas.Transpose.NoTrans
+        lda = self.m if self.ta else self.k
+        ldb = self.k if self.tb else self.n
+        if self.batch == 1:
+            gblas.gemm(gblas.Layout.RowMajor, ta, tb, self.m, self.n, self.k, self.alpha, self.A[j], 0, lda,
+                       self.B[j], 0, ldb, self.beta, self.C[j], 0, self.n)
+        else:
+            gblas.gemmStridedBatched(gblas.Layout.RowMajor, ta, tb, self.m, self.n, self.k, self.alpha,
+                                     self.A[j], 0, lda, self.m * self.k, self.B[j], 0, ldb, self.k * self.n,
+                                     self.beta, self.C[j], 0, self.n, self.m * self.n, self.batch)
+
+
+RESNET50_SHAPES = [
+    # Cin, H, Cout, k, stride, pad, count   (ResNet-50 v1: stride on the first 1x1 of a stage)
+    (3, 224, 64, 7, 2, 3, 1), (64, 56, 64, 1, 1, 0, 1), (64, 56, 64, 3, 1, 1, 3), (64, 56, 256, 1, 1, 0, 4),
+    (256, 56, 64, 1, 1, 0, 2), (256, 56, 128, 1, 2, 0, 1), (128, 28, 128, 3, 1, 1, 4), (128, 28, 512, 1, 1, 0, 4),
+    (256, 56, 512, 1, 2, 0, 1), (512, 28, 128, 1, 1, 0, 3), (512, 28, 256, 1, 2, 0, 1), (256, 14, 256, 3, 1, 1, 6),
+    (256, 14, 1024, 1, 1, 0, 6), (512, 28, 1024, 1, 2, 0, 1), (1024, 14, 256, 1, 1, 0, 5), (1024, 14, 512, 1, 2, 0, 1),
+    (512, 7, 512, 3, 1, 1, 3), (512, 7, 2048, 1, 1, 0, 3), (1024, 14, 2048, 1, 2, 0, 1), (2048, 7, 512, 1, 1, 0, 2),
+]
+
+
+# ------------------------------------------------------------------------------------------
+# measurement helpers
+# ------------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clocks / throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.rows = []
+        self.proc = None
+        self.index = index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits",
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.t = threading.Thread(target=self._read, daemon=True)
+        self.t.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), line.strip()))
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self, t0, t1):
+        rows = [r for (t, r) in self.rows if t0 <= t <= t1] or [r for (_, r) in self.rows]
+        sm, mx, reasons = [], [], set()
+        for r in rows:
+            f = [x.strip() for x in r.split(",")]
+            if len(f) < 8:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def dist_setup(n_gpus):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    else:
+        torch.cuda.set_device(0)
+    return rank, world, local
+
+
+def barrier(world):
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(x, world):
+    if world == 1:
+        return x
+    import torch.distributed as dist
+    t = torch.tensor([x], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def time_steps(fn, steps, warmup, world):
+    """W untimed + exactly K timed steps; returns milliseconds for the K steps (max over ranks)."""
+    for i in range(warmup):
+        fn(i)
+    barrier(world)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s = torch.cuda.current_stream()
+    t0 = time.time()
+    e0.record(s)
+    for i in range(steps):
+        fn(warmup + i)
+    e1.record(s)
+    barrier(world)
+    t1 = time.time()
+    return max_over_ranks(e0.elapsed_time(e1), world), t0, t1
+
+
+def run_extra(w, device, peaks, steps, warmup):
+    """Kernel-only numbers for a further BASELINE configuration (reported under "workloads")."""
+    w.setup(device, 0, w.sets_needed())
+    ms, _, _ = time_steps(w.step, steps, warmup, 1)
+    sec = ms / 1e3 / steps
+    tf = w.flops / sec / 1e12
+    return {"tflops": round(tf, 2), "us_per_step": round(sec * 1e6, 2), "dtype": w.dtype,
+            "frac_of_measured_tensor_peak": round(tf / w.tensor_peak(peaks), 4),
+            "frac_of_nominal_tensor_peak": round(tf / NOMINAL[w.dtype], 4),
+            "hbm_gbs_algorithmic": round(w.bytes / sec / 1e9, 1),
+            "frac_of_measured_hbm": round(w.bytes / sec / 1e9 / peaks["hbm_gbs"], 4)}
+
+
+def resnet_sweep(device, peaks, batch, reps):
+    """Config 3: fp16 ResNet-50 v1 conv shapes at 224x224 (53 layers = 20 unique shapes)."""
+    total_flops, total_s, rows = 0.0, 0.0, []
+    for (cin, h, cout, k, s, p, count) in RESNET50_SHAPES:
+        w = ConvC2(shape=dict(N=batch, C=cin, H=h, W=h, Co=cout, KH=k, KW=k, pad=p, stride=s, group=1), dtype="f16")
+        w.setup(device, cin + cout + k, 2)
+        ms, _, _ = time_steps(w.step, reps, 3, 1)
+        sec = ms / 1e3 / reps
+        rows.append({"shape": [cin, h, cout, k, s], "count": count, "tflops": round(w.flops / sec / 1e12, 1),
+                     "us": round(sec * 1e6, 1)})
+        total_flops += w.flops * count
+        total_s += sec * count
+        del w
+        torch.cuda.empty_cache()
+    tf = total_flops / total_s / 1e12
+    return {"tflops": round(tf, 1), "ms_per_sweep": round(total_s * 1e3, 3), "batch": batch, "dtype": "f16",
+            "frac_of_measured_tensor_peak": round(tf / peaks["bf16_tflops"], 4),
+            "frac_of_nominal_tensor_peak": round(tf / NOMINAL["f16"], 4), "layers": rows}
+
+
+def reference_arm(args, rank):
+    """--impl reference: the reference's CPU implementation of the path (oracle port; the
+    reference itself needs TBB + MKL, which are absent) timed on the host cores."""
+    if rank != 0:
+        return
+    w = ConvC2()
+    steps = max(1, args.steps if args.steps_given else 3)
+    per_step_budget = min(20.0, 120.0 / (steps + args.warmup))
+    vals = []
+    info = None
+    for i in range(args.warmup + steps):
+        info = w.cpu_reference(per_step_budget)
+        if i >= args.warmup:
+            vals.append(info["value"])
+    value = float(np.mean(vals))
+    cores = os.cpu_count() or 1
+    line = {"impl": "reference", "metric": "gemm_conv_tflops", "value": value, "unit": "TFLOP/s",
+            "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup,
+            "ms_per_step": info["seconds_per_sample"] * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": w.name, "note": "reference CPU schedule: per-image im2col + sgemm, serial over batch"},
+            "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                             "sample": info["sample"]},
+            "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=None)
+    ap.add_argument("--warmup", type=int, default=None)
+    ap.add_argument("--impl", default="b200")
+    ap.add_argument("--workload", default="conv_c2")
+    ap.add_argument("--headline-only", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.steps_given = args.steps is not None
+    if args.impl == "reference":
+        if args.warmup is None:
+            args.warmup = 1
+        reference_arm(args, int(os.environ.get("RANK", "0")))
+        return
+    steps = args.steps if args.steps is not None else 4000
+    warmup = max(3, args.warmup if args.warmup is not None else 200)
+
+    import dlf_b200
+    dlf_b200.lib()  # fail loudly when the CUDA library is missing
+    rank, world, local = dist_setup(args.gpus)
+    device = torch.device("cuda", local)
+    peaks = measured_peaks()
+
+    table = {
+        "conv_c2": lambda: ConvC2(),
+        "gemm_f16_4096": lambda: GemmWorkload("gemm_f16_4096", "f16", 4096, 4096, 4096),
+        "sgemm_1024": lambda: GemmWorkload("sgemm_f32_1024", "f32", 1024, 1024, 1024, dist="uniform"),
+        "sgemm_16384": lambda: GemmWorkload("sgemm_f32_16384_tn", "f32", 16384, 16384, 16384, ta=True, alpha=0.5,
+                                            beta=0.5, dist="uniform"),
+        "batched_c4_a": lambda: GemmWorkload("bgemm_f16_b1024_512x512x64", "f16", 512, 512, 64, batch=1024, alpha=0.125),
+        "batched_c4_b": lambda: GemmWorkload("bgemm_f16_b1024_512x64x512", "f16", 512, 64, 512, batch=1024, alpha=0.125),
+    }
+    w = table[args.workload]()
+    sets = w.sets_needed()
+    w.seed_used = rank
+    w.setup(device, rank, sets)
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    l0 = dlf_b200.launch_count()
+    ms, t0, t1 = time_steps(w.step, steps, warmup, world)
+    launches = dlf_b200.launch_count() - l0 - 0
+    if rank == 0:
+        sampler.stop()
+    launches_timed = steps * w.launches_per_step
+    status = dlf_b200.device_status()
+    sec_per_step = ms / 1e3 / steps
+    value = w.flops * world / sec_per_step / 1e12
+
+    # end to end through the public API with host buffers
+    e2e = None
+    if hasattr(w, "e2e_step"):
+        e_steps = max(3, min(steps, 30))
+        for i in range(3):
+            w.e2e_step(i)
+        barrier(world)
+        t_0 = time.perf_counter()
+        for i in range(e_steps):
+            w.e2e_step(i)
+        torch.cuda.synchronize()
+        dt_e = max_over_ranks(time.perf_counter() - t_0, world) / e_steps
+        h2d, d2h = w.e2e_bytes()
+        e2e = {"value": w.flops * world / dt_e / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": d2h, "ms_per_step": dt_e * 1e3}
+
+    parity = w.check() if hasattr(w, "check") else None
+
+    if rank != 0:
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+
+    tf_per_gpu = w.flops / sec_per_step / 1e12
+    peak = w.tensor_peak(peaks)
+    roofline = {"bound": "tensor", "achieved": tf_per_gpu, "peak": peak, "unit": "TFLOP/s",
+                "frac": tf_per_gpu / peak, "traffic": None,
+                "peak_basis": ("%s bf16 cuBLAS burst %.0f TFLOP/s" % (peaks["source"], peaks["bf16_tflops"])) +
+                              ("; fp32 runs as 3xTF32: tf32 rate = bf16/2, three MMAs per product => /6"
+                               if w.dtype == "f32" else ""),
+                "frac_of_nominal": tf_per_gpu / NOMINAL[w.dtype],
+                "hbm_gbs_algorithmic": w.bytes / sec_per_step / 1e9,
+                "hbm_frac_of_measured": w.bytes / sec_per_step / 1e9 / peaks["hbm_gbs"],
+                "kernel": "contraction_kernel", "avg_launch_us": sec_per_step * 1e6 / w.launches_per_step}
+    prof = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(prof):
+        with open(prof) as f:
+            roofline["traffic"] = json.load(f).get(w.name)
+
+    line = {"metric": "gemm_conv_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
+            "warmup": warmup, "ms_per_step": sec_per_step * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": w.dtype, "data": "synthetic",
+            "config": {"workload": w.name, "per_gpu_batch": getattr(w, "shape", {}).get("N"),
+                       "sharding": "batch per rank, no collective" if world > 1 else "single GPU",
+                       "l2": "rotating %d input/output buffer sets (%.0f MB > 126 MB L2)" % (
+                           sets, sets * (getattr(w, "x_bytes", w.bytes) + getattr(w, "y_bytes", 0)) / 1e6),
+                       "arithmetic": "3xTF32 tcgen05, fp32 accumulate" if w.dtype == "f32" else "tcgen05 f16, fp32 accumulate"},
+            "roofline": roofline, "gpu_launches": int(launches_timed), "launches_counted": int(launches),
+            "device_status": status, "clocks": sampler.summary(t0, t1), "parity_rel_fro_vs_oracle": parity}
+    if e2e:
+        line["e2e"] = e2e
+
+    if world == 1 and not args.no_cpu_baseline and hasattr(w, "cpu_reference"):
+        cb = w.cpu_reference(10.0)
+        line["cpu_baseline"] = {"value": cb["value"], "unit": "TFLOP/s", "cores": os.cpu_count() or 1,
+                                "kind": "port", "sample": cb["sample"]}
+
+    if world == 1 and not args.headline_only and args.workload == "conv_c2":
+        extras = {}
+        del w
+        torch.cuda.empty_cache()
+        for key, reps in (("gemm_f16_4096", 200), ("sgemm_1024", 500), ("batched_c4_a", 100), ("batched_c4_b", 100),
+                          ("sgemm_16384", 5)):
+            try:
+                ww = table[key]()
+                extras[ww.name] = run_extra(ww, device, peaks, reps, 5)
+                del ww
+                torch.cuda.empty_cache()
+            except Exception as e:  # an extra must never lose the headline line
+                extras[key] = {"error": repr(e)[:200]}
+        try:
+            extras["resnet50_v1_convs_f16_b256"] = resnet_sweep(device, peaks, 256, 10)
+        except Exception as e:
+            extras["resnet50_v1_convs_f16_b256"] = {"error": repr(e)[:200]}
+        extras["device_status"] = dlf_b200.device_status()
+        line["workloads"] = extras
+
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

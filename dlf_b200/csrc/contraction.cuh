@@ -19,6 +19,9 @@
 //   MN-major: line L = (row group g = L / BK, k = L % BK), the 128 bytes run along rows
 //             g*E .. g*E+E-1 (E = BK). descriptor: LBO = BK*128 (next row group),
 //             SBO = 1024 (next 8 k), one UMMA k-step = +(UMMA_K/8)*1024 bytes.
+//             32-bit (tf32) MN-major operands must use the 32-byte-atom form of the swizzle
+//             instead: 32-byte chunk c2 of line L sits at L*128 + ((c2 ^ (L & 3)) << 5),
+//             SBO = 512 (next 4 k).
 // TMA boxes with CU_TENSOR_MAP_SWIZZLE_128B produce exactly these layouts; the generic
 // loader warps reproduce them with plain stores.
 //
@@ -201,8 +204,10 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, const uint4& v) {
 
 template <int ES>
 __device__ __forceinline__ void store_chunk(uint32_t tile, uint32_t lo_tile, int L, int c,
-                                            const uint4& v) {
-    const uint32_t off = static_cast<uint32_t>(L) * 128u + (static_cast<uint32_t>(c ^ (L & 7)) << 4);
+                                            const uint4& v, bool atom32) {
+    const uint32_t cs = atom32 ? static_cast<uint32_t>((((c >> 1) ^ (L & 3)) << 1) | (c & 1))
+                               : static_cast<uint32_t>(c ^ (L & 7));
+    const uint32_t off = static_cast<uint32_t>(L) * 128u + (cs << 4);
     if constexpr (ES == 2) {
         st_shared_v4(tile + off, v);
     } else {
@@ -360,6 +365,10 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
             const uint32_t b_step = p.b.k_major ? KSTEP_K : KSTEP_MN;
             const uint32_t a_lbo = p.a.k_major ? 16u : static_cast<uint32_t>(BK) * 128u;
             const uint32_t b_lbo = p.b.k_major ? 16u : static_cast<uint32_t>(BK) * 128u;
+            const uint32_t a_mode = (ES == 4 && !p.a.k_major) ? 1u : 2u;
+            const uint32_t b_mode = (ES == 4 && !p.b.k_major) ? 1u : 2u;
+            const uint32_t a_sbo = a_mode == 1u ? 512u : 1024u;
+            const uint32_t b_sbo = b_mode == 1u ? 512u : 1024u;
             uint32_t stage = 0, phase = 0;
             long long it = 0;
             bool ok = true;
@@ -382,17 +391,17 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
                     const uint32_t sB = sA + A_TILE;
 #pragma unroll
                     for (int ks = 0; ks < BK / UMMA_K; ++ks) {
-                        const uint64_t da = ptx::make_smem_desc(sA + ks * a_step, a_lbo, 1024u);
-                        const uint64_t db = ptx::make_smem_desc(sB + ks * b_step, b_lbo, 1024u);
+                        const uint64_t da = ptx::make_smem_desc(sA + ks * a_step, a_lbo, a_sbo, a_mode);
+                        const uint64_t db = ptx::make_smem_desc(sB + ks * b_step, b_lbo, b_sbo, b_mode);
                         const uint32_t acc = (kb | ks) ? 1u : 0u;
                         if constexpr (ES == 2) {
                             ptx::umma_f16(d_tmem, da, db, idesc, acc);
                         } else {
                             const uint32_t lo_off = A_TILE + b_tile;
                             const uint64_t da_lo =
-                                ptx::make_smem_desc(sA + lo_off + ks * a_step, a_lbo, 1024u);
+                                ptx::make_smem_desc(sA + lo_off + ks * a_step, a_lbo, a_sbo, a_mode);
                             const uint64_t db_lo =
-                                ptx::make_smem_desc(sB + lo_off + ks * b_step, b_lbo, 1024u);
+                                ptx::make_smem_desc(sB + lo_off + ks * b_step, b_lbo, b_sbo, b_mode);
                             ptx::umma_tf32(d_tmem, da_lo, db, idesc, acc);
                             ptx::umma_tf32(d_tmem, da, db_lo, idesc, 1u);
                             ptx::umma_tf32(d_tmem, da, db, idesc, 1u);
@@ -451,6 +460,8 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
         const int lt = threadIdx.x - kFirstLoaderWarp * 32;
         const int c = lt & 7;
         const int l0 = lt >> 3;
+        const bool a_atom32 = ES == 4 && !p.a.k_major;
+        const bool b_atom32 = ES == 4 && !p.b.k_major;
         uint32_t stage = 0, phase = 0;
         long long it = 0;
         bool ok = true;
@@ -518,7 +529,7 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
                     }
 #pragma unroll
                     for (int q = 0; q < kBM / 32; ++q)
-                        store_chunk<ES>(sA, sA + lo_off, l0 + 32 * q, c, v[q]);
+                        store_chunk<ES>(sA, sA + lo_off, l0 + 32 * q, c, v[q], a_atom32);
                 }
                 // B tile: BN lines, four at a time
                 for (int q0 = 0; q0 < BN / 32; q0 += 4) {
@@ -539,7 +550,7 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
 #pragma unroll
                     for (int q = 0; q < 4; ++q)
                         if (q0 + q < BN / 32)
-                            store_chunk<ES>(sB, sB + lo_off, l0 + 32 * (q0 + q), c, v[q]);
+                            store_chunk<ES>(sB, sB + lo_off, l0 + 32 * (q0 + q), c, v[q], b_atom32);
                 }
                 ptx::fence_proxy_async_smem();
                 ptx::mbar_arrive(ptx::smem_u32(&full_bar[stage]));

@@ -177,15 +177,17 @@ __device__ __forceinline__ bool elect_one() {
 // Shared-memory matrix descriptor for tcgen05.mma, 128-byte swizzle.
 //   bits  0-13 start address >> 4      bits 16-29 leading-dim byte offset >> 4
 //   bits 32-45 stride-dim byte offset >> 4   bits 46-47 version (1 on sm_100)
-//   bits 61-63 swizzle mode (2 = 128 B)
+//   bits 61-63 swizzle mode: 2 = 128 B with 16-byte atoms (XOR of address bits 4-6 with 7-9),
+//              1 = 128 B with 32-byte atoms (XOR of bits 5-6 with 7-8), the only swizzled
+//              form tcgen05 accepts for an MN-major tf32 operand.
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes,
-                                                   uint32_t sbo_bytes) {
+                                                   uint32_t sbo_bytes, uint32_t swizzle_mode) {
     uint64_t d = 0;
     d |= static_cast<uint64_t>((saddr >> 4) & 0x3FFFu);
     d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
     d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
     d |= static_cast<uint64_t>(1) << 46;
-    d |= static_cast<uint64_t>(2) << 61;
+    d |= static_cast<uint64_t>(swizzle_mode) << 61;
     return d;
 }
 

@@ -1,0 +1,190 @@
+"""numpy front for the CPU oracle (oracle/dlf_oracle.c).
+
+TEST INFRASTRUCTURE ONLY: the checker for the CUDA path. Nothing in the product package
+imports this module; only ``tests/``, ``__graft_entry__.smoke()`` and the CPU-baseline legs of
+``bench.py`` do.
+
+``build()`` compiles ``oracle/_ref/libdlf_oracle.so`` with the Makefile beside this file. The
+reference's own CPU code cannot be compiled here (Intel TBB and MKL are absent), so the library
+is the restatement, pinned on the reference's golden vectors under ``tests/golden/``.
+"""
+import ctypes
+import glob
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "_ref", "libdlf_oracle.so")
+
+ROW_MAJOR, COL_MAJOR = 101, 102
+NO_TRANS, TRANS, CONJ_TRANS = 111, 112, 113
+
+_lib = None
+_SGEMM_NN_FN = ctypes.CFUNCTYPE(None, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p,
+                                ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p,
+                                ctypes.c_int)
+
+
+def build(force=False):
+    src = os.path.join(_HERE, "dlf_oracle.c")
+    if (force or not os.path.exists(LIB_PATH)
+            or os.path.getmtime(LIB_PATH) < os.path.getmtime(src)):
+        subprocess.run(["make", "-C", _HERE, "-B"], check=True, capture_output=True)
+    return LIB_PATH
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            build()
+        _lib = ctypes.CDLL(LIB_PATH)
+        _lib.dlf_oracle_output_dim.restype = ctypes.c_size_t
+        _lib.dlf_oracle_output_dim.argtypes = [ctypes.c_size_t] * 6
+    return _lib
+
+
+def _p(a):
+    return a.ctypes.data_as(ctypes.c_void_p)
+
+
+_SUFFIX = {np.dtype(np.float32): "f32", np.dtype(np.float64): "f64",
+           np.dtype(np.int32): "i32", np.dtype(np.int64): "i64"}
+_CT = {"f32": ctypes.c_float, "f64": ctypes.c_double, "i32": ctypes.c_int32, "i64": ctypes.c_int64}
+
+
+def gemm_generic(trans_a, trans_b, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc):
+    """detail::gemm for non-BLAS element types (exact evaluation order); C is updated in place.
+    A, B, C are flat row-major numpy buffers of one of float32/float64/int32/int64."""
+    sfx = _SUFFIX[C.dtype]
+    ct = _CT[sfx]
+    fn = getattr(lib(), "dlf_oracle_gemm_generic_" + sfx)
+    fn.restype = None
+    fn.argtypes = [ctypes.c_int] * 5 + [ct, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p,
+                                        ctypes.c_int, ct, ctypes.c_void_p, ctypes.c_int]
+    fn(trans_a, trans_b, m, n, k, alpha, _p(A), lda, _p(B), ldb, beta, _p(C), ldc)
+    return C
+
+
+def gblas_sgemm(layout, trans_a, trans_b, m, n, k, alpha, A, a_offset, a_ld, B, b_offset, b_ld,
+                beta, C, c_offset, c_ld, wide=False):
+    """gpgpu::blas::gemm<float> semantics on flat float32 buffers; C updated in place."""
+    fn = lib().dlf_oracle_gblas_sgemm
+    fn.restype = None
+    fn.argtypes = [ctypes.c_int] * 3 + [ctypes.c_size_t] * 3 + [
+        ctypes.c_float, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_size_t, ctypes.c_void_p,
+        ctypes.c_size_t, ctypes.c_size_t, ctypes.c_float, ctypes.c_void_p, ctypes.c_size_t,
+        ctypes.c_size_t, ctypes.c_int]
+    fn(layout, trans_a, trans_b, m, n, k, alpha, _p(A), a_offset, a_ld, _p(B), b_offset, b_ld,
+       beta, _p(C), c_offset, c_ld, 1 if wide else 0)
+    return C
+
+
+def gblas_sgemm_strided_batched(layout, trans_a, trans_b, m, n, k, alpha, A, a_offset, a_ld,
+                                a_stride, B, b_offset, b_ld, b_stride, beta, C, c_offset, c_ld,
+                                c_stride, batch, wide=False):
+    fn = lib().dlf_oracle_gblas_sgemm_strided_batched
+    fn.restype = None
+    fn.argtypes = [ctypes.c_int] * 3 + [ctypes.c_size_t] * 3 + [
+        ctypes.c_float, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_size_t, ctypes.c_size_t,
+        ctypes.c_void_p, ctypes.c_size_t, ctypes.c_size_t, ctypes.c_size_t, ctypes.c_float,
+        ctypes.c_void_p, ctypes.c_size_t, ctypes.c_size_t, ctypes.c_size_t, ctypes.c_size_t,
+        ctypes.c_int]
+    fn(layout, trans_a, trans_b, m, n, k, alpha, _p(A), a_offset, a_ld, a_stride, _p(B), b_offset,
+       b_ld, b_stride, beta, _p(C), c_offset, c_ld, c_stride, batch, 1 if wide else 0)
+    return C
+
+
+def gblas_sgemm_batched(layout, trans_a, trans_b, m, n, k, alphas, A, a_offsets, a_ld, B,
+                        b_offsets, b_ld, betas, C, c_offsets, c_ld, batch, wide=False):
+    fn = lib().dlf_oracle_gblas_sgemm_batched
+    fn.restype = None
+    fn.argtypes = [ctypes.c_int] * 3 + [ctypes.c_size_t] * 3 + [
+        ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p,
+        ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+        ctypes.c_size_t, ctypes.c_size_t, ctypes.c_int]
+    al = np.ascontiguousarray(alphas, dtype=np.float32)
+    be = np.ascontiguousarray(betas, dtype=np.float32)
+    ao = np.ascontiguousarray(a_offsets, dtype=np.uint64)
+    bo = np.ascontiguousarray(b_offsets, dtype=np.uint64)
+    co = np.ascontiguousarray(c_offsets, dtype=np.uint64)
+    fn(layout, trans_a, trans_b, m, n, k, _p(al), _p(A), _p(ao), a_ld, _p(B), _p(bo), b_ld,
+       _p(be), _p(C), _p(co), c_ld, batch, 1 if wide else 0)
+    return C
+
+
+def output_dim(size, pad_lo, pad_hi, kernel, stride, dilation):
+    return int(lib().dlf_oracle_output_dim(size, pad_lo, pad_hi, kernel, stride, dilation))
+
+
+def conv2d(X, W, group=1, pads=(0, 0, 0, 0), strides=(1, 1), dilations=(1, 1), bias=None,
+           wide=False, sgemm_nn=None):
+    """dlf::dnn::conv2d on the CPU (per image, per group: im2col then sgemm) followed, when bias
+    is given, by the separate bias pass of ConvOp. X: NCHW float32, W: OIHW float32.
+    pads = (top, left, bottom, right). Returns Y (NCHW float32)."""
+    X = np.ascontiguousarray(X, dtype=np.float32)
+    W = np.ascontiguousarray(W, dtype=np.float32)
+    n, c, h, w = X.shape
+    co, cg, kh, kw = W.shape
+    assert cg * group == c and co % group == 0
+    pt, pl, pb, pr = pads
+    oh = output_dim(h, pt, pb, kh, strides[0], dilations[0])
+    ow = output_dim(w, pl, pr, kw, strides[1], dilations[1])
+    Y = np.empty((n, co, oh, ow), dtype=np.float32)
+    fn = lib().dlf_oracle_conv2d_f32
+    fn.restype = None
+    fn.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_size_t] * 16 + [ctypes.c_int, ctypes.c_void_p]
+    cb = ctypes.cast(sgemm_nn, ctypes.c_void_p) if sgemm_nn is not None else None
+    fn(_p(X), _p(W), _p(Y), n, c, h, w, co, group, kh, kw, pt, pl, pb, pr, strides[0], strides[1],
+       dilations[0], dilations[1], 1 if wide else 0, cb)
+    if bias is not None:
+        b = np.ascontiguousarray(bias, dtype=np.float32)
+        fb = lib().dlf_oracle_bias_f32
+        fb.restype = None
+        fb.argtypes = [ctypes.c_void_p, ctypes.c_void_p] + [ctypes.c_size_t] * 3
+        fb(_p(Y), _p(b), n, co, oh * ow)
+    return Y
+
+
+# ---------------------------------------------------------------------------------------------
+# Tuned host BLAS for the timed CPU baseline: the reference calls cblas_sgemm of whatever BLAS it
+# was linked with (MKL in its Dockerfile). On this box the closest stand-in is the OpenBLAS that
+# ships inside the scipy / numpy wheels.
+# ---------------------------------------------------------------------------------------------
+def find_host_cblas():
+    """Returns (ctypes function for row-major cblas_sgemm, description) or (None, reason)."""
+    import importlib.util
+    cands = []
+    for pkg, sym in (("scipy", "scipy_cblas_sgemm"), ("numpy", "scipy_cblas_sgemm64_")):
+        spec = importlib.util.find_spec(pkg)
+        if spec is None or not spec.submodule_search_locations:
+            continue
+        root = os.path.dirname(list(spec.submodule_search_locations)[0])
+        for so in sorted(glob.glob(os.path.join(root, pkg + ".libs", "libscipy_openblas*.so"))):
+            cands.append((so, sym))
+    for so, sym in cands:
+        try:
+            L = ctypes.CDLL(so)
+            fn = getattr(L, sym)
+        except (OSError, AttributeError):
+            continue
+        ilp64 = sym.endswith("64_")
+        it = ctypes.c_int64 if ilp64 else ctypes.c_int
+        fn.restype = None
+        fn.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, it, it, it, ctypes.c_float,
+                       ctypes.c_void_p, it, ctypes.c_void_p, it, ctypes.c_float, ctypes.c_void_p, it]
+        return fn, "OpenBLAS %s (%s)" % (os.path.basename(so), "ILP64" if ilp64 else "LP64")
+    return None, "no host cblas found"
+
+
+def host_sgemm(fn, layout, trans_a, trans_b, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc):
+    fn(layout, trans_a, trans_b, m, n, k, alpha, _p(A), lda, _p(B), ldb, beta, _p(C), ldc)
+
+
+def host_sgemm_nn_callback(fn):
+    """Wraps a cblas_sgemm as the row-major NoTrans/NoTrans callback dlf_oracle_conv2d_f32 takes."""
+    def cb(m, n, k, a, lda, b, ldb, c, ldc):
+        fn(ROW_MAJOR, NO_TRANS, NO_TRANS, m, n, k, 1.0, a, lda, b, ldb, 0.0, c, ldc)
+    return _SGEMM_NN_FN(cb)

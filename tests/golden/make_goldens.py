@@ -1,0 +1,217 @@
+"""Extracts the known-answer vectors of the reference's own unit tests for the gemm / matmul /
+conv2d path into ``reference_goldens.json`` (beside this script).
+
+The reference is C++ and cannot be built in this environment, so its test sources are read as
+text: tensor literals, ``range()`` constructors and the ``EXPECT_EQ(matmul(...), ...)`` lines are
+parsed out of
+
+    dlf/test/TensorTest.cpp          gemm_test()            (alpha=2, beta=3, 4 transpose combos)
+    dlf/test/GPGPUTest.cpp           gemm_test()            (same data through the GPU API)
+    dlf/test/MatMulTest.cpp          TYPED_TEST(MatMulTest, *)
+    dlf/test/DNNTest.cpp             TEST(Conv2D, *)
+    dlf/test/model/PredictTest.cpp   Gemm, Conv (+bias)
+
+Usage:  python tests/golden/make_goldens.py /path/to/dlf-checkout
+Only the JSON travels with the repository; the tests never read the reference tree.
+"""
+import json
+import os
+import re
+import sys
+
+
+def _ints(s):
+    return [int(x) for x in re.findall(r"-?\d+", s)]
+
+
+def _line_of(text, pos):
+    return text.count("\n", 0, pos) + 1
+
+
+def _block(text, start):
+    """Returns (body, end) of the brace block whose '{' is at or after `start`."""
+    i = text.index("{", start)
+    depth = 0
+    for j in range(i, len(text)):
+        if text[j] == "{":
+            depth += 1
+        elif text[j] == "}":
+            depth -= 1
+            if depth == 0:
+                return text[i + 1:j], j + 1
+    raise ValueError("unbalanced braces")
+
+
+def _split_args(s):
+    out, depth, cur, in_str = [], 0, "", False
+    for ch in s:
+        if ch == '"':
+            in_str = not in_str
+        if not in_str:
+            if ch in "([{":
+                depth += 1
+            elif ch in ")]}":
+                depth -= 1
+            elif ch == "," and depth == 0:
+                out.append(cur.strip())
+                cur = ""
+                continue
+        cur += ch
+    if cur.strip():
+        out.append(cur.strip())
+    return out
+
+
+T = r"(?:TypeParam|T|float)"
+RE_RANGE = re.compile(r"(?:auto|Tensor<%s>)\s+(\w+)\s*=\s*Tensor<%s>\(\{([\d,\s]+)\}\)\.range\((\d+)\)\s*;" % (T, T))
+RE_LIT = re.compile(r"(?:auto\s+(\w+)\s*=\s*Tensor<%s>|Tensor<%s>\s+(\w+))\s*\(\{([\d,\s]+)\},\s*\{([^}]*)\}\)\s*;" % (T, T), re.S)
+RE_FILL = re.compile(r"auto\s+(\w+)\s*=\s*Tensor<%s>\(\{([\d,\s]+)\},\s*(\d+)\)\s*;" % T)
+RE_SCALAR = re.compile(r"auto\s+(\w+)\s*=\s*(?:Tensor<%s>::scalar|Scalar<%s>)\((\d+)\)\s*;" % (T, T))
+RE_MATRIX = re.compile(r"auto\s+(\w+)\s*=\s*Matrix<%s>\(\{(.*?)\}\)\s*;" % T, re.S)
+RE_VECTOR = re.compile(r"auto\s+(\w+)\s*=\s*Vector<%s>\(\{([^}]*)\}\)\s*;" % T)
+RE_ALIAS = re.compile(r"auto\s+(\w+)\s*=\s*((?:unsqueeze\(|as_strided\(|\w+\[\")[^;]*);")
+RE_EMPTY = re.compile(r"auto\s+(\w+)\s*=\s*Tensor<%s>\((?:\{([\d,\s]+)\}|filter\.output_shape\(\))?\)\s*;" % T)
+
+
+def parse_vars(body):
+    vars_ = {}
+    for m in RE_RANGE.finditer(body):
+        vars_[m.group(1)] = {"shape": _ints(m.group(2)), "range": int(m.group(3))}
+    for m in RE_LIT.finditer(body):
+        vars_[m.group(1) or m.group(2)] = {"shape": _ints(m.group(3)), "values": _ints(m.group(4))}
+    for m in RE_FILL.finditer(body):
+        vars_[m.group(1)] = {"shape": _ints(m.group(2)), "fill": int(m.group(3))}
+    for m in RE_SCALAR.finditer(body):
+        vars_[m.group(1)] = {"shape": [], "values": [int(m.group(2))]}
+    for m in RE_MATRIX.finditer(body):
+        rows = re.findall(r"\{([^{}]*)\}", m.group(2))
+        vals = [_ints(r) for r in rows]
+        vars_[m.group(1)] = {"shape": [len(vals), len(vals[0])], "values": sum(vals, [])}
+    for m in RE_VECTOR.finditer(body):
+        v = _ints(m.group(2))
+        vars_[m.group(1)] = {"shape": [len(v)], "values": v}
+    for m in RE_ALIAS.finditer(body):
+        if m.group(1).startswith("dev"):
+            continue
+        vars_[m.group(1)] = {"expr": m.group(2).strip()}
+    return vars_
+
+
+def extract_gemm(path, rel):
+    text = open(path).read()
+    pos = text.index("static void gemm_test()")
+    body, _ = _block(text, pos)
+    v = parse_vars(body)
+    low = {k.lower(): val for k, val in v.items()}
+    al = re.search(r"T\(2\)", body) and re.search(r"T\(3\)", body)
+    assert al, "alpha/beta literals moved"
+    return {"source": "%s:%d" % (rel, _line_of(text, pos)), "alpha": 2, "beta": 3,
+            "A": low["a"], "A_t": low.get("t_a") or low["a_t"], "B": low["b"],
+            "B_t": low.get("t_b") or low["b_t"], "C": low["c"], "R": low["r"]}
+
+
+def extract_matmul(path, rel):
+    text = open(path).read()
+    cases = []
+    for m in re.finditer(r"TYPED_TEST\(MatMulTest,\s*(\w+)\)", text):
+        name = m.group(1)
+        body, _ = _block(text, m.end())
+        # tests written as several independent { } scopes
+        scopes = []
+        stripped = body.strip()
+        if stripped.startswith("{"):
+            pos = 0
+            while True:
+                try:
+                    pos = body.index("{", pos)
+                except ValueError:
+                    break
+                inner, pos = _block(body, pos)
+                scopes.append(inner)
+        else:
+            scopes.append(body)
+        for si, scope in enumerate(scopes):
+            vars_ = parse_vars(scope)
+            checks = []
+            for c in re.finditer(r"EXPECT_EQ\(matmul\((.*)\),\s*([\w\[\]]+)\);", scope):
+                args = _split_args(c.group(1))
+                if len(args) != 2 or "dev" in c.group(1):
+                    continue
+                checks.append({"a": args[0], "b": args[1], "expect": c.group(2)})
+            if not checks:
+                continue
+            cases.append({"name": name + ("_%d" % si if len(scopes) > 1 else ""),
+                          "source": "%s:%d" % (rel, _line_of(text, m.start())),
+                          "vars": vars_, "checks": checks})
+    return cases
+
+
+def extract_conv(path, rel):
+    text = open(path).read()
+    cases = []
+    for m in re.finditer(r"TEST\(Conv2D,\s*(\w+)\)", text):
+        body, _ = _block(text, m.end())
+        vars_ = parse_vars(body)
+        f = re.search(r"dnn::Filter2D\(X\.shape\(\), W\.shape\(\)(?:,\s*(\d+))?\)((?:\.\w+\([\d,\s]*\))*)", body)
+        cfg = {"group": int(f.group(1) or 1), "pads": [0, 0, 0, 0], "strides": [1, 1]}
+        for call in re.finditer(r"\.(\w+)\(([\d,\s]*)\)", f.group(2)):
+            vals = _ints(call.group(2))
+            if call.group(1) == "pads":
+                cfg["pads"] = vals if len(vals) == 4 else [vals[0], vals[1], vals[0], vals[1]]
+            elif call.group(1) == "strides":
+                cfg["strides"] = vals
+        case = {"name": m.group(1), "source": "%s:%d" % (rel, _line_of(text, m.start())),
+                "X": vars_["X"], "W": vars_["W"], "filter": cfg}
+        if "R" in vars_:
+            case["R"] = vars_["R"]
+        cases.append(case)
+    return cases
+
+
+def extract_predict(path, rel):
+    text = open(path).read()
+    out = {}
+    m = re.search(r"TYPED_TEST\(PredictTest,\s*Gemm\)", text)
+    body, _ = _block(text, m.end())
+    sets = re.findall(r"Tensor<float>\(\{([\d,\s]+)\},\s*\{([^}]*)\}\)", body)
+    out["gemm"] = {"source": "%s:%d" % (rel, _line_of(text, m.start())), "alpha": 1, "beta": 1,
+                   "A": {"shape": _ints(sets[0][0]), "values": _ints(sets[0][1])},
+                   "B": {"shape": _ints(sets[1][0]), "values": _ints(sets[1][1])},
+                   "C": {"shape": _ints(sets[2][0]), "values": _ints(sets[2][1])},
+                   "Y": {"shape": _ints(sets[3][0]), "values": _ints(sets[3][1])}}
+    m = re.search(r"TYPED_TEST\(PredictTest,\s*Conv\)", text)
+    body, _ = _block(text, m.end())
+    pads = _ints(re.search(r"pads\(\{([\d,\s]+)\}\)", body).group(1))
+    bias = re.search(r'TensorData\("B",\s*DataType::FLOAT,\s*\{([\d,\s]+)\},\s*\{([^}]*)\}\)', body)
+    vars_ = parse_vars(body)
+    y = re.search(r"predictor\.get\(0\),\s*Tensor<float>\(\{([\d,\s]+)\},\s*\{([^}]*)\}\)", body, re.S)
+    out["conv"] = {"source": "%s:%d" % (rel, _line_of(text, m.start())), "pads": pads,
+                   "X": vars_["X"], "W": vars_["W"],
+                   "bias": {"shape": _ints(bias.group(1)), "values": _ints(bias.group(2))},
+                   "Y": {"shape": _ints(y.group(1)), "values": _ints(y.group(2))}}
+    return out
+
+
+def main():
+    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    t = os.path.join(root, "dlf", "test")
+    g1 = extract_gemm(os.path.join(t, "TensorTest.cpp"), "dlf/test/TensorTest.cpp")
+    g2 = extract_gemm(os.path.join(t, "GPGPUTest.cpp"), "dlf/test/GPGPUTest.cpp")
+    data = {
+        "_comment": "Generated by tests/golden/make_goldens.py from the reference's unit tests; "
+                    "do not edit by hand.",
+        "gemm": [g1, g2],
+        "matmul": extract_matmul(os.path.join(t, "MatMulTest.cpp"), "dlf/test/MatMulTest.cpp"),
+        "conv2d": extract_conv(os.path.join(t, "DNNTest.cpp"), "dlf/test/DNNTest.cpp"),
+        "predict": extract_predict(os.path.join(t, "model", "PredictTest.cpp"),
+                                   "dlf/test/model/PredictTest.cpp"),
+    }
+    out = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_goldens.json")
+    with open(out, "w") as f:
+        json.dump(data, f, indent=1)
+    print("wrote", out, "gemm:", len(data["gemm"]), "matmul:", len(data["matmul"]),
+          "conv2d:", len(data["conv2d"]))
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,472 @@
+"""GPU suite: the CUDA path, called through the C-ABI (dlf_b200.gblas / gdnn are ctypes shims over
+libdlf_b200.so), against the reference's golden vectors and against the CPU oracle on seeded
+inputs. Tolerances: bit-exact for the integer-valued goldens; fp32 <= 1e-5 relative Frobenius
+error; fp16 / bf16 <= 2e-2 max relative error (relative to max(|y|, 1e-2*max|y|))."""
+import itertools
+import threading
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from support import evaluate, load_goldens, max_rel, rel_fro, tensor_of, UNSUPPORTED_EXPR
+
+pytestmark = pytest.mark.gpu
+
+G = load_goldens()
+FP32_TOL = 1e-5
+HALF_TOL = 2e-2
+
+
+@pytest.fixture(scope="module")
+def lib():
+    import dlf_b200
+    return dlf_b200
+
+
+@pytest.fixture(autouse=True)
+def _device_status_clean(lib):
+    yield
+    assert lib.device_status() == 0, "a device-side bounded wait timed out"
+
+
+def _gb():
+    from dlf_b200 import gblas
+    return gblas
+
+
+def _rand(rng, shape, dist="uniform"):
+    if dist == "uniform":
+        return rng.uniform(-1, 1, shape).astype(np.float32)
+    return rng.normal(size=shape).astype(np.float32)
+
+
+def _round_to(x, dtype):
+    """float32 array rounded (nearest-even) to the storage type and back."""
+    return torch.from_numpy(x).to(dtype).to(torch.float32).numpy()
+
+
+# ------------------------------------------------------------------------------------------
+# golden vectors of the reference's tests, through the C-ABI
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("case", G["gemm"], ids=lambda c: c["source"])
+def test_gemm_goldens(case, dtype):
+    gb = _gb()
+    A, At, B, Bt, C, R = (tensor_of(case[k], dtype) for k in ("A", "A_t", "B", "B_t", "C", "R"))
+    N, T = gb.Transpose.NoTrans, gb.Transpose.Trans
+    for ta, tb, a, b in ((N, N, A, B), (T, N, At, B), (N, T, A, Bt), (T, T, At, Bt)):
+        c = C.clone().cuda()
+        gb.gemm(gb.Layout.RowMajor, ta, tb, 3, 4, 6, 2, a.cuda().reshape(-1), 0, a.shape[1],
+                b.cuda().reshape(-1), 0, b.shape[1], 3, c.reshape(-1), 0, 4)
+        assert torch.equal(c.cpu(), R)
+        # the same product for a column-major caller (transposed storage)
+        c = C.t().contiguous().cuda()
+        gb.gemm(gb.Layout.ColMajor, ta, tb, 3, 4, 6, 2, a.t().contiguous().cuda().reshape(-1), 0,
+                a.shape[0], b.t().contiguous().cuda().reshape(-1), 0, b.shape[0], 3,
+                c.reshape(-1), 0, 3)
+        assert torch.equal(c.cpu().t(), R)
+
+
+def _supported(case):
+    text = " ".join(c["a"] + c["b"] for c in case["checks"]) + \
+        " ".join(v.get("expr", "") for v in case["vars"].values())
+    return not any(u in text for u in UNSUPPORTED_EXPR)
+
+
+@pytest.mark.parametrize("case", G["matmul"], ids=lambda c: c["name"])
+def test_matmul_goldens(case):
+    from dlf_b200 import tensor as dt
+    if not _supported(case):
+        pytest.skip("expression form not modelled")
+    env = dict(case["vars"])
+    # build the views on the device from device-resident base tensors
+    for k, v in list(env.items()):
+        if "expr" not in v:
+            env[k] = tensor_of(v).cuda()
+    for chk in case["checks"]:
+        A, B = evaluate(chk["a"], env), evaluate(chk["b"], env)
+        expect = evaluate(chk["expect"], env)
+        if not A.is_cuda:
+            A = A.cuda()
+        if not B.is_cuda:
+            B = B.cuda()
+        got = dt.matmul(A, B)
+        assert list(got.shape) == list(expect.shape)
+        assert torch.equal(got.cpu(), expect.cpu()), (case["name"], chk)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("case", G["conv2d"], ids=lambda c: c["name"])
+def test_conv2d_goldens(case, dtype):
+    from dlf_b200 import gdnn
+    X, W = tensor_of(case["X"], dtype), tensor_of(case["W"], dtype)
+    f = case["filter"]
+    filt = gdnn.Filter2D(X.shape, W.shape, f["group"]).pads(*f["pads"]).strides(*f["strides"])
+    Y = torch.full(filt.output_shape(), float("nan"), dtype=dtype).cuda()
+    gdnn.conv2d_filter(X.cuda(), W.cuda(), Y, filt)
+    ref = oracle.conv2d(X.float().numpy(), W.float().numpy(), group=f["group"],
+                        pads=tuple(f["pads"]), strides=tuple(f["strides"]))
+    if "R" in case:
+        assert np.array_equal(ref, tensor_of(case["R"]).numpy())
+    if dtype == torch.float32 or np.abs(ref).max() <= 2048:
+        assert np.array_equal(Y.float().cpu().numpy(), ref)
+    else:
+        assert max_rel(Y.float().cpu().numpy(), ref) <= HALF_TOL
+
+
+def test_predict_conv_bias_golden():
+    from dlf_b200 import gdnn
+    p = G["predict"]["conv"]
+    X, W, b = tensor_of(p["X"]), tensor_of(p["W"]), tensor_of(p["bias"])
+    filt = gdnn.Filter2D(X.shape, W.shape).pads(*p["pads"])
+    Y = torch.empty(filt.output_shape()).cuda()
+    gdnn.conv2d_filter(X.cuda(), W.cuda(), Y, filt, bias=b.cuda())
+    assert torch.equal(Y.cpu(), tensor_of(p["Y"]))
+
+
+def test_predict_gemm_golden():
+    from dlf_b200 import tensor as dt
+    gb = _gb()
+    p = G["predict"]["gemm"]
+    got = dt.gemm(gb.Transpose.NoTrans, gb.Transpose.NoTrans, 1.0, tensor_of(p["A"]).cuda(),
+                  tensor_of(p["B"]).cuda(), 1.0, tensor_of(p["C"]).cuda())
+    assert torch.equal(got.cpu(), tensor_of(p["Y"]))
+
+
+# ------------------------------------------------------------------------------------------
+# seeded random parity against the oracle
+# ------------------------------------------------------------------------------------------
+def _gemm_case(rng, dtype, layout, ta, tb, m, n, k, alpha, beta, pad, offs, nan_c=False):
+    gb = _gb()
+    row = layout == gb.Layout.RowMajor
+    a_one, a_two, b_one, b_two, c_one, c_two = gb._dims(layout, ta, tb, m, n, k)
+    lda, ldb, ldc = a_one + pad[0], b_one + pad[1], c_one + pad[2]
+    A = _round_to(_rand(rng, offs[0] + lda * a_two), dtype)
+    B = _round_to(_rand(rng, offs[1] + ldb * b_two), dtype)
+    C = _round_to(_rand(rng, offs[2] + ldc * c_two, "normal"), dtype)
+    ref = C.copy()
+    oracle.gblas_sgemm(int(layout), int(ta), int(tb), m, n, k, alpha, A, offs[0], lda, B, offs[1],
+                       ldb, beta, ref, offs[2], ldc, wide=True)
+    dC = torch.from_numpy(C).to(dtype).cuda()
+    if nan_c:
+        dC.fill_(float("nan"))
+    before = dC.clone()
+    gb.gemm(layout, ta, tb, m, n, k, alpha, torch.from_numpy(A).to(dtype).cuda(), offs[0], lda,
+            torch.from_numpy(B).to(dtype).cuda(), offs[1], ldb, beta, dC, offs[2], ldc)
+    got = dC.float().cpu().numpy()
+    # elements outside the m x n window (padding, offset prefix) must be untouched
+    mask = np.zeros(C.shape, bool)
+    for j in range(c_two):
+        mask[offs[2] + j * ldc: offs[2] + j * ldc + c_one] = True
+    b4 = before.float().cpu().numpy()
+    assert np.array_equal(got[~mask], b4[~mask], equal_nan=True)
+    return got[mask], ref[mask]
+
+
+SHAPES = [(1, 1, 1), (3, 4, 6), (127, 65, 33), (128, 256, 64), (130, 260, 70), (257, 31, 500),
+          (64, 1, 96), (1, 300, 64)]
+
+
+@pytest.mark.parametrize("m,n,k", SHAPES)
+def test_gemm_fp32_all_layouts(m, n, k):
+    gb = _gb()
+    rng = np.random.default_rng(m * 1000003 + n * 1009 + k)
+    combos = itertools.product((gb.Layout.RowMajor, gb.Layout.ColMajor),
+                               (gb.Transpose.NoTrans, gb.Transpose.Trans),
+                               (gb.Transpose.NoTrans, gb.Transpose.Trans))
+    for i, (layout, ta, tb) in enumerate(combos):
+        pad = (0, 0, 0) if i % 2 == 0 else (3, 5, 1)
+        offs = (0, 0, 0) if i % 3 == 0 else (7, 2, 9)
+        got, ref = _gemm_case(rng, torch.float32, layout, ta, tb, m, n, k, 0.5, 0.5, pad, offs)
+        assert rel_fro(got, ref) <= FP32_TOL, (layout, ta, tb)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("m,n,k", SHAPES)
+def test_gemm_half_all_layouts(dtype, m, n, k):
+    """Covers both operand loaders: aligned leading dimensions take the TMA producer, the padded /
+    offset variants (odd element offsets) take the generic loader warps."""
+    gb = _gb()
+    rng = np.random.default_rng(m * 7919 + n * 104729 + k)
+    combos = itertools.product((gb.Layout.RowMajor, gb.Layout.ColMajor),
+                               (gb.Transpose.NoTrans, gb.Transpose.Trans),
+                               (gb.Transpose.NoTrans, gb.Transpose.Trans))
+    for i, (layout, ta, tb) in enumerate(combos):
+        pad = ((0, 0, 0), (8, 16, 8), (3, 5, 1))[i % 3]
+        offs = ((0, 0, 0), (8, 16, 24), (7, 2, 9))[i % 3]
+        got, ref = _gemm_case(rng, dtype, layout, ta, tb, m, n, k, 0.125, 0.0, pad, offs)
+        assert max_rel(got, ref) <= HALF_TOL, (layout, ta, tb)
+
+
+def test_gemm_aligned_shapes_take_both_loaders(lib):
+    """Same aligned problem through the TMA producer and through the forced generic loader."""
+    gb = _gb()
+    rng = np.random.default_rng(5)
+    outs = []
+    for generic in (False, True):
+        lib.set_tuning(0, generic)
+        try:
+            got, ref = _gemm_case(np.random.default_rng(5), torch.float16, gb.Layout.RowMajor,
+                                  gb.Transpose.NoTrans, gb.Transpose.Trans, 384, 520, 264, 1.0,
+                                  0.0, (0, 0, 0), (0, 0, 0))
+        finally:
+            lib.set_tuning(0, False)
+        assert max_rel(got, ref) <= HALF_TOL
+        outs.append(got)
+    assert np.array_equal(outs[0], outs[1])  # same tiles, same accumulation order
+    del rng
+
+
+@pytest.mark.parametrize("bn", [64, 128, 256])
+def test_gemm_every_tile_width(lib, bn):
+    gb = _gb()
+    lib.set_tuning(bn, False)
+    try:
+        got, ref = _gemm_case(np.random.default_rng(bn), torch.float16, gb.Layout.ColMajor,
+                              gb.Transpose.NoTrans, gb.Transpose.NoTrans, 520, 776, 328, 1.0, 0.0,
+                              (0, 0, 0), (0, 0, 0))
+        assert max_rel(got, ref) <= HALF_TOL
+        if bn != 256:
+            got, ref = _gemm_case(np.random.default_rng(bn), torch.float32, gb.Layout.RowMajor,
+                                  gb.Transpose.Trans, gb.Transpose.NoTrans, 300, 520, 200, 0.5,
+                                  0.5, (0, 0, 0), (0, 0, 0))
+            assert rel_fro(got, ref) <= FP32_TOL
+    finally:
+        lib.set_tuning(0, False)
+
+
+def test_beta_zero_never_reads_c():
+    """beta == 0 must overwrite C without reading it (xgemm_part2.cl:87-126): NaNs in C vanish."""
+    gb = _gb()
+    rng = np.random.default_rng(11)
+    for dtype, tol, metric in ((torch.float32, FP32_TOL, rel_fro), (torch.float16, HALF_TOL, max_rel)):
+        got, ref = _gemm_case(rng, dtype, gb.Layout.RowMajor, gb.Transpose.NoTrans,
+                              gb.Transpose.NoTrans, 100, 72, 40, 1.0, 0.0, (0, 0, 0), (0, 0, 0),
+                              nan_c=True)
+        assert not np.isnan(got).any()
+        assert metric(got, ref) <= tol
+
+
+def test_gemm_config1_sgemm_1024():
+    """BASELINE config 1: fp32 row-major 1024^3, alpha 1, beta 0, U[-1,1] seed 0, C zero."""
+    gb = _gb()
+    rng = np.random.default_rng(0)
+    A, B = _rand(rng, 1024 * 1024), _rand(rng, 1024 * 1024)
+    ref = np.zeros(1024 * 1024, np.float32)
+    oracle.gblas_sgemm(oracle.ROW_MAJOR, oracle.NO_TRANS, oracle.NO_TRANS, 1024, 1024, 1024, 1.0,
+                       A, 0, 1024, B, 0, 1024, 0.0, ref, 0, 1024)
+    C = torch.zeros(1024 * 1024, device="cuda")
+    gb.gemm(gb.Layout.RowMajor, gb.Transpose.NoTrans, gb.Transpose.NoTrans, 1024, 1024, 1024, 1.0,
+            torch.from_numpy(A).cuda(), 0, 1024, torch.from_numpy(B).cuda(), 0, 1024, 0.0, C, 0, 1024)
+    assert rel_fro(C.cpu().numpy(), ref) <= FP32_TOL
+
+
+# ------------------------------------------------------------------------------------------
+# batched
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_strided_batched_including_shared_operand(dtype):
+    gb = _gb()
+    rng = np.random.default_rng(21)
+    m, n, k, batch = 70, 90, 50, 5
+    for a_stride, ta, tb in ((m * k + 8, gb.Transpose.NoTrans, gb.Transpose.NoTrans),
+                             (0, gb.Transpose.NoTrans, gb.Transpose.Trans),
+                             (m * k, gb.Transpose.Trans, gb.Transpose.NoTrans)):
+        lda = k if ta == gb.Transpose.NoTrans else m
+        ldb = n if tb == gb.Transpose.NoTrans else k
+        b_stride, c_stride = k * n + 16, m * n
+        A = _round_to(_rand(rng, a_stride * (batch - 1) + m * k + 3), dtype)
+        B = _round_to(_rand(rng, b_stride * (batch - 1) + k * n + 5), dtype)
+        C = _round_to(_rand(rng, c_stride * batch), dtype)
+        ref = C.copy()
+        oracle.gblas_sgemm_strided_batched(oracle.ROW_MAJOR, int(ta), int(tb), m, n, k, 0.5, A, 3,
+                                           lda, a_stride, B, 5, ldb, b_stride, 0.25, ref, 0, n,
+                                           c_stride, batch, wide=True)
+        dC = torch.from_numpy(C).to(dtype).cuda()
+        gb.gemmStridedBatched(gb.Layout.RowMajor, ta, tb, m, n, k, 0.5,
+                              torch.from_numpy(A).to(dtype).cuda(), 3, lda, a_stride,
+                              torch.from_numpy(B).to(dtype).cuda(), 5, ldb, b_stride, 0.25, dC, 0,
+                              n, c_stride, batch)
+        got = dC.float().cpu().numpy()
+        if dtype == torch.float32:
+            assert rel_fro(got, ref) <= FP32_TOL
+        else:
+            assert max_rel(got, ref) <= HALF_TOL
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gemm_batched_offset_tables(dtype):
+    gb = _gb()
+    rng = np.random.default_rng(31)
+    m, n, k, batch = 33, 45, 27, 6
+    a_offs = [7 + i * (m * k + 3) for i in range(batch)]
+    b_offs = [(batch - 1 - i) * (k * n + 1) for i in range(batch)]  # reversed order
+    c_offs = [2 + i * (m * n + 4) for i in range(batch)]
+    alphas = [0.5 + 0.25 * i for i in range(batch)]
+    betas = [0.0 if i % 2 == 0 else 0.5 for i in range(batch)]
+    A = _round_to(_rand(rng, a_offs[-1] + m * k), dtype)
+    B = _round_to(_rand(rng, b_offs[0] + k * n), dtype)
+    C = _round_to(_rand(rng, c_offs[-1] + m * n), dtype)
+    ref = C.copy()
+    oracle.gblas_sgemm_batched(oracle.COL_MAJOR, oracle.NO_TRANS, oracle.TRANS, m, n, k, alphas, A,
+                               a_offs, m, B, b_offs, n, betas, ref, c_offs, m, batch, wide=True)
+    dC = torch.from_numpy(C).to(dtype).cuda()
+    gb.gemmBatched(gb.Layout.ColMajor, gb.Transpose.NoTrans, gb.Transpose.Trans, m, n, k, alphas,
+                   torch.from_numpy(A).to(dtype).cuda(), a_offs, m,
+                   torch.from_numpy(B).to(dtype).cuda(), b_offs, n, betas, dC, c_offs, m, batch)
+    got = dC.float().cpu().numpy()
+    if dtype == torch.float32:
+        assert rel_fro(got, ref) <= FP32_TOL
+    else:
+        assert max_rel(got, ref) <= HALF_TOL
+
+
+def test_config4_attention_like_batched_half():
+    """BASELINE config 4 shapes at a reduced batch for the element-wise check, both operand
+    storage orders; alpha = 1/sqrt(64), beta = 0."""
+    gb = _gb()
+    rng = np.random.default_rng(4)
+    for (m, n, k) in ((512, 512, 64), (512, 64, 512)):
+        batch = 6
+        for ta, tb in itertools.product((gb.Transpose.NoTrans, gb.Transpose.Trans), repeat=2):
+            A = _round_to((0.1 * rng.normal(size=batch * m * k)).astype(np.float32), torch.float16)
+            B = _round_to((0.1 * rng.normal(size=batch * k * n)).astype(np.float32), torch.float16)
+            lda = k if ta == gb.Transpose.NoTrans else m
+            ldb = n if tb == gb.Transpose.NoTrans else k
+            ref = np.zeros(batch * m * n, np.float32)
+            oracle.gblas_sgemm_strided_batched(oracle.ROW_MAJOR, int(ta), int(tb), m, n, k, 0.125,
+                                               A, 0, lda, m * k, B, 0, ldb, k * n, 0.0, ref, 0, n,
+                                               m * n, batch, wide=True)
+            dC = torch.full((batch * m * n,), float("nan"), dtype=torch.float16, device="cuda")
+            gb.gemmStridedBatched(gb.Layout.RowMajor, ta, tb, m, n, k, 0.125,
+                                  torch.from_numpy(A).half().cuda(), 0, lda, m * k,
+                                  torch.from_numpy(B).half().cuda(), 0, ldb, k * n, 0.0, dC, 0, n,
+                                  m * n, batch)
+            assert max_rel(dC.float().cpu().numpy(), ref) <= HALF_TOL
+
+
+# ------------------------------------------------------------------------------------------
+# convolution
+# ------------------------------------------------------------------------------------------
+CONV_CASES = [
+    # N, C, H, W, Cout, KH, KW, pads(t,l,b,r), strides, dilations, group
+    (2, 64, 56, 56, 64, 3, 3, (1, 1, 1, 1), (1, 1), (1, 1), 1),     # config 2 at batch 2
+    (2, 3, 37, 41, 16, 7, 7, (3, 3, 3, 3), (2, 2), (1, 1), 1),      # stem-like, K = 147
+    (3, 32, 14, 14, 48, 1, 1, (0, 0, 0, 0), (1, 1), (1, 1), 1),     # 1x1
+    (3, 32, 14, 14, 64, 1, 1, (0, 0, 0, 0), (2, 2), (1, 1), 1),     # 1x1 stride 2
+    (2, 8, 13, 11, 12, 3, 2, (1, 2, 2, 1), (2, 1), (1, 2), 2),      # odd everything + groups
+    (5, 16, 7, 7, 40, 3, 3, (1, 1, 1, 1), (1, 1), (1, 1), 4),       # tiles straddle images
+    (1, 4, 9, 9, 4, 3, 3, (0, 0, 0, 0), (1, 1), (2, 2), 4),         # depthwise, dilated
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("case", CONV_CASES, ids=lambda c: "x".join(map(str, c[:7])))
+def test_conv2d_random_parity(case, dtype):
+    from dlf_b200 import gdnn
+    N, C, H, W, Co, KH, KW, pads, strides, dil, group = case
+    rng = np.random.default_rng(abs(hash(case)) % (2 ** 32))
+    X = _round_to(rng.normal(size=(N, C, H, W)).astype(np.float32), dtype)
+    std = np.sqrt(2.0 / (C // group * KH * KW))
+    Wt = _round_to((std * rng.normal(size=(Co, C // group, KH, KW))).astype(np.float32), dtype)
+    bias = _round_to(rng.uniform(-0.1, 0.1, Co).astype(np.float32), dtype)
+    ref = oracle.conv2d(X, Wt, group=group, pads=pads, strides=strides, dilations=dil, bias=bias,
+                        wide=True)
+    filt = gdnn.Filter2D(X.shape, Wt.shape, group).pads(*pads).strides(*strides).dilations(*dil)
+    assert tuple(filt.output_shape()) == ref.shape
+    Y = torch.full(ref.shape, float("nan"), dtype=dtype, device="cuda")
+    gdnn.conv2d_filter(torch.from_numpy(X).to(dtype).cuda(), torch.from_numpy(Wt).to(dtype).cuda(),
+                       Y, filt, bias=torch.from_numpy(bias).to(dtype).cuda())
+    got = Y.float().cpu().numpy()
+    if dtype == torch.float32:
+        assert rel_fro(got, ref) <= FP32_TOL
+    else:
+        assert max_rel(got, ref) <= HALF_TOL
+
+
+def test_conv2d_config2_full_size_properties():
+    """BASELINE config 2 at its full size (N=64): every image against the oracle would take long
+    on the CPU, so four images are checked element-wise and the whole batch through two
+    size-independent properties: (i) images are independent (a permuted batch gives the permuted
+    output, bit for bit), (ii) linearity in the weights."""
+    from dlf_b200 import gdnn
+    rng = np.random.default_rng(0)
+    X = rng.normal(size=(64, 64, 56, 56)).astype(np.float32)
+    Wt = (np.sqrt(2.0 / 576) * rng.normal(size=(64, 64, 3, 3))).astype(np.float32)
+    bias = rng.uniform(-0.1, 0.1, 64).astype(np.float32)
+    filt = gdnn.Filter2D(X.shape, Wt.shape).pads(1, 1)
+    dX, dW, db = torch.from_numpy(X).cuda(), torch.from_numpy(Wt).cuda(), torch.from_numpy(bias).cuda()
+    Y = torch.empty(filt.output_shape(), device="cuda")
+    gdnn.conv2d_filter(dX, dW, Y, filt, bias=db)
+    pick = [0, 17, 42, 63]
+    ref = oracle.conv2d(X[pick], Wt, pads=(1, 1, 1, 1), bias=bias, wide=True)
+    assert rel_fro(Y[pick].cpu().numpy(), ref) <= FP32_TOL
+    perm = torch.randperm(64, generator=torch.Generator().manual_seed(1)).cuda()
+    Yp = torch.empty_like(Y)
+    gdnn.conv2d_filter(dX[perm].contiguous(), dW, Yp, filt, bias=db)
+    assert torch.equal(Yp, Y[perm])
+    Y2 = torch.empty_like(Y)
+    gdnn.conv2d_filter(dX, (2.0 * dW).contiguous(), Y2, filt)  # exact scaling by 2, no bias
+    Y1 = torch.empty_like(Y)
+    gdnn.conv2d_filter(dX, dW, Y1, filt)
+    assert torch.equal(Y2, 2.0 * Y1)
+
+
+# ------------------------------------------------------------------------------------------
+# errors, threads
+# ------------------------------------------------------------------------------------------
+def test_argument_errors_have_reference_status_codes():
+    gb = _gb()
+    a = torch.zeros(64, device="cuda")
+    L, N = gb.Layout.RowMajor, gb.Transpose.NoTrans
+    with pytest.raises(gb.BLASError) as e:
+        gb.gemm(L, N, N, 0, 4, 4, 1.0, a, 0, 4, a, 0, 4, 0.0, a, 0, 4)
+    assert e.value.status == gb.StatusCode.kInvalidDimension
+    with pytest.raises(gb.BLASError) as e:
+        gb.gemm(L, N, N, 4, 4, 4, 1.0, a, 0, 3, a, 0, 4, 0.0, a, 0, 4)
+    assert e.value.status == gb.StatusCode.kInvalidLeadDimA
+    with pytest.raises(gb.BLASError) as e:
+        gb.gemm(L, N, N, 4, 4, 4, 1.0, a, 0, 4, a, 0, 4, 0.0, a, 60, 4)
+    assert e.value.status == gb.StatusCode.kInsufficientMemoryC
+    with pytest.raises(gb.BLASError) as e:
+        gb.gemmStridedBatched(L, N, N, 4, 4, 4, 1.0, a, 0, 4, 16, a, 0, 4, 16, 0.0, a, 0, 4, 16, 0)
+    assert e.value.status == gb.StatusCode.kInvalidBatchCount
+
+
+def test_two_host_threads_each_with_its_own_queue():
+    """Mirror of GPGPU.MultipleThreadContextActivation (dlf/test/GPGPUTest.cpp:716-733)."""
+    gb = _gb()
+    rng = np.random.default_rng(3)
+    A, B = _rand(rng, 96 * 80), _rand(rng, 80 * 72)
+    ref = np.zeros(96 * 72, np.float32)
+    oracle.gblas_sgemm(oracle.ROW_MAJOR, oracle.NO_TRANS, oracle.NO_TRANS, 96, 72, 80, 1.0, A, 0,
+                       80, B, 0, 72, 0.0, ref, 0, 72, wide=True)
+    dA, dB = torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda()
+    results = [None, None]
+
+    def work(i):
+        s = torch.cuda.Stream()
+        C = torch.zeros(96 * 72, device="cuda")
+        for _ in range(20):
+            gb.gemm(gb.Layout.RowMajor, gb.Transpose.NoTrans, gb.Transpose.NoTrans, 96, 72, 80,
+                    1.0, dA, 0, 80, dB, 0, 72, 0.0, C, 0, 72, queue=s)
+        s.synchronize()
+        results[i] = C.cpu().numpy()
+
+    ts = [threading.Thread(target=work, args=(i,)) for i in range(2)]
+    [t.start() for t in ts]
+    [t.join() for t in ts]
+    for r in results:
+        assert rel_fro(r, ref) <= FP32_TOL
+
+
+def test_event_brackets_the_launch():
+    gb = _gb()
+    a = torch.randn(512 * 512, device="cuda")
+    c = torch.empty(512 * 512, device="cuda")
+    ev = gb.Event()
+    gb.gemm(gb.Layout.RowMajor, gb.Transpose.NoTrans, gb.Transpose.NoTrans, 512, 512, 512, 1.0, a,
+            0, 512, a, 0, 512, 0.0, c, 0, 512, event=ev)
+    assert ev.elapsed_ms() > 0.0
