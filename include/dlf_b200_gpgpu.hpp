@@ -1,0 +1,313 @@
+// dlf_b200_gpgpu.hpp - C++ host side of the backend: the reference's template API for this path,
+// implemented over the C ABI of dlf_b200.h.
+//
+// Namespace dlf_b200::gpgpu holds
+//   * a small CUDA-runtime rendition of the plumbing types the reference's API is written
+//     against - Buffer<T> (gpgpu/include/gpgpu.h:639-698), Queue (:593-623), Event (:625-637),
+//     TemporaryBuffer<T> (:710-746) - so that this header can be built and tested on its own, and
+//   * blas::gemm / blas::gemmBatched / blas::gemmStridedBatched and dnn::conv2d with the
+//     reference's exact signatures (gpgpu/include/gblas.h:496-504, 661-683; gdnn.h:201-213).
+// Inside dlf itself the same four function bodies go where the CUBLAS(...) lambdas and cudnnConv
+// sit today; only the two `unwrap` helpers change (INTEGRATION.md shows the lines).
+//
+// Error behaviour follows the reference: argument errors throw BLASError carrying the StatusCode
+// (gpgpu/src/utilities/exceptions.hpp:24-35), CUDA failures throw APIError (gpgpu.h:21-121).
+// Buffer sizes are validated here (TestMatrixA/B/C, gpgpu/src/utilities/buffer_test.hpp:24-55)
+// because only the Buffer knows its size.
+#ifndef DLF_B200_GPGPU_HPP_
+#define DLF_B200_GPGPU_HPP_
+
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <memory>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "dlf_b200.h"
+
+namespace dlf_b200 {
+namespace gpgpu {
+
+class APIError : public std::runtime_error {
+public:
+    APIError(int status, const std::string& where)
+        : std::runtime_error(where + ": " + dlf_b200_status_string(status)), status_(status) {}
+    int status() const noexcept { return status_; }
+private:
+    int status_;
+};
+
+inline void check_cuda(cudaError_t e, const char* where) {
+    if (e != cudaSuccess) throw APIError(static_cast<int>(e), where);
+}
+
+// ---------------------------------------------------------------------------- Queue / Event
+class Event {
+public:
+    Event() {
+        check_cuda(cudaEventCreate(&start_), "cudaEventCreate");
+        check_cuda(cudaEventCreate(&end_), "cudaEventCreate");
+    }
+    ~Event() { cudaEventDestroy(start_); cudaEventDestroy(end_); }
+    Event(const Event&) = delete;
+    Event& operator=(const Event&) = delete;
+    void waitForCompletion() const { check_cuda(cudaEventSynchronize(end_), "cudaEventSynchronize"); }
+    float getElapsedTime() const {
+        waitForCompletion();
+        float ms = 0;
+        check_cuda(cudaEventElapsedTime(&ms, start_, end_), "cudaEventElapsedTime");
+        return ms;
+    }
+    cudaEvent_t start() const { return start_; }
+    cudaEvent_t end() const { return end_; }
+private:
+    cudaEvent_t start_{}, end_{};
+};
+
+class Queue {
+public:
+    Queue() {
+        auto s = new cudaStream_t;
+        check_cuda(cudaStreamCreateWithFlags(s, cudaStreamNonBlocking), "cudaStreamCreate");
+        stream_ = std::shared_ptr<cudaStream_t>(s, [](cudaStream_t* p) { cudaStreamDestroy(*p); delete p; });
+    }
+    void finish() const { check_cuda(cudaStreamSynchronize(*stream_), "cudaStreamSynchronize"); }
+    cudaStream_t unwrap() const { return *stream_; }
+private:
+    std::shared_ptr<cudaStream_t> stream_;
+};
+
+namespace current {
+inline const Queue& queue() {
+    thread_local Queue q;  // one queue per host thread (gpgpu/src/gpgpu.cpp:155-168)
+    return q;
+}
+}  // namespace current
+
+// ---------------------------------------------------------------------------- Buffer<T>
+template <typename T>
+class Buffer {
+public:
+    Buffer() = default;
+    explicit Buffer(size_t size) : size_(size) {
+        void* p = nullptr;
+        check_cuda(cudaMalloc(&p, (size ? size : 1) * sizeof(T)), "cudaMalloc");
+        mem_ = std::shared_ptr<void>(p, [](void* q) { cudaFree(q); });
+    }
+    size_t size() const noexcept { return size_; }
+    size_t data_size() const noexcept { return size_ * sizeof(T); }
+    void write(const Queue& q, const T* host, size_t n, size_t offset = 0) {
+        check_cuda(cudaMemcpyAsync(unwrap() + offset, host, n * sizeof(T), cudaMemcpyHostToDevice, q.unwrap()),
+                   "cudaMemcpyAsync");
+        q.finish();
+    }
+    void read(const Queue& q, T* host, size_t n, size_t offset = 0) const {
+        check_cuda(cudaMemcpyAsync(host, unwrap() + offset, n * sizeof(T), cudaMemcpyDeviceToHost, q.unwrap()),
+                   "cudaMemcpyAsync");
+        q.finish();
+    }
+    T* unwrap() const noexcept { return static_cast<T*>(mem_.get()); }
+private:
+    std::shared_ptr<void> mem_;
+    size_t size_ = 0;
+};
+
+// LIFO scratch taken from the context in the reference (gpgpu/src/gpgpu.cpp:189-214); here a
+// plain owned allocation with the same offset()/size() view.
+template <typename T>
+class TemporaryBuffer : public Buffer<T> {
+public:
+    TemporaryBuffer() = default;
+    explicit TemporaryBuffer(size_t size) : Buffer<T>(size) {}
+    size_t offset() const noexcept { return 0; }
+};
+
+// ---------------------------------------------------------------------------- blas
+namespace blas {
+
+enum class StatusCode {
+    kSuccess = 0, kInvalidValue = -30, kNotImplemented = -1024, kInvalidMatrixA = -1022,
+    kInvalidMatrixB = -1021, kInvalidMatrixC = -1020, kInvalidDimension = -1017,
+    kInvalidLeadDimA = -1016, kInvalidLeadDimB = -1015, kInvalidLeadDimC = -1014,
+    kInsufficientMemoryA = -1011, kInsufficientMemoryB = -1010, kInsufficientMemoryC = -1009,
+    kInsufficientMemoryTemp = -2050, kInvalidBatchCount = -2049, kUnexpectedError = -2039,
+};
+enum class Layout { RowMajor = 101, ColMajor = 102 };
+enum class Transpose { NoTrans = 111, Trans = 112, ConjTrans = 113 };
+
+class BLASError : public std::runtime_error {
+public:
+    explicit BLASError(StatusCode status)
+        : std::runtime_error(std::string("BLAS error: ") + dlf_b200_status_string(static_cast<int>(status))),
+          status_(status) {}
+    StatusCode status() const noexcept { return status_; }
+private:
+    StatusCode status_;
+};
+
+using half = __half;
+using bfloat16 = __nv_bfloat16;
+
+template <typename T> struct PrecisionOf;
+template <> struct PrecisionOf<float> { static constexpr int value = DLF_B200_SINGLE; };
+template <> struct PrecisionOf<half> { static constexpr int value = DLF_B200_HALF; };
+template <> struct PrecisionOf<bfloat16> { static constexpr int value = DLF_B200_BFLOAT16; };
+
+namespace detail {
+
+inline void raise(int rc, const char* where) {
+    if (rc == 0) return;
+    if (rc < 0) throw BLASError(static_cast<StatusCode>(rc));
+    throw APIError(rc, where);
+}
+
+struct Dims { size_t a_one, a_two, b_one, b_two, c_one, c_two; };
+
+// Xgemm<T>::ProcessArguments (gpgpu/src/routines/level3/xgemm.hpp:54-91)
+inline Dims process_arguments(Layout layout, Transpose ta, Transpose tb, size_t m, size_t n, size_t k) {
+    if (m == 0 || n == 0 || k == 0) throw BLASError(StatusCode::kInvalidDimension);
+    const bool row = layout == Layout::RowMajor;
+    const bool a_rot = (!row && ta != Transpose::NoTrans) || (row && ta == Transpose::NoTrans);
+    const bool b_rot = (!row && tb != Transpose::NoTrans) || (row && tb == Transpose::NoTrans);
+    return Dims{a_rot ? k : m, a_rot ? m : k, b_rot ? n : k, b_rot ? k : n, row ? n : m, row ? m : n};
+}
+
+// TestMatrixA/B/C (gpgpu/src/utilities/buffer_test.hpp:24-55)
+template <typename T>
+void test_matrix(size_t one, size_t two, const Buffer<T>& buf, size_t offset, size_t ld,
+                 StatusCode lead, StatusCode mem) {
+    if (ld < one) throw BLASError(lead);
+    if (buf.data_size() < (ld * (two - 1) + one + offset) * sizeof(T)) throw BLASError(mem);
+}
+
+struct EventScope {  // start/end events around the launch, like cuKernel::launch (gpgpu_cu.cpp:389-398)
+    EventScope(const Queue& q, Event* e) : q_(q), e_(e) { if (e_) cudaEventRecord(e_->start(), q_.unwrap()); }
+    ~EventScope() { if (e_) cudaEventRecord(e_->end(), q_.unwrap()); }
+    const Queue& q_;
+    Event* e_;
+};
+
+}  // namespace detail
+
+template <typename T>
+void gemm(const Layout layout, const Transpose a_transpose, const Transpose b_transpose,
+          const size_t m, const size_t n, const size_t k,
+          const T alpha,
+          const Buffer<T>& a_buffer, const size_t a_offset, const size_t a_ld,
+          const Buffer<T>& b_buffer, const size_t b_offset, const size_t b_ld,
+          const T beta,
+          Buffer<T>& c_buffer, const size_t c_offset, const size_t c_ld,
+          const Queue& queue = current::queue(), Event* event = nullptr) {
+    const auto d = detail::process_arguments(layout, a_transpose, b_transpose, m, n, k);
+    detail::test_matrix(d.a_one, d.a_two, a_buffer, a_offset, a_ld, StatusCode::kInvalidLeadDimA, StatusCode::kInsufficientMemoryA);
+    detail::test_matrix(d.b_one, d.b_two, b_buffer, b_offset, b_ld, StatusCode::kInvalidLeadDimB, StatusCode::kInsufficientMemoryB);
+    detail::test_matrix(d.c_one, d.c_two, c_buffer, c_offset, c_ld, StatusCode::kInvalidLeadDimC, StatusCode::kInsufficientMemoryC);
+    detail::EventScope scope(queue, event);
+    detail::raise(dlf_b200_gemm(PrecisionOf<T>::value, static_cast<int>(layout), static_cast<int>(a_transpose),
+                                static_cast<int>(b_transpose), m, n, k, &alpha,
+                                a_buffer.unwrap() + a_offset, a_ld, b_buffer.unwrap() + b_offset, b_ld, &beta,
+                                c_buffer.unwrap() + c_offset, c_ld, queue.unwrap()),
+                  "dlf_b200_gemm");
+}
+
+template <typename T>
+void gemmStridedBatched(const Layout layout, const Transpose a_transpose, const Transpose b_transpose,
+                        const size_t m, const size_t n, const size_t k,
+                        const T alpha,
+                        const Buffer<T>& a_buffer, const size_t a_offset, const size_t a_ld, const size_t a_stride,
+                        const Buffer<T>& b_buffer, const size_t b_offset, const size_t b_ld, const size_t b_stride,
+                        const T beta,
+                        Buffer<T>& c_buffer, const size_t c_offset, const size_t c_ld, const size_t c_stride,
+                        const size_t batch_count,
+                        const Queue& queue = current::queue(), Event* event = nullptr) {
+    if (batch_count < 1) throw BLASError(StatusCode::kInvalidBatchCount);
+    const auto d = detail::process_arguments(layout, a_transpose, b_transpose, m, n, k);
+    const size_t last = batch_count - 1;
+    detail::test_matrix(d.a_one, d.a_two, a_buffer, a_offset + last * a_stride, a_ld, StatusCode::kInvalidLeadDimA, StatusCode::kInsufficientMemoryA);
+    detail::test_matrix(d.b_one, d.b_two, b_buffer, b_offset + last * b_stride, b_ld, StatusCode::kInvalidLeadDimB, StatusCode::kInsufficientMemoryB);
+    detail::test_matrix(d.c_one, d.c_two, c_buffer, c_offset + last * c_stride, c_ld, StatusCode::kInvalidLeadDimC, StatusCode::kInsufficientMemoryC);
+    detail::EventScope scope(queue, event);
+    detail::raise(dlf_b200_gemm_strided_batched(
+                      PrecisionOf<T>::value, static_cast<int>(layout), static_cast<int>(a_transpose),
+                      static_cast<int>(b_transpose), m, n, k, &alpha, a_buffer.unwrap() + a_offset, a_ld, a_stride,
+                      b_buffer.unwrap() + b_offset, b_ld, b_stride, &beta, c_buffer.unwrap() + c_offset, c_ld,
+                      c_stride, batch_count, queue.unwrap()),
+                  "dlf_b200_gemm_strided_batched");
+}
+
+template <typename T>
+void gemmBatched(const Layout layout, const Transpose a_transpose, const Transpose b_transpose,
+                 const size_t m, const size_t n, const size_t k,
+                 const T* alphas,
+                 const Buffer<T>& a_buffer, const size_t* a_offsets, const size_t a_ld,
+                 const Buffer<T>& b_buffer, const size_t* b_offsets, const size_t b_ld,
+                 const T* betas,
+                 Buffer<T>& c_buffer, const size_t* c_offsets, const size_t c_ld,
+                 const size_t batch_count,
+                 const Queue& queue = current::queue(), Event* event = nullptr) {
+    if (batch_count < 1) throw BLASError(StatusCode::kInvalidBatchCount);
+    const auto d = detail::process_arguments(layout, a_transpose, b_transpose, m, n, k);
+    for (size_t i = 0; i < batch_count; ++i) {
+        detail::test_matrix(d.a_one, d.a_two, a_buffer, a_offsets[i], a_ld, StatusCode::kInvalidLeadDimA, StatusCode::kInsufficientMemoryA);
+        detail::test_matrix(d.b_one, d.b_two, b_buffer, b_offsets[i], b_ld, StatusCode::kInvalidLeadDimB, StatusCode::kInsufficientMemoryB);
+        detail::test_matrix(d.c_one, d.c_two, c_buffer, c_offsets[i], c_ld, StatusCode::kInvalidLeadDimC, StatusCode::kInsufficientMemoryC);
+    }
+    // scratch for the per-batch tables: the reference takes its equivalents from the context's
+    // temporary-buffer pool (gpgpu/src/gblas.cpp:2972-2988)
+    TemporaryBuffer<unsigned char> work(dlf_b200_gemm_batched_workspace_bytes(batch_count));
+    detail::EventScope scope(queue, event);
+    detail::raise(dlf_b200_gemm_batched(
+                      PrecisionOf<T>::value, static_cast<int>(layout), static_cast<int>(a_transpose),
+                      static_cast<int>(b_transpose), m, n, k, alphas, a_buffer.unwrap(), a_offsets, a_ld,
+                      b_buffer.unwrap(), b_offsets, b_ld, betas, c_buffer.unwrap(), c_offsets, c_ld, batch_count,
+                      work.unwrap(), work.data_size(), queue.unwrap()),
+                  "dlf_b200_gemm_batched");
+    queue.finish();  // `work` is released on return
+}
+
+}  // namespace blas
+
+// ---------------------------------------------------------------------------- dnn
+namespace dnn {
+
+// gpgpu::dnn::conv2d (gpgpu/include/gdnn.h:201-213). `bias` is an addition (default: none): the
+// reference adds it in a separate pass (dlf/include/predict.h:1272-1281).
+template <typename T>
+void conv2d(const size_t batches, const size_t channels,
+            const size_t height, const size_t width,
+            const size_t output_h, const size_t output_w,
+            const size_t num_kernels, const size_t group,
+            const size_t kernel_h, const size_t kernel_w,
+            const size_t pad_top, const size_t pad_left,
+            const size_t pad_bottom, const size_t pad_right,
+            const size_t stride_h, const size_t stride_w,
+            const size_t dilation_h, const size_t dilation_w,
+            const Buffer<T>& im_buffer, const Buffer<T>& kernel_buffer,
+            Buffer<T>& result_buffer,
+            const Queue& queue = current::queue(), Event* event = nullptr,
+            const Buffer<T>* bias = nullptr) {
+    using blas::BLASError;
+    using blas::StatusCode;
+    if (group == 0 || channels % group != 0 || num_kernels % group != 0) throw BLASError(StatusCode::kInvalidDimension);
+    if (im_buffer.size() < batches * channels * height * width) throw BLASError(StatusCode::kInsufficientMemoryA);
+    if (kernel_buffer.size() < num_kernels * (channels / group) * kernel_h * kernel_w) throw BLASError(StatusCode::kInsufficientMemoryB);
+    if (result_buffer.size() < batches * num_kernels * output_h * output_w) throw BLASError(StatusCode::kInsufficientMemoryC);
+    if (bias && bias->size() < num_kernels) throw BLASError(StatusCode::kInvalidValue);
+    blas::detail::EventScope scope(queue, event);
+    blas::detail::raise(dlf_b200_conv2d(blas::PrecisionOf<T>::value, batches, channels, height, width, output_h,
+                                        output_w, num_kernels, group, kernel_h, kernel_w, pad_top, pad_left,
+                                        pad_bottom, pad_right, stride_h, stride_w, dilation_h, dilation_w,
+                                        im_buffer.unwrap(), kernel_buffer.unwrap(), bias ? bias->unwrap() : nullptr,
+                                        result_buffer.unwrap(), nullptr, 0, queue.unwrap()),
+                        "dlf_b200_conv2d");
+}
+
+}  // namespace dnn
+}  // namespace gpgpu
+}  // namespace dlf_b200
+
+#endif  // DLF_B200_GPGPU_HPP_

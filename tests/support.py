@@ -43,7 +43,7 @@ def _slice(t, spec):
             idx.append(slice(i, i + 1 if i != -1 else None))
     if any(isinstance(i, slice) and i.step is not None and i.step < 0 for i in idx):
         # torch has no negative strides; the reference reorders such operands on the GPU anyway
-        return torch.from_numpy(np.ascontiguousarray(t.numpy()[tuple(idx)]))
+        return torch.from_numpy(np.ascontiguousarray(t.cpu().numpy()[tuple(idx)])).to(t.device)
     return t[tuple(idx)]
 
 
