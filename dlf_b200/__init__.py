@@ -97,4 +97,4 @@ def launch_count():
 
 
 def set_tuning(force_bn=0, force_generic_loader=False):
-    lib().dlf_b200_set_tuning(int(force_bn), 1 if force_generic_loader else 0)
+    lib().dlf_b200_set_tuning(int(force_bn), int(force_generic_loader))

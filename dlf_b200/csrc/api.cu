@@ -17,6 +17,7 @@
 
 #include "../../include/dlf_b200.h"
 #include "contraction.cuh"
+#include "contraction_ts.cuh"
 
 using namespace dlfb200;
 
@@ -50,6 +51,8 @@ struct DeviceState {
     int static_smem_tma = 0;
     int static_smem_gen2 = 0;
     int static_smem_gen4 = 0;
+    int static_smem_ts2 = 0;
+    int static_smem_ts4 = 0;
     PFN_cuTensorMapEncodeTiled_v12000 encode = nullptr;
 };
 
@@ -92,6 +95,16 @@ int ensure_device(DeviceState** out) {
         CUDA_TRY(cudaFuncSetAttribute(contraction_kernel<4, false>,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       kSmemPerBlockOptin - st.static_smem_gen4));
+        CUDA_TRY(cudaFuncGetAttributes(&fa, contraction_ts_kernel<2>));
+        st.static_smem_ts2 = static_cast<int>(fa.sharedSizeBytes);
+        CUDA_TRY(cudaFuncGetAttributes(&fa, contraction_ts_kernel<4>));
+        st.static_smem_ts4 = static_cast<int>(fa.sharedSizeBytes);
+        CUDA_TRY(cudaFuncSetAttribute(contraction_ts_kernel<2>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      kSmemPerBlockOptin - st.static_smem_ts2));
+        CUDA_TRY(cudaFuncSetAttribute(contraction_ts_kernel<4>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      kSmemPerBlockOptin - st.static_smem_ts4));
         void* fn = nullptr;
         cudaDriverEntryPointQueryResult qres;
         CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
@@ -191,6 +204,79 @@ int encode_map(const DeviceState& st, CUtensorMap* map, const GenOperand& op, in
     return r == CUDA_SUCCESS ? kSuccess : kUnexpectedError;
 }
 
+int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
+    const int a_cols = q.es == 4 ? 64 : 32;
+    const int BK = 128 / q.es;
+    const long long tiles_m = (q.M + kBM - 1) / kBM;
+    int bn = q.N <= 64 ? 64 : (q.N <= 128 ? 128 : 256);
+    auto tiles_for = [&](int w) { return q.batch * tiles_m * ((q.N + w - 1) / w); };
+    while (bn > 64 && tiles_for(bn) < st.num_sms) bn /= 2;
+    const int forced = g_force_bn.load();
+    if (forced == 64 || forced == 128 || forced == 256) bn = forced;
+    const long long tiles_n = (q.N + bn - 1) / bn;
+    const long long total = q.batch * tiles_m * tiles_n;
+
+    const int acc_bufs = (2 * bn + 2 * a_cols <= 512) ? 2 : 1;
+    const long long num_kb = (q.K + BK - 1) / BK;
+    int ktable_bytes = 0;
+    if (q.a.im2col) {
+        const long long need = num_kb * BK * static_cast<long long>(sizeof(KEntry));
+        if (need > 96 * 1024) return kNotImplemented;  // caller falls back to the smem-A kernel
+        ktable_bytes = static_cast<int>((need + 15) & ~15ll);
+    }
+    const int static_smem = q.es == 2 ? st.static_smem_ts2 : st.static_smem_ts4;
+    const int stage_bytes = bn * 128 * (q.es == 4 ? 2 : 1);
+    int stages = (kSmemPerBlockOptin - static_smem - 1024 - ktable_bytes) / stage_bytes;
+    const int tmem_stages = (512 - acc_bufs * bn) / a_cols;
+    if (stages > tmem_stages) stages = tmem_stages;
+    if (stages > kMaxStages) stages = kMaxStages;
+    if (stages < 2) return kUnexpectedError;
+    size_t dyn_smem = static_cast<size_t>(stages) * stage_bytes + 1024 + ktable_bytes;
+    // more than half of the SM's shared memory: never two CTAs (and two 512-column TMEM
+    // allocations) on one SM
+    if (dyn_smem < 120 * 1024) dyn_smem = 120 * 1024;
+
+    TsParams tp{};
+    Params& p = tp.base;
+    p.M = static_cast<int>(q.M);
+    p.N = static_cast<int>(q.N);
+    p.K = static_cast<int>(q.K);
+    p.batch = static_cast<int>(q.batch);
+    p.BN = bn;
+    p.stages = stages;
+    p.fmt = q.fmt;
+    p.tiles_m = static_cast<int>(tiles_m);
+    p.tiles_n = static_cast<int>(tiles_n);
+    p.total_tiles = total;
+    p.alpha = q.alpha;
+    p.beta = q.beta;
+    p.a = q.a;
+    p.b = q.b;
+    p.d = q.d;
+    p.ldd = q.ldd;
+    p.d_batch_stride = q.d_batch_stride;
+    p.a_offs = q.a_offs;
+    p.b_offs = q.b_offs;
+    p.d_offs = q.d_offs;
+    p.alphas = q.alphas;
+    p.betas = q.betas;
+    p.bias = q.bias;
+    p.g = q.g;
+    p.status = st.status;
+    tp.a_kind = q.a.im2col ? A_IM2COL : (q.a.k_major ? A_DENSE_K : A_DENSE_MN);
+    tp.acc_bufs = acc_bufs;
+    tp.ktable_bytes = ktable_bytes;
+
+    const unsigned grid = static_cast<unsigned>(total < st.num_sms ? total : st.num_sms);
+    if (q.es == 2)
+        contraction_ts_kernel<2><<<grid, kTsThreads, dyn_smem, stream>>>(tp);
+    else
+        contraction_ts_kernel<4><<<grid, kTsThreads, dyn_smem, stream>>>(tp);
+    g_launches.fetch_add(1);
+    CUDA_TRY(cudaGetLastError());
+    return kSuccess;
+}
+
 int launch(const Problem& q, cudaStream_t stream) {
     DeviceState* st = nullptr;
     int rc = ensure_device(&st);
@@ -201,6 +287,12 @@ int launch(const Problem& q, cudaStream_t stream) {
     const bool use_tma = q.es == 2 && !g_force_generic.load() && q.a_offs == nullptr &&
                          tma_ok(q.a, q.es, q.M, q.K, q.batch) &&
                          tma_ok(q.b, q.es, q.N, q.K, q.batch);
+    // A through tensor memory: every convolution and every fp32 product (see contraction_ts.cuh)
+    const int force_path = g_force_generic.load();
+    if (force_path != 2 && !use_tma && (q.a.im2col || q.es == 4 || force_path == 3)) {
+        rc = launch_ts(*st, q, stream);
+        if (rc != kNotImplemented) return rc;  // else: im2col table too large, use the smem-A kernel
+    }
 
     const long long tiles_m = (q.M + kBM - 1) / kBM;
     int bn = q.N <= 64 ? 64 : (q.N <= 128 ? 128 : 256);

@@ -36,6 +36,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include "epilogue.cuh"
 #include "ptx.cuh"
 
 namespace dlfb200 {
@@ -221,27 +222,6 @@ __device__ __forceinline__ void store_chunk(uint32_t tile, uint32_t lo_tile, int
     }
 }
 
-template <int ES>
-__device__ __forceinline__ void store_out(char* ptr, float v, int fmt) {
-    if constexpr (ES == 4) {
-        *reinterpret_cast<float*>(ptr) = v;
-    } else {
-        if (fmt == FMT_F16)
-            *reinterpret_cast<__half*>(ptr) = __float2half_rn(v);
-        else
-            *reinterpret_cast<__nv_bfloat16*>(ptr) = __float2bfloat16_rn(v);
-    }
-}
-template <int ES>
-__device__ __forceinline__ float load_out(const char* ptr, int fmt) {
-    if constexpr (ES == 4) {
-        return *reinterpret_cast<const float*>(ptr);
-    } else {
-        if (fmt == FMT_F16) return __half2float(*reinterpret_cast<const __half*>(ptr));
-        return __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(ptr));
-    }
-}
-
 template <int ES, bool USE_TMA>
 __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
     contraction_kernel(const __grid_constant__ Params p, const __grid_constant__ CUtensorMap tmA,
@@ -330,27 +310,21 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
             }
             const float alpha = p.alphas ? p.alphas[b] : p.alpha;
             const float beta = p.betas ? p.betas[b] : p.beta;
-            const char* bias = p.bias ? p.bias + static_cast<long long>(b) * p.N * ES : nullptr;
+            const char* bias =
+                p.bias ? p.bias + (static_cast<long long>(b) * p.N + n0) * ES : nullptr;
             const uint32_t trow = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + buf * BN;
-
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                if (n0 + c0 >= p.N) break;
-                uint32_t v[32];
-                ptx::tmem_ld_32x32(trow + c0, v);
-                ptx::tmem_ld_wait();
-                if (row_ok) {
-#pragma unroll
-                    for (int jj = 0; jj < 32; ++jj) {
-                        const int j = n0 + c0 + jj;
-                        if (j < p.N) {
-                            char* optr = p.d + (rowbase + static_cast<long long>(j) * colstride) * ES;
-                            float r = alpha * __uint_as_float(v[jj]);
-                            if (beta != 0.0f) r += beta * load_out<ES>(optr, p.fmt);
-                            if (bias) r += load_out<ES>(bias + static_cast<long long>(j) * ES, p.fmt);
-                            store_out<ES>(optr, r, p.fmt);
-                        }
-                    }
-                }
+            char* optr = p.d + (rowbase + static_cast<long long>(n0) * colstride) * ES;
+            const int ncols = min(BN, p.N - n0);
+            if constexpr (ES == 4) {
+                epilogue_dispatch<OUT_F32>(trow, ncols, optr, colstride * ES, row_ok, alpha, beta,
+                                           bias, lane);
+            } else {
+                if (p.fmt == FMT_F16)
+                    epilogue_dispatch<OUT_F16>(trow, ncols, optr, colstride * ES, row_ok, alpha,
+                                               beta, bias, lane);
+                else
+                    epilogue_dispatch<OUT_BF16>(trow, ncols, optr, colstride * ES, row_ok, alpha,
+                                                beta, bias, lane);
             }
             ptx::tc_fence_before();
             ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));

@@ -1,0 +1,464 @@
+// Contraction kernel whose A operand lives in tensor memory ("TS" form of tcgen05.mma).
+//
+// Same canonical problem as contraction.cuh:
+//     D[i + j*ldd] = alpha * sum_k Au(i,k) * Bu(j,k) + beta * D (+ bias[j])
+// but the 128 x BK tile of Au never touches shared memory. Eight producer warps own the 128
+// TMEM lanes (two warps per 32-lane quadrant, alternating k-blocks); thread <-> row i of the
+// tile. Each thread loads its row's BK values straight from global memory into registers -
+// for an MN-major Au and for the implicit im2col view of an NCHW tensor the 32 lanes of a warp
+// read 32 consecutive addresses - splits fp32 values into tf32 (hi, lo) in registers, and writes
+// them to TMEM with tcgen05.st. The UMMA issuer then runs tcgen05.mma with A = [tmem] and
+// B = shared-memory descriptor. Only Bu (for convolutions: the filter bank) is staged in
+// swizzled shared memory, by four loader warps.
+//
+// Why: with both operands in shared memory a 3xTF32 tile reads each operand three times and
+// writes hi and lo copies of both; for the 128 x 64 tiles of a 64-channel convolution that is
+// more shared-memory traffic than the tensor pipe can be fed with. Moving A to TMEM removes
+// two thirds of it and all the address swizzling from the gather.
+//
+// Convolution (im2col) gather: k = (c*KH + kh)*KW + kw. A per-CTA table in shared memory holds,
+// for every k, the element offset c*H*W + kh*dh*W + kw*dw and (kh*dh, kw*dw); a thread keeps
+// its pixel's (ih0, iw0, base offset) in registers and a tap is valid when
+// 0 <= ih0 + kh*dh < H and 0 <= iw0 + kw*dw < W (zero otherwise: the padding).
+//
+// TMEM columns: [0, acc_bufs*BN) accumulators, then `stages` A slots of 32 (16-bit types: 64 k
+// packed two per column) or 64 (fp32: 32 hi + 32 lo) columns.
+// Warp roles: 0-3 epilogue, 4-11 A producers (quadrant = warp % 4), 12-14 B loaders, 15 UMMA
+// issuer and TMEM owner.
+#pragma once
+#include "contraction.cuh"
+
+namespace dlfb200 {
+
+constexpr int kTsProducerWarp0 = 4;
+constexpr int kTsLoaderWarp0 = 12;
+constexpr int kTsMmaWarp = 15;
+constexpr int kTsThreads = 16 * 32;  // 512 threads: 128 registers each
+constexpr int kTsLoaderThreads = 3 * 32;
+constexpr int kTsLoaderLines = kTsLoaderThreads / 8;  // lines covered per pass of the B loaders
+
+enum : int { A_DENSE_MN = 0, A_DENSE_K = 1, A_IM2COL = 2 };
+
+struct KEntry {  // one k of the implicit im2col operand
+    int off;     // c*H*W + kh*dh*W + kw*dw
+    short dy;    // kh*dh
+    short dx;    // kw*dw
+};
+
+struct TsParams {
+    Params base;
+    int a_kind;
+    int acc_bufs;      // 1 or 2 accumulator buffers in TMEM
+    int ktable_bytes;  // bytes reserved at the start of dynamic shared memory for KEntry[k]
+};
+
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        :
+        : "r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]),
+          "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]),
+          "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]),
+          "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]),
+          "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() {
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem desc]
+__device__ __forceinline__ void umma_ts_f16(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc,
+                                            uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+        "}"
+        :
+        : "r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_ts_tf32(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc,
+                                             uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t"
+        "}"
+        :
+        : "r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+template <int ES>
+__global__ void __launch_bounds__(kTsThreads, 1)
+    contraction_ts_kernel(const __grid_constant__ TsParams tp) {
+    const Params& p = tp.base;
+    constexpr int BK = 128 / ES;             // k per stage: 32 (fp32) or 64 (16-bit)
+    constexpr int CPE = 16 / ES;
+    constexpr int UMMA_K = 32 / ES;
+    constexpr int A_COLS = ES == 4 ? 64 : 32;  // TMEM columns per A slot
+    constexpr int A_KSTEP_COLS = 8;            // columns one UMMA k-step consumes
+    constexpr uint32_t KSTEP_K = 32;
+    constexpr uint32_t KSTEP_MN = (UMMA_K / 8) * 1024;
+
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t full_a[kMaxStages];
+    __shared__ __align__(8) uint64_t full_b[kMaxStages];
+    __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
+    __shared__ __align__(8) uint64_t tfull_bar[2];
+    __shared__ __align__(8) uint64_t tempty_bar[2];
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int BN = p.BN;
+    const int S = p.stages;
+    const int nbuf = tp.acc_bufs;
+    const uint32_t b_tile = static_cast<uint32_t>(BN) * 128u;
+    const uint32_t stage_bytes = b_tile * (ES == 4 ? 2u : 1u);
+    const KEntry* ktable = reinterpret_cast<const KEntry*>(smem_raw);
+    const uint32_t smem0 =
+        (ptx::smem_u32(smem_raw) + static_cast<uint32_t>(tp.ktable_bytes) + 1023u) & ~1023u;
+    const int num_kb = (p.K + BK - 1) / BK;
+    const uint32_t a_col0 = static_cast<uint32_t>(nbuf * BN);
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < S; ++s) {
+            ptx::mbar_init(ptx::smem_u32(&full_a[s]), 128u);
+            ptx::mbar_init(ptx::smem_u32(&full_b[s]), kTsLoaderThreads);
+            ptx::mbar_init(ptx::smem_u32(&empty_bar[s]), 1u);
+        }
+        for (int i = 0; i < 2; ++i) {
+            ptx::mbar_init(ptx::smem_u32(&tfull_bar[i]), 1u);
+            ptx::mbar_init(ptx::smem_u32(&tempty_bar[i]), 128u);
+        }
+        ptx::fence_mbar_init();
+    }
+    if (tp.a_kind == A_IM2COL) {
+        // k -> (offset, dy, dx) table, filled cooperatively; k beyond K is never read as valid
+        KEntry* kt = reinterpret_cast<KEntry*>(smem_raw);
+        const int khw = p.g.KH * p.g.KW;
+        for (int k = threadIdx.x; k < num_kb * BK; k += blockDim.x) {
+            KEntry e;
+            const int kk = k < p.K ? k : 0;
+            const int ch = kk / khw;
+            const int rem = kk - ch * khw;
+            const int kh = rem / p.g.KW;
+            const int kw = rem - kh * p.g.KW;
+            e.off = (ch * p.g.H + kh * p.g.dh) * p.g.W + kw * p.g.dw;
+            e.dy = static_cast<short>(kh * p.g.dh);
+            e.dx = static_cast<short>(kw * p.g.dw);
+            kt[k] = e;
+        }
+    }
+    if (warp == kTsMmaWarp) {
+        __syncwarp();
+        ptx::tmem_alloc(ptx::smem_u32(&tmem_slot), 512u);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&tmem_slot);
+    volatile int* abort_p = &abort_flag;
+
+    if (warp < 4) {
+        // ------------------------------------------------------------ epilogue
+        long long it = 0;
+        for (long long t = blockIdx.x; t < p.total_tiles; t += gridDim.x, ++it) {
+            int b, m0, n0;
+            decode_tile(p, t, b, m0, n0);
+            const uint32_t buf = static_cast<uint32_t>(it % nbuf);
+            const uint32_t tphase = static_cast<uint32_t>((it / nbuf) & 1);
+            const bool w = ptx::mbar_wait_bounded(ptx::smem_u32(&tfull_bar[buf]), tphase, abort_p);
+            if (!__all_sync(0xffffffffu, w)) break;
+            ptx::tc_fence_after();
+            const int i = m0 + warp * 32 + lane;
+            const bool row_ok = i < p.M;
+            long long rowbase, colstride;
+            if (tp.a_kind == A_IM2COL) {
+                const int img = i / p.g.P;
+                const int pp = i - img * p.g.P;
+                rowbase = static_cast<long long>(img) * p.g.out_img_stride +
+                          static_cast<long long>(b) * p.d_batch_stride + pp;
+                colstride = p.g.P;
+            } else {
+                rowbase = (p.d_offs ? p.d_offs[b] : static_cast<long long>(b) * p.d_batch_stride) + i;
+                colstride = p.ldd;
+            }
+            const float alpha = p.alphas ? p.alphas[b] : p.alpha;
+            const float beta = p.betas ? p.betas[b] : p.beta;
+            const char* bias =
+                p.bias ? p.bias + (static_cast<long long>(b) * p.N + n0) * ES : nullptr;
+            const uint32_t trow = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + buf * BN;
+            char* optr = p.d + (rowbase + static_cast<long long>(n0) * colstride) * ES;
+            const int ncols = min(BN, p.N - n0);
+            if constexpr (ES == 4) {
+                epilogue_dispatch<OUT_F32>(trow, ncols, optr, colstride * ES, row_ok, alpha, beta,
+                                           bias, lane);
+            } else {
+                if (p.fmt == FMT_F16)
+                    epilogue_dispatch<OUT_F16>(trow, ncols, optr, colstride * ES, row_ok, alpha,
+                                               beta, bias, lane);
+                else
+                    epilogue_dispatch<OUT_BF16>(trow, ncols, optr, colstride * ES, row_ok, alpha,
+                                                beta, bias, lane);
+            }
+            ptx::tc_fence_before();
+            ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));
+        }
+    } else if (warp >= kTsProducerWarp0 && warp < kTsLoaderWarp0) {
+        // ------------------------------------------------------------ A producers (-> TMEM)
+        const int q = warp & 3;                          // TMEM lane quadrant this warp may access
+        const int par = (warp - kTsProducerWarp0) >> 2;  // which k-blocks (global parity) it takes
+        const uint32_t lane_base = static_cast<uint32_t>(q * 32) << 16;
+        long long g = 0;  // k-blocks issued by this CTA so far
+        bool ok = true;
+        for (long long t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x) {
+            int b, m0, n0;
+            decode_tile(p, t, b, m0, n0);
+            const long long a_boff =
+                p.a_offs ? p.a_offs[b] : static_cast<long long>(b) * p.a.batch_stride;
+            const int i = m0 + q * 32 + lane;
+            const bool row_ok = i < p.M;
+            long long pbase = 0;
+            int ih0 = -(1 << 30), iw0 = -(1 << 30);
+            if (tp.a_kind == A_IM2COL) {
+                if (row_ok) {
+                    const int img = i / p.g.P;
+                    const int pp = i - img * p.g.P;
+                    const int oh = pp / p.g.OW;
+                    const int ow = pp - oh * p.g.OW;
+                    ih0 = oh * p.g.sh - p.g.pad_t;
+                    iw0 = ow * p.g.sw - p.g.pad_l;
+                    pbase = a_boff + static_cast<long long>(img) * p.g.img_stride +
+                            static_cast<long long>(ih0) * p.g.W + iw0;
+                }
+            } else if (tp.a_kind == A_DENSE_MN) {
+                pbase = a_boff + i;
+            } else {
+                pbase = a_boff + static_cast<long long>(i) * p.a.ld;
+            }
+            for (int kb = 0; kb < num_kb; ++kb, ++g) {
+                if ((g & 1) != par) continue;
+                const int k0 = kb * BK;
+                const int kcount = min(BK, p.K - k0);
+                uint32_t v[32];  // fp32: raw values; 16-bit: two k per register (low half first)
+                if (tp.a_kind == A_IM2COL) {
+                    const KEntry* te = ktable + k0;
+                    if constexpr (ES == 4) {
+                        const uint32_t* x = reinterpret_cast<const uint32_t*>(p.a.base);
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const KEntry e = te[j];
+                            const bool in = j < kcount &&
+                                            static_cast<unsigned>(ih0 + e.dy) < static_cast<unsigned>(p.g.H) &&
+                                            static_cast<unsigned>(iw0 + e.dx) < static_cast<unsigned>(p.g.W);
+                            v[j] = in ? x[pbase + e.off] : 0u;
+                        }
+                    } else {
+                        const unsigned short* x = reinterpret_cast<const unsigned short*>(p.a.base);
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const KEntry e0 = te[2 * j], e1 = te[2 * j + 1];
+                            const bool in0 = 2 * j < kcount &&
+                                             static_cast<unsigned>(ih0 + e0.dy) < static_cast<unsigned>(p.g.H) &&
+                                             static_cast<unsigned>(iw0 + e0.dx) < static_cast<unsigned>(p.g.W);
+                            const bool in1 = 2 * j + 1 < kcount &&
+                                             static_cast<unsigned>(ih0 + e1.dy) < static_cast<unsigned>(p.g.H) &&
+                                             static_cast<unsigned>(iw0 + e1.dx) < static_cast<unsigned>(p.g.W);
+                            const uint32_t lo = in0 ? x[pbase + e0.off] : 0u;
+                            const uint32_t hi = in1 ? x[pbase + e1.off] : 0u;
+                            v[j] = lo | (hi << 16);
+                        }
+                    }
+                } else if (tp.a_kind == A_DENSE_MN) {
+                    if constexpr (ES == 4) {
+                        const uint32_t* x = reinterpret_cast<const uint32_t*>(p.a.base) + pbase;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            v[j] = (row_ok && j < kcount) ? x[static_cast<long long>(k0 + j) * p.a.ld] : 0u;
+                    } else {
+                        const unsigned short* x = reinterpret_cast<const unsigned short*>(p.a.base) + pbase;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const uint32_t lo = (row_ok && 2 * j < kcount)
+                                                    ? x[static_cast<long long>(k0 + 2 * j) * p.a.ld] : 0u;
+                            const uint32_t hi = (row_ok && 2 * j + 1 < kcount)
+                                                    ? x[static_cast<long long>(k0 + 2 * j + 1) * p.a.ld] : 0u;
+                            v[j] = lo | (hi << 16);
+                        }
+                    }
+                } else {  // A_DENSE_K: this thread's row is contiguous along k
+                    const char* x = p.a.base + (pbase + k0) * ES;
+                    const bool vec = row_ok && kcount == BK && (reinterpret_cast<uintptr_t>(x) & 15u) == 0u;
+                    if (vec) {
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) {
+                            const uint4 u = reinterpret_cast<const uint4*>(x)[c];
+                            v[4 * c + 0] = u.x;
+                            v[4 * c + 1] = u.y;
+                            v[4 * c + 2] = u.z;
+                            v[4 * c + 3] = u.w;
+                        }
+                    } else if constexpr (ES == 4) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            v[j] = (row_ok && j < kcount) ? reinterpret_cast<const uint32_t*>(x)[j] : 0u;
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const uint32_t lo = (row_ok && 2 * j < kcount)
+                                                    ? reinterpret_cast<const unsigned short*>(x)[2 * j] : 0u;
+                            const uint32_t hi = (row_ok && 2 * j + 1 < kcount)
+                                                    ? reinterpret_cast<const unsigned short*>(x)[2 * j + 1] : 0u;
+                            v[j] = lo | (hi << 16);
+                        }
+                    }
+                }
+                const uint32_t s = static_cast<uint32_t>(g % S);
+                const uint32_t ph = static_cast<uint32_t>((g / S) & 1);
+                const bool w = ptx::mbar_wait_bounded(ptx::smem_u32(&empty_bar[s]), ph ^ 1u, abort_p);
+                if (!__all_sync(0xffffffffu, w)) {
+                    ok = false;
+                    break;
+                }
+                ptx::tc_fence_after();
+                const uint32_t slot = tmem_base + lane_base + a_col0 + s * A_COLS;
+                if constexpr (ES == 4) {
+                    uint32_t lo[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) split_tf32(v[j], v[j], lo[j]);
+                    tmem_st_32x32(slot, v);
+                    tmem_st_32x32(slot + 32, lo);
+                } else {
+                    tmem_st_32x32(slot, v);
+                }
+                tmem_st_wait();
+                ptx::tc_fence_before();
+                ptx::mbar_arrive(ptx::smem_u32(&full_a[s]));
+            }
+        }
+    } else if (warp >= kTsLoaderWarp0 && warp < kTsMmaWarp) {
+        // ------------------------------------------------------------ B loaders (-> swizzled smem)
+        const int lt = threadIdx.x - kTsLoaderWarp0 * 32;
+        const int c = lt & 7;
+        const int l0 = lt >> 3;  // 0..kTsLoaderLines-1
+        const bool b_atom32 = ES == 4 && !p.b.k_major;
+        long long g = 0;
+        bool ok = true;
+        for (long long t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x) {
+            int b, m0, n0;
+            decode_tile(p, t, b, m0, n0);
+            const long long b_boff =
+                p.b_offs ? p.b_offs[b] : static_cast<long long>(b) * p.b.batch_stride;
+            for (int kb = 0; kb < num_kb; ++kb, ++g) {
+                const uint32_t s = static_cast<uint32_t>(g % S);
+                const uint32_t ph = static_cast<uint32_t>((g / S) & 1);
+                const bool w = ptx::mbar_wait_bounded(ptx::smem_u32(&empty_bar[s]), ph ^ 1u, abort_p);
+                if (!__all_sync(0xffffffffu, w)) {
+                    ok = false;
+                    break;
+                }
+                const uint32_t sB = smem0 + s * stage_bytes;
+                for (int L0 = l0; L0 < BN; L0 += 4 * kTsLoaderLines) {
+                    uint4 v[4];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const int L = L0 + q * kTsLoaderLines;
+                        if (L >= BN) {
+                            v[q] = make_uint4(0u, 0u, 0u, 0u);
+                        } else if (p.b.k_major) {
+                            v[q] = load_chunk_dense<ES>(p.b, b_boff, n0 + L, p.N, kb * BK + c * CPE, p.K);
+                        } else {
+                            v[q] = load_chunk_dense<ES>(p.b, b_boff, kb * BK + (L % BK), p.K,
+                                                        n0 + (L / BK) * BK + c * CPE, p.N);
+                        }
+                    }
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const int L = L0 + q * kTsLoaderLines;
+                        if (L < BN) store_chunk<ES>(sB, sB + b_tile, L, c, v[q], b_atom32);
+                    }
+                }
+                ptx::fence_proxy_async_smem();
+                ptx::mbar_arrive(ptx::smem_u32(&full_b[s]));
+            }
+        }
+    } else if (warp == kTsMmaWarp) {
+        // ------------------------------------------------------------ UMMA issuer
+        if (lane == 0) {
+            const uint32_t idesc =
+                ptx::make_idesc(p.fmt == FMT_F32 ? 2u : static_cast<uint32_t>(p.fmt), 0u,
+                                p.b.k_major ? 0u : 1u, kBM, BN);
+            const uint32_t b_step = p.b.k_major ? KSTEP_K : KSTEP_MN;
+            const uint32_t b_lbo = p.b.k_major ? 16u : static_cast<uint32_t>(BK) * 128u;
+            const uint32_t b_mode = (ES == 4 && !p.b.k_major) ? 1u : 2u;
+            const uint32_t b_sbo = b_mode == 1u ? 512u : 1024u;
+            long long g = 0, it = 0;
+            bool ok = true;
+            for (long long t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x, ++it) {
+                const uint32_t buf = static_cast<uint32_t>(it % nbuf);
+                const uint32_t tphase = static_cast<uint32_t>((it / nbuf) & 1);
+                if (!ptx::mbar_wait_bounded(ptx::smem_u32(&tempty_bar[buf]), tphase ^ 1u, abort_p)) {
+                    ok = false;
+                    break;
+                }
+                ptx::tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (int kb = 0; kb < num_kb; ++kb, ++g) {
+                    const uint32_t s = static_cast<uint32_t>(g % S);
+                    const uint32_t ph = static_cast<uint32_t>((g / S) & 1);
+                    if (!ptx::mbar_wait_bounded(ptx::smem_u32(&full_a[s]), ph, abort_p) ||
+                        !ptx::mbar_wait_bounded(ptx::smem_u32(&full_b[s]), ph, abort_p)) {
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after();
+                    const uint32_t sB = smem0 + s * stage_bytes;
+                    const uint32_t a_slot = tmem_base + a_col0 + s * A_COLS;
+#pragma unroll
+                    for (int ks = 0; ks < BK / UMMA_K; ++ks) {
+                        const uint64_t db = ptx::make_smem_desc(sB + ks * b_step, b_lbo, b_sbo, b_mode);
+                        const uint32_t acc = (kb | ks) ? 1u : 0u;
+                        const uint32_t a_hi = a_slot + ks * A_KSTEP_COLS;
+                        if constexpr (ES == 2) {
+                            umma_ts_f16(d_tmem, a_hi, db, idesc, acc);
+                        } else {
+                            const uint64_t db_lo =
+                                ptx::make_smem_desc(sB + b_tile + ks * b_step, b_lbo, b_sbo, b_mode);
+                            umma_ts_tf32(d_tmem, a_hi + 32, db, idesc, acc);
+                            umma_ts_tf32(d_tmem, a_hi, db_lo, idesc, 1u);
+                            umma_ts_tf32(d_tmem, a_hi, db, idesc, 1u);
+                        }
+                    }
+                    ptx::umma_commit(ptx::smem_u32(&empty_bar[s]));
+                }
+                if (ok) ptx::umma_commit(ptx::smem_u32(&tfull_bar[buf]));
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (*abort_p) {
+        for (int i = 0; i < 200; ++i) __nanosleep(1000);
+        if (threadIdx.x == 0) atomicOr(p.status, DEV_STATUS_WAIT_TIMEOUT);
+        __syncthreads();
+    }
+    if (warp == kTsMmaWarp) {
+        __syncwarp();
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc(tmem_base, 512u);
+    }
+}
+
+}  // namespace dlfb200

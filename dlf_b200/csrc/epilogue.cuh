@@ -1,0 +1,130 @@
+// Epilogue shared by the contraction kernels: one warp owns 32 TMEM lanes (32 consecutive
+// values of the output's contiguous index i) and walks the tile's columns 32 at a time.
+// For every column j the warp writes 32 consecutive output elements, so stores and the
+// optional reads of C (beta != 0) are fully coalesced without staging.
+//
+// The per-element work is kept to a multiply-add, a conversion and a store: alpha / beta /
+// bias / output-format decisions are taken once per tile (template parameters), addresses
+// advance by a constant stride, and interior chunks run without bounds checks.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "ptx.cuh"
+
+namespace dlfb200 {
+
+enum : int { OUT_F32 = 0, OUT_F16 = 1, OUT_BF16 = 2 };
+
+template <int OUT>
+__device__ __forceinline__ void out_store(char* ptr, float v) {
+    if constexpr (OUT == OUT_F32) {
+        *reinterpret_cast<float*>(ptr) = v;
+    } else if constexpr (OUT == OUT_F16) {
+        *reinterpret_cast<__half*>(ptr) = __float2half_rn(v);
+    } else {
+        *reinterpret_cast<__nv_bfloat16*>(ptr) = __float2bfloat16_rn(v);
+    }
+}
+template <int OUT>
+__device__ __forceinline__ float out_load(const char* ptr) {
+    if constexpr (OUT == OUT_F32) {
+        return *reinterpret_cast<const float*>(ptr);
+    } else if constexpr (OUT == OUT_F16) {
+        return __half2float(*reinterpret_cast<const __half*>(ptr));
+    } else {
+        return __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(ptr));
+    }
+}
+
+// One 32-column chunk. `ptr` addresses D(i, j0) for this lane's row i; consecutive columns are
+// `stride` bytes apart. `ncols` (1..32) columns of the chunk exist; `row_ok` says whether this
+// lane's row exists. `bias` addresses bias[j0] (storage type) and is only read when HAS_BIAS.
+template <int OUT, bool HAS_BETA, bool HAS_BIAS>
+__device__ __forceinline__ void epilogue_chunk(const uint32_t (&v)[32], char* ptr, long long stride,
+                                               int ncols, bool row_ok, float alpha, float beta,
+                                               const char* bias, int lane) {
+    constexpr int OES = OUT == OUT_F32 ? 4 : 2;
+    float bv = 0.0f;
+    if constexpr (HAS_BIAS) {
+        if (lane < ncols) bv = out_load<OUT>(bias + lane * OES);
+    }
+    if (ncols == 32) {
+        float c[HAS_BETA ? 32 : 1];
+        if constexpr (HAS_BETA) {
+            if (row_ok) {
+#pragma unroll
+                for (int jj = 0; jj < 32; ++jj) c[jj] = out_load<OUT>(ptr + jj * stride);
+            } else {
+#pragma unroll
+                for (int jj = 0; jj < 32; ++jj) c[jj] = 0.0f;
+            }
+        }
+#pragma unroll
+        for (int jj = 0; jj < 32; ++jj) {
+            float r = alpha * __uint_as_float(v[jj]);
+            if constexpr (HAS_BETA) r += beta * c[jj];
+            if constexpr (HAS_BIAS) r += __shfl_sync(0xffffffffu, bv, jj);
+            if (row_ok) out_store<OUT>(ptr + jj * stride, r);
+        }
+    } else {
+#pragma unroll
+        for (int jj = 0; jj < 32; ++jj) {
+            float r = alpha * __uint_as_float(v[jj]);
+            const bool ok = row_ok && jj < ncols;
+            if constexpr (HAS_BETA) {
+                if (ok) r += beta * out_load<OUT>(ptr + jj * stride);
+            }
+            if constexpr (HAS_BIAS) r += __shfl_sync(0xffffffffu, bv, jj);
+            if (ok) out_store<OUT>(ptr + jj * stride, r);
+        }
+    }
+}
+
+// All columns of one accumulator tile held in TMEM at `trow` (lane base and column base already
+// applied). ncols_total = number of valid columns of this tile (<= BN).
+template <int OUT, bool HAS_BETA, bool HAS_BIAS>
+__device__ __forceinline__ void epilogue_tile(uint32_t trow, int ncols_total, char* ptr,
+                                              long long stride, bool row_ok, float alpha,
+                                              float beta, const char* bias, int lane) {
+    constexpr int OES = OUT == OUT_F32 ? 4 : 2;
+    for (int c0 = 0; c0 < ncols_total; c0 += 32) {
+        uint32_t v[32];
+        ptx::tmem_ld_32x32(trow + c0, v);
+        ptx::tmem_ld_wait();
+        const int nc = min(32, ncols_total - c0);
+        epilogue_chunk<OUT, HAS_BETA, HAS_BIAS>(v, ptr + c0 * stride, stride, nc, row_ok, alpha,
+                                                beta, HAS_BIAS ? bias + c0 * OES : nullptr, lane);
+    }
+}
+
+template <int OUT>
+__device__ __forceinline__ void epilogue_dispatch(uint32_t trow, int ncols_total, char* ptr,
+                                                  long long stride, bool row_ok, float alpha,
+                                                  float beta, const char* bias, int lane) {
+    if (beta != 0.0f) {
+        if (bias)
+            epilogue_tile<OUT, true, true>(trow, ncols_total, ptr, stride, row_ok, alpha, beta, bias, lane);
+        else
+            epilogue_tile<OUT, true, false>(trow, ncols_total, ptr, stride, row_ok, alpha, beta, bias, lane);
+    } else {
+        if (bias)
+            epilogue_tile<OUT, false, true>(trow, ncols_total, ptr, stride, row_ok, alpha, beta, bias, lane);
+        else
+            epilogue_tile<OUT, false, false>(trow, ncols_total, ptr, stride, row_ok, alpha, beta, bias, lane);
+    }
+}
+
+// fmt: FMT_F16 = 0, FMT_BF16 = 1, FMT_F32 = 2 (storage type of D)
+__device__ __forceinline__ void epilogue_run(int fmt, uint32_t trow, int ncols_total, char* ptr,
+                                             long long stride, bool row_ok, float alpha, float beta,
+                                             const char* bias, int lane) {
+    if (fmt == 2)
+        epilogue_dispatch<OUT_F32>(trow, ncols_total, ptr, stride, row_ok, alpha, beta, bias, lane);
+    else if (fmt == 0)
+        epilogue_dispatch<OUT_F16>(trow, ncols_total, ptr, stride, row_ok, alpha, beta, bias, lane);
+    else
+        epilogue_dispatch<OUT_BF16>(trow, ncols_total, ptr, stride, row_ok, alpha, beta, bias, lane);
+}
+
+}  // namespace dlfb200

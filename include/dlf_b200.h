@@ -99,8 +99,10 @@ const char* dlf_b200_status_string(int status);
  * up (bit 0). Kernels never trap or spin forever; this is how such a failure is reported. */
 int dlf_b200_device_status(int* device_status);
 
-/* Tuning overrides for experiments: force the N-tile width (64, 128 or 256; 0 = automatic) and
- * force the generic (non-TMA) operand loader (1) for every following call of this process. */
+/* Tuning overrides for experiments, for every following call of this process: force the N-tile
+ * width (64, 128 or 256; 0 = automatic) and the operand path: 0 = automatic, 1 = never the TMA
+ * producer, 2 = always the loader-warp kernel with both operands in shared memory, 3 = the
+ * kernel that keeps operand A in tensor memory whenever the TMA producer is not used. */
 void dlf_b200_set_tuning(int force_bn, int force_generic_loader);
 
 /* Counts kernel launches made by this library in this process (all threads). */
