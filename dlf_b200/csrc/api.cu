@@ -110,8 +110,8 @@ int ensure_device(DeviceState** out) {
         CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
         if (qres != cudaDriverEntryPointSuccess || fn == nullptr) return kUnexpectedError;
         st.encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
-        CUDA_TRY(cudaMalloc(&st.status, sizeof(int)));
-        CUDA_TRY(cudaMemset(st.status, 0, sizeof(int)));
+        CUDA_TRY(cudaMalloc(&st.status, 2 * sizeof(int)));
+        CUDA_TRY(cudaMemset(st.status, 0, 2 * sizeof(int)));
         st.ready = true;
     }
     *out = &st;
@@ -156,6 +156,7 @@ struct Problem {
     const float* alphas = nullptr;
     const float* betas = nullptr;
     const char* bias = nullptr;
+    long long bias_stride = 0;
     Im2colGeom g{};
 };
 
@@ -204,17 +205,38 @@ int encode_map(const DeviceState& st, CUtensorMap* map, const GenOperand& op, in
     return r == CUDA_SUCCESS ? kSuccess : kUnexpectedError;
 }
 
+// Tile width. tcgen05.mma with M = 128 was measured (back-to-back issue, this GPU) at about
+// 112-116 clocks for any N <= 128, 171 clocks for N = 256 with both operands in shared memory and
+// 138 clocks for N = 256 with A in tensor memory: narrow tiles waste most of the tensor pipe.
+// Pick the width that minimises (waves of tiles) x (clocks per UMMA of that width).
+int choose_bn(long long M, long long N, long long batch, int num_sms, bool a_in_tmem, int max_bn) {
+    const long long tiles_m = (M + kBM - 1) / kBM;
+    int best = 64;
+    double best_cost = 0;
+    for (int w = 64; w <= max_bn; w *= 2) {
+        const long long tiles = batch * tiles_m * ((N + w - 1) / w);
+        const double waves = static_cast<double>((tiles + num_sms - 1) / num_sms);
+        const double clk = w == 256 ? (a_in_tmem ? 138.0 : 171.0) : 114.0;
+        const double cost = waves * clk;
+        if (w == 64 || cost < best_cost) {
+            best = w;
+            best_cost = cost;
+        }
+        if (N <= w) break;
+    }
+    return best;
+}
+
 int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
     const int a_cols = q.es == 4 ? 64 : 32;
     const int BK = 128 / q.es;
     const long long tiles_m = (q.M + kBM - 1) / kBM;
-    int bn = q.N <= 64 ? 64 : (q.N <= 128 ? 128 : 256);
-    auto tiles_for = [&](int w) { return q.batch * tiles_m * ((q.N + w - 1) / w); };
-    while (bn > 64 && tiles_for(bn) < st.num_sms) bn /= 2;
+    int bn = choose_bn(q.M, q.N, q.batch, st.num_sms, true, 256);
     const int forced = g_force_bn.load();
     if (forced == 64 || forced == 128 || forced == 256) bn = forced;
     const long long tiles_n = (q.N + bn - 1) / bn;
     const long long total = q.batch * tiles_m * tiles_n;
+    if (total >= INT_MAX) return kInvalidDimension;
 
     const int acc_bufs = (2 * bn + 2 * a_cols <= 512) ? 2 : 1;
     const long long num_kb = (q.K + BK - 1) / BK;
@@ -247,7 +269,7 @@ int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
     p.fmt = q.fmt;
     p.tiles_m = static_cast<int>(tiles_m);
     p.tiles_n = static_cast<int>(tiles_n);
-    p.total_tiles = total;
+    p.total_tiles = static_cast<int>(total);
     p.alpha = q.alpha;
     p.beta = q.beta;
     p.a = q.a;
@@ -261,8 +283,10 @@ int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
     p.alphas = q.alphas;
     p.betas = q.betas;
     p.bias = q.bias;
+    p.bias_stride = q.bias_stride;
     p.g = q.g;
     p.status = st.status;
+    p.ablate = g_force_generic.load() >> 8;
     tp.a_kind = q.a.im2col ? A_IM2COL : (q.a.k_major ? A_DENSE_K : A_DENSE_MN);
     tp.acc_bufs = acc_bufs;
     tp.ktable_bytes = ktable_bytes;
@@ -284,25 +308,24 @@ int launch(const Problem& q, cudaStream_t stream) {
     if (q.M > INT_MAX - 512 || q.N > INT_MAX - 512 || q.K > INT_MAX - 512 || q.batch > INT_MAX)
         return kInvalidDimension;
 
-    const bool use_tma = q.es == 2 && !g_force_generic.load() && q.a_offs == nullptr &&
+    const bool use_tma = q.es == 2 && !(g_force_generic.load() & 0xff) && q.a_offs == nullptr &&
                          tma_ok(q.a, q.es, q.M, q.K, q.batch) &&
                          tma_ok(q.b, q.es, q.N, q.K, q.batch);
     // A through tensor memory: every convolution and every fp32 product (see contraction_ts.cuh)
-    const int force_path = g_force_generic.load();
+    const int force_path = g_force_generic.load() & 0xff;
     if (force_path != 2 && !use_tma && (q.a.im2col || q.es == 4 || force_path == 3)) {
         rc = launch_ts(*st, q, stream);
         if (rc != kNotImplemented) return rc;  // else: im2col table too large, use the smem-A kernel
     }
 
     const long long tiles_m = (q.M + kBM - 1) / kBM;
-    int bn = q.N <= 64 ? 64 : (q.N <= 128 ? 128 : 256);
-    if (q.es == 4 && bn == 256) bn = 128;  // two (hi, lo) copies per stage: keep >= 3 stages
-    auto tiles_for = [&](int w) { return q.batch * tiles_m * ((q.N + w - 1) / w); };
-    while (bn > 64 && tiles_for(bn) < st->num_sms) bn /= 2;
+    // fp32 here keeps hi and lo copies of both operands per stage: 128 columns leave >= 3 stages
+    int bn = choose_bn(q.M, q.N, q.batch, st->num_sms, false, q.es == 4 ? 128 : 256);
     const int forced = g_force_bn.load();
     if (forced == 64 || forced == 128 || (forced == 256 && q.es == 2)) bn = forced;
     const long long tiles_n = (q.N + bn - 1) / bn;
     const long long total = q.batch * tiles_m * tiles_n;
+    if (total >= INT_MAX) return kInvalidDimension;
 
     const int static_smem =
         use_tma ? st->static_smem_tma : (q.es == 2 ? st->static_smem_gen2 : st->static_smem_gen4);
@@ -322,7 +345,7 @@ int launch(const Problem& q, cudaStream_t stream) {
     p.fmt = q.fmt;
     p.tiles_m = static_cast<int>(tiles_m);
     p.tiles_n = static_cast<int>(tiles_n);
-    p.total_tiles = total;
+    p.total_tiles = static_cast<int>(total);
     p.alpha = q.alpha;
     p.beta = q.beta;
     p.a = q.a;
@@ -336,6 +359,7 @@ int launch(const Problem& q, cudaStream_t stream) {
     p.alphas = q.alphas;
     p.betas = q.betas;
     p.bias = q.bias;
+    p.bias_stride = q.bias_stride;
     p.g = q.g;
     p.status = st->status;
 
@@ -530,6 +554,35 @@ int dlf_b200_conv2d(int dtype, size_t batches, size_t channels, size_t height, s
         dilation_w >= lim || static_cast<long long>(height) * width >= INT_MAX)
         return kInvalidDimension;
 
+    // A 1x1, stride-1, unpadded convolution is a batched GEMM over the images,
+    //     Y[b] (Cout x P) = W (Cout x Cin) * X[b] (Cin x P),
+    // exactly the reference's convWithIm2Col shortcut (gpgpu/src/gdnn.cpp:1512-1559: weights
+    // shared with stride 0). With TMA-compatible strides it takes the TMA-fed kernel.
+    if (kernel_h == 1 && kernel_w == 1 && stride_h == 1 && stride_w == 1 && pad_top == 0 &&
+        pad_left == 0 && output_h == height && output_w == width && group == 1 && q.es == 2 &&
+        (P * q.es) % 16 == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 &&
+        (reinterpret_cast<uintptr_t>(w) & 15u) == 0 && (channels * q.es) % 16 == 0 &&
+        !(g_force_generic.load() & 0xff)) {
+        q.M = P;
+        q.N = static_cast<long long>(num_kernels);
+        q.K = static_cast<long long>(channels);
+        q.batch = static_cast<long long>(batches);
+        q.a.base = static_cast<const char*>(x);
+        q.a.k_major = 0;
+        q.a.ld = P;
+        q.a.batch_stride = static_cast<long long>(channels) * P;
+        q.b.base = static_cast<const char*>(w);
+        q.b.k_major = 1;
+        q.b.ld = static_cast<long long>(channels);
+        q.b.batch_stride = 0;
+        q.d = static_cast<char*>(y);
+        q.ldd = P;
+        q.d_batch_stride = static_cast<long long>(num_kernels) * P;
+        q.bias = static_cast<const char*>(bias);
+        q.bias_stride = 0;
+        return launch(q, static_cast<cudaStream_t>(stream));
+    }
+
     q.M = static_cast<long long>(batches) * P;  // global output pixel index
     q.N = ng;
     q.K = K;
@@ -549,6 +602,7 @@ int dlf_b200_conv2d(int dtype, size_t batches, size_t channels, size_t height, s
     q.alpha = 1.f;
     q.beta = 0.f;
     q.bias = static_cast<const char*>(bias);
+    q.bias_stride = ng;
     q.g.H = static_cast<int>(height);
     q.g.W = static_cast<int>(width);
     q.g.OH = static_cast<int>(output_h);

@@ -80,7 +80,7 @@ struct Params {
     int M, N, K, batch;
     int BN, stages, fmt;
     int tiles_m, tiles_n;
-    long long total_tiles;
+    int total_tiles;
     float alpha, beta;
     GenOperand a, b;
     char* d;
@@ -91,9 +91,12 @@ struct Params {
     const long long* d_offs;
     const float* alphas;
     const float* betas;
-    const char* bias;  // bias[batch*N + j] in the storage type, or null
+    const char* bias;  // bias[batch*bias_stride + j] in the storage type, or null
+    long long bias_stride;
     Im2colGeom g;
     int* status;
+    int ablate;  // measurement aid: bit 0 A producer skips its loads, bit 1 B loaders skip theirs,
+                 // bit 2 producers skip the TMEM stores (results are then meaningless)
 };
 
 struct PixelEntry {  // one output pixel of the current tile (implicit im2col operand)
@@ -101,11 +104,11 @@ struct PixelEntry {  // one output pixel of the current tile (implicit im2col op
     int ih0, iw0;    // oh*sh - pad_t, ow*sw - pad_l ; ih0 = INT_MIN/2 marks "no such pixel"
 };
 
-__device__ __forceinline__ void decode_tile(const Params& p, long long t, int& b, int& m0,
-                                            int& n0) {
-    const long long per = static_cast<long long>(p.tiles_m) * p.tiles_n;
-    b = static_cast<int>(t / per);
-    const int r = static_cast<int>(t - b * per);
+// total_tiles < 2^31 is checked on the host, so tile arithmetic stays in 32 bits.
+__device__ __forceinline__ void decode_tile(const Params& p, int t, int& b, int& m0, int& n0) {
+    const int per = p.tiles_m * p.tiles_n;
+    b = t / per;
+    const int r = t - b * per;
     const int group = kGroupM * p.tiles_n;
     const int gi = r / group;
     const int first = gi * kGroupM;
@@ -283,12 +286,12 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
 
     if (warp < 4) {
         // ------------------------------------------------------------ epilogue
-        long long it = 0;
-        for (long long t = blockIdx.x; t < p.total_tiles; t += gridDim.x, ++it) {
+        uint32_t it = 0;
+        for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x, ++it) {
             int b, m0, n0;
             decode_tile(p, t, b, m0, n0);
-            const uint32_t buf = static_cast<uint32_t>(it & 1);
-            const uint32_t tphase = static_cast<uint32_t>((it >> 1) & 1);
+            const uint32_t buf = it & 1u;
+            const uint32_t tphase = (it >> 1) & 1u;
             // tcgen05.ld is warp-collective: the warp leaves together or not at all
             const bool w = ptx::mbar_wait_bounded(ptx::smem_u32(&tfull_bar[buf]), tphase, abort_p);
             if (!__all_sync(0xffffffffu, w)) break;
@@ -311,7 +314,7 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
             const float alpha = p.alphas ? p.alphas[b] : p.alpha;
             const float beta = p.betas ? p.betas[b] : p.beta;
             const char* bias =
-                p.bias ? p.bias + (static_cast<long long>(b) * p.N + n0) * ES : nullptr;
+                p.bias ? p.bias + (static_cast<long long>(b) * p.bias_stride + n0) * ES : nullptr;
             const uint32_t trow = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + buf * BN;
             char* optr = p.d + (rowbase + static_cast<long long>(n0) * colstride) * ES;
             const int ncols = min(BN, p.N - n0);
@@ -343,12 +346,17 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
             const uint32_t b_mode = (ES == 4 && !p.b.k_major) ? 1u : 2u;
             const uint32_t a_sbo = a_mode == 1u ? 512u : 1024u;
             const uint32_t b_sbo = b_mode == 1u ? 512u : 1024u;
+            // descriptors differ only in the 14-bit start-address field (address >> 4): build
+            // them once and advance by plain adds
+            const uint64_t da0 = ptx::make_smem_desc(smem0, a_lbo, a_sbo, a_mode);
+            const uint64_t db0 = ptx::make_smem_desc(smem0 + A_TILE, b_lbo, b_sbo, b_mode);
+            const uint32_t lo_units = (A_TILE + b_tile) >> 4;
             uint32_t stage = 0, phase = 0;
-            long long it = 0;
+            uint32_t it = 0;
             bool ok = true;
-            for (long long t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x, ++it) {
-                const uint32_t buf = static_cast<uint32_t>(it & 1);
-                const uint32_t tphase = static_cast<uint32_t>((it >> 1) & 1);
+            for (int t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x, ++it) {
+                const uint32_t buf = it & 1u;
+                const uint32_t tphase = (it >> 1) & 1u;
                 if (!ptx::mbar_wait_bounded(ptx::smem_u32(&tempty_bar[buf]), tphase ^ 1u, abort_p)) {
                     ok = false;
                     break;
@@ -361,23 +369,17 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
                         break;
                     }
                     ptx::tc_fence_after();
-                    const uint32_t sA = smem0 + stage * stage_bytes;
-                    const uint32_t sB = sA + A_TILE;
+                    const uint32_t st_units = (stage * stage_bytes) >> 4;
 #pragma unroll
                     for (int ks = 0; ks < BK / UMMA_K; ++ks) {
-                        const uint64_t da = ptx::make_smem_desc(sA + ks * a_step, a_lbo, a_sbo, a_mode);
-                        const uint64_t db = ptx::make_smem_desc(sB + ks * b_step, b_lbo, b_sbo, b_mode);
+                        const uint64_t da = da0 + (st_units + ((ks * a_step) >> 4));
+                        const uint64_t db = db0 + (st_units + ((ks * b_step) >> 4));
                         const uint32_t acc = (kb | ks) ? 1u : 0u;
                         if constexpr (ES == 2) {
                             ptx::umma_f16(d_tmem, da, db, idesc, acc);
                         } else {
-                            const uint32_t lo_off = A_TILE + b_tile;
-                            const uint64_t da_lo =
-                                ptx::make_smem_desc(sA + lo_off + ks * a_step, a_lbo, a_sbo, a_mode);
-                            const uint64_t db_lo =
-                                ptx::make_smem_desc(sB + lo_off + ks * b_step, b_lbo, b_sbo, b_mode);
-                            ptx::umma_tf32(d_tmem, da_lo, db, idesc, acc);
-                            ptx::umma_tf32(d_tmem, da, db_lo, idesc, 1u);
+                            ptx::umma_tf32(d_tmem, da + lo_units, db, idesc, acc);
+                            ptx::umma_tf32(d_tmem, da, db + lo_units, idesc, 1u);
                             ptx::umma_tf32(d_tmem, da, db, idesc, 1u);
                         }
                     }
@@ -395,7 +397,7 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            for (long long t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x) {
+            for (int t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x) {
                 int b, m0, n0;
                 decode_tile(p, t, b, m0, n0);
                 const int ba = p.a.batch_stride ? b : 0;
@@ -437,9 +439,9 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
         const bool a_atom32 = ES == 4 && !p.a.k_major;
         const bool b_atom32 = ES == 4 && !p.b.k_major;
         uint32_t stage = 0, phase = 0;
-        long long it = 0;
+        uint32_t it = 0;
         bool ok = true;
-        for (long long t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x, ++it) {
+        for (int t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x, ++it) {
             int b, m0, n0;
             decode_tile(p, t, b, m0, n0);
             const long long a_boff =

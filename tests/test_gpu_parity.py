@@ -355,6 +355,8 @@ CONV_CASES = [
     (2, 64, 56, 56, 64, 3, 3, (1, 1, 1, 1), (1, 1), (1, 1), 1),     # config 2 at batch 2
     (2, 3, 37, 41, 16, 7, 7, (3, 3, 3, 3), (2, 2), (1, 1), 1),      # stem-like, K = 147
     (3, 32, 14, 14, 48, 1, 1, (0, 0, 0, 0), (1, 1), (1, 1), 1),     # 1x1
+    (3, 64, 8, 16, 80, 1, 1, (0, 0, 0, 0), (1, 1), (1, 1), 1),      # 1x1, 16-byte-aligned planes: batched-GEMM route
+    (2, 16, 12, 12, 320, 3, 3, (1, 1, 1, 1), (1, 1), (1, 1), 1),    # wide output: 256-column tiles
     (3, 32, 14, 14, 64, 1, 1, (0, 0, 0, 0), (2, 2), (1, 1), 1),     # 1x1 stride 2
     (2, 8, 13, 11, 12, 3, 2, (1, 2, 2, 1), (2, 1), (1, 2), 2),      # odd everything + groups
     (5, 16, 7, 7, 40, 3, 3, (1, 1, 1, 1), (1, 1), (1, 1), 4),       # tiles straddle images
