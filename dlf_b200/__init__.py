@@ -48,6 +48,10 @@ def _declare(L):
     L.dlf_b200_gemm_batched.argtypes = [c_int] * 4 + [c_size] * 3 + [
         c_void, c_void, psize, c_size, c_void, psize, c_size, c_void, c_void, psize, c_size,
         c_size, c_void, c_size, c_void]
+    L.dlf_b200_gemm_batched_noalloc.restype = c_int
+    L.dlf_b200_gemm_batched_noalloc.argtypes = [c_int] * 4 + [c_size] * 3 + [
+        c_void, c_void, psize, c_size, c_void, psize, c_size, c_void, c_void, psize, c_size,
+        c_size, c_void]
     L.dlf_b200_gemm_batched_workspace_bytes.restype = c_size
     L.dlf_b200_gemm_batched_workspace_bytes.argtypes = [c_size]
     L.dlf_b200_conv2d.restype = c_int
@@ -70,6 +74,7 @@ EXPORTED_SYMBOLS = (
     "dlf_b200_gemm_strided_batched",
     "dlf_b200_gemm_batched",
     "dlf_b200_gemm_batched_workspace_bytes",
+    "dlf_b200_gemm_batched_noalloc",
     "dlf_b200_conv2d",
     "dlf_b200_conv2d_workspace_bytes",
     "dlf_b200_status_string",

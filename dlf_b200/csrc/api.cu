@@ -301,10 +301,13 @@ int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
     return kSuccess;
 }
 
-int launch(const Problem& q, cudaStream_t stream) {
-    DeviceState* st = nullptr;
-    int rc = ensure_device(&st);
-    if (rc != kSuccess) return rc;
+int launch(const Problem& q, cudaStream_t stream, DeviceState* preset = nullptr) {
+    DeviceState* st = preset;
+    int rc = kSuccess;
+    if (st == nullptr) {
+        rc = ensure_device(&st);
+        if (rc != kSuccess) return rc;
+    }
     if (q.M > INT_MAX - 512 || q.N > INT_MAX - 512 || q.K > INT_MAX - 512 || q.batch > INT_MAX)
         return kInvalidDimension;
 
@@ -383,6 +386,83 @@ int launch(const Problem& q, cudaStream_t stream) {
     }
     g_launches.fetch_add(1);
     CUDA_TRY(cudaGetLastError());
+    return kSuccess;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Scratch that lives in the library image instead of in allocated memory.
+//
+// dlf_b200_gemm_batched needs its per-batch tables (three offset tables, alpha, beta) in device
+// memory and takes that scratch from the caller. Some callers have no scratch to give and may not
+// create any: a dlf routine that runs while the context's temporary-buffer pool is in use by an
+// enclosing routine (the pool is a LIFO slab that throws on out-of-order release and is not
+// thread-safe), or a serving process whose device memory was handed in full to another owner at
+// start-up. For them the tables - and the status word the kernels report to - sit in these
+// file-scope device arrays, which every GPU that loads the library holds until the process exits.
+// The names below are host-side stand-ins, not device addresses: the device address is looked up
+// once per device with cudaGetSymbolAddress (noalloc_device) and that pointer goes to the kernel.
+constexpr size_t kNoAllocMaxBatch = 4096;
+constexpr size_t kNoAllocTableBytes = kNoAllocMaxBatch * (3 * sizeof(long long) + 2 * sizeof(float));
+static __device__ __align__(256) unsigned char g_noalloc_tables[kNoAllocTableBytes];
+static __device__ __align__(256) int g_noalloc_status[2];
+
+struct NoAllocDevice {
+    bool ready = false;
+    DeviceState st;          // same per-device facts as the allocating path, status -> static word
+    unsigned char* tables = nullptr;
+};
+NoAllocDevice g_noalloc_dev[kMaxDevices];
+
+// Per-device set-up of the no-allocation path, with that device current: kernel attributes, the
+// tensor-map encoder and the device addresses of the two static arrays. Allocates nothing.
+int noalloc_device(NoAllocDevice** out) {
+    int dev = 0;
+    CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return kInvalidValue;
+    std::lock_guard<std::mutex> lock(g_mu);
+    NoAllocDevice& nd = g_noalloc_dev[dev];
+    if (!nd.ready) {
+        DeviceState& st = nd.st;
+        CUDA_TRY(cudaDeviceGetAttribute(&st.num_sms, cudaDevAttrMultiProcessorCount, dev));
+        int major = 0;
+        CUDA_TRY(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+        if (major != 10) return kNotImplemented;
+        cudaFuncAttributes fa;
+        CUDA_TRY(cudaFuncGetAttributes(&fa, contraction_kernel<2, true>));
+        st.static_smem_tma = static_cast<int>(fa.sharedSizeBytes);
+        CUDA_TRY(cudaFuncGetAttributes(&fa, contraction_kernel<2, false>));
+        st.static_smem_gen2 = static_cast<int>(fa.sharedSizeBytes);
+        CUDA_TRY(cudaFuncGetAttributes(&fa, contraction_kernel<4, false>));
+        st.static_smem_gen4 = static_cast<int>(fa.sharedSizeBytes);
+        CUDA_TRY(cudaFuncGetAttributes(&fa, contraction_ts_kernel<2>));
+        st.static_smem_ts2 = static_cast<int>(fa.sharedSizeBytes);
+        CUDA_TRY(cudaFuncGetAttributes(&fa, contraction_ts_kernel<4>));
+        st.static_smem_ts4 = static_cast<int>(fa.sharedSizeBytes);
+        CUDA_TRY(cudaFuncSetAttribute(contraction_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      kSmemPerBlockOptin - st.static_smem_tma));
+        CUDA_TRY(cudaFuncSetAttribute(contraction_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      kSmemPerBlockOptin - st.static_smem_gen2));
+        CUDA_TRY(cudaFuncSetAttribute(contraction_kernel<4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      kSmemPerBlockOptin - st.static_smem_gen4));
+        CUDA_TRY(cudaFuncSetAttribute(contraction_ts_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      kSmemPerBlockOptin - st.static_smem_ts2));
+        CUDA_TRY(cudaFuncSetAttribute(contraction_ts_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      kSmemPerBlockOptin - st.static_smem_ts4));
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+        if (qres != cudaDriverEntryPointSuccess || fn == nullptr) return kUnexpectedError;
+        st.encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+        void* p_tables = nullptr;
+        void* p_status = nullptr;
+        CUDA_TRY(cudaGetSymbolAddress(&p_tables, g_noalloc_tables));
+        CUDA_TRY(cudaGetSymbolAddress(&p_status, g_noalloc_status));
+        nd.tables = static_cast<unsigned char*>(p_tables);
+        st.status = static_cast<int*>(p_status);
+        st.ready = true;
+        nd.ready = true;
+    }
+    *out = &nd;
     return kSuccess;
 }
 
@@ -516,6 +596,51 @@ int dlf_b200_gemm_batched(int dtype, int layout, int trans_a, int trans_b, size_
     q.betas = q.alphas + batch_count;
     q.batch = static_cast<long long>(batch_count);
     return launch(q, s);
+}
+
+int dlf_b200_gemm_batched_noalloc(int dtype, int layout, int trans_a, int trans_b, size_t m,
+                                  size_t n, size_t k, const void* alphas, const void* a,
+                                  const size_t* a_offsets, size_t a_ld, const void* b,
+                                  const size_t* b_offsets, size_t b_ld, const void* betas, void* c,
+                                  const size_t* c_offsets, size_t c_ld, size_t batch_count,
+                                  void* stream) {
+    if (batch_count < 1 || alphas == nullptr || betas == nullptr || a_offsets == nullptr ||
+        b_offsets == nullptr || c_offsets == nullptr)
+        return kInvalidBatchCount;
+    if (batch_count > kNoAllocMaxBatch) return kInsufficientMemoryTemp;  // static scratch is fixed
+    Problem q;
+    int rc = setup_gemm(q, dtype, layout, trans_a, trans_b, m, n, k, a, a_ld, b, b_ld, c, c_ld);
+    if (rc != kSuccess) return rc;
+    NoAllocDevice* nd = nullptr;
+    rc = noalloc_device(&nd);  // first call on a device: looks up the static arrays' addresses
+    if (rc != kSuccess) return rc;
+
+    // host staging for the tables is per-thread static storage as well
+    thread_local static unsigned char host[kNoAllocTableBytes];
+    const bool row = layout == DLF_B200_ROW_MAJOR;
+    long long* h_a = reinterpret_cast<long long*>(host);
+    long long* h_b = h_a + batch_count;
+    long long* h_d = h_b + batch_count;
+    float* h_alpha = reinterpret_cast<float*>(h_d + batch_count);
+    float* h_beta = h_alpha + batch_count;
+    for (size_t i = 0; i < batch_count; ++i) {
+        h_a[i] = static_cast<long long>(row ? b_offsets[i] : a_offsets[i]);
+        h_b[i] = static_cast<long long>(row ? a_offsets[i] : b_offsets[i]);
+        h_d[i] = static_cast<long long>(c_offsets[i]);
+        h_alpha[i] = scalar_to_float(q.fmt, static_cast<const char*>(alphas) + i * q.es);
+        h_beta[i] = scalar_to_float(q.fmt, static_cast<const char*>(betas) + i * q.es);
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const size_t need = batch_count * (3 * sizeof(long long) + 2 * sizeof(float));
+    // every byte the kernel reads is rewritten here, so nothing of an earlier call survives
+    CUDA_TRY(cudaMemcpyAsync(nd->tables, host, need, cudaMemcpyHostToDevice, s));
+    q.a_offs = reinterpret_cast<const long long*>(nd->tables);
+    q.b_offs = q.a_offs + batch_count;
+    q.d_offs = q.b_offs + batch_count;
+    q.alphas = reinterpret_cast<const float*>(q.d_offs + batch_count);
+    q.betas = q.alphas + batch_count;
+    q.batch = static_cast<long long>(batch_count);
+    return launch(q, s, &nd->st);
 }
 
 size_t dlf_b200_conv2d_workspace_bytes(int, size_t, size_t, size_t, size_t, size_t, size_t, size_t,
@@ -652,6 +777,17 @@ int dlf_b200_device_status(int* device_status) {
     int v = 0;
     CUDA_TRY(cudaMemcpy(&v, st->status, sizeof(int), cudaMemcpyDeviceToHost));
     if (v != 0) CUDA_TRY(cudaMemset(st->status, 0, sizeof(int)));
+    {
+        int dev = 0;
+        CUDA_TRY(cudaGetDevice(&dev));
+        NoAllocDevice& nd = g_noalloc_dev[dev];
+        if (nd.ready) {  // kernels launched by dlf_b200_gemm_batched_noalloc report here
+            int w = 0;
+            CUDA_TRY(cudaMemcpy(&w, nd.st.status, sizeof(int), cudaMemcpyDeviceToHost));
+            if (w != 0) CUDA_TRY(cudaMemset(nd.st.status, 0, sizeof(int)));
+            v |= w;
+        }
+    }
     if (device_status) *device_status = v;
     return kSuccess;
 }

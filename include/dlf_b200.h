@@ -69,6 +69,28 @@ int dlf_b200_gemm_batched(int dtype, int layout, int trans_a, int trans_b, size_
                           void* stream);
 size_t dlf_b200_gemm_batched_workspace_bytes(size_t batch_count);
 
+/* dlf_b200_gemm_batched without the workspace argument, for callers that have no device scratch
+ * to hand over and must not create any at call time - for instance a dlf routine that is invoked
+ * while its context's temporary-buffer pool (a LIFO slab, not thread-safe) is already in use
+ * further up the call stack, or a process whose device memory was given away in full at start-up.
+ * This entry point has no counterpart in the reference. It allocates nothing: the per-batch
+ * tables go into a fixed array inside the library's device image (128 KiB on every GPU that loads
+ * the library, kept until the process exits), so batch_count is limited to
+ * DLF_B200_NOALLOC_MAX_BATCH; a larger count returns kInsufficientMemoryTemp (-2050) and does
+ * nothing. The first call on each device looks up the array's device address and sets kernel
+ * attributes; make that first call outside any stream capture. All calls share the one array:
+ * each call rewrites the part it uses before its kernel reads it, in stream order, so calls on
+ * the same stream are safe, but two calls whose work overlaps on the GPU (different streams or
+ * host threads without ordering between them) race on the tables. Results are identical to
+ * dlf_b200_gemm_batched. */
+#define DLF_B200_NOALLOC_MAX_BATCH 4096
+int dlf_b200_gemm_batched_noalloc(int dtype, int layout, int trans_a, int trans_b, size_t m,
+                                  size_t n, size_t k, const void* alphas, const void* a,
+                                  const size_t* a_offsets, size_t a_ld, const void* b,
+                                  const size_t* b_offsets, size_t b_ld, const void* betas, void* c,
+                                  const size_t* c_offsets, size_t c_ld, size_t batch_count,
+                                  void* stream);
+
 /* NCHW cross-correlation Y = conv2d(X, W) (+ bias), computed as an implicit GEMM: no im2col
  * buffer is materialised. X is {batches, channels, height, width}, W is
  * {num_kernels, channels/group, kernel_h, kernel_w}, Y is {batches, num_kernels, output_h,
