@@ -158,6 +158,11 @@ struct Problem {
     const char* bias = nullptr;
     long long bias_stride = 0;
     Im2colGeom g{};
+    // row form of a convolution (contraction_ts.cuh, A_ROWCONV); rc_kw == 0: not used
+    int rc_kw = 0, rc_cpt = 0, rc_T = 0, rc_lo = 0;
+    // caller-provided scratch for the packed filter bank of a convolution (may be null)
+    unsigned char* pack_ws = nullptr;
+    size_t pack_ws_bytes = 0;
 };
 
 bool tma_ok(const GenOperand& op, int es, long long rows, long long K, long long batch) {
@@ -230,18 +235,25 @@ int choose_bn(long long M, long long N, long long batch, int num_sms, bool a_in_
 int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
     const int a_cols = q.es == 4 ? 64 : 32;
     const int BK = 128 / q.es;
-    const long long tiles_m = (q.M + kBM - 1) / kBM;
+    long long tiles_m = (q.M + kBM - 1) / kBM;
     int bn = choose_bn(q.M, q.N, q.batch, st.num_sms, true, 256);
     const int forced = g_force_bn.load();
     if (forced == 64 || forced == 128 || forced == 256) bn = forced;
-    const long long tiles_n = (q.N + bn - 1) / bn;
+    long long tiles_n = (q.N + bn - 1) / bn;
+    if (q.rc_kw) {  // tile = 4 warps x rc_T output positions by rc_cpt channels (x rc_kw columns)
+        bn = q.rc_cpt * q.rc_kw;
+        tiles_m = (q.M + 4 * q.rc_T - 1) / (4 * q.rc_T);
+        tiles_n = (q.N + q.rc_cpt - 1) / q.rc_cpt;
+    }
     const long long total = q.batch * tiles_m * tiles_n;
     if (total >= INT_MAX) return kInvalidDimension;
 
-    const int acc_bufs = (2 * bn + 2 * a_cols <= 512) ? 2 : 1;
+    // two accumulator buffers (epilogue overlaps the next main loop) unless that would leave
+    // fewer than three A slots in tensor memory
+    const int acc_bufs = ((512 - 2 * bn) / a_cols >= 3) ? 2 : 1;
     const long long num_kb = (q.K + BK - 1) / BK;
     int ktable_bytes = 0;
-    if (q.a.im2col) {
+    if (q.a.im2col || q.rc_kw) {
         const long long need = num_kb * BK * static_cast<long long>(sizeof(KEntry));
         if (need > 96 * 1024) return kNotImplemented;  // caller falls back to the smem-A kernel
         ktable_bytes = static_cast<int>((need + 15) & ~15ll);
@@ -287,9 +299,31 @@ int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
     p.g = q.g;
     p.status = st.status;
     p.ablate = g_force_generic.load() >> 8;
-    tp.a_kind = q.a.im2col ? A_IM2COL : (q.a.k_major ? A_DENSE_K : A_DENSE_MN);
+    tp.a_kind = q.rc_kw ? A_ROWCONV : (q.a.im2col ? A_IM2COL : (q.a.k_major ? A_DENSE_K : A_DENSE_MN));
+    tp.rc_kw = q.rc_kw;
+    tp.rc_cpt = q.rc_cpt;
+    tp.rc_T = q.rc_T;
+    tp.rc_lo = q.rc_lo;
     tp.acc_bufs = acc_bufs;
     tp.ktable_bytes = ktable_bytes;
+
+    tp.b_packed = nullptr;
+    if (q.pack_ws != nullptr && (q.a.im2col || q.rc_kw) && p.b.k_major && !(g_force_generic.load() & 0x8000)) {
+        // lay the filter bank out as stage images first (same stream), then stream them with bulk copies
+        unsigned char* ws = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(q.pack_ws) + 127) & ~uintptr_t(127));
+        const size_t slack = static_cast<size_t>(ws - q.pack_ws);
+        const long long need = q.batch * tiles_n * num_kb * stage_bytes;
+        if (q.pack_ws_bytes >= slack && static_cast<long long>(q.pack_ws_bytes - slack) >= need) {
+            const long long chunks = q.batch * tiles_n * num_kb * bn * 8;
+            const unsigned pgrid = static_cast<unsigned>(chunks / 256 + 1 < 148 * 16 ? chunks / 256 + 1 : 148 * 16);
+            if (q.es == 2)
+                pack_weights_kernel<2><<<pgrid, 256, 0, stream>>>(tp, ws, chunks);
+            else
+                pack_weights_kernel<4><<<pgrid, 256, 0, stream>>>(tp, ws, chunks);
+            g_launches.fetch_add(1);
+            tp.b_packed = ws;
+        }
+    }
 
     const unsigned grid = static_cast<unsigned>(total < st.num_sms ? total : st.num_sms);
     if (q.es == 2)
@@ -643,9 +677,27 @@ int dlf_b200_gemm_batched_noalloc(int dtype, int layout, int trans_a, int trans_
     return launch(q, s, &nd->st);
 }
 
-size_t dlf_b200_conv2d_workspace_bytes(int, size_t, size_t, size_t, size_t, size_t, size_t, size_t,
-                                       size_t, size_t, size_t) {
-    return 0;  // implicit GEMM: the im2col matrix only ever exists tile by tile in shared memory
+size_t dlf_b200_conv2d_workspace_bytes(int dtype, size_t, size_t channels, size_t, size_t, size_t,
+                                       size_t, size_t num_kernels, size_t group, size_t kernel_h,
+                                       size_t kernel_w) {
+    // Optional scratch: the filter bank re-laid as the kernel's shared-memory stage images (a few
+    // hundred KB to a few MB). The im2col matrix itself is never materialised. An upper bound over
+    // the tilings the library may choose is returned; with less (or none) the kernel gathers the
+    // filter bank itself, more slowly.
+    int fmt = 0, es = 0;
+    if (!dtype_info(dtype, fmt, es) || group == 0 || kernel_w == 0) return 0;
+    const size_t cg = channels / group, ng = num_kernels / group;
+    const size_t bk = 128 / es, dup = es == 4 ? 2 : 1;
+    const size_t plain = group * ((ng + 255) / 256 * 256) * 128 * dup * ((cg * kernel_h * kernel_w + bk - 1) / bk);
+    size_t row = 0;
+    if (kernel_w >= 2 && kernel_w <= 8) {
+        const size_t cpt_max = (256 / kernel_w) / 16 * 16;
+        const size_t n_tiles = (ng + cpt_max - 1) / cpt_max;
+        size_t cpt = ((ng + n_tiles - 1) / n_tiles + 15) / 16 * 16;
+        if (cpt > cpt_max) cpt = cpt_max;
+        row = group * n_tiles * ((cg * kernel_h + bk - 1) / bk) * (cpt * kernel_w * 128 * dup);
+    }
+    return (plain > row ? plain : row) + 256;
 }
 
 int dlf_b200_conv2d(int dtype, size_t batches, size_t channels, size_t height, size_t width,
@@ -657,9 +709,9 @@ int dlf_b200_conv2d(int dtype, size_t batches, size_t channels, size_t height, s
                     void* stream) {
     (void)pad_bottom;
     (void)pad_right;
-    (void)workspace;
-    (void)workspace_bytes;
     Problem q;
+    q.pack_ws = static_cast<unsigned char*>(workspace);
+    q.pack_ws_bytes = workspace_bytes;
     if (!dtype_info(dtype, q.fmt, q.es)) return kNotImplemented;
     if (batches == 0 || channels == 0 || height == 0 || width == 0 || output_h == 0 ||
         output_w == 0 || num_kernels == 0 || kernel_h == 0 || kernel_w == 0)
@@ -744,6 +796,32 @@ int dlf_b200_conv2d(int dtype, size_t batches, size_t channels, size_t height, s
     q.g.img_stride = static_cast<long long>(channels) * height * width;
     q.g.out_img_stride = static_cast<long long>(num_kernels) * P;
     if (P > INT_MAX) return kInvalidDimension;
+
+    // Row form (see contraction_ts.cuh): horizontal taps become output columns of the GEMM.
+    const int path = g_force_generic.load() & 0xff;
+    const long long lo = static_cast<long long>(pad_left);
+    const long long hi = static_cast<long long>(kernel_w) - 1 - lo > 0 ? static_cast<long long>(kernel_w) - 1 - lo : 0;
+    if (path != 2 && path != 4 && stride_w == 1 && dilation_w == 1 && kernel_w >= 2 && kernel_w <= 8 &&
+        output_w <= width && lo + hi <= 16 &&
+        static_cast<long long>(batches) * output_h * width < INT_MAX - 4096) {
+        const int cpt_max = static_cast<int>((256 / kernel_w) / 16 * 16);
+        const int n_tiles = static_cast<int>((ng + cpt_max - 1) / cpt_max);
+        int cpt = static_cast<int>(((ng + n_tiles - 1) / n_tiles + 15) / 16 * 16);
+        if (cpt > cpt_max) cpt = cpt_max;
+        Problem r = q;
+        r.rc_kw = static_cast<int>(kernel_w);
+        r.rc_cpt = cpt;
+        r.rc_lo = static_cast<int>(lo);
+        r.rc_T = 32 - static_cast<int>(lo + hi);
+        r.M = static_cast<long long>(batches) * output_h * width;  // positions (img, oh, input column)
+        r.K = cg * static_cast<long long>(kernel_h);                // (c, kh)
+        r.a.im2col = 1;
+        DeviceState* st = nullptr;
+        int rc = ensure_device(&st);
+        if (rc != kSuccess) return rc;
+        rc = launch_ts(*st, r, static_cast<cudaStream_t>(stream));
+        if (rc != kNotImplemented) return rc;
+    }
     return launch(q, static_cast<cudaStream_t>(stream));
 }
 

@@ -21,6 +21,17 @@
 // its pixel's (ih0, iw0, base offset) in registers and a tap is valid when
 // 0 <= ih0 + kh*dh < H and 0 <= iw0 + kw*dw < W (zero otherwise: the padding).
 //
+// Row form of the convolution (A_ROWCONV; stride_w = dilation_w = 1, KW >= 2). A UMMA costs the
+// same ~115 clocks for any N <= 128, so a 64-channel layer wastes most of the tensor pipe when N is
+// the channel count. Here the horizontal taps move from K into N:
+//     D'[(img,oh,u), (kw,co)] = sum_{kh,c} X[img][c][oh*sh-pt+kh*dh][u] * W[co][c][kh][kw]
+//     Y[img][co][oh][ow]      = sum_kw D'[(img,oh,ow+kw-pl), (kw,co)]
+// K shrinks to C*KH and N grows to KW*cpt (192 for 3x3 with 64 channels per tile): a third of the
+// MMAs and a third of the gathered elements. Rows of D' are input columns u; the sum over kw is
+// done in the epilogue with warp shuffles between neighbouring lanes, so every warp owns a window
+// of 32 consecutive positions of which the inner T = 32 - (KW-1) produce outputs (windows of
+// consecutive warps overlap by KW-1 positions).
+//
 // TMEM columns: [0, acc_bufs*BN) accumulators, then `stages` A slots of 32 (16-bit types: 64 k
 // packed two per column) or 64 (fp32: 32 hi + 32 lo) columns.
 // Warp roles: 0-3 epilogue, 4-11 A producers (quadrant = warp % 4), 12-14 B loaders, 15 UMMA
@@ -37,7 +48,7 @@ constexpr int kTsThreads = 16 * 32;  // 512 threads: 128 registers each
 constexpr int kTsLoaderThreads = 3 * 32;
 constexpr int kTsLoaderLines = kTsLoaderThreads / 8;  // lines covered per pass of the B loaders
 
-enum : int { A_DENSE_MN = 0, A_DENSE_K = 1, A_IM2COL = 2 };
+enum : int { A_DENSE_MN = 0, A_DENSE_K = 1, A_IM2COL = 2, A_ROWCONV = 3 };
 
 struct KEntry {  // one k of the implicit im2col operand
     int off;     // c*H*W + kh*dh*W + kw*dw
@@ -50,6 +61,12 @@ struct TsParams {
     int a_kind;
     int acc_bufs;      // 1 or 2 accumulator buffers in TMEM
     int ktable_bytes;  // bytes reserved at the start of dynamic shared memory for KEntry[k]
+    // A_ROWCONV only (see the header comment): taps per row, output channels per tile, output
+    // positions per warp, lanes of left halo
+    int rc_kw, rc_cpt, rc_T, rc_lo;
+    // Filter bank already laid out as the kernel's shared-memory stage images (pack_weights_kernel):
+    // [batch][n-tile][k-block][stage_bytes]; null = the loader warps gather from the OIHW tensor
+    const unsigned char* b_packed;
 };
 
 __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&v)[32]) {
@@ -94,6 +111,85 @@ __device__ __forceinline__ void umma_ts_tf32(uint32_t d_tmem, uint32_t a_tmem, u
         : "memory");
 }
 
+// Element k' = kh*C + c of the row-form filter operand for one (co, kw):
+// W[co][c][kh][kw] = base[off + (c*KH + kh)*KW], with off already at (co, kw). Returns 0 beyond K'.
+template <int ES>
+__device__ __forceinline__ uint32_t rowconv_weight(const char* base, long long off, int KH, int KW,
+                                                   int cg, int k, int k_lim) {
+    if (k >= k_lim) return 0u;
+    const int kh = k / cg;
+    const int c = k - kh * cg;
+    const long long idx = off + static_cast<long long>(c * KH + kh) * KW;
+    if constexpr (ES == 4) return reinterpret_cast<const uint32_t*>(base)[idx];
+    else return reinterpret_cast<const unsigned short*>(base)[idx];
+}
+template <int ES>
+__device__ __forceinline__ uint4 load_chunk_rowconv(const char* base, long long off, int KH, int KW,
+                                                    bool row_ok, int k0, int k_lim) {
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (!row_ok || k0 >= k_lim) return v;
+    const int cg = k_lim / KH;
+    if constexpr (ES == 4) {
+        v.x = rowconv_weight<ES>(base, off, KH, KW, cg, k0, k_lim);
+        v.y = rowconv_weight<ES>(base, off, KH, KW, cg, k0 + 1, k_lim);
+        v.z = rowconv_weight<ES>(base, off, KH, KW, cg, k0 + 2, k_lim);
+        v.w = rowconv_weight<ES>(base, off, KH, KW, cg, k0 + 3, k_lim);
+    } else {
+        uint32_t e[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) e[i] = rowconv_weight<ES>(base, off, KH, KW, cg, k0 + i, k_lim);
+        v = make_uint4(e[0] | (e[1] << 16), e[2] | (e[3] << 16), e[4] | (e[5] << 16), e[6] | (e[7] << 16));
+    }
+    return v;
+}
+
+// Lays the filter bank of a convolution out as the stage images the kernel above consumes, once
+// per call: for every (batch entry = group, n-tile, k-block) BN lines of 128 bytes in the swizzled
+// K-major layout (hi image, then lo image for fp32). One thread per 16-byte chunk.
+template <int ES>
+__global__ void pack_weights_kernel(const TsParams tp, unsigned char* out, long long total_chunks) {
+    const Params& p = tp.base;
+    constexpr int BK = 128 / ES;
+    constexpr int CPE = 16 / ES;
+    const int BN = p.BN;
+    const int num_kb = (p.K + BK - 1) / BK;
+    const long long stage_bytes = static_cast<long long>(BN) * 128 * (ES == 4 ? 2 : 1);
+    for (long long id = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; id < total_chunks;
+         id += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int c = static_cast<int>(id & 7);
+        long long r = id >> 3;
+        const int L = static_cast<int>(r % BN);
+        r /= BN;
+        const int kb = static_cast<int>(r % num_kb);
+        r /= num_kb;
+        const int tn = static_cast<int>(r % p.tiles_n);
+        const int b = static_cast<int>(r / p.tiles_n);
+        const long long b_boff = static_cast<long long>(b) * p.b.batch_stride;
+        uint4 v;
+        if (tp.a_kind == A_ROWCONV) {
+            const int kw = L / tp.rc_cpt;
+            const int co = tn * tp.rc_cpt + (L - kw * tp.rc_cpt);
+            v = load_chunk_rowconv<ES>(p.b.base, b_boff + (static_cast<long long>(co) * p.K) * tp.rc_kw + kw,
+                                       p.g.KH, tp.rc_kw, co < p.N, kb * BK + c * CPE, p.K);
+        } else {
+            v = load_chunk_dense<ES>(p.b, b_boff, tn * BN + L, p.N, kb * BK + c * CPE, p.K);
+        }
+        unsigned char* img = out + (((static_cast<long long>(b) * p.tiles_n + tn) * num_kb) + kb) * stage_bytes;
+        const long long o = static_cast<long long>(L) * 128 + ((c ^ (L & 7)) << 4);
+        if constexpr (ES == 2) {
+            *reinterpret_cast<uint4*>(img + o) = v;
+        } else {
+            uint4 hi, lo;
+            split_tf32(v.x, hi.x, lo.x);
+            split_tf32(v.y, hi.y, lo.y);
+            split_tf32(v.z, hi.z, lo.z);
+            split_tf32(v.w, hi.w, lo.w);
+            *reinterpret_cast<uint4*>(img + o) = hi;
+            *reinterpret_cast<uint4*>(img + static_cast<long long>(BN) * 128 + o) = lo;
+        }
+    }
+}
+
 template <int ES>
 __global__ void __launch_bounds__(kTsThreads, 1)
     contraction_ts_kernel(const __grid_constant__ TsParams tp) {
@@ -132,7 +228,7 @@ __global__ void __launch_bounds__(kTsThreads, 1)
         abort_flag = 0;
         for (int s = 0; s < S; ++s) {
             ptx::mbar_init(ptx::smem_u32(&full_a[s]), 128u);
-            ptx::mbar_init(ptx::smem_u32(&full_b[s]), kTsLoaderThreads);
+            ptx::mbar_init(ptx::smem_u32(&full_b[s]), tp.b_packed ? 1u : kTsLoaderThreads);
             ptx::mbar_init(ptx::smem_u32(&empty_bar[s]), 1u);
         }
         for (int i = 0; i < 2; ++i) {
@@ -140,6 +236,23 @@ __global__ void __launch_bounds__(kTsThreads, 1)
             ptx::mbar_init(ptx::smem_u32(&tempty_bar[i]), 128u);
         }
         ptx::fence_mbar_init();
+    }
+    if (tp.a_kind == A_ROWCONV) {
+        // k' = kh*C + c -> (offset of the input row, kh*dh); the column is the thread's own.
+        // Channel-fastest, so that a k-block usually lies inside one kh: one validity test and a
+        // constant address stride (H*W) for the whole block.
+        KEntry* kt = reinterpret_cast<KEntry*>(smem_raw);
+        for (int k = threadIdx.x; k < num_kb * BK; k += blockDim.x) {
+            KEntry e;
+            const int kk = k < p.K ? k : 0;
+            const int cg = p.K / p.g.KH;  // channels per group
+            const int kh = kk / cg;
+            const int ch = kk - kh * cg;
+            e.off = (ch * p.g.H + kh * p.g.dh) * p.g.W;
+            e.dy = static_cast<short>(kh * p.g.dh);
+            e.dx = 0;
+            kt[k] = e;
+        }
     }
     if (tp.a_kind == A_IM2COL) {
         // k -> (offset, dy, dx) table, filled cooperatively; k beyond K is never read as valid
@@ -178,6 +291,78 @@ __global__ void __launch_bounds__(kTsThreads, 1)
             const bool w = ptx::mbar_wait_bounded(ptx::smem_u32(&tfull_bar[buf]), tphase, abort_p);
             if (!__all_sync(0xffffffffu, w)) break;
             ptx::tc_fence_after();
+            if (tp.a_kind == A_ROWCONV) {
+                const int tm = m0 / kBM, tn = n0 / BN;
+                const int pos = (tm * 4 + warp) * tp.rc_T - tp.rc_lo + lane;
+                const int OHW = p.g.OH * p.g.W;
+                const bool pos_ok = pos >= 0 && pos < p.M;
+                const int img = pos_ok ? pos / OHW : 0;
+                const int rem = pos_ok ? pos - img * OHW : 0;
+                const int oh = rem / p.g.W;
+                const int u = rem - oh * p.g.W;
+                const bool produce = pos_ok && lane >= tp.rc_lo && lane < tp.rc_lo + tp.rc_T && u < p.g.OW;
+                const int c0 = tn * tp.rc_cpt;
+                const long long obase = static_cast<long long>(img) * p.g.out_img_stride +
+                                        static_cast<long long>(b) * p.d_batch_stride +
+                                        static_cast<long long>(oh) * p.g.OW + u;
+                const uint32_t trow = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + buf * BN;
+                const int nco = min(tp.rc_cpt, p.N - c0);
+                const char* bias_g =
+                    p.bias ? p.bias + (static_cast<long long>(b) * p.bias_stride + c0) * ES : nullptr;
+                for (int co0 = 0; co0 < ((p.ablate & 8) ? 0 : nco); co0 += 16) {
+                    // bias first (one value per lane, broadcast later): keeps loads out of the
+                    // store loop, where they would serialise behind each store
+                    float bv = 0.0f;
+                    if (bias_g != nullptr && lane < 16 && co0 + lane < nco) {
+                        const char* bp = bias_g + static_cast<long long>(co0 + lane) * ES;
+                        if constexpr (ES == 4) bv = out_load<OUT_F32>(bp);
+                        else bv = p.fmt == FMT_F16 ? out_load<OUT_F16>(bp) : out_load<OUT_BF16>(bp);
+                    }
+                    float acc[16];
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) acc[e] = __shfl_sync(0xffffffffu, bv, e);
+                    for (int kw = 0; kw < tp.rc_kw; ++kw) {
+                        uint32_t d[16];
+                        ptx::tmem_ld_32x16(trow + kw * tp.rc_cpt + co0, d);
+                        ptx::tmem_ld_wait();
+                        const int src = lane + kw - tp.rc_lo;
+                        const bool in = static_cast<unsigned>(u + kw - tp.rc_lo) < static_cast<unsigned>(p.g.W);
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) {
+                            const float tv = __uint_as_float(__shfl_sync(0xffffffffu, d[e], src & 31));
+                            acc[e] += in ? tv : 0.0f;
+                        }
+                    }
+                    if (produce && !((p.ablate & 16) && acc[0] != 123.456f)) {
+                        char* optr = p.d + (obase + static_cast<long long>(c0 + co0) * p.g.P) * ES;
+                        const long long cstride = static_cast<long long>(p.g.P) * ES;
+                        if (co0 + 16 <= nco) {
+#pragma unroll
+                            for (int e = 0; e < 16; ++e) {
+                                if constexpr (ES == 4) out_store<OUT_F32>(optr + e * cstride, acc[e]);
+                                else if (p.fmt == FMT_F16) out_store<OUT_F16>(optr + e * cstride, acc[e]);
+                                else out_store<OUT_BF16>(optr + e * cstride, acc[e]);
+                            }
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 16; ++e) {
+                                if (co0 + e < nco) {
+                                    if constexpr (ES == 4) out_store<OUT_F32>(optr + e * cstride, acc[e]);
+                                    else if (p.fmt == FMT_F16) out_store<OUT_F16>(optr + e * cstride, acc[e]);
+                                    else out_store<OUT_BF16>(optr + e * cstride, acc[e]);
+                                }
+                            }
+                        }
+                    }
+                }
+                ptx::tc_fence_before();
+                ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));
+                if (++buf == static_cast<uint32_t>(nbuf)) {
+                    buf = 0;
+                    tphase ^= 1u;
+                }
+                continue;
+            }
             const int i = m0 + warp * 32 + lane;
             const bool row_ok = i < p.M;
             long long rowbase, colstride;
@@ -232,7 +417,19 @@ __global__ void __launch_bounds__(kTsThreads, 1)
             const bool row_ok = i < p.M;
             long long pbase = 0;
             int ih0 = -(1 << 30), iw0 = -(1 << 30);
-            if (tp.a_kind == A_IM2COL) {
+            if (tp.a_kind == A_ROWCONV) {
+                const int pos = ((m0 / kBM) * 4 + q) * tp.rc_T - tp.rc_lo + lane;
+                if (pos >= 0 && pos < p.M) {
+                    const int OHW = p.g.OH * p.g.W;
+                    const int img = pos / OHW;
+                    const int rem = pos - img * OHW;
+                    const int oh = rem / p.g.W;
+                    iw0 = rem - oh * p.g.W;  // the input column itself: always inside the row
+                    ih0 = oh * p.g.sh - p.g.pad_t;
+                    pbase = a_boff + static_cast<long long>(img) * p.g.img_stride +
+                            static_cast<long long>(ih0) * p.g.W + iw0;
+                }
+            } else if (tp.a_kind == A_IM2COL) {
                 if (row_ok) {
                     const int img = i / p.g.P;
                     const int pp = i - img * p.g.P;
@@ -263,7 +460,25 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                 if (p.ablate & 1) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] = 0x3f800000u + j;
-                } else if (tp.a_kind == A_IM2COL) {
+                } else if (tp.a_kind == A_ROWCONV && kcount == BK && ktable[k0].dy == ktable[k0 + BK - 1].dy) {
+                    // whole k-block inside one kh: consecutive k are consecutive channels
+                    const KEntry e0 = ktable[k0];
+                    const bool in = static_cast<unsigned>(ih0 + e0.dy) < static_cast<unsigned>(p.g.H);
+                    const long long hw = static_cast<long long>(p.g.H) * p.g.W;
+                    if constexpr (ES == 4) {
+                        const uint32_t* x = reinterpret_cast<const uint32_t*>(p.a.base) + (in ? pbase + e0.off : 0);
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = in ? x[j * hw] : 0u;
+                    } else {
+                        const unsigned short* x = reinterpret_cast<const unsigned short*>(p.a.base) + (in ? pbase + e0.off : 0);
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const uint32_t lo = in ? x[(2 * j) * hw] : 0u;
+                            const uint32_t hi = in ? x[(2 * j + 1) * hw] : 0u;
+                            v[j] = lo | (hi << 16);
+                        }
+                    }
+                } else if (tp.a_kind == A_IM2COL || tp.a_kind == A_ROWCONV) {
                     const KEntry* te = ktable + k0;
                     if constexpr (ES == 4) {
                         const uint32_t* x = reinterpret_cast<const uint32_t*>(p.a.base);
@@ -376,6 +591,35 @@ __global__ void __launch_bounds__(kTsThreads, 1)
         const bool b_atom32 = ES == 4 && !p.b.k_major;
         uint32_t s = 0, ph = 0;
         bool ok = true;
+        if (tp.b_packed != nullptr) {
+            // stage images were prepared in global memory: one thread streams them in with bulk
+            // copies, the other loader threads have nothing to do
+            if (lt == 0) {
+                for (int t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x) {
+                    int b, m0, n0;
+                    decode_tile(p, t, b, m0, n0);
+                    const unsigned char* src =
+                        tp.b_packed + (static_cast<long long>(b) * p.tiles_n + n0 / BN) * num_kb * stage_bytes;
+                    for (int kb = 0; kb < num_kb; ++kb) {
+                        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&empty_bar[s]), ph ^ 1u, abort_p)) {
+                            ok = false;
+                            break;
+                        }
+                        const uint32_t bar = ptx::smem_u32(&full_b[s]);
+                        const uint32_t sB = smem0 + s * stage_bytes;
+                        ptx::mbar_arrive_expect_tx(bar, stage_bytes);
+                        for (uint32_t o = 0; o < stage_bytes; o += 8192u)
+                            ptx::bulk_load(sB + o, src + static_cast<long long>(kb) * stage_bytes + o,
+                                           min(8192u, stage_bytes - o), bar);
+                        if (++s == static_cast<uint32_t>(S)) {
+                            s = 0;
+                            ph ^= 1u;
+                        }
+                    }
+                }
+            }
+            ok = false;  // skip the gather loop below
+        }
         for (int t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x) {
             int b, m0, n0;
             decode_tile(p, t, b, m0, n0);
@@ -395,6 +639,12 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                         const int L = L0 + q * kTsLoaderLines;
                         if (L >= BN || (p.ablate & 2)) {
                             v[q] = make_uint4(0u, 0u, 0u, 0u);
+                        } else if (tp.a_kind == A_ROWCONV) {
+                            // column L = (kw, co): W[c0+co][c][kh][kw] for k' = kh*C + c
+                            const int kw = L / tp.rc_cpt;
+                            const int co = (n0 / BN) * tp.rc_cpt + (L - kw * tp.rc_cpt);
+                            v[q] = load_chunk_rowconv<ES>(p.b.base, b_boff + (static_cast<long long>(co) * p.K) * tp.rc_kw + kw,
+                                                          p.g.KH, tp.rc_kw, co < p.N, kb * BK + c * CPE, p.K);
                         } else if (p.b.k_major) {
                             v[q] = load_chunk_dense<ES>(p.b, b_boff, n0 + L, p.N, kb * BK + c * CPE, p.K);
                         } else {

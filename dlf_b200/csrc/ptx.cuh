@@ -27,16 +27,19 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                  : "memory");
 }
+// The suspend-time hint lets the hardware park the thread (up to about that many nanoseconds)
+// until the phase completes instead of spinning: pollers then leave the issue slots of their
+// scheduler to the warps that share it (loaders, producers).
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t"
         ".reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t"
         "}"
         : "=r"(ok)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(4000u)
         : "memory");
     return ok != 0;
 }
@@ -50,7 +53,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
     const long long t0 = clock64();
     for (uint32_t it = 1;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((it & 127u) == 0u) {
+        if ((it & 15u) == 0u) {
             if (*abort_flag) return false;
             if (clock64() - t0 > (1ll << 32)) {
                 *abort_flag = 1;
@@ -80,6 +83,15 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
         " [%0], [%1, {%3, %4, %5}], [%2];"
         :
         : "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+// Untiled bulk copy global -> shared (both 16-byte aligned, size a multiple of 16), completing on
+// an mbarrier of this CTA.
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        :
+        : "r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
         : "memory");
 }
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {

@@ -8,6 +8,8 @@ convolution's epilogue.
 """
 import ctypes
 
+import torch
+
 from . import lib
 from .gblas import BLASError, StatusCode, _check, _ptr, _stream, precision_of
 
@@ -57,6 +59,21 @@ class Filter2D:
         return (self.batches, self.num_kernels, self.output_h, self.output_w)
 
 
+_WORKSPACES = {}
+
+
+def _workspace(device, stream, nbytes):
+    """Scratch for the packed filter bank, one buffer per (device, stream), grown on demand - the
+    role the context's temporary-buffer pool plays in the reference (gpgpu/src/gpgpu.cpp:189-214).
+    Calls on one stream are ordered, so they can share it."""
+    key = (device.index, stream.cuda_stream)
+    buf = _WORKSPACES.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+        _WORKSPACES[key] = buf
+    return buf
+
+
 def conv2d(batches, channels, height, width, output_h, output_w, num_kernels, group, kernel_h,
            kernel_w, pad_top, pad_left, pad_bottom, pad_right, stride_h, stride_w, dilation_h,
            dilation_w, im_buffer, kernel_buffer, result_buffer, queue=None, event=None, bias=None):
@@ -77,6 +94,9 @@ def conv2d(batches, channels, height, width, output_h, output_w, num_kernels, gr
     if bias is not None and bias.numel() < num_kernels:
         raise BLASError(StatusCode.kInvalidValue)
     s, sp = _stream(queue)
+    ws = _workspace(result_buffer.device, s, lib().dlf_b200_conv2d_workspace_bytes(
+        int(prec), batches, channels, height, width, output_h, output_w, num_kernels, group,
+        kernel_h, kernel_w))
     if event is not None:
         event.start.record(s)
     rc = lib().dlf_b200_conv2d(
@@ -84,7 +104,7 @@ def conv2d(batches, channels, height, width, output_h, output_w, num_kernels, gr
         kernel_h, kernel_w, pad_top, pad_left, pad_bottom, pad_right, stride_h, stride_w,
         dilation_h, dilation_w, _ptr(im_buffer), _ptr(kernel_buffer),
         _ptr(bias) if bias is not None else ctypes.c_void_p(0), _ptr(result_buffer),
-        ctypes.c_void_p(0), 0, sp)
+        ctypes.c_void_p(ws.data_ptr()), ws.numel(), sp)
     if event is not None:
         event.end.record(s)
     _check(rc)

@@ -124,7 +124,8 @@ int dlf_b200_device_status(int* device_status);
 /* Tuning overrides for experiments, for every following call of this process: force the N-tile
  * width (64, 128 or 256; 0 = automatic) and the operand path: 0 = automatic, 1 = never the TMA
  * producer, 2 = always the loader-warp kernel with both operands in shared memory, 3 = the
- * kernel that keeps operand A in tensor memory whenever the TMA producer is not used. */
+ * kernel that keeps operand A in tensor memory whenever the TMA producer is not used, 4 = as 0
+ * but convolutions never use the row form (horizontal taps as GEMM columns). */
 void dlf_b200_set_tuning(int force_bn, int force_generic_loader);
 
 /* Counts kernel launches made by this library in this process (all threads). */

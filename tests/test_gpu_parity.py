@@ -361,6 +361,10 @@ CONV_CASES = [
     (2, 8, 13, 11, 12, 3, 2, (1, 2, 2, 1), (2, 1), (1, 2), 2),      # odd everything + groups
     (5, 16, 7, 7, 40, 3, 3, (1, 1, 1, 1), (1, 1), (1, 1), 4),       # tiles straddle images
     (1, 4, 9, 9, 4, 3, 3, (0, 0, 0, 0), (1, 1), (2, 2), 4),         # depthwise, dilated
+    (3, 8, 11, 37, 20, 5, 3, (2, 0, 2, 1), (2, 1), (2, 1), 1),      # row form: 5x3, stride_h 2, dilation_h 2, one-sided pad
+    (2, 6, 6, 70, 150, 2, 7, (0, 3, 1, 3), (1, 1), (1, 1), 1),      # row form: 7 taps per row, several channel tiles
+    (2, 12, 8, 8, 24, 3, 3, (1, 1, 1, 1), (1, 1), (1, 1), 3),       # row form with groups
+    (1, 4, 5, 40, 8, 1, 4, (0, 0, 0, 0), (1, 1), (1, 1), 1),        # row form, no padding: OW < W
 ]
 
 
@@ -386,6 +390,34 @@ def test_conv2d_random_parity(case, dtype):
         assert rel_fro(got, ref) <= FP32_TOL
     else:
         assert max_rel(got, ref) <= HALF_TOL
+
+
+@pytest.mark.parametrize("path", [2, 4, 0x8000, 0x8004])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_conv2d_every_kernel_variant(lib, path, dtype):
+    """Convolutions normally take the row form (horizontal taps as GEMM columns) when stride_w =
+    dilation_w = 1 and the plain implicit-im2col gather otherwise; the loader-warp kernel with
+    both operands in shared memory is the fallback for very long K. Force each of the other two
+    on cases the row form would take, and compare all of them with the oracle."""
+    from dlf_b200 import gdnn
+    lib.set_tuning(0, path)
+    try:
+        for case in (CONV_CASES[0], CONV_CASES[7], CONV_CASES[11]):
+            N, C, H, W, Co, KH, KW, pads, strides, dil, group = case
+            rng = np.random.default_rng(7)
+            X = _round_to(rng.normal(size=(N, C, H, W)).astype(np.float32), dtype)
+            Wt = _round_to((0.1 * rng.normal(size=(Co, C // group, KH, KW))).astype(np.float32), dtype)
+            ref = oracle.conv2d(X, Wt, group=group, pads=pads, strides=strides, dilations=dil, wide=True)
+            filt = gdnn.Filter2D(X.shape, Wt.shape, group).pads(*pads).strides(*strides).dilations(*dil)
+            Y = torch.full(ref.shape, float("nan"), dtype=dtype, device="cuda")
+            gdnn.conv2d_filter(torch.from_numpy(X).to(dtype).cuda(), torch.from_numpy(Wt).to(dtype).cuda(), Y, filt)
+            got = Y.float().cpu().numpy()
+            if dtype == torch.float32:
+                assert rel_fro(got, ref) <= FP32_TOL, case
+            else:
+                assert max_rel(got, ref) <= HALF_TOL, case
+    finally:
+        lib.set_tuning(0, 0)
 
 
 def test_conv2d_config2_full_size_properties():
