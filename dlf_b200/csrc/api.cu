@@ -400,23 +400,46 @@ int launch(const Problem& q, cudaStream_t stream, DeviceState* preset = nullptr)
     p.g = q.g;
     p.status = st->status;
 
-    CUtensorMap tm_a, tm_b;
+    CUtensorMap tm_a, tm_b, tm_d;
     std::memset(&tm_a, 0, sizeof(tm_a));
     std::memset(&tm_b, 0, sizeof(tm_b));
+    std::memset(&tm_d, 0, sizeof(tm_d));
+    p.d_tma = 0;
     if (use_tma) {
         rc = encode_map(*st, &tm_a, q.a, q.es, q.M, q.K, q.batch, kBM);
         if (rc != kSuccess) return rc;
         rc = encode_map(*st, &tm_b, q.b, q.es, q.N, q.K, q.batch, bn);
         if (rc != kSuccess) return rc;
+        // output through TMA stores when nothing of C has to be read and its strides allow it
+        const bool d_ok = q.beta == 0.0f && q.betas == nullptr && q.d_offs == nullptr &&
+                          (reinterpret_cast<uintptr_t>(q.d) & 15u) == 0 && (q.ldd * q.es) % 16 == 0 &&
+                          (q.batch == 1 || (q.d_batch_stride * q.es) % 16 == 0) &&
+                          q.ldd * q.es < (1ll << 40) && q.d_batch_stride * q.es < (1ll << 40) &&
+                          !(g_force_generic.load() & 0x4000);
+        if (d_ok) {
+            cuuint64_t dims[3] = {static_cast<cuuint64_t>(q.M), static_cast<cuuint64_t>(q.N),
+                                  static_cast<cuuint64_t>(q.batch > 1 && q.d_batch_stride ? q.batch : 1)};
+            cuuint64_t strides[2] = {static_cast<cuuint64_t>(q.ldd * q.es),
+                                     static_cast<cuuint64_t>(q.batch > 1 && q.d_batch_stride
+                                                                 ? q.d_batch_stride * q.es
+                                                                 : q.ldd * q.es * (q.N > 0 ? q.N : 1))};
+            if (strides[1] >= (1ull << 40)) strides[1] = strides[0];
+            cuuint32_t box[3] = {32, 32, 1};
+            cuuint32_t estr[3] = {1, 1, 1};
+            CUresult r = st->encode(&tm_d, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, q.d, dims, strides, box, estr,
+                                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                    CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r == CUDA_SUCCESS) p.d_tma = 1;
+        }
     }
 
     const unsigned grid = static_cast<unsigned>(total < st->num_sms ? total : st->num_sms);
     if (use_tma) {
-        contraction_kernel<2, true><<<grid, kThreadsTma, dyn_smem, stream>>>(p, tm_a, tm_b);
+        contraction_kernel<2, true><<<grid, kThreadsTma, dyn_smem, stream>>>(p, tm_a, tm_b, tm_d);
     } else if (q.es == 2) {
-        contraction_kernel<2, false><<<grid, kThreadsGen, dyn_smem, stream>>>(p, tm_a, tm_b);
+        contraction_kernel<2, false><<<grid, kThreadsGen, dyn_smem, stream>>>(p, tm_a, tm_b, tm_d);
     } else {
-        contraction_kernel<4, false><<<grid, kThreadsGen, dyn_smem, stream>>>(p, tm_a, tm_b);
+        contraction_kernel<4, false><<<grid, kThreadsGen, dyn_smem, stream>>>(p, tm_a, tm_b, tm_d);
     }
     g_launches.fetch_add(1);
     CUDA_TRY(cudaGetLastError());

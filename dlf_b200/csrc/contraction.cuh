@@ -47,7 +47,7 @@ constexpr int kTmaWarp = 5;
 constexpr int kFirstLoaderWarp = 6;
 constexpr int kLoaderWarps = 8;
 constexpr int kLoaderThreads = kLoaderWarps * 32;
-constexpr int kThreadsTma = 6 * 32;
+constexpr int kThreadsTma = 10 * 32;  // warps 6-9: a second set of epilogue warps (other half of the columns)
 constexpr int kThreadsGen = (kFirstLoaderWarp + kLoaderWarps) * 32;
 constexpr int kMaxStages = 8;
 constexpr int kGroupM = 8;  // tile rasterisation: kGroupM row-tiles share their column sweep
@@ -95,6 +95,8 @@ struct Params {
     long long bias_stride;
     Im2colGeom g;
     int* status;
+    int d_tma;   // 16-bit outputs with beta == 0 and TMA-compatible strides: the epilogue stages
+                 // 32 x 32 blocks in shared memory and writes them with TMA stores
     int ablate;  // measurement aid: bit 0 A producer skips its loads, bit 1 B loaders skip theirs,
                  // bit 2 producers skip the TMEM stores (results are then meaningless)
 };
@@ -228,7 +230,7 @@ __device__ __forceinline__ void store_chunk(uint32_t tile, uint32_t lo_tile, int
 template <int ES, bool USE_TMA>
 __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
     contraction_kernel(const __grid_constant__ Params p, const __grid_constant__ CUtensorMap tmA,
-                       const __grid_constant__ CUtensorMap tmB) {
+                       const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmD) {
     static_assert(!(USE_TMA && ES == 4), "fp32 operands need the split done by loader warps");
     constexpr int BK = 128 / ES;               // k-values per stage (one 128-byte line)
     constexpr int E = BK;                      // rows per MN-major row group
@@ -246,6 +248,9 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
     __shared__ __align__(16) PixelEntry pix_table[USE_TMA ? 1 : kLoaderWarps * kBM];
+    // output staging of the TMA-store epilogue: per epilogue warp two 32 x 32 blocks of 16-bit
+    // values, [column][row] with rows contiguous (64-byte lines)
+    __shared__ __align__(128) uint8_t d_stage[USE_TMA ? 8 * 2 * 2048 : 16];
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -265,7 +270,7 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
         }
         for (int i = 0; i < 2; ++i) {
             ptx::mbar_init(ptx::smem_u32(&tfull_bar[i]), 1u);
-            ptx::mbar_init(ptx::smem_u32(&tempty_bar[i]), 128u);
+            ptx::mbar_init(ptx::smem_u32(&tempty_bar[i]), USE_TMA ? 256u : 128u);
         }
         ptx::fence_mbar_init();
     }
@@ -284,9 +289,14 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&tmem_slot);
     volatile int* abort_p = &abort_flag;
 
-    if (warp < 4) {
+    if (warp < 4 || (USE_TMA && warp >= 6)) {
         // ------------------------------------------------------------ epilogue
+        // TMA variant: warps 0-3 take the first half of the tile's columns, warps 6-9 the second
+        const int q = warp & 3;                       // TMEM lane quadrant (warp index mod 4)
+        const int ewarp = warp < 4 ? warp : warp - 2;  // 0..7: staging buffer index
+        const int chalf = (USE_TMA && warp >= 6) ? 1 : 0;
         uint32_t it = 0;
+        uint32_t chunk_no = 0;  // TMA-store epilogue: 32-column blocks written so far by this warp
         for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x, ++it) {
             int b, m0, n0;
             decode_tile(p, t, b, m0, n0);
@@ -297,7 +307,7 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
             if (!__all_sync(0xffffffffu, w)) break;
             ptx::tc_fence_after();
 
-            const int i = m0 + warp * 32 + lane;
+            const int i = m0 + q * 32 + lane;
             const bool row_ok = i < p.M;
             long long rowbase;
             long long colstride;
@@ -314,10 +324,56 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
             const float alpha = p.alphas ? p.alphas[b] : p.alpha;
             const float beta = p.betas ? p.betas[b] : p.beta;
             const char* bias =
-                p.bias ? p.bias + (static_cast<long long>(b) * p.bias_stride + n0) * ES : nullptr;
-            const uint32_t trow = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + buf * BN;
-            char* optr = p.d + (rowbase + static_cast<long long>(n0) * colstride) * ES;
-            const int ncols = min(BN, p.N - n0);
+                p.bias ? p.bias + (static_cast<long long>(b) * p.bias_stride + n0 + (USE_TMA ? chalf * (BN / 2) : 0)) * ES : nullptr;
+            const int cb = USE_TMA ? chalf * (BN / 2) : 0;  // first column of this warp's share
+            const uint32_t trow = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN + cb;
+            char* optr = p.d + (rowbase + static_cast<long long>(n0 + cb) * colstride) * ES;
+            const int ncols = max(0, min(USE_TMA ? BN / 2 : BN, p.N - n0 - cb));
+            if constexpr (USE_TMA) {
+                if (p.d_tma) {
+                    const int i0 = m0 + q * 32;
+                    for (int c0 = 0; c0 < ncols && i0 < p.M; c0 += 32, ++chunk_no) {
+                        uint32_t v[32];
+                        ptx::tmem_ld_32x32(trow + c0, v);
+                        ptx::tmem_ld_wait();
+                        float bv = 0.0f;
+                        if (bias != nullptr && c0 + lane < ncols)
+                            bv = p.fmt == FMT_F16 ? out_load<OUT_F16>(bias + (c0 + lane) * 2)
+                                                  : out_load<OUT_BF16>(bias + (c0 + lane) * 2);
+                        // the block written two chunks ago used the same staging buffer
+                        if (chunk_no >= 2) {
+                            if (lane == 0) ptx::bulk_wait_group_read<1>();
+                            __syncwarp();
+                        }
+                        const uint32_t sbuf =
+                            ptx::smem_u32(d_stage) + (ewarp * 2 + (chunk_no & 1u)) * 2048u + lane * 2u;
+                        if (p.fmt == FMT_F16) {
+#pragma unroll
+                            for (int jj = 0; jj < 32; ++jj) {
+                                const float r = alpha * __uint_as_float(v[jj]) + __shfl_sync(0xffffffffu, bv, jj);
+                                const unsigned short h = __half_as_ushort(__float2half_rn(r));
+                                asm volatile("st.shared.u16 [%0], %1;" ::"r"(sbuf + jj * 64u), "h"(h) : "memory");
+                            }
+                        } else {
+#pragma unroll
+                            for (int jj = 0; jj < 32; ++jj) {
+                                const float r = alpha * __uint_as_float(v[jj]) + __shfl_sync(0xffffffffu, bv, jj);
+                                const unsigned short h = __bfloat16_as_ushort(__float2bfloat16_rn(r));
+                                asm volatile("st.shared.u16 [%0], %1;" ::"r"(sbuf + jj * 64u), "h"(h) : "memory");
+                            }
+                        }
+                        ptx::fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            ptx::tma_store_3d(&tmD, sbuf - lane * 2u, i0, n0 + cb + c0, p.d_batch_stride ? b : 0);
+                            ptx::bulk_commit_group();
+                        }
+                    }
+                    ptx::tc_fence_before();
+                    ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));
+                    continue;
+                }
+            }
             if constexpr (ES == 4) {
                 epilogue_dispatch<OUT_F32>(trow, ncols, optr, colstride * ES, row_ok, alpha, beta,
                                            bias, lane);
@@ -331,6 +387,9 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
             }
             ptx::tc_fence_before();
             ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));
+        }
+        if constexpr (USE_TMA) {
+            if (p.d_tma && lane == 0) ptx::bulk_wait_group<0>();  // all staged blocks are in global memory
         }
     } else if (warp == kMmaWarp) {
         // ------------------------------------------------------------ UMMA issuer
