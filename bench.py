@@ -396,9 +396,14 @@ def main():
     ap.add_argument("--workload", default="conv_c2")
     ap.add_argument("--headline-only", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--batch", type=int, default=None, help="images per GPU for conv_c2 (profiling: a small case)")
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="only the timed kernel loop: no end-to-end leg, parity check, CPU baseline or extras")
     args = ap.parse_args()
     args.steps_given = args.steps is not None
     if args.impl == "reference":
+        os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)  # torchrun sets it to 1
+        os.environ["OPENBLAS_NUM_THREADS"] = str(os.cpu_count() or 1)
         if args.warmup is None:
             args.warmup = 1
         reference_arm(args, int(os.environ.get("RANK", "0")))
@@ -413,7 +418,7 @@ def main():
     peaks = measured_peaks()
 
     table = {
-        "conv_c2": lambda: ConvC2(),
+        "conv_c2": lambda: ConvC2(shape=dict(N=args.batch) if args.batch else None),
         "gemm_f16_4096": lambda: GemmWorkload("gemm_f16_4096", "f16", 4096, 4096, 4096),
         "sgemm_1024": lambda: GemmWorkload("sgemm_f32_1024", "f32", 1024, 1024, 1024, dist="uniform"),
         "sgemm_16384": lambda: GemmWorkload("sgemm_f32_16384_tn", "f32", 16384, 16384, 16384, ta=True, alpha=0.5,
@@ -443,7 +448,7 @@ def main():
 
     # end to end through the public API with host buffers
     e2e = None
-    if hasattr(w, "e2e_step"):
+    if hasattr(w, "e2e_step") and not args.kernel_only:
         e_steps = max(3, min(steps, 30))
         for i in range(3):
             w.e2e_step(i)
@@ -457,7 +462,7 @@ def main():
         e2e = {"value": w.flops * world / dt_e / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
                "d2h_bytes_per_step": d2h, "ms_per_step": dt_e * 1e3}
 
-    parity = w.check() if hasattr(w, "check") else None
+    parity = w.check() if hasattr(w, "check") and not args.kernel_only else None
 
     if rank != 0:
         if world > 1:
@@ -497,12 +502,12 @@ def main():
     if e2e:
         line["e2e"] = e2e
 
-    if world == 1 and not args.no_cpu_baseline and hasattr(w, "cpu_reference"):
+    if world == 1 and not args.no_cpu_baseline and not args.kernel_only and hasattr(w, "cpu_reference"):
         cb = w.cpu_reference(10.0)
         line["cpu_baseline"] = {"value": cb["value"], "unit": "TFLOP/s", "cores": os.cpu_count() or 1,
                                 "kind": "port", "sample": cb["sample"]}
 
-    if world == 1 and not args.headline_only and args.workload == "conv_c2":
+    if world == 1 and not args.headline_only and not args.kernel_only and args.workload == "conv_c2":
         extras = {}
         del w
         torch.cuda.empty_cache()
