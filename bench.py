@@ -196,6 +196,17 @@ class GemmWorkload(Workload):
         self.C = [torch.randn(self.batch * self.m * self.n, generator=g, device=device, dtype=torch.float32).to(td)
                   for _ in range(sets)]
 
+    def step_sharded(self, i, world, rank):
+        """One large GEMM over `world` GPUs: rank r computes its block of rows of C, then the row
+        blocks are all-gathered (NCCL) so that every rank holds all of C. Operands are replicated."""
+        from dlf_b200 import gblas, shard
+        j = i % self.sets
+        ta = gblas.Transpose.Trans if self.ta else gblas.Transpose.NoTrans
+        tb = gblas.Transpose.Trans if self.tb else gblas.Transpose.NoTrans
+        A = self.A[j].view(self.k, self.m) if self.ta else self.A[j].view(self.m, self.k)
+        B = self.B[j].view(self.n, self.k) if self.tb else self.B[j].view(self.k, self.n)
+        shard.gemm_row_sharded(ta, tb, self.alpha, A, B, self.beta, self.C[j].view(self.m, self.n), world, rank)
+
     def step(self, i):
         from dlf_b200 import gblas
         j = i % self.sets
@@ -428,23 +439,27 @@ def main():
     }
     w = table[args.workload]()
     sets = w.sets_needed()
-    w.seed_used = rank
-    w.setup(device, rank, sets)
+    # a single (unbatched) GEMM is sharded by rows of C with an all-gather: strong scaling, and
+    # every rank must hold the same operands
+    row_sharded = world > 1 and isinstance(w, GemmWorkload) and w.batch == 1
+    w.seed_used = 0 if row_sharded else rank
+    w.setup(device, w.seed_used, sets)
+    step_fn = (lambda i: w.step_sharded(i, world, rank)) if row_sharded else w.step
 
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
     for i in range(warmup):  # warm-up happens here so that the launch counter brackets the timed steps only
-        w.step(i)
+        step_fn(i)
     l0 = dlf_b200.launch_count()
-    ms, t0, t1 = time_steps(w.step, steps, 0, world)
+    ms, t0, t1 = time_steps(step_fn, steps, 0, world)
     launches = dlf_b200.launch_count() - l0
     if rank == 0:
         sampler.stop()
     launches_timed = launches
     status = dlf_b200.device_status()
     sec_per_step = ms / 1e3 / steps
-    value = w.flops * world / sec_per_step / 1e12
+    value = (w.flops if row_sharded else w.flops * world) / sec_per_step / 1e12
 
     # end to end through the public API with host buffers
     e2e = None
@@ -471,7 +486,7 @@ def main():
             dist.destroy_process_group()
         return
 
-    tf_per_gpu = w.flops / sec_per_step / 1e12
+    tf_per_gpu = (w.flops / world if row_sharded else w.flops) / sec_per_step / 1e12
     peak = w.tensor_peak(peaks)
     roofline = {"bound": "tensor", "achieved": tf_per_gpu, "peak": peak, "unit": "TFLOP/s",
                 "frac": tf_per_gpu / peak, "traffic": None,
@@ -487,13 +502,18 @@ def main():
     prof = os.path.join(ROOT, "profiles", "traffic.json")
     if os.path.exists(prof):
         with open(prof) as f:
-            roofline["traffic"] = json.load(f).get(w.name)
+            entry = json.load(f).get(w.name)
+            if isinstance(entry, dict):
+                roofline["traffic"] = entry.get("bytes_per_launch")
+                roofline["traffic_note"] = entry.get("captured")
 
     line = {"metric": "gemm_conv_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
-            "warmup": warmup, "ms_per_step": sec_per_step * 1e3, "higher_is_better": True, "scaling": "weak",
+            "warmup": warmup, "ms_per_step": sec_per_step * 1e3, "higher_is_better": True,
+            "scaling": "strong" if row_sharded else "weak",
             "vs_baseline": None, "dtype": w.dtype, "data": "synthetic",
             "config": {"workload": w.name, "per_gpu_batch": getattr(w, "shape", {}).get("N"),
-                       "sharding": "batch per rank, no collective" if world > 1 else "single GPU",
+                       "sharding": ("rows of C per rank + NCCL all-gather of the row blocks" if row_sharded else
+                                    "batch per rank, no collective") if world > 1 else "single GPU",
                        "l2": "rotating %d input/output buffer sets (%.0f MB > 126 MB L2)" % (
                            sets, sets * (getattr(w, "x_bytes", w.bytes) + getattr(w, "y_bytes", 0)) / 1e6),
                        "arithmetic": "3xTF32 tcgen05, fp32 accumulate" if w.dtype == "f32" else "tcgen05 f16, fp32 accumulate"},

@@ -11,6 +11,8 @@
 #include <atomic>
 #include <climits>
 #include <cstdint>
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <vector>
@@ -53,6 +55,8 @@ struct DeviceState {
     int static_smem_gen4 = 0;
     int static_smem_ts2 = 0;
     int static_smem_ts4 = 0;
+    int static_smem_pair = 0;
+    int max_pair_clusters = 0;  // co-resident CTA pairs of the pair kernel (0 = not usable)
     PFN_cuTensorMapEncodeTiled_v12000 encode = nullptr;
 };
 
@@ -105,6 +109,31 @@ int ensure_device(DeviceState** out) {
         CUDA_TRY(cudaFuncSetAttribute(contraction_ts_kernel<4>,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       kSmemPerBlockOptin - st.static_smem_ts4));
+        {
+            auto pair_kernel = contraction_kernel<2, true, true>;
+            CUDA_TRY(cudaFuncGetAttributes(&fa, pair_kernel));
+            st.static_smem_pair = static_cast<int>(fa.sharedSizeBytes);
+            const int dyn = kSmemPerBlockOptin - st.static_smem_pair;
+            CUDA_TRY(cudaFuncSetAttribute(pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn));
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(2 * st.num_sms, 1, 1);
+            cfg.blockDim = dim3(kThreadsTma, 1, 1);
+            cfg.dynamicSmemBytes = static_cast<size_t>(dyn);
+            cudaLaunchAttribute attr;
+            attr.id = cudaLaunchAttributeClusterDimension;
+            attr.val.clusterDim.x = 2;
+            attr.val.clusterDim.y = 1;
+            attr.val.clusterDim.z = 1;
+            cfg.attrs = &attr;
+            cfg.numAttrs = 1;
+            int n = 0;
+            const cudaError_t oe = cudaOccupancyMaxActiveClusters(&n, pair_kernel, &cfg);
+            if (oe == cudaSuccess) st.max_pair_clusters = n;
+            if (std::getenv("DLF_B200_DEBUG"))
+                std::fprintf(stderr, "dlf_b200: pair kernel static smem %d, dyn %d, max clusters %d (%s)\n",
+                             st.static_smem_pair, dyn, n, cudaGetErrorString(oe));
+            (void)cudaGetLastError();
+        }
         void* fn = nullptr;
         cudaDriverEntryPointQueryResult qres;
         CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
@@ -204,10 +233,37 @@ int encode_map(const DeviceState& st, CUtensorMap* map, const GenOperand& op, in
     box[2] = 1;
     const CUtensorMapDataType dt =
         es == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT32;
+    // MN-major fp32 tiles use the 32-byte-atom form of the 128-byte swizzle (see contraction.cuh)
+    const CUtensorMapSwizzle swz =
+        (es == 4 && !op.k_major) ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B;
     CUresult r = st.encode(map, dt, 3, const_cast<char*>(op.base), dims, strides, box, estr,
-                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? kSuccess : kUnexpectedError;
+}
+
+// Tensor map for TMA stores of the output (32 x 32 blocks, no swizzle): only when nothing of C has
+// to be read (beta == 0, no per-batch tables) and D's base and strides are 16-byte multiples.
+bool encode_output_map(const DeviceState& st, CUtensorMap* map, const Problem& q) {
+    const bool d_ok = q.es == 2 && q.beta == 0.0f && q.betas == nullptr && q.d_offs == nullptr &&
+                      (reinterpret_cast<uintptr_t>(q.d) & 15u) == 0 && (q.ldd * q.es) % 16 == 0 &&
+                      (q.batch == 1 || (q.d_batch_stride * q.es) % 16 == 0) &&
+                      q.ldd * q.es < (1ll << 40) && q.d_batch_stride * q.es < (1ll << 40) &&
+                      !(g_force_generic.load() & 0x4000);
+    if (!d_ok) return false;
+    const bool batched = q.batch > 1 && q.d_batch_stride != 0;
+    cuuint64_t dims[3] = {static_cast<cuuint64_t>(q.M), static_cast<cuuint64_t>(q.N),
+                          static_cast<cuuint64_t>(batched ? q.batch : 1)};
+    cuuint64_t strides[2] = {static_cast<cuuint64_t>(q.ldd * q.es),
+                             static_cast<cuuint64_t>(batched ? q.d_batch_stride * q.es
+                                                             : q.ldd * q.es * (q.N > 0 ? q.N : 1))};
+    if (strides[1] >= (1ull << 40)) strides[1] = strides[0];
+    cuuint32_t box[3] = {32, 32, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = st.encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, q.d, dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                           CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
 }
 
 // Tile width. tcgen05.mma with M = 128 was measured (back-to-back issue, this GPU) at about
@@ -236,9 +292,14 @@ int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
     const int a_cols = q.es == 4 ? 64 : 32;
     const int BK = 128 / q.es;
     long long tiles_m = (q.M + kBM - 1) / kBM;
-    int bn = choose_bn(q.M, q.N, q.batch, st.num_sms, true, 256);
+    // fp32 with more than 16 k-blocks (K > 512): accumulate in chunks of 8 k-blocks and sum the
+    // chunks in shared memory (the tensor core's accumulate truncates; see drain_chunk). The
+    // float[BN][128] sum array limits such tiles to 128 columns.
+    const long long num_kb_all = (q.K + BK - 1) / BK;
+    const int kc_blocks = (q.es == 4 && num_kb_all > 16 && !(g_force_generic.load() & 0x1000)) ? 8 : 0;
+    int bn = choose_bn(q.M, q.N, q.batch, st.num_sms, true, kc_blocks ? 128 : 256);
     const int forced = g_force_bn.load();
-    if (forced == 64 || forced == 128 || forced == 256) bn = forced;
+    if (forced == 64 || forced == 128 || (forced == 256 && !kc_blocks)) bn = forced;
     long long tiles_n = (q.N + bn - 1) / bn;
     if (q.rc_kw) {  // tile = 4 warps x rc_T output positions by rc_cpt channels (x rc_kw columns)
         bn = q.rc_cpt * q.rc_kw;
@@ -260,12 +321,16 @@ int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
     }
     const int static_smem = q.es == 2 ? st.static_smem_ts2 : st.static_smem_ts4;
     const int stage_bytes = bn * 128 * (q.es == 4 ? 2 : 1);
-    int stages = (kSmemPerBlockOptin - static_smem - 1024 - ktable_bytes) / stage_bytes;
+    const int sums_bytes = kc_blocks ? bn * 128 * 4 : 0;
+    if (kc_blocks && bn > 128) return kUnexpectedError;
+    int stages = (kSmemPerBlockOptin - static_smem - 1024 - ktable_bytes - sums_bytes) / stage_bytes;
     const int tmem_stages = (512 - acc_bufs * bn) / a_cols;
     if (stages > tmem_stages) stages = tmem_stages;
     if (stages > kMaxStages) stages = kMaxStages;
     if (stages < 2) return kUnexpectedError;
-    size_t dyn_smem = static_cast<size_t>(stages) * stage_bytes + 1024 + ktable_bytes;
+    // dynamic segment: [k table][pad to 1024][B stages][partial sums]
+    const int sums_off = ((ktable_bytes + 1023) / 1024 * 1024) + 1024 + stages * stage_bytes;
+    size_t dyn_smem = static_cast<size_t>(sums_off) + sums_bytes;
     // more than half of the SM's shared memory: never two CTAs (and two 512-column TMEM
     // allocations) on one SM
     if (dyn_smem < 120 * 1024) dyn_smem = 120 * 1024;
@@ -304,10 +369,16 @@ int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
     tp.rc_cpt = q.rc_cpt;
     tp.rc_T = q.rc_T;
     tp.rc_lo = q.rc_lo;
+    tp.kc_blocks = kc_blocks;
+    tp.sums_off = sums_off;
     tp.acc_bufs = acc_bufs;
     tp.ktable_bytes = ktable_bytes;
 
     tp.b_packed = nullptr;
+    {
+        const int raw = (g_force_generic.load() >> 13) & 1;  // experiment: see g_split_raw
+        cudaMemcpyToSymbolAsync(g_split_raw, &raw, sizeof(int), 0, cudaMemcpyHostToDevice, stream);
+    }
     if (q.pack_ws != nullptr && (q.a.im2col || q.rc_kw) && p.b.k_major && !(g_force_generic.load() & 0x8000)) {
         // lay the filter bank out as stage images first (same stream), then stream them with bulk copies
         unsigned char* ws = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(q.pack_ws) + 127) & ~uintptr_t(127));
@@ -325,11 +396,19 @@ int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
         }
     }
 
+    CUtensorMap tm_b;
+    std::memset(&tm_b, 0, sizeof(tm_b));
+    tp.b_tma = 0;
+    if (q.es == 4 && !q.a.im2col && !q.rc_kw && q.b_offs == nullptr && !(g_force_generic.load() & 0x800) &&
+        tma_ok(q.b, q.es, q.N, q.K, q.batch)) {
+        if (encode_map(st, &tm_b, q.b, q.es, q.N, q.K, q.batch, bn) == kSuccess) tp.b_tma = 1;
+    }
+
     const unsigned grid = static_cast<unsigned>(total < st.num_sms ? total : st.num_sms);
     if (q.es == 2)
-        contraction_ts_kernel<2><<<grid, kTsThreads, dyn_smem, stream>>>(tp);
+        contraction_ts_kernel<2><<<grid, kTsThreads, dyn_smem, stream>>>(tp, tm_b);
     else
-        contraction_ts_kernel<4><<<grid, kTsThreads, dyn_smem, stream>>>(tp);
+        contraction_ts_kernel<4><<<grid, kTsThreads, dyn_smem, stream>>>(tp, tm_b);
     g_launches.fetch_add(1);
     CUDA_TRY(cudaGetLastError());
     return kSuccess;
@@ -360,6 +439,63 @@ int launch(const Problem& q, cudaStream_t stream, DeviceState* preset = nullptr)
     int bn = choose_bn(q.M, q.N, q.batch, st->num_sms, false, q.es == 4 ? 128 : 256);
     const int forced = g_force_bn.load();
     if (forced == 64 || forced == 128 || (forced == 256 && q.es == 2)) bn = forced;
+
+    // CTA pairs (cta_group::2): 256 x 256 tiles, each CTA stages 128 rows of A and 128 of B, so
+    // a third less shared-memory fill per flop than a lone 128 x 256 tile.
+    if (use_tma && bn == 256 && q.M > kBM && st->max_pair_clusters > 0 && (g_force_generic.load() & 0x200)) {
+        const long long ptiles_m = (q.M + 2 * kBM - 1) / (2 * kBM);
+        const long long ptiles_n = (q.N + bn - 1) / bn;
+        const long long ptotal = q.batch * ptiles_m * ptiles_n;
+        if (ptotal >= INT_MAX) return kInvalidDimension;
+        const int pstage = (kBM + bn / 2) * 128;
+        int pstages = (kSmemPerBlockOptin - st->static_smem_pair - 1024) / pstage;
+        if (pstages > kMaxStages) pstages = kMaxStages;
+        Params p{};
+        p.M = static_cast<int>(q.M);
+        p.N = static_cast<int>(q.N);
+        p.K = static_cast<int>(q.K);
+        p.batch = static_cast<int>(q.batch);
+        p.BN = bn;
+        p.stages = pstages;
+        p.fmt = q.fmt;
+        p.tiles_m = static_cast<int>(ptiles_m);
+        p.tiles_n = static_cast<int>(ptiles_n);
+        p.total_tiles = static_cast<int>(ptotal);
+        p.alpha = q.alpha;
+        p.beta = q.beta;
+        p.a = q.a;
+        p.b = q.b;
+        p.d = q.d;
+        p.ldd = q.ldd;
+        p.d_batch_stride = q.d_batch_stride;
+        p.bias = q.bias;
+        p.bias_stride = q.bias_stride;
+        p.g = q.g;
+        p.status = st->status;
+        CUtensorMap tm_a, tm_b, tm_d;
+        std::memset(&tm_d, 0, sizeof(tm_d));
+        rc = encode_map(*st, &tm_a, q.a, q.es, q.M, q.K, q.batch, kBM);
+        if (rc != kSuccess) return rc;
+        rc = encode_map(*st, &tm_b, q.b, q.es, q.N, q.K, q.batch, bn / 2);
+        if (rc != kSuccess) return rc;
+        p.d_tma = encode_output_map(*st, &tm_d, q) ? 1 : 0;
+        const long long clusters = ptotal < st->max_pair_clusters ? ptotal : st->max_pair_clusters;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(static_cast<unsigned>(2 * clusters), 1, 1);
+        cfg.blockDim = dim3(kThreadsTma, 1, 1);
+        cfg.dynamicSmemBytes = static_cast<size_t>(pstages) * pstage + 1024;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2;
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        CUDA_TRY(cudaLaunchKernelEx(&cfg, contraction_kernel<2, true, true>, p, tm_a, tm_b, tm_d));
+        g_launches.fetch_add(1);
+        return kSuccess;
+    }
     const long long tiles_n = (q.N + bn - 1) / bn;
     const long long total = q.batch * tiles_m * tiles_n;
     if (total >= INT_MAX) return kInvalidDimension;
@@ -410,27 +546,7 @@ int launch(const Problem& q, cudaStream_t stream, DeviceState* preset = nullptr)
         if (rc != kSuccess) return rc;
         rc = encode_map(*st, &tm_b, q.b, q.es, q.N, q.K, q.batch, bn);
         if (rc != kSuccess) return rc;
-        // output through TMA stores when nothing of C has to be read and its strides allow it
-        const bool d_ok = q.beta == 0.0f && q.betas == nullptr && q.d_offs == nullptr &&
-                          (reinterpret_cast<uintptr_t>(q.d) & 15u) == 0 && (q.ldd * q.es) % 16 == 0 &&
-                          (q.batch == 1 || (q.d_batch_stride * q.es) % 16 == 0) &&
-                          q.ldd * q.es < (1ll << 40) && q.d_batch_stride * q.es < (1ll << 40) &&
-                          !(g_force_generic.load() & 0x4000);
-        if (d_ok) {
-            cuuint64_t dims[3] = {static_cast<cuuint64_t>(q.M), static_cast<cuuint64_t>(q.N),
-                                  static_cast<cuuint64_t>(q.batch > 1 && q.d_batch_stride ? q.batch : 1)};
-            cuuint64_t strides[2] = {static_cast<cuuint64_t>(q.ldd * q.es),
-                                     static_cast<cuuint64_t>(q.batch > 1 && q.d_batch_stride
-                                                                 ? q.d_batch_stride * q.es
-                                                                 : q.ldd * q.es * (q.N > 0 ? q.N : 1))};
-            if (strides[1] >= (1ull << 40)) strides[1] = strides[0];
-            cuuint32_t box[3] = {32, 32, 1};
-            cuuint32_t estr[3] = {1, 1, 1};
-            CUresult r = st->encode(&tm_d, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, q.d, dims, strides, box, estr,
-                                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
-                                    CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-            if (r == CUDA_SUCCESS) p.d_tma = 1;
-        }
+        p.d_tma = encode_output_map(*st, &tm_d, q) ? 1 : 0;
     }
 
     const unsigned grid = static_cast<unsigned>(total < st->num_sms ? total : st->num_sms);
@@ -827,7 +943,9 @@ int dlf_b200_conv2d(int dtype, size_t batches, size_t channels, size_t height, s
     if (path != 2 && path != 4 && stride_w == 1 && dilation_w == 1 && kernel_w >= 2 && kernel_w <= 8 &&
         output_w <= width && lo + hi <= 16 &&
         static_cast<long long>(batches) * output_h * width < INT_MAX - 4096) {
-        const int cpt_max = static_cast<int>((256 / kernel_w) / 16 * 16);
+        // fp32 with K' = C*KH > 512 sums K-chunks in a float[N][128] shared array: N <= 128 then
+        const bool chunked = q.es == 4 && cg * static_cast<long long>(kernel_h) > 512;
+        const int cpt_max = static_cast<int>(((chunked ? 128 : 256) / kernel_w) / 16 * 16);
         const int n_tiles = static_cast<int>((ng + cpt_max - 1) / cpt_max);
         int cpt = static_cast<int>(((ng + n_tiles - 1) / n_tiles + 15) / 16 * 16);
         if (cpt > cpt_max) cpt = cpt_max;

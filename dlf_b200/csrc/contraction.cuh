@@ -107,7 +107,8 @@ struct PixelEntry {  // one output pixel of the current tile (implicit im2col op
 };
 
 // total_tiles < 2^31 is checked on the host, so tile arithmetic stays in 32 bits.
-__device__ __forceinline__ void decode_tile(const Params& p, int t, int& b, int& m0, int& n0) {
+__device__ __forceinline__ void decode_tile(const Params& p, int t, int& b, int& m0, int& n0,
+                                            int rows_per_tile = kBM) {
     const int per = p.tiles_m * p.tiles_n;
     b = t / per;
     const int r = t - b * per;
@@ -116,7 +117,7 @@ __device__ __forceinline__ void decode_tile(const Params& p, int t, int& b, int&
     const int first = gi * kGroupM;
     const int gm = min(p.tiles_m - first, kGroupM);
     const int rr = r - gi * group;
-    m0 = (first + rr % gm) * kBM;
+    m0 = (first + rr % gm) * rows_per_tile;
     n0 = (rr / gm) * p.BN;
 }
 
@@ -194,8 +195,16 @@ __device__ __forceinline__ uint4 load_chunk_im2col(const Params& p, const PixelE
     return v;
 }
 
+// Experiment switch (set from Params::ablate bit 5 by the kernels): hi = the raw fp32 word (the
+// tensor core is expected to ignore its low 13 bits), lo = x - trunc(x) left unrounded.
+__device__ int g_split_raw = 0;
 // x = hi + lo with hi, lo both exactly representable in tf32 (10 explicit mantissa bits).
 __device__ __forceinline__ void split_tf32(uint32_t x, uint32_t& hi, uint32_t& lo) {
+    if (g_split_raw) {
+        hi = x;
+        lo = __float_as_uint(__uint_as_float(x) - __uint_as_float(x & 0xffffe000u));
+        return;
+    }
     const float xf = __uint_as_float(x);
     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(xf));
     const float rest = xf - __uint_as_float(hi);
@@ -227,11 +236,15 @@ __device__ __forceinline__ void store_chunk(uint32_t tile, uint32_t lo_tile, int
     }
 }
 
-template <int ES, bool USE_TMA>
+// PAIR: the CTA is one of a cluster of two that share 256 x BN tiles through cta_group::2 UMMAs
+// (only with USE_TMA). Each CTA loads its own 128 rows of A and BN/2 rows of B; no load is
+// multicast. Rank 0 issues the UMMAs and signals both CTAs' barriers.
+template <int ES, bool USE_TMA, bool PAIR = false>
 __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
     contraction_kernel(const __grid_constant__ Params p, const __grid_constant__ CUtensorMap tmA,
                        const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmD) {
     static_assert(!(USE_TMA && ES == 4), "fp32 operands need the split done by loader warps");
+    static_assert(!PAIR || USE_TMA, "CTA pairs are fed by TMA");
     constexpr int BK = 128 / ES;               // k-values per stage (one 128-byte line)
     constexpr int E = BK;                      // rows per MN-major row group
     constexpr int CPE = 16 / ES;               // elements per 16-byte chunk
@@ -256,11 +269,17 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
     const int lane = threadIdx.x & 31;
     const int BN = p.BN;
     const int S = p.stages;
-    const uint32_t b_tile = static_cast<uint32_t>(BN) * 128u;
+    const uint32_t rank = PAIR ? ptx::cluster_ctarank() : 0u;  // position in the CTA pair
+    const int b_rows = PAIR ? BN / 2 : BN;                     // rows of Bu this CTA stages
+    const uint32_t b_tile = static_cast<uint32_t>(b_rows) * 128u;
     const uint32_t stage_bytes = (A_TILE + b_tile) * (ES == 4 ? 2u : 1u);
     const uint32_t smem0 = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
     const int num_kb = (p.K + BK - 1) / BK;
-    const uint32_t tmem_cols = (2 * BN <= 128) ? 128u : (2 * BN <= 256 ? 256u : 512u);
+    const uint32_t tmem_cols = (PAIR || 2 * BN > 256) ? 512u : (2 * BN <= 128 ? 128u : 256u);
+    const int tile0 = PAIR ? blockIdx.x / 2 : blockIdx.x;
+    const int tile_step = PAIR ? gridDim.x / 2 : gridDim.x;
+    const int tile_rows = PAIR ? 2 * kBM : kBM;
+    const int row_off = PAIR ? static_cast<int>(rank) * kBM : 0;
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
@@ -270,14 +289,20 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
         }
         for (int i = 0; i < 2; ++i) {
             ptx::mbar_init(ptx::smem_u32(&tfull_bar[i]), 1u);
-            ptx::mbar_init(ptx::smem_u32(&tempty_bar[i]), USE_TMA ? 256u : 128u);
+            // PAIR: one arrival per epilogue warp of both CTAs (8 + 8), all on rank 0's barrier
+            ptx::mbar_init(ptx::smem_u32(&tempty_bar[i]), PAIR ? 16u : (USE_TMA ? 256u : 128u));
         }
         ptx::fence_mbar_init();
     }
     if (warp == kMmaWarp) {
         __syncwarp();
-        ptx::tmem_alloc(ptx::smem_u32(&tmem_slot), tmem_cols);
-        ptx::tmem_relinquish();
+        if constexpr (PAIR) {
+            ptx::tmem_alloc_pair(ptx::smem_u32(&tmem_slot), tmem_cols);
+            ptx::tmem_relinquish_pair();
+        } else {
+            ptx::tmem_alloc(ptx::smem_u32(&tmem_slot), tmem_cols);
+            ptx::tmem_relinquish();
+        }
     }
     if (USE_TMA && warp == kTmaWarp && lane == 0) {
         ptx::tma_prefetch_desc(&tmA);
@@ -285,6 +310,7 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
     }
     ptx::tc_fence_before();
     __syncthreads();
+    if constexpr (PAIR) ptx::cluster_sync();  // the peer's barriers exist before anything remote happens
     ptx::tc_fence_after();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&tmem_slot);
     volatile int* abort_p = &abort_flag;
@@ -297,9 +323,10 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
         const int chalf = (USE_TMA && warp >= 6) ? 1 : 0;
         uint32_t it = 0;
         uint32_t chunk_no = 0;  // TMA-store epilogue: 32-column blocks written so far by this warp
-        for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x, ++it) {
+        for (int t = tile0; t < p.total_tiles; t += tile_step, ++it) {
             int b, m0, n0;
-            decode_tile(p, t, b, m0, n0);
+            decode_tile(p, t, b, m0, n0, tile_rows);
+            m0 += row_off;
             const uint32_t buf = it & 1u;
             const uint32_t tphase = (it >> 1) & 1u;
             // tcgen05.ld is warp-collective: the warp leaves together or not at all
@@ -370,7 +397,12 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
                         }
                     }
                     ptx::tc_fence_before();
-                    ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));
+                    if constexpr (PAIR) {
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_u32(&tempty_bar[buf]), 0u));
+                    } else {
+                        ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));
+                    }
                     continue;
                 }
             }
@@ -386,17 +418,22 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
                                                 beta, bias, lane);
             }
             ptx::tc_fence_before();
-            ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));
+            if constexpr (PAIR) {
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_u32(&tempty_bar[buf]), 0u));
+            } else {
+                ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));
+            }
         }
         if constexpr (USE_TMA) {
             if (p.d_tma && lane == 0) ptx::bulk_wait_group<0>();  // all staged blocks are in global memory
         }
     } else if (warp == kMmaWarp) {
         // ------------------------------------------------------------ UMMA issuer
-        if (lane == 0) {
+        if (lane == 0 && rank == 0) {
             const uint32_t idesc =
                 ptx::make_idesc(p.fmt == FMT_F32 ? 2u : static_cast<uint32_t>(p.fmt),
-                                p.a.k_major ? 0u : 1u, p.b.k_major ? 0u : 1u, kBM, BN);
+                                p.a.k_major ? 0u : 1u, p.b.k_major ? 0u : 1u, PAIR ? 2 * kBM : kBM, BN);
             const uint32_t a_step = p.a.k_major ? KSTEP_K : KSTEP_MN;
             const uint32_t b_step = p.b.k_major ? KSTEP_K : KSTEP_MN;
             const uint32_t a_lbo = p.a.k_major ? 16u : static_cast<uint32_t>(BK) * 128u;
@@ -413,7 +450,7 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
             uint32_t stage = 0, phase = 0;
             uint32_t it = 0;
             bool ok = true;
-            for (int t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x, ++it) {
+            for (int t = tile0; ok && t < p.total_tiles; t += tile_step, ++it) {
                 const uint32_t buf = it & 1u;
                 const uint32_t tphase = (it >> 1) & 1u;
                 if (!ptx::mbar_wait_bounded(ptx::smem_u32(&tempty_bar[buf]), tphase ^ 1u, abort_p)) {
@@ -434,7 +471,9 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
                         const uint64_t da = da0 + (st_units + ((ks * a_step) >> 4));
                         const uint64_t db = db0 + (st_units + ((ks * b_step) >> 4));
                         const uint32_t acc = (kb | ks) ? 1u : 0u;
-                        if constexpr (ES == 2) {
+                        if constexpr (PAIR) {
+                            ptx::umma_f16_pair(d_tmem, da, db, idesc, acc);
+                        } else if constexpr (ES == 2) {
                             ptx::umma_f16(d_tmem, da, db, idesc, acc);
                         } else {
                             ptx::umma_tf32(d_tmem, da + lo_units, db, idesc, acc);
@@ -442,13 +481,25 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
                             ptx::umma_tf32(d_tmem, da, db, idesc, 1u);
                         }
                     }
-                    ptx::umma_commit(ptx::smem_u32(&empty_bar[stage]));
+                    if constexpr (PAIR) {  // free the stage in both CTAs
+                        ptx::umma_commit_pair(ptx::smem_u32(&empty_bar[stage]));
+                        ptx::umma_commit_pair(ptx::map_to_cta(ptx::smem_u32(&empty_bar[stage]), 1u));
+                    } else {
+                        ptx::umma_commit(ptx::smem_u32(&empty_bar[stage]));
+                    }
                     if (++stage == static_cast<uint32_t>(S)) {
                         stage = 0;
                         phase ^= 1u;
                     }
                 }
-                if (ok) ptx::umma_commit(ptx::smem_u32(&tfull_bar[buf]));
+                if (ok) {
+                    if constexpr (PAIR) {  // both CTAs' epilogue warps read their half of the tile
+                        ptx::umma_commit_pair(ptx::smem_u32(&tfull_bar[buf]));
+                        ptx::umma_commit_pair(ptx::map_to_cta(ptx::smem_u32(&tfull_bar[buf]), 1u));
+                    } else {
+                        ptx::umma_commit(ptx::smem_u32(&tfull_bar[buf]));
+                    }
+                }
             }
         }
     } else if (USE_TMA && warp == kTmaWarp) {
@@ -456,9 +507,11 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            for (int t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x) {
+            for (int t = tile0; ok && t < p.total_tiles; t += tile_step) {
                 int b, m0, n0;
-                decode_tile(p, t, b, m0, n0);
+                decode_tile(p, t, b, m0, n0, tile_rows);
+                m0 += row_off;
+                n0 += PAIR ? static_cast<int>(rank) * b_rows : 0;  // this CTA's share of the Bu rows
                 const int ba = p.a.batch_stride ? b : 0;
                 const int bb = p.b.batch_stride ? b : 0;
                 for (int kb = 0; kb < num_kb; ++kb) {
@@ -467,21 +520,40 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
                         ok = false;
                         break;
                     }
-                    const uint32_t bar = ptx::smem_u32(&full_bar[stage]);
                     const uint32_t sA = smem0 + stage * stage_bytes;
                     const uint32_t sB = sA + A_TILE;
-                    ptx::mbar_arrive_expect_tx(bar, A_TILE + b_tile);
-                    if (p.a.k_major) {
-                        ptx::tma_load_3d(sA, &tmA, bar, kb * BK, m0, ba);
+                    if constexpr (PAIR) {
+                        // both CTAs' copies are counted on rank 0's barrier, which rank 0 arms
+                        // with the bytes of the two CTAs together
+                        const uint32_t bar = ptx::map_to_cta(ptx::smem_u32(&full_bar[stage]), 0u);
+                        if (rank == 0) ptx::mbar_arrive_expect_tx(ptx::smem_u32(&full_bar[stage]), 2u * (A_TILE + b_tile));
+                        if (p.a.k_major) {
+                            ptx::tma_load_3d_pair(sA, &tmA, bar, kb * BK, m0, ba);
+                        } else {
+                            for (int g = 0; g < kBM / E; ++g)
+                                ptx::tma_load_3d_pair(sA + g * BK * 128, &tmA, bar, m0 + g * E, kb * BK, ba);
+                        }
+                        if (p.b.k_major) {
+                            ptx::tma_load_3d_pair(sB, &tmB, bar, kb * BK, n0, bb);
+                        } else {
+                            for (int g = 0; g < b_rows / E; ++g)
+                                ptx::tma_load_3d_pair(sB + g * BK * 128, &tmB, bar, n0 + g * E, kb * BK, bb);
+                        }
                     } else {
-                        for (int g = 0; g < kBM / E; ++g)
-                            ptx::tma_load_3d(sA + g * BK * 128, &tmA, bar, m0 + g * E, kb * BK, ba);
-                    }
-                    if (p.b.k_major) {
-                        ptx::tma_load_3d(sB, &tmB, bar, kb * BK, n0, bb);
-                    } else {
-                        for (int g = 0; g < BN / E; ++g)
-                            ptx::tma_load_3d(sB + g * BK * 128, &tmB, bar, n0 + g * E, kb * BK, bb);
+                        const uint32_t bar = ptx::smem_u32(&full_bar[stage]);
+                        ptx::mbar_arrive_expect_tx(bar, A_TILE + b_tile);
+                        if (p.a.k_major) {
+                            ptx::tma_load_3d(sA, &tmA, bar, kb * BK, m0, ba);
+                        } else {
+                            for (int g = 0; g < kBM / E; ++g)
+                                ptx::tma_load_3d(sA + g * BK * 128, &tmA, bar, m0 + g * E, kb * BK, ba);
+                        }
+                        if (p.b.k_major) {
+                            ptx::tma_load_3d(sB, &tmB, bar, kb * BK, n0, bb);
+                        } else {
+                            for (int g = 0; g < BN / E; ++g)
+                                ptx::tma_load_3d(sB + g * BK * 128, &tmB, bar, n0 + g * E, kb * BK, bb);
+                        }
                     }
                     if (++stage == static_cast<uint32_t>(S)) {
                         stage = 0;
@@ -607,10 +679,14 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
         if (threadIdx.x == 0) atomicOr(p.status, DEV_STATUS_WAIT_TIMEOUT);
         __syncthreads();
     }
+    if constexpr (PAIR) ptx::cluster_sync();  // the peer may still signal this CTA's barriers until here
     if (warp == kMmaWarp) {
         __syncwarp();
         ptx::tc_fence_after();
-        ptx::tmem_dealloc(tmem_base, tmem_cols);
+        if constexpr (PAIR)
+            ptx::tmem_dealloc_pair(tmem_base, tmem_cols);
+        else
+            ptx::tmem_dealloc(tmem_base, tmem_cols);
     }
 }
 

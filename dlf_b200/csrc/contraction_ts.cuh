@@ -67,6 +67,13 @@ struct TsParams {
     // Filter bank already laid out as the kernel's shared-memory stage images (pack_weights_kernel):
     // [batch][n-tile][k-block][stage_bytes]; null = the loader warps gather from the OIHW tensor
     const unsigned char* b_packed;
+    // fp32 with long K: the accumulator is restarted every kc_blocks k-blocks and the finished
+    // chunks are summed in shared memory at byte offset sums_off of the dynamic segment
+    // (float[BN][128]); 0 = one chunk (see drain_chunk in epilogue.cuh)
+    int kc_blocks, sums_off;
+    // fp32 dense products whose B operand satisfies the TMA rules: one thread of warp 12 streams
+    // the raw fp32 tiles with TMA, warps 13-14 split them in place into the hi and lo images
+    int b_tma;
 };
 
 __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&v)[32]) {
@@ -192,7 +199,7 @@ __global__ void pack_weights_kernel(const TsParams tp, unsigned char* out, long 
 
 template <int ES>
 __global__ void __launch_bounds__(kTsThreads, 1)
-    contraction_ts_kernel(const __grid_constant__ TsParams tp) {
+    contraction_ts_kernel(const __grid_constant__ TsParams tp, const __grid_constant__ CUtensorMap tmB) {
     const Params& p = tp.base;
     constexpr int BK = 128 / ES;             // k per stage: 32 (fp32) or 64 (16-bit)
     constexpr int CPE = 16 / ES;
@@ -205,6 +212,7 @@ __global__ void __launch_bounds__(kTsThreads, 1)
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t full_a[kMaxStages];
     __shared__ __align__(8) uint64_t full_b[kMaxStages];
+    __shared__ __align__(8) uint64_t raw_b[kMaxStages];  // b_tma: raw tile landed
     __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
     __shared__ __align__(8) uint64_t tfull_bar[2];
     __shared__ __align__(8) uint64_t tempty_bar[2];
@@ -228,7 +236,8 @@ __global__ void __launch_bounds__(kTsThreads, 1)
         abort_flag = 0;
         for (int s = 0; s < S; ++s) {
             ptx::mbar_init(ptx::smem_u32(&full_a[s]), 128u);
-            ptx::mbar_init(ptx::smem_u32(&full_b[s]), tp.b_packed ? 1u : kTsLoaderThreads);
+            ptx::mbar_init(ptx::smem_u32(&full_b[s]), tp.b_packed ? 1u : (tp.b_tma ? 64u : kTsLoaderThreads));
+            ptx::mbar_init(ptx::smem_u32(&raw_b[s]), 1u);
             ptx::mbar_init(ptx::smem_u32(&empty_bar[s]), 1u);
         }
         for (int i = 0; i < 2; ++i) {
@@ -285,9 +294,30 @@ __global__ void __launch_bounds__(kTsThreads, 1)
     if (warp < 4) {
         // ------------------------------------------------------------ epilogue
         uint32_t buf = 0, tphase = 0;
-        for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x) {
+        const int kc = tp.kc_blocks > 0 ? tp.kc_blocks : num_kb;
+        float* part_row = reinterpret_cast<float*>(smem_raw + tp.sums_off) + warp * 32 + lane;
+        bool alive = true;
+        for (int t = blockIdx.x; alive && t < p.total_tiles; t += gridDim.x) {
             int b, m0, n0;
             decode_tile(p, t, b, m0, n0);
+            // all K-chunks but the last only feed the running sums
+            for (int kb0 = 0; kb0 + kc < num_kb; kb0 += kc) {
+                const bool wc = ptx::mbar_wait_bounded(ptx::smem_u32(&tfull_bar[buf]), tphase, abort_p);
+                if (!__all_sync(0xffffffffu, wc)) {
+                    alive = false;
+                    break;
+                }
+                ptx::tc_fence_after();
+                drain_chunk(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + buf * BN, BN, part_row, kb0 == 0);
+                ptx::tc_fence_before();
+                ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));
+                if (++buf == static_cast<uint32_t>(nbuf)) {
+                    buf = 0;
+                    tphase ^= 1u;
+                }
+            }
+            if (!alive) break;
+            const float* part = kc < num_kb ? part_row : nullptr;
             const bool w = ptx::mbar_wait_bounded(ptx::smem_u32(&tfull_bar[buf]), tphase, abort_p);
             if (!__all_sync(0xffffffffu, w)) break;
             ptx::tc_fence_after();
@@ -325,6 +355,11 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                         uint32_t d[16];
                         ptx::tmem_ld_32x16(trow + kw * tp.rc_cpt + co0, d);
                         ptx::tmem_ld_wait();
+                        if (part != nullptr) {
+#pragma unroll
+                            for (int e = 0; e < 16; ++e)
+                                d[e] = __float_as_uint(__uint_as_float(d[e]) + part[(kw * tp.rc_cpt + co0 + e) * 128]);
+                        }
                         const int src = lane + kw - tp.rc_lo;
                         const bool in = static_cast<unsigned>(u + kw - tp.rc_lo) < static_cast<unsigned>(p.g.W);
 #pragma unroll
@@ -385,14 +420,14 @@ __global__ void __launch_bounds__(kTsThreads, 1)
             const int ncols = min(BN, p.N - n0);
             if constexpr (ES == 4) {
                 epilogue_dispatch<OUT_F32>(trow, ncols, optr, colstride * ES, row_ok, alpha, beta,
-                                           bias, lane);
+                                           bias, lane, part);
             } else {
                 if (p.fmt == FMT_F16)
                     epilogue_dispatch<OUT_F16>(trow, ncols, optr, colstride * ES, row_ok, alpha,
-                                               beta, bias, lane);
+                                               beta, bias, lane, part);
                 else
                     epilogue_dispatch<OUT_BF16>(trow, ncols, optr, colstride * ES, row_ok, alpha,
-                                                beta, bias, lane);
+                                                beta, bias, lane, part);
             }
             ptx::tc_fence_before();
             ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));
@@ -591,6 +626,73 @@ __global__ void __launch_bounds__(kTsThreads, 1)
         const bool b_atom32 = ES == 4 && !p.b.k_major;
         uint32_t s = 0, ph = 0;
         bool ok = true;
+        if (tp.b_tma) {
+            if (warp == kTsLoaderWarp0) {
+                // TMA producer: raw fp32 tile of Bu into the hi image of the stage
+                if (lane == 0) {
+                    ptx::tma_prefetch_desc(&tmB);
+                    for (int t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x) {
+                        int b, m0, n0;
+                        decode_tile(p, t, b, m0, n0);
+                        const int bb = p.b.batch_stride ? b : 0;
+                        for (int kb = 0; kb < num_kb; ++kb) {
+                            if (!ptx::mbar_wait_bounded(ptx::smem_u32(&empty_bar[s]), ph ^ 1u, abort_p)) {
+                                ok = false;
+                                break;
+                            }
+                            const uint32_t bar = ptx::smem_u32(&raw_b[s]);
+                            const uint32_t sB = smem0 + s * stage_bytes;
+                            ptx::mbar_arrive_expect_tx(bar, b_tile);
+                            if (p.b.k_major) {
+                                ptx::tma_load_3d(sB, &tmB, bar, kb * BK, n0, bb);
+                            } else {
+                                for (int g = 0; g < BN / BK; ++g)
+                                    ptx::tma_load_3d(sB + g * BK * 128, &tmB, bar, n0 + g * BK, kb * BK, bb);
+                            }
+                            if (++s == static_cast<uint32_t>(S)) {
+                                s = 0;
+                                ph ^= 1u;
+                            }
+                        }
+                    }
+                }
+            } else {
+                // converters: split every 16-byte chunk of the raw tile where it lies (the split
+                // is element-wise, so the swizzle does not matter): hi in place, lo beside it
+                const int ct = threadIdx.x - (kTsLoaderWarp0 + 1) * 32;  // 0..63
+                for (int t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x) {
+                    for (int kb = 0; kb < num_kb; ++kb) {
+                        const bool w = ptx::mbar_wait_bounded(ptx::smem_u32(&raw_b[s]), ph, abort_p);
+                        if (!__all_sync(0xffffffffu, w)) {
+                            ok = false;
+                            break;
+                        }
+                        const uint32_t sB = smem0 + s * stage_bytes;
+                        for (uint32_t o = ct * 16u; o < b_tile; o += 64u * 16u) {
+                            uint4 v;
+                            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                                         : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                                         : "r"(sB + o)
+                                         : "memory");
+                            uint4 hi, lo;
+                            split_tf32(v.x, hi.x, lo.x);
+                            split_tf32(v.y, hi.y, lo.y);
+                            split_tf32(v.z, hi.z, lo.z);
+                            split_tf32(v.w, hi.w, lo.w);
+                            st_shared_v4(sB + o, hi);
+                            st_shared_v4(sB + b_tile + o, lo);
+                        }
+                        ptx::fence_proxy_async_smem();
+                        ptx::mbar_arrive(ptx::smem_u32(&full_b[s]));
+                        if (++s == static_cast<uint32_t>(S)) {
+                            s = 0;
+                            ph ^= 1u;
+                        }
+                    }
+                }
+            }
+            ok = false;  // skip the gather loop below
+        }
         if (tp.b_packed != nullptr) {
             // stage images were prepared in global memory: one thread streams them in with bulk
             // copies, the other loader threads have nothing to do
@@ -680,45 +782,49 @@ __global__ void __launch_bounds__(kTsThreads, 1)
             const uint32_t lo_units = b_tile >> 4;
             uint32_t s = 0, ph = 0, buf = 0, tphase = 0;
             bool ok = true;
+            const int kc = tp.kc_blocks > 0 ? tp.kc_blocks : num_kb;
             for (int t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x) {
-                if (!ptx::mbar_wait_bounded(ptx::smem_u32(&tempty_bar[buf]), tphase ^ 1u, abort_p)) {
-                    ok = false;
-                    break;
-                }
-                ptx::tc_fence_after();
-                const uint32_t d_tmem = tmem_base + buf * BN;
-                for (int kb = 0; kb < num_kb; ++kb) {
-                    if (!ptx::mbar_wait_bounded(ptx::smem_u32(&full_a[s]), ph, abort_p) ||
-                        !ptx::mbar_wait_bounded(ptx::smem_u32(&full_b[s]), ph, abort_p)) {
+                for (int kb0 = 0; ok && kb0 < num_kb; kb0 += kc) {  // one accumulator per K-chunk
+                    if (!ptx::mbar_wait_bounded(ptx::smem_u32(&tempty_bar[buf]), tphase ^ 1u, abort_p)) {
                         ok = false;
                         break;
                     }
                     ptx::tc_fence_after();
-                    const uint32_t st_units = (s * stage_bytes) >> 4;
-                    const uint32_t a_slot = tmem_base + a_col0 + s * A_COLS;
+                    const uint32_t d_tmem = tmem_base + buf * BN;
+                    const int kb1 = min(kb0 + kc, num_kb);
+                    for (int kb = kb0; kb < kb1; ++kb) {
+                        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&full_a[s]), ph, abort_p) ||
+                            !ptx::mbar_wait_bounded(ptx::smem_u32(&full_b[s]), ph, abort_p)) {
+                            ok = false;
+                            break;
+                        }
+                        ptx::tc_fence_after();
+                        const uint32_t st_units = (s * stage_bytes) >> 4;
+                        const uint32_t a_slot = tmem_base + a_col0 + s * A_COLS;
 #pragma unroll
-                    for (int ks = 0; ks < BK / UMMA_K; ++ks) {
-                        const uint64_t db = db0 + (st_units + ((ks * b_step) >> 4));
-                        const uint32_t acc = (kb | ks) ? 1u : 0u;
-                        const uint32_t a_hi = a_slot + ks * A_KSTEP_COLS;
-                        if constexpr (ES == 2) {
-                            umma_ts_f16(d_tmem, a_hi, db, idesc, acc);
-                        } else {
-                            umma_ts_tf32(d_tmem, a_hi + 32, db, idesc, acc);
-                            umma_ts_tf32(d_tmem, a_hi, db + lo_units, idesc, 1u);
-                            umma_ts_tf32(d_tmem, a_hi, db, idesc, 1u);
+                        for (int ks = 0; ks < BK / UMMA_K; ++ks) {
+                            const uint64_t db = db0 + (st_units + ((ks * b_step) >> 4));
+                            const uint32_t acc = ((kb - kb0) | ks) ? 1u : 0u;
+                            const uint32_t a_hi = a_slot + ks * A_KSTEP_COLS;
+                            if constexpr (ES == 2) {
+                                umma_ts_f16(d_tmem, a_hi, db, idesc, acc);
+                            } else {
+                                umma_ts_tf32(d_tmem, a_hi + 32, db, idesc, acc);
+                                umma_ts_tf32(d_tmem, a_hi, db + lo_units, idesc, 1u);
+                                umma_ts_tf32(d_tmem, a_hi, db, idesc, 1u);
+                            }
+                        }
+                        ptx::umma_commit(ptx::smem_u32(&empty_bar[s]));
+                        if (++s == static_cast<uint32_t>(S)) {
+                            s = 0;
+                            ph ^= 1u;
                         }
                     }
-                    ptx::umma_commit(ptx::smem_u32(&empty_bar[s]));
-                    if (++s == static_cast<uint32_t>(S)) {
-                        s = 0;
-                        ph ^= 1u;
+                    if (ok) ptx::umma_commit(ptx::smem_u32(&tfull_bar[buf]));
+                    if (++buf == static_cast<uint32_t>(nbuf)) {
+                        buf = 0;
+                        tphase ^= 1u;
                     }
-                }
-                if (ok) ptx::umma_commit(ptx::smem_u32(&tfull_bar[buf]));
-                if (++buf == static_cast<uint32_t>(nbuf)) {
-                    buf = 0;
-                    tphase ^= 1u;
                 }
             }
         }

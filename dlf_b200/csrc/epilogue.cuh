@@ -83,15 +83,23 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&v)[32], char* pt
 
 // All columns of one accumulator tile held in TMEM at `trow` (lane base and column base already
 // applied). ncols_total = number of valid columns of this tile (<= BN).
+// `part` (optional): this thread's row of fp32 partial sums of earlier K-chunks in shared memory,
+// element of column j at part[j*128]; added to the accumulator before alpha is applied.
 template <int OUT, bool HAS_BETA, bool HAS_BIAS>
 __device__ __forceinline__ void epilogue_tile(uint32_t trow, int ncols_total, char* ptr,
                                               long long stride, bool row_ok, float alpha,
-                                              float beta, const char* bias, int lane) {
+                                              float beta, const char* bias, int lane,
+                                              const float* part = nullptr) {
     constexpr int OES = OUT == OUT_F32 ? 4 : 2;
     for (int c0 = 0; c0 < ncols_total; c0 += 32) {
         uint32_t v[32];
         ptx::tmem_ld_32x32(trow + c0, v);
         ptx::tmem_ld_wait();
+        if (part != nullptr) {
+#pragma unroll
+            for (int jj = 0; jj < 32; ++jj)
+                v[jj] = __float_as_uint(__uint_as_float(v[jj]) + part[(c0 + jj) * 128]);
+        }
         const int nc = min(32, ncols_total - c0);
         epilogue_chunk<OUT, HAS_BETA, HAS_BIAS>(v, ptr + c0 * stride, stride, nc, row_ok, alpha,
                                                 beta, HAS_BIAS ? bias + c0 * OES : nullptr, lane);
@@ -101,17 +109,37 @@ __device__ __forceinline__ void epilogue_tile(uint32_t trow, int ncols_total, ch
 template <int OUT>
 __device__ __forceinline__ void epilogue_dispatch(uint32_t trow, int ncols_total, char* ptr,
                                                   long long stride, bool row_ok, float alpha,
-                                                  float beta, const char* bias, int lane) {
+                                                  float beta, const char* bias, int lane,
+                                                  const float* part = nullptr) {
     if (beta != 0.0f) {
         if (bias)
-            epilogue_tile<OUT, true, true>(trow, ncols_total, ptr, stride, row_ok, alpha, beta, bias, lane);
+            epilogue_tile<OUT, true, true>(trow, ncols_total, ptr, stride, row_ok, alpha, beta, bias, lane, part);
         else
-            epilogue_tile<OUT, true, false>(trow, ncols_total, ptr, stride, row_ok, alpha, beta, bias, lane);
+            epilogue_tile<OUT, true, false>(trow, ncols_total, ptr, stride, row_ok, alpha, beta, bias, lane, part);
     } else {
         if (bias)
-            epilogue_tile<OUT, false, true>(trow, ncols_total, ptr, stride, row_ok, alpha, beta, bias, lane);
+            epilogue_tile<OUT, false, true>(trow, ncols_total, ptr, stride, row_ok, alpha, beta, bias, lane, part);
         else
-            epilogue_tile<OUT, false, false>(trow, ncols_total, ptr, stride, row_ok, alpha, beta, bias, lane);
+            epilogue_tile<OUT, false, false>(trow, ncols_total, ptr, stride, row_ok, alpha, beta, bias, lane, part);
+    }
+}
+
+// Adds (or, for the first chunk, stores) one finished K-chunk accumulator to the running fp32
+// sums in shared memory. The tensor core truncates when it adds into its fp32 accumulator, a
+// bias that grows linearly with the number of accumulation steps (about 6e-9 * K relative for
+// 3xTF32); summing short chunks with round-to-nearest adds on the CUDA cores keeps it bounded.
+__device__ __forceinline__ void drain_chunk(uint32_t trow, int ncols, float* part, bool first) {
+    for (int c0 = 0; c0 < ncols; c0 += 32) {
+        uint32_t v[32];
+        ptx::tmem_ld_32x32(trow + c0, v);
+        ptx::tmem_ld_wait();
+        if (first) {
+#pragma unroll
+            for (int jj = 0; jj < 32; ++jj) part[(c0 + jj) * 128] = __uint_as_float(v[jj]);
+        } else {
+#pragma unroll
+            for (int jj = 0; jj < 32; ++jj) part[(c0 + jj) * 128] += __uint_as_float(v[jj]);
+        }
     }
 }
 

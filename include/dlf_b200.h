@@ -125,7 +125,10 @@ int dlf_b200_device_status(int* device_status);
  * width (64, 128 or 256; 0 = automatic) and the operand path: 0 = automatic, 1 = never the TMA
  * producer, 2 = always the loader-warp kernel with both operands in shared memory, 3 = the
  * kernel that keeps operand A in tensor memory whenever the TMA producer is not used, 4 = as 0
- * but convolutions never use the row form (horizontal taps as GEMM columns). */
+ * but convolutions never use the row form (horizontal taps as GEMM columns). Higher bits switch
+ * single features for measurements: 0x200 use CTA pairs (cta_group::2) for 256-column fp16 tiles,
+ * 0x800 no TMA for the fp32 B operand, 0x1000 no K-chunked fp32 accumulation, 0x4000 no TMA
+ * stores, 0x8000 never pack the filter bank of a convolution. */
 void dlf_b200_set_tuning(int force_bn, int force_generic_loader);
 
 /* Counts kernel launches made by this library in this process (all threads). */

@@ -237,6 +237,26 @@ def test_gemm_every_tile_width(lib, bn):
         lib.set_tuning(0, False)
 
 
+@pytest.mark.parametrize("m,n,k", [(512, 512, 264), (300, 520, 200), (1000, 264, 72)])
+def test_gemm_cta_pair_kernel(lib, m, n, k):
+    """The cta_group::2 variant (two CTAs share 256 x 256 tiles; opt-in, tuning bit 0x200) on all
+    four transpose combinations, with a ragged M whose second half-tile is partly or wholly
+    outside the matrix; the result must equal the single-CTA kernel's bit for bit."""
+    gb = _gb()
+    for ta, tb in itertools.product((gb.Transpose.NoTrans, gb.Transpose.Trans), repeat=2):
+        outs = []
+        for flag in (0, 0x200):
+            lib.set_tuning(256, flag)
+            try:
+                got, ref = _gemm_case(np.random.default_rng(m + n), torch.float16, gb.Layout.RowMajor,
+                                      ta, tb, m, n, k, 1.0, 0.0, (0, 0, 0), (0, 0, 0))
+            finally:
+                lib.set_tuning(0, 0)
+            assert max_rel(got, ref) <= HALF_TOL
+            outs.append(got)
+        assert np.array_equal(outs[0], outs[1])
+
+
 def test_beta_zero_never_reads_c():
     """beta == 0 must overwrite C without reading it (xgemm_part2.cl:87-126): NaNs in C vanish."""
     gb = _gb()
@@ -247,6 +267,19 @@ def test_beta_zero_never_reads_c():
                               nan_c=True)
         assert not np.isnan(got).any()
         assert metric(got, ref) <= tol
+
+
+@pytest.mark.parametrize("k", [1056, 4096])
+def test_gemm_fp32_long_k_stays_accurate(k):
+    """The tensor core truncates when it adds into its fp32 accumulator; without countermeasure the
+    3xTF32 result drifts by about 6e-9*K (1e-4 at K = 16384). Long K is therefore accumulated in
+    chunks that are summed with ordinary fp32 adds: the error must stay well inside 1e-5."""
+    gb = _gb()
+    rng = np.random.default_rng(k)
+    for (layout, ta, tb, m, n) in ((gb.Layout.RowMajor, gb.Transpose.Trans, gb.Transpose.NoTrans, 200, 136),
+                                   (gb.Layout.ColMajor, gb.Transpose.NoTrans, gb.Transpose.Trans, 130, 300)):
+        got, ref = _gemm_case(rng, torch.float32, layout, ta, tb, m, n, k, 0.5, 0.5, (0, 0, 0), (0, 0, 0))
+        assert rel_fro(got, ref) <= 4e-6
 
 
 def test_gemm_config1_sgemm_1024():
@@ -365,6 +398,8 @@ CONV_CASES = [
     (2, 6, 6, 70, 150, 2, 7, (0, 3, 1, 3), (1, 1), (1, 1), 1),      # row form: 7 taps per row, several channel tiles
     (2, 12, 8, 8, 24, 3, 3, (1, 1, 1, 1), (1, 1), (1, 1), 3),       # row form with groups
     (1, 4, 5, 40, 8, 1, 4, (0, 0, 0, 0), (1, 1), (1, 1), 1),        # row form, no padding: OW < W
+    (1, 192, 9, 12, 40, 3, 3, (1, 1, 1, 1), (1, 1), (1, 1), 1),     # row form, K' = 576: chunked accumulation in fp32
+    (1, 72, 9, 12, 24, 3, 3, (1, 1, 1, 1), (2, 2), (1, 1), 1),      # im2col form, K = 648: chunked accumulation in fp32
 ]
 
 
