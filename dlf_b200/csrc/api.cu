@@ -375,10 +375,6 @@ int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
     tp.ktable_bytes = ktable_bytes;
 
     tp.b_packed = nullptr;
-    {
-        const int raw = (g_force_generic.load() >> 13) & 1;  // experiment: see g_split_raw
-        cudaMemcpyToSymbolAsync(g_split_raw, &raw, sizeof(int), 0, cudaMemcpyHostToDevice, stream);
-    }
     if (q.pack_ws != nullptr && (q.a.im2col || q.rc_kw) && p.b.k_major && !(g_force_generic.load() & 0x8000)) {
         // lay the filter bank out as stage images first (same stream), then stream them with bulk copies
         unsigned char* ws = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(q.pack_ws) + 127) & ~uintptr_t(127));

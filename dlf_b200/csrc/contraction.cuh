@@ -195,16 +195,8 @@ __device__ __forceinline__ uint4 load_chunk_im2col(const Params& p, const PixelE
     return v;
 }
 
-// Experiment switch (set from Params::ablate bit 5 by the kernels): hi = the raw fp32 word (the
-// tensor core is expected to ignore its low 13 bits), lo = x - trunc(x) left unrounded.
-__device__ int g_split_raw = 0;
 // x = hi + lo with hi, lo both exactly representable in tf32 (10 explicit mantissa bits).
 __device__ __forceinline__ void split_tf32(uint32_t x, uint32_t& hi, uint32_t& lo) {
-    if (g_split_raw) {
-        hi = x;
-        lo = __float_as_uint(__uint_as_float(x) - __uint_as_float(x & 0xffffe000u));
-        return;
-    }
     const float xf = __uint_as_float(x);
     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(xf));
     const float rest = xf - __uint_as_float(hi);

@@ -71,8 +71,8 @@ struct TsParams {
     // chunks are summed in shared memory at byte offset sums_off of the dynamic segment
     // (float[BN][128]); 0 = one chunk (see drain_chunk in epilogue.cuh)
     int kc_blocks, sums_off;
-    // fp32 dense products whose B operand satisfies the TMA rules: one thread of warp 12 streams
-    // the raw fp32 tiles with TMA, warps 13-14 split them in place into the hi and lo images
+    // fp32 dense products whose B operand satisfies the TMA rules: TMA delivers the raw fp32 tiles
+    // (which double as the hi image), the loader warps derive the lo image from them
     int b_tma;
 };
 
@@ -657,8 +657,10 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                     }
                 }
             } else {
-                // converters: split every 16-byte chunk of the raw tile where it lies (the split
-                // is element-wise, so the swizzle does not matter): hi in place, lo beside it
+                // Converters (warps 13-14). The tensor core reads a raw fp32 word as its tf32
+                // truncation, so the tile TMA delivered already is the hi image; only
+                // lo = x - trunc(x) is written, chunk by chunk where the data lies (the operation
+                // is element-wise, so the swizzle does not matter).
                 const int ct = threadIdx.x - (kTsLoaderWarp0 + 1) * 32;  // 0..63
                 for (int t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x) {
                     for (int kb = 0; kb < num_kb; ++kb) {
@@ -674,12 +676,11 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                                          : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                                          : "r"(sB + o)
                                          : "memory");
-                            uint4 hi, lo;
-                            split_tf32(v.x, hi.x, lo.x);
-                            split_tf32(v.y, hi.y, lo.y);
-                            split_tf32(v.z, hi.z, lo.z);
-                            split_tf32(v.w, hi.w, lo.w);
-                            st_shared_v4(sB + o, hi);
+                            uint4 lo;
+                            lo.x = __float_as_uint(__uint_as_float(v.x) - __uint_as_float(v.x & 0xffffe000u));
+                            lo.y = __float_as_uint(__uint_as_float(v.y) - __uint_as_float(v.y & 0xffffe000u));
+                            lo.z = __float_as_uint(__uint_as_float(v.z) - __uint_as_float(v.z & 0xffffe000u));
+                            lo.w = __float_as_uint(__uint_as_float(v.w) - __uint_as_float(v.w & 0xffffe000u));
                             st_shared_v4(sB + b_tile + o, lo);
                         }
                         ptx::fence_proxy_async_smem();

@@ -44,6 +44,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
+// Non-blocking test of a phase (no suspension): for threads that poll two things at once.
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
 // Bounded wait. Returns false when the wait gave up: either another role of this CTA
 // raised *abort_flag, or ~2^32 SM clocks passed (about two seconds), in which case this
 // thread raises the flag itself. Callers leave their role loop on false.
