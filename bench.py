@@ -496,8 +496,9 @@ def main():
                 "frac_of_nominal": tf_per_gpu / NOMINAL[w.dtype],
                 "hbm_gbs_algorithmic": w.bytes / sec_per_step / 1e9,
                 "hbm_frac_of_measured": w.bytes / sec_per_step / 1e9 / peaks["hbm_gbs"],
-                "kernel": "contraction_ts_kernel (row-form implicit GEMM); the step also launches "
-                          "pack_weights_kernel once, its time is inside the measured step",
+                "kernel": ("contraction_ts_kernel (row-form implicit GEMM); the step also launches "
+                           "pack_weights_kernel once, its time is inside the measured step") if isinstance(w, ConvC2)
+                          else ("contraction_ts_kernel" if w.dtype == "f32" else "contraction_kernel<2,true>"),
                 "avg_launch_us": sec_per_step * 1e6}
     prof = os.path.join(ROOT, "profiles", "traffic.json")
     if os.path.exists(prof):

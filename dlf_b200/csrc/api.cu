@@ -363,8 +363,11 @@ int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
     p.bias_stride = q.bias_stride;
     p.g = q.g;
     p.status = st.status;
-    p.ablate = g_force_generic.load() >> 8;
+    p.ablate = g_force_generic.load() >> 16;
     tp.a_kind = q.rc_kw ? A_ROWCONV : (q.a.im2col ? A_IM2COL : (q.a.k_major ? A_DENSE_K : A_DENSE_MN));
+    tp.a_pointwise = tp.a_kind == A_IM2COL && q.g.KH == 1 && q.g.KW == 1 && q.g.pad_t == 0 && q.g.pad_l == 0 &&
+                     (q.g.OH - 1) * q.g.sh < q.g.H && (q.g.OW - 1) * q.g.sw < q.g.W &&
+                     !(g_force_generic.load() & 0x2000);
     tp.rc_kw = q.rc_kw;
     tp.rc_cpt = q.rc_cpt;
     tp.rc_T = q.rc_T;

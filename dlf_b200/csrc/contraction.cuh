@@ -97,8 +97,10 @@ struct Params {
     int* status;
     int d_tma;   // 16-bit outputs with beta == 0 and TMA-compatible strides: the epilogue stages
                  // 32 x 32 blocks in shared memory and writes them with TMA stores
-    int ablate;  // measurement aid: bit 0 A producer skips its loads, bit 1 B loaders skip theirs,
-                 // bit 2 producers skip the TMEM stores (results are then meaningless)
+    int ablate;  // measurement aid (tuning flags >> 16; results are then meaningless):
+                 // 1 A producer skips its loads, 2 B loaders skip theirs, 4 producers skip the TMEM
+                 // stores, 8 / 16 row-form epilogue skips its body / its stores, 32 the plain
+                 // epilogue of the TMEM-operand kernel is skipped
 };
 
 struct PixelEntry {  // one output pixel of the current tile (implicit im2col operand)
@@ -402,12 +404,13 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
                 epilogue_dispatch<OUT_F32>(trow, ncols, optr, colstride * ES, row_ok, alpha, beta,
                                            bias, lane);
             } else {
+                const bool pair_ok = pair_store_ok(optr, rowbase, colstride, row_ok, lane);
                 if (p.fmt == FMT_F16)
                     epilogue_dispatch<OUT_F16>(trow, ncols, optr, colstride * ES, row_ok, alpha,
-                                               beta, bias, lane);
+                                               beta, bias, lane, nullptr, pair_ok);
                 else
                     epilogue_dispatch<OUT_BF16>(trow, ncols, optr, colstride * ES, row_ok, alpha,
-                                                beta, bias, lane);
+                                                beta, bias, lane, nullptr, pair_ok);
             }
             ptx::tc_fence_before();
             if constexpr (PAIR) {

@@ -74,6 +74,8 @@ struct TsParams {
     // fp32 dense products whose B operand satisfies the TMA rules: TMA delivers the raw fp32 tiles
     // (which double as the hi image), the loader warps derive the lo image from them
     int b_tma;
+    // A_IM2COL with a 1x1 filter and no padding (any stride): addresses are affine in k
+    int a_pointwise;
 };
 
 __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&v)[32]) {
@@ -418,16 +420,18 @@ __global__ void __launch_bounds__(kTsThreads, 1)
             const uint32_t trow = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + buf * BN;
             char* optr = p.d + (rowbase + static_cast<long long>(n0) * colstride) * ES;
             const int ncols = min(BN, p.N - n0);
-            if constexpr (ES == 4) {
+            if (p.ablate & 32) {
+            } else if constexpr (ES == 4) {
                 epilogue_dispatch<OUT_F32>(trow, ncols, optr, colstride * ES, row_ok, alpha, beta,
                                            bias, lane, part);
             } else {
+                const bool pair_ok = pair_store_ok(optr, rowbase, colstride, row_ok, lane);
                 if (p.fmt == FMT_F16)
                     epilogue_dispatch<OUT_F16>(trow, ncols, optr, colstride * ES, row_ok, alpha,
-                                               beta, bias, lane, part);
+                                               beta, bias, lane, part, pair_ok);
                 else
                     epilogue_dispatch<OUT_BF16>(trow, ncols, optr, colstride * ES, row_ok, alpha,
-                                                beta, bias, lane, part);
+                                                beta, bias, lane, part, pair_ok);
             }
             ptx::tc_fence_before();
             ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));
@@ -511,6 +515,33 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                             const uint32_t lo = in ? x[(2 * j) * hw] : 0u;
                             const uint32_t hi = in ? x[(2 * j + 1) * hw] : 0u;
                             v[j] = lo | (hi << 16);
+                        }
+                    }
+                } else if (tp.a_kind == A_IM2COL && tp.a_pointwise) {
+                    // 1x1 filter without padding: k is the channel, every tap lies inside the
+                    // image, consecutive k are H*W elements apart (no table, no bounds tests)
+                    const long long hw = static_cast<long long>(p.g.H) * p.g.W;
+                    if constexpr (ES == 4) {
+                        const uint32_t* x = reinterpret_cast<const uint32_t*>(p.a.base) + pbase + k0 * hw;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = (row_ok && j < kcount) ? x[j * hw] : 0u;
+                    } else {
+                        const unsigned short* x =
+                            reinterpret_cast<const unsigned short*>(p.a.base) + pbase + k0 * hw;
+                        if (row_ok && kcount == BK) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                const uint32_t lo = x[(2 * j) * hw];
+                                const uint32_t hi = x[(2 * j + 1) * hw];
+                                v[j] = lo | (hi << 16);
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                const uint32_t lo = (row_ok && 2 * j < kcount) ? x[(2 * j) * hw] : 0u;
+                                const uint32_t hi = (row_ok && 2 * j + 1 < kcount) ? x[(2 * j + 1) * hw] : 0u;
+                                v[j] = lo | (hi << 16);
+                            }
                         }
                     }
                 } else if (tp.a_kind == A_IM2COL || tp.a_kind == A_ROWCONV) {

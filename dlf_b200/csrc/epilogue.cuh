@@ -40,14 +40,47 @@ __device__ __forceinline__ float out_load(const char* ptr) {
 // One 32-column chunk. `ptr` addresses D(i, j0) for this lane's row i; consecutive columns are
 // `stride` bytes apart. `ncols` (1..32) columns of the chunk exist; `row_ok` says whether this
 // lane's row exists. `bias` addresses bias[j0] (storage type) and is only read when HAS_BIAS.
+// `pair_ok` (16-bit outputs, beta == 0): this lane and its neighbour (lane ^ 1) hold rows that are
+// adjacent in memory, both exist, and the even lane's element is 4-byte aligned in every column.
+// Then the two lanes trade one value per column pair and each writes one 32-bit word (two rows of
+// one column) instead of two 16-bit values: half the store instructions, 128 bytes per warp store.
 template <int OUT, bool HAS_BETA, bool HAS_BIAS>
 __device__ __forceinline__ void epilogue_chunk(const uint32_t (&v)[32], char* ptr, long long stride,
                                                int ncols, bool row_ok, float alpha, float beta,
-                                               const char* bias, int lane) {
+                                               const char* bias, int lane, bool pair_ok = false) {
     constexpr int OES = OUT == OUT_F32 ? 4 : 2;
     float bv = 0.0f;
     if constexpr (HAS_BIAS) {
         if (lane < ncols) bv = out_load<OUT>(bias + lane * OES);
+    }
+    if constexpr (OUT != OUT_F32 && !HAS_BETA) {
+        if (ncols == 32 && __all_sync(0xffffffffu, pair_ok || !row_ok)) {
+            const bool odd = lane & 1;
+#pragma unroll
+            for (int jj = 0; jj < 32; jj += 2) {
+                float r0 = alpha * __uint_as_float(v[jj]);
+                float r1 = alpha * __uint_as_float(v[jj + 1]);
+                if constexpr (HAS_BIAS) {
+                    r0 += __shfl_sync(0xffffffffu, bv, jj);
+                    r1 += __shfl_sync(0xffffffffu, bv, jj + 1);
+                }
+                const float got = __shfl_xor_sync(0xffffffffu, odd ? r0 : r1, 1);
+                // even lane: rows (i, i+1) of column jj; odd lane: rows (i-1, i) of column jj+1
+                const float lo = odd ? got : r0;
+                const float hi = odd ? r1 : got;
+                uint32_t word;
+                if constexpr (OUT == OUT_F16) {
+                    const __half2 h = __floats2half2_rn(lo, hi);
+                    word = *reinterpret_cast<const uint32_t*>(&h);
+                } else {
+                    const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+                    word = *reinterpret_cast<const uint32_t*>(&h);
+                }
+                char* dst = odd ? ptr - 2 + (jj + 1) * stride : ptr + jj * stride;
+                if (row_ok) *reinterpret_cast<uint32_t*>(dst) = word;
+            }
+            return;
+        }
     }
     if (ncols == 32) {
         float c[HAS_BETA ? 32 : 1];
@@ -81,6 +114,18 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&v)[32], char* pt
     }
 }
 
+// Whether this lane and lane ^ 1 can share 32-bit stores (see epilogue_chunk): rows adjacent in
+// memory, both present, column stride even and the even lane's first element 4-byte aligned.
+__device__ __forceinline__ bool pair_store_ok(const char* ptr, long long rowbase, long long colstride,
+                                              bool row_ok, int lane) {
+    const long long other = __shfl_xor_sync(0xffffffffu, rowbase, 1);
+    const bool other_ok = __shfl_xor_sync(0xffffffffu, row_ok ? 1 : 0, 1) != 0;
+    const bool odd = lane & 1;
+    const bool adjacent = odd ? (other == rowbase - 1) : (other == rowbase + 1);
+    const uintptr_t even_addr = reinterpret_cast<uintptr_t>(ptr) - (odd ? 2 : 0);
+    return row_ok && other_ok && adjacent && (colstride & 1) == 0 && (even_addr & 3u) == 0;
+}
+
 // All columns of one accumulator tile held in TMEM at `trow` (lane base and column base already
 // applied). ncols_total = number of valid columns of this tile (<= BN).
 // `part` (optional): this thread's row of fp32 partial sums of earlier K-chunks in shared memory,
@@ -89,7 +134,7 @@ template <int OUT, bool HAS_BETA, bool HAS_BIAS>
 __device__ __forceinline__ void epilogue_tile(uint32_t trow, int ncols_total, char* ptr,
                                               long long stride, bool row_ok, float alpha,
                                               float beta, const char* bias, int lane,
-                                              const float* part = nullptr) {
+                                              const float* part = nullptr, bool pair_ok = false) {
     constexpr int OES = OUT == OUT_F32 ? 4 : 2;
     for (int c0 = 0; c0 < ncols_total; c0 += 32) {
         uint32_t v[32];
@@ -102,7 +147,7 @@ __device__ __forceinline__ void epilogue_tile(uint32_t trow, int ncols_total, ch
         }
         const int nc = min(32, ncols_total - c0);
         epilogue_chunk<OUT, HAS_BETA, HAS_BIAS>(v, ptr + c0 * stride, stride, nc, row_ok, alpha,
-                                                beta, HAS_BIAS ? bias + c0 * OES : nullptr, lane);
+                                                beta, HAS_BIAS ? bias + c0 * OES : nullptr, lane, pair_ok);
     }
 }
 
@@ -110,17 +155,17 @@ template <int OUT>
 __device__ __forceinline__ void epilogue_dispatch(uint32_t trow, int ncols_total, char* ptr,
                                                   long long stride, bool row_ok, float alpha,
                                                   float beta, const char* bias, int lane,
-                                                  const float* part = nullptr) {
+                                                  const float* part = nullptr, bool pair_ok = false) {
     if (beta != 0.0f) {
         if (bias)
-            epilogue_tile<OUT, true, true>(trow, ncols_total, ptr, stride, row_ok, alpha, beta, bias, lane, part);
+            epilogue_tile<OUT, true, true>(trow, ncols_total, ptr, stride, row_ok, alpha, beta, bias, lane, part, pair_ok);
         else
-            epilogue_tile<OUT, true, false>(trow, ncols_total, ptr, stride, row_ok, alpha, beta, bias, lane, part);
+            epilogue_tile<OUT, true, false>(trow, ncols_total, ptr, stride, row_ok, alpha, beta, bias, lane, part, pair_ok);
     } else {
         if (bias)
-            epilogue_tile<OUT, false, true>(trow, ncols_total, ptr, stride, row_ok, alpha, beta, bias, lane, part);
+            epilogue_tile<OUT, false, true>(trow, ncols_total, ptr, stride, row_ok, alpha, beta, bias, lane, part, pair_ok);
         else
-            epilogue_tile<OUT, false, false>(trow, ncols_total, ptr, stride, row_ok, alpha, beta, bias, lane, part);
+            epilogue_tile<OUT, false, false>(trow, ncols_total, ptr, stride, row_ok, alpha, beta, bias, lane, part, pair_ok);
     }
 }
 

@@ -400,6 +400,9 @@ CONV_CASES = [
     (1, 4, 5, 40, 8, 1, 4, (0, 0, 0, 0), (1, 1), (1, 1), 1),        # row form, no padding: OW < W
     (1, 192, 9, 12, 40, 3, 3, (1, 1, 1, 1), (1, 1), (1, 1), 1),     # row form, K' = 576: chunked accumulation in fp32
     (1, 72, 9, 12, 24, 3, 3, (1, 1, 1, 1), (2, 2), (1, 1), 1),      # im2col form, K = 648: chunked accumulation in fp32
+    (3, 70, 7, 7, 36, 1, 1, (0, 0, 0, 0), (1, 1), (1, 1), 1),       # 1x1, odd plane (49 pixels), K tail: affine addressing
+    (2, 40, 9, 9, 24, 1, 1, (0, 0, 1, 1), (2, 2), (1, 1), 2),       # 1x1 stride 2, trailing padding reaches outside: table lookup
+    (2, 24, 14, 14, 72, 1, 1, (0, 0, 0, 0), (1, 1), (1, 1), 1),     # 1x1, even plane (196): paired 32-bit stores for 16-bit outputs
 ]
 
 
@@ -425,6 +428,29 @@ def test_conv2d_random_parity(case, dtype):
         assert rel_fro(got, ref) <= FP32_TOL
     else:
         assert max_rel(got, ref) <= HALF_TOL
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_conv2d_pointwise_table_lookup_matches_affine(lib, dtype):
+    """1x1 filters without padding address the image affinely in k; the table lookup used for
+    every other filter must give the same bits."""
+    from dlf_b200 import gdnn
+    for case in (CONV_CASES[2], CONV_CASES[5], CONV_CASES[15]):
+        N, C, H, W, Co, KH, KW, pads, strides, dil, group = case
+        rng = np.random.default_rng(11)
+        X = torch.from_numpy(rng.normal(size=(N, C, H, W)).astype(np.float32)).to(dtype).cuda()
+        Wt = torch.from_numpy((0.1 * rng.normal(size=(Co, C // group, KH, KW))).astype(np.float32)).to(dtype).cuda()
+        filt = gdnn.Filter2D(X.shape, Wt.shape, group).pads(*pads).strides(*strides).dilations(*dil)
+        outs = []
+        for flags in (0, 0x2000):
+            lib.set_tuning(0, flags)
+            try:
+                Y = torch.full(filt.output_shape(), float("nan"), dtype=dtype, device="cuda")
+                gdnn.conv2d_filter(X, Wt, Y, filt)
+                outs.append(Y.cpu())
+            finally:
+                lib.set_tuning(0, 0)
+        assert torch.equal(outs[0], outs[1]), case
 
 
 @pytest.mark.parametrize("path", [2, 4, 0x8000, 0x8004])
