@@ -288,6 +288,39 @@ int choose_bn(long long M, long long N, long long batch, int num_sms, bool a_in_
     return best;
 }
 
+// Tile width for the kernel that keeps operand A in tensor memory. Per tile the main loop costs
+// num_kb x max(tensor-core issue time, time the producer warps need for one k-block) and the
+// epilogue about 30 clocks per column; the two overlap only with two accumulators in tensor
+// memory, which 512 columns allow up to 192 (fp16) or 192 (fp32, two A slots) columns per tile.
+// Constants are measurements on B200: issue clocks per UMMA 114 (N <= 128), 126 (192), 138 (256);
+// a gathered 16-bit k-block (64 two-byte loads per thread) takes the producers about 2600 clocks.
+int choose_bn_ts(const Problem& q, int num_sms, int max_bn, int a_cols, long long num_kb) {
+    const long long tiles_m = (q.M + kBM - 1) / kBM;
+    const bool gathered = q.es == 2 && (q.a.im2col || !q.a.k_major);
+    const double mmas = q.es == 4 ? 12.0 : 4.0;  // per k-block
+    int best = 64;
+    double best_cost = 0;
+    for (int w : {64, 128, 192, 256}) {
+        if (w > max_bn) break;
+        const long long tiles = q.batch * tiles_m * ((q.N + w - 1) / w);
+        const double waves = static_cast<double>((tiles + num_sms - 1) / num_sms);
+        const double clk = w <= 128 ? 114.0 : (w == 192 ? 126.0 : 138.0);
+        double kb_clk = mmas * clk;
+        if (gathered && kb_clk < 2600.0) kb_clk = 2600.0;
+        const double main_clk = static_cast<double>(num_kb) * kb_clk;
+        const double epi_clk = 30.0 * w;
+        const bool dual = (512 - 2 * w) / a_cols >= 2;
+        const double tile_clk = dual ? (main_clk > epi_clk ? main_clk : epi_clk) : main_clk + epi_clk + 600.0;
+        const double cost = waves * tile_clk;
+        if (w == 64 || cost < best_cost) {
+            best = w;
+            best_cost = cost;
+        }
+        if (q.N <= w) break;
+    }
+    return best;
+}
+
 int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
     const int a_cols = q.es == 4 ? 64 : 32;
     const int BK = 128 / q.es;
@@ -297,9 +330,9 @@ int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
     // float[BN][128] sum array limits such tiles to 128 columns.
     const long long num_kb_all = (q.K + BK - 1) / BK;
     const int kc_blocks = (q.es == 4 && num_kb_all > 16 && !(g_force_generic.load() & 0x1000)) ? 8 : 0;
-    int bn = choose_bn(q.M, q.N, q.batch, st.num_sms, true, kc_blocks ? 128 : 256);
+    int bn = choose_bn_ts(q, st.num_sms, kc_blocks ? 128 : 256, a_cols, num_kb_all);
     const int forced = g_force_bn.load();
-    if (forced == 64 || forced == 128 || (forced == 256 && !kc_blocks)) bn = forced;
+    if (forced >= 64 && forced <= (kc_blocks ? 128 : 256) && forced % 32 == 0) bn = forced;
     long long tiles_n = (q.N + bn - 1) / bn;
     if (q.rc_kw) {  // tile = 4 warps x rc_T output positions by rc_cpt channels (x rc_kw columns)
         bn = q.rc_cpt * q.rc_kw;
@@ -310,8 +343,10 @@ int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
     if (total >= INT_MAX) return kInvalidDimension;
 
     // two accumulator buffers (epilogue overlaps the next main loop) unless that would leave
-    // fewer than three A slots in tensor memory
-    const int acc_bufs = ((512 - 2 * bn) / a_cols >= 3) ? 2 : 1;
+    // fewer than two A slots in tensor memory. Two slots are enough: each producer warp holds one
+    // more k-block in registers while it waits for its slot. (0x400: demand three slots.)
+    const int min_slots = (g_force_generic.load() & 0x400) ? 3 : 2;
+    const int acc_bufs = ((512 - 2 * bn) / a_cols >= min_slots) ? 2 : 1;
     const long long num_kb = (q.K + BK - 1) / BK;
     int ktable_bytes = 0;
     if (q.a.im2col || q.rc_kw) {
@@ -826,7 +861,7 @@ size_t dlf_b200_conv2d_workspace_bytes(int dtype, size_t, size_t channels, size_
     if (!dtype_info(dtype, fmt, es) || group == 0 || kernel_w == 0) return 0;
     const size_t cg = channels / group, ng = num_kernels / group;
     const size_t bk = 128 / es, dup = es == 4 ? 2 : 1;
-    const size_t plain = group * ((ng + 255) / 256 * 256) * 128 * dup * ((cg * kernel_h * kernel_w + bk - 1) / bk);
+    const size_t plain = group * ((ng + 255) / 256 * 256 + 256) * 128 * dup * ((cg * kernel_h * kernel_w + bk - 1) / bk);
     size_t row = 0;
     if (kernel_w >= 2 && kernel_w <= 8) {
         const size_t cpt_max = (256 / kernel_w) / 16 * 16;

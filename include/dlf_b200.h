@@ -122,14 +122,17 @@ const char* dlf_b200_status_string(int status);
 int dlf_b200_device_status(int* device_status);
 
 /* Tuning overrides for experiments, for every following call of this process: force the N-tile
- * width (64, 128 or 256; 0 = automatic) and the operand path: 0 = automatic, 1 = never the TMA
+ * width (64, 128 or 256; the kernel that keeps operand A in tensor memory takes any multiple of
+ * 32 in that range; 0 = automatic) and the operand path: 0 = automatic, 1 = never the TMA
  * producer, 2 = always the loader-warp kernel with both operands in shared memory, 3 = the
  * kernel that keeps operand A in tensor memory whenever the TMA producer is not used, 4 = as 0
  * but convolutions never use the row form (horizontal taps as GEMM columns). Higher bits switch
  * single features for measurements: 0x200 use CTA pairs (cta_group::2) for 256-column fp16 tiles,
- * 0x800 no TMA for the fp32 B operand, 0x1000 no K-chunked fp32 accumulation, 0x2000 no affine
- * addressing for 1x1 filters, 0x4000 no TMA
- * stores, 0x8000 never pack the filter bank of a convolution. */
+ * 0x400 a second accumulator only when three operand slots remain in tensor memory (default:
+ * two), 0x800 no TMA for the fp32 B operand, 0x1000 no K-chunked fp32 accumulation, 0x2000 no
+ * affine addressing for 1x1 filters, 0x4000 no TMA stores, 0x8000 never pack the filter bank of
+ * a convolution. Bits 16 and up switch parts of a kernel off to time the rest (results are then
+ * meaningless). */
 void dlf_b200_set_tuning(int force_bn, int force_generic_loader);
 
 /* Counts kernel launches made by this library in this process (all threads). */

@@ -237,6 +237,41 @@ def test_gemm_every_tile_width(lib, bn):
         lib.set_tuning(0, False)
 
 
+@pytest.mark.parametrize("bn,flags", [(96, 3), (160, 3), (192, 3), (224, 3), (192, 3 | 0x400), (256, 3)])
+def test_tensor_memory_operand_kernel_tile_widths(lib, bn, flags):
+    """The kernel that keeps operand A in tensor memory takes any tile width that is a multiple of
+    32, with one or two accumulators (two whenever two operand slots remain; 0x400 asks for
+    three). fp16 GEMM in both operand orders, fp32 GEMM (widths up to 192 fit two accumulators)
+    and a 1x1 convolution, against the oracle."""
+    from dlf_b200 import gdnn
+    gb = _gb()
+    lib.set_tuning(bn, flags)
+    try:
+        for ta in (gb.Transpose.NoTrans, gb.Transpose.Trans):
+            got, ref = _gemm_case(np.random.default_rng(bn), torch.float16, gb.Layout.ColMajor,
+                                  ta, gb.Transpose.NoTrans, 390, 500, 200, 1.0, 0.0, (0, 0, 0), (0, 0, 0))
+            assert max_rel(got, ref) <= HALF_TOL
+        got, ref = _gemm_case(np.random.default_rng(bn), torch.float32, gb.Layout.RowMajor,
+                              gb.Transpose.Trans, gb.Transpose.NoTrans, 300, 520, 200, 0.5, 0.5,
+                              (0, 0, 0), (0, 0, 0))
+        assert rel_fro(got, ref) <= FP32_TOL
+        for dtype in (torch.float16, torch.float32):
+            rng = np.random.default_rng(bn)
+            X = _round_to(rng.normal(size=(3, 72, 14, 14)).astype(np.float32), dtype)
+            Wt = _round_to((0.1 * rng.normal(size=(424, 72, 1, 1))).astype(np.float32), dtype)
+            ref = oracle.conv2d(X, Wt, group=1, pads=(0, 0, 0, 0), strides=(1, 1), dilations=(1, 1), wide=True)
+            filt = gdnn.Filter2D(X.shape, Wt.shape)
+            Y = torch.full(ref.shape, float("nan"), dtype=dtype, device="cuda")
+            gdnn.conv2d_filter(torch.from_numpy(X).to(dtype).cuda(), torch.from_numpy(Wt).to(dtype).cuda(), Y, filt)
+            got = Y.float().cpu().numpy()
+            if dtype == torch.float32:
+                assert rel_fro(got, ref) <= FP32_TOL
+            else:
+                assert max_rel(got, ref) <= HALF_TOL
+    finally:
+        lib.set_tuning(0, 0)
+
+
 @pytest.mark.parametrize("m,n,k", [(512, 512, 264), (300, 520, 200), (1000, 264, 72)])
 def test_gemm_cta_pair_kernel(lib, m, n, k):
     """The cta_group::2 variant (two CTAs share 256 x 256 tiles; opt-in, tuning bit 0x200) on all
