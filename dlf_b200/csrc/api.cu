@@ -242,9 +242,9 @@ int encode_map(const DeviceState& st, CUtensorMap* map, const GenOperand& op, in
     return r == CUDA_SUCCESS ? kSuccess : kUnexpectedError;
 }
 
-// Tensor map for TMA stores of the output (32 x 32 blocks, no swizzle): only when nothing of C has
+// Tensor map for TMA stores of the output (blocks of 32 rows x 32 or 64 columns, no swizzle): only when nothing of C has
 // to be read (beta == 0, no per-batch tables) and D's base and strides are 16-byte multiples.
-bool encode_output_map(const DeviceState& st, CUtensorMap* map, const Problem& q) {
+bool encode_output_map(const DeviceState& st, CUtensorMap* map, const Problem& q, unsigned box_cols) {
     const bool d_ok = q.es == 2 && q.beta == 0.0f && q.betas == nullptr && q.d_offs == nullptr &&
                       (reinterpret_cast<uintptr_t>(q.d) & 15u) == 0 && (q.ldd * q.es) % 16 == 0 &&
                       (q.batch == 1 || (q.d_batch_stride * q.es) % 16 == 0) &&
@@ -258,7 +258,7 @@ bool encode_output_map(const DeviceState& st, CUtensorMap* map, const Problem& q
                              static_cast<cuuint64_t>(batched ? q.d_batch_stride * q.es
                                                              : q.ldd * q.es * (q.N > 0 ? q.N : 1))};
     if (strides[1] >= (1ull << 40)) strides[1] = strides[0];
-    cuuint32_t box[3] = {32, 32, 1};
+    cuuint32_t box[3] = {32, box_cols, 1};
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = st.encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, q.d, dims, strides, box, estr,
                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
@@ -512,7 +512,7 @@ int launch(const Problem& q, cudaStream_t stream, DeviceState* preset = nullptr)
         if (rc != kSuccess) return rc;
         rc = encode_map(*st, &tm_b, q.b, q.es, q.N, q.K, q.batch, bn / 2);
         if (rc != kSuccess) return rc;
-        p.d_tma = encode_output_map(*st, &tm_d, q) ? 1 : 0;
+        p.d_tma = encode_output_map(*st, &tm_d, q, 64) ? 64 : 0;
         const long long clusters = ptotal < st->max_pair_clusters ? ptotal : st->max_pair_clusters;
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(static_cast<unsigned>(2 * clusters), 1, 1);
@@ -580,7 +580,8 @@ int launch(const Problem& q, cudaStream_t stream, DeviceState* preset = nullptr)
         if (rc != kSuccess) return rc;
         rc = encode_map(*st, &tm_b, q.b, q.es, q.N, q.K, q.batch, bn);
         if (rc != kSuccess) return rc;
-        p.d_tma = encode_output_map(*st, &tm_d, q) ? 1 : 0;
+        const unsigned box_cols = (bn >= 128 && !(g_force_generic.load() & 0x100)) ? 64 : 32;
+        p.d_tma = encode_output_map(*st, &tm_d, q, box_cols) ? static_cast<int>(box_cols) : 0;
     }
 
     const unsigned grid = static_cast<unsigned>(total < st->num_sms ? total : st->num_sms);

@@ -95,7 +95,8 @@ struct Params {
     long long bias_stride;
     Im2colGeom g;
     int* status;
-    int d_tma;   // 16-bit outputs with beta == 0 and TMA-compatible strides: the epilogue stages
+    int d_tma;   // 0, or the column count (32 / 64) of the TMA store box. 16-bit outputs with
+                 // beta == 0 and TMA-compatible strides: the epilogue stages
                  // 32 x 32 blocks in shared memory and writes them with TMA stores
     int ablate;  // measurement aid (tuning flags >> 16; results are then meaningless):
                  // 1 A producer skips its loads, 2 B loaders skip theirs, 4 producers skip the TMEM
@@ -353,6 +354,12 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
             if constexpr (USE_TMA) {
                 if (p.d_tma) {
                     const int i0 = m0 + q * 32;
+                    // Blocks of 32 rows x 32 columns go to one of the warp's two staging buffers
+                    // (2 KB each, adjacent). With 32-column boxes the buffers alternate and every
+                    // block is one TMA store; with 64-column boxes (tiles of 128 columns or more)
+                    // two consecutive blocks fill both buffers and leave as one 4 KB store: TMA
+                    // stores this small are bound by their number, not their bytes.
+                    const bool wide = p.d_tma == 64;
                     for (int c0 = 0; c0 < ncols && i0 < p.M; c0 += 32, ++chunk_no) {
                         uint32_t v[32];
                         ptx::tmem_ld_32x32(trow + c0, v);
@@ -361,13 +368,16 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
                         if (bias != nullptr && c0 + lane < ncols)
                             bv = p.fmt == FMT_F16 ? out_load<OUT_F16>(bias + (c0 + lane) * 2)
                                                   : out_load<OUT_BF16>(bias + (c0 + lane) * 2);
-                        // the block written two chunks ago used the same staging buffer
-                        if (chunk_no >= 2) {
-                            if (lane == 0) ptx::bulk_wait_group_read<1>();
+                        const uint32_t half = wide ? static_cast<uint32_t>((c0 >> 5) & 1) : (chunk_no & 1u);
+                        // the store that last read this buffer must have drained it
+                        if (wide ? (half == 0 && chunk_no >= 1) : (chunk_no >= 2)) {
+                            if (lane == 0) {
+                                if (wide) ptx::bulk_wait_group_read<0>();
+                                else ptx::bulk_wait_group_read<1>();
+                            }
                             __syncwarp();
                         }
-                        const uint32_t sbuf =
-                            ptx::smem_u32(d_stage) + (ewarp * 2 + (chunk_no & 1u)) * 2048u + lane * 2u;
+                        const uint32_t sbuf = ptx::smem_u32(d_stage) + (ewarp * 2 + half) * 2048u + lane * 2u;
                         if (p.fmt == FMT_F16) {
 #pragma unroll
                             for (int jj = 0; jj < 32; ++jj) {
@@ -383,10 +393,14 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
                                 asm volatile("st.shared.u16 [%0], %1;" ::"r"(sbuf + jj * 64u), "h"(h) : "memory");
                             }
                         }
+                        // a wide store leaves after its second block, or after the first when no
+                        // second one exists (the box is then clipped at column N by the hardware)
+                        if (wide && half == 0 && c0 + 32 < ncols) continue;
                         ptx::fence_proxy_async_smem();
                         __syncwarp();
                         if (lane == 0) {
-                            ptx::tma_store_3d(&tmD, sbuf - lane * 2u, i0, n0 + cb + c0, p.d_batch_stride ? b : 0);
+                            ptx::tma_store_3d(&tmD, ptx::smem_u32(d_stage) + (ewarp * 2 + (wide ? 0u : half)) * 2048u, i0,
+                                              n0 + cb + (wide ? (c0 & ~63) : c0), p.d_batch_stride ? b : 0);
                             ptx::bulk_commit_group();
                         }
                     }

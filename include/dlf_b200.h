@@ -127,7 +127,8 @@ int dlf_b200_device_status(int* device_status);
  * producer, 2 = always the loader-warp kernel with both operands in shared memory, 3 = the
  * kernel that keeps operand A in tensor memory whenever the TMA producer is not used, 4 = as 0
  * but convolutions never use the row form (horizontal taps as GEMM columns). Higher bits switch
- * single features for measurements: 0x200 use CTA pairs (cta_group::2) for 256-column fp16 tiles,
+ * single features for measurements: 0x100 TMA stores of 32-column blocks only (default: 64
+ * columns for tiles of 128 columns or more), 0x200 use CTA pairs (cta_group::2) for 256-column fp16 tiles,
  * 0x400 a second accumulator only when three operand slots remain in tensor memory (default:
  * two), 0x800 no TMA for the fp32 B operand, 0x1000 no K-chunked fp32 accumulation, 0x2000 no
  * affine addressing for 1x1 filters, 0x4000 no TMA stores, 0x8000 never pack the filter bank of

@@ -272,6 +272,28 @@ def test_tensor_memory_operand_kernel_tile_widths(lib, bn, flags):
         lib.set_tuning(0, 0)
 
 
+@pytest.mark.parametrize("bn", [128, 256])
+@pytest.mark.parametrize("n", [96, 160, 200, 264, 520])
+def test_gemm_tma_store_box_widths(lib, bn, n):
+    """The TMA-fed kernel writes 16-bit outputs as TMA stores of 32 x 64 blocks (two staged 32 x 32
+    blocks per store) when tiles are 128 columns or wider, else 32 x 32; N values whose last block
+    pair is half empty or cut by the matrix edge must come out identical in both forms, with
+    nothing written beyond column N."""
+    gb = _gb()
+    outs = []
+    for flags in (0, 0x100):
+        lib.set_tuning(bn, flags)
+        try:
+            got, ref = _gemm_case(np.random.default_rng(n), torch.float16, gb.Layout.ColMajor,
+                                  gb.Transpose.NoTrans, gb.Transpose.Trans, 328, n, 136, 1.0, 0.0,
+                                  (0, 0, 8), (0, 0, 0))
+        finally:
+            lib.set_tuning(0, 0)
+        assert max_rel(got, ref) <= HALF_TOL
+        outs.append(got)
+    assert np.array_equal(outs[0], outs[1])
+
+
 @pytest.mark.parametrize("m,n,k", [(512, 512, 264), (300, 520, 200), (1000, 264, 72)])
 def test_gemm_cta_pair_kernel(lib, m, n, k):
     """The cta_group::2 variant (two CTAs share 256 x 256 tiles; opt-in, tuning bit 0x200) on all
