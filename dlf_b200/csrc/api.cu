@@ -8,6 +8,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <atomic>
 #include <climits>
 #include <cstdint>
@@ -188,7 +189,7 @@ struct Problem {
     long long bias_stride = 0;
     Im2colGeom g{};
     // row form of a convolution (contraction_ts.cuh, A_ROWCONV); rc_kw == 0: not used
-    int rc_kw = 0, rc_cpt = 0, rc_T = 0, rc_lo = 0;
+    int rc_kw = 0, rc_cpt = 0, rc_T = 0, rc_lo = 0, rc_sw = 1, rc_wv = 0, rc_dmin = 0;
     // caller-provided scratch for the packed filter bank of a convolution (may be null)
     unsigned char* pack_ws = nullptr;
     size_t pack_ws_bytes = 0;
@@ -407,6 +408,9 @@ int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
     tp.rc_cpt = q.rc_cpt;
     tp.rc_T = q.rc_T;
     tp.rc_lo = q.rc_lo;
+    tp.rc_sw = q.rc_sw;
+    tp.rc_wv = q.rc_wv;
+    tp.rc_dmin = q.rc_dmin;
     tp.kc_blocks = kc_blocks;
     tp.sums_off = sums_off;
     tp.acc_bufs = acc_bufs;
@@ -863,14 +867,10 @@ size_t dlf_b200_conv2d_workspace_bytes(int dtype, size_t, size_t channels, size_
     const size_t cg = channels / group, ng = num_kernels / group;
     const size_t bk = 128 / es, dup = es == 4 ? 2 : 1;
     const size_t plain = group * ((ng + 255) / 256 * 256 + 256) * 128 * dup * ((cg * kernel_h * kernel_w + bk - 1) / bk);
-    size_t row = 0;
-    if (kernel_w >= 2 && kernel_w <= 8) {
-        const size_t cpt_max = (256 / kernel_w) / 16 * 16;
-        const size_t n_tiles = (ng + cpt_max - 1) / cpt_max;
-        size_t cpt = ((ng + n_tiles - 1) / n_tiles + 15) / 16 * 16;
-        if (cpt > cpt_max) cpt = cpt_max;
-        row = group * n_tiles * ((cg * kernel_h + bk - 1) / bk) * (cpt * kernel_w * 128 * dup);
-    }
+    // row form: taps x K' <= (KW + 2*sw) x C*KH for strides sw <= 4 (column phases join K, taps
+    // become ceil-ish KW/sw shifts), output channels padded to the tile's channel count
+    const size_t row = group * ((ng + 255) / 256 * 256 + 256) * 128 * dup *
+                       ((cg * kernel_h * (kernel_w + 8) + bk - 1) / bk + 8);
     return (plain > row ? plain : row) + 256;
 }
 
@@ -971,26 +971,42 @@ int dlf_b200_conv2d(int dtype, size_t batches, size_t channels, size_t height, s
     q.g.out_img_stride = static_cast<long long>(num_kernels) * P;
     if (P > INT_MAX) return kInvalidDimension;
 
-    // Row form (see contraction_ts.cuh): horizontal taps become output columns of the GEMM.
+    // Row form (see contraction_ts.cuh): horizontal taps become output columns of the GEMM. With
+    // stride_w = sw the input columns split into sw phases that join the channels in K, and the
+    // taps become the shifts d = floor((kw - pad_left) / sw).
     const int path = g_force_generic.load() & 0xff;
-    const long long lo = static_cast<long long>(pad_left);
-    const long long hi = static_cast<long long>(kernel_w) - 1 - lo > 0 ? static_cast<long long>(kernel_w) - 1 - lo : 0;
-    if (path != 2 && path != 4 && stride_w == 1 && dilation_w == 1 && kernel_w >= 2 && kernel_w <= 8 &&
-        output_w <= width && lo + hi <= 16 &&
-        static_cast<long long>(batches) * output_h * width < INT_MAX - 4096) {
-        // fp32 with K' = C*KH > 512 sums K-chunks in a float[N][128] shared array: N <= 128 then
-        const bool chunked = q.es == 4 && cg * static_cast<long long>(kernel_h) > 512;
-        const int cpt_max = static_cast<int>(((chunked ? 128 : 256) / kernel_w) / 16 * 16);
+    const long long sw = static_cast<long long>(stride_w);
+    const long long pl = static_cast<long long>(pad_left);
+    auto floor_div = [](long long a, long long b) { return a >= 0 ? a / b : -((-a + b - 1) / b); };
+    const long long dmin = floor_div(-pl, sw);
+    const long long dmax = floor_div(static_cast<long long>(kernel_w) - 1 - pl, sw);
+    const long long taps = dmax - dmin + 1;
+    const long long lo = -dmin;
+    const long long hi = dmax > 0 ? dmax : 0;
+    // positions per row: every input column for sw = 1; for sw > 1 the w' that some output needs
+    // and whose columns sw*w' + r are not all beyond the row
+    const long long wv = sw == 1 ? static_cast<long long>(width)
+                                 : std::min<long long>(static_cast<long long>(output_w) + hi,
+                                                       (static_cast<long long>(width) + sw - 1) / sw);
+    if (path != 2 && path != 4 && sw >= 1 && sw <= 4 && dilation_w == 1 && dmax >= 0 && taps >= 2 && taps <= 8 &&
+        static_cast<long long>(output_w) <= wv && lo + hi <= 16 && !(sw > 1 && path == 5) &&
+        static_cast<long long>(batches) * output_h * wv < INT_MAX - 4096) {
+        // fp32 with K' = C*KH*sw > 512 sums K-chunks in a float[N][128] shared array: N <= 128 then
+        const bool chunked = q.es == 4 && cg * static_cast<long long>(kernel_h) * sw > 512;
+        const int cpt_max = static_cast<int>(((chunked ? 128 : 256) / taps) / 16 * 16);
         const int n_tiles = static_cast<int>((ng + cpt_max - 1) / cpt_max);
         int cpt = static_cast<int>(((ng + n_tiles - 1) / n_tiles + 15) / 16 * 16);
         if (cpt > cpt_max) cpt = cpt_max;
         Problem r = q;
-        r.rc_kw = static_cast<int>(kernel_w);
+        r.rc_kw = static_cast<int>(taps);
         r.rc_cpt = cpt;
         r.rc_lo = static_cast<int>(lo);
         r.rc_T = 32 - static_cast<int>(lo + hi);
-        r.M = static_cast<long long>(batches) * output_h * width;  // positions (img, oh, input column)
-        r.K = cg * static_cast<long long>(kernel_h);                // (c, kh)
+        r.rc_sw = static_cast<int>(sw);
+        r.rc_wv = static_cast<int>(wv);
+        r.rc_dmin = static_cast<int>(dmin);
+        r.M = static_cast<long long>(batches) * output_h * wv;  // positions (img, oh, w')
+        r.K = cg * static_cast<long long>(kernel_h) * sw;         // (kh, column phase, c)
         r.a.im2col = 1;
         DeviceState* st = nullptr;
         int rc = ensure_device(&st);

@@ -32,6 +32,13 @@
 // of 32 consecutive positions of which the inner T = 32 - (KW-1) produce outputs (windows of
 // consecutive warps overlap by KW-1 positions).
 //
+// With a horizontal stride sw > 1 (and dilation_w = 1) the same form applies after splitting the
+// input columns into sw phases: u = sw*ow + kw - pl = sw*(ow + d) + r with r = (kw - pl) mod sw,
+// d = floor((kw - pl) / sw). Positions are (img, oh, w') over a virtual row of w' values, the
+// column phases join the channels in K (k' = (kh*sw + r)*C + c reads X[..][sw*w' + r]) and the taps
+// become the shifts d = dmin..dmax: Y[ow] = sum_d D'[(ow + d), (d, co)]. The 7x7 stride-2 stem of
+// ResNet becomes K' = 42 (one k-block), N = 4 x 64.
+//
 // TMEM columns: [0, acc_bufs*BN) accumulators, then `stages` A slots of 32 (16-bit types: 64 k
 // packed two per column) or 64 (fp32: 32 hi + 32 lo) columns.
 // Warp roles: 0-3 epilogue, 4-11 A producers (quadrant = warp % 4), 12-14 B loaders, 15 UMMA
@@ -64,6 +71,10 @@ struct TsParams {
     // A_ROWCONV only (see the header comment): taps per row, output channels per tile, output
     // positions per warp, lanes of left halo
     int rc_kw, rc_cpt, rc_T, rc_lo;
+    // Row form with a horizontal stride (see the header comment): rc_sw = stride_w (number of
+    // column phases folded into K), rc_wv = positions per row, rc_dmin = smallest tap shift
+    // (rc_lo = -rc_dmin); with stride_w = 1 these are 1, W and -pad_left.
+    int rc_sw, rc_wv, rc_dmin;
     // Filter bank already laid out as the kernel's shared-memory stage images (pack_weights_kernel):
     // [batch][n-tile][k-block][stage_bytes]; null = the loader warps gather from the OIHW tensor
     const unsigned char* b_packed;
@@ -120,36 +131,55 @@ __device__ __forceinline__ void umma_ts_tf32(uint32_t d_tmem, uint32_t a_tmem, u
         : "memory");
 }
 
-// Element k' = kh*C + c of the row-form filter operand for one (co, kw):
-// W[co][c][kh][kw] = base[off + (c*KH + kh)*KW], with off already at (co, kw). Returns 0 beyond K'.
+// Element k' = (kh*sw + r)*C + c of the row-form filter operand for output channel `co_off`
+// (element offset of W[co][0][0][0]) and tap j: W[co][c][kh][kw] with kw = sw*(j + dmin) + r + pl,
+// zero where that kw does not exist or k' >= k_lim.
+struct RowTaps {
+    int KH, KW, cg;  // real filter height and width, channels per group
+    int sw, dmin, pl;
+};
 template <int ES>
-__device__ __forceinline__ uint32_t rowconv_weight(const char* base, long long off, int KH, int KW,
-                                                   int cg, int k, int k_lim) {
+__device__ __forceinline__ uint32_t rowconv_weight(const char* base, long long co_off, const RowTaps& rt,
+                                                   int j, int k, int k_lim) {
     if (k >= k_lim) return 0u;
-    const int kh = k / cg;
-    const int c = k - kh * cg;
-    const long long idx = off + static_cast<long long>(c * KH + kh) * KW;
+    const int cgv = rt.cg * rt.sw;
+    const int kh = k / cgv;
+    const int rem = k - kh * cgv;
+    const int r = rem / rt.cg;
+    const int c = rem - r * rt.cg;
+    const int kw = rt.sw * (j + rt.dmin) + r + rt.pl;
+    if (kw < 0 || kw >= rt.KW) return 0u;
+    const long long idx = co_off + static_cast<long long>(c * rt.KH + kh) * rt.KW + kw;
     if constexpr (ES == 4) return reinterpret_cast<const uint32_t*>(base)[idx];
     else return reinterpret_cast<const unsigned short*>(base)[idx];
 }
 template <int ES>
-__device__ __forceinline__ uint4 load_chunk_rowconv(const char* base, long long off, int KH, int KW,
-                                                    bool row_ok, int k0, int k_lim) {
+__device__ __forceinline__ uint4 load_chunk_rowconv(const char* base, long long co_off, const RowTaps& rt,
+                                                    int j, bool row_ok, int k0, int k_lim) {
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
     if (!row_ok || k0 >= k_lim) return v;
-    const int cg = k_lim / KH;
     if constexpr (ES == 4) {
-        v.x = rowconv_weight<ES>(base, off, KH, KW, cg, k0, k_lim);
-        v.y = rowconv_weight<ES>(base, off, KH, KW, cg, k0 + 1, k_lim);
-        v.z = rowconv_weight<ES>(base, off, KH, KW, cg, k0 + 2, k_lim);
-        v.w = rowconv_weight<ES>(base, off, KH, KW, cg, k0 + 3, k_lim);
+        v.x = rowconv_weight<ES>(base, co_off, rt, j, k0, k_lim);
+        v.y = rowconv_weight<ES>(base, co_off, rt, j, k0 + 1, k_lim);
+        v.z = rowconv_weight<ES>(base, co_off, rt, j, k0 + 2, k_lim);
+        v.w = rowconv_weight<ES>(base, co_off, rt, j, k0 + 3, k_lim);
     } else {
         uint32_t e[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) e[i] = rowconv_weight<ES>(base, off, KH, KW, cg, k0 + i, k_lim);
+        for (int i = 0; i < 8; ++i) e[i] = rowconv_weight<ES>(base, co_off, rt, j, k0 + i, k_lim);
         v = make_uint4(e[0] | (e[1] << 16), e[2] | (e[3] << 16), e[4] | (e[5] << 16), e[6] | (e[7] << 16));
     }
     return v;
+}
+__device__ __forceinline__ RowTaps row_taps(const TsParams& tp) {
+    RowTaps rt;
+    rt.KH = tp.base.g.KH;
+    rt.KW = tp.base.g.KW;
+    rt.sw = tp.rc_sw;
+    rt.cg = tp.base.K / (tp.base.g.KH * tp.rc_sw);
+    rt.dmin = tp.rc_dmin;
+    rt.pl = tp.base.g.pad_l;
+    return rt;
 }
 
 // Lays the filter bank of a convolution out as the stage images the kernel above consumes, once
@@ -178,8 +208,9 @@ __global__ void pack_weights_kernel(const TsParams tp, unsigned char* out, long 
         if (tp.a_kind == A_ROWCONV) {
             const int kw = L / tp.rc_cpt;
             const int co = tn * tp.rc_cpt + (L - kw * tp.rc_cpt);
-            v = load_chunk_rowconv<ES>(p.b.base, b_boff + (static_cast<long long>(co) * p.K) * tp.rc_kw + kw,
-                                       p.g.KH, tp.rc_kw, co < p.N, kb * BK + c * CPE, p.K);
+            const RowTaps rt = row_taps(tp);
+            v = load_chunk_rowconv<ES>(p.b.base, b_boff + static_cast<long long>(co) * rt.cg * rt.KH * rt.KW, rt,
+                                       kw, co < p.N, kb * BK + c * CPE, p.K);
         } else {
             v = load_chunk_dense<ES>(p.b, b_boff, tn * BN + L, p.N, kb * BK + c * CPE, p.K);
         }
@@ -249,19 +280,23 @@ __global__ void __launch_bounds__(kTsThreads, 1)
         ptx::fence_mbar_init();
     }
     if (tp.a_kind == A_ROWCONV) {
-        // k' = kh*C + c -> (offset of the input row, kh*dh); the column is the thread's own.
-        // Channel-fastest, so that a k-block usually lies inside one kh: one validity test and a
-        // constant address stride (H*W) for the whole block.
+        // k' = (kh*sw + r)*C + c -> (offset of the input row + column phase r, kh*dh, r); the
+        // column is the thread's own (times sw). Channel-fastest, so that with sw = 1 a k-block
+        // usually lies inside one kh: one validity test and a constant address stride (H*W) for
+        // the whole block.
         KEntry* kt = reinterpret_cast<KEntry*>(smem_raw);
+        const int cgv = p.K / p.g.KH;     // channels per group x column phases
+        const int cg = cgv / tp.rc_sw;    // channels per group
         for (int k = threadIdx.x; k < num_kb * BK; k += blockDim.x) {
             KEntry e;
             const int kk = k < p.K ? k : 0;
-            const int cg = p.K / p.g.KH;  // channels per group
-            const int kh = kk / cg;
-            const int ch = kk - kh * cg;
-            e.off = (ch * p.g.H + kh * p.g.dh) * p.g.W;
+            const int kh = kk / cgv;
+            const int rem = kk - kh * cgv;
+            const int r = rem / cg;
+            const int ch = rem - r * cg;
+            e.off = (ch * p.g.H + kh * p.g.dh) * p.g.W + r;
             e.dy = static_cast<short>(kh * p.g.dh);
-            e.dx = 0;
+            e.dx = static_cast<short>(r);
             kt[k] = e;
         }
     }
@@ -326,12 +361,12 @@ __global__ void __launch_bounds__(kTsThreads, 1)
             if (tp.a_kind == A_ROWCONV) {
                 const int tm = m0 / kBM, tn = n0 / BN;
                 const int pos = (tm * 4 + warp) * tp.rc_T - tp.rc_lo + lane;
-                const int OHW = p.g.OH * p.g.W;
+                const int OHW = p.g.OH * tp.rc_wv;
                 const bool pos_ok = pos >= 0 && pos < p.M;
                 const int img = pos_ok ? pos / OHW : 0;
                 const int rem = pos_ok ? pos - img * OHW : 0;
-                const int oh = rem / p.g.W;
-                const int u = rem - oh * p.g.W;
+                const int oh = rem / tp.rc_wv;
+                const int u = rem - oh * tp.rc_wv;
                 const bool produce = pos_ok && lane >= tp.rc_lo && lane < tp.rc_lo + tp.rc_T && u < p.g.OW;
                 const int c0 = tn * tp.rc_cpt;
                 const long long obase = static_cast<long long>(img) * p.g.out_img_stride +
@@ -363,7 +398,7 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                                 d[e] = __float_as_uint(__uint_as_float(d[e]) + part[(kw * tp.rc_cpt + co0 + e) * 128]);
                         }
                         const int src = lane + kw - tp.rc_lo;
-                        const bool in = static_cast<unsigned>(u + kw - tp.rc_lo) < static_cast<unsigned>(p.g.W);
+                        const bool in = static_cast<unsigned>(u + kw - tp.rc_lo) < static_cast<unsigned>(tp.rc_wv);
 #pragma unroll
                         for (int e = 0; e < 16; ++e) {
                             const float tv = __uint_as_float(__shfl_sync(0xffffffffu, d[e], src & 31));
@@ -459,11 +494,11 @@ __global__ void __launch_bounds__(kTsThreads, 1)
             if (tp.a_kind == A_ROWCONV) {
                 const int pos = ((m0 / kBM) * 4 + q) * tp.rc_T - tp.rc_lo + lane;
                 if (pos >= 0 && pos < p.M) {
-                    const int OHW = p.g.OH * p.g.W;
+                    const int OHW = p.g.OH * tp.rc_wv;
                     const int img = pos / OHW;
                     const int rem = pos - img * OHW;
-                    const int oh = rem / p.g.W;
-                    iw0 = rem - oh * p.g.W;  // the input column itself: always inside the row
+                    const int oh = rem / tp.rc_wv;
+                    iw0 = (rem - oh * tp.rc_wv) * tp.rc_sw;  // sw = 1: the input column itself, always inside the row
                     ih0 = oh * p.g.sh - p.g.pad_t;
                     pbase = a_boff + static_cast<long long>(img) * p.g.img_stride +
                             static_cast<long long>(ih0) * p.g.W + iw0;
@@ -499,7 +534,7 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                 if (p.ablate & 1) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] = 0x3f800000u + j;
-                } else if (tp.a_kind == A_ROWCONV && kcount == BK && ktable[k0].dy == ktable[k0 + BK - 1].dy) {
+                } else if (tp.a_kind == A_ROWCONV && tp.rc_sw == 1 && kcount == BK && ktable[k0].dy == ktable[k0 + BK - 1].dy) {
                     // whole k-block inside one kh: consecutive k are consecutive channels
                     const KEntry e0 = ktable[k0];
                     const bool in = static_cast<unsigned>(ih0 + e0.dy) < static_cast<unsigned>(p.g.H);
@@ -777,8 +812,9 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                             // column L = (kw, co): W[c0+co][c][kh][kw] for k' = kh*C + c
                             const int kw = L / tp.rc_cpt;
                             const int co = (n0 / BN) * tp.rc_cpt + (L - kw * tp.rc_cpt);
-                            v[q] = load_chunk_rowconv<ES>(p.b.base, b_boff + (static_cast<long long>(co) * p.K) * tp.rc_kw + kw,
-                                                          p.g.KH, tp.rc_kw, co < p.N, kb * BK + c * CPE, p.K);
+                            const RowTaps rt = row_taps(tp);
+                            v[q] = load_chunk_rowconv<ES>(p.b.base, b_boff + static_cast<long long>(co) * rt.cg * rt.KH * rt.KW,
+                                                          rt, kw, co < p.N, kb * BK + c * CPE, p.K);
                         } else if (p.b.k_major) {
                             v[q] = load_chunk_dense<ES>(p.b, b_boff, n0 + L, p.N, kb * BK + c * CPE, p.K);
                         } else {

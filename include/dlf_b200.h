@@ -126,7 +126,8 @@ int dlf_b200_device_status(int* device_status);
  * 32 in that range; 0 = automatic) and the operand path: 0 = automatic, 1 = never the TMA
  * producer, 2 = always the loader-warp kernel with both operands in shared memory, 3 = the
  * kernel that keeps operand A in tensor memory whenever the TMA producer is not used, 4 = as 0
- * but convolutions never use the row form (horizontal taps as GEMM columns). Higher bits switch
+ * but convolutions never use the row form (horizontal taps as GEMM columns), 5 = as 0 but the
+ * row form only for stride_w = 1. Higher bits switch
  * single features for measurements: 0x100 TMA stores of 32-column blocks only (default: 64
  * columns for tiles of 128 columns or more), 0x200 use CTA pairs (cta_group::2) for 256-column fp16 tiles,
  * 0x400 a second accumulator only when three operand slots remain in tensor memory (default:

@@ -456,10 +456,15 @@ CONV_CASES = [
     (2, 12, 8, 8, 24, 3, 3, (1, 1, 1, 1), (1, 1), (1, 1), 3),       # row form with groups
     (1, 4, 5, 40, 8, 1, 4, (0, 0, 0, 0), (1, 1), (1, 1), 1),        # row form, no padding: OW < W
     (1, 192, 9, 12, 40, 3, 3, (1, 1, 1, 1), (1, 1), (1, 1), 1),     # row form, K' = 576: chunked accumulation in fp32
-    (1, 72, 9, 12, 24, 3, 3, (1, 1, 1, 1), (2, 2), (1, 1), 1),      # im2col form, K = 648: chunked accumulation in fp32
+    (1, 72, 9, 12, 24, 3, 3, (1, 1, 2, 2), (2, 2), (1, 2), 1),      # im2col form (dilation_w 2), K = 648: chunked accumulation in fp32
     (3, 70, 7, 7, 36, 1, 1, (0, 0, 0, 0), (1, 1), (1, 1), 1),       # 1x1, odd plane (49 pixels), K tail: affine addressing
     (2, 40, 9, 9, 24, 1, 1, (0, 0, 1, 1), (2, 2), (1, 1), 2),       # 1x1 stride 2, trailing padding reaches outside: table lookup
     (2, 24, 14, 14, 72, 1, 1, (0, 0, 0, 0), (1, 1), (1, 1), 1),     # 1x1, even plane (196): paired 32-bit stores for 16-bit outputs
+    (2, 16, 15, 23, 40, 3, 3, (1, 1, 1, 1), (2, 2), (1, 1), 1),     # strided row form: 3x3 stride 2, odd width (2 shifts, 2 column phases)
+    (3, 6, 13, 30, 20, 5, 5, (2, 2, 2, 2), (1, 3), (1, 1), 2),      # strided row form: stride_w 3, groups
+    (2, 5, 9, 26, 12, 2, 4, (0, 0, 1, 0), (1, 2), (1, 1), 1),       # strided row form: no left padding (shifts 0..1), KW = 4
+    (1, 7, 8, 67, 24, 1, 8, (0, 1, 0, 5), (1, 4), (1, 1), 1),       # strided row form: stride_w 4, KW = 8, wide right padding
+    (2, 3, 20, 33, 64, 7, 7, (3, 3, 3, 3), (2, 2), (1, 1), 1),      # stem shape with 64 output channels: 4 shifts x 64 = one 256-column tile
 ]
 
 
@@ -508,6 +513,34 @@ def test_conv2d_pointwise_table_lookup_matches_affine(lib, dtype):
             finally:
                 lib.set_tuning(0, 0)
         assert torch.equal(outs[0], outs[1]), case
+
+
+@pytest.mark.parametrize("path", [5, 0x8005, 0x8000])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_conv2d_strided_row_form_variants(lib, path, dtype):
+    """stride_w > 1 takes the row form with the input columns split into stride_w phases; path 5
+    sends the same cases through the implicit-im2col gather instead, 0x8000 makes the loader
+    warps gather the (phase-split) filter bank instead of streaming a packed copy."""
+    from dlf_b200 import gdnn
+    lib.set_tuning(0, path)
+    try:
+        for case in CONV_CASES[18:23] + [CONV_CASES[1]]:
+            N, C, H, W, Co, KH, KW, pads, strides, dil, group = case
+            rng = np.random.default_rng(17)
+            X = _round_to(rng.normal(size=(N, C, H, W)).astype(np.float32), dtype)
+            Wt = _round_to((0.1 * rng.normal(size=(Co, C // group, KH, KW))).astype(np.float32), dtype)
+            ref = oracle.conv2d(X, Wt, group=group, pads=pads, strides=strides, dilations=dil, wide=True)
+            filt = gdnn.Filter2D(X.shape, Wt.shape, group).pads(*pads).strides(*strides).dilations(*dil)
+            Y = torch.full(ref.shape, float("nan"), dtype=dtype, device="cuda")
+            gdnn.conv2d_filter(torch.from_numpy(X).to(dtype).cuda(), torch.from_numpy(Wt).to(dtype).cuda(), Y, filt)
+            got = Y.float().cpu().numpy()
+            if dtype == torch.float32:
+                assert rel_fro(got, ref) <= FP32_TOL, case
+            else:
+                assert max_rel(got, ref) <= HALF_TOL, case
+    finally:
+        lib.set_tuning(0, 0)
+    assert lib.device_status() == 0
 
 
 @pytest.mark.parametrize("path", [2, 4, 0x8000, 0x8004])
