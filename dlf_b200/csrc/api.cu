@@ -997,6 +997,8 @@ int dlf_b200_conv2d(int dtype, size_t batches, size_t channels, size_t height, s
         const int n_tiles = static_cast<int>((ng + cpt_max - 1) / cpt_max);
         int cpt = static_cast<int>(((ng + n_tiles - 1) / n_tiles + 15) / 16 * 16);
         if (cpt > cpt_max) cpt = cpt_max;
+        const int forced_bn = g_force_bn.load();  // experiments: tile width -> channels per tile
+        if (forced_bn >= 16 * taps && forced_bn / taps / 16 * 16 <= cpt_max) cpt = static_cast<int>(forced_bn / taps / 16 * 16);
         Problem r = q;
         r.rc_kw = static_cast<int>(taps);
         r.rc_cpt = cpt;

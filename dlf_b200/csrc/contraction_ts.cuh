@@ -328,6 +328,13 @@ __global__ void __launch_bounds__(kTsThreads, 1)
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&tmem_slot);
     volatile int* abort_p = &abort_flag;
 
+    // Register reallocation between the four warpgroups (the CTA starts with 512 x 128 = the
+    // whole register file): loaders and the UMMA issuer need few, the epilogue and the producers
+    // hold 32-64 values per thread in flight. 3 x 152 + 56 = 4 x 128, so every increase is
+    // covered by the decrease; all warps pass here exactly once.
+    if (warp >= kTsLoaderWarp0) asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    else asm volatile("setmaxnreg.inc.sync.aligned.u32 152;");
+
     if (warp < 4) {
         // ------------------------------------------------------------ epilogue
         uint32_t buf = 0, tphase = 0;
