@@ -57,6 +57,9 @@ def _declare(L):
     L.dlf_b200_conv2d.restype = c_int
     L.dlf_b200_conv2d.argtypes = [c_int] + [c_size] * 18 + [
         c_void, c_void, c_void, c_void, c_void, c_size, c_void]
+    L.dlf_b200_conv2d_fused.restype = c_int
+    L.dlf_b200_conv2d_fused.argtypes = [c_int] + [c_size] * 18 + [
+        c_void, c_void, c_void, c_void, c_int, c_void, c_void, c_size, c_void]
     L.dlf_b200_conv2d_workspace_bytes.restype = c_size
     L.dlf_b200_conv2d_workspace_bytes.argtypes = [c_int] + [c_size] * 10
     L.dlf_b200_status_string.restype = ctypes.c_char_p
@@ -76,6 +79,7 @@ EXPORTED_SYMBOLS = (
     "dlf_b200_gemm_batched_workspace_bytes",
     "dlf_b200_gemm_batched_noalloc",
     "dlf_b200_conv2d",
+    "dlf_b200_conv2d_fused",
     "dlf_b200_conv2d_workspace_bytes",
     "dlf_b200_status_string",
     "dlf_b200_device_status",

@@ -187,6 +187,8 @@ struct Problem {
     const float* betas = nullptr;
     const char* bias = nullptr;
     long long bias_stride = 0;
+    const char* resid = nullptr;
+    int relu = 0;
     Im2colGeom g{};
     // row form of a convolution (contraction_ts.cuh, A_ROWCONV); rc_kw == 0: not used
     int rc_kw = 0, rc_cpt = 0, rc_T = 0, rc_lo = 0, rc_sw = 1, rc_wv = 0, rc_dmin = 0;
@@ -397,6 +399,8 @@ int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
     p.betas = q.betas;
     p.bias = q.bias;
     p.bias_stride = q.bias_stride;
+    p.resid = q.resid;
+    p.relu = q.relu;
     p.g = q.g;
     p.status = st.status;
     p.ablate = g_force_generic.load() >> 16;
@@ -508,6 +512,10 @@ int launch(const Problem& q, cudaStream_t stream, DeviceState* preset = nullptr)
         p.d_batch_stride = q.d_batch_stride;
         p.bias = q.bias;
         p.bias_stride = q.bias_stride;
+        p.resid = q.resid;
+        p.relu = q.relu;
+    p.resid = q.resid;
+    p.relu = q.relu;
         p.g = q.g;
         p.status = st->status;
         CUtensorMap tm_a, tm_b, tm_d;
@@ -571,6 +579,8 @@ int launch(const Problem& q, cudaStream_t stream, DeviceState* preset = nullptr)
     p.betas = q.betas;
     p.bias = q.bias;
     p.bias_stride = q.bias_stride;
+    p.resid = q.resid;
+    p.relu = q.relu;
     p.g = q.g;
     p.status = st->status;
 
@@ -874,16 +884,19 @@ size_t dlf_b200_conv2d_workspace_bytes(int dtype, size_t, size_t channels, size_
     return (plain > row ? plain : row) + 256;
 }
 
-int dlf_b200_conv2d(int dtype, size_t batches, size_t channels, size_t height, size_t width,
-                    size_t output_h, size_t output_w, size_t num_kernels, size_t group,
-                    size_t kernel_h, size_t kernel_w, size_t pad_top, size_t pad_left,
-                    size_t pad_bottom, size_t pad_right, size_t stride_h, size_t stride_w,
-                    size_t dilation_h, size_t dilation_w, const void* x, const void* w,
-                    const void* bias, void* y, void* workspace, size_t workspace_bytes,
-                    void* stream) {
+int dlf_b200_conv2d_fused(int dtype, size_t batches, size_t channels, size_t height, size_t width,
+                          size_t output_h, size_t output_w, size_t num_kernels, size_t group,
+                          size_t kernel_h, size_t kernel_w, size_t pad_top, size_t pad_left,
+                          size_t pad_bottom, size_t pad_right, size_t stride_h, size_t stride_w,
+                          size_t dilation_h, size_t dilation_w, const void* x, const void* w,
+                          const void* bias, const void* residual, int activation, void* y,
+                          void* workspace, size_t workspace_bytes, void* stream) {
     (void)pad_bottom;
     (void)pad_right;
     Problem q;
+    if (activation != DLF_B200_ACT_NONE && activation != DLF_B200_ACT_RELU) return kInvalidValue;
+    q.resid = static_cast<const char*>(residual);
+    q.relu = activation == DLF_B200_ACT_RELU ? 1 : 0;
     q.pack_ws = static_cast<unsigned char*>(workspace);
     q.pack_ws_bytes = workspace_bytes;
     if (!dtype_info(dtype, q.fmt, q.es)) return kNotImplemented;
@@ -1017,6 +1030,19 @@ int dlf_b200_conv2d(int dtype, size_t batches, size_t channels, size_t height, s
         if (rc != kNotImplemented) return rc;
     }
     return launch(q, static_cast<cudaStream_t>(stream));
+}
+
+int dlf_b200_conv2d(int dtype, size_t batches, size_t channels, size_t height, size_t width,
+                    size_t output_h, size_t output_w, size_t num_kernels, size_t group,
+                    size_t kernel_h, size_t kernel_w, size_t pad_top, size_t pad_left,
+                    size_t pad_bottom, size_t pad_right, size_t stride_h, size_t stride_w,
+                    size_t dilation_h, size_t dilation_w, const void* x, const void* w,
+                    const void* bias, void* y, void* workspace, size_t workspace_bytes,
+                    void* stream) {
+    return dlf_b200_conv2d_fused(dtype, batches, channels, height, width, output_h, output_w, num_kernels,
+                                 group, kernel_h, kernel_w, pad_top, pad_left, pad_bottom, pad_right,
+                                 stride_h, stride_w, dilation_h, dilation_w, x, w, bias, nullptr,
+                                 DLF_B200_ACT_NONE, y, workspace, workspace_bytes, stream);
 }
 
 const char* dlf_b200_status_string(int status) {

@@ -93,6 +93,10 @@ struct Params {
     const float* betas;
     const char* bias;  // bias[batch*bias_stride + j] in the storage type, or null
     long long bias_stride;
+    // fused convolution epilogue: resid (null or a tensor laid out like D) is added to the result,
+    // relu clamps it at zero before the store
+    const char* resid;
+    int relu;
     Im2colGeom g;
     int* status;
     int d_tma;   // 0, or the column count (32 / 64) of the TMA store box. 16-bit outputs with
@@ -378,17 +382,33 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
                             __syncwarp();
                         }
                         const uint32_t sbuf = ptx::smem_u32(d_stage) + (ewarp * 2 + half) * 2048u + lane * 2u;
+                        if (p.resid != nullptr) {
+                            // residual values first (loads must not sit between the stores)
+                            const char* rp = p.resid + (optr - p.d) + static_cast<long long>(c0) * colstride * 2;
+#pragma unroll
+                            for (int jj = 0; jj < 32; ++jj) {
+                                float rv = 0.0f;
+                                if (row_ok && c0 + jj < ncols)
+                                    rv = p.fmt == FMT_F16 ? out_load<OUT_F16>(rp + jj * colstride * 2)
+                                                          : out_load<OUT_BF16>(rp + jj * colstride * 2);
+                                v[jj] = __float_as_uint(alpha * __uint_as_float(v[jj]) + rv);
+                            }
+                        } else {
+#pragma unroll
+                            for (int jj = 0; jj < 32; ++jj) v[jj] = __float_as_uint(alpha * __uint_as_float(v[jj]));
+                        }
+                        const float floor_v = p.relu ? 0.0f : __int_as_float(0xff800000);  // -inf: no clamp
                         if (p.fmt == FMT_F16) {
 #pragma unroll
                             for (int jj = 0; jj < 32; ++jj) {
-                                const float r = alpha * __uint_as_float(v[jj]) + __shfl_sync(0xffffffffu, bv, jj);
+                                const float r = fmaxf(__uint_as_float(v[jj]) + __shfl_sync(0xffffffffu, bv, jj), floor_v);
                                 const unsigned short h = __half_as_ushort(__float2half_rn(r));
                                 asm volatile("st.shared.u16 [%0], %1;" ::"r"(sbuf + jj * 64u), "h"(h) : "memory");
                             }
                         } else {
 #pragma unroll
                             for (int jj = 0; jj < 32; ++jj) {
-                                const float r = alpha * __uint_as_float(v[jj]) + __shfl_sync(0xffffffffu, bv, jj);
+                                const float r = fmaxf(__uint_as_float(v[jj]) + __shfl_sync(0xffffffffu, bv, jj), floor_v);
                                 const unsigned short h = __bfloat16_as_ushort(__float2bfloat16_rn(r));
                                 asm volatile("st.shared.u16 [%0], %1;" ::"r"(sbuf + jj * 64u), "h"(h) : "memory");
                             }
@@ -414,17 +434,21 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
                     continue;
                 }
             }
+            EpiExtra ex;
+            ex.relu = p.relu != 0;
+            ex.rdelta = p.resid ? p.resid - p.d : 0;
+            const float beta_e = p.resid ? 1.0f : beta;  // a residual takes the place of the beta term
             if constexpr (ES == 4) {
-                epilogue_dispatch<OUT_F32>(trow, ncols, optr, colstride * ES, row_ok, alpha, beta,
-                                           bias, lane);
+                epilogue_dispatch<OUT_F32>(trow, ncols, optr, colstride * ES, row_ok, alpha, beta_e,
+                                           bias, lane, nullptr, false, ex);
             } else {
                 const bool pair_ok = pair_store_ok(optr, rowbase, colstride, row_ok, lane);
                 if (p.fmt == FMT_F16)
                     epilogue_dispatch<OUT_F16>(trow, ncols, optr, colstride * ES, row_ok, alpha,
-                                               beta, bias, lane, nullptr, pair_ok);
+                                               beta_e, bias, lane, nullptr, pair_ok, ex);
                 else
                     epilogue_dispatch<OUT_BF16>(trow, ncols, optr, colstride * ES, row_ok, alpha,
-                                                beta, bias, lane, nullptr, pair_ok);
+                                                beta_e, bias, lane, nullptr, pair_ok, ex);
             }
             ptx::tc_fence_before();
             if constexpr (PAIR) {

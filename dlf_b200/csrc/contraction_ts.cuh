@@ -395,6 +395,19 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                     float acc[16];
 #pragma unroll
                     for (int e = 0; e < 16; ++e) acc[e] = __shfl_sync(0xffffffffu, bv, e);
+                    if (p.resid != nullptr && produce) {
+                        // residual values, loaded before the taps so that their latency is hidden
+                        const char* rp = p.resid + (obase + static_cast<long long>(c0 + co0) * p.g.P) * ES;
+                        const long long cstride = static_cast<long long>(p.g.P) * ES;
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) {
+                            if (co0 + e < nco) {
+                                if constexpr (ES == 4) acc[e] += out_load<OUT_F32>(rp + e * cstride);
+                                else acc[e] += p.fmt == FMT_F16 ? out_load<OUT_F16>(rp + e * cstride)
+                                                                : out_load<OUT_BF16>(rp + e * cstride);
+                            }
+                        }
+                    }
                     for (int kw = 0; kw < tp.rc_kw; ++kw) {
                         uint32_t d[16];
                         ptx::tmem_ld_32x16(trow + kw * tp.rc_cpt + co0, d);
@@ -411,6 +424,10 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                             const float tv = __uint_as_float(__shfl_sync(0xffffffffu, d[e], src & 31));
                             acc[e] += in ? tv : 0.0f;
                         }
+                    }
+                    if (p.relu) {
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) acc[e] = fmaxf(acc[e], 0.0f);
                     }
                     if (produce && !((p.ablate & 16) && acc[0] != 123.456f)) {
                         char* optr = p.d + (obase + static_cast<long long>(c0 + co0) * p.g.P) * ES;
@@ -462,18 +479,22 @@ __global__ void __launch_bounds__(kTsThreads, 1)
             const uint32_t trow = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + buf * BN;
             char* optr = p.d + (rowbase + static_cast<long long>(n0) * colstride) * ES;
             const int ncols = min(BN, p.N - n0);
+            EpiExtra ex;
+            ex.relu = p.relu != 0;
+            ex.rdelta = p.resid ? p.resid - p.d : 0;
+            const float beta_e = p.resid ? 1.0f : beta;  // a residual takes the place of the beta term
             if (p.ablate & 32) {
             } else if constexpr (ES == 4) {
-                epilogue_dispatch<OUT_F32>(trow, ncols, optr, colstride * ES, row_ok, alpha, beta,
-                                           bias, lane, part);
+                epilogue_dispatch<OUT_F32>(trow, ncols, optr, colstride * ES, row_ok, alpha, beta_e,
+                                           bias, lane, part, false, ex);
             } else {
                 const bool pair_ok = pair_store_ok(optr, rowbase, colstride, row_ok, lane);
                 if (p.fmt == FMT_F16)
                     epilogue_dispatch<OUT_F16>(trow, ncols, optr, colstride * ES, row_ok, alpha,
-                                               beta, bias, lane, part, pair_ok);
+                                               beta_e, bias, lane, part, pair_ok, ex);
                 else
                     epilogue_dispatch<OUT_BF16>(trow, ncols, optr, colstride * ES, row_ok, alpha,
-                                                beta, bias, lane, part, pair_ok);
+                                                beta_e, bias, lane, part, pair_ok, ex);
             }
             ptx::tc_fence_before();
             ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));

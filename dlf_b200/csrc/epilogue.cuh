@@ -37,6 +37,14 @@ __device__ __forceinline__ float out_load(const char* ptr) {
     }
 }
 
+// Fused extras of the convolution epilogue: `rdelta` is the byte distance from an element of D to
+// the element of the residual tensor added to it (0: the beta term reads D itself), `relu` clamps
+// the result at zero before it is stored.
+struct EpiExtra {
+    long long rdelta = 0;
+    bool relu = false;
+};
+
 // One 32-column chunk. `ptr` addresses D(i, j0) for this lane's row i; consecutive columns are
 // `stride` bytes apart. `ncols` (1..32) columns of the chunk exist; `row_ok` says whether this
 // lane's row exists. `bias` addresses bias[j0] (storage type) and is only read when HAS_BIAS.
@@ -47,8 +55,10 @@ __device__ __forceinline__ float out_load(const char* ptr) {
 template <int OUT, bool HAS_BETA, bool HAS_BIAS>
 __device__ __forceinline__ void epilogue_chunk(const uint32_t (&v)[32], char* ptr, long long stride,
                                                int ncols, bool row_ok, float alpha, float beta,
-                                               const char* bias, int lane, bool pair_ok = false) {
+                                               const char* bias, int lane, bool pair_ok = false,
+                                               EpiExtra ex = EpiExtra()) {
     constexpr int OES = OUT == OUT_F32 ? 4 : 2;
+    const char* cptr = ptr + ex.rdelta;  // where the beta term is read
     float bv = 0.0f;
     if constexpr (HAS_BIAS) {
         if (lane < ncols) bv = out_load<OUT>(bias + lane * OES);
@@ -63,6 +73,10 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&v)[32], char* pt
                 if constexpr (HAS_BIAS) {
                     r0 += __shfl_sync(0xffffffffu, bv, jj);
                     r1 += __shfl_sync(0xffffffffu, bv, jj + 1);
+                }
+                if (ex.relu) {
+                    r0 = fmaxf(r0, 0.0f);
+                    r1 = fmaxf(r1, 0.0f);
                 }
                 const float got = __shfl_xor_sync(0xffffffffu, odd ? r0 : r1, 1);
                 // even lane: rows (i, i+1) of column jj; odd lane: rows (i-1, i) of column jj+1
@@ -87,7 +101,7 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&v)[32], char* pt
         if constexpr (HAS_BETA) {
             if (row_ok) {
 #pragma unroll
-                for (int jj = 0; jj < 32; ++jj) c[jj] = out_load<OUT>(ptr + jj * stride);
+                for (int jj = 0; jj < 32; ++jj) c[jj] = out_load<OUT>(cptr + jj * stride);
             } else {
 #pragma unroll
                 for (int jj = 0; jj < 32; ++jj) c[jj] = 0.0f;
@@ -98,6 +112,7 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&v)[32], char* pt
             float r = alpha * __uint_as_float(v[jj]);
             if constexpr (HAS_BETA) r += beta * c[jj];
             if constexpr (HAS_BIAS) r += __shfl_sync(0xffffffffu, bv, jj);
+            if (ex.relu) r = fmaxf(r, 0.0f);
             if (row_ok) out_store<OUT>(ptr + jj * stride, r);
         }
     } else {
@@ -106,9 +121,10 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&v)[32], char* pt
             float r = alpha * __uint_as_float(v[jj]);
             const bool ok = row_ok && jj < ncols;
             if constexpr (HAS_BETA) {
-                if (ok) r += beta * out_load<OUT>(ptr + jj * stride);
+                if (ok) r += beta * out_load<OUT>(cptr + jj * stride);
             }
             if constexpr (HAS_BIAS) r += __shfl_sync(0xffffffffu, bv, jj);
+            if (ex.relu) r = fmaxf(r, 0.0f);
             if (ok) out_store<OUT>(ptr + jj * stride, r);
         }
     }
@@ -134,7 +150,8 @@ template <int OUT, bool HAS_BETA, bool HAS_BIAS>
 __device__ __forceinline__ void epilogue_tile(uint32_t trow, int ncols_total, char* ptr,
                                               long long stride, bool row_ok, float alpha,
                                               float beta, const char* bias, int lane,
-                                              const float* part = nullptr, bool pair_ok = false) {
+                                              const float* part = nullptr, bool pair_ok = false,
+                                              EpiExtra ex = EpiExtra()) {
     constexpr int OES = OUT == OUT_F32 ? 4 : 2;
     for (int c0 = 0; c0 < ncols_total; c0 += 32) {
         uint32_t v[32];
@@ -147,7 +164,7 @@ __device__ __forceinline__ void epilogue_tile(uint32_t trow, int ncols_total, ch
         }
         const int nc = min(32, ncols_total - c0);
         epilogue_chunk<OUT, HAS_BETA, HAS_BIAS>(v, ptr + c0 * stride, stride, nc, row_ok, alpha,
-                                                beta, HAS_BIAS ? bias + c0 * OES : nullptr, lane, pair_ok);
+                                                beta, HAS_BIAS ? bias + c0 * OES : nullptr, lane, pair_ok, ex);
     }
 }
 
@@ -155,17 +172,18 @@ template <int OUT>
 __device__ __forceinline__ void epilogue_dispatch(uint32_t trow, int ncols_total, char* ptr,
                                                   long long stride, bool row_ok, float alpha,
                                                   float beta, const char* bias, int lane,
-                                                  const float* part = nullptr, bool pair_ok = false) {
+                                                  const float* part = nullptr, bool pair_ok = false,
+                                                  EpiExtra ex = EpiExtra()) {
     if (beta != 0.0f) {
         if (bias)
-            epilogue_tile<OUT, true, true>(trow, ncols_total, ptr, stride, row_ok, alpha, beta, bias, lane, part, pair_ok);
+            epilogue_tile<OUT, true, true>(trow, ncols_total, ptr, stride, row_ok, alpha, beta, bias, lane, part, pair_ok, ex);
         else
-            epilogue_tile<OUT, true, false>(trow, ncols_total, ptr, stride, row_ok, alpha, beta, bias, lane, part, pair_ok);
+            epilogue_tile<OUT, true, false>(trow, ncols_total, ptr, stride, row_ok, alpha, beta, bias, lane, part, pair_ok, ex);
     } else {
         if (bias)
-            epilogue_tile<OUT, false, true>(trow, ncols_total, ptr, stride, row_ok, alpha, beta, bias, lane, part, pair_ok);
+            epilogue_tile<OUT, false, true>(trow, ncols_total, ptr, stride, row_ok, alpha, beta, bias, lane, part, pair_ok, ex);
         else
-            epilogue_tile<OUT, false, false>(trow, ncols_total, ptr, stride, row_ok, alpha, beta, bias, lane, part, pair_ok);
+            epilogue_tile<OUT, false, false>(trow, ncols_total, ptr, stride, row_ok, alpha, beta, bias, lane, part, pair_ok, ex);
     }
 }
 

@@ -76,8 +76,14 @@ def _workspace(device, stream, nbytes):
 
 def conv2d(batches, channels, height, width, output_h, output_w, num_kernels, group, kernel_h,
            kernel_w, pad_top, pad_left, pad_bottom, pad_right, stride_h, stride_w, dilation_h,
-           dilation_w, im_buffer, kernel_buffer, result_buffer, queue=None, event=None, bias=None):
-    """NCHW cross-correlation into result_buffer (gpgpu::dnn::conv2d, gdnn.h:201-213)."""
+           dilation_w, im_buffer, kernel_buffer, result_buffer, queue=None, event=None, bias=None,
+           residual=None, activation=None):
+    """NCHW cross-correlation into result_buffer (gpgpu::dnn::conv2d, gdnn.h:201-213).
+
+    ``bias``, ``residual`` (a tensor shaped like the result, may be the result itself) and
+    ``activation`` (None or "relu") fuse what dlf's graph runtime runs as separate passes after
+    the convolution: the bias add of ConvOp (dlf/include/predict.h:1272-1281), the Add of a
+    residual connection and the Relu that follows it."""
     prec = precision_of(result_buffer)
     if im_buffer.dtype != result_buffer.dtype or kernel_buffer.dtype != result_buffer.dtype:
         raise BLASError(StatusCode.kInvalidValue)
@@ -93,26 +99,34 @@ def conv2d(batches, channels, height, width, output_h, output_w, num_kernels, gr
         raise BLASError(StatusCode.kInsufficientMemoryC)
     if bias is not None and bias.numel() < num_kernels:
         raise BLASError(StatusCode.kInvalidValue)
+    if residual is not None and (residual.dtype != result_buffer.dtype or
+                                 residual.numel() < batches * num_kernels * output_h * output_w):
+        raise BLASError(StatusCode.kInvalidValue)
+    if activation not in (None, "relu"):
+        raise BLASError(StatusCode.kInvalidValue)
     s, sp = _stream(queue)
     ws = _workspace(result_buffer.device, s, lib().dlf_b200_conv2d_workspace_bytes(
         int(prec), batches, channels, height, width, output_h, output_w, num_kernels, group,
         kernel_h, kernel_w))
     if event is not None:
         event.start.record(s)
-    rc = lib().dlf_b200_conv2d(
+    null = ctypes.c_void_p(0)
+    rc = lib().dlf_b200_conv2d_fused(
         int(prec), batches, channels, height, width, output_h, output_w, num_kernels, group,
         kernel_h, kernel_w, pad_top, pad_left, pad_bottom, pad_right, stride_h, stride_w,
         dilation_h, dilation_w, _ptr(im_buffer), _ptr(kernel_buffer),
-        _ptr(bias) if bias is not None else ctypes.c_void_p(0), _ptr(result_buffer),
-        ctypes.c_void_p(ws.data_ptr()), ws.numel(), sp)
+        _ptr(bias) if bias is not None else null,
+        _ptr(residual) if residual is not None else null, 1 if activation == "relu" else 0,
+        _ptr(result_buffer), ctypes.c_void_p(ws.data_ptr()), ws.numel(), sp)
     if event is not None:
         event.end.record(s)
     _check(rc)
 
 
-def conv2d_filter(X, W, Y, filt, bias=None, queue=None, event=None):
+def conv2d_filter(X, W, Y, filt, bias=None, queue=None, event=None, residual=None, activation=None):
     """dlf::dnn::conv2d(X, W, Y, filter) for device tensors (dlf/include/tensor/dnn_detail.h:154-166)."""
     conv2d(filt.batches, filt.channels, filt.height, filt.width, filt.output_h, filt.output_w,
            filt.num_kernels, filt.group, filt.kernel_h, filt.kernel_w, filt.pad_top,
            filt.pad_left, filt.pad_bottom, filt.pad_right, filt.stride_h, filt.stride_w,
-           filt.dilation_h, filt.dilation_w, X, W, Y, queue=queue, event=event, bias=bias)
+           filt.dilation_h, filt.dilation_w, X, W, Y, queue=queue, event=event, bias=bias,
+           residual=residual, activation=activation)

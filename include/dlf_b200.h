@@ -107,6 +107,23 @@ int dlf_b200_conv2d(int dtype, size_t batches, size_t channels, size_t height, s
                     size_t dilation_h, size_t dilation_w, const void* x, const void* w,
                     const void* bias, void* y, void* workspace, size_t workspace_bytes,
                     void* stream);
+/* Convolution with the operator-level fusion dlf's graph runtime applies around it: ConvOp is
+ * conv + bias (dlf/include/predict.h:1258-1286) and in ResNet-style graphs is followed by an Add
+ * of the block's input and a Relu, each a separate full pass over Y in the reference. Here
+ *     Y = act(conv2d(X, W) + bias + residual)
+ * in the convolution's epilogue. `residual` (NULL, or a tensor with Y's shape and layout; it may
+ * be Y itself) is read once per element before Y is written; `activation` is one of the values
+ * below. With residual == NULL and DLF_B200_ACT_NONE this is dlf_b200_conv2d. */
+#define DLF_B200_ACT_NONE 0
+#define DLF_B200_ACT_RELU 1
+int dlf_b200_conv2d_fused(int dtype, size_t batches, size_t channels, size_t height, size_t width,
+                          size_t output_h, size_t output_w, size_t num_kernels, size_t group,
+                          size_t kernel_h, size_t kernel_w, size_t pad_top, size_t pad_left,
+                          size_t pad_bottom, size_t pad_right, size_t stride_h, size_t stride_w,
+                          size_t dilation_h, size_t dilation_w, const void* x, const void* w,
+                          const void* bias, const void* residual, int activation, void* y,
+                          void* workspace, size_t workspace_bytes, void* stream);
+
 size_t dlf_b200_conv2d_workspace_bytes(int dtype, size_t batches, size_t channels, size_t height,
                                        size_t width, size_t output_h, size_t output_w,
                                        size_t num_kernels, size_t group, size_t kernel_h,

@@ -274,8 +274,10 @@ void gemmBatched(const Layout layout, const Transpose a_transpose, const Transpo
 // ---------------------------------------------------------------------------- dnn
 namespace dnn {
 
-// gpgpu::dnn::conv2d (gpgpu/include/gdnn.h:201-213). `bias` is an addition (default: none): the
-// reference adds it in a separate pass (dlf/include/predict.h:1272-1281).
+// gpgpu::dnn::conv2d (gpgpu/include/gdnn.h:201-213). `bias`, `residual` and `activation` are
+// additions (default: none): the reference adds the bias in a separate pass
+// (dlf/include/predict.h:1272-1281) and runs the residual Add (predict.h:928-960) and the Relu
+// (predict.h:776-784) as operators of their own; here they are fused into the epilogue.
 template <typename T>
 void conv2d(const size_t batches, const size_t channels,
             const size_t height, const size_t width,
@@ -289,7 +291,8 @@ void conv2d(const size_t batches, const size_t channels,
             const Buffer<T>& im_buffer, const Buffer<T>& kernel_buffer,
             Buffer<T>& result_buffer,
             const Queue& queue = current::queue(), Event* event = nullptr,
-            const Buffer<T>* bias = nullptr) {
+            const Buffer<T>* bias = nullptr, const Buffer<T>* residual = nullptr,
+            const int activation = DLF_B200_ACT_NONE) {
     using blas::BLASError;
     using blas::StatusCode;
     if (group == 0 || channels % group != 0 || num_kernels % group != 0) throw BLASError(StatusCode::kInvalidDimension);
@@ -297,13 +300,16 @@ void conv2d(const size_t batches, const size_t channels,
     if (kernel_buffer.size() < num_kernels * (channels / group) * kernel_h * kernel_w) throw BLASError(StatusCode::kInsufficientMemoryB);
     if (result_buffer.size() < batches * num_kernels * output_h * output_w) throw BLASError(StatusCode::kInsufficientMemoryC);
     if (bias && bias->size() < num_kernels) throw BLASError(StatusCode::kInvalidValue);
+    if (residual && residual->size() < batches * num_kernels * output_h * output_w) throw BLASError(StatusCode::kInvalidValue);
     blas::detail::EventScope scope(queue, event);
-    blas::detail::raise(dlf_b200_conv2d(blas::PrecisionOf<T>::value, batches, channels, height, width, output_h,
-                                        output_w, num_kernels, group, kernel_h, kernel_w, pad_top, pad_left,
-                                        pad_bottom, pad_right, stride_h, stride_w, dilation_h, dilation_w,
-                                        im_buffer.unwrap(), kernel_buffer.unwrap(), bias ? bias->unwrap() : nullptr,
-                                        result_buffer.unwrap(), nullptr, 0, queue.unwrap()),
-                        "dlf_b200_conv2d");
+    blas::detail::raise(dlf_b200_conv2d_fused(blas::PrecisionOf<T>::value, batches, channels, height, width,
+                                              output_h, output_w, num_kernels, group, kernel_h, kernel_w, pad_top,
+                                              pad_left, pad_bottom, pad_right, stride_h, stride_w, dilation_h,
+                                              dilation_w, im_buffer.unwrap(), kernel_buffer.unwrap(),
+                                              bias ? bias->unwrap() : nullptr,
+                                              residual ? residual->unwrap() : nullptr, activation,
+                                              result_buffer.unwrap(), nullptr, 0, queue.unwrap()),
+                        "dlf_b200_conv2d_fused");
 }
 
 }  // namespace dnn

@@ -148,6 +148,19 @@ def conv2d(X, W, group=1, pads=(0, 0, 0, 0), strides=(1, 1), dilations=(1, 1), b
     return Y
 
 
+def conv2d_fused(X, W, residual=None, relu=False, **kw):
+    """The operator chain dlf's graph runtime evaluates around a convolution, as separate passes:
+    ConvOp (conv + bias, dlf/include/predict.h:1258-1286), then Add of a residual tensor
+    (BinaryOp<xfn::plus>, predict.h:928-960), then Relu (ReluOp, predict.h:776-784;
+    xfn::relu = max(0, x), dlf/include/tensor/xfn.h:588-591). Every pass rounds to float32."""
+    Y = conv2d(X, W, **kw)
+    if residual is not None:
+        Y = (Y + np.asarray(residual, dtype=np.float32)).astype(np.float32)
+    if relu:
+        Y = np.maximum(np.float32(0), Y)
+    return Y
+
+
 # ---------------------------------------------------------------------------------------------
 # Tuned host BLAS for the timed CPU baseline: the reference calls cblas_sgemm of whatever BLAS it
 # was linked with (MKL in its Dockerfile). On this box the closest stand-in is the OpenBLAS that

@@ -79,6 +79,15 @@ static void conv_bias_golden() {
     dnn::conv2d<float>(1, 1, 5, 5, 5, 5, 1, 1, 3, 3, 1, 1, 1, 1, 1, 1, 1, 1, dX, dW, dY, current::queue(), nullptr,
                        &dBias);
     CHECK(host(dY) == Y);
+
+    // fused: relu(conv + bias + residual) with residual = -60 everywhere
+    std::vector<float> R(25, -60.0f), Yf(25);
+    for (int i = 0; i < 25; ++i) Yf[i] = Y[i] - 60.0f > 0.0f ? Y[i] - 60.0f : 0.0f;
+    auto dR = dev(R);
+    Buffer<float> dY2(25);
+    dnn::conv2d<float>(1, 1, 5, 5, 5, 5, 1, 1, 3, 3, 1, 1, 1, 1, 1, 1, 1, 1, dX, dW, dY2, current::queue(), nullptr,
+                       &dBias, &dR, DLF_B200_ACT_RELU);
+    CHECK(host(dY2) == Yf);
 }
 
 static void batched() {

@@ -515,6 +515,59 @@ def test_conv2d_pointwise_table_lookup_matches_affine(lib, dtype):
         assert torch.equal(outs[0], outs[1]), case
 
 
+FUSED_CASES = [
+    CONV_CASES[0],    # row form 3x3
+    CONV_CASES[3],    # 1x1 with aligned planes: TMA-fed GEMM route, TMA-store epilogue
+    CONV_CASES[17],   # 1x1 14x14: affine gather, paired stores
+    CONV_CASES[14],   # implicit im2col (dilation_w 2), chunked fp32
+    CONV_CASES[7],    # groups, tiles straddle images
+    CONV_CASES[18],   # strided row form
+    (2, 32, 8, 16, 300, 1, 1, (0, 0, 0, 0), (1, 1), (1, 1), 1),  # TMA route, ragged last column block
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("case", FUSED_CASES, ids=lambda c: "x".join(map(str, c[:7])))
+def test_conv2d_fused_residual_relu(lib, case, dtype):
+    """Y = relu(conv(X, W) + bias + R) in one launch, on every epilogue of the library, against
+    the oracle's conv -> bias -> Add -> Relu chain; also each part alone, and R aliasing Y."""
+    from dlf_b200 import gdnn
+    N, C, H, W, Co, KH, KW, pads, strides, dil, group = case
+    rng = np.random.default_rng(23)
+    Xh = _round_to(rng.normal(size=(N, C, H, W)).astype(np.float32), dtype)
+    Wh = _round_to((np.sqrt(2.0 / (C // group * KH * KW)) * rng.normal(size=(Co, C // group, KH, KW))).astype(np.float32), dtype)
+    bh = _round_to(rng.uniform(-0.1, 0.1, Co).astype(np.float32), dtype)
+    X, Wt, b = (torch.from_numpy(a).to(dtype).cuda() for a in (Xh, Wh, bh))
+    filt = gdnn.Filter2D(X.shape, Wt.shape, group).pads(*pads).strides(*strides).dilations(*dil)
+    Rh = _round_to(rng.normal(size=tuple(filt.output_shape())).astype(np.float32), dtype)
+    R = torch.from_numpy(Rh).to(dtype).cuda()
+    kw = dict(group=group, pads=pads, strides=strides, dilations=dil, wide=True)
+
+    def check(got, ref):
+        got = got.float().cpu().numpy()
+        if dtype == torch.float32:
+            assert rel_fro(got, ref) <= FP32_TOL
+        else:
+            assert max_rel(got, ref) <= HALF_TOL
+
+    for use_bias, use_res, relu in ((True, True, True), (False, False, True), (False, True, False)):
+        Y = torch.full(filt.output_shape(), float("nan"), dtype=dtype, device="cuda")
+        gdnn.conv2d_filter(X, Wt, Y, filt, bias=b if use_bias else None, residual=R if use_res else None,
+                           activation="relu" if relu else None)
+        ref = oracle.conv2d_fused(Xh, Wh, residual=Rh if use_res else None, relu=relu,
+                                  bias=bh if use_bias else None, **kw)
+        check(Y, ref)
+        if relu:
+            assert float(Y.float().min()) >= 0.0
+    # in place: Y holds the residual on entry
+    Y = R.clone()
+    gdnn.conv2d_filter(X, Wt, Y, filt, bias=b, residual=Y, activation="relu")
+    check(Y, oracle.conv2d_fused(Xh, Wh, residual=Rh, relu=True, bias=bh, **kw))
+    assert lib.device_status() == 0
+    with pytest.raises(_gb().BLASError):
+        gdnn.conv2d_filter(X, Wt, Y, filt, activation="gelu")
+
+
 @pytest.mark.parametrize("path", [5, 0x8005, 0x8000])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
 def test_conv2d_strided_row_form_variants(lib, path, dtype):
