@@ -348,7 +348,8 @@ def run_extra(w, device, peaks, steps, warmup):
             "frac_of_measured_tensor_peak": round(tf / w.tensor_peak(peaks), 4),
             "frac_of_nominal_tensor_peak": round(tf / NOMINAL[w.dtype], 4),
             "hbm_gbs_algorithmic": round(w.bytes / sec / 1e9, 1),
-            "frac_of_measured_hbm": round(w.bytes / sec / 1e9 / peaks["hbm_gbs"], 4)}
+            "frac_of_measured_hbm": round(w.bytes / sec / 1e9 / peaks["hbm_gbs"], 4),
+            "out_gbs": round(getattr(w, "out_bytes", 0) / sec / 1e9, 1)}
 
 
 def resnet_sweep(device, peaks, batch, reps):
@@ -436,7 +437,13 @@ def main():
                                             beta=0.5, dist="uniform"),
         "batched_c4_a": lambda: GemmWorkload("bgemm_f16_b1024_512x512x64", "f16", 512, 512, 64, batch=1024, alpha=0.125),
         "batched_c4_b": lambda: GemmWorkload("bgemm_f16_b1024_512x64x512", "f16", 512, 64, 512, batch=1024, alpha=0.125),
+        "fc_c3": lambda: GemmWorkload("resnet50_fc_f16_256x1000x2048", "f16", 256, 1000, 2048),
     }
+    for tag, ta, tb in (("tn", True, False), ("nt", False, True), ("tt", True, True)):
+        table["batched_c4_a_" + tag] = (lambda tag=tag, ta=ta, tb=tb: GemmWorkload(
+            "bgemm_f16_b1024_512x512x64_" + tag, "f16", 512, 512, 64, batch=1024, ta=ta, tb=tb, alpha=0.125))
+        table["batched_c4_b_" + tag] = (lambda tag=tag, ta=ta, tb=tb: GemmWorkload(
+            "bgemm_f16_b1024_512x64x512_" + tag, "f16", 512, 64, 512, batch=1024, ta=ta, tb=tb, alpha=0.125))
     w = table[args.workload]()
     sets = w.sets_needed()
     # a single (unbatched) GEMM is sharded by rows of C with an all-gather: strong scaling, and
@@ -532,8 +539,18 @@ def main():
         extras = {}
         del w
         torch.cuda.empty_cache()
+        try:  # write-only HBM rate (memset of 1 GiB): the roof of the output-dominated workloads
+            z = torch.empty(1 << 30, dtype=torch.uint8, device=device)
+            ms, _, _ = time_steps(lambda i: z.zero_(), 10, 3, 1)
+            extras["hbm_write_gbs_memset"] = round((1 << 30) * 10 / (ms / 1e3) / 1e9, 1)
+            del z
+            torch.cuda.empty_cache()
+        except Exception as e:
+            extras["hbm_write_gbs_memset"] = {"error": repr(e)[:200]}
         for key, reps in (("gemm_f16_4096", 200), ("sgemm_1024", 500), ("batched_c4_a", 100), ("batched_c4_b", 100),
-                          ("sgemm_16384", 5)):
+                          ("batched_c4_a_tn", 50), ("batched_c4_a_nt", 50), ("batched_c4_a_tt", 50),
+                          ("batched_c4_b_tn", 50), ("batched_c4_b_nt", 50), ("batched_c4_b_tt", 50),
+                          ("fc_c3", 200), ("sgemm_16384", 5)):
             try:
                 ww = table[key]()
                 extras[ww.name] = run_extra(ww, device, peaks, reps, 5)

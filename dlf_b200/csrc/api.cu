@@ -447,10 +447,22 @@ int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
     }
 
     const unsigned grid = static_cast<unsigned>(total < st.num_sms ? total : st.num_sms);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(kTsThreads, 1, 1);
+    cfg.dynamicSmemBytes = dyn_smem;
+    cfg.stream = stream;
+    // after a packing launch: programmatic dependent launch, so that this kernel's prologue and
+    // activation gather overlap the packing grid (only its filter loader waits for that grid)
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = (tp.b_packed != nullptr && !(g_force_generic.load() & 0x40000000)) ? 1 : 0;
     if (q.es == 2)
-        contraction_ts_kernel<2><<<grid, kTsThreads, dyn_smem, stream>>>(tp, tm_b);
+        CUDA_TRY(cudaLaunchKernelEx(&cfg, contraction_ts_kernel<2>, tp, tm_b));
     else
-        contraction_ts_kernel<4><<<grid, kTsThreads, dyn_smem, stream>>>(tp, tm_b);
+        CUDA_TRY(cudaLaunchKernelEx(&cfg, contraction_ts_kernel<4>, tp, tm_b));
     g_launches.fetch_add(1);
     CUDA_TRY(cudaGetLastError());
     return kSuccess;

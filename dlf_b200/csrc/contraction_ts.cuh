@@ -193,6 +193,10 @@ __global__ void pack_weights_kernel(const TsParams tp, unsigned char* out, long 
     const int BN = p.BN;
     const int num_kb = (p.K + BK - 1) / BK;
     const long long stage_bytes = static_cast<long long>(BN) * 128 * (ES == 4 ? 2 : 1);
+    // the contraction kernel is launched as a programmatic dependent of this grid: let it start
+    // (prologue, activation gather) while the filter bank is still being packed; its filter
+    // loader waits for this grid's completion (griddepcontrol.wait) before it reads `out`
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     for (long long id = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; id < total_chunks;
          id += static_cast<long long>(gridDim.x) * blockDim.x) {
         const int c = static_cast<int>(id & 7);
@@ -792,6 +796,8 @@ __global__ void __launch_bounds__(kTsThreads, 1)
             // stage images were prepared in global memory: one thread streams them in with bulk
             // copies, the other loader threads have nothing to do
             if (lt == 0) {
+                // the packing grid launched just before this one must have completed
+                asm volatile("griddepcontrol.wait;" ::: "memory");
                 for (int t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x) {
                     int b, m0, n0;
                     decode_tile(p, t, b, m0, n0);
