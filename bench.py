@@ -372,6 +372,31 @@ def resnet_sweep(device, peaks, batch, reps):
             "frac_of_nominal_tensor_peak": round(tf / NOMINAL["f16"], 4), "layers": rows}
 
 
+def pooling_extras(device, peaks):
+    """The two pooling layers of ResNet-50 at batch 256, fp16: HBM-bound, reported against the
+    measured copy bandwidth (bytes = input read once + output written once)."""
+    from dlf_b200 import gdnn
+    out = {}
+    for name, shape, k, s, p, kind in (("maxpool_3x3_s2_64x112x112", (256, 64, 112, 112), 3, 2, 1, "max"),
+                                       ("global_avgpool_2048x7x7", (256, 2048, 7, 7), 7, 7, 0, "avg")):
+        X = [torch.randn(shape, device=device).abs().half() for _ in range(2)]
+        f = gdnn.Filter2D(shape, k, k).pads(p, p).strides(s, s)
+        Y = [torch.empty((shape[0], shape[1], f.output_h, f.output_w), dtype=torch.float16, device=device)
+             for _ in range(2)]
+        if kind == "max":
+            fn = lambda i: gdnn.max_pooling(X[i % 2], Y[i % 2], f)
+        else:
+            fn = lambda i: gdnn.average_pooling(X[i % 2], Y[i % 2], f, False)
+        ms, _, _ = time_steps(fn, 50, 5, 1)
+        sec = ms / 1e3 / 50
+        nbytes = 2 * (X[0].numel() + Y[0].numel())
+        out[name] = {"us_per_step": round(sec * 1e6, 2), "hbm_gbs_algorithmic": round(nbytes / sec / 1e9, 1),
+                     "frac_of_measured_hbm": round(nbytes / sec / 1e9 / peaks["hbm_gbs"], 4)}
+        del X, Y
+        torch.cuda.empty_cache()
+    return out
+
+
 def reference_arm(args, rank):
     """--impl reference: the reference's CPU implementation of the path (oracle port; the
     reference itself needs TBB + MKL, which are absent) timed on the host cores."""
@@ -562,6 +587,10 @@ def main():
             extras["resnet50_v1_convs_f16_b256"] = resnet_sweep(device, peaks, 256, 10)
         except Exception as e:
             extras["resnet50_v1_convs_f16_b256"] = {"error": repr(e)[:200]}
+        try:
+            extras["pooling_f16_b256"] = pooling_extras(device, peaks)
+        except Exception as e:
+            extras["pooling_f16_b256"] = {"error": repr(e)[:200]}
         extras["device_status"] = dlf_b200.device_status()
         line["workloads"] = extras
 

@@ -60,6 +60,10 @@ def _declare(L):
     L.dlf_b200_conv2d_fused.restype = c_int
     L.dlf_b200_conv2d_fused.argtypes = [c_int] + [c_size] * 18 + [
         c_void, c_void, c_void, c_void, c_int, c_void, c_void, c_size, c_void]
+    L.dlf_b200_maxpool.restype = c_int
+    L.dlf_b200_maxpool.argtypes = [c_int] + [c_size] * 16 + [c_void, c_void, c_void]
+    L.dlf_b200_avgpool.restype = c_int
+    L.dlf_b200_avgpool.argtypes = [c_int] + [c_size] * 16 + [c_int, c_void, c_void, c_void]
     L.dlf_b200_conv2d_workspace_bytes.restype = c_size
     L.dlf_b200_conv2d_workspace_bytes.argtypes = [c_int] + [c_size] * 10
     L.dlf_b200_status_string.restype = ctypes.c_char_p
@@ -81,6 +85,8 @@ EXPORTED_SYMBOLS = (
     "dlf_b200_conv2d",
     "dlf_b200_conv2d_fused",
     "dlf_b200_conv2d_workspace_bytes",
+    "dlf_b200_maxpool",
+    "dlf_b200_avgpool",
     "dlf_b200_status_string",
     "dlf_b200_device_status",
     "dlf_b200_set_tuning",

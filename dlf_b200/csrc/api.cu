@@ -21,6 +21,7 @@
 #include "../../include/dlf_b200.h"
 #include "contraction.cuh"
 #include "contraction_ts.cuh"
+#include "pooling.cuh"
 
 using namespace dlfb200;
 
@@ -1055,6 +1056,132 @@ int dlf_b200_conv2d(int dtype, size_t batches, size_t channels, size_t height, s
                                  group, kernel_h, kernel_w, pad_top, pad_left, pad_bottom, pad_right,
                                  stride_h, stride_w, dilation_h, dilation_w, x, w, bias, nullptr,
                                  DLF_B200_ACT_NONE, y, workspace, workspace_bytes, stream);
+}
+
+namespace {
+
+int launch_pool(int dtype, int mode, int count_include_pad, size_t batches, size_t channels, size_t height,
+                size_t width, size_t output_h, size_t output_w, size_t kernel_h, size_t kernel_w, size_t pad_top,
+                size_t pad_left, size_t stride_h, size_t stride_w, size_t dilation_h, size_t dilation_w,
+                const void* x, void* y, void* stream) {
+    int fmt = 0, es = 0;
+    if (!dtype_info(dtype, fmt, es)) return kNotImplemented;
+    if (batches == 0 || channels == 0 || height == 0 || width == 0 || output_h == 0 || output_w == 0 ||
+        kernel_h == 0 || kernel_w == 0 || stride_h == 0 || stride_w == 0 || dilation_h == 0 || dilation_w == 0)
+        return kInvalidDimension;
+    if (x == nullptr || y == nullptr) return kInvalidValue;
+    const size_t lim = 1u << 30;
+    if (height >= lim || width >= lim || output_h >= lim || output_w >= lim || kernel_h >= lim || kernel_w >= lim ||
+        pad_top >= lim || pad_left >= lim || stride_h >= lim || stride_w >= lim || dilation_h >= lim ||
+        dilation_w >= lim || static_cast<long long>(height) * width >= INT_MAX ||
+        static_cast<long long>(output_h) * output_w >= INT_MAX)
+        return kInvalidDimension;
+    DeviceState* st = nullptr;
+    int rc = ensure_device(&st);
+    if (rc != kSuccess) return rc;
+    PoolParams p{};
+    p.planes = static_cast<long long>(batches) * static_cast<long long>(channels);
+    p.H = static_cast<int>(height);
+    p.W = static_cast<int>(width);
+    p.OH = static_cast<int>(output_h);
+    p.OW = static_cast<int>(output_w);
+    p.KH = static_cast<int>(kernel_h);
+    p.KW = static_cast<int>(kernel_w);
+    p.pad_t = static_cast<int>(pad_top);
+    p.pad_l = static_cast<int>(pad_left);
+    p.sh = static_cast<int>(stride_h);
+    p.sw = static_cast<int>(stride_w);
+    p.dh = static_cast<int>(dilation_h);
+    p.dw = static_cast<int>(dilation_w);
+    p.mode = mode;
+    p.count_include_pad = count_include_pad;
+    p.x = static_cast<const char*>(x);
+    p.y = static_cast<char*>(y);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // the whole plane as one unpadded, undilated window: global pooling, one warp per plane
+    const bool whole_plane = output_h == 1 && output_w == 1 && kernel_h == height && kernel_w == width &&
+                             pad_top == 0 && pad_left == 0 && dilation_h == 1 && dilation_w == 1 &&
+                             !((g_force_generic.load() >> 16) & 0x100);
+    constexpr int kPoolSmem = 48 * 1024;  // static limit: no opt-in needed
+    const long long plane_bytes = static_cast<long long>(height) * width * es;
+    if (whole_plane && plane_bytes * 8 <= kPoolSmem) {
+        // small planes: 256 / group planes per block staged through shared memory
+        int group = 1;
+        while ((256 / group) * plane_bytes > kPoolSmem) group *= 2;
+        p.group = group;
+        const long long ppb = 256 / group;
+        const long long blocks = (p.planes + ppb - 1) / ppb;
+        const unsigned grid = static_cast<unsigned>(std::min<long long>(blocks, static_cast<long long>(st->num_sms) * 8));
+        const size_t smem = static_cast<size_t>(ppb * plane_bytes + 16);
+        if (fmt == FMT_F32) pool_planes_kernel<float><<<grid, 256, smem, s>>>(p);
+        else if (fmt == FMT_F16) pool_planes_kernel<__half><<<grid, 256, smem, s>>>(p);
+        else pool_planes_kernel<__nv_bfloat16><<<grid, 256, smem, s>>>(p);
+    } else if (whole_plane) {
+        const long long blocks = (p.planes + 7) / 8;  // eight warps per block
+        const unsigned grid = static_cast<unsigned>(std::min<long long>(blocks, static_cast<long long>(st->num_sms) * 16));
+        if (fmt == FMT_F32) pool_plane_kernel<float><<<grid, 256, 0, s>>>(p);
+        else if (fmt == FMT_F16) pool_plane_kernel<__half><<<grid, 256, 0, s>>>(p);
+        else pool_plane_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(p);
+    } else {
+        // rows of the window of one output row, and how many output rows a block can take
+        const long long row_bytes = static_cast<long long>(width) * es;
+        const long long win_rows = static_cast<long long>(kernel_h - 1) * dilation_h + 1;
+        long long toh = 0;
+        if (win_rows * row_bytes <= kPoolSmem && !((g_force_generic.load() >> 16) & 0x100)) {
+            toh = (kPoolSmem / row_bytes - win_rows) / static_cast<long long>(stride_h) + 1;
+            // about 24 KB per block: eight blocks per SM keep ~200 KB of loads in flight
+            toh = std::min<long long>(toh, std::max<long long>(1, (24 * 1024 / row_bytes - win_rows) / static_cast<long long>(stride_h) + 1));
+            toh = std::min<long long>(toh, static_cast<long long>(output_h));
+        }
+        if (toh >= 1) {
+            p.toh = static_cast<int>(toh);
+            p.ih_rows = static_cast<int>((toh - 1) * stride_h + win_rows);
+            const long long blocks = p.planes * ((static_cast<long long>(output_h) + toh - 1) / toh);
+            const unsigned grid = static_cast<unsigned>(std::min<long long>(blocks, static_cast<long long>(st->num_sms) * 32));
+            const size_t smem = static_cast<size_t>(p.ih_rows * row_bytes);
+            const int k = (kernel_h == kernel_w && (kernel_h == 2 || kernel_h == 3) && dilation_h == 1 && dilation_w == 1)
+                              ? static_cast<int>(kernel_h) : 0;
+#define DLF_POOL_ROWS(T)                                                              \
+    do {                                                                              \
+        if (k == 3) pool2d_rows_kernel<T, 3><<<grid, 256, smem, s>>>(p);              \
+        else if (k == 2) pool2d_rows_kernel<T, 2><<<grid, 256, smem, s>>>(p);         \
+        else pool2d_rows_kernel<T, 0><<<grid, 256, smem, s>>>(p);                     \
+    } while (0)
+            if (fmt == FMT_F32) DLF_POOL_ROWS(float);
+            else if (fmt == FMT_F16) DLF_POOL_ROWS(__half);
+            else DLF_POOL_ROWS(__nv_bfloat16);
+#undef DLF_POOL_ROWS
+        } else {
+            const long long total = p.planes * output_h * output_w;
+            const long long blocks = (total + 255) / 256;
+            const unsigned grid = static_cast<unsigned>(std::min<long long>(blocks, static_cast<long long>(st->num_sms) * 32));
+            if (fmt == FMT_F32) pool2d_kernel<float><<<grid, 256, 0, s>>>(p);
+            else if (fmt == FMT_F16) pool2d_kernel<__half><<<grid, 256, 0, s>>>(p);
+            else pool2d_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(p);
+        }
+    }
+    g_launches.fetch_add(1);
+    CUDA_TRY(cudaGetLastError());
+    return kSuccess;
+}
+
+}  // namespace
+
+int dlf_b200_maxpool(int dtype, size_t batches, size_t channels, size_t height, size_t width, size_t output_h,
+                     size_t output_w, size_t kernel_h, size_t kernel_w, size_t pad_top, size_t pad_left,
+                     size_t, size_t, size_t stride_h, size_t stride_w, size_t dilation_h, size_t dilation_w,
+                     const void* x, void* y, void* stream) {
+    return launch_pool(dtype, 0, 0, batches, channels, height, width, output_h, output_w, kernel_h, kernel_w,
+                       pad_top, pad_left, stride_h, stride_w, dilation_h, dilation_w, x, y, stream);
+}
+
+int dlf_b200_avgpool(int dtype, size_t batches, size_t channels, size_t height, size_t width, size_t output_h,
+                     size_t output_w, size_t kernel_h, size_t kernel_w, size_t pad_top, size_t pad_left,
+                     size_t, size_t, size_t stride_h, size_t stride_w, size_t dilation_h, size_t dilation_w,
+                     int count_include_pad, const void* x, void* y, void* stream) {
+    return launch_pool(dtype, 1, count_include_pad ? 1 : 0, batches, channels, height, width, output_h, output_w,
+                       kernel_h, kernel_w, pad_top, pad_left, stride_h, stride_w, dilation_h, dilation_w, x, y,
+                       stream);
 }
 
 const char* dlf_b200_status_string(int status) {

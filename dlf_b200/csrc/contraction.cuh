@@ -105,7 +105,9 @@ struct Params {
     int ablate;  // measurement aid (tuning flags >> 16; results are then meaningless):
                  // 1 A producer skips its loads, 2 B loaders skip theirs, 4 producers skip the TMEM
                  // stores, 8 / 16 row-form epilogue skips its body / its stores, 32 the plain
-                 // epilogue of the TMEM-operand kernel is skipped
+                 // epilogue of the TMEM-operand kernel is skipped, 0x100 pooling always takes the
+                 // plain one-thread-per-output kernel (results stay valid), 0x4000 no programmatic
+                 // dependent launch after the filter-packing grid (results stay valid)
 };
 
 struct PixelEntry {  // one output pixel of the current tile (implicit im2col operand)

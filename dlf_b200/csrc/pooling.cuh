@@ -1,0 +1,274 @@
+// NCHW pooling (max / average) and the plane reduction used for global pooling.
+//
+// These are HBM-bound: every input element is needed once (windows overlap only inside a few
+// rows, which the L1/L2 absorb) and every output element is written once. One thread produces
+// `VEC` horizontally adjacent outputs of one plane row so that 16-bit outputs leave as one
+// 32-bit store; threads of a warp cover consecutive outputs, so loads of a tap are consecutive
+// (stride_w apart) addresses. Arithmetic follows dlf's CPU pooling
+// (dlf/include/tensor/dnn_detail.h:172-227): max starts from the type's lowest value, the average
+// divides the sum of the taps inside the image by their count, or by kernel_h*kernel_w with
+// count_include_pad; a window that lies entirely in the padding gives lowest / 0/0 as there.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <cfloat>
+#include <cstdint>
+
+namespace dlfb200 {
+
+struct PoolParams {
+    long long planes;  // batches * channels
+    int toh;           // pool2d_rows_kernel: output rows per block
+    int ih_rows;       // ... and input rows staged for them
+    int group;         // pool_planes_kernel: threads per plane (power of two)
+    int H, W, OH, OW, KH, KW, pad_t, pad_l, sh, sw, dh, dw;
+    int mode;               // 0 max, 1 average
+    int count_include_pad;  // average only
+    const char* x;
+    char* y;
+};
+
+template <typename T>
+struct PoolType;
+template <>
+struct PoolType<float> {
+    static __device__ __forceinline__ float load(const char* p, long long i) { return reinterpret_cast<const float*>(p)[i]; }
+    static __device__ __forceinline__ void store(char* p, long long i, float v) { reinterpret_cast<float*>(p)[i] = v; }
+    static __device__ __forceinline__ float lowest() { return -FLT_MAX; }
+    static __device__ __forceinline__ float round(float v) { return v; }
+};
+template <>
+struct PoolType<__half> {
+    static __device__ __forceinline__ float load(const char* p, long long i) { return __half2float(reinterpret_cast<const __half*>(p)[i]); }
+    static __device__ __forceinline__ void store(char* p, long long i, float v) { reinterpret_cast<__half*>(p)[i] = __float2half_rn(v); }
+    static __device__ __forceinline__ float lowest() { return -65504.0f; }
+    static __device__ __forceinline__ float round(float v) { return __half2float(__float2half_rn(v)); }
+};
+template <>
+struct PoolType<__nv_bfloat16> {
+    static __device__ __forceinline__ float load(const char* p, long long i) { return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]); }
+    static __device__ __forceinline__ void store(char* p, long long i, float v) { reinterpret_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v); }
+    static __device__ __forceinline__ float lowest() { return -3.38953139e38f; }
+    static __device__ __forceinline__ float round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+};
+
+// One thread = one output element; consecutive threads = consecutive ow, then oh, then plane.
+template <typename T>
+__global__ void __launch_bounds__(256) pool2d_kernel(const PoolParams p) {
+    const long long per_plane = static_cast<long long>(p.OH) * p.OW;
+    const long long total = p.planes * per_plane;
+    for (long long o = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; o < total;
+         o += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const long long plane = o / per_plane;
+        const int rem = static_cast<int>(o - plane * per_plane);
+        const int oh = rem / p.OW;
+        const int ow = rem - oh * p.OW;
+        const long long xbase = plane * p.H * p.W;
+        const int ih0 = oh * p.sh - p.pad_t;
+        const int iw0 = ow * p.sw - p.pad_l;
+        float acc = p.mode == 0 ? PoolType<T>::lowest() : 0.0f;
+        int count = 0;
+        for (int kh = 0; kh < p.KH; ++kh) {
+            const int ih = ih0 + kh * p.dh;
+            if (static_cast<unsigned>(ih) >= static_cast<unsigned>(p.H)) continue;
+            const long long row = xbase + static_cast<long long>(ih) * p.W;
+            for (int kw = 0; kw < p.KW; ++kw) {
+                const int iw = iw0 + kw * p.dw;
+                if (static_cast<unsigned>(iw) >= static_cast<unsigned>(p.W)) continue;
+                const float v = PoolType<T>::load(p.x, row + iw);
+                acc = p.mode == 0 ? fmaxf(acc, v) : acc + v;  // fp32 sum, taps in (kh, kw) order
+                ++count;
+            }
+        }
+        if (p.mode == 1) {
+            if (p.count_include_pad) count = p.KH * p.KW;
+            acc = acc / static_cast<float>(count);
+        }
+        PoolType<T>::store(p.y, o, acc);
+    }
+}
+
+// Windowed pooling through shared memory. A block owns `toh` consecutive output rows of one
+// plane: the input rows they need are copied in once, with 16-byte loads when the rows are
+// 16-byte multiples (every row then starts aligned), and all taps are read from shared memory.
+// HBM sees each input row once per block (rows shared by two neighbouring blocks twice).
+template <typename T, int K>
+__global__ void __launch_bounds__(256) pool2d_rows_kernel(const PoolParams p) {
+    extern __shared__ __align__(16) unsigned char pool_smem[];
+    constexpr int ES = sizeof(T);
+    const int tiles = (p.OH + p.toh - 1) / p.toh;
+    const long long nblocks = p.planes * tiles;
+    const int row_bytes = p.W * ES;
+    const bool vec = (row_bytes & 15) == 0 && (reinterpret_cast<uintptr_t>(p.x) & 15u) == 0;
+    for (long long blk = blockIdx.x; blk < nblocks; blk += gridDim.x) {
+        const long long plane = blk / tiles;
+        const int oh0 = static_cast<int>(blk - plane * tiles) * p.toh;
+        const int ih_lo = oh0 * p.sh - p.pad_t;
+        const char* xp = p.x + plane * p.H * static_cast<long long>(row_bytes);
+        __syncthreads();  // the previous tile's readers are done
+        if (vec) {
+            const int cpr = row_bytes >> 4;  // 16-byte chunks per row
+            for (int id = threadIdx.x; id < p.ih_rows * cpr; id += blockDim.x) {
+                const int r = id / cpr;
+                const int c = id - r * cpr;
+                const int ih = ih_lo + r;
+                if (static_cast<unsigned>(ih) < static_cast<unsigned>(p.H))
+                    reinterpret_cast<uint4*>(pool_smem)[id] =
+                        reinterpret_cast<const uint4*>(xp + static_cast<long long>(ih) * row_bytes)[c];
+            }
+        } else {
+            for (int id = threadIdx.x; id < p.ih_rows * p.W; id += blockDim.x) {
+                const int r = id / p.W;
+                const int ih = ih_lo + r;
+                if (static_cast<unsigned>(ih) < static_cast<unsigned>(p.H))
+                    reinterpret_cast<T*>(pool_smem)[id] =
+                        reinterpret_cast<const T*>(xp)[static_cast<long long>(ih) * p.W + (id - r * p.W)];
+            }
+        }
+        __syncthreads();
+        // Each thread produces two horizontally adjacent outputs (one 32-bit store for 16-bit
+        // types when the pair is aligned). Windows that lie inside the image - all but the border
+        // ones - run without bounds tests, fully unrolled when the window is the compile-time K x K.
+        const int rows = min(p.toh, p.OH - oh0);
+        const int pairs_per_row = (p.OW + 1) >> 1;
+        const int kh_n = K ? K : p.KH, kw_n = K ? K : p.KW;
+        for (int id = threadIdx.x; id < rows * pairs_per_row; id += blockDim.x) {
+            const int ohl = id / pairs_per_row;
+            const int ow0 = (id - ohl * pairs_per_row) * 2;
+            const int r0 = ohl * p.sh;  // first staged row of the window
+            const bool rows_in = ih_lo + r0 >= 0 && ih_lo + r0 + (kh_n - 1) * p.dh < p.H;
+            float res[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int ow = ow0 + e;
+                const int iw0 = ow * p.sw - p.pad_l;
+                float acc = p.mode == 0 ? PoolType<T>::lowest() : 0.0f;
+                int count = 0;
+                if (ow >= p.OW) {
+                    res[e] = 0.0f;
+                    continue;
+                }
+                if (rows_in && iw0 >= 0 && iw0 + (kw_n - 1) * p.dw < p.W) {
+                    const char* s0 = reinterpret_cast<const char*>(pool_smem) + static_cast<long long>(r0) * row_bytes;
+                    if (K) {
+                        // K x K window, no dilation: constant offsets from one pointer
+                        const char* b0 = s0 + iw0 * ES;
+#pragma unroll
+                        for (int kh = 0; kh < (K ? K : 1); ++kh) {
+                            const char* rp = b0 + kh * row_bytes;
+#pragma unroll
+                            for (int kw = 0; kw < (K ? K : 1); ++kw) {
+                                const float v = PoolType<T>::load(rp, kw);
+                                acc = p.mode == 0 ? fmaxf(acc, v) : acc + v;
+                            }
+                        }
+                    } else {
+                        for (int kh = 0; kh < kh_n; ++kh)
+                            for (int kw = 0; kw < kw_n; ++kw) {
+                                const float v = PoolType<T>::load(s0 + static_cast<long long>(kh * p.dh) * row_bytes, iw0 + kw * p.dw);
+                                acc = p.mode == 0 ? fmaxf(acc, v) : acc + v;
+                            }
+                    }
+                    count = kh_n * kw_n;
+                } else {
+                    for (int kh = 0; kh < kh_n; ++kh) {
+                        const int r = r0 + kh * p.dh;
+                        if (static_cast<unsigned>(ih_lo + r) >= static_cast<unsigned>(p.H)) continue;
+                        const char* srow = reinterpret_cast<const char*>(pool_smem) + static_cast<long long>(r) * row_bytes;
+                        for (int kw = 0; kw < kw_n; ++kw) {
+                            const int iw = iw0 + kw * p.dw;
+                            if (static_cast<unsigned>(iw) >= static_cast<unsigned>(p.W)) continue;
+                            const float v = PoolType<T>::load(srow, iw);
+                            acc = p.mode == 0 ? fmaxf(acc, v) : acc + v;
+                            ++count;
+                        }
+                    }
+                }
+                if (p.mode == 1) {
+                    if (p.count_include_pad) count = kh_n * kw_n;
+                    acc = acc / static_cast<float>(count);
+                }
+                res[e] = acc;
+            }
+            const long long o = (plane * p.OH + oh0 + ohl) * p.OW + ow0;
+            if (sizeof(T) == 2 && ow0 + 1 < p.OW && ((o & 1) == 0) && (reinterpret_cast<uintptr_t>(p.y) & 3u) == 0) {
+                T pair[2];
+                PoolType<T>::store(reinterpret_cast<char*>(pair), 0, res[0]);
+                PoolType<T>::store(reinterpret_cast<char*>(pair), 1, res[1]);
+                reinterpret_cast<uint32_t*>(p.y)[o >> 1] = *reinterpret_cast<const uint32_t*>(pair);
+            } else {
+                PoolType<T>::store(p.y, o, res[0]);
+                if (ow0 + 1 < p.OW) PoolType<T>::store(p.y, o + 1, res[1]);
+            }
+        }
+    }
+}
+
+// Global pooling of small planes (7 x 7, 14 x 14): a block copies the contiguous memory of
+// 256 / group planes into shared memory with coalesced loads, then `group` neighbouring lanes
+// reduce each plane and the block writes its results as one contiguous run.
+template <typename T>
+__global__ void __launch_bounds__(256) pool_planes_kernel(const PoolParams p) {
+    extern __shared__ __align__(16) unsigned char pool_smem[];
+    constexpr int ES = sizeof(T);
+    const int n = p.H * p.W;
+    const int ppb = 256 / p.group;  // planes per block
+    const long long nblocks = (p.planes + ppb - 1) / ppb;
+    for (long long blk = blockIdx.x; blk < nblocks; blk += gridDim.x) {
+        const long long plane0 = blk * ppb;
+        const int np = static_cast<int>(min(static_cast<long long>(ppb), p.planes - plane0));
+        const long long bytes = static_cast<long long>(np) * n * ES;
+        const char* src = p.x + plane0 * n * ES;
+        __syncthreads();
+        // the block's range starts at a multiple of ppb*n*ES bytes: 16-byte aligned whenever
+        // that product is (checked on the host); the tail is copied element by element
+        const long long vbytes = ((reinterpret_cast<uintptr_t>(src) & 15u) == 0) ? (bytes & ~15ll) : 0;
+        for (long long o = threadIdx.x * 16ll; o < vbytes; o += 256 * 16)
+            *reinterpret_cast<uint4*>(pool_smem + o) = *reinterpret_cast<const uint4*>(src + o);
+        for (long long o = vbytes + threadIdx.x * ES; o < bytes; o += 256 * ES)
+            *reinterpret_cast<T*>(pool_smem + o) = *reinterpret_cast<const T*>(src + o);
+        __syncthreads();
+        const int pl = threadIdx.x / p.group;
+        const int sub = threadIdx.x - pl * p.group;
+        float acc = p.mode == 0 ? PoolType<T>::lowest() : 0.0f;
+        if (pl < np) {
+            const char* sp = reinterpret_cast<const char*>(pool_smem) + static_cast<long long>(pl) * n * ES;
+            for (int i = sub; i < n; i += p.group) {
+                const float v = PoolType<T>::load(sp, i);
+                acc = p.mode == 0 ? fmaxf(acc, v) : acc + v;
+            }
+        }
+        for (int d = p.group >> 1; d > 0; d >>= 1) {
+            const float o = __shfl_xor_sync(0xffffffffu, acc, d);
+            acc = p.mode == 0 ? fmaxf(acc, o) : acc + o;
+        }
+        if (pl < np && sub == 0) PoolType<T>::store(p.y, plane0 + pl, p.mode == 0 ? acc : acc / static_cast<float>(n));
+    }
+}
+
+// Global pooling: the window is the whole plane (no padding). One warp per plane, lanes stride
+// through it (coalesced), fp32 partial results combined with shuffles.
+template <typename T>
+__global__ void __launch_bounds__(256) pool_plane_kernel(const PoolParams p) {
+    const int lane = threadIdx.x & 31;
+    const long long warp = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+    const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+    const int n = p.H * p.W;
+    for (long long plane = warp; plane < p.planes; plane += warps) {
+        const long long base = plane * n;
+        float acc = p.mode == 0 ? PoolType<T>::lowest() : 0.0f;
+        for (int i = lane; i < n; i += 32) {
+            const float v = PoolType<T>::load(p.x, base + i);
+            acc = p.mode == 0 ? fmaxf(acc, v) : acc + v;
+        }
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) {
+            const float o = __shfl_xor_sync(0xffffffffu, acc, d);
+            acc = p.mode == 0 ? fmaxf(acc, o) : acc + o;
+        }
+        if (lane == 0) PoolType<T>::store(p.y, plane, p.mode == 0 ? acc : acc / static_cast<float>(n));
+    }
+}
+
+}  // namespace dlfb200

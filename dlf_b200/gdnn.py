@@ -17,12 +17,20 @@ from .gblas import BLASError, StatusCode, _check, _ptr, _stream, precision_of
 class Filter2D:
     """Geometry of a 2-D filter: NCHW input, OIHW kernel (dnn.h:9-122)."""
 
-    def __init__(self, input_shape, kernel_shape, group=1):
+    def __init__(self, input_shape, kernel_shape, group=1, kernel_w=None):
+        """Filter2D(input_shape, kernel_shape, group) for convolutions, or
+        Filter2D(input_shape, kernel_h, kernel_w) for pooling (dlf/src/tensor/filter.cpp:5-25)."""
         self.batches, self.channels, self.height, self.width = map(int, input_shape)
-        self.num_kernels, cpg, self.kernel_h, self.kernel_w = map(int, kernel_shape)
-        self.group = int(group)
-        if cpg * self.group != self.channels:
-            raise ValueError("kernel channels * group != input channels")
+        if isinstance(kernel_shape, int):
+            # pooling form: the second and third arguments are kernel_h, kernel_w
+            self.kernel_h = int(kernel_shape)
+            self.kernel_w = int(kernel_w if kernel_w is not None else group)
+            self.num_kernels, self.group = self.channels, 1
+        else:
+            self.num_kernels, cpg, self.kernel_h, self.kernel_w = map(int, kernel_shape)
+            self.group = int(group)
+            if cpg * self.group != self.channels:
+                raise ValueError("kernel channels * group != input channels")
         self.pad_top = self.pad_left = self.pad_bottom = self.pad_right = 0
         self.stride_h = self.stride_w = 1
         self.dilation_h = self.dilation_w = 1
@@ -33,6 +41,20 @@ class Filter2D:
             self.pad_left = self.pad_right = int(p[1])
         else:
             self.pad_top, self.pad_left, self.pad_bottom, self.pad_right = map(int, p)
+        return self
+
+    def auto_pad(self, mode):
+        """dlf/src/tensor/filter.cpp:51-82."""
+        if mode == "VALID":
+            self.pad_top = self.pad_left = self.pad_bottom = self.pad_right = 0
+        elif mode in ("SAME_UPPER", "SAME_LOWER"):
+            def pad(size, kernel, stride, dilation):
+                ext = (kernel - 1) * dilation + 1
+                total = max(((size - 1) // stride) * stride + ext - size, 0)
+                half = total >> 1
+                return (half, total - half) if mode == "SAME_UPPER" else (total - half, half)
+            self.pad_top, self.pad_bottom = pad(self.height, self.kernel_h, self.stride_h, self.dilation_h)
+            self.pad_left, self.pad_right = pad(self.width, self.kernel_w, self.stride_w, self.dilation_w)
         return self
 
     def strides(self, h, w):
@@ -130,3 +152,73 @@ def conv2d_filter(X, W, Y, filt, bias=None, queue=None, event=None, residual=Non
            filt.pad_left, filt.pad_bottom, filt.pad_right, filt.stride_h, filt.stride_w,
            filt.dilation_h, filt.dilation_w, X, W, Y, queue=queue, event=event, bias=bias,
            residual=residual, activation=activation)
+
+
+def _pool(fn_name, extra, batches, channels, height, width, output_h, output_w, kernel_h, kernel_w, pad_top,
+          pad_left, pad_bottom, pad_right, stride_h, stride_w, dilation_h, dilation_w, x_buffer, y_buffer,
+          queue, event):
+    prec = precision_of(y_buffer)
+    if x_buffer.dtype != y_buffer.dtype:
+        raise BLASError(StatusCode.kInvalidValue)
+    if x_buffer.numel() < batches * channels * height * width:
+        raise BLASError(StatusCode.kInsufficientMemoryA)
+    if y_buffer.numel() < batches * channels * output_h * output_w:
+        raise BLASError(StatusCode.kInsufficientMemoryC)
+    s, sp = _stream(queue)
+    if event is not None:
+        event.start.record(s)
+    rc = getattr(lib(), fn_name)(
+        int(prec), batches, channels, height, width, output_h, output_w, kernel_h, kernel_w, pad_top,
+        pad_left, pad_bottom, pad_right, stride_h, stride_w, dilation_h, dilation_w, *extra,
+        _ptr(x_buffer), _ptr(y_buffer), sp)
+    if event is not None:
+        event.end.record(s)
+    _check(rc)
+
+
+def maxpool(batches, channels, height, width, output_h, output_w, kernel_h, kernel_w, pad_top, pad_left,
+            pad_bottom, pad_right, stride_h, stride_w, dilation_h, dilation_w, x_buffer, y_buffer,
+            queue=None, event=None):
+    """gpgpu::dnn::maxpool, in the argument order of its definition and of its callers
+    (gpgpu/src/gdnn.cpp:1667-1676; dlf/include/tensor/dnn.h:218-229)."""
+    _pool("dlf_b200_maxpool", (), batches, channels, height, width, output_h, output_w, kernel_h, kernel_w,
+          pad_top, pad_left, pad_bottom, pad_right, stride_h, stride_w, dilation_h, dilation_w, x_buffer,
+          y_buffer, queue, event)
+
+
+def avgpool(batches, channels, height, width, output_h, output_w, kernel_h, kernel_w, pad_top, pad_left,
+            pad_bottom, pad_right, stride_h, stride_w, dilation_h, dilation_w, count_include_pad, x_buffer,
+            y_buffer, queue=None, event=None):
+    """gpgpu::dnn::avgpool (gpgpu/src/gdnn.cpp:1728-1738; dlf/include/tensor/dnn.h:249-261)."""
+    _pool("dlf_b200_avgpool", (1 if count_include_pad else 0,), batches, channels, height, width, output_h,
+          output_w, kernel_h, kernel_w, pad_top, pad_left, pad_bottom, pad_right, stride_h, stride_w,
+          dilation_h, dilation_w, x_buffer, y_buffer, queue, event)
+
+
+def _filter_args(f):
+    return (f.batches, f.channels, f.height, f.width, f.output_h, f.output_w, f.kernel_h, f.kernel_w,
+            f.pad_top, f.pad_left, f.pad_bottom, f.pad_right, f.stride_h, f.stride_w, f.dilation_h,
+            f.dilation_w)
+
+
+def max_pooling(X, Y, filt, queue=None, event=None):
+    """dlf::dnn::max_pooling(X, Y, filter) for device tensors (dlf/include/tensor/dnn.h:217-229)."""
+    maxpool(*_filter_args(filt), X, Y, queue=queue, event=event)
+
+
+def average_pooling(X, Y, filt, count_include_pad, queue=None, event=None):
+    """dlf::dnn::average_pooling(X, Y, filter, count_include_pad) (dnn.h:248-262)."""
+    avgpool(*_filter_args(filt), count_include_pad, X, Y, queue=queue, event=event)
+
+
+def global_max_pooling(X, Y, queue=None, event=None):
+    """dlf::dnn::global_max_pooling for device tensors: max_pooling with the whole plane as the
+    window (dlf/include/tensor/dnn.h:346-351)."""
+    h, w = int(X.shape[2]), int(X.shape[3])
+    max_pooling(X, Y, Filter2D(X.shape, h, w).strides(h, w), queue=queue, event=event)
+
+
+def global_average_pooling(X, Y, queue=None, event=None):
+    """dlf::dnn::global_average_pooling for device tensors (dnn.h:361-375)."""
+    h, w = int(X.shape[2]), int(X.shape[3])
+    average_pooling(X, Y, Filter2D(X.shape, h, w).strides(h, w), False, queue=queue, event=event)

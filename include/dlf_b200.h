@@ -129,6 +129,28 @@ size_t dlf_b200_conv2d_workspace_bytes(int dtype, size_t batches, size_t channel
                                        size_t num_kernels, size_t group, size_t kernel_h,
                                        size_t kernel_w);
 
+/* NCHW pooling, the second "next" step around the convolution path (a ResNet forward is
+ * conv -> maxpool -> ... -> global average pool -> FC). Replace gpgpu::dnn::maxpool / avgpool
+ * (gpgpu/include/gdnn.h:215-238; definitions and the argument order that callers use - output
+ * size before kernel size - gpgpu/src/gdnn.cpp:1667-1676, 1728-1738), which run cuDNN pooling or
+ * an OpenCL kernel. Semantics are those of dlf's CPU pooling
+ * (dlf/include/tensor/dnn_detail.h:172-227): X is {batches, channels, height, width}, Y is
+ * {batches, channels, output_h, output_w}; (pad_top, pad_left) is the origin shift, pad_bottom /
+ * pad_right only enter through the output size; max starts from the type's lowest value; the
+ * average divides by the number of taps inside the image, or by kernel_h*kernel_w when
+ * count_include_pad is non-zero. Global pooling (dlf/include/tensor/dnn.h:337-375) is the case
+ * kernel = {height, width}, output 1 x 1, which takes a one-warp-per-plane reduction. */
+int dlf_b200_maxpool(int dtype, size_t batches, size_t channels, size_t height, size_t width,
+                     size_t output_h, size_t output_w, size_t kernel_h, size_t kernel_w,
+                     size_t pad_top, size_t pad_left, size_t pad_bottom, size_t pad_right,
+                     size_t stride_h, size_t stride_w, size_t dilation_h, size_t dilation_w,
+                     const void* x, void* y, void* stream);
+int dlf_b200_avgpool(int dtype, size_t batches, size_t channels, size_t height, size_t width,
+                     size_t output_h, size_t output_w, size_t kernel_h, size_t kernel_w,
+                     size_t pad_top, size_t pad_left, size_t pad_bottom, size_t pad_right,
+                     size_t stride_h, size_t stride_w, size_t dilation_h, size_t dilation_w,
+                     int count_include_pad, const void* x, void* y, void* stream);
+
 /* Name of a status code returned by the functions above (static storage). Mirrors the
  * StatusCode enumerators of gblas.h:43-107. */
 const char* dlf_b200_status_string(int status);

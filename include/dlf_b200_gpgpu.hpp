@@ -312,6 +312,55 @@ void conv2d(const size_t batches, const size_t channels,
                         "dlf_b200_conv2d_fused");
 }
 
+// gpgpu::dnn::maxpool / avgpool in the argument order of their definitions
+// (gpgpu/src/gdnn.cpp:1667-1676, 1728-1738).
+template <typename T>
+void maxpool(const size_t batches, const size_t channels,
+             const size_t height, const size_t width,
+             const size_t output_h, const size_t output_w,
+             const size_t kernel_h, const size_t kernel_w,
+             const size_t pad_top, const size_t pad_left,
+             const size_t pad_bottom, const size_t pad_right,
+             const size_t stride_h, const size_t stride_w,
+             const size_t dilation_h, const size_t dilation_w,
+             const Buffer<T>& x_buffer, Buffer<T>& y_buffer,
+             const Queue& queue = current::queue(), Event* event = nullptr) {
+    using blas::BLASError;
+    using blas::StatusCode;
+    if (x_buffer.size() < batches * channels * height * width) throw BLASError(StatusCode::kInsufficientMemoryA);
+    if (y_buffer.size() < batches * channels * output_h * output_w) throw BLASError(StatusCode::kInsufficientMemoryC);
+    blas::detail::EventScope scope(queue, event);
+    blas::detail::raise(dlf_b200_maxpool(blas::PrecisionOf<T>::value, batches, channels, height, width, output_h,
+                                         output_w, kernel_h, kernel_w, pad_top, pad_left, pad_bottom, pad_right,
+                                         stride_h, stride_w, dilation_h, dilation_w, x_buffer.unwrap(),
+                                         y_buffer.unwrap(), queue.unwrap()),
+                        "dlf_b200_maxpool");
+}
+
+template <typename T>
+void avgpool(const size_t batches, const size_t channels,
+             const size_t height, const size_t width,
+             const size_t output_h, const size_t output_w,
+             const size_t kernel_h, const size_t kernel_w,
+             const size_t pad_top, const size_t pad_left,
+             const size_t pad_bottom, const size_t pad_right,
+             const size_t stride_h, const size_t stride_w,
+             const size_t dilation_h, const size_t dilation_w,
+             const bool count_include_pad,
+             const Buffer<T>& x_buffer, Buffer<T>& y_buffer,
+             const Queue& queue = current::queue(), Event* event = nullptr) {
+    using blas::BLASError;
+    using blas::StatusCode;
+    if (x_buffer.size() < batches * channels * height * width) throw BLASError(StatusCode::kInsufficientMemoryA);
+    if (y_buffer.size() < batches * channels * output_h * output_w) throw BLASError(StatusCode::kInsufficientMemoryC);
+    blas::detail::EventScope scope(queue, event);
+    blas::detail::raise(dlf_b200_avgpool(blas::PrecisionOf<T>::value, batches, channels, height, width, output_h,
+                                         output_w, kernel_h, kernel_w, pad_top, pad_left, pad_bottom, pad_right,
+                                         stride_h, stride_w, dilation_h, dilation_w, count_include_pad ? 1 : 0,
+                                         x_buffer.unwrap(), y_buffer.unwrap(), queue.unwrap()),
+                        "dlf_b200_avgpool");
+}
+
 }  // namespace dnn
 }  // namespace gpgpu
 }  // namespace dlf_b200

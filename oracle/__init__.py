@@ -148,6 +148,38 @@ def conv2d(X, W, group=1, pads=(0, 0, 0, 0), strides=(1, 1), dilations=(1, 1), b
     return Y
 
 
+def pool2d(X, kernel, mode="max", pads=(0, 0, 0, 0), strides=(1, 1), dilations=(1, 1),
+           count_include_pad=False):
+    """dlf::dnn::max_pooling / average_pooling on the CPU (dnn.h:207-247 over
+    dnn_detail.h:172-227). X: NCHW float32; kernel = (kh, kw); pads = (top, left, bottom, right)."""
+    X = np.ascontiguousarray(X, dtype=np.float32)
+    n, c, h, w = X.shape
+    kh, kw = kernel
+    pt, pl, pb, pr = pads
+    oh = output_dim(h, pt, pb, kh, strides[0], dilations[0])
+    ow = output_dim(w, pl, pr, kw, strides[1], dilations[1])
+    Y = np.empty((n, c, oh, ow), dtype=np.float32)
+    fn = lib().dlf_oracle_pool2d_f32
+    fn.restype = None
+    fn.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int] + [ctypes.c_size_t] * 14
+    fn(_p(X), _p(Y), 0 if mode == "max" else 1, 1 if count_include_pad else 0, n, c, h, w, oh, ow, kh, kw,
+       pt, pl, strides[0], strides[1], dilations[0], dilations[1])
+    return Y
+
+
+def global_pool(X, mode="avg", wide=False):
+    """dlf::dnn::global_max_pooling / global_average_pooling (dnn.h:337-375 over
+    dnn_detail.h:229-260): {N, C, ...} -> {N, C, 1, 1}."""
+    X = np.ascontiguousarray(X, dtype=np.float32)
+    planes = X.shape[0] * X.shape[1]
+    Y = np.empty((X.shape[0], X.shape[1]) + (1,) * (X.ndim - 2), dtype=np.float32)
+    fn = lib().dlf_oracle_global_pool_f32
+    fn.restype = None
+    fn.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t, ctypes.c_size_t, ctypes.c_int]
+    fn(_p(X), _p(Y), 0 if mode == "max" else 1, planes, X.size // planes, 1 if wide else 0)
+    return Y
+
+
 def conv2d_fused(X, W, residual=None, relu=False, **kw):
     """The operator chain dlf's graph runtime evaluates around a convolution, as separate passes:
     ConvOp (conv + bias, dlf/include/predict.h:1258-1286), then Add of a residual tensor

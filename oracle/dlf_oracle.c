@@ -16,6 +16,7 @@
  *
  * Each function cites the reference lines it follows (paths relative to the dlf tree).
  */
+#include <float.h>
 #include <stddef.h>
 #include <stdint.h>
 #include <stdlib.h>
@@ -278,5 +279,66 @@ void dlf_oracle_bias_f32(float* Y, const float* bias, size_t batches, size_t cha
         float* y = Y + bc * plane;
         size_t i;
         for (i = 0; i < plane; ++i) y[i] = y[i] + v;
+    }
+}
+
+/* Pooling: dlf/include/tensor/dnn_detail.h:172-227 (detail::pooling) with the accumulators of
+ * dlf/include/tensor/dnn.h:207-247: max_pooling starts from numeric_limits<T>::lowest() and keeps
+ * std::max; average_pooling starts from T{} (0), adds in (kh, kw) order and divides by the
+ * number of taps inside the image, or by kernel_h*kernel_w with count_include_pad. mode: 0 max,
+ * 1 average. The origin shift is (pad_top, pad_left) (pad_h() / pad_w(), dnn.h:92-93). */
+void dlf_oracle_pool2d_f32(const float* X, float* Y, int mode, int count_include_pad, size_t batches,
+                           size_t channels, size_t height, size_t width, size_t output_h,
+                           size_t output_w, size_t kernel_h, size_t kernel_w, size_t pad_top,
+                           size_t pad_left, size_t stride_h, size_t stride_w, size_t dilation_h,
+                           size_t dilation_w) {
+    long b, c, h, w, kh, kw;
+    for (b = 0; b < (long)batches; ++b)
+        for (c = 0; c < (long)channels; ++c)
+            for (h = 0; h < (long)output_h; ++h)
+                for (w = 0; w < (long)output_w; ++w) {
+                    float acc = mode == 0 ? -FLT_MAX : 0.0f;
+                    int count = 0;
+                    for (kh = 0; kh < (long)kernel_h; ++kh) {
+                        const long hi = kh * (long)dilation_h + (long)stride_h * h - (long)pad_top;
+                        if (hi < 0 || hi >= (long)height) continue;
+                        for (kw = 0; kw < (long)kernel_w; ++kw) {
+                            const long wi = kw * (long)dilation_w + (long)stride_w * w - (long)pad_left;
+                            float x;
+                            if (wi < 0 || wi >= (long)width) continue;
+                            x = X[((b * (long)channels + c) * (long)height + hi) * (long)width + wi];
+                            if (mode == 0) acc = acc < x ? x : acc; /* std::max(acc, x) */
+                            else acc = acc + x;
+                            ++count;
+                        }
+                    }
+                    if (count_include_pad) count = (int)(kernel_h * kernel_w);
+                    Y[((b * (long)channels + c) * (long)output_h + h) * (long)output_w + w] =
+                        mode == 0 ? acc : acc / count;
+                }
+}
+
+/* Global pooling: dlf/include/tensor/dnn_detail.h:229-260 (detail::global_pooling) with the
+ * accumulators of dlf/include/tensor/dnn.h:337-375: one value per (batch, channel) plane, the
+ * maximum or sum / N. The reference combines partial results of a parallel reduction in an
+ * unspecified order; this restatement adds sequentially (with a double accumulator when `wide`,
+ * the error reference for tolerance tests). */
+void dlf_oracle_global_pool_f32(const float* X, float* Y, int mode, size_t planes, size_t n, int wide) {
+    size_t p, i;
+    for (p = 0; p < planes; ++p) {
+        const float* x = X + p * n;
+        if (mode == 0) {
+            float acc = -FLT_MAX;
+            for (i = 0; i < n; ++i) acc = acc < x[i] ? x[i] : acc;
+            Y[p] = acc;
+        } else if (wide) {
+            double acc = 0.0;
+            for (i = 0; i < n; ++i) acc += x[i];
+            Y[p] = (float)(acc / (double)n);
+        } else {
+            float acc = 0.0f;
+            for (i = 0; i < n; ++i) acc = acc + x[i];
+            Y[p] = acc / n;
+        }
     }
 }

@@ -90,6 +90,22 @@ static void conv_bias_golden() {
     CHECK(host(dY2) == Yf);
 }
 
+static void maxpool_golden() {
+    // TEST(MaxPool, basic_2d_with_padding), dlf/test/DNNTest.cpp:625-644
+    std::vector<float> X(25);
+    for (int i = 0; i < 25; ++i) X[i] = static_cast<float>(i + 1);
+    const std::vector<float> R = {7,  8,  9,  10, 10, 12, 13, 14, 15, 15, 17, 18, 19,
+                                  20, 20, 22, 23, 24, 25, 25, 22, 23, 24, 25, 25};
+    auto dX = dev(X);
+    Buffer<float> dY(25);
+    dnn::maxpool<float>(1, 1, 5, 5, 5, 5, 3, 3, 1, 1, 1, 1, 1, 1, 1, 1, dX, dY);
+    CHECK(host(dY) == R);
+    // global average of the same plane through avgpool with the plane as the window
+    Buffer<float> dG(1);
+    dnn::avgpool<float>(1, 1, 5, 5, 1, 1, 5, 5, 0, 0, 0, 0, 5, 5, 1, 1, false, dX, dG);
+    CHECK(host(dG) == std::vector<float>{13.0f});
+}
+
 static void batched() {
     const size_t m = 5, n = 7, k = 9, batch = 3;
     std::vector<float> A(batch * m * k), B(k * n), C(batch * m * n, 0.0f);
@@ -142,6 +158,7 @@ static void errors() {
 int main() {
     gemm_golden();
     conv_bias_golden();
+    maxpool_golden();
     batched();
     errors();
     int dev_status = -1;

@@ -8,7 +8,7 @@ parsed out of
     dlf/test/TensorTest.cpp          gemm_test()            (alpha=2, beta=3, 4 transpose combos)
     dlf/test/GPGPUTest.cpp           gemm_test()            (same data through the GPU API)
     dlf/test/MatMulTest.cpp          TYPED_TEST(MatMulTest, *)
-    dlf/test/DNNTest.cpp             TEST(Conv2D, *)
+    dlf/test/DNNTest.cpp             TEST(Conv2D, *), TEST(MaxPool, *), TEST(DNNTest, GlobalPooling)
     dlf/test/model/PredictTest.cpp   Gemm, Conv (+bias)
 
 Usage:  python tests/golden/make_goldens.py /path/to/dlf-checkout
@@ -168,6 +168,32 @@ def extract_conv(path, rel):
     return cases
 
 
+def extract_pool(path, rel):
+    """TEST(MaxPool, *) cases that carry a literal result, and TEST(DNNTest, GlobalPooling)."""
+    text = open(path).read()
+    cases = []
+    for m in re.finditer(r"TEST\(MaxPool,\s*(\w+)\)", text):
+        body, _ = _block(text, m.end())
+        vars_ = parse_vars(body)
+        if "R" not in vars_:
+            continue
+        f = re.search(r"dnn::Filter2D\(X\.shape\(\),\s*(\d+),\s*(\d+)\)((?:\.\w+\([^()]*\))*)", body)
+        cfg = {"kernel": [int(f.group(1)), int(f.group(2))], "calls": []}
+        for call in re.finditer(r"\.(\w+)\(([^()]*)\)", f.group(3)):
+            arg = call.group(2).strip()
+            cfg["calls"].append([call.group(1), arg.strip('"') if arg.startswith('"') else _ints(arg)])
+        cases.append({"name": m.group(1), "source": "%s:%d" % (rel, _line_of(text, m.start())), "mode": "max",
+                      "X": vars_["X"], "R": vars_["R"], "filter": cfg})
+    m = re.search(r"TEST\(DNNTest,\s*GlobalPooling\)", text)
+    body, _ = _block(text, m.end())
+    vars_ = parse_vars(body)
+    lits = dict((k, [float(v) for v in vals.split(",")]) for k, vals in
+                re.findall(r"auto (\w+_R) = Tensor<float>\(\{2, 3, 1, 1\},\s*\{([^}]*)\}\)", body))
+    glob = {"source": "%s:%d" % (rel, _line_of(text, m.start())), "X": vars_["X"],
+            "max_R": lits["max_R"], "avg_R": lits["avg_R"]}
+    return {"maxpool": cases, "global": glob}
+
+
 def extract_predict(path, rel):
     text = open(path).read()
     out = {}
@@ -203,6 +229,7 @@ def main():
         "gemm": [g1, g2],
         "matmul": extract_matmul(os.path.join(t, "MatMulTest.cpp"), "dlf/test/MatMulTest.cpp"),
         "conv2d": extract_conv(os.path.join(t, "DNNTest.cpp"), "dlf/test/DNNTest.cpp"),
+        "pool": extract_pool(os.path.join(t, "DNNTest.cpp"), "dlf/test/DNNTest.cpp"),
         "predict": extract_predict(os.path.join(t, "model", "PredictTest.cpp"),
                                    "dlf/test/model/PredictTest.cpp"),
     }

@@ -708,3 +708,103 @@ def test_event_brackets_the_launch():
     gb.gemm(gb.Layout.RowMajor, gb.Transpose.NoTrans, gb.Transpose.NoTrans, 512, 512, 512, 1.0, a,
             0, 512, a, 0, 512, 0.0, c, 0, 512, event=ev)
     assert ev.elapsed_ms() > 0.0
+
+
+# ---------------------------------------------------------------------------------------------
+# pooling
+# ---------------------------------------------------------------------------------------------
+def _pool_filter(X_shape, cfg):
+    from dlf_b200 import gdnn
+    f = gdnn.Filter2D(X_shape, cfg["kernel"][0], cfg["kernel"][1])
+    for name, arg in cfg["calls"]:
+        getattr(f, name)(*arg) if isinstance(arg, list) else getattr(f, name)(arg)
+    return f
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("case", G["pool"]["maxpool"], ids=lambda c: c["name"])
+def test_maxpool_goldens_bit_exact(case, dtype):
+    from dlf_b200 import gdnn
+    X = tensor_of(case["X"]).to(dtype).cuda()
+    f = _pool_filter(X.shape, case["filter"])
+    Y = torch.full((f.batches, f.channels, f.output_h, f.output_w), float("nan"), dtype=dtype, device="cuda")
+    gdnn.max_pooling(X, Y, f)
+    assert torch.equal(Y.float().cpu(), tensor_of(case["R"]))
+
+
+def test_global_pooling_golden_gpu():
+    from dlf_b200 import gdnn
+    g = G["pool"]["global"]
+    X = tensor_of(g["X"]).cuda()
+    Y = torch.empty(2, 3, 1, 1, device="cuda")
+    gdnn.global_max_pooling(X, Y)
+    assert Y.cpu().ravel().tolist() == g["max_R"]
+    gdnn.global_average_pooling(X, Y)
+    assert Y.cpu().ravel().tolist() == g["avg_R"]
+
+
+POOL_CASES = [
+    # N, C, H, W, KH, KW, pads(t,l,b,r), strides, dilations
+    (2, 3, 100, 100, 3, 3, (1, 1, 1, 1), (1, 1), (1, 1)),     # the reference's multi-channel test shape
+    (3, 16, 112, 112, 3, 3, (1, 1, 1, 1), (2, 2), (1, 1)),    # ResNet stem pool
+    (2, 5, 13, 17, 2, 3, (0, 2, 1, 0), (2, 1), (1, 2)),       # odd everything, asymmetric pads, dilation
+    (2, 4, 9, 9, 5, 5, (4, 4, 4, 4), (3, 3), (1, 1)),         # windows mostly in the padding
+    (4, 7, 7, 7, 7, 7, (0, 0, 0, 0), (7, 7), (1, 1)),         # whole plane: one-warp-per-plane reduction
+    (2, 3, 4, 5, 4, 5, (0, 0, 0, 0), (1, 1), (1, 1)),         # whole plane smaller than a warp
+]
+
+
+@pytest.mark.parametrize("flags", [0, 0x100 << 16], ids=["staged", "plain"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("case", POOL_CASES, ids=lambda c: "x".join(map(str, c[:6])))
+def test_pooling_random_parity(lib, case, dtype, flags):
+    """max: bit-exact for every type (a maximum of stored values); average: bit-exact in fp32 for
+    windowed pooling (same order of additions as the reference), tolerance for 16-bit types and
+    for the plane reduction (the reference's own reduction order is unspecified there)."""
+    from dlf_b200 import gdnn
+    N, C, H, W, KH, KW, pads, strides, dil = case
+    lib.set_tuning(0, flags)
+    try:
+        _pooling_case(lib, case, dtype, flags)
+    finally:
+        lib.set_tuning(0, 0)
+
+
+def _pooling_case(lib, case, dtype, flags):
+    from dlf_b200 import gdnn
+    N, C, H, W, KH, KW, pads, strides, dil = case
+    rng = np.random.default_rng(31)
+    Xh = _round_to(rng.normal(size=(N, C, H, W)).astype(np.float32), dtype)
+    X = torch.from_numpy(Xh).to(dtype).cuda()
+    f = gdnn.Filter2D(X.shape, KH, KW).pads(*pads).strides(*strides).dilations(*dil)
+    shape = (N, C, f.output_h, f.output_w)
+    Y = torch.full(shape, float("nan"), dtype=dtype, device="cuda")
+    gdnn.max_pooling(X, Y, f)
+    ref = oracle.pool2d(Xh, (KH, KW), "max", pads, strides, dil)
+    assert np.array_equal(Y.float().cpu().numpy(), ref)
+    whole = shape[2:] == (1, 1) and (KH, KW) == (H, W)
+    for cip in (False, True):
+        Y = torch.full(shape, float("nan"), dtype=dtype, device="cuda")
+        gdnn.average_pooling(X, Y, f, cip)
+        ref = oracle.pool2d(Xh, (KH, KW), "avg", pads, strides, dil, count_include_pad=cip)
+        got = Y.float().cpu().numpy()
+        if dtype == torch.float32 and not (whole and not flags):
+            assert np.array_equal(got, ref, equal_nan=True)
+        else:
+            if dtype == torch.float32:
+                assert rel_fro(got, ref) <= FP32_TOL
+            else:
+                assert max_rel(got, ref) <= HALF_TOL
+    assert lib.device_status() == 0
+
+
+def test_pooling_argument_errors(lib):
+    from dlf_b200 import gdnn
+    gb = _gb()
+    X = torch.zeros(1, 1, 4, 4, device="cuda")
+    Y = torch.zeros(1, 1, 1, 1, device="cuda")
+    f = gdnn.Filter2D(X.shape, 2, 2)
+    with pytest.raises(gb.BLASError):
+        gdnn.max_pooling(X, Y, f)  # Y too small for the 3 x 3 output
+    with pytest.raises(gb.BLASError):
+        gdnn.max_pooling(X.half(), torch.zeros(1, 1, 3, 3, device="cuda"), f)  # mixed types

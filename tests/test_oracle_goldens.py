@@ -153,3 +153,45 @@ def test_host_cblas_agrees_with_oracle():
     oracle.gblas_sgemm(oracle.ROW_MAJOR, N, N, 64, 48, 96, 1.0, A.ravel(), 0, 96, B.ravel(), 0, 48,
                        0.0, c2, 0, 48)
     assert np.linalg.norm(c1 - c2) / np.linalg.norm(c2) < 1e-6
+
+
+def _pool_filter(X_shape, cfg):
+    from dlf_b200 import gdnn
+    f = gdnn.Filter2D(X_shape, cfg["kernel"][0], cfg["kernel"][1])
+    for name, arg in cfg["calls"]:
+        getattr(f, name)(*arg) if isinstance(arg, list) else getattr(f, name)(arg)
+    return f
+
+
+@pytest.mark.parametrize("case", G["pool"]["maxpool"], ids=lambda c: c["name"])
+def test_maxpool_goldens(case):
+    """TEST(MaxPool, *) of the reference (dlf/test/DNNTest.cpp:625-731), including the
+    SAME_UPPER auto-padding of Filter2D (dlf/src/tensor/filter.cpp:51-82)."""
+    X = tensor_of(case["X"]).numpy()
+    f = _pool_filter(X.shape, case["filter"])
+    Y = oracle.pool2d(X, (f.kernel_h, f.kernel_w), "max", (f.pad_top, f.pad_left, f.pad_bottom, f.pad_right),
+                      (f.stride_h, f.stride_w), (f.dilation_h, f.dilation_w))
+    R = tensor_of(case["R"]).numpy()
+    assert Y.shape == R.shape == (f.batches, f.channels, f.output_h, f.output_w)
+    assert np.array_equal(Y, R)
+
+
+def test_global_pooling_golden():
+    """TEST(DNNTest, GlobalPooling) (dlf/test/DNNTest.cpp:769-794), through the plane reduction
+    and through pooling with the whole plane as the window (the device route of the reference)."""
+    g = G["pool"]["global"]
+    X = tensor_of(g["X"]).numpy()
+    assert oracle.global_pool(X, "max").ravel().tolist() == g["max_R"]
+    assert oracle.global_pool(X, "avg").ravel().tolist() == g["avg_R"]
+    assert oracle.pool2d(X, X.shape[2:], "max", strides=X.shape[2:]).ravel().tolist() == g["max_R"]
+    assert oracle.pool2d(X, X.shape[2:], "avg", strides=X.shape[2:]).ravel().tolist() == g["avg_R"]
+
+
+def test_average_pool_counts():
+    """count_include_pad divides by kernel_h*kernel_w, otherwise by the taps inside the image
+    (dnn_detail.h:205-221)."""
+    X = np.ones((1, 1, 4, 4), np.float32)
+    a = oracle.pool2d(X, (3, 3), "avg", (1, 1, 1, 1))
+    b = oracle.pool2d(X, (3, 3), "avg", (1, 1, 1, 1), count_include_pad=True)
+    assert np.all(a == 1.0)
+    assert b[0, 0, 0, 0] == np.float32(4.0 / 9.0) and b[0, 0, 1, 1] == 1.0
