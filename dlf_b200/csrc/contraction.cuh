@@ -238,8 +238,8 @@ __device__ __forceinline__ void store_chunk(uint32_t tile, uint32_t lo_tile, int
 }
 
 // PAIR: the CTA is one of a cluster of two that share 256 x BN tiles through cta_group::2 UMMAs
-// (only with USE_TMA). Each CTA loads its own 128 rows of A and BN/2 rows of B; no load is
-// multicast. Rank 0 issues the UMMAs and signals both CTAs' barriers.
+// (only with USE_TMA). Each CTA loads its own 128 rows of A and BN/2 rows of B with plain
+// per-CTA TMA loads. Rank 0 issues the UMMAs and signals both CTAs' barriers.
 template <int ES, bool USE_TMA, bool PAIR = false>
 __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
     contraction_kernel(const __grid_constant__ Params p, const __grid_constant__ CUtensorMap tmA,
