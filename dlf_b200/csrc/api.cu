@@ -1094,6 +1094,7 @@ int launch_pool(int dtype, int mode, int count_include_pad, size_t batches, size
     p.dh = static_cast<int>(dilation_h);
     p.dw = static_cast<int>(dilation_w);
     p.mode = mode;
+    p.ablate = (g_force_generic.load() >> 26) & 3;
     p.count_include_pad = count_include_pad;
     p.x = static_cast<const char*>(x);
     p.y = static_cast<char*>(y);
@@ -1133,7 +1134,18 @@ int launch_pool(int dtype, int mode, int count_include_pad, size_t batches, size
             toh = std::min<long long>(toh, std::max<long long>(1, (24 * 1024 / row_bytes - win_rows) / static_cast<long long>(stride_h) + 1));
             toh = std::min<long long>(toh, static_cast<long long>(output_h));
         }
-        if (toh >= 1) {
+        const bool strip = mode == 0 && es == 2 && kernel_h == 3 && kernel_w == 3 && stride_h == 2 && stride_w == 2 &&
+                           dilation_h == 1 && dilation_w == 1 && pad_left == 1 && width % 8 == 0 &&
+                           output_w % 8 == 0 && output_w * 2 <= width + 1 &&
+                           (reinterpret_cast<uintptr_t>(x) & 15u) == 0 && (reinterpret_cast<uintptr_t>(y) & 15u) == 0 &&
+                           !((g_force_generic.load() >> 16) & 0x100);
+        if (strip) {
+            const long long strips = p.planes * output_h * (static_cast<long long>(output_w) / 8);
+            const unsigned grid = static_cast<unsigned>(
+                std::min<long long>((strips + 255) / 256, static_cast<long long>(st->num_sms) * 32));
+            if (fmt == FMT_F16) maxpool3s2_strip_kernel<__half, __half2><<<grid, 256, 0, s>>>(p, 0xFBFFFBFFu);
+            else maxpool3s2_strip_kernel<__nv_bfloat16, __nv_bfloat162><<<grid, 256, 0, s>>>(p, 0xFF7FFF7Fu);
+        } else if (toh >= 1) {
             p.toh = static_cast<int>(toh);
             p.ih_rows = static_cast<int>((toh - 1) * stride_h + win_rows);
             const long long blocks = p.planes * ((static_cast<long long>(output_h) + toh - 1) / toh);

@@ -22,6 +22,7 @@ struct PoolParams {
     int toh;           // pool2d_rows_kernel: output rows per block
     int ih_rows;       // ... and input rows staged for them
     int group;         // pool_planes_kernel: threads per plane (power of two)
+    int ablate;        // measurement aid: 1 skip the staging loads, 2 skip the window evaluation
     int H, W, OH, OW, KH, KW, pad_t, pad_l, sh, sw, dh, dw;
     int mode;               // 0 max, 1 average
     int count_include_pad;  // average only
@@ -107,7 +108,8 @@ __global__ void __launch_bounds__(256) pool2d_rows_kernel(const PoolParams p) {
         const int ih_lo = oh0 * p.sh - p.pad_t;
         const char* xp = p.x + plane * p.H * static_cast<long long>(row_bytes);
         __syncthreads();  // the previous tile's readers are done
-        if (vec) {
+        if (p.ablate & 1) {
+        } else if (vec) {
             const int cpr = row_bytes >> 4;  // 16-byte chunks per row
             for (int id = threadIdx.x; id < p.ih_rows * cpr; id += blockDim.x) {
                 const int r = id / cpr;
@@ -133,7 +135,7 @@ __global__ void __launch_bounds__(256) pool2d_rows_kernel(const PoolParams p) {
         const int rows = min(p.toh, p.OH - oh0);
         const int pairs_per_row = (p.OW + 1) >> 1;
         const int kh_n = K ? K : p.KH, kw_n = K ? K : p.KW;
-        for (int id = threadIdx.x; id < rows * pairs_per_row; id += blockDim.x) {
+        for (int id = threadIdx.x; id < ((p.ablate & 2) ? 0 : rows * pairs_per_row); id += blockDim.x) {
             const int ohl = id / pairs_per_row;
             const int ow0 = (id - ohl * pairs_per_row) * 2;
             const int r0 = ohl * p.sh;  // first staged row of the window
@@ -202,6 +204,87 @@ __global__ void __launch_bounds__(256) pool2d_rows_kernel(const PoolParams p) {
                 if (ow0 + 1 < p.OW) PoolType<T>::store(p.y, o + 1, res[1]);
             }
         }
+    }
+}
+
+__device__ __forceinline__ __half __high2half_or_bf16(__half2 v) { return __high2half(v); }
+__device__ __forceinline__ __half __low2half_or_bf16(__half2 v) { return __low2half(v); }
+__device__ __forceinline__ __nv_bfloat16 __high2half_or_bf16(__nv_bfloat162 v) { return __high2bfloat16(v); }
+__device__ __forceinline__ __nv_bfloat16 __low2half_or_bf16(__nv_bfloat162 v) { return __low2bfloat16(v); }
+template <typename T, typename T2>
+__device__ __forceinline__ T2 pool_make2(T lo, T hi);
+template <>
+__device__ __forceinline__ __half2 pool_make2<__half, __half2>(__half lo, __half hi) { return __halves2half2(lo, hi); }
+template <>
+__device__ __forceinline__ __nv_bfloat162 pool_make2<__nv_bfloat16, __nv_bfloat162>(__nv_bfloat16 lo, __nv_bfloat16 hi) {
+    return __halves2bfloat162(lo, hi);
+}
+
+// The pooling layer of ResNet-style stems - max, 3 x 3, stride 2, one column of left padding,
+// 16-bit storage, rows that are multiples of eight elements - without per-tap work: a thread owns
+// eight consecutive outputs of one row. Per input row it loads the three 16-byte vectors that
+// hold columns 16j-8 .. 16j+15, takes the vertical maximum on packed pairs (two values per
+// instruction), and forms each output from one odd column and one packed pair:
+//     out[t] = max(x[16j-1+2t], x[16j+2t], x[16j+1+2t]),   t = 0..7.
+// About ten instructions per output instead of about two hundred in the generic kernel.
+// Vectors outside the image (first strip of a row, rows of the vertical padding) count as the
+// type's lowest value, exactly as taps outside the image do in the reference.
+template <typename T2>
+__device__ __forceinline__ T2 pool_bits_as(uint32_t v) {
+    return *reinterpret_cast<const T2*>(&v);
+}
+template <typename T2>
+__device__ __forceinline__ uint32_t pool_as_bits(T2 v) {
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+template <typename T, typename T2>
+__global__ void __launch_bounds__(256) maxpool3s2_strip_kernel(const PoolParams p, const uint32_t lowest2) {
+    const int spr = p.OW >> 3;  // strips per output row
+    const long long rows_total = p.planes * p.OH;
+    const long long total = rows_total * spr;
+    const int vpr = p.W >> 3;  // 16-byte vectors per input row
+    for (long long sid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; sid < total;
+         sid += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const long long orow = sid / spr;  // plane * OH + oh
+        const int j = static_cast<int>(sid - orow * spr);
+        const long long plane = orow / p.OH;
+        const int oh = static_cast<int>(orow - plane * p.OH);
+        const uint4* xrow0 = reinterpret_cast<const uint4*>(p.x) + plane * p.H * vpr;
+        // packed vertical maxima of columns 16j-8 .. 16j+15 (12 pairs)
+        uint32_t v[12];
+#pragma unroll
+        for (int k = 0; k < 12; ++k) v[k] = lowest2;
+#pragma unroll
+        for (int kh = 0; kh < 3; ++kh) {
+            const int ih = oh * 2 - p.pad_t + kh;
+            if (static_cast<unsigned>(ih) >= static_cast<unsigned>(p.H)) continue;
+            const uint4* xr = xrow0 + static_cast<long long>(ih) * vpr;
+#pragma unroll
+            for (int q = 0; q < 3; ++q) {
+                const int vi = 2 * j - 1 + q;  // vector index inside the row
+                if (static_cast<unsigned>(vi) >= static_cast<unsigned>(vpr)) continue;
+                const uint4 w = xr[vi];
+                v[4 * q + 0] = pool_as_bits(__hmax2(pool_bits_as<T2>(v[4 * q + 0]), pool_bits_as<T2>(w.x)));
+                v[4 * q + 1] = pool_as_bits(__hmax2(pool_bits_as<T2>(v[4 * q + 1]), pool_bits_as<T2>(w.y)));
+                v[4 * q + 2] = pool_as_bits(__hmax2(pool_bits_as<T2>(v[4 * q + 2]), pool_bits_as<T2>(w.z)));
+                v[4 * q + 3] = pool_as_bits(__hmax2(pool_bits_as<T2>(v[4 * q + 3]), pool_bits_as<T2>(w.w)));
+            }
+        }
+        // pair k holds columns 16j-8+2k, 16j-8+2k+1; output t needs the high half of pair 3+t
+        // (column 16j-1+2t) and both halves of pair 4+t
+        uint32_t out[4];
+#pragma unroll
+        for (int t = 0; t < 8; t += 2) {
+            T r[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const T2 left = pool_bits_as<T2>(v[3 + t + e]);
+                const T2 mid = pool_bits_as<T2>(v[4 + t + e]);
+                r[e] = __hmax(__high2half_or_bf16(left), __hmax(__low2half_or_bf16(mid), __high2half_or_bf16(mid)));
+            }
+            out[t >> 1] = pool_as_bits(pool_make2<T, T2>(r[0], r[1]));
+        }
+        reinterpret_cast<uint4*>(p.y)[sid] = make_uint4(out[0], out[1], out[2], out[3]);
     }
 }
 
