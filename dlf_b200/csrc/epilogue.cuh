@@ -206,16 +206,4 @@ __device__ __forceinline__ void drain_chunk(uint32_t trow, int ncols, float* par
     }
 }
 
-// fmt: FMT_F16 = 0, FMT_BF16 = 1, FMT_F32 = 2 (storage type of D)
-__device__ __forceinline__ void epilogue_run(int fmt, uint32_t trow, int ncols_total, char* ptr,
-                                             long long stride, bool row_ok, float alpha, float beta,
-                                             const char* bias, int lane) {
-    if (fmt == 2)
-        epilogue_dispatch<OUT_F32>(trow, ncols_total, ptr, stride, row_ok, alpha, beta, bias, lane);
-    else if (fmt == 0)
-        epilogue_dispatch<OUT_F16>(trow, ncols_total, ptr, stride, row_ok, alpha, beta, bias, lane);
-    else
-        epilogue_dispatch<OUT_BF16>(trow, ncols_total, ptr, stride, row_ok, alpha, beta, bias, lane);
-}
-
 }  // namespace dlfb200

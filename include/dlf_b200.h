@@ -172,8 +172,10 @@ int dlf_b200_device_status(int* device_status);
  * 0x400 a second accumulator only when three operand slots remain in tensor memory (default:
  * two), 0x800 no TMA for the fp32 B operand, 0x1000 no K-chunked fp32 accumulation, 0x2000 no
  * affine addressing for 1x1 filters, 0x4000 no TMA stores, 0x8000 never pack the filter bank of
- * a convolution. Bits 16 and up switch parts of a kernel off to time the rest (results are then
- * meaningless). */
+ * a convolution. Bits 16 and up are measurement aids: most switch a part of a kernel off to time the
+ * rest (results are then meaningless); 0x100 << 16 (pooling always through the generic
+ * one-thread-per-output kernel) and 0x4000 << 16 (no programmatic dependent launch after the
+ * filter-packing grid) keep results valid. */
 void dlf_b200_set_tuning(int force_bn, int force_generic_loader);
 
 /* Counts kernel launches made by this library in this process (all threads). */

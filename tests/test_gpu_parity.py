@@ -808,3 +808,34 @@ def test_pooling_argument_errors(lib):
         gdnn.max_pooling(X, Y, f)  # Y too small for the 3 x 3 output
     with pytest.raises(gb.BLASError):
         gdnn.max_pooling(X.half(), torch.zeros(1, 1, 3, 3, device="cuda"), f)  # mixed types
+
+
+@pytest.mark.parametrize("shape", [
+    # Cin, H, Cout, k, stride, pad: ResNet-50 layers that run on the tensor-memory-operand kernel
+    (3, 224, 64, 7, 2, 3), (64, 56, 64, 3, 1, 1), (128, 28, 128, 3, 1, 1), (256, 14, 256, 3, 1, 1),
+    (512, 7, 512, 3, 1, 1), (256, 14, 1024, 1, 1, 0), (1024, 14, 2048, 1, 2, 0), (2048, 7, 512, 1, 1, 0),
+])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+def test_conv2d_workspace_bound_covers_the_packed_filter_bank(lib, shape, dtype):
+    """dlf_b200_conv2d_workspace_bytes is an upper bound over the tilings the library may choose:
+    with that much scratch the filter bank is packed (two launches per call: packing + main);
+    with none the same call still works (one launch, loader warps gather the filter bank) and
+    gives the same bits."""
+    from dlf_b200 import gdnn
+    cin, h, cout, k, s, p = shape
+    X = torch.randn(2, cin, h, h, device="cuda").to(dtype)
+    W = (torch.randn(cout, cin, k, k, device="cuda") * 0.05).to(dtype)
+    f = gdnn.Filter2D(X.shape, W.shape).pads(p, p).strides(s, s)
+    Y = torch.empty(f.output_shape(), device="cuda", dtype=dtype)
+    n0 = lib.launch_count()
+    gdnn.conv2d_filter(X, W, Y, f)
+    assert lib.launch_count() - n0 == 2
+    lib.set_tuning(0, 0x8000)
+    try:
+        Y2 = torch.empty_like(Y)
+        n0 = lib.launch_count()
+        gdnn.conv2d_filter(X, W, Y2, f)
+        assert lib.launch_count() - n0 == 1
+    finally:
+        lib.set_tuning(0, 0)
+    assert torch.equal(Y, Y2)
