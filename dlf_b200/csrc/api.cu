@@ -325,7 +325,13 @@ int choose_bn_ts(const Problem& q, int num_sms, int max_bn, int a_cols, long lon
     return best;
 }
 
+// A launch below is checked with cudaGetLastError(), which also returns an error that an earlier,
+// unrelated runtime call of this host thread left behind (non-sticky errors stay until read).
+// Such a leftover is not this call's failure: it is read away before the first launch.
+inline void clear_stale_error() { (void)cudaGetLastError(); }
+
 int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
+    clear_stale_error();
     const int a_cols = q.es == 4 ? 64 : 32;
     const int BK = 128 / q.es;
     long long tiles_m = (q.M + kBM - 1) / kBM;
@@ -362,7 +368,8 @@ int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
     const int stage_bytes = bn * 128 * (q.es == 4 ? 2 : 1);
     const int sums_bytes = kc_blocks ? bn * 128 * 4 : 0;
     if (kc_blocks && bn > 128) return kUnexpectedError;
-    int stages = (kSmemPerBlockOptin - static_smem - 1024 - ktable_bytes - sums_bytes) / stage_bytes;
+    // the k table is padded to a multiple of 1024 in the layout below: count it that way here too
+    int stages = (kSmemPerBlockOptin - static_smem - 1024 - ((ktable_bytes + 1023) / 1024 * 1024) - sums_bytes) / stage_bytes;
     const int tmem_stages = (512 - acc_bufs * bn) / a_cols;
     if (stages > tmem_stages) stages = tmem_stages;
     if (stages > kMaxStages) stages = kMaxStages;
@@ -460,6 +467,10 @@ int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
     attr.val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = (tp.b_packed != nullptr && !(g_force_generic.load() & 0x40000000)) ? 1 : 0;
+    if (std::getenv("DLF_B200_DEBUG"))
+        std::fprintf(stderr, "dlf_b200: ts launch es=%d bn=%d stages=%d acc_bufs=%d grid=%u dyn_smem=%zu ktable=%d sums=%d packed=%d pending=%s\n",
+                     q.es, bn, stages, acc_bufs, grid, dyn_smem, ktable_bytes, sums_bytes, tp.b_packed != nullptr,
+                     cudaGetErrorString(cudaPeekAtLastError()));
     if (q.es == 2)
         CUDA_TRY(cudaLaunchKernelEx(&cfg, contraction_ts_kernel<2>, tp, tm_b));
     else
@@ -476,6 +487,7 @@ int launch(const Problem& q, cudaStream_t stream, DeviceState* preset = nullptr)
         rc = ensure_device(&st);
         if (rc != kSuccess) return rc;
     }
+    clear_stale_error();
     if (q.M > INT_MAX - 512 || q.N > INT_MAX - 512 || q.K > INT_MAX - 512 || q.batch > INT_MAX)
         return kInvalidDimension;
 
@@ -1099,6 +1111,7 @@ int launch_pool(int dtype, int mode, int count_include_pad, size_t batches, size
     p.x = static_cast<const char*>(x);
     p.y = static_cast<char*>(y);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    clear_stale_error();
     // the whole plane as one unpadded, undilated window: global pooling, one warp per plane
     const bool whole_plane = output_h == 1 && output_w == 1 && kernel_h == height && kernel_w == width &&
                              pad_top == 0 && pad_left == 0 && dilation_h == 1 && dilation_w == 1 &&

@@ -465,6 +465,7 @@ CONV_CASES = [
     (2, 5, 9, 26, 12, 2, 4, (0, 0, 1, 0), (1, 2), (1, 1), 1),       # strided row form: no left padding (shifts 0..1), KW = 4
     (1, 7, 8, 67, 24, 1, 8, (0, 1, 0, 5), (1, 4), (1, 1), 1),       # strided row form: stride_w 4, KW = 8, wide right padding
     (2, 3, 20, 33, 64, 7, 7, (3, 3, 3, 3), (2, 2), (1, 1), 1),      # stem shape with 64 output channels: 4 shifts x 64 = one 256-column tile
+    (2, 36, 25, 21, 36, 5, 7, (3, 0, 1, 3), (1, 1), (2, 1), 1),     # row form, 7 taps x 32 channels = 224 columns: in fp32 four stages would overflow shared memory by the table padding
 ]
 
 
