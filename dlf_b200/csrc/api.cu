@@ -251,6 +251,10 @@ int encode_map(const DeviceState& st, CUtensorMap* map, const GenOperand& op, in
 bool encode_output_map(const DeviceState& st, CUtensorMap* map, const Problem& q, unsigned box_cols) {
     const bool d_ok = q.es == 2 && q.beta == 0.0f && q.betas == nullptr && q.d_offs == nullptr &&
                       (reinterpret_cast<uintptr_t>(q.d) & 15u) == 0 && (q.ldd * q.es) % 16 == 0 &&
+                      // measured: a TMA store is clipped at the next 16-byte boundary after the
+                      // tensor's contiguous extent, not at the extent itself, so with a padded
+                      // leading dimension it would overwrite up to 7 elements of the padding
+                      (q.M * q.es) % 16 == 0 &&
                       (q.batch == 1 || (q.d_batch_stride * q.es) % 16 == 0) &&
                       q.ldd * q.es < (1ll << 40) && q.d_batch_stride * q.es < (1ll << 40) &&
                       !(g_force_generic.load() & 0x4000);
@@ -359,7 +363,11 @@ int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
     const int acc_bufs = ((512 - 2 * bn) / a_cols >= min_slots) ? 2 : 1;
     const long long num_kb = (q.K + BK - 1) / BK;
     int ktable_bytes = 0;
-    if (q.a.im2col || q.rc_kw) {
+    // 1x1 filters without padding address X affinely in k and need no k table
+    const bool pointwise = q.a.im2col && !q.rc_kw && q.g.KH == 1 && q.g.KW == 1 && q.g.pad_t == 0 &&
+                           q.g.pad_l == 0 && (q.g.OH - 1) * q.g.sh < q.g.H && (q.g.OW - 1) * q.g.sw < q.g.W &&
+                           !(g_force_generic.load() & 0x2000);
+    if ((q.a.im2col || q.rc_kw) && !pointwise) {
         const long long need = num_kb * BK * static_cast<long long>(sizeof(KEntry));
         if (need > 96 * 1024) return kNotImplemented;  // caller falls back to the smem-A kernel
         ktable_bytes = static_cast<int>((need + 15) & ~15ll);
@@ -413,9 +421,7 @@ int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
     p.status = st.status;
     p.ablate = g_force_generic.load() >> 16;
     tp.a_kind = q.rc_kw ? A_ROWCONV : (q.a.im2col ? A_IM2COL : (q.a.k_major ? A_DENSE_K : A_DENSE_MN));
-    tp.a_pointwise = tp.a_kind == A_IM2COL && q.g.KH == 1 && q.g.KW == 1 && q.g.pad_t == 0 && q.g.pad_l == 0 &&
-                     (q.g.OH - 1) * q.g.sh < q.g.H && (q.g.OW - 1) * q.g.sw < q.g.W &&
-                     !(g_force_generic.load() & 0x2000);
+    tp.a_pointwise = pointwise ? 1 : 0;
     tp.rc_kw = q.rc_kw;
     tp.rc_cpt = q.rc_cpt;
     tp.rc_T = q.rc_T;
@@ -1053,6 +1059,37 @@ int dlf_b200_conv2d_fused(int dtype, size_t batches, size_t channels, size_t hei
         if (rc != kSuccess) return rc;
         rc = launch_ts(*st, r, static_cast<cudaStream_t>(stream));
         if (rc != kNotImplemented) return rc;
+    }
+    // fp32 with a k table that would not fit (K = C*KH*KW > 12288, not row form, not 1x1): the
+    // loader-warp fallback accumulates all of K in one tensor-core accumulator, whose truncation
+    // error grows with K beyond the fp32 tolerance. Split the channels into ranges that fit the
+    // table instead and accumulate the ranges through beta = 1 (bias and residual enter with
+    // the first range, the ReLU leaves with the last).
+    const long long khw = static_cast<long long>(kernel_h) * kernel_w;
+    const bool affine_1x1 = kernel_h == 1 && kernel_w == 1 && pad_top == 0 && pad_left == 0 &&
+                            (output_h - 1) * stride_h < height && (output_w - 1) * stride_w < width &&
+                            !(g_force_generic.load() & 0x2000);  // needs no k table: one launch serves any K
+    if (q.es == 4 && K > 12288 && khw <= 12288 && path != 2 && !affine_1x1) {
+        DeviceState* st = nullptr;
+        int rc = ensure_device(&st);
+        if (rc != kSuccess) return rc;
+        const long long cpc = 12288 / khw;  // channels per range
+        for (long long c0 = 0; c0 < cg; c0 += cpc) {
+            const long long cc = std::min<long long>(cpc, cg - c0);
+            Problem r = q;
+            r.K = cc * khw;
+            r.a.base = q.a.base + c0 * static_cast<long long>(height) * width * q.es;
+            r.b.base = q.b.base + c0 * khw * q.es;
+            if (c0 > 0) {
+                r.beta = 1.f;
+                r.bias = nullptr;
+                r.resid = nullptr;
+            }
+            r.relu = (c0 + cc >= cg) ? q.relu : 0;
+            rc = launch_ts(*st, r, static_cast<cudaStream_t>(stream));
+            if (rc != kSuccess) return rc == kNotImplemented ? launch(q, static_cast<cudaStream_t>(stream)) : rc;
+        }
+        return kSuccess;
     }
     return launch(q, static_cast<cudaStream_t>(stream));
 }

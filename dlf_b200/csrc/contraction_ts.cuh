@@ -304,7 +304,7 @@ __global__ void __launch_bounds__(kTsThreads, 1)
             kt[k] = e;
         }
     }
-    if (tp.a_kind == A_IM2COL) {
+    if (tp.a_kind == A_IM2COL && !tp.a_pointwise) {
         // k -> (offset, dy, dx) table, filled cooperatively; k beyond K is never read as valid
         KEntry* kt = reinterpret_cast<KEntry*>(smem_raw);
         const int khw = p.g.KH * p.g.KW;

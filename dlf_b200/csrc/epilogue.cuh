@@ -160,7 +160,7 @@ __device__ __forceinline__ void epilogue_tile(uint32_t trow, int ncols_total, ch
         if (part != nullptr) {
 #pragma unroll
             for (int jj = 0; jj < 32; ++jj)
-                v[jj] = __float_as_uint(__uint_as_float(v[jj]) + part[(c0 + jj) * 128]);
+                if (c0 + jj < ncols_total) v[jj] = __float_as_uint(__uint_as_float(v[jj]) + part[(c0 + jj) * 128]);
         }
         const int nc = min(32, ncols_total - c0);
         epilogue_chunk<OUT, HAS_BETA, HAS_BIAS>(v, ptr + c0 * stride, stride, nc, row_ok, alpha,
@@ -196,12 +196,16 @@ __device__ __forceinline__ void drain_chunk(uint32_t trow, int ncols, float* par
         uint32_t v[32];
         ptx::tmem_ld_32x32(trow + c0, v);
         ptx::tmem_ld_wait();
+        // ncols need not be a multiple of 32 (row form: taps x channels, e.g. 7 x 16 = 112): the
+        // sum array has exactly ncols rows
         if (first) {
 #pragma unroll
-            for (int jj = 0; jj < 32; ++jj) part[(c0 + jj) * 128] = __uint_as_float(v[jj]);
+            for (int jj = 0; jj < 32; ++jj)
+                if (c0 + jj < ncols) part[(c0 + jj) * 128] = __uint_as_float(v[jj]);
         } else {
 #pragma unroll
-            for (int jj = 0; jj < 32; ++jj) part[(c0 + jj) * 128] += __uint_as_float(v[jj]);
+            for (int jj = 0; jj < 32; ++jj)
+                if (c0 + jj < ncols) part[(c0 + jj) * 128] += __uint_as_float(v[jj]);
         }
     }
 }

@@ -294,6 +294,25 @@ def test_gemm_tma_store_box_widths(lib, bn, n):
     assert np.array_equal(outs[0], outs[1])
 
 
+@pytest.mark.parametrize("m", [85, 88, 381])
+def test_gemm_padded_c_keeps_its_padding_with_tma_compatible_strides(lib, m):
+    """C has a leading dimension that is a multiple of 16 bytes but a contiguous extent that is
+    not (m = 85 or 381 with ld = m + 3): a TMA store would be clipped only at the next 16-byte
+    boundary and overwrite the padding, so such outputs must take the plain stores. The helper
+    checks that nothing outside the m x n window changes."""
+    gb = _gb()
+    for dtype in (torch.float16, torch.bfloat16):
+        got, ref = _gemm_case(np.random.default_rng(m), dtype, gb.Layout.ColMajor, gb.Transpose.NoTrans,
+                              gb.Transpose.Trans, m, 200, 136, -2.0, 0.0, (3, 0, 3), (0, 8, 0))
+        assert max_rel(got, ref) <= HALF_TOL
+        # the same for loads: K-major operands whose rows hold k = 133 values and 3 of padding
+        # (ld = 136): the TMA loads must zero-fill from element 133 on, not from the next
+        # 16-byte boundary
+        got, ref = _gemm_case(np.random.default_rng(m + 1), dtype, gb.Layout.RowMajor, gb.Transpose.NoTrans,
+                              gb.Transpose.Trans, 96, 72, 133, 1.0, 0.0, (3, 3, 0), (8, 0, 0))
+        assert max_rel(got, ref) <= HALF_TOL
+
+
 @pytest.mark.parametrize("m,n,k", [(512, 512, 264), (300, 520, 200), (1000, 264, 72)])
 def test_gemm_cta_pair_kernel(lib, m, n, k):
     """The cta_group::2 variant (two CTAs share 256 x 256 tiles; opt-in, tuning bit 0x200) on all
@@ -466,6 +485,8 @@ CONV_CASES = [
     (1, 7, 8, 67, 24, 1, 8, (0, 1, 0, 5), (1, 4), (1, 1), 1),       # strided row form: stride_w 4, KW = 8, wide right padding
     (2, 3, 20, 33, 64, 7, 7, (3, 3, 3, 3), (2, 2), (1, 1), 1),      # stem shape with 64 output channels: 4 shifts x 64 = one 256-column tile
     (2, 36, 25, 21, 36, 5, 7, (3, 0, 1, 3), (1, 1), (2, 1), 1),     # row form, 7 taps x 32 channels = 224 columns: in fp32 four stages would overflow shared memory by the table padding
+    (3, 96, 7, 7, 32, 7, 7, (3, 1, 1, 1), (1, 1), (1, 1), 1),       # row form, K' = 672 chunked in fp32 with 7 taps x 16 channels = 112 columns: the sum array is not a multiple of 32 columns
+    (2, 120, 9, 10, 24, 5, 5, (2, 2, 2, 2), (1, 1), (1, 1), 1),     # same with 5 taps x 16 channels = 80 columns
 ]
 
 
@@ -840,3 +861,51 @@ def test_conv2d_workspace_bound_covers_the_packed_filter_bank(lib, shape, dtype)
     finally:
         lib.set_tuning(0, 0)
     assert torch.equal(Y, Y2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_conv2d_very_long_k_falls_back_to_shared_memory_operands(lib, dtype):
+    """K = C*KH*KW = 12600 needs a 100 KB k table, more than the tensor-memory-operand kernel
+    reserves: the call must take the loader-warp kernel with both operands in shared memory by
+    itself (dilation_w = 2 keeps it off the row form) and still meet the tolerance."""
+    from dlf_b200 import gdnn
+    rng = np.random.default_rng(5)
+    N, C, H, W, Co, KH, KW = 1, 1400, 6, 9, 24, 3, 3
+    X = _round_to(rng.normal(size=(N, C, H, W)).astype(np.float32), dtype)
+    Wt = _round_to((rng.normal(size=(Co, C, KH, KW)) / np.sqrt(C * KH * KW)).astype(np.float32), dtype)
+    pads, strides, dil = (1, 2, 1, 2), (1, 1), (1, 2)
+    ref = oracle.conv2d(X, Wt, pads=pads, strides=strides, dilations=dil, wide=True)
+    f = gdnn.Filter2D(X.shape, Wt.shape).pads(*pads).strides(*strides).dilations(*dil)
+    Y = torch.full(f.output_shape(), float("nan"), dtype=dtype, device="cuda")
+    gdnn.conv2d_filter(torch.from_numpy(X).to(dtype).cuda(), torch.from_numpy(Wt).to(dtype).cuda(), Y, f)
+    got = Y.float().cpu().numpy()
+    if dtype == torch.float32:
+        assert rel_fro(got, ref) <= FP32_TOL
+    else:
+        assert max_rel(got, ref) <= HALF_TOL
+    assert lib.device_status() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("stride", [1, 2])
+def test_conv2d_pointwise_with_very_many_channels(lib, dtype, stride):
+    """A 1x1 filter over 13000 channels: K is beyond what a k table could hold, but affine
+    addressing needs none, so the call stays on the tensor-memory-operand kernel (packing launch
+    + one main launch) and, in fp32, keeps its K-chunked accumulation."""
+    from dlf_b200 import gdnn
+    rng = np.random.default_rng(9)
+    N, C, H, W, Co = 2, 13000, 5, 6, 40
+    X = _round_to(rng.normal(size=(N, C, H, W)).astype(np.float32), dtype)
+    Wt = _round_to((rng.normal(size=(Co, C, 1, 1)) / np.sqrt(C)).astype(np.float32), dtype)
+    ref = oracle.conv2d(X, Wt, strides=(stride, stride), wide=True)
+    f = gdnn.Filter2D(X.shape, Wt.shape).strides(stride, stride)
+    Y = torch.full(f.output_shape(), float("nan"), dtype=dtype, device="cuda")
+    n0 = lib.launch_count()
+    gdnn.conv2d_filter(torch.from_numpy(X).to(dtype).cuda(), torch.from_numpy(Wt).to(dtype).cuda(), Y, f)
+    assert lib.launch_count() - n0 == 2
+    got = Y.float().cpu().numpy()
+    if dtype == torch.float32:
+        assert rel_fro(got, ref) <= FP32_TOL
+    else:
+        assert max_rel(got, ref) <= HALF_TOL
+    assert lib.device_status() == 0
