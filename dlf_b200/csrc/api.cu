@@ -347,6 +347,9 @@ int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
     int bn = choose_bn_ts(q, st.num_sms, kc_blocks ? 128 : 256, a_cols, num_kb_all);
     const int forced = g_force_bn.load();
     if (forced >= 64 && forced <= (kc_blocks ? 128 : 256) && forced % 32 == 0) bn = forced;
+    // an MN-major B tile is made of whole groups of BK columns (the UMMA reads all k-rows of the
+    // last group it touches): a width that ends inside a group would make it read past the stage
+    if (!q.b.k_major && bn % BK != 0) bn = bn / BK * BK;
     long long tiles_n = (q.N + bn - 1) / bn;
     if (q.rc_kw) {  // tile = 4 warps x rc_T output positions by rc_cpt channels (x rc_kw columns)
         bn = q.rc_cpt * q.rc_kw;
@@ -1155,10 +1158,11 @@ int launch_pool(int dtype, int mode, int count_include_pad, size_t batches, size
                              !((g_force_generic.load() >> 16) & 0x100);
     constexpr int kPoolSmem = 48 * 1024;  // static limit: no opt-in needed
     const long long plane_bytes = static_cast<long long>(height) * width * es;
-    if (whole_plane && plane_bytes * 8 <= kPoolSmem) {
-        // small planes: 256 / group planes per block staged through shared memory
+    if (whole_plane && plane_bytes * 8 + 16 <= kPoolSmem) {
+        // small planes: 256 / group planes per block staged through shared memory (+16 bytes of
+        // alignment slack, counted against the 48 KB limit)
         int group = 1;
-        while ((256 / group) * plane_bytes > kPoolSmem) group *= 2;
+        while ((256 / group) * plane_bytes + 16 > kPoolSmem) group *= 2;
         p.group = group;
         const long long ppb = 256 / group;
         const long long blocks = (p.planes + ppb - 1) / ppb;

@@ -251,6 +251,12 @@ def test_tensor_memory_operand_kernel_tile_widths(lib, bn, flags):
             got, ref = _gemm_case(np.random.default_rng(bn), torch.float16, gb.Layout.ColMajor,
                                   ta, gb.Transpose.NoTrans, 390, 500, 200, 1.0, 0.0, (0, 0, 0), (0, 0, 0))
             assert max_rel(got, ref) <= HALF_TOL
+        # B stored n-contiguous (MN-major tile made of whole 64-column groups: widths that end
+        # inside a group are rounded down), odd leading dimensions keep it off the TMA kernel
+        got, ref = _gemm_case(np.random.default_rng(bn + 1), torch.float16, gb.Layout.RowMajor,
+                              gb.Transpose.Trans, gb.Transpose.NoTrans, 281, 303, 323, 0.125, 0.0,
+                              (0, 0, 0), (0, 0, 0))
+        assert max_rel(got, ref) <= HALF_TOL
         got, ref = _gemm_case(np.random.default_rng(bn), torch.float32, gb.Layout.RowMajor,
                               gb.Transpose.Trans, gb.Transpose.NoTrans, 300, 520, 200, 0.5, 0.5,
                               (0, 0, 0), (0, 0, 0))
@@ -773,6 +779,7 @@ POOL_CASES = [
     (2, 4, 9, 9, 5, 5, (4, 4, 4, 4), (3, 3), (1, 1)),         # windows mostly in the padding
     (4, 7, 7, 7, 7, 7, (0, 0, 0, 0), (7, 7), (1, 1)),         # whole plane: one-warp-per-plane reduction
     (2, 3, 4, 5, 4, 5, (0, 0, 0, 0), (1, 1), (1, 1)),         # whole plane smaller than a warp
+    (3, 14, 8, 24, 8, 24, (0, 0, 0, 0), (8, 24), (1, 1)),     # whole plane of 768 bytes in fp32: 64 planes fill the 48 KB of staging exactly
 ]
 
 
