@@ -40,6 +40,13 @@ def _worker(rank, world, port, m, n, k, trans_a, out):
                            backend=OracleBlas())
     ref = 0.5 * ((A.t() if trans_a else A).double() @ B.double()) + 0.5 * C0.double()
     err = float((C.double() - ref).norm() / ref.norm())
+    if m % (world * 4) == 0:
+        # the panel-wise form (all-gather of a finished panel while the next is computed; on the
+        # CPU the two simply alternate) must give the same C on every rank
+        C2 = C0.clone()
+        shard.gemm_row_sharded_overlapped(ta, Transpose.NoTrans, 0.5, A, B, 0.5, C2, world, rank, 4,
+                                          backend=OracleBlas())
+        err = max(err, float((C2.double() - ref).norm() / ref.norm()))
     # conv-style batch split: slabs are disjoint and cover the batch
     start, cnt = shard.split(11, world, rank)
     gathered = [None] * world
