@@ -230,7 +230,7 @@ class GemmWorkload(Workload):
         A = self.A[j].view(self.k, self.m) if self.ta else self.A[j].view(self.m, self.k)
         B = self.B[j].view(self.n, self.k) if self.tb else self.B[j].view(self.k, self.n)
         C = self.C[j].view(self.m, self.n)
-        if self.m % (world * 4 * 128) == 0:
+        if getattr(self, "overlap_gather", False) and self.m % (world * 4 * 128) == 0:
             # four panels: the all-gather of a finished panel overlaps the next panel's GEMM
             shard.gemm_row_sharded_overlapped(ta, tb, self.alpha, A, B, self.beta, C, world, rank, 4)
         else:
@@ -463,6 +463,8 @@ def main():
     ap.add_argument("--headline-only", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=None, help="images per GPU for conv_c2 (profiling: a small case)")
+    ap.add_argument("--overlap-gather", action="store_true",
+                    help="row-sharded GEMM: all-gather finished panels while the next panel is computed")
     ap.add_argument("--kernel-only", action="store_true",
                     help="only the timed kernel loop: no end-to-end leg, parity check, CPU baseline or extras")
     args = ap.parse_args()
@@ -499,6 +501,7 @@ def main():
         table["batched_c4_b_" + tag] = (lambda tag=tag, ta=ta, tb=tb: GemmWorkload(
             "bgemm_f16_b1024_512x64x512_" + tag, "f16", 512, 64, 512, batch=1024, ta=ta, tb=tb, alpha=0.125))
     w = table[args.workload]()
+    w.overlap_gather = args.overlap_gather
     sets = w.sets_needed()
     # a single (unbatched) GEMM is sharded by rows of C with an all-gather: strong scaling, and
     # every rank must hold the same operands
@@ -575,7 +578,8 @@ def main():
             "scaling": "strong" if row_sharded else "weak",
             "vs_baseline": None, "dtype": w.dtype, "data": "synthetic",
             "config": {"workload": w.name, "per_gpu_batch": getattr(w, "shape", {}).get("N"),
-                       "sharding": ("rows of C per rank in four panels; the NCCL all-gather of a panel overlaps the next panel's GEMM" if row_sharded else
+                       "sharding": (("rows of C per rank in four panels; the NCCL all-gather of a panel overlaps the next panel's GEMM"
+                                     if args.overlap_gather else "rows of C per rank + NCCL all-gather of the row blocks") if row_sharded else
                                     "batch per rank, no collective") if world > 1 else "single GPU",
                        "l2": "rotating %d input/output buffer sets (%.0f MB > 126 MB L2)" % (
                            sets, sets * (getattr(w, "x_bytes", w.bytes) + getattr(w, "y_bytes", 0)) / 1e6),
