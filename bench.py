@@ -463,9 +463,8 @@ def main():
     ap.add_argument("--headline-only", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=None, help="images per GPU for conv_c2 (profiling: a small case)")
-    ap.add_argument("--no-overlap-gather", dest="overlap_gather", action="store_false",
-                    help="row-sharded GEMM: one all-gather after the whole row block instead of all-gathering "
-                         "finished panels while the next panel is computed")
+    ap.add_argument("--overlap-gather", action="store_true",
+                    help="row-sharded GEMM: all-gather finished panels while the next panel is computed")
     ap.add_argument("--kernel-only", action="store_true",
                     help="only the timed kernel loop: no end-to-end leg, parity check, CPU baseline or extras")
     args = ap.parse_args()
