@@ -74,6 +74,45 @@ std::atomic<int> g_force_generic{0};
         if (e__ != cudaSuccess) return static_cast<int>(e__); \
     } while (0)
 
+// The device a call works on is the one its stream belongs to (the reference binds a queue to its
+// context's device, gpgpu/src/gpgpu_cu.cpp:174-204), not whatever device happens to be current on
+// the calling thread. The guard makes that device current for the duration of the call and puts
+// the previous one back; the legacy default stream (null) means the current device.
+struct StreamDevice {
+    int dev = 0;
+    int prev = -1;
+    int rc = kSuccess;
+    explicit StreamDevice(cudaStream_t s) {
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) {
+            rc = static_cast<int>(e);
+            return;
+        }
+        if (s != nullptr && s != cudaStreamLegacy && s != cudaStreamPerThread) {
+            int sd = dev;
+            e = cudaStreamGetDevice(s, &sd);
+            if (e != cudaSuccess) {
+                rc = static_cast<int>(e);
+                return;
+            }
+            if (sd != dev) {
+                e = cudaSetDevice(sd);
+                if (e != cudaSuccess) {
+                    rc = static_cast<int>(e);
+                    return;
+                }
+                prev = dev;
+                dev = sd;
+            }
+        }
+    }
+    ~StreamDevice() {
+        if (prev >= 0) (void)cudaSetDevice(prev);
+    }
+    StreamDevice(const StreamDevice&) = delete;
+    StreamDevice& operator=(const StreamDevice&) = delete;
+};
+
 int ensure_device(DeviceState** out) {
     int dev = 0;
     CUDA_TRY(cudaGetDevice(&dev));
@@ -196,6 +235,7 @@ struct Problem {
     // caller-provided scratch for the packed filter bank of a convolution (may be null)
     unsigned char* pack_ws = nullptr;
     size_t pack_ws_bytes = 0;
+    bool no_ts = false;  // convolution whose taps overflow the k table's 16/32-bit fields
 };
 
 bool tma_ok(const GenOperand& op, int es, long long rows, long long K, long long batch) {
@@ -274,7 +314,7 @@ bool encode_output_map(const DeviceState& st, CUtensorMap* map, const Problem& q
     return r == CUDA_SUCCESS;
 }
 
-// Tile width. tcgen05.mma with M = 128 was measured (back-to-back issue, this GPU) at about
+// Tile width. tcgen05.mma with M = 128 was measured (back-to-back issue, on a B200) at about
 // 112-116 clocks for any N <= 128, 171 clocks for N = 256 with both operands in shared memory and
 // 138 clocks for N = 256 with A in tensor memory: narrow tiles waste most of the tensor pipe.
 // Pick the width that minimises (waves of tiles) x (clocks per UMMA of that width).
@@ -505,7 +545,7 @@ int launch(const Problem& q, cudaStream_t stream, DeviceState* preset = nullptr)
                          tma_ok(q.b, q.es, q.N, q.K, q.batch);
     // A through tensor memory: every convolution and every fp32 product (see contraction_ts.cuh)
     const int force_path = g_force_generic.load() & 0xff;
-    if (force_path != 2 && !use_tma && (q.a.im2col || q.es == 4 || force_path == 3)) {
+    if (force_path != 2 && !q.no_ts && !use_tma && (q.a.im2col || q.es == 4 || force_path == 3)) {
         rc = launch_ts(*st, q, stream);
         if (rc != kNotImplemented) return rc;  // else: im2col table too large, use the smem-A kernel
     }
@@ -548,8 +588,6 @@ int launch(const Problem& q, cudaStream_t stream, DeviceState* preset = nullptr)
         p.bias_stride = q.bias_stride;
         p.resid = q.resid;
         p.relu = q.relu;
-    p.resid = q.resid;
-    p.relu = q.relu;
         p.g = q.g;
         p.status = st->status;
         CUtensorMap tm_a, tm_b, tm_d;
@@ -574,6 +612,7 @@ int launch(const Problem& q, cudaStream_t stream, DeviceState* preset = nullptr)
         cfg.numAttrs = 1;
         CUDA_TRY(cudaLaunchKernelEx(&cfg, contraction_kernel<2, true, true>, p, tm_a, tm_b, tm_d));
         g_launches.fetch_add(1);
+        CUDA_TRY(cudaGetLastError());
         return kSuccess;
     }
     const long long tiles_n = (q.N + bn - 1) / bn;
@@ -782,6 +821,8 @@ int dlf_b200_gemm(int dtype, int layout, int trans_a, int trans_b, size_t m, siz
     if (alpha == nullptr || beta == nullptr) return kInvalidValue;
     q.alpha = scalar_to_float(q.fmt, alpha);
     q.beta = scalar_to_float(q.fmt, beta);
+    StreamDevice sd(static_cast<cudaStream_t>(stream));
+    if (sd.rc != kSuccess) return sd.rc;
     return launch(q, static_cast<cudaStream_t>(stream));
 }
 
@@ -802,6 +843,8 @@ int dlf_b200_gemm_strided_batched(int dtype, int layout, int trans_a, int trans_
     (row ? q.b : q.a).batch_stride = static_cast<long long>(a_stride);
     (row ? q.a : q.b).batch_stride = static_cast<long long>(b_stride);
     q.d_batch_stride = static_cast<long long>(c_stride);
+    StreamDevice sd(static_cast<cudaStream_t>(stream));
+    if (sd.rc != kSuccess) return sd.rc;
     return launch(q, static_cast<cudaStream_t>(stream));
 }
 
@@ -842,6 +885,8 @@ int dlf_b200_gemm_batched(int dtype, int layout, int trans_a, int trans_b, size_
         h_beta[i] = scalar_to_float(q.fmt, static_cast<const char*>(betas) + i * q.es);
     }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    StreamDevice sd(s);
+    if (sd.rc != kSuccess) return sd.rc;
     // pageable source: the runtime stages it before returning, so `host` may go out of scope
     CUDA_TRY(cudaMemcpyAsync(workspace, host.data(), need, cudaMemcpyHostToDevice, s));
     char* w = static_cast<char*>(workspace);
@@ -867,6 +912,8 @@ int dlf_b200_gemm_batched_noalloc(int dtype, int layout, int trans_a, int trans_
     Problem q;
     int rc = setup_gemm(q, dtype, layout, trans_a, trans_b, m, n, k, a, a_ld, b, b_ld, c, c_ld);
     if (rc != kSuccess) return rc;
+    StreamDevice sd(static_cast<cudaStream_t>(stream));
+    if (sd.rc != kSuccess) return sd.rc;
     NoAllocDevice* nd = nullptr;
     rc = noalloc_device(&nd);  // first call on a device: looks up the static arrays' addresses
     if (rc != kSuccess) return rc;
@@ -952,6 +999,15 @@ int dlf_b200_conv2d_fused(int dtype, size_t batches, size_t channels, size_t hei
         dilation_w >= lim || static_cast<long long>(height) * width >= INT_MAX)
         return kInvalidDimension;
 
+    // The k table of the tensor-memory-operand kernel keeps kh*dilation_h and kw*dilation_w as
+    // 16-bit values and the offset of a tap inside one image's channel group as a 32-bit one;
+    // a convolution beyond either takes the shared-memory-operand kernel, which uses wide indices.
+    const bool ktable_fits = (kernel_h - 1) * dilation_h <= 32767 && (kernel_w - 1) * dilation_w <= 32767 &&
+                             cg * static_cast<long long>(height) * width < INT_MAX;
+    q.no_ts = !ktable_fits;
+    StreamDevice sd(static_cast<cudaStream_t>(stream));
+    if (sd.rc != kSuccess) return sd.rc;
+
     // A 1x1, stride-1, unpadded convolution is a batched GEMM over the images,
     //     Y[b] (Cout x P) = W (Cout x Cin) * X[b] (Cin x P),
     // exactly the reference's convWithIm2Col shortcut (gpgpu/src/gdnn.cpp:1512-1559: weights
@@ -1021,7 +1077,7 @@ int dlf_b200_conv2d_fused(int dtype, size_t batches, size_t channels, size_t hei
     // Row form (see contraction_ts.cuh): horizontal taps become output columns of the GEMM. With
     // stride_w = sw the input columns split into sw phases that join the channels in K, and the
     // taps become the shifts d = floor((kw - pad_left) / sw).
-    const int path = g_force_generic.load() & 0xff;
+    const int path = ktable_fits ? (g_force_generic.load() & 0xff) : 2;
     const long long sw = static_cast<long long>(stride_w);
     const long long pl = static_cast<long long>(pad_left);
     auto floor_div = [](long long a, long long b) { return a >= 0 ? a / b : -((-a + b - 1) / b); };
@@ -1128,6 +1184,8 @@ int launch_pool(int dtype, int mode, int count_include_pad, size_t batches, size
         dilation_w >= lim || static_cast<long long>(height) * width >= INT_MAX ||
         static_cast<long long>(output_h) * output_w >= INT_MAX)
         return kInvalidDimension;
+    StreamDevice sd(static_cast<cudaStream_t>(stream));
+    if (sd.rc != kSuccess) return sd.rc;
     DeviceState* st = nullptr;
     int rc = ensure_device(&st);
     if (rc != kSuccess) return rc;
@@ -1273,23 +1331,26 @@ const char* dlf_b200_status_string(int status) {
 }
 
 int dlf_b200_device_status(int* device_status) {
-    DeviceState* st = nullptr;
-    int rc = ensure_device(&st);
-    if (rc != kSuccess) return rc;
-    CUDA_TRY(cudaDeviceSynchronize());
-    int v = 0;
-    CUDA_TRY(cudaMemcpy(&v, st->status, sizeof(int), cudaMemcpyDeviceToHost));
-    if (v != 0) CUDA_TRY(cudaMemset(st->status, 0, sizeof(int)));
+    // Reads (and clears) the status words of the current device that exist already; it sets
+    // nothing up and allocates nothing, so it also works for a process that only ever uses
+    // dlf_b200_gemm_batched_noalloc and has no device memory to spare.
+    int dev = 0;
+    CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return kInvalidValue;
+    int* words[2] = {nullptr, nullptr};
     {
-        int dev = 0;
-        CUDA_TRY(cudaGetDevice(&dev));
-        NoAllocDevice& nd = g_noalloc_dev[dev];
-        if (nd.ready) {  // kernels launched by dlf_b200_gemm_batched_noalloc report here
-            int w = 0;
-            CUDA_TRY(cudaMemcpy(&w, nd.st.status, sizeof(int), cudaMemcpyDeviceToHost));
-            if (w != 0) CUDA_TRY(cudaMemset(nd.st.status, 0, sizeof(int)));
-            v |= w;
-        }
+        std::lock_guard<std::mutex> lock(g_mu);
+        if (g_dev[dev].ready) words[0] = g_dev[dev].status;
+        if (g_noalloc_dev[dev].ready) words[1] = g_noalloc_dev[dev].st.status;
+    }
+    int v = 0;
+    if (words[0] != nullptr || words[1] != nullptr) CUDA_TRY(cudaDeviceSynchronize());
+    for (int* w : words) {
+        if (w == nullptr) continue;
+        int x = 0;
+        CUDA_TRY(cudaMemcpy(&x, w, sizeof(int), cudaMemcpyDeviceToHost));
+        if (x != 0) CUDA_TRY(cudaMemset(w, 0, sizeof(int)));
+        v |= x;
     }
     if (device_status) *device_status = v;
     return kSuccess;

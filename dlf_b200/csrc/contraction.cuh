@@ -399,18 +399,22 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
 #pragma unroll
                             for (int jj = 0; jj < 32; ++jj) v[jj] = __float_as_uint(alpha * __uint_as_float(v[jj]));
                         }
-                        const float floor_v = p.relu ? 0.0f : __int_as_float(0xff800000);  // -inf: no clamp
+                        // the clamp only exists under ReLU: fmaxf drops a NaN operand, so an
+                        // unconditional fmaxf(r, -inf) would turn NaN results into -inf
+                        const bool relu = p.relu != 0;
                         if (p.fmt == FMT_F16) {
 #pragma unroll
                             for (int jj = 0; jj < 32; ++jj) {
-                                const float r = fmaxf(__uint_as_float(v[jj]) + __shfl_sync(0xffffffffu, bv, jj), floor_v);
+                                float r = __uint_as_float(v[jj]) + __shfl_sync(0xffffffffu, bv, jj);
+                                r = relu ? fmaxf(r, 0.0f) : r;
                                 const unsigned short h = __half_as_ushort(__float2half_rn(r));
                                 asm volatile("st.shared.u16 [%0], %1;" ::"r"(sbuf + jj * 64u), "h"(h) : "memory");
                             }
                         } else {
 #pragma unroll
                             for (int jj = 0; jj < 32; ++jj) {
-                                const float r = fmaxf(__uint_as_float(v[jj]) + __shfl_sync(0xffffffffu, bv, jj), floor_v);
+                                float r = __uint_as_float(v[jj]) + __shfl_sync(0xffffffffu, bv, jj);
+                                r = relu ? fmaxf(r, 0.0f) : r;
                                 const unsigned short h = __bfloat16_as_ushort(__float2bfloat16_rn(r));
                                 asm volatile("st.shared.u16 [%0], %1;" ::"r"(sbuf + jj * 64u), "h"(h) : "memory");
                             }

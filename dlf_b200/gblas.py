@@ -214,13 +214,16 @@ def gemmBatched(layout, a_transpose, b_transpose, m, n, k, alphas, a_buffer, a_o
     _validate(layout, a_transpose, b_transpose, m, n, k, a_buffer, list(a_offsets), a_ld,
               b_buffer, list(b_offsets), b_ld, c_buffer, list(c_offsets), c_ld)
     need = lib().dlf_b200_gemm_batched_workspace_bytes(batch_count)
+    s, sp = _stream(queue)
     if workspace is None:
         workspace = torch.empty(max(need, 8), dtype=torch.uint8, device=c_buffer.device)
+        # the tables are read by work queued on `s`, which may not be the allocator's current
+        # stream: the block must not be handed out again before that work has passed
+        workspace.record_stream(s)
     arr = ctypes.c_size_t * batch_count
     ao, bo, co = arr(*map(int, a_offsets)), arr(*map(int, b_offsets)), arr(*map(int, c_offsets))
     al_keep, al = _scalars(alphas, c_buffer.dtype)
     be_keep, be = _scalars(betas, c_buffer.dtype)
-    s, sp = _stream(queue)
     if event is not None:
         event.start.record(s)
     rc = lib().dlf_b200_gemm_batched(

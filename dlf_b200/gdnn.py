@@ -91,7 +91,11 @@ def _workspace(device, stream, nbytes):
     key = (device.index, stream.cuda_stream)
     buf = _WORKSPACES.get(key)
     if buf is None or buf.numel() < nbytes:
+        if buf is not None:
+            # earlier convolutions queued on this stream may still read the old buffer
+            buf.record_stream(stream)
         buf = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+        buf.record_stream(stream)
         _WORKSPACES[key] = buf
     return buf
 

@@ -169,7 +169,7 @@ def matmul(A, B, C=None, alpha=1, beta=0, backend=None, trace=None):
         ldb = max(ldb, n)
 
     if _lhs_need_reorder(m, n, k, lda, incA):
-        tmp = A.contiguous() if not a_vec else A.contiguous()
+        tmp = A.contiguous()
         vA, _, _, _ = _broadcast(tmp, B)
         lda, incA = k, 1
     if _rhs_need_reorder(k, n, ldb, incB):
@@ -257,6 +257,64 @@ def dot(A, B, backend=None):
     Bm = B.movedim(-2, 0).reshape(b_shape[-2], -1)
     out = matmul(A2, Bm.contiguous() if not Bm.is_contiguous() else Bm, backend=backend)
     return out.reshape(a_shape[:-1] + b_shape[:-2] + b_shape[-1:])
+
+
+def _matrix_chain_order(dims):
+    """detail::matrix_chain_order (linalg_detail.h:1701-1720): split table of the cheapest
+    parenthesisation of a chain whose i-th matrix is dims[i] x dims[i+1]."""
+    n = len(dims) - 1
+    inf = float("inf")
+    cost = [[0 if i == j else inf for j in range(n)] for i in range(n)]
+    split = [[0] * n for _ in range(n)]
+    for length in range(1, n):
+        for i in range(n - length):
+            j = i + length
+            for k in range(i, j):
+                c = cost[i][k] + cost[k + 1][j] + dims[i] * dims[k + 1] * dims[j + 1]
+                if c < cost[i][j]:
+                    cost[i][j] = c
+                    split[i][j] = k
+    return split
+
+
+def multi_dot(*args, backend=None):
+    """dlf::multi_dot (linalg.h:569-603): the product of a chain of matrices, evaluated in the
+    order that costs the fewest multiplications. A 1-D first argument is a row vector, a 1-D last
+    argument a column vector, everything in between must be 2-D (linalg_detail.h:1664-1699)."""
+    if len(args) == 1 and isinstance(args[0], (list, tuple)):
+        args = tuple(args[0])
+    if len(args) == 0:
+        raise ValueError("multi_dot: at least 1 argument is required")
+    if len(args) == 1:
+        return args[0]
+    first = args[0]
+    if first.dim() == 1:
+        dims = [1, first.shape[0]]
+    elif first.dim() == 2:
+        dims = [first.shape[0], first.shape[1]]
+    else:
+        raise ShapeError("multi_dot: the first argument must be a vector or a matrix")
+    n = dims[1]
+    for i, t in enumerate(args[1:], start=1):
+        if t.dim() == 2:
+            if t.shape[0] != n:
+                raise ShapeError("multi_dot: incompatible shape")
+            n = t.shape[1]
+        elif i == len(args) - 1 and t.dim() == 1:
+            if t.shape[0] != n:
+                raise ShapeError("multi_dot: incompatible shape")
+            n = 1
+        else:
+            raise ShapeError("multi_dot: the arguments in the middle must be matrices")
+        dims.append(n)
+    split = _matrix_chain_order(dims)
+
+    def product(i, j):
+        if i == j:
+            return args[i]
+        return matmul(product(i, split[i][j]), product(split[i][j] + 1, j), backend=backend)
+
+    return product(0, len(args) - 1)
 
 
 def conv2d(X, W, Y, filt, bias=None, backend=None):

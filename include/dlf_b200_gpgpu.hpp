@@ -116,14 +116,76 @@ private:
     size_t size_ = 0;
 };
 
-// LIFO scratch taken from the context in the reference (gpgpu/src/gpgpu.cpp:189-214); here a
-// plain owned allocation with the same offset()/size() view.
+// Scratch that lives as long as one call: a LIFO slab like the reference's per-context pool
+// (rawContext::getTemporaryBuffer / releaseTemporaryBuffer, gpgpu/src/gpgpu.cpp:189-214): a
+// buffer is carved off the end of the slab, buffers are released in reverse order of their
+// creation (anything else throws, as in the reference), and the slab only grows. One pool per
+// host thread and device, next to that thread's queue: work that uses the scratch is ordered by
+// the queue, so the next call may overwrite it without waiting - which is what lets the calls
+// below stay asynchronous. Like the reference's pool it must not be shared between queues whose
+// work overlaps.
+class TemporaryPool {
+public:
+    static TemporaryPool& current() {
+        thread_local TemporaryPool pools[16];
+        int dev = 0;
+        check_cuda(cudaGetDevice(&dev), "cudaGetDevice");
+        if (dev < 0 || dev >= 16) throw APIError(static_cast<int>(cudaErrorInvalidDevice), "TemporaryPool");
+        return pools[dev];
+    }
+    // returns the byte offset of `bytes` bytes of scratch, aligned to `align`
+    size_t acquire(size_t bytes, size_t align, void** base) {
+        size_t off = top_;
+        if (off % align) off += align - off % align;
+        const size_t end = off + bytes;
+        if (end > size_) {
+            // earlier work may still use the old slab: it is freed only after the device drained
+            // (cudaFree waits), and nothing carved from it may be alive
+            if (top_ != 0) throw std::runtime_error("temporary buffer pool cannot grow while in use");
+            if (slab_) check_cuda(cudaFree(slab_), "cudaFree");
+            slab_ = nullptr;
+            size_t want = end < (size_t(1) << 20) ? (size_t(1) << 20) : end;
+            check_cuda(cudaMalloc(&slab_, want), "cudaMalloc");
+            size_ = want;
+        }
+        *base = slab_;
+        marks_.push_back(top_);
+        top_ = end;
+        return off;
+    }
+    void release(size_t end) {
+        if (end != top_ || marks_.empty()) throw std::runtime_error("temporary buffer allocation violation");
+        top_ = marks_.back();
+        marks_.pop_back();
+    }
+    ~TemporaryPool() { if (slab_) cudaFree(slab_); }
+private:
+    void* slab_ = nullptr;
+    size_t size_ = 0, top_ = 0;
+    std::vector<size_t> marks_;
+};
+
 template <typename T>
-class TemporaryBuffer : public Buffer<T> {
+class TemporaryBuffer {
 public:
     TemporaryBuffer() = default;
-    explicit TemporaryBuffer(size_t size) : Buffer<T>(size) {}
-    size_t offset() const noexcept { return 0; }
+    explicit TemporaryBuffer(size_t size) : pool_(&TemporaryPool::current()), size_(size) {
+        void* base = nullptr;
+        const size_t align = sizeof(T) > 256 ? sizeof(T) : 256;
+        offset_bytes_ = pool_->acquire(size * sizeof(T), align, &base);
+        ptr_ = reinterpret_cast<T*>(static_cast<char*>(base) + offset_bytes_);
+    }
+    ~TemporaryBuffer() noexcept(false) { if (pool_) pool_->release(offset_bytes_ + size_ * sizeof(T)); }
+    TemporaryBuffer(const TemporaryBuffer&) = delete;
+    TemporaryBuffer& operator=(const TemporaryBuffer&) = delete;
+    size_t size() const noexcept { return size_; }
+    size_t data_size() const noexcept { return size_ * sizeof(T); }
+    size_t offset() const noexcept { return offset_bytes_ / sizeof(T); }
+    T* unwrap() const noexcept { return ptr_; }
+private:
+    TemporaryPool* pool_ = nullptr;
+    size_t size_ = 0, offset_bytes_ = 0;
+    T* ptr_ = nullptr;
 };
 
 // ---------------------------------------------------------------------------- blas
@@ -257,7 +319,8 @@ void gemmBatched(const Layout layout, const Transpose a_transpose, const Transpo
         detail::test_matrix(d.c_one, d.c_two, c_buffer, c_offsets[i], c_ld, StatusCode::kInvalidLeadDimC, StatusCode::kInsufficientMemoryC);
     }
     // scratch for the per-batch tables: the reference takes its equivalents from the context's
-    // temporary-buffer pool (gpgpu/src/gblas.cpp:2972-2988)
+    // temporary-buffer pool (gpgpu/src/gblas.cpp:2972-2988). The pool's slab outlives the call and
+    // later users of it are ordered behind this call's kernel by the queue, so nothing waits here.
     TemporaryBuffer<unsigned char> work(dlf_b200_gemm_batched_workspace_bytes(batch_count));
     detail::EventScope scope(queue, event);
     detail::raise(dlf_b200_gemm_batched(
@@ -266,7 +329,6 @@ void gemmBatched(const Layout layout, const Transpose a_transpose, const Transpo
                       b_buffer.unwrap(), b_offsets, b_ld, betas, c_buffer.unwrap(), c_offsets, c_ld, batch_count,
                       work.unwrap(), work.data_size(), queue.unwrap()),
                   "dlf_b200_gemm_batched");
-    queue.finish();  // `work` is released on return
 }
 
 }  // namespace blas
@@ -301,6 +363,12 @@ void conv2d(const size_t batches, const size_t channels,
     if (result_buffer.size() < batches * num_kernels * output_h * output_w) throw BLASError(StatusCode::kInsufficientMemoryC);
     if (bias && bias->size() < num_kernels) throw BLASError(StatusCode::kInvalidValue);
     if (residual && residual->size() < batches * num_kernels * output_h * output_w) throw BLASError(StatusCode::kInvalidValue);
+    // scratch for the filter bank in the kernel's shared-memory layout, from the temporary-buffer
+    // pool as cudnnConv takes its workspace (gpgpu/src/gdnn.cpp:1452-1508). Without it the kernel
+    // gathers the filter bank inside its main loop, at well under half the speed.
+    TemporaryBuffer<unsigned char> work(dlf_b200_conv2d_workspace_bytes(
+        blas::PrecisionOf<T>::value, batches, channels, height, width, output_h, output_w, num_kernels, group,
+        kernel_h, kernel_w));
     blas::detail::EventScope scope(queue, event);
     blas::detail::raise(dlf_b200_conv2d_fused(blas::PrecisionOf<T>::value, batches, channels, height, width,
                                               output_h, output_w, num_kernels, group, kernel_h, kernel_w, pad_top,
@@ -308,7 +376,8 @@ void conv2d(const size_t batches, const size_t channels,
                                               dilation_w, im_buffer.unwrap(), kernel_buffer.unwrap(),
                                               bias ? bias->unwrap() : nullptr,
                                               residual ? residual->unwrap() : nullptr, activation,
-                                              result_buffer.unwrap(), nullptr, 0, queue.unwrap()),
+                                              result_buffer.unwrap(), work.unwrap(), work.data_size(),
+                                              queue.unwrap()),
                         "dlf_b200_conv2d_fused");
 }
 

@@ -4,6 +4,7 @@
 // strided-batched and an offset-table batched product against a host loop, and the reference's
 // exceptions for bad arguments. Prints "ok" and exits 0 on success.
 #include <cmath>
+#include <cstdint>
 #include <cstdio>
 #include <cstdlib>
 #include <vector>
@@ -76,8 +77,12 @@ static void conv_bias_golden() {
                                   118, 82, 94, 145, 154, 163, 112, 73, 112, 118, 124, 85};
     auto dX = dev(X), dW = dev(W), dBias = dev(bias);
     Buffer<float> dY(25);
+    // the binding hands the library scratch from the temporary-buffer pool, so the filter bank is
+    // packed by a launch of its own before the main kernel: two launches per convolution
+    const unsigned long long launches0 = dlf_b200_launch_count();
     dnn::conv2d<float>(1, 1, 5, 5, 5, 5, 1, 1, 3, 3, 1, 1, 1, 1, 1, 1, 1, 1, dX, dW, dY, current::queue(), nullptr,
                        &dBias);
+    CHECK(dlf_b200_launch_count() - launches0 == 2);
     CHECK(host(dY) == Y);
 
     // fused: relu(conv + bias + residual) with residual = -60 everywhere
@@ -129,9 +134,31 @@ static void batched() {
     const std::vector<size_t> ao = {0, m * k, 2 * m * k}, bo = {0, 0, 0}, co = {2 * m * n, 0, m * n};
     blas::gemmBatched<float>(Layout::RowMajor, Transpose::NoTrans, Transpose::NoTrans, m, n, k, alphas.data(), dA,
                              ao.data(), k, dB, bo.data(), n, betas.data(), dC2, co.data(), n, batch);
+    // a second offset-table call right behind the first, without waiting: both take their tables
+    // from the same pool slab, ordered by the queue
+    auto dC3 = dev(C);
+    const std::vector<size_t> co3 = {m * n, 2 * m * n, 0};
+    blas::gemmBatched<float>(Layout::RowMajor, Transpose::NoTrans, Transpose::NoTrans, m, n, k, alphas.data(), dA,
+                             ao.data(), k, dB, bo.data(), n, betas.data(), dC3, co3.data(), n, batch);
     auto got = host(dC2);
+    auto got3 = host(dC3);
     for (size_t b = 0; b < batch; ++b)
-        for (size_t e = 0; e < m * n; ++e) CHECK(got[co[b] + e] == ref[b * m * n + e]);
+        for (size_t e = 0; e < m * n; ++e) {
+            CHECK(got[co[b] + e] == ref[b * m * n + e]);
+            CHECK(got3[co3[b] + e] == ref[b * m * n + e]);
+        }
+}
+
+static void temporary_pool_is_lifo() {
+    // releaseTemporaryBuffer (gpgpu/src/gpgpu.cpp:207-214): out-of-order release is an error
+    TemporaryBuffer<float> outer(100);
+    {
+        TemporaryBuffer<unsigned char> inner(33);
+        CHECK(inner.offset() >= 400);
+        CHECK(reinterpret_cast<uintptr_t>(inner.unwrap()) % 256 == 0);
+    }
+    TemporaryBuffer<float> again(10);
+    CHECK(again.offset() * sizeof(float) >= 400 && again.offset() * sizeof(float) < 1024);
 }
 
 static void errors() {
@@ -160,6 +187,7 @@ int main() {
     conv_bias_golden();
     maxpool_golden();
     batched();
+    temporary_pool_is_lifo();
     errors();
     int dev_status = -1;
     CHECK(dlf_b200_device_status(&dev_status) == 0 && dev_status == 0);

@@ -10,6 +10,9 @@ parsed out of
     dlf/test/MatMulTest.cpp          TYPED_TEST(MatMulTest, *)
     dlf/test/DNNTest.cpp             TEST(Conv2D, *), TEST(MaxPool, *), TEST(DNNTest, GlobalPooling)
     dlf/test/model/PredictTest.cpp   Gemm, Conv (+bias)
+    dlf/test/TensorTest.cpp          dot_test()             (v.v, v.M, M.v, M.M)
+    dlf/test/UniformTest.cpp         TEST(UniformTest, Dot), TEST(UniformTest, MultiDot*)
+    dlf/test/GPGPUTest.cpp           vector_dot_vector_test() ... matrix_dot_matrix_test()
 
 Usage:  python tests/golden/make_goldens.py /path/to/dlf-checkout
 Only the JSON travels with the repository; the tests never read the reference tree.
@@ -218,8 +221,86 @@ def extract_predict(path, rel):
     return out
 
 
+RE_ANY_TENSOR = re.compile(
+    r"(?:auto\s+(\w+)\s*=\s*Tensor<\w+>|Tensor<\w+>\s+(\w+))\s*\(\{?\{([\d,\s]+)\},\s*\{([^}]*)\}\}?\)\s*;", re.S)
+RE_ANY_RANGE = re.compile(r"auto\s+(\w+)\s*=\s*Tensor<\w+>\(\{([\d,\s]+)\}\)\.range\((\d*)\)\s*;")
+
+
+def _dot_vars(body):
+    v = {}
+    for m in RE_ANY_RANGE.finditer(body):
+        v[m.group(1)] = {"shape": _ints(m.group(2)), "range": int(m.group(3) or 0)}
+    for m in RE_ANY_TENSOR.finditer(body):
+        v[m.group(1) or m.group(2)] = {"shape": _ints(m.group(3)), "values": _ints(m.group(4))}
+    m = re.search(r"auto\s+(\w+)\s*=\s*Tensor<\w+>::scalar\((\d+)\)\s*;", body)
+    if m:
+        v[m.group(1)] = {"shape": [], "values": [int(m.group(2))]}
+    return v
+
+
+def _dot_expected(expr, v):
+    expr = expr.strip()
+    m = re.fullmatch(r"Tensor<\w+>::scalar\((\d+)\)", expr)
+    if m:
+        return {"shape": [], "values": [int(m.group(1))]}
+    m = re.fullmatch(r"Tensor<\w+>\(\{([\d,\s]+)\},\s*\{([^}]*)\}\)", expr, re.S)
+    if m:
+        return {"shape": _ints(m.group(1)), "values": _ints(m.group(2))}
+    return v[expr]
+
+
+def extract_dot(tensor_test, uniform_test, gpgpu_test):
+    """dot / multi_dot known answers: every case is {source, args: [tensor...], expected}."""
+    cases = []
+    # TensorTest.cpp dot_test(): four brace scopes, each with a, b and one EXPECT_EQ(dot(a, b), ...)
+    path, rel = tensor_test
+    text = open(path).read()
+    pos = text.index("static void dot_test()")
+    body, _ = _block(text, pos)
+    i = 0
+    while True:
+        j = body.find("{", i)
+        if j < 0:
+            break
+        scope, end = _block(body, j)
+        i = end
+        m = re.search(r"EXPECT_EQ\(dot\((\w+),\s*(\w+)\),\s*(.*?)\);", scope, re.S)
+        if not m:
+            continue
+        v = _dot_vars(scope)
+        cases.append({"source": "%s:%d" % (rel, _line_of(text, pos)), "name": "TensorTest.Dot.%d" % len(cases),
+                      "args": [v[m.group(1)], v[m.group(2)]], "expected": _dot_expected(m.group(3), v)})
+    # UniformTest.cpp: Dot and the MultiDot family
+    path, rel = uniform_test
+    text = open(path).read()
+    for m in re.finditer(r"TEST\(UniformTest,\s*((?:Dot|MultiDot)\w*)\)", text):
+        body, _ = _block(text, m.end())
+        v = _dot_vars(body)
+        call = re.search(r"(?:auto\s+(\w+)\s*=\s*|EXPECT_EQ\()(multi_dot|dot)\(([\w,\s]+)\)", body)
+        names = [x.strip() for x in call.group(3).split(",")]
+        if call.group(1):  # auto D = multi_dot(A, B, C); EXPECT_EQ(D, <expected>);
+            e = re.search(r"EXPECT_EQ\(%s,\s*(.*?)\);" % call.group(1), body, re.S)
+            expected = _dot_expected(e.group(1), v)
+        else:              # EXPECT_EQ(dot(A, B), C);
+            e = re.search(r"EXPECT_EQ\(dot\([\w,\s]+\),\s*(\w+)\);", body)
+            expected = v[e.group(1)]
+        cases.append({"source": "%s:%d" % (rel, _line_of(text, m.start())), "name": "UniformTest." + m.group(1),
+                      "args": [v[n] for n in names], "expected": expected})
+    # GPGPUTest.cpp: vector/matrix dot helpers (A, B, R)
+    path, rel = gpgpu_test
+    text = open(path).read()
+    for m in re.finditer(r"static void (\w+_dot_\w+_test)\(\)", text):
+        body, _ = _block(text, m.end())
+        v = _dot_vars(body)
+        cases.append({"source": "%s:%d" % (rel, _line_of(text, m.start())), "name": "GPGPUTest." + m.group(1),
+                      "args": [v["A"], v["B"]], "expected": v["R"]})
+    return cases
+
+
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_goldens.py /path/to/dlf-checkout")
+    root = sys.argv[1]
     t = os.path.join(root, "dlf", "test")
     g1 = extract_gemm(os.path.join(t, "TensorTest.cpp"), "dlf/test/TensorTest.cpp")
     g2 = extract_gemm(os.path.join(t, "GPGPUTest.cpp"), "dlf/test/GPGPUTest.cpp")
@@ -232,12 +313,15 @@ def main():
         "pool": extract_pool(os.path.join(t, "DNNTest.cpp"), "dlf/test/DNNTest.cpp"),
         "predict": extract_predict(os.path.join(t, "model", "PredictTest.cpp"),
                                    "dlf/test/model/PredictTest.cpp"),
+        "dot": extract_dot((os.path.join(t, "TensorTest.cpp"), "dlf/test/TensorTest.cpp"),
+                           (os.path.join(t, "UniformTest.cpp"), "dlf/test/UniformTest.cpp"),
+                           (os.path.join(t, "GPGPUTest.cpp"), "dlf/test/GPGPUTest.cpp")),
     }
     out = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_goldens.json")
     with open(out, "w") as f:
         json.dump(data, f, indent=1)
     print("wrote", out, "gemm:", len(data["gemm"]), "matmul:", len(data["matmul"]),
-          "conv2d:", len(data["conv2d"]))
+          "conv2d:", len(data["conv2d"]), "dot:", len(data["dot"]))
 
 
 if __name__ == "__main__":

@@ -98,6 +98,21 @@ def test_matmul_goldens(case):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("case", G["dot"], ids=lambda c: c["name"])
+def test_dot_goldens(case, dtype):
+    """dlf::dot / multi_dot on device tensors: TensorTest.Dot, UniformTest.Dot / MultiDot* and the
+    GPGPUTest vector / matrix dots, bit-exact (all values are small integers)."""
+    from dlf_b200 import tensor as dt
+    expect = tensor_of(case["expected"], dtype)
+    if dtype == torch.float16 and float(expect.float().abs().max()) > 2048:
+        pytest.skip("expected values are not exactly representable in fp16")
+    args = [tensor_of(a, dtype).cuda() for a in case["args"]]
+    got = dt.dot(args[0], args[1]) if len(args) == 2 else dt.multi_dot(*args)
+    assert list(got.shape) == list(expect.shape)
+    assert torch.equal(got.cpu(), expect), case["name"]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
 @pytest.mark.parametrize("case", G["conv2d"], ids=lambda c: c["name"])
 def test_conv2d_goldens(case, dtype):
     from dlf_b200 import gdnn
@@ -351,6 +366,91 @@ def test_beta_zero_never_reads_c():
         assert metric(got, ref) <= tol
 
 
+@pytest.mark.parametrize("flags", [0, 1], ids=["tma-store-epilogue", "generic-epilogue"])
+def test_nan_in_an_operand_stays_nan(lib, flags):
+    """A NaN in A reaches every output it contributes to, and only those, on the TMA-fed kernel
+    (whose epilogue writes through TMA stores) as on the loader-warp kernel - the oracle's
+    positions exactly. (fmaxf drops a NaN operand: the ReLU clamp must not run without ReLU.)"""
+    gb = _gb()
+    m, n, k = 160, 136, 72
+    rng = np.random.default_rng(99)
+    A = _round_to(_rand(rng, m * k), torch.float16)
+    B = _round_to(_rand(rng, k * n), torch.float16)
+    A[5 * k + 3] = np.nan   # row 5
+    A[130 * k + 70] = np.nan  # row 130
+    ref = np.zeros(m * n, np.float32)
+    oracle.gblas_sgemm(oracle.ROW_MAJOR, oracle.NO_TRANS, oracle.NO_TRANS, m, n, k, 1.0, A, 0, k, B, 0, n,
+                       0.0, ref, 0, n)
+    C = torch.zeros(m * n, dtype=torch.float16, device="cuda")
+    lib.set_tuning(0, flags)
+    try:
+        gb.gemm(gb.Layout.RowMajor, gb.Transpose.NoTrans, gb.Transpose.NoTrans, m, n, k, 1.0,
+                torch.from_numpy(A).half().cuda(), 0, k, torch.from_numpy(B).half().cuda(), 0, n, 0.0, C, 0, n)
+        torch.cuda.synchronize()
+    finally:
+        lib.set_tuning(0, 0)
+    got = C.float().cpu().numpy()
+    assert np.array_equal(np.isnan(got), np.isnan(ref))
+    assert np.isnan(got).sum() == 2 * n
+    ok = ~np.isnan(ref)
+    assert max_rel(got[ok], ref[ok]) <= HALF_TOL
+
+
+def test_calls_on_a_queue_that_is_not_the_current_stream(lib):
+    """gemmBatched and conv2d on an explicit queue while another stream is current: their scratch
+    (offset tables, packed filter bank) is allocated by the caller's allocator and must stay alive
+    until the queue has passed the work that reads it."""
+    from dlf_b200 import gdnn
+    gb = _gb()
+    q = torch.cuda.Stream()
+    rng = np.random.default_rng(21)
+    m, n, k, batch = 48, 40, 56, 6
+    A = torch.from_numpy(_rand(rng, batch * m * k)).cuda()
+    B = torch.from_numpy(_rand(rng, batch * k * n)).cuda()
+    X = torch.from_numpy(_rand(rng, (2, 8, 12, 12), "normal")).cuda()
+    W = torch.from_numpy(0.1 * _rand(rng, (16, 8, 3, 3), "normal")).cuda()
+    f = gdnn.Filter2D(X.shape, W.shape).pads(1, 1)
+    torch.cuda.synchronize()
+    outs = []
+    for _ in range(3):
+        C = torch.zeros(batch * m * n, device="cuda")
+        Y = torch.empty(f.output_shape(), device="cuda")
+        q.wait_stream(torch.cuda.current_stream())
+        gb.gemmBatched(gb.Layout.RowMajor, gb.Transpose.NoTrans, gb.Transpose.NoTrans, m, n, k, [1.0] * batch,
+                       A, [i * m * k for i in range(batch)], k, B, [i * k * n for i in range(batch)], n,
+                       [0.0] * batch, C, [i * m * n for i in range(batch)], n, batch, queue=q)
+        gdnn.conv2d_filter(X, W, Y, f, queue=q)
+        # allocator traffic on the current stream while the queue may still be working
+        junk = [torch.full((1 << 16,), 7.0, device="cuda") for _ in range(8)]
+        del junk
+        outs.append((C, Y))
+    q.synchronize()
+    torch.cuda.synchronize()
+    refC = torch.bmm(A.view(batch, m, k).double(), B.view(batch, k, n).double()).float().flatten()
+    refY = oracle.conv2d(X.cpu().numpy(), W.cpu().numpy(), pads=(1, 1, 1, 1), wide=True)
+    for C, Y in outs:
+        assert rel_fro(C.cpu().numpy(), refC.cpu().numpy()) <= FP32_TOL
+        assert rel_fro(Y.cpu().numpy(), refY) <= FP32_TOL
+
+
+def test_conv2d_dilation_beyond_16_bits_takes_the_wide_index_kernel(lib):
+    """(KH-1)*dilation_h = 40000 does not fit the 16-bit tap offsets of the tensor-memory-operand
+    kernel's k table: the call must be served by the kernel with wide indices (one launch, no
+    packing grid) and give the oracle's result (only the kh = 0 tap lies inside the image)."""
+    from dlf_b200 import gdnn
+    rng = np.random.default_rng(40000)
+    X = _rand(rng, (2, 3, 6, 9), "normal")
+    Wt = _rand(rng, (5, 3, 2, 2), "normal")
+    ref = oracle.conv2d(X, Wt, dilations=(40000, 1), wide=True)
+    filt = gdnn.Filter2D(X.shape, Wt.shape).dilations(40000, 1)
+    assert tuple(filt.output_shape()) == ref.shape
+    Y = torch.full(ref.shape, float("nan"), device="cuda")
+    n0 = lib.launch_count()
+    gdnn.conv2d_filter(torch.from_numpy(X).cuda(), torch.from_numpy(Wt).cuda(), Y, filt)
+    assert lib.launch_count() - n0 == 1
+    assert rel_fro(Y.cpu().numpy(), ref) <= FP32_TOL
+
+
 @pytest.mark.parametrize("k", [1056, 4096])
 def test_gemm_fp32_long_k_stays_accurate(k):
     """The tensor core truncates when it adds into its fp32 accumulator; without countermeasure the
@@ -362,6 +462,37 @@ def test_gemm_fp32_long_k_stays_accurate(k):
                                    (gb.Layout.ColMajor, gb.Transpose.NoTrans, gb.Transpose.Trans, 130, 300)):
         got, ref = _gemm_case(rng, torch.float32, layout, ta, tb, m, n, k, 0.5, 0.5, (0, 0, 0), (0, 0, 0))
         assert rel_fro(got, ref) <= 4e-6
+
+
+@pytest.mark.parametrize("chunked", [True, False], ids=["chunked", "one-accumulator"])
+def test_gemm_config5_shape_at_k_16384(lib, chunked):
+    """BASELINE config 5 at its own K: row-major, A stored K x M and passed Trans, alpha = beta =
+    0.5, K = 16384 (M, N kept small so that the oracle finishes in seconds). With the K-chunked
+    accumulation the error stays inside the 1e-5 tolerance; accumulating all of K in one
+    tensor-core accumulator (tuning bit 0x1000) shows the truncation drift the chunks remove."""
+    gb = _gb()
+    m, n, k = 256, 384, 16384
+    rng = np.random.default_rng(5)
+    A = _rand(rng, k * m)
+    B = _rand(rng, k * n)
+    C0 = rng.normal(size=m * n).astype(np.float32)
+    ref = C0.copy()
+    oracle.gblas_sgemm(oracle.ROW_MAJOR, oracle.TRANS, oracle.NO_TRANS, m, n, k, 0.5, A, 0, m, B, 0, n,
+                       0.5, ref, 0, n, wide=True)
+    C = torch.from_numpy(C0.copy()).cuda()
+    lib.set_tuning(0, 0 if chunked else 0x1000)
+    try:
+        gb.gemm(gb.Layout.RowMajor, gb.Transpose.Trans, gb.Transpose.NoTrans, m, n, k, 0.5,
+                torch.from_numpy(A).cuda(), 0, m, torch.from_numpy(B).cuda(), 0, n, 0.5, C, 0, n)
+        torch.cuda.synchronize()
+    finally:
+        lib.set_tuning(0, 0)
+    err = rel_fro(C.cpu().numpy(), ref)
+    if chunked:
+        assert err <= 4e-6, err
+        test_gemm_config5_shape_at_k_16384.chunked_err = err
+    else:
+        assert err > getattr(test_gemm_config5_shape_at_k_16384, "chunked_err", 4e-6), err
 
 
 def test_gemm_config1_sgemm_1024():
@@ -518,6 +649,47 @@ def test_conv2d_random_parity(case, dtype):
         assert rel_fro(got, ref) <= FP32_TOL
     else:
         assert max_rel(got, ref) <= HALF_TOL
+
+
+def _resnet_shapes():
+    from bench import RESNET50_SHAPES
+    return RESNET50_SHAPES
+
+
+@pytest.mark.parametrize("shape", _resnet_shapes(), ids=lambda c: "x".join(map(str, c[:6])))
+def test_conv2d_resnet50_layer_shapes_vs_oracle(shape):
+    """BASELINE config 3 at its real layer shapes: every one of the 20 distinct ResNet-50 v1
+    convolutions (224 x 224 input), fp16 with bias, two images, against the oracle with a wide
+    accumulator. Inputs follow the configuration: activations |N(0,1)|, He-normal weights."""
+    from dlf_b200 import gdnn
+    cin, h, cout, k, s, p, _count = shape
+    rng = np.random.default_rng(cin * 1000 + cout + k)
+    X = _round_to(np.abs(rng.normal(size=(2, cin, h, h))).astype(np.float32), torch.float16)
+    Wt = _round_to((np.sqrt(2.0 / (cin * k * k)) * rng.normal(size=(cout, cin, k, k))).astype(np.float32),
+                   torch.float16)
+    bias = _round_to(rng.uniform(-0.1, 0.1, cout).astype(np.float32), torch.float16)
+    ref = oracle.conv2d(X, Wt, pads=(p,) * 4, strides=(s, s), bias=bias, wide=True)
+    filt = gdnn.Filter2D(X.shape, Wt.shape).pads(p, p).strides(s, s)
+    Y = torch.full(ref.shape, float("nan"), dtype=torch.float16, device="cuda")
+    gdnn.conv2d_filter(torch.from_numpy(X).half().cuda(), torch.from_numpy(Wt).half().cuda(), Y, filt,
+                       bias=torch.from_numpy(bias).half().cuda())
+    assert max_rel(Y.float().cpu().numpy(), ref) <= HALF_TOL
+
+
+def test_resnet50_fc_gemm_vs_oracle():
+    """The final fully connected layer of config 3 as a GEMM: 256 x 1000 x 2048, fp16."""
+    gb = _gb()
+    m, n, k = 256, 1000, 2048
+    rng = np.random.default_rng(2048)
+    A = _round_to(np.abs(rng.normal(size=m * k)).astype(np.float32), torch.float16)
+    B = _round_to((np.sqrt(2.0 / k) * rng.normal(size=k * n)).astype(np.float32), torch.float16)
+    ref = np.zeros(m * n, np.float32)
+    oracle.gblas_sgemm(oracle.ROW_MAJOR, oracle.NO_TRANS, oracle.NO_TRANS, m, n, k, 1.0, A, 0, k, B, 0, n,
+                       0.0, ref, 0, n, wide=True)
+    C = torch.full((m * n,), float("nan"), dtype=torch.float16, device="cuda")
+    gb.gemm(gb.Layout.RowMajor, gb.Transpose.NoTrans, gb.Transpose.NoTrans, m, n, k, 1.0,
+            torch.from_numpy(A).half().cuda(), 0, k, torch.from_numpy(B).half().cuda(), 0, n, 0.0, C, 0, n)
+    assert max_rel(C.float().cpu().numpy(), ref) <= HALF_TOL
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16])

@@ -69,6 +69,30 @@ def test_matmul_goldens_through_front_end(case, dtype):
         assert torch.equal(got, expect), (case["name"], chk)
 
 
+@pytest.mark.parametrize("case", G["dot"], ids=lambda c: c["name"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.int32])
+def test_dot_goldens_through_front_end(case, dtype):
+    """dlf::dot / multi_dot known answers (TensorTest.Dot, UniformTest.Dot / MultiDot*, the
+    GPGPUTest vector / matrix dots) on CPU tensors with the oracle as the BLAS."""
+    args = [tensor_of(a, dtype) for a in case["args"]]
+    expect = tensor_of(case["expected"], dtype)
+    be = OracleBlas()
+    got = dt.dot(args[0], args[1], backend=be) if len(args) == 2 else dt.multi_dot(*args, backend=be)
+    assert list(got.shape) == list(expect.shape)
+    assert torch.equal(got, expect), case["name"]
+
+
+def test_multi_dot_picks_the_cheapest_order():
+    """(10x2)(2x10)(10x2): multiplying the last two first costs 80 multiplications instead of
+    400; the split table must say so (detail::matrix_chain_order, linalg_detail.h:1701-1720)."""
+    assert dt._matrix_chain_order([10, 2, 10, 2])[0][2] == 0
+    assert dt._matrix_chain_order([2, 10, 2, 10])[0][2] == 1
+    with pytest.raises(dt.ShapeError):
+        dt.multi_dot(torch.zeros(2, 3), torch.zeros(4, 5))
+    with pytest.raises(dt.ShapeError):
+        dt.multi_dot(torch.zeros(2, 3), torch.zeros(3), torch.zeros(3, 4))
+
+
 def test_matmul_routing_choices():
     """The three branches of detail::matmul (linalg_detail.h:1573-1662)."""
     A = torch.arange(24, dtype=torch.float32).reshape(2, 3, 4)

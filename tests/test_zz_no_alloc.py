@@ -22,7 +22,7 @@ HALF_TOL = 2e-2   # fp16 max relative error, as in test_gpu_parity.py
 FP32_TOL = 1e-5   # fp32 relative Frobenius error
 
 
-def _call(L, noalloc, dtype, m, n, k, alphas, A, a_offs, lda, B, b_offs, ldb, betas, C, c_offs, ldc):
+def _call(L, noalloc, dtype, m, n, k, alphas, A, a_offs, lda, B, b_offs, ldb, betas, C, c_offs, ldc, sync=True):
     batch = len(a_offs)
     prec = 32 if dtype == torch.float32 else 16
     arr = ctypes.c_size_t * batch
@@ -39,7 +39,8 @@ def _call(L, noalloc, dtype, m, n, k, alphas, A, a_offs, lda, B, b_offs, ldb, be
         need = L.dlf_b200_gemm_batched_workspace_bytes(batch)
         ws = torch.empty(need, dtype=torch.uint8, device="cuda")
         rc = L.dlf_b200_gemm_batched(*common, ctypes.c_void_p(ws.data_ptr()), need, stream)
-    torch.cuda.synchronize()
+    if sync:
+        torch.cuda.synchronize()
     return rc
 
 
@@ -84,6 +85,37 @@ def test_noalloc_entry_matches_workspace_entry_on_two_calls_in_a_row():
         want = al * (a @ b.t()) + be * c0
         have = c_new[c_offs[i]:c_offs[i] + m * n].double().cpu().reshape(m, n)
         assert float((have - want).norm() / want.norm()) <= (1e-5 if dtype == torch.float32 else 2e-3)
+    assert dlf_b200.device_status() == 0
+
+
+def test_noalloc_calls_queued_back_to_back_share_the_table_in_stream_order():
+    """Two calls of different size on one stream with no host wait between them: the second call's
+    tables overwrite the first call's only after the first kernel has run. The second problem uses
+    every entry the fixed array has (4096 batches). Device memory in use must not change."""
+    import dlf_b200
+    L = dlf_b200.lib()
+    dtype = torch.float16
+    p1 = _problem(3, dtype, 64, 48, 72, 11)
+    p2 = _problem(4, dtype, 8, 16, 8, 4096)
+    outs = []
+    for (A, a_offs, B, b_offs, C, c_offs, alphas, betas), (m, n, k) in ((p1, (64, 48, 72)), (p2, (8, 16, 8))):
+        c_ref = C.clone().cuda()
+        assert _call(L, False, dtype, m, n, k, alphas, A, a_offs, k, B, b_offs, k, betas, c_ref, c_offs, n) == 0
+        outs.append((c_ref, C.clone().cuda()))
+    # one warmed-up call first, so that the per-device set-up is not what is measured below
+    A, a_offs, B, b_offs, C, c_offs, alphas, betas = p1
+    scratch = C.clone().cuda()
+    assert _call(L, True, dtype, 64, 48, 72, alphas, A, a_offs, 72, B, b_offs, 72, betas, scratch, c_offs, 48) == 0
+    free0, _ = torch.cuda.mem_get_info()
+    for (A, a_offs, B, b_offs, C, c_offs, alphas, betas), (m, n, k), (_, c_new) in (
+            (p1, (64, 48, 72), outs[0]), (p2, (8, 16, 8), outs[1])):
+        assert _call(L, True, dtype, m, n, k, alphas, A, a_offs, k, B, b_offs, k, betas, c_new, c_offs, n,
+                     sync=False) == 0
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 >= free0  # nothing was taken from the device's free memory
+    for c_ref, c_new in outs:
+        assert torch.equal(c_ref, c_new)
     assert dlf_b200.device_status() == 0
 
 
