@@ -695,6 +695,10 @@ def main():
             "bgemm_f16_b1024_512x512x64_" + tag, "f16", 512, 512, 64, batch=1024, ta=ta, tb=tb, alpha=0.125))
         table["batched_c4_b_" + tag] = (lambda tag=tag, ta=ta, tb=tb: GemmWorkload(
             "bgemm_f16_b1024_512x64x512_" + tag, "f16", 512, 64, 512, batch=1024, ta=ta, tb=tb, alpha=0.125))
+    if args.workload == "resnet_sweep":  # development aid: config 3 alone, per layer
+        summary, rows = resnet_sweep(device, peaks, args.batch or 256, steps if args.steps is not None else 10)
+        print(json.dumps({"resnet50_v1_convs_f16": summary, "layers": rows, "device_status": dlf_b200.device_status()}), flush=True)
+        return
     w = table[args.workload]()
     w.overlap_gather = args.overlap_gather
     sets = w.sets_needed()

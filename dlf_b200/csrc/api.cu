@@ -419,15 +419,19 @@ int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
     const int stage_bytes = bn * 128 * (q.es == 4 ? 2 : 1);
     const int sums_bytes = kc_blocks ? bn * 128 * 4 : 0;
     if (kc_blocks && bn > 128) return kUnexpectedError;
+    // 16-bit outputs for which nothing of D is read leave through staged 16-byte stores
+    // (epilogue.cuh); a residual is read by the staging threads themselves
+    const bool d_staged = q.es == 2 && q.beta == 0.0f && q.betas == nullptr && !((g_force_generic.load() >> 16) & 64);
+    const int out_stage_bytes = d_staged ? kStageBytes : 0;
     // the k table is padded to a multiple of 1024 in the layout below: count it that way here too
-    int stages = (kSmemPerBlockOptin - static_smem - 1024 - ((ktable_bytes + 1023) / 1024 * 1024) - sums_bytes) / stage_bytes;
+    int stages = (kSmemPerBlockOptin - static_smem - 1024 - ((ktable_bytes + 1023) / 1024 * 1024) - sums_bytes - out_stage_bytes) / stage_bytes;
     const int tmem_stages = (512 - acc_bufs * bn) / a_cols;
     if (stages > tmem_stages) stages = tmem_stages;
     if (stages > kMaxStages) stages = kMaxStages;
     if (stages < 2) return kUnexpectedError;
     // dynamic segment: [k table][pad to 1024][B stages][partial sums]
     const int sums_off = ((ktable_bytes + 1023) / 1024 * 1024) + 1024 + stages * stage_bytes;
-    size_t dyn_smem = static_cast<size_t>(sums_off) + sums_bytes;
+    size_t dyn_smem = static_cast<size_t>(sums_off) + sums_bytes + out_stage_bytes;
     // more than half of the SM's shared memory: never two CTAs (and two 512-column TMEM
     // allocations) on one SM
     if (dyn_smem < 120 * 1024) dyn_smem = 120 * 1024;
@@ -474,6 +478,8 @@ int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
     tp.rc_dmin = q.rc_dmin;
     tp.kc_blocks = kc_blocks;
     tp.sums_off = sums_off;
+    tp.d_staged = d_staged ? 1 : 0;
+    tp.stage_off = sums_off + sums_bytes;
     tp.acc_bufs = acc_bufs;
     tp.ktable_bytes = ktable_bytes;
 

@@ -87,6 +87,10 @@ struct TsParams {
     int b_tma;
     // A_IM2COL with a 1x1 filter and no padding (any stride): addresses are affine in k
     int a_pointwise;
+    // 16-bit outputs that nothing has to be read for: the epilogue warps stage blocks of columns in
+    // shared memory (kStageBytes at byte offset stage_off of the dynamic segment) and write them
+    // out as 16-byte vectors (see "Staged stores" in epilogue.cuh)
+    int d_staged, stage_off;
 };
 
 __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&v)[32]) {
@@ -255,6 +259,7 @@ __global__ void __launch_bounds__(kTsThreads, 1)
     __shared__ __align__(8) uint64_t tempty_bar[2];
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
+    __shared__ int epi_ok[4];  // staged stores: outcome of each epilogue warp's wait for the tile
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -342,6 +347,7 @@ __global__ void __launch_bounds__(kTsThreads, 1)
     if (warp < 4) {
         // ------------------------------------------------------------ epilogue
         uint32_t buf = 0, tphase = 0;
+        uint32_t stage_buf = 0;  // which of the two staging blocks the next block of columns takes
         const int kc = tp.kc_blocks > 0 ? tp.kc_blocks : num_kb;
         float* part_row = reinterpret_cast<float*>(smem_raw + tp.sums_off) + warp * 32 + lane;
         bool alive = true;
@@ -367,7 +373,24 @@ __global__ void __launch_bounds__(kTsThreads, 1)
             if (!alive) break;
             const float* part = kc < num_kb ? part_row : nullptr;
             const bool w = ptx::mbar_wait_bounded(ptx::smem_u32(&tfull_bar[buf]), tphase, abort_p);
-            if (!__all_sync(0xffffffffu, w)) break;
+            if constexpr (ES == 2) {
+                if (tp.d_staged) {
+                    // The staged stores below synchronise the four epilogue warps with a named
+                    // barrier, which has no time limit: the warps must agree on whether this tile
+                    // is processed. Every warp gets here (its wait is bounded), votes, and all
+                    // leave together if any wait gave up.
+                    const bool warp_ok = __all_sync(0xffffffffu, w);
+                    if (lane == 0) epi_ok[warp] = warp_ok ? 1 : 0;
+                    epilogue_bar();
+                    const bool all_ok = epi_ok[0] && epi_ok[1] && epi_ok[2] && epi_ok[3];
+                    epilogue_bar();  // the words may be rewritten for the next tile only after all have read them
+                    if (!all_ok) break;
+                } else if (!__all_sync(0xffffffffu, w)) {
+                    break;
+                }
+            } else {
+                if (!__all_sync(0xffffffffu, w)) break;
+            }
             ptx::tc_fence_after();
             if (tp.a_kind == A_ROWCONV) {
                 const int tm = m0 / kBM, tn = n0 / BN;
@@ -387,6 +410,41 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                 const int nco = min(tp.rc_cpt, p.N - c0);
                 const char* bias_g =
                     p.bias ? p.bias + (static_cast<long long>(b) * p.bias_stride + c0) * ES : nullptr;
+                // staged stores: the tile's produced positions, in order, are consecutive output
+                // pixels (a row's outputs end at OW, the next row's follow at once in memory)
+                StageGeom sg;
+                StageRun srun;
+                int slot = 0;
+                bool staged = false;
+                if constexpr (ES == 2) {
+                    if (tp.d_staged) {
+                        auto first_pixel = [&](long long pos) -> long long {  // first output pixel at or after position pos
+                            if (pos >= p.M) return static_cast<long long>(p.M / OHW) * p.g.P;
+                            const long long im = pos / OHW;
+                            const int rm = static_cast<int>(pos - im * OHW);
+                            const int r_oh = rm / tp.rc_wv;
+                            const int r_u = rm - r_oh * tp.rc_wv;
+                            return im * p.g.P + static_cast<long long>(r_oh + (r_u < p.g.OW ? 0 : 1)) * p.g.OW +
+                                   (r_u < p.g.OW ? r_u : 0);
+                        };
+                        const long long pos0 = static_cast<long long>(tm) * 4 * tp.rc_T;
+                        sg.q0 = first_pixel(pos0);
+                        sg.nslots = static_cast<int>(first_pixel(pos0 + 4 * tp.rc_T) - sg.q0);
+                        sg.base = static_cast<long long>(b) * p.d_batch_stride;
+                        sg.ois = p.g.out_img_stride;
+                        sg.colstride = p.g.P;
+                        sg.P = p.g.P;
+                        if (sg.nslots > 0) {
+                            stage_geom_finish(sg);
+                            staged = sg.runs <= kStageMaxRuns;
+                        }
+                        if (staged && produce) {
+                            slot = static_cast<int>(static_cast<long long>(img) * p.g.P + static_cast<long long>(oh) * p.g.OW + u - sg.q0);
+                            srun = stage_run(sg, img - sg.img0);
+                        }
+                    }
+                }
+                const long long d_elem0 = static_cast<long long>(reinterpret_cast<uintptr_t>(p.d) >> 1);
                 for (int co0 = 0; co0 < ((p.ablate & 8) ? 0 : nco); co0 += 16) {
                     // bias first (one value per lane, broadcast later): keeps loads out of the
                     // store loop, where they would serialise behind each store
@@ -433,6 +491,30 @@ __global__ void __launch_bounds__(kTsThreads, 1)
 #pragma unroll
                         for (int e = 0; e < 16; ++e) acc[e] = fmaxf(acc[e], 0.0f);
                     }
+                    if constexpr (ES == 2) {
+                        if (staged) {
+                            const uint32_t sbuf = ptx::smem_u32(smem_raw) + static_cast<uint32_t>(tp.stage_off) + stage_buf * kStageBufBytes;
+                            if (produce) {
+#pragma unroll
+                                for (int e = 0; e < 16; ++e) {
+                                    if (co0 + e < nco) {
+                                        const int idx = stage_index(srun, slot, d_elem0, sg.colstride, c0 + co0 + e);
+                                        const unsigned short h = p.fmt == FMT_F16 ? to_bits16<OUT_F16>(acc[e])
+                                                                                  : to_bits16<OUT_BF16>(acc[e]);
+                                        asm volatile("st.shared.u16 [%0], %1;" ::"r"(sbuf + static_cast<uint32_t>(e * kStageRowStride + idx) * 2u), "h"(h) : "memory");
+                                    }
+                                }
+                            }
+                            if (co0 + 16 >= nco) {  // the accumulator has been read for the last time
+                                ptx::tc_fence_before();
+                                ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));
+                            }
+                            epilogue_bar();
+                            staged_writeout(sg, sbuf, p.d, c0 + co0, min(16, nco - co0), threadIdx.x);
+                            stage_buf ^= 1u;
+                            continue;
+                        }
+                    }
                     if (produce && !((p.ablate & 16) && acc[0] != 123.456f)) {
                         char* optr = p.d + (obase + static_cast<long long>(c0 + co0) * p.g.P) * ES;
                         const long long cstride = static_cast<long long>(p.g.P) * ES;
@@ -455,8 +537,10 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                         }
                     }
                 }
-                ptx::tc_fence_before();
-                ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));
+                if (!staged || (p.ablate & 8)) {  // (the staged path released the accumulator after its last read)
+                    ptx::tc_fence_before();
+                    ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));
+                }
                 if (++buf == static_cast<uint32_t>(nbuf)) {
                     buf = 0;
                     tphase ^= 1u;
@@ -487,6 +571,73 @@ __global__ void __launch_bounds__(kTsThreads, 1)
             ex.relu = p.relu != 0;
             ex.rdelta = p.resid ? p.resid - p.d : 0;
             const float beta_e = p.resid ? 1.0f : beta;  // a residual takes the place of the beta term
+            if constexpr (ES == 2) {
+                if (tp.d_staged && !(p.ablate & 32)) {
+                    StageGeom sg;
+                    sg.base = tp.a_kind == A_IM2COL ? static_cast<long long>(b) * p.d_batch_stride
+                                                    : (p.d_offs ? p.d_offs[b] : static_cast<long long>(b) * p.d_batch_stride);
+                    sg.q0 = m0;
+                    sg.nslots = min(kBM, p.M - m0);
+                    sg.ois = tp.a_kind == A_IM2COL ? p.g.out_img_stride : 0;
+                    sg.colstride = colstride;
+                    sg.P = tp.a_kind == A_IM2COL ? p.g.P : 0;
+                    stage_geom_finish(sg);
+                    if (sg.runs <= kStageMaxRuns) {
+                        const int slot = warp * 32 + lane;
+                        StageRun srun;
+                        if (row_ok) srun = stage_run(sg, sg.P ? i / sg.P - sg.img0 : 0);
+                        const long long d_elem0 = static_cast<long long>(reinterpret_cast<uintptr_t>(p.d) >> 1);
+                        for (int cc = 0; cc < ncols; cc += 32) {
+                            uint32_t v[32];
+                            ptx::tmem_ld_32x32(trow + cc, v);
+                            ptx::tmem_ld_wait();
+                            const int nc = min(32, ncols - cc);
+                            if (cc + 32 >= ncols) {  // last read of the accumulator
+                                ptx::tc_fence_before();
+                                ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));
+                            }
+                            float bv = 0.0f;
+                            if (bias != nullptr && lane < nc)
+                                bv = p.fmt == FMT_F16 ? out_load<OUT_F16>(bias + (cc + lane) * 2)
+                                                      : out_load<OUT_BF16>(bias + (cc + lane) * 2);
+                            if (p.resid != nullptr) {
+                                const char* rp = p.resid + (optr - p.d) + static_cast<long long>(cc) * colstride * 2;
+#pragma unroll
+                                for (int jj = 0; jj < 32; ++jj) {
+                                    float rv = 0.0f;
+                                    if (row_ok && jj < nc)
+                                        rv = p.fmt == FMT_F16 ? out_load<OUT_F16>(rp + jj * colstride * 2)
+                                                              : out_load<OUT_BF16>(rp + jj * colstride * 2);
+                                    v[jj] = __float_as_uint(alpha * __uint_as_float(v[jj]) + rv);
+                                }
+                            } else {
+#pragma unroll
+                                for (int jj = 0; jj < 32; ++jj) v[jj] = __float_as_uint(alpha * __uint_as_float(v[jj]));
+                            }
+                            const uint32_t sbuf = ptx::smem_u32(smem_raw) + static_cast<uint32_t>(tp.stage_off) + stage_buf * kStageBufBytes;
+                            const bool relu = p.relu != 0;
+#pragma unroll
+                            for (int jj = 0; jj < 32; ++jj) {
+                                float r = __uint_as_float(v[jj]) + __shfl_sync(0xffffffffu, bv, jj);
+                                r = relu ? fmaxf(r, 0.0f) : r;
+                                if (row_ok && jj < nc) {
+                                    const int idx = stage_index(srun, slot, d_elem0, colstride, n0 + cc + jj);
+                                    const unsigned short h = p.fmt == FMT_F16 ? to_bits16<OUT_F16>(r) : to_bits16<OUT_BF16>(r);
+                                    asm volatile("st.shared.u16 [%0], %1;" ::"r"(sbuf + static_cast<uint32_t>(jj * kStageRowStride + idx) * 2u), "h"(h) : "memory");
+                                }
+                            }
+                            epilogue_bar();
+                            staged_writeout(sg, sbuf, p.d, n0 + cc, nc, threadIdx.x);
+                            stage_buf ^= 1u;
+                        }
+                        if (++buf == static_cast<uint32_t>(nbuf)) {
+                            buf = 0;
+                            tphase ^= 1u;
+                        }
+                        continue;
+                    }
+                }
+            }
             if (p.ablate & 32) {
             } else if constexpr (ES == 4) {
                 epilogue_dispatch<OUT_F32>(trow, ncols, optr, colstride * ES, row_ok, alpha, beta_e,

@@ -187,6 +187,119 @@ __device__ __forceinline__ void epilogue_dispatch(uint32_t trow, int ncols_total
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Staged stores of 16-bit outputs.
+//
+// A warp that writes one 2-byte element per lane moves 64 bytes per store instruction, and stores
+// of that width were measured at about 0.4-0.5 TB/s for the whole GPU (one 4-byte word per lane:
+// about twice that) - far below what HBM accepts. Where a tile's results cannot leave through a
+// TMA store (planes that are not 16-byte multiples, offsets, the row form of the convolution)
+// the four epilogue warps therefore put a block of columns into shared memory first and write it
+// out together as 16-byte vectors.
+//
+// Model. The tile's valid rows, in lane order, are `nslots` consecutive output pixels q0, q0+1, ..
+// ("slots"). For a convolution pixel q lies in image q / P at offset q % P of every channel plane,
+// so the slots split into at most four runs (one per image the tile touches), each contiguous in
+// memory for a fixed column; a GEMM tile is one run (P = 0). Element (slot s of run r, column j)
+// sits at element offset  base + img_r*ois + j*colstride + (q0 + s - img_r*P)  of D.
+// In shared memory column jj of the block occupies kStageRowStride elements; run r starts at
+// index rb_r + sh, where rb_r is a multiple of 8 and sh = (global element address of the run's
+// first element in that column) mod 8: 16-byte chunks of shared memory then map to 16-byte
+// aligned chunks of global memory, whatever the alignment of D, of the planes or of the run.
+constexpr int kStageCols = 32;
+constexpr int kStageRowStride = 200;  // >= 128 slots + 3 gaps of 16 + 7 of shift, multiple of 8
+constexpr int kStageBufBytes = kStageCols * kStageRowStride * 2;
+constexpr int kStageBytes = 2 * kStageBufBytes;  // two blocks: one is written while the other drains
+constexpr int kStageMaxRuns = 4;
+
+struct StageGeom {        // uniform over the tile
+    long long base;       // element offset of (image 0, column 0, pixel 0) for this batch entry
+    long long q0;         // pixel index of slot 0
+    long long ois;        // elements between images
+    long long colstride;  // elements between columns
+    int nslots;
+    int P;                // pixels per image; 0: no images (one run)
+    int img0, runs;       // image of slot 0, number of runs
+};
+
+struct StageRun {
+    int s, len, rb;       // first slot, slots, shared-memory index base (multiple of 8)
+    long long gelem;      // element offset in D of the run's first element, column 0
+};
+
+__device__ __forceinline__ void stage_geom_finish(StageGeom& g) {
+    g.img0 = g.P ? static_cast<int>(g.q0 / g.P) : 0;
+    g.runs = g.P ? static_cast<int>((g.q0 + g.nslots - 1) / g.P) - g.img0 + 1 : 1;
+}
+
+__device__ __forceinline__ StageRun stage_run(const StageGeom& g, int r) {
+    StageRun run;
+    const long long img = g.img0 + r;
+    run.s = r == 0 ? 0 : static_cast<int>(img * g.P - g.q0);
+    const int e = g.P ? min(g.nslots, static_cast<int>((img + 1) * g.P - g.q0)) : g.nslots;
+    run.len = e - run.s;
+    run.rb = ((run.s + 7) & ~7) + 16 * r;
+    run.gelem = g.base + img * g.ois + (g.q0 + run.s - img * g.P);
+    return run;
+}
+
+// The four epilogue warps (threads 0-127 of the CTA) meet here; barrier 0 belongs to __syncthreads.
+__device__ __forceinline__ void epilogue_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// Shared-memory index of (slot, column) for the staging thread; `run` is the slot's own run and
+// d_elem0 = (address of D) / 2.
+__device__ __forceinline__ int stage_index(const StageRun& run, int slot, long long d_elem0, long long colstride,
+                                           long long col) {
+    const int sh = static_cast<int>((d_elem0 + run.gelem + col * colstride) & 7);
+    return run.rb + sh + (slot - run.s);
+}
+
+// Writes the staged block (columns col0 .. col0+ncols-1 of D) to global memory. tid = 0..127.
+// Half-warps take (column, run) items; lane l of a half-warp takes 16-byte chunks l, l+16 of the
+// item. Chunks that lie wholly inside the run leave as one 16-byte store, the ragged first and
+// last chunk element by element.
+__device__ __forceinline__ void staged_writeout(const StageGeom& g, uint32_t sbuf, char* d, long long col0, int ncols,
+                                                int tid) {
+    const long long d_elem0 = static_cast<long long>(reinterpret_cast<uintptr_t>(d) >> 1);
+    const int l16 = tid & 15;
+    const int items = ncols * g.runs;
+    for (int it = tid >> 4; it < items; it += 8) {
+        const int jj = it / g.runs;
+        const int r = it - jj * g.runs;
+        const StageRun run = stage_run(g, r);
+        const long long gfirst = run.gelem + (col0 + jj) * g.colstride;  // element offset of the run's first element
+        const int sh = static_cast<int>((d_elem0 + gfirst) & 7);
+        const int nchunks = (sh + run.len + 7) >> 3;
+        const uint32_t scol = sbuf + static_cast<uint32_t>(jj * kStageRowStride + run.rb) * 2u;
+        char* gcol = d + (gfirst - sh) * 2;  // 16-byte aligned
+        for (int c = l16; c < nchunks; c += 16) {
+            const int lo = max(0, sh - 8 * c);
+            const int hi = min(8, sh + run.len - 8 * c);
+            const uint32_t sa = scol + static_cast<uint32_t>(c) * 16u;
+            if (lo == 0 && hi == 8) {
+                uint4 v;
+                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                             : "r"(sa)
+                             : "memory");
+                *reinterpret_cast<uint4*>(gcol + c * 16) = v;
+            } else {
+                for (int t = lo; t < hi; ++t) {
+                    unsigned short h;
+                    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(h) : "r"(sa + t * 2u) : "memory");
+                    *reinterpret_cast<unsigned short*>(gcol + c * 16 + t * 2) = h;
+                }
+            }
+        }
+    }
+}
+
+template <int OUT>
+__device__ __forceinline__ unsigned short to_bits16(float v) {
+    if constexpr (OUT == OUT_F16) return __half_as_ushort(__float2half_rn(v));
+    else return __bfloat16_as_ushort(__float2bfloat16_rn(v));
+}
+
 // Adds (or, for the first chunk, stores) one finished K-chunk accumulator to the running fp32
 // sums in shared memory. The tensor core truncates when it adds into its fp32 accumulator, a
 // bias that grows linearly with the number of accumulation steps (about 6e-9 * K relative for
