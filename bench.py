@@ -658,6 +658,8 @@ def main():
     ap.add_argument("--headline-only", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=None, help="images per GPU for conv_c2 (profiling: a small case)")
+    ap.add_argument("--shape", default="64,56,64,3,1,1", help="--workload conv: Cin,H,Cout,k,stride,pad")
+    ap.add_argument("--dtype", default="f16", help="--workload conv: f16, bf16 or f32")
     ap.add_argument("--overlap-gather", action="store_true",
                     help="row-sharded GEMM: all-gather finished panels while the next panel is computed")
     ap.add_argument("--kernel-only", action="store_true",
@@ -695,6 +697,18 @@ def main():
             "bgemm_f16_b1024_512x512x64_" + tag, "f16", 512, 512, 64, batch=1024, ta=ta, tb=tb, alpha=0.125))
         table["batched_c4_b_" + tag] = (lambda tag=tag, ta=ta, tb=tb: GemmWorkload(
             "bgemm_f16_b1024_512x64x512_" + tag, "f16", 512, 64, 512, batch=1024, ta=ta, tb=tb, alpha=0.125))
+    if args.workload == "conv":  # profiling aid: one convolution layer, e.g. --shape 64,56,64,3,1,1 --batch 16 --dtype f16
+        cin, h, cout, k, st_, pd = [int(x) for x in args.shape.split(",")]
+        w = ConvC2(shape=dict(N=args.batch or 16, C=cin, H=h, W=h, Co=cout, KH=k, KW=k, pad=pd, stride=st_, group=1),
+                   dtype=args.dtype)
+        w.setup(device, 0, w.sets_needed())
+        n = steps if args.steps is not None else 20
+        ms, _, _ = time_steps(w.step, n, warmup, 1)
+        sec = ms / 1e3 / n
+        print(json.dumps({"workload": "conv", "shape": args.shape, "batch": w.shape["N"], "dtype": args.dtype,
+                          "us_per_step": sec * 1e6, "tflops": w.flops / sec / 1e12,
+                          "algorithmic_bytes": w.bytes, "device_status": dlf_b200.device_status()}), flush=True)
+        return
     if args.workload == "resnet_sweep":  # development aid: config 3 alone, per layer
         summary, rows = resnet_sweep(device, peaks, args.batch or 256, steps if args.steps is not None else 10)
         print(json.dumps({"resnet50_v1_convs_f16": summary, "layers": rows, "device_status": dlf_b200.device_status()}), flush=True)

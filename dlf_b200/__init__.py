@@ -66,6 +66,17 @@ def _declare(L):
     L.dlf_b200_avgpool.argtypes = [c_int] + [c_size] * 16 + [c_int, c_void, c_void, c_void]
     L.dlf_b200_conv2d_workspace_bytes.restype = c_size
     L.dlf_b200_conv2d_workspace_bytes.argtypes = [c_int] + [c_size] * 10
+    L.dlf_b200_level3_workspace_bytes.restype = c_size
+    L.dlf_b200_level3_workspace_bytes.argtypes = [c_int, c_int, c_size, c_size]
+    L.dlf_b200_symm.restype = c_int
+    L.dlf_b200_symm.argtypes = [c_int] * 4 + [c_size, c_size, c_void, c_void, c_size, c_void, c_size, c_void, c_void,
+                                              c_size, c_void, c_size, c_void]
+    L.dlf_b200_syrk.restype = c_int
+    L.dlf_b200_syrk.argtypes = [c_int] * 4 + [c_size, c_size, c_void, c_void, c_size, c_void, c_void, c_size, c_void,
+                                              c_size, c_void]
+    for fn in (L.dlf_b200_trmm, L.dlf_b200_trsm):
+        fn.restype = c_int
+        fn.argtypes = [c_int] * 6 + [c_size, c_size, c_void, c_void, c_size, c_void, c_size, c_void, c_size, c_void]
     L.dlf_b200_status_string.restype = ctypes.c_char_p
     L.dlf_b200_status_string.argtypes = [c_int]
     L.dlf_b200_device_status.restype = c_int
@@ -85,6 +96,11 @@ EXPORTED_SYMBOLS = (
     "dlf_b200_conv2d",
     "dlf_b200_conv2d_fused",
     "dlf_b200_conv2d_workspace_bytes",
+    "dlf_b200_level3_workspace_bytes",
+    "dlf_b200_symm",
+    "dlf_b200_syrk",
+    "dlf_b200_trmm",
+    "dlf_b200_trsm",
     "dlf_b200_maxpool",
     "dlf_b200_avgpool",
     "dlf_b200_status_string",

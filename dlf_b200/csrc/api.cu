@@ -21,6 +21,7 @@
 #include "../../include/dlf_b200.h"
 #include "contraction.cuh"
 #include "contraction_ts.cuh"
+#include "level3.cuh"
 #include "pooling.cuh"
 
 using namespace dlfb200;
@@ -232,6 +233,7 @@ struct Problem {
     Im2colGeom g{};
     // row form of a convolution (contraction_ts.cuh, A_ROWCONV); rc_kw == 0: not used
     int rc_kw = 0, rc_cpt = 0, rc_T = 0, rc_lo = 0, rc_sw = 1, rc_wv = 0, rc_dmin = 0;
+    int rc_tpi = 0;  // row form with image-aligned tiles and TMA stores: tiles per image (0: off)
     // caller-provided scratch for the packed filter bank of a convolution (may be null)
     unsigned char* pack_ws = nullptr;
     size_t pack_ws_bytes = 0;
@@ -381,12 +383,14 @@ int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
     long long tiles_m = (q.M + kBM - 1) / kBM;
     // fp32 with more than 16 k-blocks (K > 512): accumulate in chunks of 8 k-blocks and sum the
     // chunks in shared memory (the tensor core's accumulate truncates; see drain_chunk). The
-    // float[BN][128] sum array limits such tiles to 128 columns.
+    // float[BN][128] sum array (96 KB at 192 columns) and two operand stages of 48 KB limit such
+    // tiles to 192 columns, which is also the widest tile that leaves room for two accumulators.
     const long long num_kb_all = (q.K + BK - 1) / BK;
     const int kc_blocks = (q.es == 4 && num_kb_all > 16 && !(g_force_generic.load() & 0x1000)) ? 8 : 0;
-    int bn = choose_bn_ts(q, st.num_sms, kc_blocks ? 128 : 256, a_cols, num_kb_all);
+    const int kc_max_bn = (g_force_generic.load() >> 16) & 0x200 ? 128 : 192;  // (0x200: the former limit, for comparison)
+    int bn = choose_bn_ts(q, st.num_sms, kc_blocks ? kc_max_bn : 256, a_cols, num_kb_all);
     const int forced = g_force_bn.load();
-    if (forced >= 64 && forced <= (kc_blocks ? 128 : 256) && forced % 32 == 0) bn = forced;
+    if (forced >= 64 && forced <= (kc_blocks ? 192 : 256) && forced % 32 == 0) bn = forced;
     // an MN-major B tile is made of whole groups of BK columns (the UMMA reads all k-rows of the
     // last group it touches): a width that ends inside a group would make it read past the stage
     if (!q.b.k_major && bn % BK != 0) bn = bn / BK * BK;
@@ -394,6 +398,7 @@ int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
     if (q.rc_kw) {  // tile = 4 warps x rc_T output positions by rc_cpt channels (x rc_kw columns)
         bn = q.rc_cpt * q.rc_kw;
         tiles_m = (q.M + 4 * q.rc_T - 1) / (4 * q.rc_T);
+        if (q.rc_tpi) tiles_m = q.M / (static_cast<long long>(q.g.OH) * q.rc_wv) * q.rc_tpi;  // images x tiles per image
         tiles_n = (q.N + q.rc_cpt - 1) / q.rc_cpt;
     }
     const long long total = q.batch * tiles_m * tiles_n;
@@ -418,11 +423,14 @@ int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
     const int static_smem = q.es == 2 ? st.static_smem_ts2 : st.static_smem_ts4;
     const int stage_bytes = bn * 128 * (q.es == 4 ? 2 : 1);
     const int sums_bytes = kc_blocks ? bn * 128 * 4 : 0;
-    if (kc_blocks && bn > 128) return kUnexpectedError;
+    if (kc_blocks && bn > 192) return kUnexpectedError;
     // 16-bit outputs for which nothing of D is read leave through staged 16-byte stores
     // (epilogue.cuh); a residual is read by the staging threads themselves
     const bool d_staged = q.es == 2 && q.beta == 0.0f && q.betas == nullptr && !((g_force_generic.load() >> 16) & 64);
-    const int out_stage_bytes = d_staged ? kStageBytes : 0;
+    // row form with image-aligned tiles: two blocks of [channels of the tile][positions of the tile]
+    const int rc_tma_buf = q.rc_tpi ? (q.rc_cpt * 4 * q.rc_T * 2 + 127) / 128 * 128 : 0;
+    const int out_stage_bytes = !d_staged ? 0 : (q.rc_tpi ? 2 * rc_tma_buf : kStageBytes) + 128;  // + alignment slack
+    if (q.rc_tpi && !d_staged) return kUnexpectedError;
     // the k table is padded to a multiple of 1024 in the layout below: count it that way here too
     int stages = (kSmemPerBlockOptin - static_smem - 1024 - ((ktable_bytes + 1023) / 1024 * 1024) - sums_bytes - out_stage_bytes) / stage_bytes;
     const int tmem_stages = (512 - acc_bufs * bn) / a_cols;
@@ -480,6 +488,9 @@ int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
     tp.sums_off = sums_off;
     tp.d_staged = d_staged ? 1 : 0;
     tp.stage_off = sums_off + sums_bytes;
+    tp.rc_tpi = q.rc_tpi;
+    tp.rc_tma = q.rc_tpi ? 1 : 0;
+    tp.rc_tma_buf = rc_tma_buf;
     tp.acc_bufs = acc_bufs;
     tp.ktable_bytes = ktable_bytes;
 
@@ -509,6 +520,22 @@ int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
         if (encode_map(st, &tm_b, q.b, q.es, q.N, q.K, q.batch, bn) == kSuccess) tp.b_tma = 1;
     }
 
+    CUtensorMap tm_d;
+    std::memset(&tm_d, 0, sizeof(tm_d));
+    if (q.rc_tpi) {
+        // Y as {pixels of a plane, all channels, images}; a box is one tile's positions x 16 channels
+        const long long ctot = q.batch * q.N;
+        cuuint64_t dims[3] = {static_cast<cuuint64_t>(q.g.P), static_cast<cuuint64_t>(ctot),
+                              static_cast<cuuint64_t>(q.M / (static_cast<long long>(q.g.OH) * q.rc_wv))};
+        cuuint64_t strides[2] = {static_cast<cuuint64_t>(q.g.P) * 2u, static_cast<cuuint64_t>(q.g.out_img_stride) * 2u};
+        cuuint32_t box[3] = {static_cast<cuuint32_t>(4 * q.rc_T), 16u, 1u};
+        cuuint32_t estr[3] = {1, 1, 1};
+        CUresult r = st.encode(&tm_d, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, q.d, dims, strides, box, estr,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                               CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return kUnexpectedError;
+    }
+
     const unsigned grid = static_cast<unsigned>(total < st.num_sms ? total : st.num_sms);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid, 1, 1);
@@ -527,9 +554,9 @@ int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
                      q.es, bn, stages, acc_bufs, grid, dyn_smem, ktable_bytes, sums_bytes, tp.b_packed != nullptr,
                      cudaGetErrorString(cudaPeekAtLastError()));
     if (q.es == 2)
-        CUDA_TRY(cudaLaunchKernelEx(&cfg, contraction_ts_kernel<2>, tp, tm_b));
+        CUDA_TRY(cudaLaunchKernelEx(&cfg, contraction_ts_kernel<2>, tp, tm_b, tm_d));
     else
-        CUDA_TRY(cudaLaunchKernelEx(&cfg, contraction_ts_kernel<4>, tp, tm_b));
+        CUDA_TRY(cudaLaunchKernelEx(&cfg, contraction_ts_kernel<4>, tp, tm_b, tm_d));
     g_launches.fetch_add(1);
     CUDA_TRY(cudaGetLastError());
     return kSuccess;
@@ -811,6 +838,93 @@ int setup_gemm(Problem& q, int dtype, int layout, int ta, int tb, size_t m, size
     }
     q.d = static_cast<char*>(c);
     q.ldd = static_cast<long long>(c_ld);
+    return kSuccess;
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------------
+// helpers of the level-3 routines (symm, syrk, trmm, trsm) further down
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+enum : int { kUpper = 121, kLower = 122, kNonUnit = 131, kUnit = 132, kLeft = 141, kRight = 142 };
+
+void float_to_scalar(int fmt, float v, void* out) {
+    if (fmt == FMT_F16) {
+        const __half h = __float2half_rn(v);
+        std::memcpy(out, &h, 2);
+    } else if (fmt == FMT_BF16) {
+        const __nv_bfloat16 h = __float2bfloat16_rn(v);
+        std::memcpy(out, &h, 2);
+    } else {
+        std::memcpy(out, &v, 4);
+    }
+}
+
+int dtype_of(int fmt) { return fmt == FMT_F16 ? DLF_B200_HALF : (fmt == FMT_BF16 ? DLF_B200_BFLOAT16 : DLF_B200_SINGLE); }
+
+// row-major GEMM on device pointers with float scalars, through the public entry point
+int rm_gemm(int fmt, int ta, int tb, size_t m, size_t n, size_t k, float alpha, const void* a, size_t lda,
+            const void* b, size_t ldb, float beta, void* c, size_t ldc, void* stream) {
+    unsigned char al[4], be[4];
+    float_to_scalar(fmt, alpha, al);
+    float_to_scalar(fmt, beta, be);
+    return dlf_b200_gemm(dtype_of(fmt), DLF_B200_ROW_MAJOR, ta, tb, m, n, k, al, a, lda, b, ldb, be, c, ldc, stream);
+}
+
+unsigned l3_grid(long long total) {
+    const long long blocks = (total + 255) / 256;
+    return static_cast<unsigned>(blocks < 1 ? 1 : (blocks > 148 * 16 ? 148 * 16 : blocks));
+}
+
+char* align256(void* p) { return reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(p) + 255) & ~uintptr_t(255)); }
+
+template <typename T>
+int l3_expand(T* dst, const void* src, size_t ld, size_t n, bool symmetric, bool upper, bool unit, cudaStream_t s) {
+    l3_expand_square_kernel<T><<<l3_grid(static_cast<long long>(n) * n), 256, 0, s>>>(
+        dst, static_cast<const T*>(src), static_cast<long long>(ld), static_cast<int>(n), symmetric ? 1 : 0,
+        upper ? 1 : 0, unit ? 1 : 0);
+    g_launches.fetch_add(1);
+    CUDA_TRY(cudaGetLastError());
+    return kSuccess;
+}
+
+int l3_expand_any(int fmt, void* dst, const void* src, size_t ld, size_t n, bool symmetric, bool upper, bool unit,
+                  cudaStream_t s) {
+    if (fmt == FMT_F32) return l3_expand(static_cast<float*>(dst), src, ld, n, symmetric, upper, unit, s);
+    if (fmt == FMT_F16) return l3_expand(static_cast<__half*>(dst), src, ld, n, symmetric, upper, unit, s);
+    return l3_expand(static_cast<__nv_bfloat16*>(dst), src, ld, n, symmetric, upper, unit, s);
+}
+
+}  // namespace
+
+namespace {
+
+// common argument rules of trmm / trsm; on success the call is in row-major form
+int tri_args(int dtype, int& fmt, int& es, int layout, int& side, int& triangle, int a_transpose, int diagonal,
+             size_t& m, size_t& n, const void* alpha, const void* a, size_t a_ld, const void* b, size_t b_ld) {
+    if (!dtype_info(dtype, fmt, es)) return kNotImplemented;
+    if (layout != DLF_B200_ROW_MAJOR && layout != DLF_B200_COL_MAJOR) return kInvalidValue;
+    if ((side != kLeft && side != kRight) || (triangle != kUpper && triangle != kLower)) return kInvalidValue;
+    if (a_transpose < DLF_B200_NO_TRANS || a_transpose > DLF_B200_CONJ_TRANS) return kInvalidValue;
+    if (diagonal != kNonUnit && diagonal != kUnit) return kInvalidValue;
+    if (m == 0 || n == 0) return kInvalidDimension;
+    const bool row = layout == DLF_B200_ROW_MAJOR;
+    if (a_ld < (side == kLeft ? m : n)) return kInvalidLeadDimA;
+    if (b_ld < (row ? n : m)) return kInvalidLeadDimB;
+    if (a == nullptr) return kInvalidMatrixA;
+    if (b == nullptr) return kInvalidMatrixB;
+    if (alpha == nullptr) return kInvalidValue;
+    // column-major: B^T (n x m, row-major) = B^T op(T)^T: the other side, and the stored
+    // triangle of the row-major view of A is the other one; op stays as given
+    if (!row) {
+        side = side == kLeft ? kRight : kLeft;
+        triangle = triangle == kUpper ? kLower : kUpper;
+        const size_t t = m;
+        m = n;
+        n = t;
+    }
     return kSuccess;
 }
 
@@ -1100,9 +1214,9 @@ int dlf_b200_conv2d_fused(int dtype, size_t batches, size_t channels, size_t hei
     if (path != 2 && path != 4 && sw >= 1 && sw <= 4 && dilation_w == 1 && dmax >= 0 && taps >= 2 && taps <= 8 &&
         static_cast<long long>(output_w) <= wv && lo + hi <= 16 && !(sw > 1 && path == 5) &&
         static_cast<long long>(batches) * output_h * wv < INT_MAX - 4096) {
-        // fp32 with K' = C*KH*sw > 512 sums K-chunks in a float[N][128] shared array: N <= 128 then
+        // fp32 with K' = C*KH*sw > 512 sums K-chunks in a float[N][128] shared array: N <= 192 then
         const bool chunked = q.es == 4 && cg * static_cast<long long>(kernel_h) * sw > 512;
-        const int cpt_max = static_cast<int>(((chunked ? 128 : 256) / taps) / 16 * 16);
+        const int cpt_max = static_cast<int>(((chunked ? 192 : 256) / taps) / 16 * 16);
         const int n_tiles = static_cast<int>((ng + cpt_max - 1) / cpt_max);
         int cpt = static_cast<int>(((ng + n_tiles - 1) / n_tiles + 15) / 16 * 16);
         if (cpt > cpt_max) cpt = cpt_max;
@@ -1113,6 +1227,21 @@ int dlf_b200_conv2d_fused(int dtype, size_t batches, size_t channels, size_t hei
         r.rc_cpt = cpt;
         r.rc_lo = static_cast<int>(lo);
         r.rc_T = 32 - static_cast<int>(lo + hi);
+        // 16-bit results of large planes leave as TMA stores: tiles are then aligned to images (a
+        // tile is one contiguous range of pixels of one image) and start on 16-byte boundaries
+        // (even rc_T). Needs every position to be an output (wv == OW), planes of a 16-byte
+        // multiple, channel blocks of 16 that stay inside their group, and a plane large enough
+        // that the partly filled last tile of an image is a small loss.
+        {
+            const int t_even = r.rc_T & ~1;
+            const long long ohw = static_cast<long long>(output_h) * wv;
+            if (q.es == 2 && wv == static_cast<long long>(output_w) && (P * 2) % 16 == 0 && t_even >= 16 &&
+                ohw >= 4ll * 4 * t_even && (group == 1 || ng % 16 == 0) &&
+                (reinterpret_cast<uintptr_t>(y) & 15u) == 0 && !((g_force_generic.load() >> 16) & (64 | 128))) {
+                r.rc_T = t_even;
+                r.rc_tpi = static_cast<int>((ohw + 4 * t_even - 1) / (4 * t_even));
+            }
+        }
         r.rc_sw = static_cast<int>(sw);
         r.rc_wv = static_cast<int>(wv);
         r.rc_dmin = static_cast<int>(dmin);
@@ -1157,6 +1286,217 @@ int dlf_b200_conv2d_fused(int dtype, size_t batches, size_t channels, size_t hei
         return kSuccess;
     }
     return launch(q, static_cast<cudaStream_t>(stream));
+}
+
+// ---------------------------------------------------------------------------------------------
+// Level-3 routines on the GEMM main loop: symm, syrk, trmm, trsm
+// (gpgpu/include/gblas.h:506-586). Scheme as in level3.cuh.
+// ---------------------------------------------------------------------------------------------
+
+size_t dlf_b200_level3_workspace_bytes(int routine, int dtype, size_t m, size_t n) {
+    int fmt = 0, es = 0;
+    if (!dtype_info(dtype, fmt, es)) return 0;
+    switch (routine) {
+        case DLF_B200_SYMM: { const size_t ka = m > n ? m : n; return ka * ka * es + 512; }           // the expanded A
+        case DLF_B200_SYRK: return n * n * es + 512;                                                 // alpha*op(A)*op(A)^T
+        case DLF_B200_TRMM: { const size_t ka = m > n ? m : n; return ka * ka * es + m * n * es + 1024; }  // expanded A + copy of B
+        case DLF_B200_TRSM: return 0;
+        default: return 0;
+    }
+}
+
+int dlf_b200_symm(int dtype, int layout, int side, int triangle, size_t m, size_t n, const void* alpha,
+                  const void* a, size_t a_ld, const void* b, size_t b_ld, const void* beta, void* c, size_t c_ld,
+                  void* workspace, size_t workspace_bytes, void* stream) {
+    int fmt = 0, es = 0;
+    if (!dtype_info(dtype, fmt, es)) return kNotImplemented;
+    if (layout != DLF_B200_ROW_MAJOR && layout != DLF_B200_COL_MAJOR) return kInvalidValue;
+    if ((side != kLeft && side != kRight) || (triangle != kUpper && triangle != kLower)) return kInvalidValue;
+    if (m == 0 || n == 0) return kInvalidDimension;
+    const size_t ka = side == kLeft ? m : n;  // order of A
+    const bool row = layout == DLF_B200_ROW_MAJOR;
+    if (a_ld < ka) return kInvalidLeadDimA;
+    if (b_ld < (row ? n : m)) return kInvalidLeadDimB;
+    if (c_ld < (row ? n : m)) return kInvalidLeadDimC;
+    if (a == nullptr) return kInvalidMatrixA;
+    if (b == nullptr) return kInvalidMatrixB;
+    if (c == nullptr) return kInvalidMatrixC;
+    if (alpha == nullptr || beta == nullptr) return kInvalidValue;
+    // column-major: C^T (n x m, row-major) = B^T S (Left) resp. S B^T (Right), and the stored
+    // triangle of A^T is the other one
+    if (!row) {
+        side = side == kLeft ? kRight : kLeft;
+        triangle = triangle == kUpper ? kLower : kUpper;
+        const size_t t = m;
+        m = n;
+        n = t;
+    }
+    const size_t need = ka * ka * es;
+    char* full = align256(workspace);
+    if (workspace == nullptr || workspace_bytes < need + static_cast<size_t>(full - static_cast<char*>(workspace)))
+        return kInsufficientMemoryTemp;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    StreamDevice sd(s);
+    if (sd.rc != kSuccess) return sd.rc;
+    int rc = l3_expand_any(fmt, full, a, a_ld, ka, true, triangle == kUpper, false, s);
+    if (rc != kSuccess) return rc;
+    const float al = scalar_to_float(fmt, alpha), be = scalar_to_float(fmt, beta);
+    if (side == kLeft)
+        return rm_gemm(fmt, DLF_B200_NO_TRANS, DLF_B200_NO_TRANS, m, n, m, al, full, m, b, b_ld, be, c, c_ld, stream);
+    return rm_gemm(fmt, DLF_B200_NO_TRANS, DLF_B200_NO_TRANS, m, n, n, al, b, b_ld, full, n, be, c, c_ld, stream);
+}
+
+int dlf_b200_syrk(int dtype, int layout, int triangle, int a_transpose, size_t n, size_t k, const void* alpha,
+                  const void* a, size_t a_ld, const void* beta, void* c, size_t c_ld, void* workspace,
+                  size_t workspace_bytes, void* stream) {
+    int fmt = 0, es = 0;
+    if (!dtype_info(dtype, fmt, es)) return kNotImplemented;
+    if (layout != DLF_B200_ROW_MAJOR && layout != DLF_B200_COL_MAJOR) return kInvalidValue;
+    if (triangle != kUpper && triangle != kLower) return kInvalidValue;
+    if (a_transpose < DLF_B200_NO_TRANS || a_transpose > DLF_B200_CONJ_TRANS) return kInvalidValue;
+    if (n == 0 || k == 0) return kInvalidDimension;
+    const bool row = layout == DLF_B200_ROW_MAJOR;
+    bool trans = a_transpose != DLF_B200_NO_TRANS;
+    // column-major: the stored A is the row-major transpose, C^T = C
+    if (!row) {
+        trans = !trans;
+        triangle = triangle == kUpper ? kLower : kUpper;
+    }
+    if (a_ld < (trans ? n : k)) return kInvalidLeadDimA;
+    if (c_ld < n) return kInvalidLeadDimC;
+    if (a == nullptr) return kInvalidMatrixA;
+    if (c == nullptr) return kInvalidMatrixC;
+    if (alpha == nullptr || beta == nullptr) return kInvalidValue;
+    const size_t need = n * n * es;
+    char* prod = align256(workspace);
+    if (workspace == nullptr || workspace_bytes < need + static_cast<size_t>(prod - static_cast<char*>(workspace)))
+        return kInsufficientMemoryTemp;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    StreamDevice sd(s);
+    if (sd.rc != kSuccess) return sd.rc;
+    const float al = scalar_to_float(fmt, alpha), be = scalar_to_float(fmt, beta);
+    const int ta = trans ? DLF_B200_TRANS : DLF_B200_NO_TRANS, tb = trans ? DLF_B200_NO_TRANS : DLF_B200_TRANS;
+    int rc = rm_gemm(fmt, ta, tb, n, n, k, al, a, a_ld, a, a_ld, 0.0f, prod, n, stream);
+    if (rc != kSuccess) return rc;
+    const unsigned grid = l3_grid(static_cast<long long>(n) * n);
+    const int up = triangle == kUpper ? 1 : 0;
+    if (fmt == FMT_F32)
+        l3_triangle_merge_kernel<float><<<grid, 256, 0, s>>>(static_cast<float*>(c), static_cast<long long>(c_ld), reinterpret_cast<const float*>(prod), static_cast<int>(n), up, be);
+    else if (fmt == FMT_F16)
+        l3_triangle_merge_kernel<__half><<<grid, 256, 0, s>>>(static_cast<__half*>(c), static_cast<long long>(c_ld), reinterpret_cast<const __half*>(prod), static_cast<int>(n), up, be);
+    else
+        l3_triangle_merge_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(static_cast<__nv_bfloat16*>(c), static_cast<long long>(c_ld), reinterpret_cast<const __nv_bfloat16*>(prod), static_cast<int>(n), up, be);
+    g_launches.fetch_add(1);
+    CUDA_TRY(cudaGetLastError());
+    return kSuccess;
+}
+
+
+int dlf_b200_trmm(int dtype, int layout, int side, int triangle, int a_transpose, int diagonal, size_t m, size_t n,
+                  const void* alpha, const void* a, size_t a_ld, void* b, size_t b_ld, void* workspace,
+                  size_t workspace_bytes, void* stream) {
+    int fmt = 0, es = 0;
+    int rc = tri_args(dtype, fmt, es, layout, side, triangle, a_transpose, diagonal, m, n, alpha, a, a_ld, b, b_ld);
+    if (rc != kSuccess) return rc;
+    const size_t ka = side == kLeft ? m : n;
+    char* full = align256(workspace);
+    char* copy = align256(full + ka * ka * es);
+    const size_t need = static_cast<size_t>(copy - static_cast<char*>(workspace)) + m * n * es;
+    if (workspace == nullptr || workspace_bytes < need) return kInsufficientMemoryTemp;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    StreamDevice sd(s);
+    if (sd.rc != kSuccess) return sd.rc;
+    rc = l3_expand_any(fmt, full, a, a_ld, ka, false, triangle == kUpper, diagonal == kUnit, s);
+    if (rc != kSuccess) return rc;
+    // the product reads all of B while it writes B: work from a copy
+    CUDA_TRY(cudaMemcpy2DAsync(copy, n * es, b, b_ld * es, n * es, m, cudaMemcpyDeviceToDevice, s));
+    const float al = scalar_to_float(fmt, alpha);
+    const int ta = a_transpose == DLF_B200_NO_TRANS ? DLF_B200_NO_TRANS : DLF_B200_TRANS;
+    if (side == kLeft)
+        return rm_gemm(fmt, ta, DLF_B200_NO_TRANS, m, n, m, al, full, m, copy, n, 0.0f, b, b_ld, stream);
+    return rm_gemm(fmt, DLF_B200_NO_TRANS, ta, m, n, n, al, copy, n, full, n, 0.0f, b, b_ld, stream);
+}
+
+int dlf_b200_trsm(int dtype, int layout, int side, int triangle, int a_transpose, int diagonal, size_t m, size_t n,
+                  const void* alpha, const void* a, size_t a_ld, void* b, size_t b_ld, void* workspace,
+                  size_t workspace_bytes, void* stream) {
+    (void)workspace;
+    (void)workspace_bytes;
+    int fmt = 0, es = 0;
+    int rc = tri_args(dtype, fmt, es, layout, side, triangle, a_transpose, diagonal, m, n, alpha, a, a_ld, b, b_ld);
+    if (rc != kSuccess) return rc;
+    if (m > INT_MAX || n > INT_MAX) return kInvalidDimension;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    StreamDevice sd(s);
+    if (sd.rc != kSuccess) return sd.rc;
+    clear_stale_error();
+    const bool trans = a_transpose != DLF_B200_NO_TRANS;
+    const bool lower = triangle == kLower;
+    const bool op_lower = lower != trans;
+    const float al = scalar_to_float(fmt, alpha);
+    const char* A = static_cast<const char*>(a);
+    char* B = static_cast<char*>(b);
+    auto a_at = [&](size_t r, size_t c) { return A + (r * a_ld + c) * es; };
+    auto b_at = [&](size_t r, size_t c) { return B + (r * b_ld + c) * es; };
+    if (al != 1.0f) {
+        const unsigned grid = l3_grid(static_cast<long long>(m) * n);
+        if (fmt == FMT_F32) l3_scale_kernel<float><<<grid, 256, 0, s>>>(reinterpret_cast<float*>(B), static_cast<long long>(b_ld), static_cast<int>(m), static_cast<int>(n), al);
+        else if (fmt == FMT_F16) l3_scale_kernel<__half><<<grid, 256, 0, s>>>(reinterpret_cast<__half*>(B), static_cast<long long>(b_ld), static_cast<int>(m), static_cast<int>(n), al);
+        else l3_scale_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(reinterpret_cast<__nv_bfloat16*>(B), static_cast<long long>(b_ld), static_cast<int>(m), static_cast<int>(n), al);
+        g_launches.fetch_add(1);
+        CUDA_TRY(cudaGetLastError());
+    }
+    auto diag_solve = [&](size_t d0, size_t nb, char* bblk, size_t nsys) -> int {
+        const unsigned grid = static_cast<unsigned>((nsys + kTrsmThreads - 1) / kTrsmThreads);
+        const int rs = side == kRight ? 1 : 0;
+        if (fmt == FMT_F32)
+            l3_trsm_diag_kernel<float><<<grid, kTrsmThreads, 0, s>>>(reinterpret_cast<const float*>(a_at(d0, d0)), static_cast<long long>(a_ld), trans, lower, diagonal == kUnit, rs, static_cast<int>(nb), reinterpret_cast<float*>(bblk), static_cast<long long>(b_ld), static_cast<int>(nsys));
+        else if (fmt == FMT_F16)
+            l3_trsm_diag_kernel<__half><<<grid, kTrsmThreads, 0, s>>>(reinterpret_cast<const __half*>(a_at(d0, d0)), static_cast<long long>(a_ld), trans, lower, diagonal == kUnit, rs, static_cast<int>(nb), reinterpret_cast<__half*>(bblk), static_cast<long long>(b_ld), static_cast<int>(nsys));
+        else
+            l3_trsm_diag_kernel<__nv_bfloat16><<<grid, kTrsmThreads, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(a_at(d0, d0)), static_cast<long long>(a_ld), trans, lower, diagonal == kUnit, rs, static_cast<int>(nb), reinterpret_cast<__nv_bfloat16*>(bblk), static_cast<long long>(b_ld), static_cast<int>(nsys));
+        g_launches.fetch_add(1);
+        CUDA_TRY(cudaGetLastError());
+        return kSuccess;
+    };
+    const int N = DLF_B200_NO_TRANS, T = DLF_B200_TRANS;
+    if (side == kLeft) {
+        // op(T) X = B: row blocks of B, top to bottom when op(T) is lower, else bottom to top;
+        // every block first loses the contribution of the rows already solved (a GEMM)
+        const size_t blocks = (m + kTrsmBlock - 1) / kTrsmBlock;
+        for (size_t bi = 0; bi < blocks; ++bi) {
+            const size_t blk = op_lower ? bi : blocks - 1 - bi;
+            const size_t i0 = blk * kTrsmBlock, i1 = std::min<size_t>(m, i0 + kTrsmBlock), ib = i1 - i0;
+            if (op_lower && i0 > 0) {
+                rc = trans ? rm_gemm(fmt, T, N, ib, n, i0, -1.0f, a_at(0, i0), a_ld, b_at(0, 0), b_ld, 1.0f, b_at(i0, 0), b_ld, stream)
+                           : rm_gemm(fmt, N, N, ib, n, i0, -1.0f, a_at(i0, 0), a_ld, b_at(0, 0), b_ld, 1.0f, b_at(i0, 0), b_ld, stream);
+            } else if (!op_lower && i1 < m) {
+                rc = trans ? rm_gemm(fmt, T, N, ib, n, m - i1, -1.0f, a_at(i1, i0), a_ld, b_at(i1, 0), b_ld, 1.0f, b_at(i0, 0), b_ld, stream)
+                           : rm_gemm(fmt, N, N, ib, n, m - i1, -1.0f, a_at(i0, i1), a_ld, b_at(i1, 0), b_ld, 1.0f, b_at(i0, 0), b_ld, stream);
+            }
+            if (rc != kSuccess) return rc;
+            rc = diag_solve(i0, ib, b_at(i0, 0), n);
+            if (rc != kSuccess) return rc;
+        }
+    } else {
+        // X op(T) = B: column blocks of B, left to right when op(T) is upper, else right to left
+        const size_t blocks = (n + kTrsmBlock - 1) / kTrsmBlock;
+        for (size_t bi = 0; bi < blocks; ++bi) {
+            const size_t blk = op_lower ? blocks - 1 - bi : bi;
+            const size_t j0 = blk * kTrsmBlock, j1 = std::min<size_t>(n, j0 + kTrsmBlock), jb = j1 - j0;
+            if (!op_lower && j0 > 0) {
+                rc = trans ? rm_gemm(fmt, N, T, m, jb, j0, -1.0f, b_at(0, 0), b_ld, a_at(j0, 0), a_ld, 1.0f, b_at(0, j0), b_ld, stream)
+                           : rm_gemm(fmt, N, N, m, jb, j0, -1.0f, b_at(0, 0), b_ld, a_at(0, j0), a_ld, 1.0f, b_at(0, j0), b_ld, stream);
+            } else if (op_lower && j1 < n) {
+                rc = trans ? rm_gemm(fmt, N, T, m, jb, n - j1, -1.0f, b_at(0, j1), b_ld, a_at(j0, j1), a_ld, 1.0f, b_at(0, j0), b_ld, stream)
+                           : rm_gemm(fmt, N, N, m, jb, n - j1, -1.0f, b_at(0, j1), b_ld, a_at(j1, j0), a_ld, 1.0f, b_at(0, j0), b_ld, stream);
+            }
+            if (rc != kSuccess) return rc;
+            rc = diag_solve(j0, jb, b_at(0, j0), m);
+            if (rc != kSuccess) return rc;
+        }
+    }
+    return kSuccess;
 }
 
 int dlf_b200_conv2d(int dtype, size_t batches, size_t channels, size_t height, size_t width,

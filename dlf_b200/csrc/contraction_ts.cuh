@@ -91,7 +91,21 @@ struct TsParams {
     // shared memory (kStageBytes at byte offset stage_off of the dynamic segment) and write them
     // out as 16-byte vectors (see "Staged stores" in epilogue.cuh)
     int d_staged, stage_off;
+    // Row form with image-aligned tiles (rc_tpi = tiles per image, 0 = tiles run across images): a
+    // tile then is one contiguous range of one image's pixels for every channel, and 16-bit
+    // results leave as TMA stores (rc_tma; two blocks of rc_tma_buf bytes at stage_off).
+    int rc_tpi, rc_tma, rc_tma_buf;
 };
+
+// First position of row-form tile `tm`, and (image-aligned tiles) the image it belongs to.
+__device__ __forceinline__ int rowconv_pos0(const TsParams& tp, int tm, int OHW, int& tile_img) {
+    if (tp.rc_tpi) {
+        tile_img = tm / tp.rc_tpi;
+        return tile_img * OHW + (tm - tile_img * tp.rc_tpi) * 4 * tp.rc_T;
+    }
+    tile_img = -1;
+    return tm * 4 * tp.rc_T;
+}
 
 __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&v)[32]) {
     asm volatile(
@@ -240,7 +254,8 @@ __global__ void pack_weights_kernel(const TsParams tp, unsigned char* out, long 
 
 template <int ES>
 __global__ void __launch_bounds__(kTsThreads, 1)
-    contraction_ts_kernel(const __grid_constant__ TsParams tp, const __grid_constant__ CUtensorMap tmB) {
+    contraction_ts_kernel(const __grid_constant__ TsParams tp, const __grid_constant__ CUtensorMap tmB,
+                          const __grid_constant__ CUtensorMap tmD) {
     const Params& p = tp.base;
     constexpr int BK = 128 / ES;             // k per stage: 32 (fp32) or 64 (16-bit)
     constexpr int CPE = 16 / ES;
@@ -259,7 +274,8 @@ __global__ void __launch_bounds__(kTsThreads, 1)
     __shared__ __align__(8) uint64_t tempty_bar[2];
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
-    __shared__ int epi_ok[4];  // staged stores: outcome of each epilogue warp's wait for the tile
+    __shared__ int epi_ok[2][4];  // staged stores: outcome of each epilogue warp's wait for the tile
+    __shared__ StageTile st_tab[2];
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -348,12 +364,51 @@ __global__ void __launch_bounds__(kTsThreads, 1)
         // ------------------------------------------------------------ epilogue
         uint32_t buf = 0, tphase = 0;
         uint32_t stage_buf = 0;  // which of the two staging blocks the next block of columns takes
+        uint32_t tile_par = 0;   // alternates between consecutive tiles of this CTA
+        // staging blocks of the output (TMA stores want their source on a 128-byte boundary)
+        const uint32_t stage_base = (ptx::smem_u32(smem_raw) + static_cast<uint32_t>(tp.stage_off) + 127u) & ~127u;
         const int kc = tp.kc_blocks > 0 ? tp.kc_blocks : num_kb;
         float* part_row = reinterpret_cast<float*>(smem_raw + tp.sums_off) + warp * 32 + lane;
         bool alive = true;
-        for (int t = blockIdx.x; alive && t < p.total_tiles; t += gridDim.x) {
+        for (int t = blockIdx.x; alive && t < p.total_tiles; t += gridDim.x, tile_par ^= 1u) {
             int b, m0, n0;
             decode_tile(p, t, b, m0, n0);
+            // Row form: where this tile's positions start. With image-aligned tiles (rc_tpi > 0,
+            // see TsParams) a tile never crosses into the next image.
+            const int OHW = p.g.OH * tp.rc_wv;
+            int tile_img = -1, pos0 = 0;
+            if (tp.a_kind == A_ROWCONV) pos0 = rowconv_pos0(tp, m0 / kBM, OHW, tile_img);
+            // Staged stores: warp 0 describes the tile's runs (the divisions happen here, once per
+            // tile, and before the wait for the accumulator, which hides them); the table is
+            // published by the barrier of the vote below.
+            StageTile* stt = &st_tab[tile_par];
+            if constexpr (ES == 2) {
+                if (tp.d_staged && !tp.rc_tma && warp == 0) {
+                    if (tp.a_kind == A_ROWCONV) {
+                        // the tile's produced positions, in order, are consecutive output pixels
+                        // (a row's outputs end at OW, the next row's follow at once in memory)
+                        auto first_pixel = [&](int pos) -> unsigned {  // first output pixel at or after position pos
+                            if (pos >= p.M) return static_cast<unsigned>(p.M / OHW) * static_cast<unsigned>(p.g.P);
+                            const int im = pos / OHW;
+                            const int rm = pos - im * OHW;
+                            const int r_oh = rm / tp.rc_wv;
+                            const int r_u = rm - r_oh * tp.rc_wv;
+                            return static_cast<unsigned>(im) * static_cast<unsigned>(p.g.P) +
+                                   static_cast<unsigned>((r_oh + (r_u < p.g.OW ? 0 : 1)) * p.g.OW + (r_u < p.g.OW ? r_u : 0));
+                        };
+                        const unsigned q0 = first_pixel(pos0);
+                        const int nslots = static_cast<int>(first_pixel(pos0 + 4 * tp.rc_T) - q0);
+                        stage_tile_fill(stt, lane, q0, nslots, static_cast<unsigned>(p.g.P),
+                                        static_cast<long long>(b) * p.d_batch_stride, p.g.out_img_stride, p.g.P);
+                    } else if (tp.a_kind == A_IM2COL) {
+                        stage_tile_fill(stt, lane, static_cast<unsigned>(m0), min(kBM, p.M - m0), static_cast<unsigned>(p.g.P),
+                                        static_cast<long long>(b) * p.d_batch_stride, p.g.out_img_stride, p.g.P);
+                    } else {
+                        stage_tile_fill(stt, lane, static_cast<unsigned>(m0), min(kBM, p.M - m0), 0u,
+                                        p.d_offs ? p.d_offs[b] : static_cast<long long>(b) * p.d_batch_stride, 0, p.ldd);
+                    }
+                }
+            }
             // all K-chunks but the last only feed the running sums
             for (int kb0 = 0; kb0 + kc < num_kb; kb0 += kc) {
                 const bool wc = ptx::mbar_wait_bounded(ptx::smem_u32(&tfull_bar[buf]), tphase, abort_p);
@@ -380,11 +435,9 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                     // is processed. Every warp gets here (its wait is bounded), votes, and all
                     // leave together if any wait gave up.
                     const bool warp_ok = __all_sync(0xffffffffu, w);
-                    if (lane == 0) epi_ok[warp] = warp_ok ? 1 : 0;
+                    if (lane == 0) epi_ok[tile_par][warp] = warp_ok ? 1 : 0;
                     epilogue_bar();
-                    const bool all_ok = epi_ok[0] && epi_ok[1] && epi_ok[2] && epi_ok[3];
-                    epilogue_bar();  // the words may be rewritten for the next tile only after all have read them
-                    if (!all_ok) break;
+                    if (!(epi_ok[tile_par][0] && epi_ok[tile_par][1] && epi_ok[tile_par][2] && epi_ok[tile_par][3])) break;
                 } else if (!__all_sync(0xffffffffu, w)) {
                     break;
                 }
@@ -393,15 +446,15 @@ __global__ void __launch_bounds__(kTsThreads, 1)
             }
             ptx::tc_fence_after();
             if (tp.a_kind == A_ROWCONV) {
-                const int tm = m0 / kBM, tn = n0 / BN;
-                const int pos = (tm * 4 + warp) * tp.rc_T - tp.rc_lo + lane;
-                const int OHW = p.g.OH * tp.rc_wv;
+                const int tn = n0 / BN;
+                const int pos = pos0 + warp * tp.rc_T - tp.rc_lo + lane;
                 const bool pos_ok = pos >= 0 && pos < p.M;
                 const int img = pos_ok ? pos / OHW : 0;
                 const int rem = pos_ok ? pos - img * OHW : 0;
                 const int oh = rem / tp.rc_wv;
                 const int u = rem - oh * tp.rc_wv;
-                const bool produce = pos_ok && lane >= tp.rc_lo && lane < tp.rc_lo + tp.rc_T && u < p.g.OW;
+                const bool produce = pos_ok && lane >= tp.rc_lo && lane < tp.rc_lo + tp.rc_T && u < p.g.OW &&
+                                     (tile_img < 0 || img == tile_img);
                 const int c0 = tn * tp.rc_cpt;
                 const long long obase = static_cast<long long>(img) * p.g.out_img_stride +
                                         static_cast<long long>(b) * p.d_batch_stride +
@@ -410,41 +463,24 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                 const int nco = min(tp.rc_cpt, p.N - c0);
                 const char* bias_g =
                     p.bias ? p.bias + (static_cast<long long>(b) * p.bias_stride + c0) * ES : nullptr;
-                // staged stores: the tile's produced positions, in order, are consecutive output
-                // pixels (a row's outputs end at OW, the next row's follow at once in memory)
-                StageGeom sg;
-                StageRun srun;
-                int slot = 0;
-                bool staged = false;
+                // how this tile's results leave: 0 one element per lane, 1 staged 16-byte stores,
+                // 2 TMA stores of whole blocks (image-aligned tiles)
+                int mode = 0;
+                StageSlot ss{0, 0, 0};
+                uint32_t sbuf = 0;
                 if constexpr (ES == 2) {
-                    if (tp.d_staged) {
-                        auto first_pixel = [&](long long pos) -> long long {  // first output pixel at or after position pos
-                            if (pos >= p.M) return static_cast<long long>(p.M / OHW) * p.g.P;
-                            const long long im = pos / OHW;
-                            const int rm = static_cast<int>(pos - im * OHW);
-                            const int r_oh = rm / tp.rc_wv;
-                            const int r_u = rm - r_oh * tp.rc_wv;
-                            return im * p.g.P + static_cast<long long>(r_oh + (r_u < p.g.OW ? 0 : 1)) * p.g.OW +
-                                   (r_u < p.g.OW ? r_u : 0);
-                        };
-                        const long long pos0 = static_cast<long long>(tm) * 4 * tp.rc_T;
-                        sg.q0 = first_pixel(pos0);
-                        sg.nslots = static_cast<int>(first_pixel(pos0 + 4 * tp.rc_T) - sg.q0);
-                        sg.base = static_cast<long long>(b) * p.d_batch_stride;
-                        sg.ois = p.g.out_img_stride;
-                        sg.colstride = p.g.P;
-                        sg.P = p.g.P;
-                        if (sg.nslots > 0) {
-                            stage_geom_finish(sg);
-                            staged = sg.runs <= kStageMaxRuns;
-                        }
-                        if (staged && produce) {
-                            slot = static_cast<int>(static_cast<long long>(img) * p.g.P + static_cast<long long>(oh) * p.g.OW + u - sg.q0);
-                            srun = stage_run(sg, img - sg.img0);
-                        }
+                    if (tp.rc_tma) {
+                        mode = 2;
+                        sbuf = stage_base + stage_buf * static_cast<uint32_t>(tp.rc_tma_buf);
+                        ss.idx0 = warp * tp.rc_T + (lane - tp.rc_lo);  // position inside the tile
+                    } else if (tp.d_staged && stt->runs > 0) {
+                        mode = 1;
+                        sbuf = stage_base + stage_buf * kStageBufBytes;
+                        if (produce)
+                            ss = stage_slot(stt, static_cast<int>(static_cast<unsigned>(img) * static_cast<unsigned>(p.g.P) +
+                                                                  static_cast<unsigned>(oh * p.g.OW + u) - stt->q0), p.d);
                     }
                 }
-                const long long d_elem0 = static_cast<long long>(reinterpret_cast<uintptr_t>(p.d) >> 1);
                 for (int co0 = 0; co0 < ((p.ablate & 8) ? 0 : nco); co0 += 16) {
                     // bias first (one value per lane, broadcast later): keeps loads out of the
                     // store loop, where they would serialise behind each store
@@ -492,15 +528,25 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                         for (int e = 0; e < 16; ++e) acc[e] = fmaxf(acc[e], 0.0f);
                     }
                     if constexpr (ES == 2) {
-                        if (staged) {
-                            const uint32_t sbuf = ptx::smem_u32(smem_raw) + static_cast<uint32_t>(tp.stage_off) + stage_buf * kStageBufBytes;
+                        if (mode == 2) {
+                            // block [channel][position of the tile]: one TMA store per 16 channels below
+                            if (produce) {
+                                const uint32_t sa = sbuf + static_cast<uint32_t>(co0 * 4 * tp.rc_T + ss.idx0) * 2u;
+#pragma unroll
+                                for (int e = 0; e < 16; ++e) {
+                                    const unsigned short h = p.fmt == FMT_F16 ? to_bits16<OUT_F16>(acc[e]) : to_bits16<OUT_BF16>(acc[e]);
+                                    asm volatile("st.shared.u16 [%0], %1;" ::"r"(sa + static_cast<uint32_t>(e * 4 * tp.rc_T) * 2u), "h"(h) : "memory");
+                                }
+                            }
+                            continue;
+                        }
+                        if (mode == 1) {
                             if (produce) {
 #pragma unroll
                                 for (int e = 0; e < 16; ++e) {
                                     if (co0 + e < nco) {
-                                        const int idx = stage_index(srun, slot, d_elem0, sg.colstride, c0 + co0 + e);
-                                        const unsigned short h = p.fmt == FMT_F16 ? to_bits16<OUT_F16>(acc[e])
-                                                                                  : to_bits16<OUT_BF16>(acc[e]);
+                                        const int idx = ss.idx0 + ((ss.a7 + (c0 + co0 + e) * ss.cs7) & 7);
+                                        const unsigned short h = p.fmt == FMT_F16 ? to_bits16<OUT_F16>(acc[e]) : to_bits16<OUT_BF16>(acc[e]);
                                         asm volatile("st.shared.u16 [%0], %1;" ::"r"(sbuf + static_cast<uint32_t>(e * kStageRowStride + idx) * 2u), "h"(h) : "memory");
                                     }
                                 }
@@ -510,8 +556,9 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                                 ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));
                             }
                             epilogue_bar();
-                            staged_writeout(sg, sbuf, p.d, c0 + co0, min(16, nco - co0), threadIdx.x);
+                            staged_writeout(stt, sbuf, p.d, c0 + co0, min(16, nco - co0), threadIdx.x);
                             stage_buf ^= 1u;
+                            sbuf = stage_base + stage_buf * kStageBufBytes;
                             continue;
                         }
                     }
@@ -537,9 +584,28 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                         }
                     }
                 }
-                if (!staged || (p.ablate & 8)) {  // (the staged path released the accumulator after its last read)
+                if (mode != 1 || (p.ablate & 8)) {  // (mode 1 released the accumulator after its last read)
                     ptx::tc_fence_before();
                     ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));
+                }
+                if constexpr (ES == 2) {
+                    if (mode == 2) {
+                        // every staging thread makes its writes visible to the async proxy, then
+                        // one thread hands the block to the TMA unit, 16 channels per store; rows
+                        // beyond the image's last pixel are clipped by the hardware
+                        ptx::fence_proxy_async_smem();
+                        epilogue_bar();
+                        if (threadIdx.x == 0 && !(p.ablate & 8)) {
+                            const int x = pos0 - tile_img * OHW;
+                            for (int co0 = 0; co0 < nco; co0 += 16)
+                                ptx::tma_store_3d(&tmD, sbuf + static_cast<uint32_t>(co0 * 4 * tp.rc_T) * 2u, x,
+                                                  b * p.N + c0 + co0, tile_img);
+                            ptx::bulk_commit_group();
+                            // the block written two tiles ago is reused next: its store must have read it
+                            ptx::bulk_wait_group_read<1>();
+                        }
+                        stage_buf ^= 1u;
+                    }
                 }
                 if (++buf == static_cast<uint32_t>(nbuf)) {
                     buf = 0;
@@ -572,70 +638,58 @@ __global__ void __launch_bounds__(kTsThreads, 1)
             ex.rdelta = p.resid ? p.resid - p.d : 0;
             const float beta_e = p.resid ? 1.0f : beta;  // a residual takes the place of the beta term
             if constexpr (ES == 2) {
-                if (tp.d_staged && !(p.ablate & 32)) {
-                    StageGeom sg;
-                    sg.base = tp.a_kind == A_IM2COL ? static_cast<long long>(b) * p.d_batch_stride
-                                                    : (p.d_offs ? p.d_offs[b] : static_cast<long long>(b) * p.d_batch_stride);
-                    sg.q0 = m0;
-                    sg.nslots = min(kBM, p.M - m0);
-                    sg.ois = tp.a_kind == A_IM2COL ? p.g.out_img_stride : 0;
-                    sg.colstride = colstride;
-                    sg.P = tp.a_kind == A_IM2COL ? p.g.P : 0;
-                    stage_geom_finish(sg);
-                    if (sg.runs <= kStageMaxRuns) {
-                        const int slot = warp * 32 + lane;
-                        StageRun srun;
-                        if (row_ok) srun = stage_run(sg, sg.P ? i / sg.P - sg.img0 : 0);
-                        const long long d_elem0 = static_cast<long long>(reinterpret_cast<uintptr_t>(p.d) >> 1);
-                        for (int cc = 0; cc < ncols; cc += 32) {
-                            uint32_t v[32];
-                            ptx::tmem_ld_32x32(trow + cc, v);
-                            ptx::tmem_ld_wait();
-                            const int nc = min(32, ncols - cc);
-                            if (cc + 32 >= ncols) {  // last read of the accumulator
-                                ptx::tc_fence_before();
-                                ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));
-                            }
-                            float bv = 0.0f;
-                            if (bias != nullptr && lane < nc)
-                                bv = p.fmt == FMT_F16 ? out_load<OUT_F16>(bias + (cc + lane) * 2)
-                                                      : out_load<OUT_BF16>(bias + (cc + lane) * 2);
-                            if (p.resid != nullptr) {
-                                const char* rp = p.resid + (optr - p.d) + static_cast<long long>(cc) * colstride * 2;
-#pragma unroll
-                                for (int jj = 0; jj < 32; ++jj) {
-                                    float rv = 0.0f;
-                                    if (row_ok && jj < nc)
-                                        rv = p.fmt == FMT_F16 ? out_load<OUT_F16>(rp + jj * colstride * 2)
-                                                              : out_load<OUT_BF16>(rp + jj * colstride * 2);
-                                    v[jj] = __float_as_uint(alpha * __uint_as_float(v[jj]) + rv);
-                                }
-                            } else {
-#pragma unroll
-                                for (int jj = 0; jj < 32; ++jj) v[jj] = __float_as_uint(alpha * __uint_as_float(v[jj]));
-                            }
-                            const uint32_t sbuf = ptx::smem_u32(smem_raw) + static_cast<uint32_t>(tp.stage_off) + stage_buf * kStageBufBytes;
-                            const bool relu = p.relu != 0;
+                if (tp.d_staged && stt->runs > 0 && !(p.ablate & 32)) {
+                    StageSlot ss{0, 0, 0};
+                    if (row_ok) ss = stage_slot(stt, warp * 32 + lane, p.d);
+                    for (int cc = 0; cc < ncols; cc += 32) {
+                        uint32_t v[32];
+                        ptx::tmem_ld_32x32(trow + cc, v);
+                        ptx::tmem_ld_wait();
+                        const int nc = min(32, ncols - cc);
+                        if (cc + 32 >= ncols) {  // last read of the accumulator
+                            ptx::tc_fence_before();
+                            ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));
+                        }
+                        float bv = 0.0f;
+                        if (bias != nullptr && lane < nc)
+                            bv = p.fmt == FMT_F16 ? out_load<OUT_F16>(bias + (cc + lane) * 2)
+                                                  : out_load<OUT_BF16>(bias + (cc + lane) * 2);
+                        if (p.resid != nullptr) {
+                            const char* rp = p.resid + (optr - p.d) + static_cast<long long>(cc) * colstride * 2;
 #pragma unroll
                             for (int jj = 0; jj < 32; ++jj) {
-                                float r = __uint_as_float(v[jj]) + __shfl_sync(0xffffffffu, bv, jj);
-                                r = relu ? fmaxf(r, 0.0f) : r;
-                                if (row_ok && jj < nc) {
-                                    const int idx = stage_index(srun, slot, d_elem0, colstride, n0 + cc + jj);
-                                    const unsigned short h = p.fmt == FMT_F16 ? to_bits16<OUT_F16>(r) : to_bits16<OUT_BF16>(r);
-                                    asm volatile("st.shared.u16 [%0], %1;" ::"r"(sbuf + static_cast<uint32_t>(jj * kStageRowStride + idx) * 2u), "h"(h) : "memory");
-                                }
+                                float rv = 0.0f;
+                                if (row_ok && jj < nc)
+                                    rv = p.fmt == FMT_F16 ? out_load<OUT_F16>(rp + jj * colstride * 2)
+                                                          : out_load<OUT_BF16>(rp + jj * colstride * 2);
+                                v[jj] = __float_as_uint(alpha * __uint_as_float(v[jj]) + rv);
                             }
-                            epilogue_bar();
-                            staged_writeout(sg, sbuf, p.d, n0 + cc, nc, threadIdx.x);
-                            stage_buf ^= 1u;
+                        } else {
+#pragma unroll
+                            for (int jj = 0; jj < 32; ++jj) v[jj] = __float_as_uint(alpha * __uint_as_float(v[jj]));
                         }
-                        if (++buf == static_cast<uint32_t>(nbuf)) {
-                            buf = 0;
-                            tphase ^= 1u;
+                        const uint32_t sbuf = stage_base + stage_buf * kStageBufBytes;
+                        const bool relu = p.relu != 0;
+                        const int colsh0 = ss.a7 + (n0 + cc) * ss.cs7;
+#pragma unroll
+                        for (int jj = 0; jj < 32; ++jj) {
+                            float r = __uint_as_float(v[jj]) + __shfl_sync(0xffffffffu, bv, jj);
+                            r = relu ? fmaxf(r, 0.0f) : r;
+                            if (row_ok && jj < nc) {
+                                const int idx = ss.idx0 + ((colsh0 + jj * ss.cs7) & 7);
+                                const unsigned short h = p.fmt == FMT_F16 ? to_bits16<OUT_F16>(r) : to_bits16<OUT_BF16>(r);
+                                asm volatile("st.shared.u16 [%0], %1;" ::"r"(sbuf + static_cast<uint32_t>(jj * kStageRowStride + idx) * 2u), "h"(h) : "memory");
+                            }
                         }
-                        continue;
+                        epilogue_bar();
+                        staged_writeout(stt, sbuf, p.d, n0 + cc, nc, threadIdx.x);
+                        stage_buf ^= 1u;
                     }
+                    if (++buf == static_cast<uint32_t>(nbuf)) {
+                        buf = 0;
+                        tphase ^= 1u;
+                    }
+                    continue;
                 }
             }
             if (p.ablate & 32) {
@@ -658,6 +712,10 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                 tphase ^= 1u;
             }
         }
+        if constexpr (ES == 2) {
+            // TMA stores of the last blocks must have left shared memory before the CTA ends
+            if (tp.rc_tma && threadIdx.x == 0) ptx::bulk_wait_group<0>();
+        }
     } else if (warp >= kTsProducerWarp0 && warp < kTsLoaderWarp0) {
         // ------------------------------------------------------------ A producers (-> TMEM)
         const int q = warp & 3;                          // TMEM lane quadrant this warp may access
@@ -675,9 +733,10 @@ __global__ void __launch_bounds__(kTsThreads, 1)
             long long pbase = 0;
             int ih0 = -(1 << 30), iw0 = -(1 << 30);
             if (tp.a_kind == A_ROWCONV) {
-                const int pos = ((m0 / kBM) * 4 + q) * tp.rc_T - tp.rc_lo + lane;
+                const int OHW = p.g.OH * tp.rc_wv;
+                int tile_img;
+                const int pos = rowconv_pos0(tp, m0 / kBM, OHW, tile_img) + q * tp.rc_T - tp.rc_lo + lane;
                 if (pos >= 0 && pos < p.M) {
-                    const int OHW = p.g.OH * tp.rc_wv;
                     const int img = pos / OHW;
                     const int rem = pos - img * OHW;
                     const int oh = rem / tp.rc_wv;

@@ -212,82 +212,106 @@ constexpr int kStageBufBytes = kStageCols * kStageRowStride * 2;
 constexpr int kStageBytes = 2 * kStageBufBytes;  // two blocks: one is written while the other drains
 constexpr int kStageMaxRuns = 4;
 
-struct StageGeom {        // uniform over the tile
-    long long base;       // element offset of (image 0, column 0, pixel 0) for this batch entry
-    long long q0;         // pixel index of slot 0
-    long long ois;        // elements between images
-    long long colstride;  // elements between columns
-    int nslots;
-    int P;                // pixels per image; 0: no images (one run)
-    int img0, runs;       // image of slot 0, number of runs
-};
-
 struct StageRun {
     int s, len, rb;       // first slot, slots, shared-memory index base (multiple of 8)
+    int pad;
     long long gelem;      // element offset in D of the run's first element, column 0
 };
 
-__device__ __forceinline__ void stage_geom_finish(StageGeom& g) {
-    g.img0 = g.P ? static_cast<int>(g.q0 / g.P) : 0;
-    g.runs = g.P ? static_cast<int>((g.q0 + g.nslots - 1) / g.P) - g.img0 + 1 : 1;
-}
+// Per-tile description of the runs, filled by the first lanes of epilogue warp 0 and read by all
+// 128 epilogue threads after a barrier (two copies, alternating between consecutive tiles, so a
+// warp that runs ahead never overwrites what a slower one still reads). All index arithmetic that
+// needs a division happens once per tile, in those lanes.
+struct StageTile {
+    int runs;             // 0: this tile does not use staged stores (more than kStageMaxRuns images)
+    int nslots;
+    unsigned q0, pad;     // pixel index of slot 0
+    long long colstride;  // elements between columns of D
+    StageRun run[kStageMaxRuns];
+};
 
-__device__ __forceinline__ StageRun stage_run(const StageGeom& g, int r) {
-    StageRun run;
-    const long long img = g.img0 + r;
-    run.s = r == 0 ? 0 : static_cast<int>(img * g.P - g.q0);
-    const int e = g.P ? min(g.nslots, static_cast<int>((img + 1) * g.P - g.q0)) : g.nslots;
-    run.len = e - run.s;
-    run.rb = ((run.s + 7) & ~7) + 16 * r;
-    run.gelem = g.base + img * g.ois + (g.q0 + run.s - img * g.P);
-    return run;
+// q0 = pixel index of slot 0; P = pixels per image (0: one run); base = element offset of
+// (image 0, column 0, pixel 0) of this batch entry; ois = elements between images.
+__device__ __forceinline__ void stage_tile_fill(StageTile* st, int lane, unsigned q0, int nslots, unsigned P,
+                                                long long base, long long ois, long long colstride) {
+    const unsigned img0 = P ? q0 / P : 0u;
+    const int runs = nslots <= 0 ? 0 : (P ? static_cast<int>((q0 + nslots - 1) / P - img0) + 1 : 1);
+    if (lane == 0) {
+        st->runs = runs <= kStageMaxRuns ? runs : 0;
+        st->nslots = nslots;
+        st->q0 = q0;
+        st->pad = 0;
+        st->colstride = colstride;
+    }
+    if (lane < runs && lane < kStageMaxRuns) {
+        const long long img = static_cast<long long>(img0) + lane;
+        StageRun run;
+        run.s = lane == 0 ? 0 : static_cast<int>(img * P - q0);
+        const int e = P ? min(nslots, static_cast<int>((img + 1) * P - q0)) : nslots;
+        run.len = e - run.s;
+        run.rb = ((run.s + 7) & ~7) + 16 * lane;
+        run.pad = 0;
+        run.gelem = base + img * ois + (static_cast<long long>(q0) + run.s - img * P);
+        st->run[lane] = run;
+    }
 }
 
 // The four epilogue warps (threads 0-127 of the CTA) meet here; barrier 0 belongs to __syncthreads.
 __device__ __forceinline__ void epilogue_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
-// Shared-memory index of (slot, column) for the staging thread; `run` is the slot's own run and
-// d_elem0 = (address of D) / 2.
-__device__ __forceinline__ int stage_index(const StageRun& run, int slot, long long d_elem0, long long colstride,
-                                           long long col) {
-    const int sh = static_cast<int>((d_elem0 + run.gelem + col * colstride) & 7);
-    return run.rb + sh + (slot - run.s);
+// What a staging thread needs for its own slot: the index of its element in column `col` is
+//     idx0 + ((a7 + col * cs7) & 7)
+// (run base + position inside the run + that column's alignment shift).
+struct StageSlot {
+    int idx0, a7, cs7;
+};
+__device__ __forceinline__ StageSlot stage_slot(const StageTile* st, int slot, const char* d) {
+    int r = 0;
+    for (int k = 1; k < st->runs; ++k) r += slot >= st->run[k].s ? 1 : 0;
+    const StageRun run = st->run[r];
+    StageSlot o;
+    o.idx0 = run.rb + (slot - run.s);
+    o.a7 = static_cast<int>((static_cast<long long>(reinterpret_cast<uintptr_t>(d) >> 1) + run.gelem) & 7);
+    o.cs7 = static_cast<int>(st->colstride & 7);
+    return o;
 }
 
 // Writes the staged block (columns col0 .. col0+ncols-1 of D) to global memory. tid = 0..127.
-// Half-warps take (column, run) items; lane l of a half-warp takes 16-byte chunks l, l+16 of the
-// item. Chunks that lie wholly inside the run leave as one 16-byte store, the ragged first and
-// last chunk element by element.
-__device__ __forceinline__ void staged_writeout(const StageGeom& g, uint32_t sbuf, char* d, long long col0, int ncols,
+// A half-warp takes a column (and every run of it); lane l of the half-warp takes 16-byte chunks
+// l, l+16 of a run. Chunks that lie wholly inside the run leave as one 16-byte store, the ragged
+// first and last chunk element by element.
+__device__ __forceinline__ void staged_writeout(const StageTile* st, uint32_t sbuf, char* d, long long col0, int ncols,
                                                 int tid) {
     const long long d_elem0 = static_cast<long long>(reinterpret_cast<uintptr_t>(d) >> 1);
     const int l16 = tid & 15;
-    const int items = ncols * g.runs;
-    for (int it = tid >> 4; it < items; it += 8) {
-        const int jj = it / g.runs;
-        const int r = it - jj * g.runs;
-        const StageRun run = stage_run(g, r);
-        const long long gfirst = run.gelem + (col0 + jj) * g.colstride;  // element offset of the run's first element
-        const int sh = static_cast<int>((d_elem0 + gfirst) & 7);
-        const int nchunks = (sh + run.len + 7) >> 3;
-        const uint32_t scol = sbuf + static_cast<uint32_t>(jj * kStageRowStride + run.rb) * 2u;
-        char* gcol = d + (gfirst - sh) * 2;  // 16-byte aligned
-        for (int c = l16; c < nchunks; c += 16) {
-            const int lo = max(0, sh - 8 * c);
-            const int hi = min(8, sh + run.len - 8 * c);
-            const uint32_t sa = scol + static_cast<uint32_t>(c) * 16u;
-            if (lo == 0 && hi == 8) {
-                uint4 v;
-                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                             : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                             : "r"(sa)
-                             : "memory");
-                *reinterpret_cast<uint4*>(gcol + c * 16) = v;
-            } else {
-                for (int t = lo; t < hi; ++t) {
-                    unsigned short h;
-                    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(h) : "r"(sa + t * 2u) : "memory");
-                    *reinterpret_cast<unsigned short*>(gcol + c * 16 + t * 2) = h;
+    const int runs = st->runs;
+    const long long cs = st->colstride;
+    for (int jj = tid >> 4; jj < ncols; jj += 8) {
+        const long long coff = (col0 + jj) * cs;
+        for (int r = 0; r < runs; ++r) {
+            const StageRun run = st->run[r];
+            const long long gfirst = run.gelem + coff;  // element offset of the run's first element
+            const int sh = static_cast<int>((d_elem0 + gfirst) & 7);
+            const int last = sh + run.len;              // one past the run's last element, chunk-relative
+            const uint32_t scol = sbuf + static_cast<uint32_t>(jj * kStageRowStride + run.rb) * 2u;
+            char* gcol = d + (gfirst - sh) * 2;  // 16-byte aligned
+            for (int c = l16; 8 * c < last; c += 16) {
+                const uint32_t sa = scol + static_cast<uint32_t>(c) * 16u;
+                if (8 * c >= sh && 8 * c + 8 <= last) {
+                    uint4 v;
+                    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                                 : "r"(sa)
+                                 : "memory");
+                    *reinterpret_cast<uint4*>(gcol + c * 16) = v;
+                } else {
+                    const int lo = max(0, sh - 8 * c);
+                    const int hi = min(8, last - 8 * c);
+                    for (int t = lo; t < hi; ++t) {
+                        unsigned short h;
+                        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(h) : "r"(sa + t * 2u) : "memory");
+                        *reinterpret_cast<unsigned short*>(gcol + c * 16 + t * 2) = h;
+                    }
                 }
             }
         }

@@ -234,3 +234,125 @@ def gemmBatched(layout, a_transpose, b_transpose, m, n, k, alphas, a_buffer, a_o
         event.end.record(s)
     del al_keep, be_keep
     _check(rc)
+
+
+# ---------------------------------------------------------------------------------------------
+# level-3 routines on the GEMM main loop (gblas.h:506-586)
+# ---------------------------------------------------------------------------------------------
+class Triangle(enum.IntEnum):
+    Upper = 121
+    Lower = 122
+
+
+class Diagonal(enum.IntEnum):
+    NonUnit = 131
+    Unit = 132
+
+
+class Side(enum.IntEnum):
+    Left = 141
+    Right = 142
+
+
+_SYMM, _SYRK, _TRMM, _TRSM = 1, 2, 3, 4
+
+
+def _level3_workspace(routine, buf, m, n, stream):
+    need = lib().dlf_b200_level3_workspace_bytes(routine, int(precision_of(buf)), m, n)
+    ws = torch.empty(max(int(need), 8), dtype=torch.uint8, device=buf.device)
+    ws.record_stream(stream)  # read by work queued on `stream`, which may not be the allocator's
+    return ws
+
+
+def symm(layout, side, triangle, m, n, alpha, a_buffer, a_offset, a_ld, b_buffer, b_offset, b_ld, beta,
+         c_buffer, c_offset, c_ld, queue=None, event=None):
+    """C = alpha*S*B + beta*C (Left) or alpha*B*S + beta*C (Right), S symmetric, one triangle
+    stored (gpgpu::blas::symm, gblas.h:506-515)."""
+    prec = precision_of(c_buffer)
+    if a_buffer.dtype != c_buffer.dtype or b_buffer.dtype != c_buffer.dtype:
+        raise BLASError(StatusCode.kInvalidValue)
+    if m == 0 or n == 0:
+        raise BLASError(StatusCode.kInvalidDimension)
+    ka = m if int(side) == Side.Left else n
+    row = int(layout) == Layout.RowMajor
+    _test_matrix(ka, ka, a_buffer, a_offset, a_ld, StatusCode.kInvalidLeadDimA, StatusCode.kInsufficientMemoryA)
+    one, two = (n, m) if row else (m, n)
+    _test_matrix(one, two, b_buffer, b_offset, b_ld, StatusCode.kInvalidLeadDimB, StatusCode.kInsufficientMemoryB)
+    _test_matrix(one, two, c_buffer, c_offset, c_ld, StatusCode.kInvalidLeadDimC, StatusCode.kInsufficientMemoryC)
+    al, be = _scalar(alpha, c_buffer.dtype), _scalar(beta, c_buffer.dtype)
+    s, sp = _stream(queue)
+    ws = _level3_workspace(_SYMM, c_buffer, m, n, s)
+    if event is not None:
+        event.start.record(s)
+    rc = lib().dlf_b200_symm(int(prec), int(layout), int(side), int(triangle), m, n, ctypes.byref(al),
+                             _ptr(a_buffer, a_offset), a_ld, _ptr(b_buffer, b_offset), b_ld, ctypes.byref(be),
+                             _ptr(c_buffer, c_offset), c_ld, ctypes.c_void_p(ws.data_ptr()), ws.numel(), sp)
+    if event is not None:
+        event.end.record(s)
+    _check(rc)
+
+
+def syrk(layout, triangle, a_transpose, n, k, alpha, a_buffer, a_offset, a_ld, beta, c_buffer, c_offset, c_ld,
+         queue=None, event=None):
+    """The named triangle of C = alpha*op(A)*op(A)^T + beta*C (gpgpu::blas::syrk, gblas.h:528-536)."""
+    prec = precision_of(c_buffer)
+    if a_buffer.dtype != c_buffer.dtype:
+        raise BLASError(StatusCode.kInvalidValue)
+    if n == 0 or k == 0:
+        raise BLASError(StatusCode.kInvalidDimension)
+    row = int(layout) == Layout.RowMajor
+    a_rot = (row and int(a_transpose) == Transpose.NoTrans) or (not row and int(a_transpose) != Transpose.NoTrans)
+    one, two = (k, n) if a_rot else (n, k)
+    _test_matrix(one, two, a_buffer, a_offset, a_ld, StatusCode.kInvalidLeadDimA, StatusCode.kInsufficientMemoryA)
+    _test_matrix(n, n, c_buffer, c_offset, c_ld, StatusCode.kInvalidLeadDimC, StatusCode.kInsufficientMemoryC)
+    al, be = _scalar(alpha, c_buffer.dtype), _scalar(beta, c_buffer.dtype)
+    s, sp = _stream(queue)
+    ws = _level3_workspace(_SYRK, c_buffer, n, n, s)
+    if event is not None:
+        event.start.record(s)
+    rc = lib().dlf_b200_syrk(int(prec), int(layout), int(triangle), int(a_transpose), n, k, ctypes.byref(al),
+                             _ptr(a_buffer, a_offset), a_ld, ctypes.byref(be), _ptr(c_buffer, c_offset), c_ld,
+                             ctypes.c_void_p(ws.data_ptr()), ws.numel(), sp)
+    if event is not None:
+        event.end.record(s)
+    _check(rc)
+
+
+def _triangular(fn_name, routine, layout, side, triangle, a_transpose, diagonal, m, n, alpha, a_buffer, a_offset,
+                a_ld, b_buffer, b_offset, b_ld, queue, event):
+    prec = precision_of(b_buffer)
+    if a_buffer.dtype != b_buffer.dtype:
+        raise BLASError(StatusCode.kInvalidValue)
+    if m == 0 or n == 0:
+        raise BLASError(StatusCode.kInvalidDimension)
+    ka = m if int(side) == Side.Left else n
+    row = int(layout) == Layout.RowMajor
+    _test_matrix(ka, ka, a_buffer, a_offset, a_ld, StatusCode.kInvalidLeadDimA, StatusCode.kInsufficientMemoryA)
+    one, two = (n, m) if row else (m, n)
+    _test_matrix(one, two, b_buffer, b_offset, b_ld, StatusCode.kInvalidLeadDimB, StatusCode.kInsufficientMemoryB)
+    al = _scalar(alpha, b_buffer.dtype)
+    s, sp = _stream(queue)
+    ws = _level3_workspace(routine, b_buffer, m, n, s)
+    if event is not None:
+        event.start.record(s)
+    rc = getattr(lib(), fn_name)(int(prec), int(layout), int(side), int(triangle), int(a_transpose), int(diagonal),
+                                 m, n, ctypes.byref(al), _ptr(a_buffer, a_offset), a_ld, _ptr(b_buffer, b_offset),
+                                 b_ld, ctypes.c_void_p(ws.data_ptr()), ws.numel(), sp)
+    if event is not None:
+        event.end.record(s)
+    _check(rc)
+
+
+def trmm(layout, side, triangle, a_transpose, diagonal, m, n, alpha, a_buffer, a_offset, a_ld, b_buffer, b_offset,
+         b_ld, queue=None, event=None):
+    """B = alpha*op(T)*B (Left) or alpha*B*op(T) (Right), in place (gpgpu::blas::trmm, gblas.h:570-577)."""
+    _triangular("dlf_b200_trmm", _TRMM, layout, side, triangle, a_transpose, diagonal, m, n, alpha, a_buffer,
+                a_offset, a_ld, b_buffer, b_offset, b_ld, queue, event)
+
+
+def trsm(layout, side, triangle, a_transpose, diagonal, m, n, alpha, a_buffer, a_offset, a_ld, b_buffer, b_offset,
+         b_ld, queue=None, event=None):
+    """Solves op(T)*X = alpha*B (Left) or X*op(T) = alpha*B (Right); X overwrites B
+    (gpgpu::blas::trsm, gblas.h:579-586)."""
+    _triangular("dlf_b200_trsm", _TRSM, layout, side, triangle, a_transpose, diagonal, m, n, alpha, a_buffer,
+                a_offset, a_ld, b_buffer, b_offset, b_ld, queue, event)

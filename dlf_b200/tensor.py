@@ -259,6 +259,55 @@ def dot(A, B, backend=None):
     return out.reshape(a_shape[:-1] + b_shape[:-2] + b_shape[-1:])
 
 
+def symm(side, uplo, A, B, alpha=1, beta=0, C=None, backend=None):
+    """dlf::symm (linalg.h:132-163): C = alpha*S*B + beta*C (Left) or alpha*B*S + beta*C (Right) for
+    2-D tensors; S is the symmetric matrix whose `uplo` triangle is the leading block of A."""
+    be = backend or _gblas
+    if A.dim() != 2 or B.dim() != 2:
+        raise ShapeError("symm: matrices expected")
+    m, n = B.shape
+    k = m if int(side) == _gblas.Side.Left else n
+    if A.shape[0] < k or A.shape[1] < k:
+        raise ShapeError("symm: matrix A has too few dimensions")
+    if not (A.stride(1) == 1 and B.is_contiguous()):
+        raise ShapeError("symm: operands must be row-major")
+    if C is None:
+        if beta != 0:
+            raise ShapeError("symm: beta != 0 needs an output tensor")
+        C = torch.empty((m, n), dtype=A.dtype, device=A.device)
+    elif tuple(C.shape) != (m, n) or not C.is_contiguous():
+        raise ShapeError("symm: bad output tensor")
+    be.symm(Layout.RowMajor, side, uplo, m, n, alpha, _flat(A), A.storage_offset(), A.stride(0), _flat(B),
+            B.storage_offset(), B.stride(0), beta, _flat(C), C.storage_offset(), C.stride(0))
+    return C
+
+
+def _triangular(name, side, uplo, transA, diag, A, B, alpha, backend):
+    be = backend or _gblas
+    if A.dim() != 2 or B.dim() != 2:
+        raise ShapeError(name + ": matrices expected")
+    m, n = B.shape
+    k = m if int(side) == _gblas.Side.Left else n
+    if A.shape[0] < k or A.shape[1] < k:
+        raise ShapeError(name + ": matrix A has too few dimensions")
+    if A.stride(1) != 1:
+        raise ShapeError(name + ": A must be row-major")
+    C = B.contiguous().clone()  # the reference copies B into the result and works in place (linalg.h:252-258)
+    getattr(be, name)(Layout.RowMajor, side, uplo, transA, diag, m, n, alpha, _flat(A), A.storage_offset(),
+                      A.stride(0), _flat(C), C.storage_offset(), C.stride(0))
+    return C
+
+
+def trmm(side, uplo, transA, diag, A, B, alpha=1, backend=None):
+    """dlf::trmm (linalg.h:240-276): alpha*op(T)*B (Left) or alpha*B*op(T) (Right) as a new tensor."""
+    return _triangular("trmm", side, uplo, transA, diag, A, B, alpha, backend)
+
+
+def trsm(side, uplo, transA, diag, A, B, alpha=1, backend=None):
+    """dlf::trsm (linalg.h:278-314): the solution X of op(T)*X = alpha*B (Left) or X*op(T) = alpha*B."""
+    return _triangular("trsm", side, uplo, transA, diag, A, B, alpha, backend)
+
+
 def _matrix_chain_order(dims):
     """detail::matrix_chain_order (linalg_detail.h:1701-1720): split table of the cheapest
     parenthesisation of a chain whose i-th matrix is dims[i] x dims[i+1]."""

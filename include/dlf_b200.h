@@ -33,6 +33,12 @@ enum {
     DLF_B200_NO_TRANS = 111,
     DLF_B200_TRANS = 112,
     DLF_B200_CONJ_TRANS = 113,
+    DLF_B200_UPPER = 121,     /* Triangle, Diagonal, Side: gpgpu/include/gblas.h:112-114 */
+    DLF_B200_LOWER = 122,
+    DLF_B200_NON_UNIT = 131,
+    DLF_B200_UNIT = 132,
+    DLF_B200_LEFT = 141,
+    DLF_B200_RIGHT = 142,
     DLF_B200_HALF = 16,
     DLF_B200_SINGLE = 32,
     DLF_B200_BFLOAT16 = 1600
@@ -128,6 +134,36 @@ size_t dlf_b200_conv2d_workspace_bytes(int dtype, size_t batches, size_t channel
                                        size_t width, size_t output_h, size_t output_w,
                                        size_t num_kernels, size_t group, size_t kernel_h,
                                        size_t kernel_w);
+
+/* Level-3 routines that run on the GEMM main loop. Each replaces the gpgpu::blas template of the
+ * same name (gpgpu/include/gblas.h:506-586; instantiations gpgpu/src/gblas.cpp; the OpenCL
+ * routines expand the symmetric / triangular operand into a general square and call Xgemm, which
+ * is the scheme used here too) with the semantics of the CPU path
+ * (dlf/include/tensor/linalg_detail.h:362-560, 720-1334):
+ *   symm  C = alpha*S*B + beta*C (Left, S is m x m) or alpha*B*S + beta*C (Right, S is n x n);
+ *         only the named triangle of A is read;
+ *   syrk  the named triangle of C = alpha*op(A)*op(A)^T + beta*C, op(A) is n x k; the other
+ *         triangle of C is left untouched;
+ *   trmm  B = alpha*op(T)*B (Left) or alpha*B*op(T) (Right), T triangular in the named triangle
+ *         of A, with an implicit unit diagonal when diagonal == DLF_B200_UNIT;
+ *   trsm  solves op(T)*X = alpha*B (Left) or X*op(T) = alpha*B (Right); X overwrites B.
+ * `workspace` is caller-owned device scratch of at least dlf_b200_level3_workspace_bytes(...)
+ * bytes (the reference takes its temporaries from the context's pool); trsm needs none.
+ * Argument errors return the StatusCode of the matching gblas routine. */
+enum { DLF_B200_SYMM = 1, DLF_B200_SYRK = 2, DLF_B200_TRMM = 3, DLF_B200_TRSM = 4 };
+size_t dlf_b200_level3_workspace_bytes(int routine, int dtype, size_t m, size_t n);
+int dlf_b200_symm(int dtype, int layout, int side, int triangle, size_t m, size_t n, const void* alpha,
+                  const void* a, size_t a_ld, const void* b, size_t b_ld, const void* beta, void* c,
+                  size_t c_ld, void* workspace, size_t workspace_bytes, void* stream);
+int dlf_b200_syrk(int dtype, int layout, int triangle, int a_transpose, size_t n, size_t k,
+                  const void* alpha, const void* a, size_t a_ld, const void* beta, void* c, size_t c_ld,
+                  void* workspace, size_t workspace_bytes, void* stream);
+int dlf_b200_trmm(int dtype, int layout, int side, int triangle, int a_transpose, int diagonal, size_t m,
+                  size_t n, const void* alpha, const void* a, size_t a_ld, void* b, size_t b_ld,
+                  void* workspace, size_t workspace_bytes, void* stream);
+int dlf_b200_trsm(int dtype, int layout, int side, int triangle, int a_transpose, int diagonal, size_t m,
+                  size_t n, const void* alpha, const void* a, size_t a_ld, void* b, size_t b_ld,
+                  void* workspace, size_t workspace_bytes, void* stream);
 
 /* NCHW pooling, the second "next" step around the convolution path (a ResNet forward is
  * conv -> maxpool -> ... -> global average pool -> FC). Replace gpgpu::dnn::maxpool / avgpool

@@ -8,7 +8,7 @@
 //   * blas::gemm / blas::gemmBatched / blas::gemmStridedBatched and dnn::conv2d with the
 //     reference's exact signatures (gpgpu/include/gblas.h:496-504, 661-683; gdnn.h:201-213).
 // Inside dlf itself the same four function bodies go where the CUBLAS(...) lambdas and cudnnConv
-// sit today; only the two `unwrap` helpers change (INTEGRATION.md shows the lines).
+// sit today; only the two `unwrap` helpers change.
 //
 // Error behaviour follows the reference: argument errors throw BLASError carrying the StatusCode
 // (gpgpu/src/utilities/exceptions.hpp:24-35), CUDA failures throw APIError (gpgpu.h:21-121).
@@ -200,6 +200,9 @@ enum class StatusCode {
 };
 enum class Layout { RowMajor = 101, ColMajor = 102 };
 enum class Transpose { NoTrans = 111, Trans = 112, ConjTrans = 113 };
+enum class Triangle { Upper = 121, Lower = 122 };
+enum class Diagonal { NonUnit = 131, Unit = 132 };
+enum class Side { Left = 141, Right = 142 };
 
 class BLASError : public std::runtime_error {
 public:
@@ -329,6 +332,99 @@ void gemmBatched(const Layout layout, const Transpose a_transpose, const Transpo
                       b_buffer.unwrap(), b_offsets, b_ld, betas, c_buffer.unwrap(), c_offsets, c_ld, batch_count,
                       work.unwrap(), work.data_size(), queue.unwrap()),
                   "dlf_b200_gemm_batched");
+}
+
+// ---- level-3 routines on the GEMM main loop (gpgpu/include/gblas.h:506-586) ----
+
+// Symmetric matrix-matrix multiplication (gblas.h:506-515)
+template <typename T>
+void symm(const Layout layout, const Side side, const Triangle triangle,
+          const size_t m, const size_t n,
+          const T alpha,
+          const Buffer<T>& a_buffer, const size_t a_offset, const size_t a_ld,
+          const Buffer<T>& b_buffer, const size_t b_offset, const size_t b_ld,
+          const T beta,
+          Buffer<T>& c_buffer, const size_t c_offset, const size_t c_ld,
+          const Queue& queue = current::queue(), Event* event = nullptr) {
+    if (m == 0 || n == 0) throw BLASError(StatusCode::kInvalidDimension);
+    const size_t ka = side == Side::Left ? m : n;
+    const bool row = layout == Layout::RowMajor;
+    detail::test_matrix(ka, ka, a_buffer, a_offset, a_ld, StatusCode::kInvalidLeadDimA, StatusCode::kInsufficientMemoryA);
+    detail::test_matrix(row ? n : m, row ? m : n, b_buffer, b_offset, b_ld, StatusCode::kInvalidLeadDimB, StatusCode::kInsufficientMemoryB);
+    detail::test_matrix(row ? n : m, row ? m : n, c_buffer, c_offset, c_ld, StatusCode::kInvalidLeadDimC, StatusCode::kInsufficientMemoryC);
+    TemporaryBuffer<unsigned char> work(dlf_b200_level3_workspace_bytes(DLF_B200_SYMM, PrecisionOf<T>::value, m, n));
+    detail::EventScope scope(queue, event);
+    detail::raise(dlf_b200_symm(PrecisionOf<T>::value, static_cast<int>(layout), static_cast<int>(side),
+                                static_cast<int>(triangle), m, n, &alpha, a_buffer.unwrap() + a_offset, a_ld,
+                                b_buffer.unwrap() + b_offset, b_ld, &beta, c_buffer.unwrap() + c_offset, c_ld,
+                                work.unwrap(), work.data_size(), queue.unwrap()),
+                  "dlf_b200_symm");
+}
+
+// Rank-K update of a symmetric matrix (gblas.h:528-536)
+template <typename T>
+void syrk(const Layout layout, const Triangle triangle, const Transpose a_transpose,
+          const size_t n, const size_t k,
+          const T alpha,
+          const Buffer<T>& a_buffer, const size_t a_offset, const size_t a_ld,
+          const T beta,
+          Buffer<T>& c_buffer, const size_t c_offset, const size_t c_ld,
+          const Queue& queue = current::queue(), Event* event = nullptr) {
+    if (n == 0 || k == 0) throw BLASError(StatusCode::kInvalidDimension);
+    const bool row = layout == Layout::RowMajor;
+    const bool a_rot = (row && a_transpose == Transpose::NoTrans) || (!row && a_transpose != Transpose::NoTrans);
+    detail::test_matrix(a_rot ? k : n, a_rot ? n : k, a_buffer, a_offset, a_ld, StatusCode::kInvalidLeadDimA, StatusCode::kInsufficientMemoryA);
+    detail::test_matrix(n, n, c_buffer, c_offset, c_ld, StatusCode::kInvalidLeadDimC, StatusCode::kInsufficientMemoryC);
+    TemporaryBuffer<unsigned char> work(dlf_b200_level3_workspace_bytes(DLF_B200_SYRK, PrecisionOf<T>::value, n, n));
+    detail::EventScope scope(queue, event);
+    detail::raise(dlf_b200_syrk(PrecisionOf<T>::value, static_cast<int>(layout), static_cast<int>(triangle),
+                                static_cast<int>(a_transpose), n, k, &alpha, a_buffer.unwrap() + a_offset, a_ld, &beta,
+                                c_buffer.unwrap() + c_offset, c_ld, work.unwrap(), work.data_size(), queue.unwrap()),
+                  "dlf_b200_syrk");
+}
+
+namespace detail {
+template <typename T, typename Fn>
+void triangular(Fn fn, const char* name, int routine, const Layout layout, const Side side, const Triangle triangle,
+                const Transpose a_transpose, const Diagonal diagonal, const size_t m, const size_t n, const T alpha,
+                const Buffer<T>& a_buffer, const size_t a_offset, const size_t a_ld, Buffer<T>& b_buffer,
+                const size_t b_offset, const size_t b_ld, const Queue& queue, Event* event) {
+    if (m == 0 || n == 0) throw BLASError(StatusCode::kInvalidDimension);
+    const size_t ka = side == Side::Left ? m : n;
+    const bool row = layout == Layout::RowMajor;
+    test_matrix(ka, ka, a_buffer, a_offset, a_ld, StatusCode::kInvalidLeadDimA, StatusCode::kInsufficientMemoryA);
+    test_matrix(row ? n : m, row ? m : n, b_buffer, b_offset, b_ld, StatusCode::kInvalidLeadDimB, StatusCode::kInsufficientMemoryB);
+    TemporaryBuffer<unsigned char> work(dlf_b200_level3_workspace_bytes(routine, PrecisionOf<T>::value, m, n) + 16);
+    EventScope scope(queue, event);
+    raise(fn(PrecisionOf<T>::value, static_cast<int>(layout), static_cast<int>(side), static_cast<int>(triangle),
+             static_cast<int>(a_transpose), static_cast<int>(diagonal), m, n, &alpha, a_buffer.unwrap() + a_offset, a_ld,
+             b_buffer.unwrap() + b_offset, b_ld, work.unwrap(), work.data_size(), queue.unwrap()),
+          name);
+}
+}  // namespace detail
+
+// Triangular matrix-matrix multiplication (gblas.h:570-577)
+template <typename T>
+void trmm(const Layout layout, const Side side, const Triangle triangle, const Transpose a_transpose, const Diagonal diagonal,
+          const size_t m, const size_t n,
+          const T alpha,
+          const Buffer<T>& a_buffer, const size_t a_offset, const size_t a_ld,
+          Buffer<T>& b_buffer, const size_t b_offset, const size_t b_ld,
+          const Queue& queue = current::queue(), Event* event = nullptr) {
+    detail::triangular<T>(dlf_b200_trmm, "dlf_b200_trmm", DLF_B200_TRMM, layout, side, triangle, a_transpose, diagonal, m, n,
+                          alpha, a_buffer, a_offset, a_ld, b_buffer, b_offset, b_ld, queue, event);
+}
+
+// Solves a triangular system of equations (gblas.h:579-586)
+template <typename T>
+void trsm(const Layout layout, const Side side, const Triangle triangle, const Transpose a_transpose, const Diagonal diagonal,
+          const size_t m, const size_t n,
+          const T alpha,
+          const Buffer<T>& a_buffer, const size_t a_offset, const size_t a_ld,
+          Buffer<T>& b_buffer, const size_t b_offset, const size_t b_ld,
+          const Queue& queue = current::queue(), Event* event = nullptr) {
+    detail::triangular<T>(dlf_b200_trsm, "dlf_b200_trsm", DLF_B200_TRSM, layout, side, triangle, a_transpose, diagonal, m, n,
+                          alpha, a_buffer, a_offset, a_ld, b_buffer, b_offset, b_ld, queue, event);
 }
 
 }  // namespace blas

@@ -233,3 +233,53 @@ def host_sgemm_nn_callback(fn):
     def cb(m, n, k, a, lda, b, ldb, c, ldc):
         fn(ROW_MAJOR, NO_TRANS, NO_TRANS, m, n, k, 1.0, a, lda, b, ldb, 0.0, c, ldc)
     return _SGEMM_NN_FN(cb)
+
+
+# ---------------------------------------------------------------------------------------------
+# level-3 routines built on GEMM (row-major float32; flat or 2-D C-contiguous numpy buffers)
+# ---------------------------------------------------------------------------------------------
+UPPER, LOWER = 121, 122
+NON_UNIT, UNIT = 131, 132
+LEFT, RIGHT = 141, 142
+
+
+def symm(side, uplo, m, n, alpha, A, lda, B, ldb, beta, C, ldc, wide=False):
+    """gblas::symm / cblas_ssymm, row-major: C = alpha*S*B + beta*C (Left) or alpha*B*S + beta*C
+    (Right), S symmetric with only its `uplo` triangle stored in A. C is updated in place."""
+    fn = lib().dlf_oracle_symm_f32
+    fn.restype = None
+    fn.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_size_t, ctypes.c_size_t, ctypes.c_float, ctypes.c_void_p,
+                   ctypes.c_size_t, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_float, ctypes.c_void_p,
+                   ctypes.c_size_t, ctypes.c_int]
+    fn(side, uplo, m, n, alpha, _p(A), lda, _p(B), ldb, beta, _p(C), ldc, 1 if wide else 0)
+    return C
+
+
+def syrk(uplo, trans, n, k, alpha, A, lda, beta, C, ldc, wide=False):
+    """gblas::syrk / cblas_ssyrk, row-major: the `uplo` triangle of C = alpha*op(A)*op(A)^T + beta*C."""
+    fn = lib().dlf_oracle_syrk_f32
+    fn.restype = None
+    fn.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_size_t, ctypes.c_size_t, ctypes.c_float, ctypes.c_void_p,
+                   ctypes.c_size_t, ctypes.c_float, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int]
+    fn(uplo, trans, n, k, alpha, _p(A), lda, beta, _p(C), ldc, 1 if wide else 0)
+    return C
+
+
+def _tri(name, side, uplo, trans, diag, m, n, alpha, A, lda, B, ldb, wide):
+    fn = getattr(lib(), name)
+    fn.restype = None
+    fn.argtypes = [ctypes.c_int] * 4 + [ctypes.c_size_t, ctypes.c_size_t, ctypes.c_float, ctypes.c_void_p,
+                                        ctypes.c_size_t, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int]
+    fn(side, uplo, trans, diag, m, n, alpha, _p(A), lda, _p(B), ldb, 1 if wide else 0)
+    return B
+
+
+def trmm(side, uplo, trans, diag, m, n, alpha, A, lda, B, ldb, wide=False):
+    """gblas::trmm / cblas_strmm, row-major: B = alpha*op(T)*B (Left) or alpha*B*op(T) (Right), in place."""
+    return _tri("dlf_oracle_trmm_f32", side, uplo, trans, diag, m, n, alpha, A, lda, B, ldb, wide)
+
+
+def trsm(side, uplo, trans, diag, m, n, alpha, A, lda, B, ldb, wide=False):
+    """gblas::trsm / cblas_strsm, row-major: solves op(T)*X = alpha*B (Left) or X*op(T) = alpha*B
+    (Right); X overwrites B."""
+    return _tri("dlf_oracle_trsm_f32", side, uplo, trans, diag, m, n, alpha, A, lda, B, ldb, wide)

@@ -342,3 +342,171 @@ void dlf_oracle_global_pool_f32(const float* X, float* Y, int mode, size_t plane
         }
     }
 }
+
+/* ------------------------------------------------------------------------------------------
+ * Level-3 routines that sit on GEMM: symm, syrk, trmm, trsm, row-major, float.
+ *
+ * dlf's CPU path hands float operands to cblas_ssymm / cblas_ssyrk / cblas_strmm / cblas_strsm
+ * (dlf/include/tensor/linalg_detail.h:463-470, 546-552, 1265-1272, 1318-1323 over
+ * dlf/include/cxxblas.h); for element types without a BLAS it evaluates the definitions below
+ * itself (symv_up / symv_lo :365-399, syrk_serial :486-523, trmm_serial :720-812, trsm_serial).
+ * Only the named triangle of A (symm, trmm, trsm) or of C (syrk) is read or written; with
+ * Diagonal::Unit the diagonal of A is not read and counts as 1. `wide` = double accumulators.
+ * Enumerators are gblas.h:110-114: Upper 121, Lower 122; NonUnit 131, Unit 132; Left 141, Right 142.
+ * ------------------------------------------------------------------------------------------ */
+enum { DLF_UPPER = 121, DLF_LOWER = 122, DLF_NON_UNIT = 131, DLF_UNIT = 132, DLF_LEFT = 141, DLF_RIGHT = 142 };
+
+/* element (i, j) of the symmetric matrix whose `uplo` triangle is stored in A */
+static float sym_at(const float* A, size_t lda, int uplo, size_t i, size_t j) {
+    const int stored = uplo == DLF_UPPER ? (i <= j) : (i >= j);
+    return stored ? A[i * lda + j] : A[j * lda + i];
+}
+
+/* element (i, j) of op(T), T the triangular matrix stored in the `uplo` triangle of A */
+static float tri_at(const float* A, size_t lda, int uplo, int trans, int diag, size_t i, size_t j) {
+    const size_t r = trans == DLF_NO_TRANS ? i : j, c = trans == DLF_NO_TRANS ? j : i;
+    if (r == c) return diag == DLF_UNIT ? 1.0f : A[r * lda + c];
+    if (uplo == DLF_UPPER ? (r < c) : (r > c)) return A[r * lda + c];
+    return 0.0f;
+}
+
+void dlf_oracle_symm_f32(int side, int uplo, size_t m, size_t n, float alpha, const float* A, size_t lda,
+                         const float* B, size_t ldb, float beta, float* C, size_t ldc, int wide) {
+    long i;
+#pragma omp parallel for schedule(static)
+    for (i = 0; i < (long)m; ++i) {
+        size_t j, l;
+        for (j = 0; j < n; ++j) {
+            double accd = 0.0;
+            float accf = 0.0f;
+            if (side == DLF_LEFT) {  /* C = alpha * S(m x m) * B + beta * C */
+                for (l = 0; l < m; ++l) {
+                    const float a = sym_at(A, lda, uplo, (size_t)i, l), b = B[l * ldb + j];
+                    if (wide) accd += (double)a * (double)b; else accf += a * b;
+                }
+            } else {                 /* C = alpha * B * S(n x n) + beta * C */
+                for (l = 0; l < n; ++l) {
+                    const float b = B[(size_t)i * ldb + l], a = sym_at(A, lda, uplo, l, j);
+                    if (wide) accd += (double)b * (double)a; else accf += b * a;
+                }
+            }
+            float* c = C + (size_t)i * ldc + j;
+            if (wide) *c = (float)((double)alpha * accd + (beta == 0.0f ? 0.0 : (double)beta * (double)*c));
+            else *c = alpha * accf + (beta == 0.0f ? 0.0f : beta * *c);
+        }
+    }
+}
+
+/* C(uplo triangle) = alpha * op(A) * op(A)^T + beta * C; op(A) is n x k (A is n x k for NoTrans, k x n for Trans) */
+void dlf_oracle_syrk_f32(int uplo, int trans, size_t n, size_t k, float alpha, const float* A, size_t lda,
+                         float beta, float* C, size_t ldc, int wide) {
+    long i;
+#pragma omp parallel for schedule(static)
+    for (i = 0; i < (long)n; ++i) {
+        size_t j, l;
+        for (j = 0; j < n; ++j) {
+            if (!(uplo == DLF_UPPER ? ((size_t)i <= j) : ((size_t)i >= j))) continue;
+            double accd = 0.0;
+            float accf = 0.0f;
+            for (l = 0; l < k; ++l) {
+                const float a = trans == DLF_NO_TRANS ? A[(size_t)i * lda + l] : A[l * lda + (size_t)i];
+                const float b = trans == DLF_NO_TRANS ? A[j * lda + l] : A[l * lda + j];
+                if (wide) accd += (double)a * (double)b; else accf += a * b;
+            }
+            float* c = C + (size_t)i * ldc + j;
+            if (wide) *c = (float)((double)alpha * accd + (beta == 0.0f ? 0.0 : (double)beta * (double)*c));
+            else *c = alpha * accf + (beta == 0.0f ? 0.0f : beta * *c);
+        }
+    }
+}
+
+/* B = alpha * op(T) * B (Left, T is m x m) or alpha * B * op(T) (Right, T is n x n), in place */
+void dlf_oracle_trmm_f32(int side, int uplo, int trans, int diag, size_t m, size_t n, float alpha,
+                         const float* A, size_t lda, float* B, size_t ldb, int wide) {
+    float* out = (float*)malloc(m * n * sizeof(float));
+    long i;
+#pragma omp parallel for schedule(static)
+    for (i = 0; i < (long)m; ++i) {
+        size_t j, l;
+        for (j = 0; j < n; ++j) {
+            double accd = 0.0;
+            float accf = 0.0f;
+            if (side == DLF_LEFT) {
+                for (l = 0; l < m; ++l) {
+                    const float t = tri_at(A, lda, uplo, trans, diag, (size_t)i, l), b = B[l * ldb + j];
+                    if (wide) accd += (double)t * (double)b; else accf += t * b;
+                }
+            } else {
+                for (l = 0; l < n; ++l) {
+                    const float b = B[(size_t)i * ldb + l], t = tri_at(A, lda, uplo, trans, diag, l, j);
+                    if (wide) accd += (double)b * (double)t; else accf += b * t;
+                }
+            }
+            out[(size_t)i * n + j] = wide ? (float)((double)alpha * accd) : alpha * accf;
+        }
+    }
+    {
+        size_t r, c;
+        for (r = 0; r < m; ++r)
+            for (c = 0; c < n; ++c) B[r * ldb + c] = out[r * n + c];
+    }
+    free(out);
+}
+
+/* Solves op(T) * X = alpha * B (Left) or X * op(T) = alpha * B (Right) by substitution; X overwrites B. */
+void dlf_oracle_trsm_f32(int side, int uplo, int trans, int diag, size_t m, size_t n, float alpha,
+                         const float* A, size_t lda, float* B, size_t ldb, int wide) {
+    /* op(T) is lower triangular when (Lower, NoTrans) or (Upper, Trans) */
+    const int eff_lower = (uplo == DLF_LOWER) == (trans == DLF_NO_TRANS);
+    if (side == DLF_LEFT) {
+        long j;
+#pragma omp parallel for schedule(static)
+        for (j = 0; j < (long)n; ++j) {  /* columns of B are independent systems */
+            size_t s, l;
+            double* x = (double*)malloc(m * sizeof(double));
+            for (s = 0; s < m; ++s) {
+                const size_t i = eff_lower ? s : m - 1 - s;
+                double acc = (double)alpha * (double)B[i * ldb + (size_t)j];
+                float accf = alpha * B[i * ldb + (size_t)j];
+                for (l = 0; l < s; ++l) {
+                    const size_t c = eff_lower ? l : m - 1 - l;
+                    const float t = tri_at(A, lda, uplo, trans, diag, i, c);
+                    acc -= (double)t * x[c];
+                    accf -= t * (float)x[c];
+                }
+                {
+                    const float d = tri_at(A, lda, uplo, trans, diag, i, i);
+                    x[i] = wide ? acc / (double)d : (double)(accf / d);
+                }
+            }
+            for (s = 0; s < m; ++s) B[s * ldb + (size_t)j] = (float)x[s];
+            free(x);
+        }
+    } else {
+        long i;
+#pragma omp parallel for schedule(static)
+        for (i = 0; i < (long)m; ++i) {  /* rows of B are independent systems: x * op(T) = alpha * b */
+            size_t s, l;
+            double* x = (double*)malloc(n * sizeof(double));
+            float* b = B + (size_t)i * ldb;
+            for (s = 0; s < n; ++s) {
+                /* x_j needs x_l for the l with op(T)(l, j) != 0, l != j: l < j when op(T) is upper */
+                const size_t j = eff_lower ? n - 1 - s : s;
+                double acc = (double)alpha * (double)b[j];
+                float accf = alpha * b[j];
+                for (l = 0; l < s; ++l) {
+                    const size_t r = eff_lower ? n - 1 - l : l;
+                    const float t = tri_at(A, lda, uplo, trans, diag, r, j);
+                    acc -= x[r] * (double)t;
+                    accf -= (float)x[r] * t;
+                }
+                {
+                    const float d = tri_at(A, lda, uplo, trans, diag, j, j);
+                    x[j] = wide ? acc / (double)d : (double)(accf / d);
+                }
+            }
+            for (s = 0; s < n; ++s) b[s] = (float)x[s];
+            free(x);
+        }
+    }
+}

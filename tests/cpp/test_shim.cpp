@@ -161,6 +161,34 @@ static void temporary_pool_is_lifo() {
     CHECK(again.offset() * sizeof(float) >= 400 && again.offset() * sizeof(float) < 1024);
 }
 
+static void level3_goldens() {
+    // symm_test / trmm_test of dlf/test/GPGPUTest.cpp:307-470: A = {6,5}.range(1), B = {4,3}.range(1) / identity
+    std::vector<float> A(30), B(12);
+    for (int i = 0; i < 30; ++i) A[i] = static_cast<float>(i + 1);
+    for (int i = 0; i < 12; ++i) B[i] = static_cast<float>(i + 1);
+    auto dA = dev(A), dB = dev(B);
+    Buffer<float> dC(12);
+    blas::symm<float>(Layout::RowMajor, blas::Side::Left, blas::Triangle::Lower, 4, 3, 1.0f, dA, 0, 5, dB, 0, 3, 0.0f, dC, 0, 3);
+    CHECK(host(dC) == (std::vector<float>{262, 296, 330, 288, 330, 372, 330, 384, 438, 400, 470, 540}));
+    blas::symm<float>(Layout::RowMajor, blas::Side::Right, blas::Triangle::Upper, 4, 3, 1.0f, dA, 0, 5, dB, 0, 3, 0.0f, dC, 0, 3);
+    CHECK(host(dC) == (std::vector<float>{14, 40, 58, 32, 91, 130, 50, 142, 202, 68, 193, 274}));
+    std::vector<float> I(16, 0.0f);
+    for (int i = 0; i < 4; ++i) I[i * 5] = 1.0f;
+    auto dI = dev(I);
+    blas::trmm<float>(Layout::RowMajor, blas::Side::Left, blas::Triangle::Upper, Transpose::NoTrans, blas::Diagonal::Unit, 4, 4,
+                      1.0f, dA, 0, 5, dI, 0, 4);
+    CHECK(host(dI) == (std::vector<float>{1, 2, 3, 4, 0, 1, 8, 9, 0, 0, 1, 14, 0, 0, 0, 1}));
+    // trsm undoes it
+    blas::trsm<float>(Layout::RowMajor, blas::Side::Left, blas::Triangle::Upper, Transpose::NoTrans, blas::Diagonal::Unit, 4, 4,
+                      1.0f, dA, 0, 5, dI, 0, 4);
+    CHECK(host(dI) == I);
+    // syrk: lower triangle of C = A A^T for the leading 3 x 5 block of A; the strict upper triangle keeps its 7s
+    std::vector<float> C(9, 7.0f);
+    auto dS = dev(C);
+    blas::syrk<float>(Layout::RowMajor, blas::Triangle::Lower, Transpose::NoTrans, 3, 5, 1.0f, dA, 0, 5, 0.0f, dS, 0, 3);
+    CHECK(host(dS) == (std::vector<float>{55, 7, 7, 130, 330, 7, 205, 530, 855}));
+}
+
 static void errors() {
     Buffer<float> a(16), c(15);
     auto status_of = [&](auto&& fn) {
@@ -188,6 +216,7 @@ int main() {
     maxpool_golden();
     batched();
     temporary_pool_is_lifo();
+    level3_goldens();
     errors();
     int dev_status = -1;
     CHECK(dlf_b200_device_status(&dev_status) == 0 && dev_status == 0);

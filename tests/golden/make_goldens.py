@@ -13,6 +13,7 @@ parsed out of
     dlf/test/TensorTest.cpp          dot_test()             (v.v, v.M, M.v, M.M)
     dlf/test/UniformTest.cpp         TEST(UniformTest, Dot), TEST(UniformTest, MultiDot*)
     dlf/test/GPGPUTest.cpp           vector_dot_vector_test() ... matrix_dot_matrix_test()
+    dlf/test/GPGPUTest.cpp           symm_test(), trmm_test()
 
 Usage:  python tests/golden/make_goldens.py /path/to/dlf-checkout
 Only the JSON travels with the repository; the tests never read the reference tree.
@@ -297,6 +298,30 @@ def extract_dot(tensor_test, uniform_test, gpgpu_test):
     return cases
 
 
+def extract_level3(path, rel):
+    """symm_test() and trmm_test() of GPGPUTest.cpp: A = {6,5}.range(1); B = {4,3}.range(1) (symm)
+    or the 4x4 identity (trmm); every EXPECT_EQ against a literal is one case."""
+    text = open(path).read()
+    out = {"symm": [], "trmm": []}
+    pos = text.index("void symm_test()")
+    body, _ = _block(text, pos)
+    for m in re.finditer(r"EXPECT_EQ\(symm\(Side::(\w+),\s*Triangle::(\w+),\s*A,\s*B\),\s*"
+                         r"Tensor<T>\(\{([\d,\s]+)\},\s*\{([^}]*)\}\)\)", body, re.S):
+        out["symm"].append({"source": "%s:%d" % (rel, _line_of(text, pos)), "side": m.group(1), "triangle": m.group(2),
+                            "A": {"shape": [6, 5], "range": 1}, "B": {"shape": [4, 3], "range": 1},
+                            "expected": {"shape": _ints(m.group(3)), "values": _ints(m.group(4))}})
+    pos = text.index("void trmm_test()")
+    body, _ = _block(text, pos)
+    for m in re.finditer(r"EXPECT_EQ\(trmm\(Side::(\w+),\s*Triangle::(\w+),\s*Transpose::(\w+),\s*Diagonal::(\w+),"
+                         r"\s*A,\s*B\),\s*Tensor<T>\(\{([\d,\s]+)\},\s*\{([^}]*)\}\)\)", body, re.S):
+        out["trmm"].append({"source": "%s:%d" % (rel, _line_of(text, pos)), "side": m.group(1), "triangle": m.group(2),
+                            "transpose": m.group(3), "diagonal": m.group(4),
+                            "A": {"shape": [6, 5], "range": 1}, "B": {"shape": [4, 4], "identity": True},
+                            "expected": {"shape": _ints(m.group(5)), "values": _ints(m.group(6))}})
+    assert "range(1)" in body and "identity({4, 4})" in body, "trmm_test inputs moved"
+    return out
+
+
 def main():
     if len(sys.argv) < 2:
         sys.exit("usage: make_goldens.py /path/to/dlf-checkout")
@@ -313,6 +338,7 @@ def main():
         "pool": extract_pool(os.path.join(t, "DNNTest.cpp"), "dlf/test/DNNTest.cpp"),
         "predict": extract_predict(os.path.join(t, "model", "PredictTest.cpp"),
                                    "dlf/test/model/PredictTest.cpp"),
+        "level3": extract_level3(os.path.join(t, "GPGPUTest.cpp"), "dlf/test/GPGPUTest.cpp"),
         "dot": extract_dot((os.path.join(t, "TensorTest.cpp"), "dlf/test/TensorTest.cpp"),
                            (os.path.join(t, "UniformTest.cpp"), "dlf/test/UniformTest.cpp"),
                            (os.path.join(t, "GPGPUTest.cpp"), "dlf/test/GPGPUTest.cpp")),

@@ -1088,3 +1088,164 @@ def test_conv2d_pointwise_with_very_many_channels(lib, dtype, stride):
     else:
         assert max_rel(got, ref) <= HALF_TOL
     assert lib.device_status() == 0
+
+
+# ------------------------------------------------------------------------------------------
+# level-3 routines on the GEMM main loop: symm, syrk, trmm, trsm
+# ------------------------------------------------------------------------------------------
+def _l3_operand(spec, dtype):
+    if spec.get("identity"):
+        return torch.eye(spec["shape"][0], dtype=dtype)
+    return tensor_of(spec, dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("case", G["level3"]["symm"], ids=lambda c: c["side"] + c["triangle"])
+def test_symm_goldens(case, dtype):
+    """symm_test of dlf/test/GPGPUTest.cpp:307-351 through the front-end, bit-exact."""
+    from dlf_b200 import tensor as dt
+    gb = _gb()
+    A, B = _l3_operand(case["A"], dtype).cuda(), _l3_operand(case["B"], dtype).cuda()
+    got = dt.symm(gb.Side[case["side"]], gb.Triangle[case["triangle"]], A, B)
+    assert torch.equal(got.cpu(), tensor_of(case["expected"], dtype))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("case", G["level3"]["trmm"],
+                         ids=lambda c: c["side"] + c["triangle"] + c["transpose"] + c["diagonal"])
+def test_trmm_goldens_and_trsm_inverts_them(case, dtype):
+    """trmm_test of dlf/test/GPGPUTest.cpp:361-470, bit-exact; trsm with the same arguments gives
+    the identity back (fp32: the values are small integers, the solve is exact up to rounding)."""
+    from dlf_b200 import tensor as dt
+    gb = _gb()
+    A, B = _l3_operand(case["A"], dtype).cuda(), _l3_operand(case["B"], dtype).cuda()
+    args = (gb.Side[case["side"]], gb.Triangle[case["triangle"]], gb.Transpose[case["transpose"]],
+            gb.Diagonal[case["diagonal"]])
+    got = dt.trmm(*args, A, B)
+    assert torch.equal(got.cpu(), tensor_of(case["expected"], dtype))
+    if dtype == torch.float32:
+        back = dt.trsm(*args, A, got)
+        assert torch.allclose(back.cpu(), B.cpu(), atol=1e-5)
+
+
+L3_SHAPES = [(5, 7), (64, 64), (100, 100), (130, 257), (300, 70)]
+
+
+@pytest.mark.parametrize("layout", ["RowMajor", "ColMajor"])
+@pytest.mark.parametrize("m,n", L3_SHAPES)
+def test_symm_and_syrk_random_parity(lib, layout, m, n):
+    """symm (both sides, both triangles) and syrk (both triangles, both transpositions) on seeded
+    inputs with padded leading dimensions and element offsets, fp32, against the oracle; the
+    triangle of C that syrk does not own must keep its values. Column-major calls are checked
+    through the transposed row-major problem."""
+    gb = _gb()
+    rng = np.random.default_rng(m * 1000 + n)
+    lay = gb.Layout[layout]
+    row = layout == "RowMajor"
+    for side in (gb.Side.Left, gb.Side.Right):
+        for tri in (gb.Triangle.Upper, gb.Triangle.Lower):
+            ka = m if side == gb.Side.Left else n
+            lda, ldb, ldc = ka + 3, (n if row else m) + 2, (n if row else m) + 5
+            A = _rand(rng, 7 + lda * ka)
+            B = _rand(rng, 3 + ldb * (m if row else n))
+            C0 = _rand(rng, 1 + ldc * (m if row else n))
+            got = torch.from_numpy(C0.copy()).cuda()
+            gb.symm(lay, side, tri, m, n, 0.75, torch.from_numpy(A).cuda(), 7, lda, torch.from_numpy(B).cuda(), 3, ldb,
+                    -0.5, got, 1, ldc)
+            ref = C0.copy()
+            if row:
+                oracle.symm(int(side), int(tri), m, n, 0.75, A[7:], lda, B[3:], ldb, -0.5, ref[1:], ldc, wide=True)
+            else:  # C^T = B^T S (Left) / S B^T (Right), the other triangle of the row-major view of A
+                oracle.symm(oracle.RIGHT if side == gb.Side.Left else oracle.LEFT,
+                            oracle.LOWER if tri == gb.Triangle.Upper else oracle.UPPER, n, m, 0.75, A[7:], lda, B[3:],
+                            ldb, -0.5, ref[1:], ldc, wide=True)
+            assert rel_fro(got.cpu().numpy(), ref) <= FP32_TOL
+    k = n
+    for tri in (gb.Triangle.Upper, gb.Triangle.Lower):
+        for ta in (gb.Transpose.NoTrans, gb.Transpose.Trans):
+            a_rot = (row and ta == gb.Transpose.NoTrans) or (not row and ta != gb.Transpose.NoTrans)
+            one, two = (k, m) if a_rot else (m, k)
+            lda, ldc = one + 4, m + 3
+            A = _rand(rng, 5 + lda * two)
+            C0 = _rand(rng, 2 + ldc * m)
+            got = torch.from_numpy(C0.copy()).cuda()
+            gb.syrk(lay, tri, ta, m, k, 1.25, torch.from_numpy(A).cuda(), 5, lda, 0.5, got, 2, ldc)
+            ref = C0.copy()
+            if row:
+                oracle.syrk(int(tri), int(ta), m, k, 1.25, A[5:], lda, 0.5, ref[2:], ldc, wide=True)
+            else:
+                oracle.syrk(oracle.LOWER if tri == gb.Triangle.Upper else oracle.UPPER,
+                            oracle.TRANS if ta == gb.Transpose.NoTrans else oracle.NO_TRANS, m, k, 1.25, A[5:], lda,
+                            0.5, ref[2:], ldc, wide=True)
+            g = got.cpu().numpy()
+            assert rel_fro(g, ref) <= FP32_TOL
+            # outside the owned triangle nothing changed, bit for bit
+            changed = g != C0
+            idx = np.nonzero(changed)[0] - 2
+            r, c = idx // ldc, idx % ldc
+            owned_upper = (tri == gb.Triangle.Upper) == row
+            assert np.all((c < m) & ((r <= c) if owned_upper else (r >= c)))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("layout", ["RowMajor", "ColMajor"])
+@pytest.mark.parametrize("m,n", L3_SHAPES)
+def test_trmm_and_trsm_random_parity(lib, layout, m, n, dtype):
+    """All sixteen (side, triangle, transposition, diagonal) forms of trmm and trsm on seeded
+    inputs (padded leading dimensions, offsets) against the oracle; the triangle of A that the
+    call does not name is filled with NaN and must never be read. trsm operands are made
+    diagonally dominant so that the systems are well conditioned."""
+    gb = _gb()
+    rng = np.random.default_rng(m * 31 + n)
+    lay = gb.Layout[layout]
+    row = layout == "RowMajor"
+    tol = FP32_TOL if dtype == torch.float32 else None
+    for side in (gb.Side.Left, gb.Side.Right):
+        ka = m if side == gb.Side.Left else n
+        for tri in (gb.Triangle.Upper, gb.Triangle.Lower):
+            for ta in (gb.Transpose.NoTrans, gb.Transpose.Trans):
+                for diag in (gb.Diagonal.NonUnit, gb.Diagonal.Unit):
+                    lda, ldb = ka + 2, (n if row else m) + 3
+                    Am = (0.5 / np.sqrt(ka)) * rng.uniform(-1, 1, (ka, lda)).astype(np.float32)
+                    Am[np.arange(ka), np.arange(ka)] = rng.uniform(1.0, 2.0, ka).astype(np.float32)
+                    # the stored triangle in the layout's own view; everything else is poison
+                    ii, jj = np.indices((ka, lda))
+                    stored_upper = (tri == gb.Triangle.Upper) == row
+                    keep = (jj < ka) & ((ii <= jj) if stored_upper else (ii >= jj))
+                    if diag == gb.Diagonal.Unit:
+                        keep &= ii != jj
+                    Am = _round_to(Am, dtype)
+                    A_clean = np.where(keep, Am, 0.0).astype(np.float32)
+                    A_dev = np.where(keep, Am, np.nan).astype(np.float32)
+                    B0 = _round_to(_rand(rng, 4 + ldb * (m if row else n)), dtype)
+                    o_side = int(side) if row else (oracle.RIGHT if side == gb.Side.Left else oracle.LEFT)
+                    o_tri = int(tri) if row else (oracle.LOWER if tri == gb.Triangle.Upper else oracle.UPPER)
+                    om, on = (m, n) if row else (n, m)
+                    for name in ("trmm", "trsm"):
+                        got = torch.from_numpy(B0.copy()).to(dtype).cuda()
+                        getattr(gb, name)(lay, side, tri, ta, diag, m, n, 0.5, torch.from_numpy(A_dev.ravel()).to(dtype).cuda(),
+                                          0, lda, got, 4, ldb)
+                        ref = B0.copy()
+                        getattr(oracle, name)(o_side, o_tri, int(ta), int(diag), om, on, 0.5, A_clean.ravel(), lda,
+                                              ref[4:], ldb, wide=True)
+                        g = got.float().cpu().numpy()
+                        assert np.isfinite(g).all(), (name, side, tri, ta, diag)
+                        if dtype == torch.float32:
+                            assert rel_fro(g, ref) <= tol, (name, side, tri, ta, diag)
+                        else:
+                            assert max_rel(g, ref) <= (HALF_TOL if name == "trmm" else 5e-2), (name, side, tri, ta, diag)
+
+
+def test_level3_argument_errors(lib):
+    gb = _gb()
+    a = torch.zeros(64, device="cuda")
+    with pytest.raises(gb.BLASError) as e:
+        gb.symm(gb.Layout.RowMajor, gb.Side.Left, gb.Triangle.Upper, 4, 4, 1.0, a, 0, 3, a, 0, 4, 0.0, a, 0, 4)
+    assert e.value.status == gb.StatusCode.kInvalidLeadDimA
+    with pytest.raises(gb.BLASError) as e:
+        gb.trsm(gb.Layout.RowMajor, gb.Side.Right, gb.Triangle.Upper, gb.Transpose.NoTrans, gb.Diagonal.Unit, 4, 0, 1.0,
+                a, 0, 4, a, 0, 4)
+    assert e.value.status == gb.StatusCode.kInvalidDimension
+    with pytest.raises(gb.BLASError) as e:
+        gb.syrk(gb.Layout.RowMajor, gb.Triangle.Lower, gb.Transpose.NoTrans, 8, 8, 1.0, a, 0, 8, 0.0, a, 1, 8)
+    assert e.value.status == gb.StatusCode.kInsufficientMemoryC

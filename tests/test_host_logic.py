@@ -68,6 +68,35 @@ def test_c_abi_argument_errors_without_a_device(built_lib):
     assert rc == -1017                                   # channels not divisible by group
 
 
+def test_level3_argument_errors_without_a_device(built_lib):
+    """symm / syrk / trmm / trsm check their arguments before any CUDA call, with the StatusCode
+    values of the reference's routines."""
+    L = built_lib
+    one = ctypes.c_float(1.0)
+    al = ctypes.byref(one)
+    p = ctypes.c_void_p(0x1000)
+    assert L.dlf_b200_symm(32, 101, 141, 121, 0, 4, al, p, 4, p, 4, al, p, 4, p, 1 << 20, None) == -1017
+    assert L.dlf_b200_symm(32, 101, 141, 121, 4, 6, al, p, 3, p, 6, al, p, 6, p, 1 << 20, None) == -1016   # A is m x m
+    assert L.dlf_b200_symm(32, 101, 142, 121, 4, 6, al, p, 5, p, 6, al, p, 6, p, 1 << 20, None) == -1016   # A is n x n
+    assert L.dlf_b200_symm(32, 101, 141, 121, 4, 6, al, p, 4, p, 5, al, p, 6, p, 1 << 20, None) == -1015
+    assert L.dlf_b200_symm(32, 102, 141, 121, 4, 6, al, p, 4, p, 4, al, p, 3, p, 1 << 20, None) == -1014   # col-major: ld >= m
+    assert L.dlf_b200_symm(32, 101, 141, 121, 4, 6, al, p, 4, p, 6, al, p, 6, None, 0, None) == -2050
+    assert L.dlf_b200_symm(32, 101, 140, 121, 4, 6, al, p, 4, p, 6, al, p, 6, p, 1 << 20, None) == -30
+    assert L.dlf_b200_syrk(32, 101, 121, 111, 4, 0, al, p, 4, al, p, 4, p, 1 << 20, None) == -1017
+    assert L.dlf_b200_syrk(32, 101, 121, 111, 4, 8, al, p, 7, al, p, 4, p, 1 << 20, None) == -1016         # row-major NoTrans: ld >= k
+    assert L.dlf_b200_syrk(32, 101, 121, 112, 4, 8, al, p, 3, al, p, 4, p, 1 << 20, None) == -1016         # row-major Trans: ld >= n
+    assert L.dlf_b200_syrk(32, 101, 121, 111, 4, 8, al, p, 8, al, p, 3, p, 1 << 20, None) == -1014
+    for fn in (L.dlf_b200_trmm, L.dlf_b200_trsm):
+        assert fn(32, 101, 141, 121, 111, 131, 4, 0, al, p, 4, p, 4, p, 1 << 20, None) == -1017
+        assert fn(32, 101, 141, 121, 111, 131, 4, 6, al, p, 3, p, 6, p, 1 << 20, None) == -1016
+        assert fn(32, 101, 142, 121, 111, 131, 4, 6, al, p, 6, p, 5, p, 1 << 20, None) == -1015
+        assert fn(32, 101, 141, 121, 111, 130, 4, 6, al, p, 4, p, 6, p, 1 << 20, None) == -30
+        assert fn(64, 101, 141, 121, 111, 131, 4, 6, al, p, 4, p, 6, p, 1 << 20, None) == -1024           # double: not implemented
+    assert L.dlf_b200_trmm(32, 101, 141, 121, 111, 131, 4, 6, al, p, 4, p, 6, None, 0, None) == -2050
+    assert L.dlf_b200_level3_workspace_bytes(4, 32, 100, 100) == 0
+    assert L.dlf_b200_level3_workspace_bytes(1, 32, 100, 50) >= 100 * 100 * 4
+
+
 def test_python_mirror_validates_buffer_sizes():
     from dlf_b200 import gblas
     a = torch.zeros(16)

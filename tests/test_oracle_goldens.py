@@ -219,3 +219,42 @@ def test_average_pool_counts():
     b = oracle.pool2d(X, (3, 3), "avg", (1, 1, 1, 1), count_include_pad=True)
     assert np.all(a == 1.0)
     assert b[0, 0, 0, 0] == np.float32(4.0 / 9.0) and b[0, 0, 1, 1] == 1.0
+
+
+# ------------------------------------------------------------------------------------------
+# level-3 routines built on GEMM
+# ------------------------------------------------------------------------------------------
+_SIDE = {"Left": oracle.LEFT, "Right": oracle.RIGHT}
+_TRI = {"Upper": oracle.UPPER, "Lower": oracle.LOWER}
+_TRANS = {"NoTrans": oracle.NO_TRANS, "Trans": oracle.TRANS}
+_DIAG = {"NonUnit": oracle.NON_UNIT, "Unit": oracle.UNIT}
+
+
+def _level3_operand(spec):
+    if spec.get("identity"):
+        return np.eye(spec["shape"][0], dtype=np.float32)
+    return tensor_of(spec).numpy().astype(np.float32)
+
+
+@pytest.mark.parametrize("case", G["level3"]["symm"], ids=lambda c: c["side"] + c["triangle"])
+def test_symm_goldens(case):
+    """symm_test of dlf/test/GPGPUTest.cpp:307-351: the oracle's symm reproduces the literals."""
+    A, B = _level3_operand(case["A"]), _level3_operand(case["B"])
+    m, n = B.shape
+    C = np.zeros((m, n), np.float32)
+    oracle.symm(_SIDE[case["side"]], _TRI[case["triangle"]], m, n, 1.0, A, A.shape[1], B, n, 0.0, C, n)
+    assert C.flatten().tolist() == [float(v) for v in case["expected"]["values"]]
+
+
+@pytest.mark.parametrize("case", G["level3"]["trmm"],
+                         ids=lambda c: c["side"] + c["triangle"] + c["transpose"] + c["diagonal"])
+def test_trmm_goldens(case):
+    """trmm_test of dlf/test/GPGPUTest.cpp:361-470; trsm must undo each of them."""
+    A, B = _level3_operand(case["A"]), _level3_operand(case["B"])
+    m, n = B.shape
+    args = (_SIDE[case["side"]], _TRI[case["triangle"]], _TRANS[case["transpose"]], _DIAG[case["diagonal"]])
+    X = B.copy()
+    oracle.trmm(*args, m, n, 1.0, A, A.shape[1], X, n)
+    assert X.flatten().tolist() == [float(v) for v in case["expected"]["values"]]
+    oracle.trsm(*args, m, n, 1.0, A, A.shape[1], X, n, wide=True)
+    assert np.allclose(X, B, atol=1e-5)
