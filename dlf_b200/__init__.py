@@ -40,6 +40,10 @@ def _declare(L):
     L.dlf_b200_gemm.restype = c_int
     L.dlf_b200_gemm.argtypes = [c_int] * 4 + [c_size] * 3 + [
         c_void, c_void, c_size, c_void, c_size, c_void, c_void, c_size, c_void]
+    L.dlf_b200_gemm_ex.restype = c_int
+    L.dlf_b200_gemm_ex.argtypes = L.dlf_b200_gemm.argtypes[:-1] + [c_void, c_size, c_void]
+    L.dlf_b200_gemm_workspace_bytes.restype = c_size
+    L.dlf_b200_gemm_workspace_bytes.argtypes = [c_int, c_size, c_size, c_size]
     L.dlf_b200_gemm_strided_batched.restype = c_int
     L.dlf_b200_gemm_strided_batched.argtypes = [c_int] * 4 + [c_size] * 3 + [
         c_void, c_void, c_size, c_size, c_void, c_size, c_size, c_void, c_void, c_size, c_size,
@@ -89,6 +93,8 @@ def _declare(L):
 
 EXPORTED_SYMBOLS = (
     "dlf_b200_gemm",
+    "dlf_b200_gemm_ex",
+    "dlf_b200_gemm_workspace_bytes",
     "dlf_b200_gemm_strided_batched",
     "dlf_b200_gemm_batched",
     "dlf_b200_gemm_batched_workspace_bytes",

@@ -237,6 +237,7 @@ struct Problem {
     // caller-provided scratch for the packed filter bank of a convolution (may be null)
     unsigned char* pack_ws = nullptr;
     size_t pack_ws_bytes = 0;
+    bool d_f32 = false;  // 16-bit operands with fp32 output (partial products of a K-split GEMM)
     bool no_ts = false;  // convolution whose taps overflow the k table's 16/32-bit fields
 };
 
@@ -371,6 +372,18 @@ int choose_bn_ts(const Problem& q, int num_sms, int max_bn, int a_cols, long lon
     return best;
 }
 
+// Wait limit of a launch, and the one host-made failure the device-side time-out path can be
+// exercised with: tuning bit 0x10000000 makes a launch that consists of a single tile leave out the
+// commit that hands the finished accumulator to the epilogue, with a wait limit of 2^21 clocks
+// (about a millisecond) instead of 2^32. The epilogue's wait then runs out, every role drains,
+// tensor memory is freed and the status word reports the time-out; nothing traps or faults, and
+// the next launch runs normally.
+void set_wait_policy(Params& p, long long total_tiles) {
+    const bool inject = (g_force_generic.load() & 0x10000000) != 0 && total_tiles == 1;
+    p.wait_limit = inject ? (1ll << 21) : (1ll << 32);
+    p.skip_tile_commit = inject ? 1 : 0;
+}
+
 // A launch below is checked with cudaGetLastError(), which also returns an error that an earlier,
 // unrelated runtime call of this host thread left behind (non-sticky errors stay until read).
 // Such a leftover is not this call's failure: it is read away before the first launch.
@@ -475,6 +488,7 @@ int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
     p.g = q.g;
     p.status = st.status;
     p.ablate = g_force_generic.load() >> 16;
+    set_wait_policy(p, total);
     tp.a_kind = q.rc_kw ? A_ROWCONV : (q.a.im2col ? A_IM2COL : (q.a.k_major ? A_DENSE_K : A_DENSE_MN));
     tp.a_pointwise = pointwise ? 1 : 0;
     tp.rc_kw = q.rc_kw;
@@ -623,6 +637,7 @@ int launch(const Problem& q, cudaStream_t stream, DeviceState* preset = nullptr)
         p.relu = q.relu;
         p.g = q.g;
         p.status = st->status;
+        set_wait_policy(p, ptotal);
         CUtensorMap tm_a, tm_b, tm_d;
         std::memset(&tm_d, 0, sizeof(tm_d));
         rc = encode_map(*st, &tm_a, q.a, q.es, q.M, q.K, q.batch, kBM);
@@ -689,6 +704,8 @@ int launch(const Problem& q, cudaStream_t stream, DeviceState* preset = nullptr)
     p.relu = q.relu;
     p.g = q.g;
     p.status = st->status;
+    p.d_f32 = q.d_f32 ? 1 : 0;
+    set_wait_policy(p, total);
 
     CUtensorMap tm_a, tm_b, tm_d;
     std::memset(&tm_a, 0, sizeof(tm_a));
@@ -701,7 +718,7 @@ int launch(const Problem& q, cudaStream_t stream, DeviceState* preset = nullptr)
         rc = encode_map(*st, &tm_b, q.b, q.es, q.N, q.K, q.batch, bn);
         if (rc != kSuccess) return rc;
         const unsigned box_cols = (bn >= 128 && !(g_force_generic.load() & 0x100)) ? 64 : 32;
-        p.d_tma = encode_output_map(*st, &tm_d, q, box_cols) ? static_cast<int>(box_cols) : 0;
+        p.d_tma = (!q.d_f32 && encode_output_map(*st, &tm_d, q, box_cols)) ? static_cast<int>(box_cols) : 0;
     }
 
     const unsigned grid = static_cast<unsigned>(total < st->num_sms ? total : st->num_sms);
@@ -844,6 +861,57 @@ int setup_gemm(Problem& q, int dtype, int layout, int ta, int tb, size_t m, size
 }  // namespace
 
 // ---------------------------------------------------------------------------------------------
+// K-split GEMM. A product with few output tiles and a long K leaves most SMs idle (the fully
+// connected layer 256 x 1000 x 2048: 16 tiles on 148 SMs). With scratch from the caller the K range
+// is cut into slices that run as the batch entries of one launch, each writing an fp32 partial
+// product, and a second kernel adds the slices and applies alpha / beta.
+// ---------------------------------------------------------------------------------------------
+size_t splitk_slices(const Problem& q, int num_sms) {
+    if (q.batch != 1 || q.a_offs != nullptr || q.a.im2col) return 1;
+    const long long BK = 128 / q.es;
+    const long long tiles = ((q.M + kBM - 1) / kBM) * ((q.N + 127) / 128);
+    if (tiles * 2 > num_sms || q.K < 8 * BK) return 1;
+    // the fewest slices that fill about three quarters of the SMs, each at least four k-blocks long
+    size_t best = 1;
+    for (size_t s : {2, 4, 8}) {
+        if (q.K % (static_cast<long long>(s) * BK) != 0 || q.K / static_cast<long long>(s) < 4 * BK) break;
+        best = s;
+        if (tiles * static_cast<long long>(s) * 4 >= 3ll * num_sms) break;
+    }
+    return best;
+}
+
+int launch_splitk(const Problem& q, size_t slices, void* workspace, cudaStream_t stream, DeviceState* st) {
+    Problem r = q;
+    const long long ks = q.K / static_cast<long long>(slices);
+    r.K = ks;
+    r.batch = static_cast<long long>(slices);
+    r.a.batch_stride = q.a.k_major ? ks : ks * q.a.ld;
+    r.b.batch_stride = q.b.k_major ? ks : ks * q.b.ld;
+    r.d = static_cast<char*>(workspace);
+    r.ldd = q.M;
+    r.d_batch_stride = q.M * q.N;
+    r.alpha = 1.0f;
+    r.beta = 0.0f;
+    r.bias = nullptr;
+    r.d_f32 = q.es == 2;
+    int rc = launch(r, stream, st);
+    if (rc != kSuccess) return rc;
+    const long long total = q.M * q.N;
+    const unsigned grid = static_cast<unsigned>(std::min<long long>((total + 255) / 256, 148 * 8));
+    const float* part = static_cast<const float*>(workspace);
+    if (q.fmt == FMT_F32)
+        splitk_reduce_kernel<float><<<grid, 256, 0, stream>>>(reinterpret_cast<float*>(q.d), q.ldd, part, static_cast<int>(q.M), static_cast<int>(q.N), static_cast<int>(slices), q.alpha, q.beta);
+    else if (q.fmt == FMT_F16)
+        splitk_reduce_kernel<__half><<<grid, 256, 0, stream>>>(reinterpret_cast<__half*>(q.d), q.ldd, part, static_cast<int>(q.M), static_cast<int>(q.N), static_cast<int>(slices), q.alpha, q.beta);
+    else
+        splitk_reduce_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(reinterpret_cast<__nv_bfloat16*>(q.d), q.ldd, part, static_cast<int>(q.M), static_cast<int>(q.N), static_cast<int>(slices), q.alpha, q.beta);
+    g_launches.fetch_add(1);
+    CUDA_TRY(cudaGetLastError());
+    return kSuccess;
+}
+
+// ---------------------------------------------------------------------------------------------
 // helpers of the level-3 routines (symm, syrk, trmm, trsm) further down
 // ---------------------------------------------------------------------------------------------
 namespace {
@@ -944,6 +1012,48 @@ int dlf_b200_gemm(int dtype, int layout, int trans_a, int trans_b, size_t m, siz
     StreamDevice sd(static_cast<cudaStream_t>(stream));
     if (sd.rc != kSuccess) return sd.rc;
     return launch(q, static_cast<cudaStream_t>(stream));
+}
+
+size_t dlf_b200_gemm_workspace_bytes(int dtype, size_t m, size_t n, size_t k) {
+    // optional scratch of dlf_b200_gemm_ex: up to 8 fp32 partial products of m x n elements, only
+    // for products small enough to profit from a K-split (an upper bound; 0 = never used)
+    int fmt = 0, es = 0;
+    if (!dtype_info(dtype, fmt, es) || m == 0 || n == 0 || k == 0) return 0;
+    const size_t tiles = ((m + 127) / 128) * ((n + 127) / 128);
+    if (tiles > 148 || k < 8 * static_cast<size_t>(128 / es)) return 0;
+    return 8 * m * n * sizeof(float) + 256;
+}
+
+int dlf_b200_gemm_ex(int dtype, int layout, int trans_a, int trans_b, size_t m, size_t n, size_t k,
+                     const void* alpha, const void* a, size_t a_ld, const void* b, size_t b_ld,
+                     const void* beta, void* c, size_t c_ld, void* workspace, size_t workspace_bytes,
+                     void* stream) {
+    Problem q;
+    int rc = setup_gemm(q, dtype, layout, trans_a, trans_b, m, n, k, a, a_ld, b, b_ld, c, c_ld);
+    if (rc != kSuccess) return rc;
+    if (alpha == nullptr || beta == nullptr) return kInvalidValue;
+    q.alpha = scalar_to_float(q.fmt, alpha);
+    q.beta = scalar_to_float(q.fmt, beta);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    StreamDevice sd(s);
+    if (sd.rc != kSuccess) return sd.rc;
+    DeviceState* st = nullptr;
+    rc = ensure_device(&st);
+    if (rc != kSuccess) return rc;
+    if (workspace != nullptr && !(g_force_generic.load() & 0x20000000)) {
+        char* ws = align256(workspace);
+        const size_t slack = static_cast<size_t>(ws - static_cast<char*>(workspace));
+        size_t slices = splitk_slices(q, st->num_sms);
+        // the partial products are plain dense products: they need the TMA-fed kernel (16-bit) or
+        // the tensor-memory-operand kernel (fp32); other operand layouts run unsplit
+        const bool fast = q.es == 4 || (!(g_force_generic.load() & 0xff) && tma_ok(q.a, q.es, q.M, q.K, 1) &&
+                                        tma_ok(q.b, q.es, q.N, q.K, 1) &&
+                                        (q.K / static_cast<long long>(slices) * (q.a.k_major ? 1 : q.a.ld) * q.es) % 16 == 0 &&
+                                        (q.K / static_cast<long long>(slices) * (q.b.k_major ? 1 : q.b.ld) * q.es) % 16 == 0);
+        while (slices > 1 && workspace_bytes < slack + slices * q.M * q.N * sizeof(float)) slices /= 2;
+        if (slices > 1 && fast) return launch_splitk(q, slices, ws, s, st);
+    }
+    return launch(q, s, st);
 }
 
 int dlf_b200_gemm_strided_batched(int dtype, int layout, int trans_a, int trans_b, size_t m,

@@ -102,6 +102,10 @@ struct Params {
     int d_tma;   // 0, or the column count (32 / 64) of the TMA store box. 16-bit outputs with
                  // beta == 0 and TMA-compatible strides: the epilogue stages
                  // 32 x 32 blocks in shared memory and writes them with TMA stores
+    int d_f32;   // 16-bit operands, but D is written as fp32 (partial products of a K-split GEMM)
+    long long wait_limit;  // SM clocks a bounded wait may take (see ptx::mbar_wait_bounded)
+    int skip_tile_commit;  // test aid: the UMMA issuer leaves out the commit that hands a finished
+                           // accumulator to the epilogue, so that the epilogue's wait runs out
     int ablate;  // measurement aid (tuning flags >> 16; results are then meaningless):
                  // 1 A producer skips its loads, 2 B loaders skip theirs, 4 producers skip the TMEM
                  // stores, 8 / 16 row-form epilogue skips its body / its stores, 32 the plain
@@ -315,6 +319,7 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
     ptx::tc_fence_after();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&tmem_slot);
     volatile int* abort_p = &abort_flag;
+    const long long wait_limit = p.wait_limit;  // clocks a bounded wait may take before it gives up
 
     if (warp < 4 || (USE_TMA && warp >= 6)) {
         // ------------------------------------------------------------ epilogue
@@ -331,7 +336,7 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
             const uint32_t buf = it & 1u;
             const uint32_t tphase = (it >> 1) & 1u;
             // tcgen05.ld is warp-collective: the warp leaves together or not at all
-            const bool w = ptx::mbar_wait_bounded(ptx::smem_u32(&tfull_bar[buf]), tphase, abort_p);
+            const bool w = ptx::mbar_wait_bounded(ptx::smem_u32(&tfull_bar[buf]), tphase, abort_p, wait_limit);
             if (!__all_sync(0xffffffffu, w)) break;
             ptx::tc_fence_after();
 
@@ -447,6 +452,10 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
             if constexpr (ES == 4) {
                 epilogue_dispatch<OUT_F32>(trow, ncols, optr, colstride * ES, row_ok, alpha, beta_e,
                                            bias, lane, nullptr, false, ex);
+            } else if (p.d_f32) {
+                char* o32 = p.d + (rowbase + static_cast<long long>(n0 + cb) * colstride) * 4;
+                epilogue_dispatch<OUT_F32>(trow, ncols, o32, colstride * 4, row_ok, alpha, beta_e, nullptr, lane,
+                                           nullptr, false, ex);
             } else {
                 const bool pair_ok = pair_store_ok(optr, rowbase, colstride, row_ok, lane);
                 if (p.fmt == FMT_F16)
@@ -492,14 +501,14 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
             for (int t = tile0; ok && t < p.total_tiles; t += tile_step, ++it) {
                 const uint32_t buf = it & 1u;
                 const uint32_t tphase = (it >> 1) & 1u;
-                if (!ptx::mbar_wait_bounded(ptx::smem_u32(&tempty_bar[buf]), tphase ^ 1u, abort_p)) {
+                if (!ptx::mbar_wait_bounded(ptx::smem_u32(&tempty_bar[buf]), tphase ^ 1u, abort_p, wait_limit)) {
                     ok = false;
                     break;
                 }
                 ptx::tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BN;
                 for (int kb = 0; kb < num_kb; ++kb) {
-                    if (!ptx::mbar_wait_bounded(ptx::smem_u32(&full_bar[stage]), phase, abort_p)) {
+                    if (!ptx::mbar_wait_bounded(ptx::smem_u32(&full_bar[stage]), phase, abort_p, wait_limit)) {
                         ok = false;
                         break;
                     }
@@ -531,7 +540,7 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
                         phase ^= 1u;
                     }
                 }
-                if (ok) {
+                if (ok && !p.skip_tile_commit) {
                     if constexpr (PAIR) {  // both CTAs' epilogue warps read their half of the tile
                         ptx::umma_commit_pair(ptx::smem_u32(&tfull_bar[buf]));
                         ptx::umma_commit_pair(ptx::map_to_cta(ptx::smem_u32(&tfull_bar[buf]), 1u));
@@ -555,7 +564,7 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
                 const int bb = p.b.batch_stride ? b : 0;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!ptx::mbar_wait_bounded(ptx::smem_u32(&empty_bar[stage]), phase ^ 1u,
-                                                abort_p)) {
+                                                abort_p, wait_limit)) {
                         ok = false;
                         break;
                     }
@@ -648,7 +657,7 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
             for (int kb = 0; kb < num_kb; ++kb) {
                 // the whole warp leaves together: later __syncwarp()s need every lane
                 const bool w =
-                    ptx::mbar_wait_bounded(ptx::smem_u32(&empty_bar[stage]), phase ^ 1u, abort_p);
+                    ptx::mbar_wait_bounded(ptx::smem_u32(&empty_bar[stage]), phase ^ 1u, abort_p, wait_limit);
                 if (!__all_sync(0xffffffffu, w)) {
                     ok = false;
                     break;

@@ -352,6 +352,7 @@ __global__ void __launch_bounds__(kTsThreads, 1)
     ptx::tc_fence_after();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&tmem_slot);
     volatile int* abort_p = &abort_flag;
+    const long long wait_limit = p.wait_limit;  // clocks a bounded wait may take before it gives up
 
     // Register reallocation between the four warpgroups (the CTA starts with 512 x 128 = the
     // whole register file): loaders and the UMMA issuer need few, the epilogue and the producers
@@ -411,7 +412,7 @@ __global__ void __launch_bounds__(kTsThreads, 1)
             }
             // all K-chunks but the last only feed the running sums
             for (int kb0 = 0; kb0 + kc < num_kb; kb0 += kc) {
-                const bool wc = ptx::mbar_wait_bounded(ptx::smem_u32(&tfull_bar[buf]), tphase, abort_p);
+                const bool wc = ptx::mbar_wait_bounded(ptx::smem_u32(&tfull_bar[buf]), tphase, abort_p, wait_limit);
                 if (!__all_sync(0xffffffffu, wc)) {
                     alive = false;
                     break;
@@ -427,7 +428,7 @@ __global__ void __launch_bounds__(kTsThreads, 1)
             }
             if (!alive) break;
             const float* part = kc < num_kb ? part_row : nullptr;
-            const bool w = ptx::mbar_wait_bounded(ptx::smem_u32(&tfull_bar[buf]), tphase, abort_p);
+            const bool w = ptx::mbar_wait_bounded(ptx::smem_u32(&tfull_bar[buf]), tphase, abort_p, wait_limit);
             if constexpr (ES == 2) {
                 if (tp.d_staged) {
                     // The staged stores below synchronise the four epilogue warps with a named
@@ -893,7 +894,7 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                         }
                     }
                 }
-                const bool w = ptx::mbar_wait_bounded(ptx::smem_u32(&empty_bar[s]), ph ^ 1u, abort_p);
+                const bool w = ptx::mbar_wait_bounded(ptx::smem_u32(&empty_bar[s]), ph ^ 1u, abort_p, wait_limit);
                 if (!__all_sync(0xffffffffu, w)) {
                     ok = false;
                     break;
@@ -944,7 +945,7 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                         decode_tile(p, t, b, m0, n0);
                         const int bb = p.b.batch_stride ? b : 0;
                         for (int kb = 0; kb < num_kb; ++kb) {
-                            if (!ptx::mbar_wait_bounded(ptx::smem_u32(&empty_bar[s]), ph ^ 1u, abort_p)) {
+                            if (!ptx::mbar_wait_bounded(ptx::smem_u32(&empty_bar[s]), ph ^ 1u, abort_p, wait_limit)) {
                                 ok = false;
                                 break;
                             }
@@ -972,7 +973,7 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                 const int ct = threadIdx.x - (kTsLoaderWarp0 + 1) * 32;  // 0..63
                 for (int t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x) {
                     for (int kb = 0; kb < num_kb; ++kb) {
-                        const bool w = ptx::mbar_wait_bounded(ptx::smem_u32(&raw_b[s]), ph, abort_p);
+                        const bool w = ptx::mbar_wait_bounded(ptx::smem_u32(&raw_b[s]), ph, abort_p, wait_limit);
                         if (!__all_sync(0xffffffffu, w)) {
                             ok = false;
                             break;
@@ -1014,7 +1015,7 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                     const unsigned char* src =
                         tp.b_packed + (static_cast<long long>(b) * p.tiles_n + n0 / BN) * num_kb * stage_bytes;
                     for (int kb = 0; kb < num_kb; ++kb) {
-                        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&empty_bar[s]), ph ^ 1u, abort_p)) {
+                        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&empty_bar[s]), ph ^ 1u, abort_p, wait_limit)) {
                             ok = false;
                             break;
                         }
@@ -1039,7 +1040,7 @@ __global__ void __launch_bounds__(kTsThreads, 1)
             const long long b_boff =
                 p.b_offs ? p.b_offs[b] : static_cast<long long>(b) * p.b.batch_stride;
             for (int kb = 0; kb < num_kb; ++kb) {
-                const bool w = ptx::mbar_wait_bounded(ptx::smem_u32(&empty_bar[s]), ph ^ 1u, abort_p);
+                const bool w = ptx::mbar_wait_bounded(ptx::smem_u32(&empty_bar[s]), ph ^ 1u, abort_p, wait_limit);
                 if (!__all_sync(0xffffffffu, w)) {
                     ok = false;
                     break;
@@ -1097,7 +1098,7 @@ __global__ void __launch_bounds__(kTsThreads, 1)
             const int kc = tp.kc_blocks > 0 ? tp.kc_blocks : num_kb;
             for (int t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x) {
                 for (int kb0 = 0; ok && kb0 < num_kb; kb0 += kc) {  // one accumulator per K-chunk
-                    if (!ptx::mbar_wait_bounded(ptx::smem_u32(&tempty_bar[buf]), tphase ^ 1u, abort_p)) {
+                    if (!ptx::mbar_wait_bounded(ptx::smem_u32(&tempty_bar[buf]), tphase ^ 1u, abort_p, wait_limit)) {
                         ok = false;
                         break;
                     }
@@ -1105,8 +1106,8 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                     const uint32_t d_tmem = tmem_base + buf * BN;
                     const int kb1 = min(kb0 + kc, num_kb);
                     for (int kb = kb0; kb < kb1; ++kb) {
-                        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&full_a[s]), ph, abort_p) ||
-                            !ptx::mbar_wait_bounded(ptx::smem_u32(&full_b[s]), ph, abort_p)) {
+                        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&full_a[s]), ph, abort_p, wait_limit) ||
+                            !ptx::mbar_wait_bounded(ptx::smem_u32(&full_b[s]), ph, abort_p, wait_limit)) {
                             ok = false;
                             break;
                         }
@@ -1132,7 +1133,7 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                             ph ^= 1u;
                         }
                     }
-                    if (ok) ptx::umma_commit(ptx::smem_u32(&tfull_bar[buf]));
+                    if (ok && !p.skip_tile_commit) ptx::umma_commit(ptx::smem_u32(&tfull_bar[buf]));
                     if (++buf == static_cast<uint32_t>(nbuf)) {
                         buf = 0;
                         tphase ^= 1u;

@@ -71,6 +71,25 @@ __global__ void l3_scale_kernel(T* __restrict__ b, long long ldb, int m, int n, 
     }
 }
 
+// K-split GEMM: D[i + j*ldd] = alpha * sum_s part[s][i + j*M] + beta * D[i + j*ldd] over the M x N
+// window (i contiguous); `part` holds `slices` fp32 products of M*N elements each.
+template <typename T>
+__global__ void splitk_reduce_kernel(T* __restrict__ d, long long ldd, const float* __restrict__ part, int M, int N,
+                                     int slices, float alpha, float beta) {
+    const long long total = static_cast<long long>(M) * N;
+    for (long long id = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; id < total;
+         id += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int j = static_cast<int>(id / M);
+        const int i = static_cast<int>(id - static_cast<long long>(j) * M);
+        float acc = 0.0f;
+        for (int s = 0; s < slices; ++s) acc += part[s * total + id];
+        float v = alpha * acc;
+        T* o = d + j * ldd + i;
+        if (beta != 0.0f) v += beta * l3_load(o);
+        *o = l3_make<T>(v);
+    }
+}
+
 constexpr int kTrsmBlock = 64;     // order of a diagonal block
 constexpr int kTrsmThreads = 128;  // independent systems per CTA
 

@@ -60,17 +60,18 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
 }
 
 // Bounded wait. Returns false when the wait gave up: either another role of this CTA
-// raised *abort_flag, or ~2^32 SM clocks passed (about two seconds), in which case this
-// thread raises the flag itself. Callers leave their role loop on false.
+// raised *abort_flag, or `limit` SM clocks passed (2^32, about two seconds, unless the launch
+// says otherwise), in which case this thread raises the flag itself. Callers leave their role
+// loop on false.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
-                                                  volatile int* abort_flag) {
+                                                  volatile int* abort_flag, long long limit) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (uint32_t it = 1;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((it & 15u) == 0u) {
             if (*abort_flag) return false;
-            if (clock64() - t0 > (1ll << 32)) {
+            if (clock64() - t0 > limit) {
                 *abort_flag = 1;
                 return false;
             }

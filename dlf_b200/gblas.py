@@ -110,6 +110,23 @@ def _stream(queue):
     return s, ctypes.c_void_p(s.cuda_stream)
 
 
+_GEMM_WORKSPACES = {}
+
+
+def _gemm_workspace(device, stream, nbytes):
+    """One scratch buffer per (device, stream), grown on demand; calls on a stream are ordered, so
+    they can share it."""
+    key = (device.index, stream.cuda_stream)
+    buf = _GEMM_WORKSPACES.get(key)
+    if buf is None or buf.numel() < nbytes:
+        if buf is not None:
+            buf.record_stream(stream)
+        buf = torch.empty(int(nbytes), dtype=torch.uint8, device=device)
+        buf.record_stream(stream)
+        _GEMM_WORKSPACES[key] = buf
+    return buf
+
+
 def _check(rc):
     if rc != 0:
         raise BLASError(rc)
@@ -159,12 +176,18 @@ def gemm(layout, a_transpose, b_transpose, m, n, k, alpha, a_buffer, a_offset, a
               [b_offset], b_ld, c_buffer, [c_offset], c_ld)
     al, be = _scalar(alpha, c_buffer.dtype), _scalar(beta, c_buffer.dtype)
     s, sp = _stream(queue)
+    # scratch for a K-split of products with few output tiles (the reference's Xgemm takes its
+    # temporaries from the context's pool, routines/level3/xgemm.cpp:107-223); 0 bytes = not useful
+    need = lib().dlf_b200_gemm_workspace_bytes(int(prec), m, n, k)
+    ws = _gemm_workspace(c_buffer.device, s, need) if need else None
     if event is not None:
         event.start.record(s)
-    rc = lib().dlf_b200_gemm(int(prec), int(layout), int(a_transpose), int(b_transpose), m, n, k,
-                             ctypes.byref(al), _ptr(a_buffer, a_offset), a_ld,
-                             _ptr(b_buffer, b_offset), b_ld, ctypes.byref(be),
-                             _ptr(c_buffer, c_offset), c_ld, sp)
+    rc = lib().dlf_b200_gemm_ex(int(prec), int(layout), int(a_transpose), int(b_transpose), m, n, k,
+                                ctypes.byref(al), _ptr(a_buffer, a_offset), a_ld,
+                                _ptr(b_buffer, b_offset), b_ld, ctypes.byref(be),
+                                _ptr(c_buffer, c_offset), c_ld,
+                                ctypes.c_void_p(ws.data_ptr()) if ws is not None else None,
+                                ws.numel() if ws is not None else 0, sp)
     if event is not None:
         event.end.record(s)
     _check(rc)

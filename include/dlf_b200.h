@@ -52,6 +52,19 @@ int dlf_b200_gemm(int dtype, int layout, int trans_a, int trans_b, size_t m, siz
                   const void* alpha, const void* a, size_t a_ld, const void* b, size_t b_ld,
                   const void* beta, void* c, size_t c_ld, void* stream);
 
+/* dlf_b200_gemm with optional scratch (may be NULL: then exactly dlf_b200_gemm). With at least
+ * dlf_b200_gemm_workspace_bytes(...) bytes of caller-owned device memory, products that have few
+ * output tiles and a long K (a fully connected layer 256 x 1000 x 2048, a 1024^3 product) are cut
+ * along K into slices that run side by side, followed by a reduction kernel; other products run
+ * as before. The reference takes such temporaries from its context's pool
+ * (Xgemm's temp buffer, gpgpu/src/routines/level3/xgemm.cpp:107-223). Results of a split product
+ * differ from the unsplit one by fp32 rounding of the slice sums only. */
+int dlf_b200_gemm_ex(int dtype, int layout, int trans_a, int trans_b, size_t m, size_t n, size_t k,
+                     const void* alpha, const void* a, size_t a_ld, const void* b, size_t b_ld,
+                     const void* beta, void* c, size_t c_ld, void* workspace, size_t workspace_bytes,
+                     void* stream);
+size_t dlf_b200_gemm_workspace_bytes(int dtype, size_t m, size_t n, size_t k);
+
 /* Same product for batch_count matrices spaced by fixed strides; a stride of 0 shares one
  * operand between all batches. Replaces gpgpu::blas::gemmStridedBatched<T>
  * (gblas.h:673-683; gblas.cpp:3090-3141; routines/levelx/xgemmstridedbatched.cpp:53-95). */
@@ -211,7 +224,10 @@ int dlf_b200_device_status(int* device_status);
  * a convolution. Bits 16 and up are measurement aids: most switch a part of a kernel off to time the
  * rest (results are then meaningless); 0x100 << 16 (pooling always through the generic
  * one-thread-per-output kernel) and 0x4000 << 16 (no programmatic dependent launch after the
- * filter-packing grid) keep results valid. */
+ * filter-packing grid) keep results valid. 0x10000000 is a test aid for the device-side time-out
+ * path: a launch that consists of one tile leaves out the commit that hands its accumulator to the
+ * epilogue and waits at most 2^21 clocks (about a millisecond): the call returns, the output is
+ * not written and dlf_b200_device_status() reports bit 0 once. */
 void dlf_b200_set_tuning(int force_bn, int force_generic_loader);
 
 /* Counts kernel launches made by this library in this process (all threads). */

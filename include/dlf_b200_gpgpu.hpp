@@ -271,12 +271,16 @@ void gemm(const Layout layout, const Transpose a_transpose, const Transpose b_tr
     detail::test_matrix(d.a_one, d.a_two, a_buffer, a_offset, a_ld, StatusCode::kInvalidLeadDimA, StatusCode::kInsufficientMemoryA);
     detail::test_matrix(d.b_one, d.b_two, b_buffer, b_offset, b_ld, StatusCode::kInvalidLeadDimB, StatusCode::kInsufficientMemoryB);
     detail::test_matrix(d.c_one, d.c_two, c_buffer, c_offset, c_ld, StatusCode::kInvalidLeadDimC, StatusCode::kInsufficientMemoryC);
+    // scratch for a K-split of products with few output tiles, from the temporary-buffer pool as
+    // Xgemm takes its temporaries (gpgpu/src/routines/level3/xgemm.cpp:107-223); 0 bytes = no use
+    TemporaryBuffer<unsigned char> work(dlf_b200_gemm_workspace_bytes(PrecisionOf<T>::value, m, n, k));
     detail::EventScope scope(queue, event);
-    detail::raise(dlf_b200_gemm(PrecisionOf<T>::value, static_cast<int>(layout), static_cast<int>(a_transpose),
-                                static_cast<int>(b_transpose), m, n, k, &alpha,
-                                a_buffer.unwrap() + a_offset, a_ld, b_buffer.unwrap() + b_offset, b_ld, &beta,
-                                c_buffer.unwrap() + c_offset, c_ld, queue.unwrap()),
-                  "dlf_b200_gemm");
+    detail::raise(dlf_b200_gemm_ex(PrecisionOf<T>::value, static_cast<int>(layout), static_cast<int>(a_transpose),
+                                   static_cast<int>(b_transpose), m, n, k, &alpha,
+                                   a_buffer.unwrap() + a_offset, a_ld, b_buffer.unwrap() + b_offset, b_ld, &beta,
+                                   c_buffer.unwrap() + c_offset, c_ld, work.size() ? work.unwrap() : nullptr,
+                                   work.data_size(), queue.unwrap()),
+                  "dlf_b200_gemm_ex");
 }
 
 template <typename T>

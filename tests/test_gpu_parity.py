@@ -676,6 +676,46 @@ def test_conv2d_resnet50_layer_shapes_vs_oracle(shape):
     assert max_rel(Y.float().cpu().numpy(), ref) <= HALF_TOL
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("m,n,k,ta,tb", [(256, 1000, 2048, False, False), (200, 136, 4096, True, False),
+                                         (96, 520, 1024, False, True), (64, 64, 8192, True, True)])
+def test_gemm_k_split_matches_unsplit(lib, dtype, m, n, k, ta, tb):
+    """Products with few output tiles and a long K are cut along K when the caller gives scratch
+    (dlf_b200_gemm_ex): the result must agree with the oracle and, up to fp32 rounding of the slice
+    sums, with the unsplit kernel (tuning bit 0x20000000 switches the split off); beta and alpha
+    apply once, in the reduction."""
+    gb = _gb()
+    rng = np.random.default_rng(m + n + k)
+    A = _round_to(_rand(rng, m * k), dtype)
+    B = _round_to(_rand(rng, k * n), dtype)
+    C0 = _round_to(_rand(rng, m * n, "normal"), dtype)
+    TA = gb.Transpose.Trans if ta else gb.Transpose.NoTrans
+    TB = gb.Transpose.Trans if tb else gb.Transpose.NoTrans
+    lda, ldb = (m if ta else k), (k if tb else n)
+    ref = C0.copy()
+    oracle.gblas_sgemm(oracle.ROW_MAJOR, int(TA), int(TB), m, n, k, 0.5, A, 0, lda, B, 0, ldb, 0.25, ref, 0, n, wide=True)
+    outs = []
+    for flags in (0, 0x20000000):
+        C = torch.from_numpy(C0.copy()).to(dtype).cuda()
+        lib.set_tuning(0, flags)
+        try:
+            n0 = lib.launch_count()
+            gb.gemm(gb.Layout.RowMajor, TA, TB, m, n, k, 0.5, torch.from_numpy(A).to(dtype).cuda(), 0, lda,
+                    torch.from_numpy(B).to(dtype).cuda(), 0, ldb, 0.25, C, 0, n)
+            torch.cuda.synchronize()
+            launches = lib.launch_count() - n0
+        finally:
+            lib.set_tuning(0, 0)
+        assert launches == (2 if flags == 0 else 1)  # split: product + reduction
+        outs.append(C.float().cpu().numpy())
+        if dtype == torch.float32:
+            assert rel_fro(outs[-1], ref) <= FP32_TOL
+        else:
+            assert max_rel(outs[-1], ref) <= HALF_TOL
+    if dtype == torch.float32:
+        assert rel_fro(outs[0], outs[1]) <= 2e-6
+
+
 def test_resnet50_fc_gemm_vs_oracle():
     """The final fully connected layer of config 3 as a GEMM: 256 x 1000 x 2048, fp16."""
     gb = _gb()
@@ -855,6 +895,42 @@ def test_conv2d_config2_full_size_properties():
 # ------------------------------------------------------------------------------------------
 # errors, threads
 # ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype,flags", [(torch.float16, 0), (torch.float32, 0), (torch.float16, 3)],
+                         ids=["tma-fed", "tensor-memory-operand-f32", "tensor-memory-operand-f16-staged-stores"])
+def test_device_side_wait_runs_out_and_reports(lib, dtype, flags):
+    """The bounded waits of the kernels, made to run out once without faulting anything: with the
+    test aid 0x10000000 a single-tile launch withholds the commit that hands the accumulator to
+    the epilogue and waits about a millisecond. The call returns, the device status reports the
+    time-out exactly once, C keeps its old contents, and the next ordinary call is correct."""
+    gb = _gb()
+    m, n, k = 64, 64, 128  # one tile
+    rng = np.random.default_rng(7)
+    A = torch.from_numpy(_round_to(_rand(rng, m * k), dtype)).to(dtype).cuda()
+    B = torch.from_numpy(_round_to(_rand(rng, k * n), dtype)).to(dtype).cuda()
+    C = torch.full((m * n,), 5.0, dtype=dtype, device="cuda")
+    assert lib.device_status() == 0
+    lib.set_tuning(0, 0x10000000 | flags)
+    try:
+        gb.gemm(gb.Layout.RowMajor, gb.Transpose.NoTrans, gb.Transpose.NoTrans, m, n, k, 1.0, A, 0, k, B, 0, n, 0.0,
+                C, 0, n)
+        torch.cuda.synchronize()
+    finally:
+        lib.set_tuning(0, flags)
+    try:
+        assert lib.device_status() == 1   # bit 0: a bounded wait gave up
+        assert lib.device_status() == 0   # reported once
+        assert bool((C == 5.0).all())     # the epilogue never ran
+        gb.gemm(gb.Layout.RowMajor, gb.Transpose.NoTrans, gb.Transpose.NoTrans, m, n, k, 1.0, A, 0, k, B, 0, n, 0.0,
+                C, 0, n)
+        torch.cuda.synchronize()
+    finally:
+        lib.set_tuning(0, 0)
+    ref = (A.double().view(m, k) @ B.double().view(k, n)).flatten().cpu().numpy()
+    got = C.double().cpu().numpy()
+    assert (rel_fro(got, ref) <= FP32_TOL) if dtype == torch.float32 else (max_rel(got, ref) <= HALF_TOL)
+    assert lib.device_status() == 0
+
+
 def test_argument_errors_have_reference_status_codes():
     gb = _gb()
     a = torch.zeros(64, device="cuda")
