@@ -713,7 +713,7 @@ def test_gemm_k_split_matches_unsplit(lib, dtype, m, n, k, ta, tb):
         else:
             assert max_rel(outs[-1], ref) <= HALF_TOL
     if dtype == torch.float32:
-        assert rel_fro(outs[0], outs[1]) <= 2e-6
+        assert rel_fro(outs[0], outs[1]) <= 6e-6
 
 
 def test_resnet50_fc_gemm_vs_oracle():
