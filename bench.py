@@ -660,6 +660,8 @@ def main():
     ap.add_argument("--batch", type=int, default=None, help="images per GPU for conv_c2 (profiling: a small case)")
     ap.add_argument("--shape", default="64,56,64,3,1,1", help="--workload conv: Cin,H,Cout,k,stride,pad")
     ap.add_argument("--dtype", default="f16", help="--workload conv: f16, bf16 or f32")
+    ap.add_argument("--tuning", type=lambda x: int(x, 0), default=0,
+                    help="experiments: second argument of dlf_b200_set_tuning for the whole run")
     ap.add_argument("--overlap-gather", action="store_true",
                     help="row-sharded GEMM: all-gather finished panels while the next panel is computed")
     ap.add_argument("--kernel-only", action="store_true",
@@ -676,6 +678,8 @@ def main():
 
     import dlf_b200
     dlf_b200.lib()  # fail loudly when the CUDA library is missing
+    if args.tuning:
+        dlf_b200.set_tuning(0, args.tuning)
     rank, world, local = dist_setup(args.gpus)
     device = torch.device("cuda", local)
     peaks = measured_peaks()
@@ -686,6 +690,9 @@ def main():
         "sgemm_1024": lambda: GemmWorkload("sgemm_f32_1024", "f32", 1024, 1024, 1024, dist="uniform"),
         "sgemm_16384": lambda: GemmWorkload("sgemm_f32_16384_tn", "f32", 16384, 16384, 16384, ta=True, alpha=0.5,
                                             beta=0.5, dist="uniform"),
+        # config 5's operand layout and K at a size that an ncu capture can hold (profiling aid)
+        "sgemm_4096_k16384": lambda: GemmWorkload("sgemm_f32_4096x4096x16384_tn", "f32", 4096, 4096, 16384, ta=True,
+                                                  alpha=0.5, beta=0.5, dist="uniform"),
         "batched_c4_a": lambda: GemmWorkload("bgemm_f16_b1024_512x512x64", "f16", 512, 512, 64, batch=1024, alpha=0.125),
         "batched_c4_b": lambda: GemmWorkload("bgemm_f16_b1024_512x64x512", "f16", 512, 64, 512, batch=1024, alpha=0.125),
         "fc_c3": lambda: GemmWorkload("resnet50_fc_f16_256x1000x2048", "f16", 256, 1000, 2048),

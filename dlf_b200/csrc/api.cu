@@ -114,6 +114,39 @@ struct StreamDevice {
     StreamDevice& operator=(const StreamDevice&) = delete;
 };
 
+// The tensor-memory-operand kernel exists once per element size and operand kind (see
+// contraction_ts.cuh): attributes are set on all of them, the largest static shared-memory use is
+// what the launch arithmetic counts with.
+template <int ES>
+int setup_ts_kernels(int* static_smem) {
+    cudaFuncAttributes fa;
+    int worst = 0;
+#define DLF_TS_SETUP(AK)                                                                              \
+    CUDA_TRY(cudaFuncGetAttributes(&fa, contraction_ts_kernel<ES, AK>));                              \
+    worst = std::max(worst, static_cast<int>(fa.sharedSizeBytes));
+    DLF_TS_SETUP(A_DENSE_MN)
+    DLF_TS_SETUP(A_IM2COL)
+    DLF_TS_SETUP(A_ROWCONV)
+#undef DLF_TS_SETUP
+#define DLF_TS_ATTR(AK)                                                                               \
+    CUDA_TRY(cudaFuncSetAttribute(contraction_ts_kernel<ES, AK>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                  kSmemPerBlockOptin - worst));
+    DLF_TS_ATTR(A_DENSE_MN)
+    DLF_TS_ATTR(A_IM2COL)
+    DLF_TS_ATTR(A_ROWCONV)
+#undef DLF_TS_ATTR
+    *static_smem = worst;
+    return kSuccess;
+}
+
+template <int ES>
+cudaError_t launch_ts_kernel(const cudaLaunchConfig_t* cfg, const TsParams& tp, const CUtensorMap& tm_b,
+                             const CUtensorMap& tm_d) {
+    if (tp.a_kind == A_ROWCONV) return cudaLaunchKernelEx(cfg, contraction_ts_kernel<ES, A_ROWCONV>, tp, tm_b, tm_d);
+    if (tp.a_kind == A_IM2COL) return cudaLaunchKernelEx(cfg, contraction_ts_kernel<ES, A_IM2COL>, tp, tm_b, tm_d);
+    return cudaLaunchKernelEx(cfg, contraction_ts_kernel<ES, A_DENSE_MN>, tp, tm_b, tm_d);
+}
+
 int ensure_device(DeviceState** out) {
     int dev = 0;
     CUDA_TRY(cudaGetDevice(&dev));
@@ -141,16 +174,12 @@ int ensure_device(DeviceState** out) {
         CUDA_TRY(cudaFuncSetAttribute(contraction_kernel<4, false>,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       kSmemPerBlockOptin - st.static_smem_gen4));
-        CUDA_TRY(cudaFuncGetAttributes(&fa, contraction_ts_kernel<2>));
-        st.static_smem_ts2 = static_cast<int>(fa.sharedSizeBytes);
-        CUDA_TRY(cudaFuncGetAttributes(&fa, contraction_ts_kernel<4>));
-        st.static_smem_ts4 = static_cast<int>(fa.sharedSizeBytes);
-        CUDA_TRY(cudaFuncSetAttribute(contraction_ts_kernel<2>,
-                                      cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      kSmemPerBlockOptin - st.static_smem_ts2));
-        CUDA_TRY(cudaFuncSetAttribute(contraction_ts_kernel<4>,
-                                      cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      kSmemPerBlockOptin - st.static_smem_ts4));
+        {
+            int rc2 = setup_ts_kernels<2>(&st.static_smem_ts2);
+            if (rc2 != kSuccess) return rc2;
+            rc2 = setup_ts_kernels<4>(&st.static_smem_ts4);
+            if (rc2 != kSuccess) return rc2;
+        }
         {
             auto pair_kernel = contraction_kernel<2, true, true>;
             CUDA_TRY(cudaFuncGetAttributes(&fa, pair_kernel));
@@ -400,8 +429,7 @@ int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
     // tiles to 192 columns, which is also the widest tile that leaves room for two accumulators.
     const long long num_kb_all = (q.K + BK - 1) / BK;
     const int kc_blocks = (q.es == 4 && num_kb_all > 16 && !(g_force_generic.load() & 0x1000)) ? 8 : 0;
-    const int kc_max_bn = (g_force_generic.load() >> 16) & 0x200 ? 128 : 192;  // (0x200: the former limit, for comparison)
-    int bn = choose_bn_ts(q, st.num_sms, kc_blocks ? kc_max_bn : 256, a_cols, num_kb_all);
+    int bn = choose_bn_ts(q, st.num_sms, kc_blocks ? 192 : 256, a_cols, num_kb_all);
     const int forced = g_force_bn.load();
     if (forced >= 64 && forced <= (kc_blocks ? 192 : 256) && forced % 32 == 0) bn = forced;
     // an MN-major B tile is made of whole groups of BK columns (the UMMA reads all k-rows of the
@@ -439,19 +467,27 @@ int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
     if (kc_blocks && bn > 192) return kUnexpectedError;
     // 16-bit outputs for which nothing of D is read leave through staged 16-byte stores
     // (epilogue.cuh); a residual is read by the staging threads themselves
-    const bool d_staged = q.es == 2 && q.beta == 0.0f && q.betas == nullptr && !((g_force_generic.load() >> 16) & 64);
+    // Measured: the staged 16-byte stores cost the four epilogue warps more instructions and
+    // barrier waits than they save (the epilogue is bound by instruction latency, not by the
+    // width of its stores), so they are only used on request (measurement bit 64 << 16) and by
+    // the row form with image-aligned tiles, whose blocks leave through TMA stores.
+    const bool d_staged = q.es == 2 && q.beta == 0.0f && q.betas == nullptr &&
+                          (q.rc_tpi != 0 || ((g_force_generic.load() >> 16) & 64));
     // row form with image-aligned tiles: two blocks of [channels of the tile][positions of the tile]
     const int rc_tma_buf = q.rc_tpi ? (q.rc_cpt * 4 * q.rc_T * 2 + 127) / 128 * 128 : 0;
     const int out_stage_bytes = !d_staged ? 0 : (q.rc_tpi ? 2 * rc_tma_buf : kStageBytes) + 128;  // + alignment slack
     if (q.rc_tpi && !d_staged) return kUnexpectedError;
     // the k table is padded to a multiple of 1024 in the layout below: count it that way here too
-    int stages = (kSmemPerBlockOptin - static_smem - 1024 - ((ktable_bytes + 1023) / 1024 * 1024) - sums_bytes - out_stage_bytes) / stage_bytes;
-    const int tmem_stages = (512 - acc_bufs * bn) / a_cols;
-    if (stages > tmem_stages) stages = tmem_stages;
+    // B stages in shared memory and A slots in tensor memory are separate rings (0x200 << 16: the
+    // former single ring, both as deep as the shallower one)
+    int b_stages = (kSmemPerBlockOptin - static_smem - 1024 - ((ktable_bytes + 1023) / 1024 * 1024) - sums_bytes - out_stage_bytes) / stage_bytes;
+    int stages = (512 - acc_bufs * bn) / a_cols;
+    if (b_stages > kMaxStages) b_stages = kMaxStages;
     if (stages > kMaxStages) stages = kMaxStages;
-    if (stages < 2) return kUnexpectedError;
+    if ((g_force_generic.load() >> 16) & 0x200) b_stages = stages = std::min(b_stages, stages);
+    if (stages < 2 || b_stages < 2) return kUnexpectedError;
     // dynamic segment: [k table][pad to 1024][B stages][partial sums]
-    const int sums_off = ((ktable_bytes + 1023) / 1024 * 1024) + 1024 + stages * stage_bytes;
+    const int sums_off = ((ktable_bytes + 1023) / 1024 * 1024) + 1024 + b_stages * stage_bytes;
     size_t dyn_smem = static_cast<size_t>(sums_off) + sums_bytes + out_stage_bytes;
     // more than half of the SM's shared memory: never two CTAs (and two 512-column TMEM
     // allocations) on one SM
@@ -505,10 +541,12 @@ int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
     tp.rc_tpi = q.rc_tpi;
     tp.rc_tma = q.rc_tpi ? 1 : 0;
     tp.rc_tma_buf = rc_tma_buf;
+    tp.b_stages = b_stages;
     tp.acc_bufs = acc_bufs;
     tp.ktable_bytes = ktable_bytes;
 
     tp.b_packed = nullptr;
+    tp.b_tma = 0;
     if (q.pack_ws != nullptr && (q.a.im2col || q.rc_kw) && p.b.k_major && !(g_force_generic.load() & 0x8000)) {
         // lay the filter bank out as stage images first (same stream), then stream them with bulk copies
         unsigned char* ws = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(q.pack_ws) + 127) & ~uintptr_t(127));
@@ -528,7 +566,6 @@ int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
 
     CUtensorMap tm_b;
     std::memset(&tm_b, 0, sizeof(tm_b));
-    tp.b_tma = 0;
     if (q.es == 4 && !q.a.im2col && !q.rc_kw && q.b_offs == nullptr && !(g_force_generic.load() & 0x800) &&
         tma_ok(q.b, q.es, q.N, q.K, q.batch)) {
         if (encode_map(st, &tm_b, q.b, q.es, q.N, q.K, q.batch, bn) == kSuccess) tp.b_tma = 1;
@@ -564,13 +601,13 @@ int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
     cfg.attrs = &attr;
     cfg.numAttrs = (tp.b_packed != nullptr && !(g_force_generic.load() & 0x40000000)) ? 1 : 0;
     if (std::getenv("DLF_B200_DEBUG"))
-        std::fprintf(stderr, "dlf_b200: ts launch es=%d bn=%d stages=%d acc_bufs=%d grid=%u dyn_smem=%zu ktable=%d sums=%d packed=%d pending=%s\n",
+        std::fprintf(stderr, "dlf_b200: ts launch es=%d bn=%d a_slots=%d acc_bufs=%d grid=%u dyn_smem=%zu ktable=%d sums=%d packed=%d pending=%s\n",
                      q.es, bn, stages, acc_bufs, grid, dyn_smem, ktable_bytes, sums_bytes, tp.b_packed != nullptr,
                      cudaGetErrorString(cudaPeekAtLastError()));
     if (q.es == 2)
-        CUDA_TRY(cudaLaunchKernelEx(&cfg, contraction_ts_kernel<2>, tp, tm_b, tm_d));
+        CUDA_TRY(launch_ts_kernel<2>(&cfg, tp, tm_b, tm_d));
     else
-        CUDA_TRY(cudaLaunchKernelEx(&cfg, contraction_ts_kernel<4>, tp, tm_b, tm_d));
+        CUDA_TRY(launch_ts_kernel<4>(&cfg, tp, tm_b, tm_d));
     g_launches.fetch_add(1);
     CUDA_TRY(cudaGetLastError());
     return kSuccess;
@@ -779,20 +816,18 @@ int noalloc_device(NoAllocDevice** out) {
         st.static_smem_gen2 = static_cast<int>(fa.sharedSizeBytes);
         CUDA_TRY(cudaFuncGetAttributes(&fa, contraction_kernel<4, false>));
         st.static_smem_gen4 = static_cast<int>(fa.sharedSizeBytes);
-        CUDA_TRY(cudaFuncGetAttributes(&fa, contraction_ts_kernel<2>));
-        st.static_smem_ts2 = static_cast<int>(fa.sharedSizeBytes);
-        CUDA_TRY(cudaFuncGetAttributes(&fa, contraction_ts_kernel<4>));
-        st.static_smem_ts4 = static_cast<int>(fa.sharedSizeBytes);
+        {
+            int rc2 = setup_ts_kernels<2>(&st.static_smem_ts2);
+            if (rc2 != kSuccess) return rc2;
+            rc2 = setup_ts_kernels<4>(&st.static_smem_ts4);
+            if (rc2 != kSuccess) return rc2;
+        }
         CUDA_TRY(cudaFuncSetAttribute(contraction_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       kSmemPerBlockOptin - st.static_smem_tma));
         CUDA_TRY(cudaFuncSetAttribute(contraction_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       kSmemPerBlockOptin - st.static_smem_gen2));
         CUDA_TRY(cudaFuncSetAttribute(contraction_kernel<4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       kSmemPerBlockOptin - st.static_smem_gen4));
-        CUDA_TRY(cudaFuncSetAttribute(contraction_ts_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      kSmemPerBlockOptin - st.static_smem_ts2));
-        CUDA_TRY(cudaFuncSetAttribute(contraction_ts_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      kSmemPerBlockOptin - st.static_smem_ts4));
         void* fn = nullptr;
         cudaDriverEntryPointQueryResult qres;
         CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
@@ -1345,9 +1380,13 @@ int dlf_b200_conv2d_fused(int dtype, size_t batches, size_t channels, size_t hei
         {
             const int t_even = r.rc_T & ~1;
             const long long ohw = static_cast<long long>(output_h) * wv;
-            if (q.es == 2 && wv == static_cast<long long>(output_w) && (P * 2) % 16 == 0 && t_even >= 16 &&
+            // (measured: a gain for the strided row form - the 7x7 stride-2 stem, 1183 -> 1102 us -
+            // and a small loss for stride 1, where the partly filled last tile of every image
+            // costs more than the stores save; measurement bit 128 << 16 forces it on for stride 1)
+            const bool want = sw > 1 || ((g_force_generic.load() >> 16) & 128);
+            if (want && q.es == 2 && wv == static_cast<long long>(output_w) && (P * 2) % 16 == 0 && t_even >= 16 &&
                 ohw >= 4ll * 4 * t_even && (group == 1 || ng % 16 == 0) &&
-                (reinterpret_cast<uintptr_t>(y) & 15u) == 0 && !((g_force_generic.load() >> 16) & (64 | 128))) {
+                (reinterpret_cast<uintptr_t>(y) & 15u) == 0) {
                 r.rc_T = t_even;
                 r.rc_tpi = static_cast<int>((ohw + 4 * t_even - 1) / (4 * t_even));
             }

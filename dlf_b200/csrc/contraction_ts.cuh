@@ -83,7 +83,10 @@ struct TsParams {
     // (float[BN][128]); 0 = one chunk (see drain_chunk in epilogue.cuh)
     int kc_blocks, sums_off;
     // fp32 dense products whose B operand satisfies the TMA rules: TMA delivers the raw fp32 tiles
-    // (which double as the hi image), the loader warps derive the lo image from them
+    // (which double as the hi image), the loader warps derive the lo image from them. (The same
+    // scheme for the packed filter bank of a convolution - raw images only, half the bytes from
+    // L2 - was measured slower, 123 vs 90 us on the 64-channel 3x3 layer: with two operand stages
+    // the extra hop through the converter warps is not hidden.)
     int b_tma;
     // A_IM2COL with a 1x1 filter and no padding (any stride): addresses are affine in k
     int a_pointwise;
@@ -95,6 +98,7 @@ struct TsParams {
     // tile then is one contiguous range of one image's pixels for every channel, and 16-bit
     // results leave as TMA stores (rc_tma; two blocks of rc_tma_buf bytes at stage_off).
     int rc_tpi, rc_tma, rc_tma_buf;
+    int b_stages;  // depth of the B ring in shared memory (Params::stages is the depth of the A ring)
 };
 
 // First position of row-form tile `tm`, and (image-aligned tiles) the image it belongs to.
@@ -252,11 +256,16 @@ __global__ void pack_weights_kernel(const TsParams tp, unsigned char* out, long 
     }
 }
 
-template <int ES>
+// AK: the kind of the A operand the instantiation serves - A_ROWCONV, A_IM2COL, or A_DENSE_MN for
+// both dense kinds (told apart at run time). One instantiation per kind keeps the code of the
+// other kinds' gathers and epilogues out of the kernel: fewer registers and a smaller footprint
+// in the instruction cache for every role.
+template <int ES, int AK>
 __global__ void __launch_bounds__(kTsThreads, 1)
     contraction_ts_kernel(const __grid_constant__ TsParams tp, const __grid_constant__ CUtensorMap tmB,
                           const __grid_constant__ CUtensorMap tmD) {
     const Params& p = tp.base;
+    const int a_kind = (AK == A_ROWCONV || AK == A_IM2COL) ? AK : tp.a_kind;
     constexpr int BK = 128 / ES;             // k per stage: 32 (fp32) or 64 (16-bit)
     constexpr int CPE = 16 / ES;
     constexpr int UMMA_K = 32 / ES;
@@ -269,7 +278,8 @@ __global__ void __launch_bounds__(kTsThreads, 1)
     __shared__ __align__(8) uint64_t full_a[kMaxStages];
     __shared__ __align__(8) uint64_t full_b[kMaxStages];
     __shared__ __align__(8) uint64_t raw_b[kMaxStages];  // b_tma: raw tile landed
-    __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
+    __shared__ __align__(8) uint64_t empty_a[kMaxStages];  // A slot (tensor memory) consumed
+    __shared__ __align__(8) uint64_t empty_b[kMaxStages];  // B stage (shared memory) consumed
     __shared__ __align__(8) uint64_t tfull_bar[2];
     __shared__ __align__(8) uint64_t tempty_bar[2];
     __shared__ uint32_t tmem_slot;
@@ -280,7 +290,11 @@ __global__ void __launch_bounds__(kTsThreads, 1)
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int BN = p.BN;
-    const int S = p.stages;
+    // The A slots live in tensor memory and the B stages in shared memory: the two rings have their
+    // own depths (a wide fp32 tile leaves room for only two A slots but for four B stages, whose
+    // bulk copies take longer than the tensor core needs for a k-block).
+    const int SA = p.stages;
+    const int SB = tp.b_stages;
     const int nbuf = tp.acc_bufs;
     const uint32_t b_tile = static_cast<uint32_t>(BN) * 128u;
     const uint32_t stage_bytes = b_tile * (ES == 4 ? 2u : 1u);
@@ -292,11 +306,12 @@ __global__ void __launch_bounds__(kTsThreads, 1)
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
-        for (int s = 0; s < S; ++s) {
+        for (int s = 0; s < kMaxStages; ++s) {
             ptx::mbar_init(ptx::smem_u32(&full_a[s]), 128u);
             ptx::mbar_init(ptx::smem_u32(&full_b[s]), tp.b_packed ? 1u : (tp.b_tma ? 64u : kTsLoaderThreads));
             ptx::mbar_init(ptx::smem_u32(&raw_b[s]), 1u);
-            ptx::mbar_init(ptx::smem_u32(&empty_bar[s]), 1u);
+            ptx::mbar_init(ptx::smem_u32(&empty_a[s]), 1u);
+            ptx::mbar_init(ptx::smem_u32(&empty_b[s]), 1u);
         }
         for (int i = 0; i < 2; ++i) {
             ptx::mbar_init(ptx::smem_u32(&tfull_bar[i]), 1u);
@@ -304,7 +319,7 @@ __global__ void __launch_bounds__(kTsThreads, 1)
         }
         ptx::fence_mbar_init();
     }
-    if (tp.a_kind == A_ROWCONV) {
+    if (a_kind == A_ROWCONV) {
         // k' = (kh*sw + r)*C + c -> (offset of the input row + column phase r, kh*dh, r); the
         // column is the thread's own (times sw). Channel-fastest, so that with sw = 1 a k-block
         // usually lies inside one kh: one validity test and a constant address stride (H*W) for
@@ -325,7 +340,7 @@ __global__ void __launch_bounds__(kTsThreads, 1)
             kt[k] = e;
         }
     }
-    if (tp.a_kind == A_IM2COL && !tp.a_pointwise) {
+    if (a_kind == A_IM2COL && !tp.a_pointwise) {
         // k -> (offset, dy, dx) table, filled cooperatively; k beyond K is never read as valid
         KEntry* kt = reinterpret_cast<KEntry*>(smem_raw);
         const int khw = p.g.KH * p.g.KW;
@@ -378,14 +393,14 @@ __global__ void __launch_bounds__(kTsThreads, 1)
             // see TsParams) a tile never crosses into the next image.
             const int OHW = p.g.OH * tp.rc_wv;
             int tile_img = -1, pos0 = 0;
-            if (tp.a_kind == A_ROWCONV) pos0 = rowconv_pos0(tp, m0 / kBM, OHW, tile_img);
+            if (a_kind == A_ROWCONV) pos0 = rowconv_pos0(tp, m0 / kBM, OHW, tile_img);
             // Staged stores: warp 0 describes the tile's runs (the divisions happen here, once per
             // tile, and before the wait for the accumulator, which hides them); the table is
             // published by the barrier of the vote below.
             StageTile* stt = &st_tab[tile_par];
             if constexpr (ES == 2) {
                 if (tp.d_staged && !tp.rc_tma && warp == 0) {
-                    if (tp.a_kind == A_ROWCONV) {
+                    if (a_kind == A_ROWCONV) {
                         // the tile's produced positions, in order, are consecutive output pixels
                         // (a row's outputs end at OW, the next row's follow at once in memory)
                         auto first_pixel = [&](int pos) -> unsigned {  // first output pixel at or after position pos
@@ -401,7 +416,7 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                         const int nslots = static_cast<int>(first_pixel(pos0 + 4 * tp.rc_T) - q0);
                         stage_tile_fill(stt, lane, q0, nslots, static_cast<unsigned>(p.g.P),
                                         static_cast<long long>(b) * p.d_batch_stride, p.g.out_img_stride, p.g.P);
-                    } else if (tp.a_kind == A_IM2COL) {
+                    } else if (a_kind == A_IM2COL) {
                         stage_tile_fill(stt, lane, static_cast<unsigned>(m0), min(kBM, p.M - m0), static_cast<unsigned>(p.g.P),
                                         static_cast<long long>(b) * p.d_batch_stride, p.g.out_img_stride, p.g.P);
                     } else {
@@ -446,7 +461,7 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                 if (!__all_sync(0xffffffffu, w)) break;
             }
             ptx::tc_fence_after();
-            if (tp.a_kind == A_ROWCONV) {
+            if (a_kind == A_ROWCONV) {
                 const int tn = n0 / BN;
                 const int pos = pos0 + warp * tp.rc_T - tp.rc_lo + lane;
                 const bool pos_ok = pos >= 0 && pos < p.M;
@@ -617,7 +632,7 @@ __global__ void __launch_bounds__(kTsThreads, 1)
             const int i = m0 + warp * 32 + lane;
             const bool row_ok = i < p.M;
             long long rowbase, colstride;
-            if (tp.a_kind == A_IM2COL) {
+            if (a_kind == A_IM2COL) {
                 const int img = i / p.g.P;
                 const int pp = i - img * p.g.P;
                 rowbase = static_cast<long long>(img) * p.g.out_img_stride +
@@ -733,7 +748,7 @@ __global__ void __launch_bounds__(kTsThreads, 1)
             const bool row_ok = i < p.M;
             long long pbase = 0;
             int ih0 = -(1 << 30), iw0 = -(1 << 30);
-            if (tp.a_kind == A_ROWCONV) {
+            if (a_kind == A_ROWCONV) {
                 const int OHW = p.g.OH * tp.rc_wv;
                 int tile_img;
                 const int pos = rowconv_pos0(tp, m0 / kBM, OHW, tile_img) + q * tp.rc_T - tp.rc_lo + lane;
@@ -746,7 +761,7 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                     pbase = a_boff + static_cast<long long>(img) * p.g.img_stride +
                             static_cast<long long>(ih0) * p.g.W + iw0;
                 }
-            } else if (tp.a_kind == A_IM2COL) {
+            } else if (a_kind == A_IM2COL) {
                 if (row_ok) {
                     const int img = i / p.g.P;
                     const int pp = i - img * p.g.P;
@@ -757,7 +772,7 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                     pbase = a_boff + static_cast<long long>(img) * p.g.img_stride +
                             static_cast<long long>(ih0) * p.g.W + iw0;
                 }
-            } else if (tp.a_kind == A_DENSE_MN) {
+            } else if (a_kind == A_DENSE_MN) {
                 pbase = a_boff + i;
             } else {
                 pbase = a_boff + static_cast<long long>(i) * p.a.ld;
@@ -765,7 +780,7 @@ __global__ void __launch_bounds__(kTsThreads, 1)
             for (int kb = 0; kb < num_kb; ++kb) {
                 if (gpar != static_cast<uint32_t>(par)) {  // the other warp of this quadrant takes it
                     gpar ^= 1u;
-                    if (++s == static_cast<uint32_t>(S)) {
+                    if (++s == static_cast<uint32_t>(SA)) {
                         s = 0;
                         ph ^= 1u;
                     }
@@ -777,7 +792,7 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                 if (p.ablate & 1) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] = 0x3f800000u + j;
-                } else if (tp.a_kind == A_ROWCONV && tp.rc_sw == 1 && kcount == BK && ktable[k0].dy == ktable[k0 + BK - 1].dy) {
+                } else if (a_kind == A_ROWCONV && tp.rc_sw == 1 && kcount == BK && ktable[k0].dy == ktable[k0 + BK - 1].dy) {
                     // whole k-block inside one kh: consecutive k are consecutive channels
                     const KEntry e0 = ktable[k0];
                     const bool in = static_cast<unsigned>(ih0 + e0.dy) < static_cast<unsigned>(p.g.H);
@@ -795,7 +810,7 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                             v[j] = lo | (hi << 16);
                         }
                     }
-                } else if (tp.a_kind == A_IM2COL && tp.a_pointwise) {
+                } else if (a_kind == A_IM2COL && tp.a_pointwise) {
                     // 1x1 filter without padding: k is the channel, every tap lies inside the
                     // image, consecutive k are H*W elements apart (no table, no bounds tests)
                     const long long hw = static_cast<long long>(p.g.H) * p.g.W;
@@ -822,7 +837,7 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                             }
                         }
                     }
-                } else if (tp.a_kind == A_IM2COL || tp.a_kind == A_ROWCONV) {
+                } else if (a_kind == A_IM2COL || a_kind == A_ROWCONV) {
                     const KEntry* te = ktable + k0;
                     if constexpr (ES == 4) {
                         const uint32_t* x = reinterpret_cast<const uint32_t*>(p.a.base);
@@ -850,7 +865,7 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                             v[j] = lo | (hi << 16);
                         }
                     }
-                } else if (tp.a_kind == A_DENSE_MN) {
+                } else if (a_kind == A_DENSE_MN) {
                     if constexpr (ES == 4) {
                         const uint32_t* x = reinterpret_cast<const uint32_t*>(p.a.base) + pbase;
 #pragma unroll
@@ -894,7 +909,7 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                         }
                     }
                 }
-                const bool w = ptx::mbar_wait_bounded(ptx::smem_u32(&empty_bar[s]), ph ^ 1u, abort_p, wait_limit);
+                const bool w = ptx::mbar_wait_bounded(ptx::smem_u32(&empty_a[s]), ph ^ 1u, abort_p, wait_limit);
                 if (!__all_sync(0xffffffffu, w)) {
                     ok = false;
                     break;
@@ -921,7 +936,7 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                 ptx::tc_fence_before();
                 ptx::mbar_arrive(ptx::smem_u32(&full_a[s]));
                 gpar ^= 1u;
-                if (++s == static_cast<uint32_t>(S)) {
+                if (++s == static_cast<uint32_t>(SA)) {
                     s = 0;
                     ph ^= 1u;
                 }
@@ -945,7 +960,7 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                         decode_tile(p, t, b, m0, n0);
                         const int bb = p.b.batch_stride ? b : 0;
                         for (int kb = 0; kb < num_kb; ++kb) {
-                            if (!ptx::mbar_wait_bounded(ptx::smem_u32(&empty_bar[s]), ph ^ 1u, abort_p, wait_limit)) {
+                            if (!ptx::mbar_wait_bounded(ptx::smem_u32(&empty_b[s]), ph ^ 1u, abort_p, wait_limit)) {
                                 ok = false;
                                 break;
                             }
@@ -958,7 +973,7 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                                 for (int g = 0; g < BN / BK; ++g)
                                     ptx::tma_load_3d(sB + g * BK * 128, &tmB, bar, n0 + g * BK, kb * BK, bb);
                             }
-                            if (++s == static_cast<uint32_t>(S)) {
+                            if (++s == static_cast<uint32_t>(SB)) {
                                 s = 0;
                                 ph ^= 1u;
                             }
@@ -994,7 +1009,7 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                         }
                         ptx::fence_proxy_async_smem();
                         ptx::mbar_arrive(ptx::smem_u32(&full_b[s]));
-                        if (++s == static_cast<uint32_t>(S)) {
+                        if (++s == static_cast<uint32_t>(SB)) {
                             s = 0;
                             ph ^= 1u;
                         }
@@ -1015,7 +1030,7 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                     const unsigned char* src =
                         tp.b_packed + (static_cast<long long>(b) * p.tiles_n + n0 / BN) * num_kb * stage_bytes;
                     for (int kb = 0; kb < num_kb; ++kb) {
-                        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&empty_bar[s]), ph ^ 1u, abort_p, wait_limit)) {
+                        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&empty_b[s]), ph ^ 1u, abort_p, wait_limit)) {
                             ok = false;
                             break;
                         }
@@ -1025,7 +1040,7 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                         for (uint32_t o = 0; o < stage_bytes; o += 8192u)
                             ptx::bulk_load(sB + o, src + static_cast<long long>(kb) * stage_bytes + o,
                                            min(8192u, stage_bytes - o), bar);
-                        if (++s == static_cast<uint32_t>(S)) {
+                        if (++s == static_cast<uint32_t>(SB)) {
                             s = 0;
                             ph ^= 1u;
                         }
@@ -1040,7 +1055,7 @@ __global__ void __launch_bounds__(kTsThreads, 1)
             const long long b_boff =
                 p.b_offs ? p.b_offs[b] : static_cast<long long>(b) * p.b.batch_stride;
             for (int kb = 0; kb < num_kb; ++kb) {
-                const bool w = ptx::mbar_wait_bounded(ptx::smem_u32(&empty_bar[s]), ph ^ 1u, abort_p, wait_limit);
+                const bool w = ptx::mbar_wait_bounded(ptx::smem_u32(&empty_b[s]), ph ^ 1u, abort_p, wait_limit);
                 if (!__all_sync(0xffffffffu, w)) {
                     ok = false;
                     break;
@@ -1053,7 +1068,7 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                         const int L = L0 + q * kTsLoaderLines;
                         if (L >= BN || (p.ablate & 2)) {
                             v[q] = make_uint4(0u, 0u, 0u, 0u);
-                        } else if (tp.a_kind == A_ROWCONV) {
+                        } else if (a_kind == A_ROWCONV) {
                             // column L = (kw, co): W[c0+co][c][kh][kw] for k' = kh*C + c
                             const int kw = L / tp.rc_cpt;
                             const int co = (n0 / BN) * tp.rc_cpt + (L - kw * tp.rc_cpt);
@@ -1075,7 +1090,7 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                 }
                 ptx::fence_proxy_async_smem();
                 ptx::mbar_arrive(ptx::smem_u32(&full_b[s]));
-                if (++s == static_cast<uint32_t>(S)) {
+                if (++s == static_cast<uint32_t>(SB)) {
                     s = 0;
                     ph ^= 1u;
                 }
@@ -1093,7 +1108,7 @@ __global__ void __launch_bounds__(kTsThreads, 1)
             const uint32_t b_sbo = b_mode == 1u ? 512u : 1024u;
             const uint64_t db0 = ptx::make_smem_desc(smem0, b_lbo, b_sbo, b_mode);
             const uint32_t lo_units = b_tile >> 4;
-            uint32_t s = 0, ph = 0, buf = 0, tphase = 0;
+            uint32_t s = 0, ph = 0, sb = 0, phb = 0, buf = 0, tphase = 0;  // A slot / B stage and their phases
             bool ok = true;
             const int kc = tp.kc_blocks > 0 ? tp.kc_blocks : num_kb;
             for (int t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x) {
@@ -1107,12 +1122,12 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                     const int kb1 = min(kb0 + kc, num_kb);
                     for (int kb = kb0; kb < kb1; ++kb) {
                         if (!ptx::mbar_wait_bounded(ptx::smem_u32(&full_a[s]), ph, abort_p, wait_limit) ||
-                            !ptx::mbar_wait_bounded(ptx::smem_u32(&full_b[s]), ph, abort_p, wait_limit)) {
+                            !ptx::mbar_wait_bounded(ptx::smem_u32(&full_b[sb]), phb, abort_p, wait_limit)) {
                             ok = false;
                             break;
                         }
                         ptx::tc_fence_after();
-                        const uint32_t st_units = (s * stage_bytes) >> 4;
+                        const uint32_t st_units = (sb * stage_bytes) >> 4;
                         const uint32_t a_slot = tmem_base + a_col0 + s * A_COLS;
 #pragma unroll
                         for (int ks = 0; ks < BK / UMMA_K; ++ks) {
@@ -1127,10 +1142,15 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                                 umma_ts_tf32(d_tmem, a_hi, db, idesc, 1u);
                             }
                         }
-                        ptx::umma_commit(ptx::smem_u32(&empty_bar[s]));
-                        if (++s == static_cast<uint32_t>(S)) {
+                        ptx::umma_commit(ptx::smem_u32(&empty_a[s]));
+                        ptx::umma_commit(ptx::smem_u32(&empty_b[sb]));
+                        if (++s == static_cast<uint32_t>(SA)) {
                             s = 0;
                             ph ^= 1u;
+                        }
+                        if (++sb == static_cast<uint32_t>(SB)) {
+                            sb = 0;
+                            phb ^= 1u;
                         }
                     }
                     if (ok && !p.skip_tile_commit) ptx::umma_commit(ptx::smem_u32(&tfull_bar[buf]));

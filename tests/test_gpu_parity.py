@@ -732,6 +732,64 @@ def test_resnet50_fc_gemm_vs_oracle():
     assert max_rel(C.float().cpu().numpy(), ref) <= HALF_TOL
 
 
+STORE_MODE_CASES = [
+    # N, C, H, W, Cout, k, pad, stride
+    (2, 16, 24, 24, 32, 3, 1, 1),    # plane of 576 pixels: image-aligned tiles + TMA stores when forced for stride 1
+    (3, 16, 14, 14, 40, 3, 1, 1),    # 196-pixel planes: tiles cross images, two runs, 8-byte-aligned planes
+    (5, 8, 7, 7, 24, 3, 1, 1),       # 49-pixel planes: up to four runs per tile, 2-byte-aligned planes
+    (3, 32, 14, 14, 72, 1, 0, 1),    # 1x1 on the plain epilogue
+    (5, 24, 7, 7, 40, 1, 0, 1),      # 1x1, odd planes
+    (2, 3, 40, 48, 64, 7, 3, 2),     # strided row form (stem-like): TMA stores by default
+    (2, 8, 9, 40, 16, 3, 0, 1),      # no padding: output rows shorter than the position rows
+    (40, 4, 3, 3, 8, 3, 1, 1),       # 9-pixel planes: more images per tile than the staging handles -> direct stores
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("case", STORE_MODE_CASES, ids=lambda c: "x".join(map(str, c)))
+def test_conv2d_output_store_modes_agree(lib, case, dtype):
+    """The three ways 16-bit results of the tensor-memory-operand kernel leave the SM - one element
+    per lane, staged 16-byte stores (measurement bit 64 << 16), TMA stores of image-aligned tiles
+    (default for the strided row form, bit 128 << 16 for stride 1) - give the same bits, with and
+    without a residual + ReLU, and touch nothing outside Y."""
+    from dlf_b200 import gdnn
+    N, C, H, W, Co, k, p, s = case
+    rng = np.random.default_rng(sum(case))
+    X = torch.from_numpy(_rand(rng, (N, C, H, W), "normal")).to(dtype).cuda()
+    Wt = torch.from_numpy(0.2 * _rand(rng, (Co, C, k, k), "normal")).to(dtype).cuda()
+    bias = torch.from_numpy(_rand(rng, Co)).to(dtype).cuda()
+    f = gdnn.Filter2D(X.shape, Wt.shape).pads(p, p).strides(s, s)
+    n_out = int(np.prod(f.output_shape()))
+    R = torch.from_numpy(_rand(rng, f.output_shape(), "normal")).to(dtype).cuda()
+    for fused in (False, True):
+        outs = []
+        for flags in (0, 64 << 16, 128 << 16, (64 | 128) << 16):
+            buf = torch.full((n_out + 64,), 3.0, dtype=dtype, device="cuda")  # guard band on both sides
+            Y = buf[32:32 + n_out].view(f.output_shape())
+            lib.set_tuning(0, flags)
+            try:
+                if fused:
+                    gdnn.conv2d_filter(X, Wt, Y, f, bias=bias, residual=R, activation="relu")
+                else:
+                    gdnn.conv2d_filter(X, Wt, Y, f, bias=bias)
+                torch.cuda.synchronize()
+            finally:
+                lib.set_tuning(0, 0)
+            assert bool((buf[:32] == 3.0).all()) and bool((buf[32 + n_out:] == 3.0).all())
+            outs.append(Y.clone())
+        for o in outs[1:]:
+            assert torch.equal(outs[0], o)
+    ref = oracle.conv2d(X.float().cpu().numpy(), Wt.float().cpu().numpy(), pads=(p,) * 4, strides=(s, s),
+                        bias=bias.float().cpu().numpy(), wide=True)
+    lib.set_tuning(0, 64 << 16)
+    try:
+        Y = torch.empty(f.output_shape(), dtype=dtype, device="cuda")
+        gdnn.conv2d_filter(X, Wt, Y, f, bias=bias)
+    finally:
+        lib.set_tuning(0, 0)
+    assert max_rel(Y.float().cpu().numpy(), ref) <= HALF_TOL
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
 def test_conv2d_pointwise_table_lookup_matches_affine(lib, dtype):
     """1x1 filters without padding address the image affinely in k; the table lookup used for
