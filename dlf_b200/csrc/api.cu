@@ -465,26 +465,20 @@ int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
     const int stage_bytes = bn * 128 * (q.es == 4 ? 2 : 1);
     const int sums_bytes = kc_blocks ? bn * 128 * 4 : 0;
     if (kc_blocks && bn > 192) return kUnexpectedError;
-    // 16-bit outputs for which nothing of D is read leave through staged 16-byte stores
-    // (epilogue.cuh); a residual is read by the staging threads themselves
-    // Measured: the staged 16-byte stores cost the four epilogue warps more instructions and
-    // barrier waits than they save (the epilogue is bound by instruction latency, not by the
-    // width of its stores), so they are only used on request (measurement bit 64 << 16) and by
-    // the row form with image-aligned tiles, whose blocks leave through TMA stores.
-    const bool d_staged = q.es == 2 && q.beta == 0.0f && q.betas == nullptr &&
-                          (q.rc_tpi != 0 || ((g_force_generic.load() >> 16) & 64));
     // row form with image-aligned tiles: two blocks of [channels of the tile][positions of the tile]
     const int rc_tma_buf = q.rc_tpi ? (q.rc_cpt * 4 * q.rc_T * 2 + 127) / 128 * 128 : 0;
-    const int out_stage_bytes = !d_staged ? 0 : (q.rc_tpi ? 2 * rc_tma_buf : kStageBytes) + 128;  // + alignment slack
-    if (q.rc_tpi && !d_staged) return kUnexpectedError;
+    const int out_stage_bytes = q.rc_tpi ? 2 * rc_tma_buf + 128 : 0;  // + alignment slack
+    if (q.rc_tpi && (q.es != 2 || q.beta != 0.0f)) return kUnexpectedError;
     // the k table is padded to a multiple of 1024 in the layout below: count it that way here too
-    // B stages in shared memory and A slots in tensor memory are separate rings (0x200 << 16: the
-    // former single ring, both as deep as the shallower one)
+    // B stages in shared memory and A slots in tensor memory are separate rings in the kernel, but
+    // a B ring deeper than the A ring was measured as no gain or a loss (64-channel 3x3 layer in
+    // fp16 245 -> 265 us, fp32 80.3 -> 81.1 us), so both get the depth of the shallower one unless
+    // measurement bit 0x200 << 16 asks for the deeper B ring
     int b_stages = (kSmemPerBlockOptin - static_smem - 1024 - ((ktable_bytes + 1023) / 1024 * 1024) - sums_bytes - out_stage_bytes) / stage_bytes;
     int stages = (512 - acc_bufs * bn) / a_cols;
     if (b_stages > kMaxStages) b_stages = kMaxStages;
     if (stages > kMaxStages) stages = kMaxStages;
-    if ((g_force_generic.load() >> 16) & 0x200) b_stages = stages = std::min(b_stages, stages);
+    if (!((g_force_generic.load() >> 16) & 0x200)) b_stages = stages = std::min(b_stages, stages);
     if (stages < 2 || b_stages < 2) return kUnexpectedError;
     // dynamic segment: [k table][pad to 1024][B stages][partial sums]
     const int sums_off = ((ktable_bytes + 1023) / 1024 * 1024) + 1024 + b_stages * stage_bytes;
@@ -536,7 +530,6 @@ int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
     tp.rc_dmin = q.rc_dmin;
     tp.kc_blocks = kc_blocks;
     tp.sums_off = sums_off;
-    tp.d_staged = d_staged ? 1 : 0;
     tp.stage_off = sums_off + sums_bytes;
     tp.rc_tpi = q.rc_tpi;
     tp.rc_tma = q.rc_tpi ? 1 : 0;

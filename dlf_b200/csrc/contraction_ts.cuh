@@ -90,10 +90,8 @@ struct TsParams {
     int b_tma;
     // A_IM2COL with a 1x1 filter and no padding (any stride): addresses are affine in k
     int a_pointwise;
-    // 16-bit outputs that nothing has to be read for: the epilogue warps stage blocks of columns in
-    // shared memory (kStageBytes at byte offset stage_off of the dynamic segment) and write them
-    // out as 16-byte vectors (see "Staged stores" in epilogue.cuh)
-    int d_staged, stage_off;
+    // byte offset, in the dynamic segment, of the blocks that rc_tma stages its results in
+    int stage_off;
     // Row form with image-aligned tiles (rc_tpi = tiles per image, 0 = tiles run across images): a
     // tile then is one contiguous range of one image's pixels for every channel, and 16-bit
     // results leave as TMA stores (rc_tma; two blocks of rc_tma_buf bytes at stage_off).
@@ -284,8 +282,7 @@ __global__ void __launch_bounds__(kTsThreads, 1)
     __shared__ __align__(8) uint64_t tempty_bar[2];
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
-    __shared__ int epi_ok[2][4];  // staged stores: outcome of each epilogue warp's wait for the tile
-    __shared__ StageTile st_tab[2];
+    __shared__ int epi_ok[2][4];  // TMA-store epilogue: outcome of each epilogue warp's wait for the tile
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -394,37 +391,6 @@ __global__ void __launch_bounds__(kTsThreads, 1)
             const int OHW = p.g.OH * tp.rc_wv;
             int tile_img = -1, pos0 = 0;
             if (a_kind == A_ROWCONV) pos0 = rowconv_pos0(tp, m0 / kBM, OHW, tile_img);
-            // Staged stores: warp 0 describes the tile's runs (the divisions happen here, once per
-            // tile, and before the wait for the accumulator, which hides them); the table is
-            // published by the barrier of the vote below.
-            StageTile* stt = &st_tab[tile_par];
-            if constexpr (ES == 2) {
-                if (tp.d_staged && !tp.rc_tma && warp == 0) {
-                    if (a_kind == A_ROWCONV) {
-                        // the tile's produced positions, in order, are consecutive output pixels
-                        // (a row's outputs end at OW, the next row's follow at once in memory)
-                        auto first_pixel = [&](int pos) -> unsigned {  // first output pixel at or after position pos
-                            if (pos >= p.M) return static_cast<unsigned>(p.M / OHW) * static_cast<unsigned>(p.g.P);
-                            const int im = pos / OHW;
-                            const int rm = pos - im * OHW;
-                            const int r_oh = rm / tp.rc_wv;
-                            const int r_u = rm - r_oh * tp.rc_wv;
-                            return static_cast<unsigned>(im) * static_cast<unsigned>(p.g.P) +
-                                   static_cast<unsigned>((r_oh + (r_u < p.g.OW ? 0 : 1)) * p.g.OW + (r_u < p.g.OW ? r_u : 0));
-                        };
-                        const unsigned q0 = first_pixel(pos0);
-                        const int nslots = static_cast<int>(first_pixel(pos0 + 4 * tp.rc_T) - q0);
-                        stage_tile_fill(stt, lane, q0, nslots, static_cast<unsigned>(p.g.P),
-                                        static_cast<long long>(b) * p.d_batch_stride, p.g.out_img_stride, p.g.P);
-                    } else if (a_kind == A_IM2COL) {
-                        stage_tile_fill(stt, lane, static_cast<unsigned>(m0), min(kBM, p.M - m0), static_cast<unsigned>(p.g.P),
-                                        static_cast<long long>(b) * p.d_batch_stride, p.g.out_img_stride, p.g.P);
-                    } else {
-                        stage_tile_fill(stt, lane, static_cast<unsigned>(m0), min(kBM, p.M - m0), 0u,
-                                        p.d_offs ? p.d_offs[b] : static_cast<long long>(b) * p.d_batch_stride, 0, p.ldd);
-                    }
-                }
-            }
             // all K-chunks but the last only feed the running sums
             for (int kb0 = 0; kb0 + kc < num_kb; kb0 += kc) {
                 const bool wc = ptx::mbar_wait_bounded(ptx::smem_u32(&tfull_bar[buf]), tphase, abort_p, wait_limit);
@@ -445,8 +411,8 @@ __global__ void __launch_bounds__(kTsThreads, 1)
             const float* part = kc < num_kb ? part_row : nullptr;
             const bool w = ptx::mbar_wait_bounded(ptx::smem_u32(&tfull_bar[buf]), tphase, abort_p, wait_limit);
             if constexpr (ES == 2) {
-                if (tp.d_staged) {
-                    // The staged stores below synchronise the four epilogue warps with a named
+                if (tp.rc_tma) {
+                    // The TMA-store epilogue below synchronises the four epilogue warps with a named
                     // barrier, which has no time limit: the warps must agree on whether this tile
                     // is processed. Every warp gets here (its wait is bounded), votes, and all
                     // leave together if any wait gave up.
@@ -479,22 +445,16 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                 const int nco = min(tp.rc_cpt, p.N - c0);
                 const char* bias_g =
                     p.bias ? p.bias + (static_cast<long long>(b) * p.bias_stride + c0) * ES : nullptr;
-                // how this tile's results leave: 0 one element per lane, 1 staged 16-byte stores,
-                // 2 TMA stores of whole blocks (image-aligned tiles)
+                // how this tile's results leave: 0 one element per lane, 2 TMA stores of whole blocks
+                // (image-aligned tiles)
                 int mode = 0;
-                StageSlot ss{0, 0, 0};
+                int tile_slot = 0;
                 uint32_t sbuf = 0;
                 if constexpr (ES == 2) {
                     if (tp.rc_tma) {
                         mode = 2;
                         sbuf = stage_base + stage_buf * static_cast<uint32_t>(tp.rc_tma_buf);
-                        ss.idx0 = warp * tp.rc_T + (lane - tp.rc_lo);  // position inside the tile
-                    } else if (tp.d_staged && stt->runs > 0) {
-                        mode = 1;
-                        sbuf = stage_base + stage_buf * kStageBufBytes;
-                        if (produce)
-                            ss = stage_slot(stt, static_cast<int>(static_cast<unsigned>(img) * static_cast<unsigned>(p.g.P) +
-                                                                  static_cast<unsigned>(oh * p.g.OW + u) - stt->q0), p.d);
+                        tile_slot = warp * tp.rc_T + (lane - tp.rc_lo);  // position inside the tile
                     }
                 }
                 for (int co0 = 0; co0 < ((p.ablate & 8) ? 0 : nco); co0 += 16) {
@@ -547,34 +507,13 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                         if (mode == 2) {
                             // block [channel][position of the tile]: one TMA store per 16 channels below
                             if (produce) {
-                                const uint32_t sa = sbuf + static_cast<uint32_t>(co0 * 4 * tp.rc_T + ss.idx0) * 2u;
+                                const uint32_t sa = sbuf + static_cast<uint32_t>(co0 * 4 * tp.rc_T + tile_slot) * 2u;
 #pragma unroll
                                 for (int e = 0; e < 16; ++e) {
                                     const unsigned short h = p.fmt == FMT_F16 ? to_bits16<OUT_F16>(acc[e]) : to_bits16<OUT_BF16>(acc[e]);
                                     asm volatile("st.shared.u16 [%0], %1;" ::"r"(sa + static_cast<uint32_t>(e * 4 * tp.rc_T) * 2u), "h"(h) : "memory");
                                 }
                             }
-                            continue;
-                        }
-                        if (mode == 1) {
-                            if (produce) {
-#pragma unroll
-                                for (int e = 0; e < 16; ++e) {
-                                    if (co0 + e < nco) {
-                                        const int idx = ss.idx0 + ((ss.a7 + (c0 + co0 + e) * ss.cs7) & 7);
-                                        const unsigned short h = p.fmt == FMT_F16 ? to_bits16<OUT_F16>(acc[e]) : to_bits16<OUT_BF16>(acc[e]);
-                                        asm volatile("st.shared.u16 [%0], %1;" ::"r"(sbuf + static_cast<uint32_t>(e * kStageRowStride + idx) * 2u), "h"(h) : "memory");
-                                    }
-                                }
-                            }
-                            if (co0 + 16 >= nco) {  // the accumulator has been read for the last time
-                                ptx::tc_fence_before();
-                                ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));
-                            }
-                            epilogue_bar();
-                            staged_writeout(stt, sbuf, p.d, c0 + co0, min(16, nco - co0), threadIdx.x);
-                            stage_buf ^= 1u;
-                            sbuf = stage_base + stage_buf * kStageBufBytes;
                             continue;
                         }
                     }
@@ -600,10 +539,8 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                         }
                     }
                 }
-                if (mode != 1 || (p.ablate & 8)) {  // (mode 1 released the accumulator after its last read)
-                    ptx::tc_fence_before();
-                    ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));
-                }
+                ptx::tc_fence_before();
+                ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));
                 if constexpr (ES == 2) {
                     if (mode == 2) {
                         // every staging thread makes its writes visible to the async proxy, then
@@ -653,61 +590,6 @@ __global__ void __launch_bounds__(kTsThreads, 1)
             ex.relu = p.relu != 0;
             ex.rdelta = p.resid ? p.resid - p.d : 0;
             const float beta_e = p.resid ? 1.0f : beta;  // a residual takes the place of the beta term
-            if constexpr (ES == 2) {
-                if (tp.d_staged && stt->runs > 0 && !(p.ablate & 32)) {
-                    StageSlot ss{0, 0, 0};
-                    if (row_ok) ss = stage_slot(stt, warp * 32 + lane, p.d);
-                    for (int cc = 0; cc < ncols; cc += 32) {
-                        uint32_t v[32];
-                        ptx::tmem_ld_32x32(trow + cc, v);
-                        ptx::tmem_ld_wait();
-                        const int nc = min(32, ncols - cc);
-                        if (cc + 32 >= ncols) {  // last read of the accumulator
-                            ptx::tc_fence_before();
-                            ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));
-                        }
-                        float bv = 0.0f;
-                        if (bias != nullptr && lane < nc)
-                            bv = p.fmt == FMT_F16 ? out_load<OUT_F16>(bias + (cc + lane) * 2)
-                                                  : out_load<OUT_BF16>(bias + (cc + lane) * 2);
-                        if (p.resid != nullptr) {
-                            const char* rp = p.resid + (optr - p.d) + static_cast<long long>(cc) * colstride * 2;
-#pragma unroll
-                            for (int jj = 0; jj < 32; ++jj) {
-                                float rv = 0.0f;
-                                if (row_ok && jj < nc)
-                                    rv = p.fmt == FMT_F16 ? out_load<OUT_F16>(rp + jj * colstride * 2)
-                                                          : out_load<OUT_BF16>(rp + jj * colstride * 2);
-                                v[jj] = __float_as_uint(alpha * __uint_as_float(v[jj]) + rv);
-                            }
-                        } else {
-#pragma unroll
-                            for (int jj = 0; jj < 32; ++jj) v[jj] = __float_as_uint(alpha * __uint_as_float(v[jj]));
-                        }
-                        const uint32_t sbuf = stage_base + stage_buf * kStageBufBytes;
-                        const bool relu = p.relu != 0;
-                        const int colsh0 = ss.a7 + (n0 + cc) * ss.cs7;
-#pragma unroll
-                        for (int jj = 0; jj < 32; ++jj) {
-                            float r = __uint_as_float(v[jj]) + __shfl_sync(0xffffffffu, bv, jj);
-                            r = relu ? fmaxf(r, 0.0f) : r;
-                            if (row_ok && jj < nc) {
-                                const int idx = ss.idx0 + ((colsh0 + jj * ss.cs7) & 7);
-                                const unsigned short h = p.fmt == FMT_F16 ? to_bits16<OUT_F16>(r) : to_bits16<OUT_BF16>(r);
-                                asm volatile("st.shared.u16 [%0], %1;" ::"r"(sbuf + static_cast<uint32_t>(jj * kStageRowStride + idx) * 2u), "h"(h) : "memory");
-                            }
-                        }
-                        epilogue_bar();
-                        staged_writeout(stt, sbuf, p.d, n0 + cc, nc, threadIdx.x);
-                        stage_buf ^= 1u;
-                    }
-                    if (++buf == static_cast<uint32_t>(nbuf)) {
-                        buf = 0;
-                        tphase ^= 1u;
-                    }
-                    continue;
-                }
-            }
             if (p.ablate & 32) {
             } else if constexpr (ES == 4) {
                 epilogue_dispatch<OUT_F32>(trow, ncols, optr, colstride * ES, row_ok, alpha, beta_e,

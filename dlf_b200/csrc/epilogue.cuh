@@ -187,136 +187,9 @@ __device__ __forceinline__ void epilogue_dispatch(uint32_t trow, int ncols_total
     }
 }
 
-// ---------------------------------------------------------------------------------------------
-// Staged stores of 16-bit outputs.
-//
-// A warp that writes one 2-byte element per lane moves 64 bytes per store instruction, and stores
-// of that width were measured at about 0.4-0.5 TB/s for the whole GPU (one 4-byte word per lane:
-// about twice that) - far below what HBM accepts. Where a tile's results cannot leave through a
-// TMA store (planes that are not 16-byte multiples, offsets, the row form of the convolution)
-// the four epilogue warps therefore put a block of columns into shared memory first and write it
-// out together as 16-byte vectors.
-//
-// Model. The tile's valid rows, in lane order, are `nslots` consecutive output pixels q0, q0+1, ..
-// ("slots"). For a convolution pixel q lies in image q / P at offset q % P of every channel plane,
-// so the slots split into at most four runs (one per image the tile touches), each contiguous in
-// memory for a fixed column; a GEMM tile is one run (P = 0). Element (slot s of run r, column j)
-// sits at element offset  base + img_r*ois + j*colstride + (q0 + s - img_r*P)  of D.
-// In shared memory column jj of the block occupies kStageRowStride elements; run r starts at
-// index rb_r + sh, where rb_r is a multiple of 8 and sh = (global element address of the run's
-// first element in that column) mod 8: 16-byte chunks of shared memory then map to 16-byte
-// aligned chunks of global memory, whatever the alignment of D, of the planes or of the run.
-constexpr int kStageCols = 32;
-constexpr int kStageRowStride = 200;  // >= 128 slots + 3 gaps of 16 + 7 of shift, multiple of 8
-constexpr int kStageBufBytes = kStageCols * kStageRowStride * 2;
-constexpr int kStageBytes = 2 * kStageBufBytes;  // two blocks: one is written while the other drains
-constexpr int kStageMaxRuns = 4;
-
-struct StageRun {
-    int s, len, rb;       // first slot, slots, shared-memory index base (multiple of 8)
-    int pad;
-    long long gelem;      // element offset in D of the run's first element, column 0
-};
-
-// Per-tile description of the runs, filled by the first lanes of epilogue warp 0 and read by all
-// 128 epilogue threads after a barrier (two copies, alternating between consecutive tiles, so a
-// warp that runs ahead never overwrites what a slower one still reads). All index arithmetic that
-// needs a division happens once per tile, in those lanes.
-struct StageTile {
-    int runs;             // 0: this tile does not use staged stores (more than kStageMaxRuns images)
-    int nslots;
-    unsigned q0, pad;     // pixel index of slot 0
-    long long colstride;  // elements between columns of D
-    StageRun run[kStageMaxRuns];
-};
-
-// q0 = pixel index of slot 0; P = pixels per image (0: one run); base = element offset of
-// (image 0, column 0, pixel 0) of this batch entry; ois = elements between images.
-__device__ __forceinline__ void stage_tile_fill(StageTile* st, int lane, unsigned q0, int nslots, unsigned P,
-                                                long long base, long long ois, long long colstride) {
-    const unsigned img0 = P ? q0 / P : 0u;
-    const int runs = nslots <= 0 ? 0 : (P ? static_cast<int>((q0 + nslots - 1) / P - img0) + 1 : 1);
-    if (lane == 0) {
-        st->runs = runs <= kStageMaxRuns ? runs : 0;
-        st->nslots = nslots;
-        st->q0 = q0;
-        st->pad = 0;
-        st->colstride = colstride;
-    }
-    if (lane < runs && lane < kStageMaxRuns) {
-        const long long img = static_cast<long long>(img0) + lane;
-        StageRun run;
-        run.s = lane == 0 ? 0 : static_cast<int>(img * P - q0);
-        const int e = P ? min(nslots, static_cast<int>((img + 1) * P - q0)) : nslots;
-        run.len = e - run.s;
-        run.rb = ((run.s + 7) & ~7) + 16 * lane;
-        run.pad = 0;
-        run.gelem = base + img * ois + (static_cast<long long>(q0) + run.s - img * P);
-        st->run[lane] = run;
-    }
-}
-
 // The four epilogue warps (threads 0-127 of the CTA) meet here; barrier 0 belongs to __syncthreads.
+// Used where the warps hand a block of results to one thread that issues TMA stores for it.
 __device__ __forceinline__ void epilogue_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
-
-// What a staging thread needs for its own slot: the index of its element in column `col` is
-//     idx0 + ((a7 + col * cs7) & 7)
-// (run base + position inside the run + that column's alignment shift).
-struct StageSlot {
-    int idx0, a7, cs7;
-};
-__device__ __forceinline__ StageSlot stage_slot(const StageTile* st, int slot, const char* d) {
-    int r = 0;
-    for (int k = 1; k < st->runs; ++k) r += slot >= st->run[k].s ? 1 : 0;
-    const StageRun run = st->run[r];
-    StageSlot o;
-    o.idx0 = run.rb + (slot - run.s);
-    o.a7 = static_cast<int>((static_cast<long long>(reinterpret_cast<uintptr_t>(d) >> 1) + run.gelem) & 7);
-    o.cs7 = static_cast<int>(st->colstride & 7);
-    return o;
-}
-
-// Writes the staged block (columns col0 .. col0+ncols-1 of D) to global memory. tid = 0..127.
-// A half-warp takes a column (and every run of it); lane l of the half-warp takes 16-byte chunks
-// l, l+16 of a run. Chunks that lie wholly inside the run leave as one 16-byte store, the ragged
-// first and last chunk element by element.
-__device__ __forceinline__ void staged_writeout(const StageTile* st, uint32_t sbuf, char* d, long long col0, int ncols,
-                                                int tid) {
-    const long long d_elem0 = static_cast<long long>(reinterpret_cast<uintptr_t>(d) >> 1);
-    const int l16 = tid & 15;
-    const int runs = st->runs;
-    const long long cs = st->colstride;
-    for (int jj = tid >> 4; jj < ncols; jj += 8) {
-        const long long coff = (col0 + jj) * cs;
-        for (int r = 0; r < runs; ++r) {
-            const StageRun run = st->run[r];
-            const long long gfirst = run.gelem + coff;  // element offset of the run's first element
-            const int sh = static_cast<int>((d_elem0 + gfirst) & 7);
-            const int last = sh + run.len;              // one past the run's last element, chunk-relative
-            const uint32_t scol = sbuf + static_cast<uint32_t>(jj * kStageRowStride + run.rb) * 2u;
-            char* gcol = d + (gfirst - sh) * 2;  // 16-byte aligned
-            for (int c = l16; 8 * c < last; c += 16) {
-                const uint32_t sa = scol + static_cast<uint32_t>(c) * 16u;
-                if (8 * c >= sh && 8 * c + 8 <= last) {
-                    uint4 v;
-                    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                                 : "r"(sa)
-                                 : "memory");
-                    *reinterpret_cast<uint4*>(gcol + c * 16) = v;
-                } else {
-                    const int lo = max(0, sh - 8 * c);
-                    const int hi = min(8, last - 8 * c);
-                    for (int t = lo; t < hi; ++t) {
-                        unsigned short h;
-                        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(h) : "r"(sa + t * 2u) : "memory");
-                        *reinterpret_cast<unsigned short*>(gcol + c * 16 + t * 2) = h;
-                    }
-                }
-            }
-        }
-    }
-}
 
 template <int OUT>
 __device__ __forceinline__ unsigned short to_bits16(float v) {
