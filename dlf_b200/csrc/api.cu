@@ -478,8 +478,23 @@ int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
     int stages = (512 - acc_bufs * bn) / a_cols;
     if (b_stages > kMaxStages) b_stages = kMaxStages;
     if (stages > kMaxStages) stages = kMaxStages;
+    const int b_room = b_stages;  // B stages that shared memory has room for
     if (!((g_force_generic.load() >> 16) & 0x200)) b_stages = stages = std::min(b_stages, stages);
     if (stages < 2 || b_stages < 2) return kUnexpectedError;
+    // One column tile, one batch entry, and the whole packed filter bank fits in the B ring: it is
+    // loaded once per CTA and stays (decided here, used where the bank is packed below).
+    const bool b_resident_ok = tiles_n == 1 && q.batch == 1 && num_kb <= b_room && num_kb <= kMaxStages &&
+                               !((static_cast<unsigned>(g_force_generic.load()) >> 16) & 0x8000u);
+    // (whether the bank will be packed: the caller's scratch must hold it)
+    bool will_pack = false;
+    if (q.pack_ws != nullptr && (q.a.im2col || q.rc_kw) && q.b.k_major && !(g_force_generic.load() & 0x8000)) {
+        const size_t slack = static_cast<size_t>(((reinterpret_cast<uintptr_t>(q.pack_ws) + 127) & ~uintptr_t(127)) -
+                                                 reinterpret_cast<uintptr_t>(q.pack_ws));
+        will_pack = q.pack_ws_bytes >= slack &&
+                    static_cast<long long>(q.pack_ws_bytes - slack) >= q.batch * tiles_n * num_kb * stage_bytes;
+    }
+    const bool b_resident = b_resident_ok && will_pack;
+    if (b_resident) b_stages = static_cast<int>(num_kb);  // ring index = k-block index
     // dynamic segment: [k table][pad to 1024][B stages][partial sums]
     const int sums_off = ((ktable_bytes + 1023) / 1024 * 1024) + 1024 + b_stages * stage_bytes;
     size_t dyn_smem = static_cast<size_t>(sums_off) + sums_bytes + out_stage_bytes;
@@ -535,6 +550,11 @@ int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
     tp.rc_tma = q.rc_tpi ? 1 : 0;
     tp.rc_tma_buf = rc_tma_buf;
     tp.b_stages = b_stages;
+    // row form with stride_w = 2 on 16-bit data: the two column phases of a tap are adjacent in
+    // memory; one aligned 32-bit load serves both when the rows and the tensor start on 4 bytes
+    tp.rc_pair = (q.rc_kw && q.rc_sw == 2 && q.es == 2 && q.g.W % 2 == 0 && 2 * q.rc_wv <= q.g.W &&
+                  (reinterpret_cast<uintptr_t>(q.a.base) & 3u) == 0 && !((g_force_generic.load() >> 16) & 64))
+                     ? 1 : 0;
     tp.acc_bufs = acc_bufs;
     tp.ktable_bytes = ktable_bytes;
 
@@ -554,6 +574,7 @@ int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
                 pack_weights_kernel<4><<<pgrid, 256, 0, stream>>>(tp, ws, chunks);
             g_launches.fetch_add(1);
             tp.b_packed = ws;
+            tp.b_resident = b_resident ? 1 : 0;
         }
     }
 

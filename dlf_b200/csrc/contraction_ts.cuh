@@ -35,7 +35,7 @@
 // With a horizontal stride sw > 1 (and dilation_w = 1) the same form applies after splitting the
 // input columns into sw phases: u = sw*ow + kw - pl = sw*(ow + d) + r with r = (kw - pl) mod sw,
 // d = floor((kw - pl) / sw). Positions are (img, oh, w') over a virtual row of w' values, the
-// column phases join the channels in K (k' = (kh*sw + r)*C + c reads X[..][sw*w' + r]) and the taps
+// column phases join the channels in K (k' = (kh*C + c)*sw + r reads X[..][sw*w' + r]) and the taps
 // become the shifts d = dmin..dmax: Y[ow] = sum_d D'[(ow + d), (d, co)]. The 7x7 stride-2 stem of
 // ResNet becomes K' = 42 (one k-block), N = 4 x 64.
 //
@@ -97,6 +97,11 @@ struct TsParams {
     // results leave as TMA stores (rc_tma; two blocks of rc_tma_buf bytes at stage_off).
     int rc_tpi, rc_tma, rc_tma_buf;
     int b_stages;  // depth of the B ring in shared memory (Params::stages is the depth of the A ring)
+    int rc_pair;   // row form, stride_w = 2, 16-bit: gather with one 32-bit load per pair of k
+    // The packed filter bank of the (only) column tile fits in the B ring as a whole (b_stages =
+    // number of k-blocks): every CTA loads it once, for its first tile, and keeps it - the bank is
+    // then not streamed from L2 again for every tile.
+    int b_resident;
 };
 
 // First position of row-form tile `tm`, and (image-aligned tiles) the image it belongs to.
@@ -151,7 +156,7 @@ __device__ __forceinline__ void umma_ts_tf32(uint32_t d_tmem, uint32_t a_tmem, u
         : "memory");
 }
 
-// Element k' = (kh*sw + r)*C + c of the row-form filter operand for output channel `co_off`
+// Element k' = (kh*C + c)*sw + r of the row-form filter operand for output channel `co_off`
 // (element offset of W[co][0][0][0]) and tap j: W[co][c][kh][kw] with kw = sw*(j + dmin) + r + pl,
 // zero where that kw does not exist or k' >= k_lim.
 struct RowTaps {
@@ -165,8 +170,8 @@ __device__ __forceinline__ uint32_t rowconv_weight(const char* base, long long c
     const int cgv = rt.cg * rt.sw;
     const int kh = k / cgv;
     const int rem = k - kh * cgv;
-    const int r = rem / rt.cg;
-    const int c = rem - r * rt.cg;
+    const int c = rem / rt.sw;
+    const int r = rem - c * rt.sw;
     const int kw = rt.sw * (j + rt.dmin) + r + rt.pl;
     if (kw < 0 || kw >= rt.KW) return 0u;
     const long long idx = co_off + static_cast<long long>(c * rt.KH + kh) * rt.KW + kw;
@@ -317,20 +322,20 @@ __global__ void __launch_bounds__(kTsThreads, 1)
         ptx::fence_mbar_init();
     }
     if (a_kind == A_ROWCONV) {
-        // k' = (kh*sw + r)*C + c -> (offset of the input row + column phase r, kh*dh, r); the
-        // column is the thread's own (times sw). Channel-fastest, so that with sw = 1 a k-block
-        // usually lies inside one kh: one validity test and a constant address stride (H*W) for
-        // the whole block.
+        // k' = (kh*C + c)*sw + r -> (offset of the input row + column phase r, kh*dh, r); the
+        // column is the thread's own (times sw). With sw = 1 a k-block usually lies inside one kh:
+        // one validity test and a constant address stride (H*W) for the whole block. With sw = 2
+        // the two phases of a (kh, c) are neighbours in k and in memory: one 32-bit load fills a
+        // packed register of 16-bit values (rc_pair).
         KEntry* kt = reinterpret_cast<KEntry*>(smem_raw);
         const int cgv = p.K / p.g.KH;     // channels per group x column phases
-        const int cg = cgv / tp.rc_sw;    // channels per group
         for (int k = threadIdx.x; k < num_kb * BK; k += blockDim.x) {
             KEntry e;
             const int kk = k < p.K ? k : 0;
             const int kh = kk / cgv;
             const int rem = kk - kh * cgv;
-            const int r = rem / cg;
-            const int ch = rem - r * cg;
+            const int ch = rem / tp.rc_sw;
+            const int r = rem - ch * tp.rc_sw;
             e.off = (ch * p.g.H + kh * p.g.dh) * p.g.W + r;
             e.dy = static_cast<short>(kh * p.g.dh);
             e.dx = static_cast<short>(r);
@@ -692,6 +697,17 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                             v[j] = lo | (hi << 16);
                         }
                     }
+                } else if (ES == 2 && a_kind == A_ROWCONV && tp.rc_pair) {
+                    // stride_w = 2, 16-bit: k = 2j and 2j+1 are the two column phases of one
+                    // (kh, channel): neighbours in memory, 4-byte aligned, both inside the row
+                    const KEntry* te = ktable + k0;
+                    const uint32_t* x32 = reinterpret_cast<const uint32_t*>(p.a.base);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const KEntry e = te[2 * j];
+                        const bool in = 2 * j < kcount && static_cast<unsigned>(ih0 + e.dy) < static_cast<unsigned>(p.g.H);
+                        v[j] = in ? x32[(pbase + e.off) >> 1] : 0u;
+                    }
                 } else if (a_kind == A_IM2COL && tp.a_pointwise) {
                     // 1x1 filter without padding: k is the channel, every tap lies inside the
                     // image, consecutive k are H*W elements apart (no table, no bounds tests)
@@ -907,6 +923,7 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                 // the packing grid launched just before this one must have completed
                 asm volatile("griddepcontrol.wait;" ::: "memory");
                 for (int t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x) {
+                    if (tp.b_resident && t != static_cast<int>(blockIdx.x)) break;  // loaded once, kept
                     int b, m0, n0;
                     decode_tile(p, t, b, m0, n0);
                     const unsigned char* src =
@@ -1003,8 +1020,10 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                     const uint32_t d_tmem = tmem_base + buf * BN;
                     const int kb1 = min(kb0 + kc, num_kb);
                     for (int kb = kb0; kb < kb1; ++kb) {
+                        // (a resident filter bank arrives once: only the first tile waits for it)
+                        const bool wait_b = !tp.b_resident || t == static_cast<int>(blockIdx.x);
                         if (!ptx::mbar_wait_bounded(ptx::smem_u32(&full_a[s]), ph, abort_p, wait_limit) ||
-                            !ptx::mbar_wait_bounded(ptx::smem_u32(&full_b[sb]), phb, abort_p, wait_limit)) {
+                            (wait_b && !ptx::mbar_wait_bounded(ptx::smem_u32(&full_b[sb]), phb, abort_p, wait_limit))) {
                             ok = false;
                             break;
                         }
@@ -1025,7 +1044,7 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                             }
                         }
                         ptx::umma_commit(ptx::smem_u32(&empty_a[s]));
-                        ptx::umma_commit(ptx::smem_u32(&empty_b[sb]));
+                        if (!tp.b_resident) ptx::umma_commit(ptx::smem_u32(&empty_b[sb]));
                         if (++s == static_cast<uint32_t>(SA)) {
                             s = 0;
                             ph ^= 1u;
