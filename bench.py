@@ -505,7 +505,8 @@ def time_steps_graph(fn, steps, warmup, per_graph=20):
         e1.record()
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) * steps / (reps * per_graph)
-    except Exception:
+    except Exception as e:
+        sys.stderr.write("graph timing not possible: %r\n" % (e,))
         torch.cuda.synchronize()
         return None
 

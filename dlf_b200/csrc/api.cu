@@ -19,6 +19,7 @@
 #include <vector>
 
 #include "../../include/dlf_b200.h"
+#include "channels_last.cuh"
 #include "contraction.cuh"
 #include "contraction_ts.cuh"
 #include "level3.cuh"
@@ -61,6 +62,7 @@ struct DeviceState {
     int static_smem_pair = 0;
     int max_pair_clusters = 0;  // co-resident CTA pairs of the pair kernel (0 = not usable)
     PFN_cuTensorMapEncodeTiled_v12000 encode = nullptr;
+    PFN_cuTensorMapEncodeIm2col_v12000 encode_im2col = nullptr;  // null: the driver has none
 };
 
 DeviceState g_dev[kMaxDevices];
@@ -210,6 +212,11 @@ int ensure_device(DeviceState** out) {
         CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
         if (qres != cudaDriverEntryPointSuccess || fn == nullptr) return kUnexpectedError;
         st.encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+        fn = nullptr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &fn, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            st.encode_im2col = reinterpret_cast<PFN_cuTensorMapEncodeIm2col_v12000>(fn);
+        (void)cudaGetLastError();
         CUDA_TRY(cudaMalloc(&st.status, 2 * sizeof(int)));
         CUDA_TRY(cudaMemset(st.status, 0, 2 * sizeof(int)));
         st.ready = true;
@@ -266,6 +273,15 @@ struct Problem {
     // caller-provided scratch for the packed filter bank of a convolution (may be null)
     unsigned char* pack_ws = nullptr;
     size_t pack_ws_bytes = 0;
+    // channels-last route of a convolution (channels_last.cuh): a.base is the channels-last copy.
+    // a_cl == 1: operand A comes through an im2col-mode tensor map over (cl_n, cl_h, cl_w, cl_cp);
+    // out_nchw: rows are output pixels of an NCHW tensor (g.P, g.out_img_stride)
+    // a_cl == 2: filters over <= 4 channels; a.base is the bordered row-pair copy (cl_n, cl_h, cl_w
+    // = images, row pairs, bordered row length; cl_rstep rows between pairs), tiles are 128 outputs
+    // of one output row
+    int a_cl = 0, cl_cblocks = 0, cl_tpr = 0, cl_rstep = 1;
+    int out_nchw = 0;
+    long long cl_n = 0, cl_h = 0, cl_w = 0, cl_cp = 0;
     bool d_f32 = false;  // 16-bit operands with fp32 output (partial products of a K-split GEMM)
     bool no_ts = false;  // convolution whose taps overflow the k table's 16/32-bit fields
 };
@@ -318,9 +334,86 @@ int encode_map(const DeviceState& st, CUtensorMap* map, const GenOperand& op, in
     return r == CUDA_SUCCESS ? kSuccess : kUnexpectedError;
 }
 
+// im2col-mode tensor map over the channels-last copy (C', W, H, N) of a convolution's input: one
+// load fetches 128 filter windows x 64 channels. The bounding box of window origins starts at
+// (-pad_left, -pad_top) and is as wide as the outputs need, (OW-1)*stride_w + 1 origins per row
+// (whatever the caller's right / bottom padding says: the tensor-map unit zero-fills what lies
+// outside the image); the traversal strides are the convolution's strides. Corners are limited to
+// [-128, 127] by the 4-D form of the map.
+int encode_im2col_map(const DeviceState& st, CUtensorMap* map, const Problem& q) {
+    if (st.encode_im2col == nullptr) return kNotImplemented;
+    const Im2colGeom& g = q.g;
+    cuuint64_t dims[4] = {static_cast<cuuint64_t>(q.cl_cp), static_cast<cuuint64_t>(q.cl_w),
+                          static_cast<cuuint64_t>(q.cl_h), static_cast<cuuint64_t>(q.cl_n)};
+    cuuint64_t strides[3] = {static_cast<cuuint64_t>(q.cl_cp * 2), static_cast<cuuint64_t>(q.cl_w * q.cl_cp * 2),
+                             static_cast<cuuint64_t>(q.cl_h * q.cl_w * q.cl_cp * 2)};
+    int lower[2] = {-g.pad_l, -g.pad_t};
+    int upper[2] = {(g.OW - 1) * g.sw + 1 - g.W - g.pad_l, (g.OH - 1) * g.sh + 1 - g.H - g.pad_t};
+    for (int i = 0; i < 2; ++i)
+        if (lower[i] < -128 || lower[i] > 127 || upper[i] < -128 || upper[i] > 127) return kNotImplemented;
+    cuuint32_t estr[4] = {1, static_cast<cuuint32_t>(g.sw), static_cast<cuuint32_t>(g.sh), 1};
+    CUresult r = st.encode_im2col(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, const_cast<char*>(q.a.base), dims, strides,
+                                  lower, upper, 64, kBM, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? kSuccess : kNotImplemented;
+}
+
+// Tiled map over the bordered row-pair copy X'' (N, J, Wp, 2, 4) of an input with <= 4 channels:
+// {64 elements = 8 pixels x 2 rows x 4 channels, outputs of a row (one step = stride_w pixels =
+// stride_w * 16 bytes, so windows of neighbouring outputs overlap), row pairs, images}; a box is
+// [128 outputs][64 elements], one 128-byte k-block line per output.
+int encode_small_map(const DeviceState& st, CUtensorMap* map, const Problem& q) {
+    cuuint64_t dims[4] = {64, static_cast<cuuint64_t>(q.g.OW), static_cast<cuuint64_t>(q.cl_h),
+                          static_cast<cuuint64_t>(q.cl_n)};
+    cuuint64_t strides[3] = {static_cast<cuuint64_t>(q.g.sw * 16), static_cast<cuuint64_t>(q.cl_w * 16),
+                             static_cast<cuuint64_t>(q.cl_h * q.cl_w * 16)};
+    cuuint32_t box[4] = {64, kBM, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = st.encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, const_cast<char*>(q.a.base), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS && std::getenv("DLF_B200_DEBUG"))
+        std::fprintf(stderr, "dlf_b200: small-channel tensor map refused (%d)\n", static_cast<int>(r));
+    return r == CUDA_SUCCESS ? kSuccess : kNotImplemented;
+}
+
 // Tensor map for TMA stores of the output (blocks of 32 rows x 32 or 64 columns, no swizzle): only when nothing of C has
 // to be read (beta == 0, no per-batch tables) and D's base and strides are 16-byte multiples.
 bool encode_output_map(const DeviceState& st, CUtensorMap* map, const Problem& q, unsigned box_cols) {
+    if (q.out_nchw == 2) {
+        // NCHW output written row by row: {OW, OH, channels, images}, boxes of 32 outputs of one row
+        const long long P = q.g.P, OW = q.g.OW;
+        const bool ok = q.es == 2 && q.beta == 0.0f && (reinterpret_cast<uintptr_t>(q.d) & 15u) == 0 &&
+                        (OW * q.es) % 16 == 0 && P * q.N * q.es < (1ll << 40) && !(g_force_generic.load() & 0x4000);
+        if (!ok) return false;
+        cuuint64_t dims[4] = {static_cast<cuuint64_t>(OW), static_cast<cuuint64_t>(q.g.OH), static_cast<cuuint64_t>(q.N),
+                              static_cast<cuuint64_t>(q.cl_n)};
+        cuuint64_t strides[3] = {static_cast<cuuint64_t>(OW * q.es), static_cast<cuuint64_t>(P * q.es),
+                                 static_cast<cuuint64_t>(P * q.N * q.es)};
+        cuuint32_t box[4] = {32, 1, box_cols, 1};
+        cuuint32_t estr[4] = {1, 1, 1, 1};
+        CUresult r = st.encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, q.d, dims, strides, box, estr,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                               CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        return r == CUDA_SUCCESS;
+    }
+    if (q.out_nchw) {
+        // NCHW output of a convolution: {pixels of a plane, channels, images}
+        const long long P = q.g.P;
+        const bool ok = q.es == 2 && q.beta == 0.0f && (reinterpret_cast<uintptr_t>(q.d) & 15u) == 0 &&
+                        (P * q.es) % 16 == 0 && P * q.N * q.es < (1ll << 40) && !(g_force_generic.load() & 0x4000);
+        if (!ok) return false;
+        cuuint64_t dims[3] = {static_cast<cuuint64_t>(P), static_cast<cuuint64_t>(q.N),
+                              static_cast<cuuint64_t>(q.M / P)};
+        cuuint64_t strides[2] = {static_cast<cuuint64_t>(P * q.es), static_cast<cuuint64_t>(P * q.N * q.es)};
+        cuuint32_t box[3] = {32, box_cols, 1};
+        cuuint32_t estr[3] = {1, 1, 1};
+        CUresult r = st.encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, q.d, dims, strides, box, estr,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                               CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        return r == CUDA_SUCCESS;
+    }
     const bool d_ok = q.es == 2 && q.beta == 0.0f && q.betas == nullptr && q.d_offs == nullptr &&
                       (reinterpret_cast<uintptr_t>(q.d) & 15u) == 0 && (q.ldd * q.es) % 16 == 0 &&
                       // measured: a TMA store is clipped at the next 16-byte boundary after the
@@ -639,8 +732,9 @@ int launch(const Problem& q, cudaStream_t stream, DeviceState* preset = nullptr)
         return kInvalidDimension;
 
     const bool use_tma = q.es == 2 && !(g_force_generic.load() & 0xff) && q.a_offs == nullptr &&
-                         tma_ok(q.a, q.es, q.M, q.K, q.batch) &&
+                         (q.a_cl != 0 || tma_ok(q.a, q.es, q.M, q.K, q.batch)) &&
                          tma_ok(q.b, q.es, q.N, q.K, q.batch);
+    if (q.a_cl != 0 && !use_tma) return kNotImplemented;
     // A through tensor memory: every convolution and every fp32 product (see contraction_ts.cuh)
     const int force_path = g_force_generic.load() & 0xff;
     if (force_path != 2 && !q.no_ts && !use_tma && (q.a.im2col || q.es == 4 || force_path == 3)) {
@@ -656,7 +750,8 @@ int launch(const Problem& q, cudaStream_t stream, DeviceState* preset = nullptr)
 
     // CTA pairs (cta_group::2): 256 x 256 tiles, each CTA stages 128 rows of A and 128 of B, so
     // a third less shared-memory fill per flop than a lone 128 x 256 tile.
-    if (use_tma && bn == 256 && q.M > kBM && st->max_pair_clusters > 0 && (g_force_generic.load() & 0x200)) {
+    if (use_tma && bn == 256 && q.M > kBM && st->max_pair_clusters > 0 && (g_force_generic.load() & 0x200) &&
+        q.a_cl == 0 && q.out_nchw == 0) {
         const long long ptiles_m = (q.M + 2 * kBM - 1) / (2 * kBM);
         const long long ptiles_n = (q.N + bn - 1) / bn;
         const long long ptotal = q.batch * ptiles_m * ptiles_n;
@@ -756,6 +851,11 @@ int launch(const Problem& q, cudaStream_t stream, DeviceState* preset = nullptr)
     p.g = q.g;
     p.status = st->status;
     p.d_f32 = q.d_f32 ? 1 : 0;
+    p.a_cl = q.a_cl;
+    p.cl_cblocks = q.cl_cblocks;
+    p.out_nchw = q.out_nchw;
+    p.cl_tpr = q.cl_tpr;
+    p.cl_rstep = q.cl_rstep;
     set_wait_policy(p, total);
 
     CUtensorMap tm_a, tm_b, tm_d;
@@ -764,7 +864,9 @@ int launch(const Problem& q, cudaStream_t stream, DeviceState* preset = nullptr)
     std::memset(&tm_d, 0, sizeof(tm_d));
     p.d_tma = 0;
     if (use_tma) {
-        rc = encode_map(*st, &tm_a, q.a, q.es, q.M, q.K, q.batch, kBM);
+        rc = q.a_cl == 1   ? encode_im2col_map(*st, &tm_a, q)
+             : q.a_cl == 2 ? encode_small_map(*st, &tm_a, q)
+                           : encode_map(*st, &tm_a, q.a, q.es, q.M, q.K, q.batch, kBM);
         if (rc != kSuccess) return rc;
         rc = encode_map(*st, &tm_b, q.b, q.es, q.N, q.K, q.batch, bn);
         if (rc != kSuccess) return rc;
@@ -1225,8 +1327,8 @@ int dlf_b200_gemm_batched_noalloc(int dtype, int layout, int trans_a, int trans_
     return launch(q, s, &nd->st);
 }
 
-size_t dlf_b200_conv2d_workspace_bytes(int dtype, size_t, size_t channels, size_t, size_t, size_t,
-                                       size_t, size_t num_kernels, size_t group, size_t kernel_h,
+size_t dlf_b200_conv2d_workspace_bytes(int dtype, size_t batches, size_t channels, size_t height, size_t width,
+                                       size_t, size_t, size_t num_kernels, size_t group, size_t kernel_h,
                                        size_t kernel_w) {
     // Optional scratch: the filter bank re-laid as the kernel's shared-memory stage images (a few
     // hundred KB to a few MB). The im2col matrix itself is never materialised. An upper bound over
@@ -1241,7 +1343,21 @@ size_t dlf_b200_conv2d_workspace_bytes(int dtype, size_t, size_t channels, size_
     // become ceil-ish KW/sw shifts), output channels padded to the tile's channel count
     const size_t row = group * ((ng + 255) / 256 * 256 + 256) * 128 * dup *
                        ((cg * kernel_h * (kernel_w + 8) + bk - 1) / bk + 8);
-    return (plain > row ? plain : row) + 256;
+    size_t need = (plain > row ? plain : row) + 256;
+    // channels-last route (16-bit, one group): channels-last copy of the activations plus the
+    // filter bank in (tap, channel) order
+    if (es == 2 && group == 1) {
+        const size_t cp = (channels + 7) / 8 * 8, ck = (channels + 63) / 64 * 64;
+        const size_t cl = batches * height * width * cp * 2 + num_kernels * kernel_h * kernel_w * ck * 2 + 4096;
+        if (cl > need) need = cl;
+        if (channels <= 4) {
+            // bordered row-pair copy: at most (H + 2*KH + 2) row pairs of (W + 2*KW + 10) pixels of 16 bytes per image
+            const size_t small = batches * (height + 2 * kernel_h + 2) * (width + 2 * kernel_w + 10) * 16 +
+                                 num_kernels * (kernel_h + 1) / 2 * 128 + 4096;
+            if (small > need) need = small;
+        }
+    }
+    return need;
 }
 
 int dlf_b200_conv2d_fused(int dtype, size_t batches, size_t channels, size_t height, size_t width,
@@ -1352,6 +1468,191 @@ int dlf_b200_conv2d_fused(int dtype, size_t batches, size_t channels, size_t hei
     q.g.img_stride = static_cast<long long>(channels) * height * width;
     q.g.out_img_stride = static_cast<long long>(num_kernels) * P;
     if (P > INT_MAX) return kInvalidDimension;
+
+    // Filters over at most 4 input channels and at most 8 taps per row (the 7x7 stride-2 RGB stem
+    // of a ResNet): bordered row-pair copy + tiled tensor map whose windows overlap, see
+    // channels_last.cuh. One M-tile is 128 outputs of one output row.
+    {
+        const int tune = g_force_generic.load();
+        const int cl_neutral = 0x100 | 0x4000 | 0x10000000 | 0x20000000;
+        const long long kb2 = (static_cast<long long>(kernel_h) + 1) / 2;
+        const long long rstep = stride_h % 2 == 0 ? 2 : 1;
+        const long long jn = ((static_cast<long long>(output_h) - 1) * stride_h + 2 * (kb2 - 1)) / rstep + 1;  // row pairs
+        const long long wp = (static_cast<long long>(output_w) - 1) * stride_w + 8;
+        const size_t w_bytes = (static_cast<size_t>(num_kernels) * kb2 * 128 + 1023) / 1024 * 1024;
+        const size_t x_bytes = static_cast<size_t>(batches) * jn * wp * 16;
+        unsigned char* ws = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(workspace) + 255u) & ~uintptr_t(255));
+        const size_t slack = static_cast<size_t>(ws - static_cast<unsigned char*>(workspace));
+        const long long tpr = (static_cast<long long>(output_w) + kBM - 1) / kBM;
+        const long long rows = static_cast<long long>(batches) * output_h;
+        if (q.es == 2 && group == 1 && channels <= 4 && (tune & ~cl_neutral) == 0 && workspace != nullptr &&
+            workspace_bytes >= slack + w_bytes + x_bytes && kernel_w <= 8 && stride_w <= 64 && stride_h <= 64 &&
+            dilation_h == 1 && dilation_w == 1 && rows * tpr < (INT_MAX - 512) / kBM && jn < (1 << 28) && wp < (1 << 27) &&
+            pad_top < (1u << 28) && pad_left < (1u << 28)) {
+            DeviceState* st = nullptr;
+            int rc = ensure_device(&st);
+            if (rc != kSuccess) return rc;
+            clear_stale_error();
+            cudaStream_t cs = static_cast<cudaStream_t>(stream);
+            uint16_t* wpk = reinterpret_cast<uint16_t*>(ws);
+            uint4* xp = reinterpret_cast<uint4*>(ws + w_bytes);
+            const long long total = static_cast<long long>(batches) * jn * wp;
+            const unsigned xblocks = static_cast<unsigned>(std::min<long long>((total + 255) / 256, 32ll * st->num_sms));
+            cl_pack_small_activations_kernel<<<xblocks, 256, 0, cs>>>(
+                static_cast<const uint16_t*>(x), xp, static_cast<int>(channels), static_cast<int>(height),
+                static_cast<int>(width), static_cast<int>(jn), static_cast<int>(wp), static_cast<int>(rstep),
+                static_cast<int>(pad_top), static_cast<int>(pad_left), total);
+            g_launches.fetch_add(1);
+            CUDA_TRY(cudaGetLastError());
+            const long long wtotal = static_cast<long long>(num_kernels) * kb2 * 64;
+            cl_pack_small_filters_kernel<<<static_cast<unsigned>(std::min<long long>((wtotal + 255) / 256, 8ll * st->num_sms)), 256, 0, cs>>>(
+                static_cast<const uint16_t*>(w), wpk, static_cast<int>(num_kernels), static_cast<int>(channels),
+                static_cast<int>(kernel_h), static_cast<int>(kernel_w), static_cast<int>(kb2));
+            g_launches.fetch_add(1);
+            CUDA_TRY(cudaGetLastError());
+            Problem r = q;
+            r.batch = 1;
+            r.M = rows * tpr * kBM;  // tiles x 128 rows; rows beyond OW of a tile are not outputs
+            r.N = static_cast<long long>(num_kernels);
+            r.K = kb2 * 64;
+            r.a.base = reinterpret_cast<const char*>(xp);
+            r.a.im2col = 0;
+            r.a.k_major = 1;
+            r.a.ld = 0;
+            r.a.batch_stride = 0;
+            r.b.base = reinterpret_cast<const char*>(wpk);
+            r.b.k_major = 1;
+            r.b.ld = r.K;
+            r.b.batch_stride = 0;
+            r.d_batch_stride = 0;
+            r.bias_stride = 0;
+            r.out_nchw = 2;
+            r.a_cl = 2;
+            r.cl_tpr = static_cast<int>(tpr);
+            r.cl_n = static_cast<long long>(batches);
+            r.cl_h = jn;
+            r.cl_w = wp;
+            r.cl_rstep = static_cast<int>(rstep);
+            r.pack_ws = nullptr;
+            r.pack_ws_bytes = 0;
+            rc = launch(r, cs, st);
+            if (rc != kNotImplemented) return rc;
+        }
+    }
+
+    // Channels-last route (channels_last.cuh): 16-bit, one group, enough scratch. The activations are
+    // copied into scratch as (N, H, W, C'), after which the tensor-map unit feeds the operand by
+    // itself: im2col-mode loads for general filters (one load = 128 filter windows x 64 channels of
+    // one tap), plain tiled loads for 1x1 filters (the copy then keeps only the pixels the strides
+    // select, and the convolution is one GEMM over all images). The reference's Xconvgemm gathers
+    // the same operand element by element (kernels/levelx/xconvgemm_part1.cl:26-117).
+    {
+        const int tune = g_force_generic.load();
+        const bool pointwise = kernel_h == 1 && kernel_w == 1 && pad_top == 0 && pad_left == 0 &&
+                               (output_h - 1) * stride_h < height && (output_w - 1) * stride_w < width;
+        const long long taps = static_cast<long long>(kernel_h) * kernel_w;
+        const long long cp = (static_cast<long long>(channels) + 7) / 8 * 8;
+        const bool w_direct = pointwise && channels % 8 == 0 && (reinterpret_cast<uintptr_t>(w) & 15u) == 0;
+        const long long ck = pointwise ? cp : (static_cast<long long>(channels) + 63) / 64 * 64;
+        const long long xh = pointwise ? static_cast<long long>(output_h) : static_cast<long long>(height);
+        const long long xw = pointwise ? static_cast<long long>(output_w) : static_cast<long long>(width);
+        const size_t w_bytes = w_direct ? 0 : (static_cast<size_t>(num_kernels) * taps * ck * 2 + 1023) / 1024 * 1024;
+        const size_t x_bytes = static_cast<size_t>(batches) * xh * xw * cp * 2;
+        unsigned char* ws = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(workspace) + 255u) & ~uintptr_t(255));
+        const size_t slack = static_cast<size_t>(ws - static_cast<unsigned char*>(workspace));
+        // a filter with few channels would spend most of each 64-channel k-block on zeros
+        const bool dense_k = pointwise || channels * 2 >= static_cast<size_t>(ck);
+        // 1x1 filters: the transposing copy costs a pass over the input, repaid by the output side
+        // (tensor-map stores, no per-element gather) only when the layer widens (measured on the
+        // ResNet-50 shapes: 256->1024 at 14x14 99 -> 74 us, 1024->256 70 -> 90 us)
+        const bool widens = !pointwise || num_kernels >= 2 * channels;
+        // every measurement / forcing bit that addresses the other convolution kernels (and the
+        // route's own off switch, 0x40000000) keeps the call on those kernels
+        const int cl_neutral = 0x100 | 0x4000 | 0x10000000 | 0x20000000;
+        if (q.es == 2 && group == 1 && (tune & ~cl_neutral) == 0 && workspace != nullptr &&
+            workspace_bytes >= slack + w_bytes + x_bytes && dense_k && widens && batches < 65536 && cp < 65536ll * 64 &&
+            (pointwise || (dilation_h * (kernel_h - 1) < 256 && dilation_w * (kernel_w - 1) < 256 && stride_h <= 8 &&
+                           stride_w <= 8)) &&
+            q.M < INT_MAX - 512 && taps * ck < INT_MAX - 512) {
+            DeviceState* st = nullptr;
+            int rc = ensure_device(&st);
+            if (rc != kSuccess) return rc;
+            if (pointwise || st->encode_im2col != nullptr) {
+                clear_stale_error();
+                cudaStream_t cs = static_cast<cudaStream_t>(stream);
+                uint16_t* wp = reinterpret_cast<uint16_t*>(ws);
+                uint16_t* xp = reinterpret_cast<uint16_t*>(ws + w_bytes);
+                const long long xpix = xh * xw;
+                dim3 grid(static_cast<unsigned>((xpix + kClTile - 1) / kClTile), static_cast<unsigned>((cp + kClTile - 1) / kClTile),
+                          static_cast<unsigned>(batches));
+                const uint16_t* xs = static_cast<const uint16_t*>(x);
+                const long long plane = static_cast<long long>(height) * width;
+                const long long total = static_cast<long long>(batches) * channels * plane;
+                const uintptr_t xa = reinterpret_cast<uintptr_t>(x);
+                const int ci = static_cast<int>(channels), cpi = static_cast<int>(cp);
+                if (!pointwise || (stride_h == 1 && stride_w == 1)) {
+                    // whole planes (a 1x1 filter with unit strides keeps every pixel): one row of `plane` pixels
+                    const int pl = static_cast<int>(plane);
+                    if (plane % 8 == 0 && xa % 16 == 0)
+                        cl_pack_activations_kernel<CL_VEC8><<<grid, 256, 0, cs>>>(xs, xp, ci, plane, pl, 1, pl, 1, 1, cpi, total);
+                    else if (plane % 4 == 0 && xa % 8 == 0)
+                        cl_pack_activations_kernel<CL_VEC4><<<grid, 256, 0, cs>>>(xs, xp, ci, plane, pl, 1, pl, 1, 1, cpi, total);
+                    else if (plane % 2 == 0 && xa % 4 == 0)
+                        cl_pack_activations_kernel<CL_VEC2><<<grid, 256, 0, cs>>>(xs, xp, ci, plane, pl, 1, pl, 1, 1, cpi, total);
+                    else
+                        cl_pack_activations_kernel<CL_FUNNEL><<<grid, 256, 0, cs>>>(xs, xp, ci, plane, pl, 1, pl, 1, 1, cpi, total);
+                } else {
+                    const int wi = static_cast<int>(width), ohi = static_cast<int>(output_h), owi = static_cast<int>(output_w);
+                    const int shi = static_cast<int>(stride_h), swi = static_cast<int>(stride_w);
+                    const long long row_bytes = static_cast<long long>(stride_h) * width * 2;
+                    const bool s2 = stride_w == 2 && 2 * output_w <= width;
+                    if (s2 && output_w % 4 == 0 && row_bytes % 16 == 0 && (plane * 2) % 16 == 0 && xa % 16 == 0)
+                        cl_pack_activations_kernel<CL_S2_VEC4><<<grid, 256, 0, cs>>>(xs, xp, ci, plane, wi, ohi, owi, shi, swi, cpi, total);
+                    else if (s2 && output_w % 2 == 0 && row_bytes % 8 == 0 && (plane * 2) % 8 == 0 && xa % 8 == 0)
+                        cl_pack_activations_kernel<CL_S2_VEC2><<<grid, 256, 0, cs>>>(xs, xp, ci, plane, wi, ohi, owi, shi, swi, cpi, total);
+                    else
+                        cl_pack_activations_kernel<CL_ANY><<<grid, 256, 0, cs>>>(xs, xp, ci, plane, wi, ohi, owi, shi, swi, cpi, total);
+                }
+                g_launches.fetch_add(1);
+                CUDA_TRY(cudaGetLastError());
+                if (!w_direct) {
+                    const long long total = static_cast<long long>(num_kernels) * ck;
+                    const unsigned blocks = static_cast<unsigned>(std::min<long long>((total + 255) / 256, 8ll * st->num_sms));
+                    cl_pack_filters_kernel<<<blocks, 256, 0, cs>>>(static_cast<const uint16_t*>(w), wp,
+                                                                  static_cast<int>(num_kernels), static_cast<int>(channels),
+                                                                  static_cast<int>(taps), static_cast<int>(ck));
+                    g_launches.fetch_add(1);
+                    CUDA_TRY(cudaGetLastError());
+                }
+                Problem r = q;
+                r.batch = 1;
+                r.N = static_cast<long long>(num_kernels);
+                r.K = w_direct ? static_cast<long long>(channels) : taps * ck;
+                r.a.base = reinterpret_cast<const char*>(xp);
+                r.a.im2col = 0;
+                r.a.k_major = 1;
+                r.a.ld = cp;
+                r.a.batch_stride = 0;
+                r.b.base = w_direct ? static_cast<const char*>(w) : reinterpret_cast<const char*>(wp);
+                r.b.k_major = 1;
+                r.b.ld = r.K;
+                r.b.batch_stride = 0;
+                r.d_batch_stride = 0;
+                r.bias_stride = 0;
+                r.out_nchw = 1;
+                r.a_cl = pointwise ? 0 : 1;
+                r.cl_cblocks = static_cast<int>(ck / 64);
+                r.cl_n = static_cast<long long>(batches);
+                r.cl_h = xh;
+                r.cl_w = xw;
+                r.cl_cp = cp;
+                r.pack_ws = nullptr;
+                r.pack_ws_bytes = 0;
+                rc = launch(r, cs, st);
+                if (rc != kNotImplemented) return rc;
+            }
+        }
+    }
 
     // Row form (see contraction_ts.cuh): horizontal taps become output columns of the GEMM. With
     // stride_w = sw the input columns split into sw phases that join the channels in K, and the

@@ -103,6 +103,17 @@ struct Params {
                  // beta == 0 and TMA-compatible strides: the epilogue stages
                  // 32 x 32 blocks in shared memory and writes them with TMA stores
     int d_f32;   // 16-bit operands, but D is written as fp32 (partial products of a K-split GEMM)
+    // Channels-last route of a convolution: operand A is a channels-last (N, H, W, C) copy of the
+    // activations. a_cl == 1: tmA is an im2col-mode tensor map; k-block kb is channel block
+    // kb % cl_cblocks of filter tap kb / cl_cblocks and one load brings the tile's 128 windows.
+    // out_nchw: row i of the problem is output pixel img * P + pp and lands in an NCHW tensor
+    // (the output mapping of the implicit-im2col operand, whatever A is).
+    // a_cl == 2 (filters over <= 4 channels, see channels_last.cuh): tmA is a tiled map over the
+    // bordered row-pair copy; an M-tile is 128 consecutive outputs of one output row (cl_tpr tiles
+    // per row, rows (image, oh)), k-block kb covers filter rows 2*kb, 2*kb+1, i.e. row pair
+    // (oh*sh + 2*kb) / cl_rstep of the copy; out_nchw == 2 is the matching output mapping (tmD is
+    // then the 4-D map {OW, OH, channels, images}).
+    int a_cl, cl_cblocks, out_nchw, cl_tpr, cl_rstep;
     long long wait_limit;  // SM clocks a bounded wait may take (see ptx::mbar_wait_bounded)
     int skip_tile_commit;  // test aid: the UMMA issuer leaves out the commit that hands a finished
                            // accumulator to the epilogue, so that the epilogue's wait runs out
@@ -341,10 +352,21 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
             ptx::tc_fence_after();
 
             const int i = m0 + q * 32 + lane;
-            const bool row_ok = i < p.M;
+            bool row_ok = i < p.M;
             long long rowbase;
             long long colstride;
-            if (p.a.im2col) {
+            int rt_n = 0, rt_oh = 0, rt_ow0 = 0;  // out_nchw == 2: image, output row, first column of the tile
+            if (p.out_nchw == 2) {
+                const int mt = m0 / kBM;
+                const int rowid = mt / p.cl_tpr;
+                rt_ow0 = (mt - rowid * p.cl_tpr) * kBM;
+                rt_n = rowid / p.g.OH;
+                rt_oh = rowid - rt_n * p.g.OH;
+                const int ow = rt_ow0 + q * 32 + lane;
+                row_ok = ow < p.g.OW;
+                rowbase = static_cast<long long>(rt_n) * p.g.out_img_stride + static_cast<long long>(rt_oh) * p.g.OW + ow;
+                colstride = p.g.P;
+            } else if (p.a.im2col || p.out_nchw) {
                 const int img = i / p.g.P;
                 const int pp = i - img * p.g.P;
                 rowbase = static_cast<long long>(img) * p.g.out_img_stride +
@@ -365,13 +387,20 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
             if constexpr (USE_TMA) {
                 if (p.d_tma) {
                     const int i0 = m0 + q * 32;
+                    // NCHW output: a block of 32 pixels is one box of the {P, channels, images} map
+                    // unless it runs over the end of its image; such a block (and only it) is
+                    // written by the lanes themselves
+                    const int img0 = p.out_nchw == 1 ? i0 / p.g.P : 0;
+                    const int pp0 = p.out_nchw == 1 ? i0 - img0 * p.g.P : i0;
+                    const bool direct = p.out_nchw == 1 && pp0 + 32 > p.g.P;
+                    const bool blk_ok = p.out_nchw == 2 ? (rt_ow0 + q * 32 < p.g.OW) : (i0 < p.M);
                     // Blocks of 32 rows x 32 columns go to one of the warp's two staging buffers
                     // (2 KB each, adjacent). With 32-column boxes the buffers alternate and every
                     // block is one TMA store; with 64-column boxes (tiles of 128 columns or more)
                     // two consecutive blocks fill both buffers and leave as one 4 KB store: TMA
                     // stores this small are bound by their number, not their bytes.
                     const bool wide = p.d_tma == 64;
-                    for (int c0 = 0; c0 < ncols && i0 < p.M; c0 += 32, ++chunk_no) {
+                    for (int c0 = 0; c0 < ncols && blk_ok; c0 += 32, ++chunk_no) {
                         uint32_t v[32];
                         ptx::tmem_ld_32x32(trow + c0, v);
                         ptx::tmem_ld_wait();
@@ -407,6 +436,19 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
                         // the clamp only exists under ReLU: fmaxf drops a NaN operand, so an
                         // unconditional fmaxf(r, -inf) would turn NaN results into -inf
                         const bool relu = p.relu != 0;
+                        if (direct) {
+                            char* op = optr + static_cast<long long>(c0) * colstride * 2;
+#pragma unroll
+                            for (int jj = 0; jj < 32; ++jj) {
+                                float r = __uint_as_float(v[jj]) + __shfl_sync(0xffffffffu, bv, jj);
+                                r = relu ? fmaxf(r, 0.0f) : r;
+                                if (row_ok && c0 + jj < ncols) {
+                                    if (p.fmt == FMT_F16) out_store<OUT_F16>(op + jj * colstride * 2, r);
+                                    else out_store<OUT_BF16>(op + jj * colstride * 2, r);
+                                }
+                            }
+                            continue;
+                        }
                         if (p.fmt == FMT_F16) {
 #pragma unroll
                             for (int jj = 0; jj < 32; ++jj) {
@@ -430,8 +472,12 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
                         ptx::fence_proxy_async_smem();
                         __syncwarp();
                         if (lane == 0) {
-                            ptx::tma_store_3d(&tmD, ptx::smem_u32(d_stage) + (ewarp * 2 + (wide ? 0u : half)) * 2048u, i0,
-                                              n0 + cb + (wide ? (c0 & ~63) : c0), p.d_batch_stride ? b : 0);
+                            const uint32_t ssrc = ptx::smem_u32(d_stage) + (ewarp * 2 + (wide ? 0u : half)) * 2048u;
+                            const int col = n0 + cb + (wide ? (c0 & ~63) : c0);
+                            if (p.out_nchw == 2)
+                                ptx::tma_store_4d(&tmD, ssrc, rt_ow0 + q * 32, rt_oh, col, rt_n);
+                            else
+                                ptx::tma_store_3d(&tmD, ssrc, pp0, col, p.out_nchw == 1 ? img0 : (p.d_batch_stride ? b : 0));
                             ptx::bulk_commit_group();
                         }
                     }
@@ -562,6 +608,16 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
                 n0 += PAIR ? static_cast<int>(rank) * b_rows : 0;  // this CTA's share of the Bu rows
                 const int ba = p.a.batch_stride ? b : 0;
                 const int bb = p.b.batch_stride ? b : 0;
+                // im2col-mode loads: base pixel of the tile's first filter window
+                int cl_n = 0, cl_h = 0, cl_w = 0;
+                if (!PAIR && p.a_cl == 1) {
+                    cl_n = m0 / p.g.P;
+                    const int pp = m0 - cl_n * p.g.P;
+                    const int oh = pp / p.g.OW;
+                    cl_h = oh * p.g.sh - p.g.pad_t;
+                    cl_w = (pp - oh * p.g.OW) * p.g.sw - p.g.pad_l;
+                }
+                int cl_cb = 0, cl_kh = 0, cl_kw = 0;  // channel block and filter tap of kb
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!ptx::mbar_wait_bounded(ptx::smem_u32(&empty_bar[stage]), phase ^ 1u,
                                                 abort_p, wait_limit)) {
@@ -570,6 +626,41 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
                     }
                     const uint32_t sA = smem0 + stage * stage_bytes;
                     const uint32_t sB = sA + A_TILE;
+                    if (!PAIR && p.a_cl == 2) {
+                        const uint32_t bar = ptx::smem_u32(&full_bar[stage]);
+                        ptx::mbar_arrive_expect_tx(bar, A_TILE + b_tile);
+                        const int mt = m0 / kBM;
+                        const int rowid = mt / p.cl_tpr;
+                        const int n = rowid / p.g.OH;
+                        ptx::tma_load_4d(sA, &tmA, bar, 0, (mt - rowid * p.cl_tpr) * kBM,
+                                         ((rowid - n * p.g.OH) * p.g.sh + 2 * kb) / p.cl_rstep, n);
+                        ptx::tma_load_3d(sB, &tmB, bar, kb * BK, n0, bb);
+                        if (++stage == static_cast<uint32_t>(S)) {
+                            stage = 0;
+                            phase ^= 1u;
+                        }
+                        continue;
+                    }
+                    if (!PAIR && p.a_cl == 1) {
+                        const uint32_t bar = ptx::smem_u32(&full_bar[stage]);
+                        ptx::mbar_arrive_expect_tx(bar, A_TILE + b_tile);
+                        ptx::tma_load_im2col_4d(sA, &tmA, bar, cl_cb * BK, cl_w, cl_h, cl_n,
+                                                static_cast<unsigned short>(cl_kw * p.g.dw),
+                                                static_cast<unsigned short>(cl_kh * p.g.dh));
+                        ptx::tma_load_3d(sB, &tmB, bar, kb * BK, n0, bb);
+                        if (++cl_cb == p.cl_cblocks) {
+                            cl_cb = 0;
+                            if (++cl_kw == p.g.KW) {
+                                cl_kw = 0;
+                                ++cl_kh;
+                            }
+                        }
+                        if (++stage == static_cast<uint32_t>(S)) {
+                            stage = 0;
+                            phase ^= 1u;
+                        }
+                        continue;
+                    }
                     if constexpr (PAIR) {
                         // both CTAs' copies are counted on rank 0's barrier, which rank 0 arms
                         // with the bytes of the two CTAs together

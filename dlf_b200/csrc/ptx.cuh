@@ -101,6 +101,23 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
         : "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
         : "memory");
 }
+// Tiled-mode's sibling for convolutions: an im2col-mode load over a channels-last (N, H, W, C)
+// tensor. Starting at base pixel (w, h, n) - the top-left corner of an output's filter window - it
+// walks `pixelsPerColumn` windows along W, then H, then N (steps = the traversal strides of the
+// map, wrapping at the map's bounding box) and for each fetches `channelsPerPixel` channels from
+// c0 of the pixel at (+off_w, +off_h) inside the window, zero where that pixel is outside the
+// image. The result is the K-major operand tile [pixel][channel] (swizzled as the map says).
+__device__ __forceinline__ void tma_load_im2col_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                                   int c0, int w, int h, int n, unsigned short off_w,
+                                                   unsigned short off_h) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};"
+        :
+        : "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(w), "r"(h), "r"(n),
+          "h"(off_w), "h"(off_h)
+        : "memory");
+}
 // Untiled bulk copy global -> shared (both 16-byte aligned, size a multiple of 16), completing on
 // an mbarrier of this CTA.
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
@@ -108,6 +125,22 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
         "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
         :
         : "r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int c0, int c1, int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        :
+        : "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+        :
+        : "l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
         : "memory");
 }
 // Tiled TMA store shared -> global (clipped at the tensor's bounds), tracked by bulk groups.

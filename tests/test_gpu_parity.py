@@ -624,12 +624,28 @@ CONV_CASES = [
     (2, 36, 25, 21, 36, 5, 7, (3, 0, 1, 3), (1, 1), (2, 1), 1),     # row form, 7 taps x 32 channels = 224 columns: in fp32 four stages would overflow shared memory by the table padding
     (3, 96, 7, 7, 32, 7, 7, (3, 1, 1, 1), (1, 1), (1, 1), 1),       # row form, K' = 672 chunked in fp32 with 7 taps x 16 channels = 112 columns: the sum array is not a multiple of 32 columns
     (2, 120, 9, 10, 24, 5, 5, (2, 2, 2, 2), (1, 1), (1, 1), 1),     # same with 5 taps x 16 channels = 80 columns
+    (3, 70, 7, 7, 150, 1, 1, (0, 0, 0, 0), (1, 1), (1, 1), 1),      # widening 1x1 on odd planes, 70 channels: channels-last copy by funnel shifts, repacked filters
+    (2, 24, 9, 9, 64, 1, 1, (0, 0, 0, 0), (2, 2), (1, 1), 1),       # widening 1x1 stride 2, odd output width: per-pixel copy
+    (2, 64, 17, 12, 136, 1, 1, (0, 0, 0, 0), (2, 2), (1, 1), 1),    # widening 1x1 stride 2, OW = 6: copy in groups of two kept pixels
+    (2, 64, 9, 16, 128, 1, 1, (0, 0, 0, 0), (1, 2), (1, 1), 1),     # widening 1x1, stride_w 2 only, OW = 8: groups of four
+    (2, 64, 15, 15, 40, 3, 3, (1, 1, 1, 1), (2, 2), (1, 1), 1),     # 3x3 stride 2, 64 channels: im2col-mode loads with traversal strides
+    (2, 4, 13, 18, 24, 2, 4, (0, 1, 1, 2), (1, 2), (1, 1), 1),      # 4 channels, even KH, KW = 4, stride_w 2: small-channel route
+    (1, 1, 9, 30, 8, 3, 8, (1, 3, 1, 3), (3, 4), (1, 1), 1),        # 1 channel, KW = 8, strides (3, 4)
+    (1, 3, 6, 530, 16, 3, 3, (1, 1, 1, 1), (1, 2), (1, 1), 1),      # 3 channels, 265 outputs per row: three tiles per row
 ]
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+# 16-bit convolutions of one group take the channels-last route (transposing copy + tensor-map-fed
+# operand) when the caller passes scratch; tuning bit 0x40000000 keeps them on the kernels that
+# gather the operand themselves. Both are the product (the second serves callers without scratch).
+ROUTES = [(torch.float32, 0), (torch.float16, 0), (torch.float16, 0x40000000), (torch.bfloat16, 0),
+          (torch.bfloat16, 0x40000000)]
+ROUTE_IDS = ["f32", "f16-channels-last", "f16-gather", "bf16-channels-last", "bf16-gather"]
+
+
+@pytest.mark.parametrize("dtype,route", ROUTES, ids=ROUTE_IDS)
 @pytest.mark.parametrize("case", CONV_CASES, ids=lambda c: "x".join(map(str, c[:7])))
-def test_conv2d_random_parity(case, dtype):
+def test_conv2d_random_parity(lib, case, dtype, route):
     from dlf_b200 import gdnn
     N, C, H, W, Co, KH, KW, pads, strides, dil, group = case
     rng = np.random.default_rng(abs(hash(case)) % (2 ** 32))
@@ -642,8 +658,12 @@ def test_conv2d_random_parity(case, dtype):
     filt = gdnn.Filter2D(X.shape, Wt.shape, group).pads(*pads).strides(*strides).dilations(*dil)
     assert tuple(filt.output_shape()) == ref.shape
     Y = torch.full(ref.shape, float("nan"), dtype=dtype, device="cuda")
-    gdnn.conv2d_filter(torch.from_numpy(X).to(dtype).cuda(), torch.from_numpy(Wt).to(dtype).cuda(),
-                       Y, filt, bias=torch.from_numpy(bias).to(dtype).cuda())
+    lib.set_tuning(0, route)
+    try:
+        gdnn.conv2d_filter(torch.from_numpy(X).to(dtype).cuda(), torch.from_numpy(Wt).to(dtype).cuda(),
+                           Y, filt, bias=torch.from_numpy(bias).to(dtype).cuda())
+    finally:
+        lib.set_tuning(0, 0)
     got = Y.float().cpu().numpy()
     if dtype == torch.float32:
         assert rel_fro(got, ref) <= FP32_TOL
@@ -656,8 +676,9 @@ def _resnet_shapes():
     return RESNET50_SHAPES
 
 
+@pytest.mark.parametrize("route", [0, 0x40000000], ids=["channels-last", "gather"])
 @pytest.mark.parametrize("shape", _resnet_shapes(), ids=lambda c: "x".join(map(str, c[:6])))
-def test_conv2d_resnet50_layer_shapes_vs_oracle(shape):
+def test_conv2d_resnet50_layer_shapes_vs_oracle(lib, shape, route):
     """BASELINE config 3 at its real layer shapes: every one of the 20 distinct ResNet-50 v1
     convolutions (224 x 224 input), fp16 with bias, two images, against the oracle with a wide
     accumulator. Inputs follow the configuration: activations |N(0,1)|, He-normal weights."""
@@ -671,8 +692,12 @@ def test_conv2d_resnet50_layer_shapes_vs_oracle(shape):
     ref = oracle.conv2d(X, Wt, pads=(p,) * 4, strides=(s, s), bias=bias, wide=True)
     filt = gdnn.Filter2D(X.shape, Wt.shape).pads(p, p).strides(s, s)
     Y = torch.full(ref.shape, float("nan"), dtype=torch.float16, device="cuda")
-    gdnn.conv2d_filter(torch.from_numpy(X).half().cuda(), torch.from_numpy(Wt).half().cuda(), Y, filt,
-                       bias=torch.from_numpy(bias).half().cuda())
+    lib.set_tuning(0, route)
+    try:
+        gdnn.conv2d_filter(torch.from_numpy(X).half().cuda(), torch.from_numpy(Wt).half().cuda(), Y, filt,
+                           bias=torch.from_numpy(bias).half().cuda())
+    finally:
+        lib.set_tuning(0, 0)
     assert max_rel(Y.float().cpu().numpy(), ref) <= HALF_TOL
 
 
@@ -763,7 +788,7 @@ def test_conv2d_output_store_modes_agree(lib, case, dtype):
     R = torch.from_numpy(_rand(rng, f.output_shape(), "normal")).to(dtype).cuda()
     for fused in (False, True):
         outs = []
-        for flags in (0, 128 << 16):
+        for flags in (0x40000000, 128 << 16):  # both on the row-form kernel (0x40000000: not the channels-last route)
             buf = torch.full((n_out + 64,), 3.0, dtype=dtype, device="cuda")  # guard band on both sides
             Y = buf[32:32 + n_out].view(f.output_shape())
             lib.set_tuning(0, flags)
@@ -802,7 +827,7 @@ def test_conv2d_pointwise_table_lookup_matches_affine(lib, dtype):
         Wt = torch.from_numpy((0.1 * rng.normal(size=(Co, C // group, KH, KW))).astype(np.float32)).to(dtype).cuda()
         filt = gdnn.Filter2D(X.shape, Wt.shape, group).pads(*pads).strides(*strides).dilations(*dil)
         outs = []
-        for flags in (0, 0x2000):
+        for flags in (0x40000000, 0x2000):  # both on the gathering kernel
             lib.set_tuning(0, flags)
             try:
                 Y = torch.full(filt.output_shape(), float("nan"), dtype=dtype, device="cuda")
@@ -824,9 +849,17 @@ FUSED_CASES = [
 ]
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
-@pytest.mark.parametrize("case", FUSED_CASES, ids=lambda c: "x".join(map(str, c[:7])))
-def test_conv2d_fused_residual_relu(lib, case, dtype):
+@pytest.fixture
+def _route(lib, request):
+    lib.set_tuning(0, request.param)
+    yield request.param
+    lib.set_tuning(0, 0)
+
+
+@pytest.mark.parametrize("dtype,_route", ROUTES, ids=ROUTE_IDS, indirect=["_route"])
+@pytest.mark.parametrize("case", FUSED_CASES + [CONV_CASES[13], CONV_CASES[7][:10] + (1,)],
+                         ids=lambda c: "x".join(map(str, c[:7])))
+def test_conv2d_fused_residual_relu(lib, case, dtype, _route):
     """Y = relu(conv(X, W) + bias + R) in one launch, on every epilogue of the library, against
     the oracle's conv -> bias -> Add -> Relu chain; also each part alone, and R aliasing Y."""
     from dlf_b200 import gdnn
@@ -1162,9 +1195,13 @@ def test_conv2d_workspace_bound_covers_the_packed_filter_bank(lib, shape, dtype)
     W = (torch.randn(cout, cin, k, k, device="cuda") * 0.05).to(dtype)
     f = gdnn.Filter2D(X.shape, W.shape).pads(p, p).strides(s, s)
     Y = torch.empty(f.output_shape(), device="cuda", dtype=dtype)
-    n0 = lib.launch_count()
-    gdnn.conv2d_filter(X, W, Y, f)
-    assert lib.launch_count() - n0 == 2
+    lib.set_tuning(0, 0x40000000)  # the kernels that gather the activations themselves
+    try:
+        n0 = lib.launch_count()
+        gdnn.conv2d_filter(X, W, Y, f)
+        assert lib.launch_count() - n0 == 2
+    finally:
+        lib.set_tuning(0, 0)
     lib.set_tuning(0, 0x8000)
     try:
         Y2 = torch.empty_like(Y)
