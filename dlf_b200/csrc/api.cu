@@ -280,6 +280,10 @@ struct Problem {
     // = images, row pairs, bordered row length; cl_rstep rows between pairs), tiles are 128 outputs
     // of one output row
     int a_cl = 0, cl_cblocks = 0, cl_tpr = 0, cl_rstep = 1;
+    // cl_swap: rows of the problem are output channels (a = filter bank), columns are output pixels
+    // (b = the channels-last copy; with a_cl == 1 through the im2col-mode map); out_nchw == 3 and
+    // out_vec = elements per store of one lane
+    int cl_swap = 0, out_vec = 1;
     int out_nchw = 0;
     long long cl_n = 0, cl_h = 0, cl_w = 0, cl_cp = 0;
     bool d_f32 = false;  // 16-bit operands with fp32 output (partial products of a K-split GEMM)
@@ -340,7 +344,7 @@ int encode_map(const DeviceState& st, CUtensorMap* map, const GenOperand& op, in
 // (whatever the caller's right / bottom padding says: the tensor-map unit zero-fills what lies
 // outside the image); the traversal strides are the convolution's strides. Corners are limited to
 // [-128, 127] by the 4-D form of the map.
-int encode_im2col_map(const DeviceState& st, CUtensorMap* map, const Problem& q) {
+int encode_im2col_map(const DeviceState& st, CUtensorMap* map, const Problem& q, const char* base, int windows) {
     if (st.encode_im2col == nullptr) return kNotImplemented;
     const Im2colGeom& g = q.g;
     cuuint64_t dims[4] = {static_cast<cuuint64_t>(q.cl_cp), static_cast<cuuint64_t>(q.cl_w),
@@ -352,8 +356,8 @@ int encode_im2col_map(const DeviceState& st, CUtensorMap* map, const Problem& q)
     for (int i = 0; i < 2; ++i)
         if (lower[i] < -128 || lower[i] > 127 || upper[i] < -128 || upper[i] > 127) return kNotImplemented;
     cuuint32_t estr[4] = {1, static_cast<cuuint32_t>(g.sw), static_cast<cuuint32_t>(g.sh), 1};
-    CUresult r = st.encode_im2col(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, const_cast<char*>(q.a.base), dims, strides,
-                                  lower, upper, 64, kBM, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+    CUresult r = st.encode_im2col(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, const_cast<char*>(base), dims, strides,
+                                  lower, upper, 64, static_cast<cuuint32_t>(windows), estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? kSuccess : kNotImplemented;
@@ -381,6 +385,7 @@ int encode_small_map(const DeviceState& st, CUtensorMap* map, const Problem& q) 
 // Tensor map for TMA stores of the output (blocks of 32 rows x 32 or 64 columns, no swizzle): only when nothing of C has
 // to be read (beta == 0, no per-batch tables) and D's base and strides are 16-byte multiples.
 bool encode_output_map(const DeviceState& st, CUtensorMap* map, const Problem& q, unsigned box_cols) {
+    if (q.out_nchw == 3) return false;  // swapped roles: the lanes write vectors themselves
     if (q.out_nchw == 2) {
         // NCHW output written row by row: {OW, OH, channels, images}, boxes of 32 outputs of one row
         const long long P = q.g.P, OW = q.g.OW;
@@ -732,8 +737,8 @@ int launch(const Problem& q, cudaStream_t stream, DeviceState* preset = nullptr)
         return kInvalidDimension;
 
     const bool use_tma = q.es == 2 && !(g_force_generic.load() & 0xff) && q.a_offs == nullptr &&
-                         (q.a_cl != 0 || tma_ok(q.a, q.es, q.M, q.K, q.batch)) &&
-                         tma_ok(q.b, q.es, q.N, q.K, q.batch);
+                         ((q.a_cl != 0 && !q.cl_swap) || tma_ok(q.a, q.es, q.M, q.K, q.batch)) &&
+                         ((q.a_cl != 0 && q.cl_swap) || tma_ok(q.b, q.es, q.N, q.K, q.batch));
     if (q.a_cl != 0 && !use_tma) return kNotImplemented;
     // A through tensor memory: every convolution and every fp32 product (see contraction_ts.cuh)
     const int force_path = g_force_generic.load() & 0xff;
@@ -856,6 +861,8 @@ int launch(const Problem& q, cudaStream_t stream, DeviceState* preset = nullptr)
     p.out_nchw = q.out_nchw;
     p.cl_tpr = q.cl_tpr;
     p.cl_rstep = q.cl_rstep;
+    p.cl_swap = q.cl_swap;
+    p.out_vec = q.out_vec;
     set_wait_policy(p, total);
 
     CUtensorMap tm_a, tm_b, tm_d;
@@ -864,11 +871,18 @@ int launch(const Problem& q, cudaStream_t stream, DeviceState* preset = nullptr)
     std::memset(&tm_d, 0, sizeof(tm_d));
     p.d_tma = 0;
     if (use_tma) {
-        rc = q.a_cl == 1   ? encode_im2col_map(*st, &tm_a, q)
-             : q.a_cl == 2 ? encode_small_map(*st, &tm_a, q)
-                           : encode_map(*st, &tm_a, q.a, q.es, q.M, q.K, q.batch, kBM);
-        if (rc != kSuccess) return rc;
-        rc = encode_map(*st, &tm_b, q.b, q.es, q.N, q.K, q.batch, bn);
+        if (q.cl_swap) {
+            rc = encode_map(*st, &tm_a, q.a, q.es, q.M, q.K, q.batch, kBM);
+            if (rc != kSuccess) return rc;
+            rc = q.a_cl == 1 ? encode_im2col_map(*st, &tm_b, q, q.b.base, bn)
+                             : encode_map(*st, &tm_b, q.b, q.es, q.N, q.K, q.batch, bn);
+        } else {
+            rc = q.a_cl == 1   ? encode_im2col_map(*st, &tm_a, q, q.a.base, kBM)
+                 : q.a_cl == 2 ? encode_small_map(*st, &tm_a, q)
+                               : encode_map(*st, &tm_a, q.a, q.es, q.M, q.K, q.batch, kBM);
+            if (rc != kSuccess) return rc;
+            rc = encode_map(*st, &tm_b, q.b, q.es, q.N, q.K, q.batch, bn);
+        }
         if (rc != kSuccess) return rc;
         const unsigned box_cols = (bn >= 128 && !(g_force_generic.load() & 0x100)) ? 64 : 32;
         p.d_tma = (!q.d_f32 && encode_output_map(*st, &tm_d, q, box_cols)) ? static_cast<int>(box_cols) : 0;
@@ -1648,6 +1662,29 @@ int dlf_b200_conv2d_fused(int dtype, size_t batches, size_t channels, size_t hei
                 r.cl_cp = cp;
                 r.pack_ws = nullptr;
                 r.pack_ws_bytes = 0;
+                // Swapped roles when the planes allow 16-byte stores: the lanes then hold output
+                // channels and each writes runs of consecutive pixels (an NCHW tensor is contiguous
+                // along pixels), and a tile is 256 pixels wide whatever the channel count, which
+                // halves the filter-bank traffic of layers with 64 or 128 output channels (128 -> 128
+                // 3x3 at 28x28: 93 -> 67 us). With smaller vectors the scattered stores of the 32
+                // lanes cost more than the paired stores of the pixel-per-lane form (256 -> 1024
+                // 1x1 at 14x14: 67 -> 92 us), so those planes stay unswapped.
+                {
+                    const uintptr_t ya = reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(residual);
+                    int vec = 1;
+                    if (P % 8 == 0 && ya % 16 == 0) vec = 8;
+                    else if (P % 4 == 0 && ya % 8 == 0) vec = 4;
+                    else if (P % 2 == 0 && ya % 4 == 0) vec = 2;
+                    const bool want = (tune & 0x100) ? vec > 1 : vec == 8;  // 0x100: measurement, swap with any vector
+                    if (want && P >= 32) {
+                        std::swap(r.a, r.b);
+                        r.M = static_cast<long long>(num_kernels);
+                        r.N = q.M;  // output pixels of all images
+                        r.cl_swap = 1;
+                        r.out_nchw = 3;
+                        r.out_vec = vec;
+                    }
+                }
                 rc = launch(r, cs, st);
                 if (rc != kNotImplemented) return rc;
             }

@@ -114,6 +114,11 @@ struct Params {
     // (oh*sh + 2*kb) / cl_rstep of the copy; out_nchw == 2 is the matching output mapping (tmD is
     // then the 4-D map {OW, OH, channels, images}).
     int a_cl, cl_cblocks, out_nchw, cl_tpr, cl_rstep;
+    // cl_swap: the roles are swapped - operand A (rows, tensor-memory lanes) is the filter bank,
+    // operand B (columns) the channels-last activations (tmB is then the im2col-mode map when
+    // a_cl == 1), and the output mapping is out_nchw == 3: row = output channel, column = output
+    // pixel img * P + pp, written as vectors of out_vec elements per lane (see epilogue.cuh).
+    int cl_swap, out_vec;
     long long wait_limit;  // SM clocks a bounded wait may take (see ptx::mbar_wait_bounded)
     int skip_tile_commit;  // test aid: the UMMA issuer leaves out the commit that hands a finished
                            // accumulator to the epilogue, so that the epilogue's wait runs out
@@ -351,6 +356,48 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
             if (!__all_sync(0xffffffffu, w)) break;
             ptx::tc_fence_after();
 
+            if constexpr (USE_TMA && !PAIR && ES == 2) {
+                if (p.out_nchw == 3) {
+                    // swapped roles: lanes are output channels, columns are output pixels
+                    const int co = m0 + q * 32 + lane;
+                    const bool co_ok = co < p.M;
+                    const int cb3 = chalf * (BN / 2);
+                    const int ncols3 = max(0, min(BN / 2, p.N - n0 - cb3));
+                    float bv3 = 0.0f;
+                    if (p.bias != nullptr && co_ok)
+                        bv3 = p.fmt == FMT_F16 ? out_load<OUT_F16>(p.bias + co * 2) : out_load<OUT_BF16>(p.bias + co * 2);
+                    const uint32_t trow3 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN + cb3;
+                    const long long rowoff = static_cast<long long>(co) * p.g.P;
+                    const bool relu3 = p.relu != 0;
+                    for (int c0 = 0; c0 < ncols3; c0 += 32) {
+                        uint32_t v[32];
+                        ptx::tmem_ld_32x32(trow3 + c0, v);
+                        ptx::tmem_ld_wait();
+                        const int j0 = n0 + cb3 + c0;
+                        const int img = j0 / p.g.P;
+                        const int pp = j0 - img * p.g.P;
+                        const int nc = min(32, ncols3 - c0);
+#define DLF_SWAPPED(OUT, G)                                                                                   \
+    epilogue_swapped_chunk<OUT, G>(v, nc, p.d, p.resid, rowoff, p.g.out_img_stride, p.g.P, img, pp, p.alpha, bv3, \
+                                   relu3, co_ok)
+                        if (p.fmt == FMT_F16) {
+                            if (p.out_vec == 8) DLF_SWAPPED(OUT_F16, 8);
+                            else if (p.out_vec == 4) DLF_SWAPPED(OUT_F16, 4);
+                            else if (p.out_vec == 2) DLF_SWAPPED(OUT_F16, 2);
+                            else DLF_SWAPPED(OUT_F16, 1);
+                        } else {
+                            if (p.out_vec == 8) DLF_SWAPPED(OUT_BF16, 8);
+                            else if (p.out_vec == 4) DLF_SWAPPED(OUT_BF16, 4);
+                            else if (p.out_vec == 2) DLF_SWAPPED(OUT_BF16, 2);
+                            else DLF_SWAPPED(OUT_BF16, 1);
+                        }
+#undef DLF_SWAPPED
+                    }
+                    ptx::tc_fence_before();
+                    ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));
+                    continue;
+                }
+            }
             const int i = m0 + q * 32 + lane;
             bool row_ok = i < p.M;
             long long rowbase;
@@ -611,8 +658,9 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
                 // im2col-mode loads: base pixel of the tile's first filter window
                 int cl_n = 0, cl_h = 0, cl_w = 0;
                 if (!PAIR && p.a_cl == 1) {
-                    cl_n = m0 / p.g.P;
-                    const int pp = m0 - cl_n * p.g.P;
+                    const int first = p.cl_swap ? n0 : m0;  // first output pixel of the tile
+                    cl_n = first / p.g.P;
+                    const int pp = first - cl_n * p.g.P;
                     const int oh = pp / p.g.OW;
                     cl_h = oh * p.g.sh - p.g.pad_t;
                     cl_w = (pp - oh * p.g.OW) * p.g.sw - p.g.pad_l;
@@ -626,6 +674,27 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
                     }
                     const uint32_t sA = smem0 + stage * stage_bytes;
                     const uint32_t sB = sA + A_TILE;
+                    if (!PAIR && p.cl_swap && p.a_cl == 1) {
+                        // swapped roles: A = filter bank (tiled), B = activations (im2col mode, BN windows)
+                        const uint32_t bar = ptx::smem_u32(&full_bar[stage]);
+                        ptx::mbar_arrive_expect_tx(bar, A_TILE + b_tile);
+                        ptx::tma_load_3d(sA, &tmA, bar, kb * BK, m0, 0);
+                        ptx::tma_load_im2col_4d(sB, &tmB, bar, cl_cb * BK, cl_w, cl_h, cl_n,
+                                                static_cast<unsigned short>(cl_kw * p.g.dw),
+                                                static_cast<unsigned short>(cl_kh * p.g.dh));
+                        if (++cl_cb == p.cl_cblocks) {
+                            cl_cb = 0;
+                            if (++cl_kw == p.g.KW) {
+                                cl_kw = 0;
+                                ++cl_kh;
+                            }
+                        }
+                        if (++stage == static_cast<uint32_t>(S)) {
+                            stage = 0;
+                            phase ^= 1u;
+                        }
+                        continue;
+                    }
                     if (!PAIR && p.a_cl == 2) {
                         const uint32_t bar = ptx::smem_u32(&full_bar[stage]);
                         ptx::mbar_arrive_expect_tx(bar, A_TILE + b_tile);

@@ -130,6 +130,89 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&v)[32], char* pt
     }
 }
 
+// Epilogue of a convolution computed with the roles swapped: the lanes hold output channels and
+// the columns are consecutive output pixels j = img * P + pp of an NCHW tensor, so one lane's
+// columns are consecutive in memory and leave as vectors of G elements (G = 8, 4, 2 or 1: the
+// largest that divides P and keeps every vector aligned; the caller guarantees that the chunk's
+// first pixel and its column count are multiples of G, so a vector never crosses an image).
+// `v`: 32 accumulator columns; `ncols` of them exist; (img, pp): image and pixel of column 0
+// (warp-uniform); `rowoff` = channel * P for this lane; `img_stride` = channels * P (elements).
+template <int OUT, int G>
+__device__ __forceinline__ void epilogue_swapped_chunk(const uint32_t (&v)[32], int ncols, char* d, const char* resid,
+                                                       long long rowoff, long long img_stride, int P, int img, int pp,
+                                                       float alpha, float bv, bool relu, bool row_ok) {
+    static_assert(OUT == OUT_F16 || OUT == OUT_BF16, "16-bit outputs");
+#pragma unroll
+    for (int k = 0; k < 32 / G; ++k) {
+        if (G * k < ncols) {
+            while (pp >= P) {  // next image (warp-uniform)
+                pp -= P;
+                ++img;
+            }
+            const long long e = static_cast<long long>(img) * img_stride + rowoff + pp;
+            float r[G];
+#pragma unroll
+            for (int g = 0; g < G; ++g) r[g] = alpha * __uint_as_float(v[G * k + g]) + bv;
+            if (resid != nullptr && row_ok) {
+                if constexpr (G == 1) {
+                    r[0] += out_load<OUT>(resid + e * 2);
+                } else {
+                    uint32_t w[G / 2];
+                    if constexpr (G == 8) {
+                        const uint4 u = *reinterpret_cast<const uint4*>(resid + e * 2);
+                        w[0] = u.x; w[1] = u.y; w[2] = u.z; w[3] = u.w;
+                    } else if constexpr (G == 4) {
+                        const uint2 u = *reinterpret_cast<const uint2*>(resid + e * 2);
+                        w[0] = u.x; w[1] = u.y;
+                    } else {
+                        w[0] = *reinterpret_cast<const uint32_t*>(resid + e * 2);
+                    }
+#pragma unroll
+                    for (int g = 0; g < G / 2; ++g) {
+                        if constexpr (OUT == OUT_F16) {
+                            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[g]));
+                            r[2 * g] += f.x;
+                            r[2 * g + 1] += f.y;
+                        } else {
+                            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[g]));
+                            r[2 * g] += f.x;
+                            r[2 * g + 1] += f.y;
+                        }
+                    }
+                }
+            }
+            if (relu) {
+#pragma unroll
+                for (int g = 0; g < G; ++g) r[g] = fmaxf(r[g], 0.0f);
+            }
+            if (row_ok) {
+                if constexpr (G == 1) {
+                    out_store<OUT>(d + e * 2, r[0]);
+                } else {
+                    uint32_t w[G / 2];
+#pragma unroll
+                    for (int g = 0; g < G / 2; ++g) {
+                        if constexpr (OUT == OUT_F16) {
+                            const __half2 h = __floats2half2_rn(r[2 * g], r[2 * g + 1]);
+                            w[g] = *reinterpret_cast<const uint32_t*>(&h);
+                        } else {
+                            const __nv_bfloat162 h = __floats2bfloat162_rn(r[2 * g], r[2 * g + 1]);
+                            w[g] = *reinterpret_cast<const uint32_t*>(&h);
+                        }
+                    }
+                    if constexpr (G == 8)
+                        *reinterpret_cast<uint4*>(d + e * 2) = make_uint4(w[0], w[1], w[2], w[3]);
+                    else if constexpr (G == 4)
+                        *reinterpret_cast<uint2*>(d + e * 2) = make_uint2(w[0], w[1]);
+                    else
+                        *reinterpret_cast<uint32_t*>(d + e * 2) = w[0];
+                }
+            }
+            pp += G;
+        }
+    }
+}
+
 // Whether this lane and lane ^ 1 can share 32-bit stores (see epilogue_chunk): rows adjacent in
 // memory, both present, column stride even and the even lane's first element 4-byte aligned.
 __device__ __forceinline__ bool pair_store_ok(const char* ptr, long long rowbase, long long colstride,

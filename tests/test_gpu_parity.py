@@ -838,6 +838,44 @@ def test_conv2d_pointwise_table_lookup_matches_affine(lib, dtype):
         assert torch.equal(outs[0], outs[1]), case
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("case", [
+    (3, 64, 14, 14, 136, 3, 1, 1),   # 196-pixel planes: vectors of 4
+    (3, 64, 9, 10, 72, 3, 1, 1),     # 90-pixel planes: vectors of 2
+    (2, 64, 12, 12, 300, 1, 1, 0),   # 1x1, 144-pixel planes take the batched-GEMM route (not swapped)
+    (5, 32, 10, 10, 64, 1, 2, 0),    # 1x1 stride 2: 25-pixel planes, odd: never swapped
+    (2, 96, 16, 12, 40, 3, 1, 1),    # 192-pixel planes: vectors of 8, two images in one 256-pixel tile
+], ids=lambda c: "x".join(map(str, c)))
+def test_conv2d_swapped_roles_every_vector_width(lib, case, dtype):
+    """The channels-last route with the roles swapped (lanes = output channels, columns = pixels,
+    each lane storing vectors of consecutive pixels) is the default only for planes of a multiple of
+    8 pixels; measurement bit 0x100 turns it on for vectors of 4 and 2 as well. All of them against
+    the oracle, with a residual and ReLU, and nothing outside Y touched."""
+    from dlf_b200 import gdnn
+    N, C, H, W, Co, k, s, p = case
+    rng = np.random.default_rng(sum(case))
+    Xh = _round_to(rng.normal(size=(N, C, H, W)).astype(np.float32), dtype)
+    Wh = _round_to((np.sqrt(2.0 / (C * k * k)) * rng.normal(size=(Co, C, k, k))).astype(np.float32), dtype)
+    bh = _round_to(rng.uniform(-0.1, 0.1, Co).astype(np.float32), dtype)
+    X, Wt, b = (torch.from_numpy(a).to(dtype).cuda() for a in (Xh, Wh, bh))
+    f = gdnn.Filter2D(X.shape, Wt.shape).pads(p, p).strides(s, s)
+    Rh = _round_to(rng.normal(size=tuple(f.output_shape())).astype(np.float32), dtype)
+    R = torch.from_numpy(Rh).to(dtype).cuda()
+    n_out = int(np.prod(f.output_shape()))
+    ref = oracle.conv2d_fused(Xh, Wh, residual=Rh, relu=True, bias=bh, pads=(p,) * 4, strides=(s, s), wide=True)
+    for flags in (0, 0x100):
+        buf = torch.full((n_out + 64,), 3.0, dtype=dtype, device="cuda")
+        Y = buf[32:32 + n_out].view(f.output_shape())
+        lib.set_tuning(0, flags)
+        try:
+            gdnn.conv2d_filter(X, Wt, Y, f, bias=b, residual=R, activation="relu")
+            torch.cuda.synchronize()
+        finally:
+            lib.set_tuning(0, 0)
+        assert bool((buf[:32] == 3.0).all()) and bool((buf[32 + n_out:] == 3.0).all())
+        assert max_rel(Y.float().cpu().numpy(), ref) <= HALF_TOL
+
+
 FUSED_CASES = [
     CONV_CASES[0],    # row form 3x3
     CONV_CASES[3],    # 1x1 with aligned planes: TMA-fed GEMM route, TMA-store epilogue
