@@ -385,7 +385,24 @@ int encode_small_map(const DeviceState& st, CUtensorMap* map, const Problem& q) 
 // Tensor map for TMA stores of the output (blocks of 32 rows x 32 or 64 columns, no swizzle): only when nothing of C has
 // to be read (beta == 0, no per-batch tables) and D's base and strides are 16-byte multiples.
 bool encode_output_map(const DeviceState& st, CUtensorMap* map, const Problem& q, unsigned box_cols) {
-    if (q.out_nchw == 3) return false;  // swapped roles: the lanes write vectors themselves
+    if (q.out_nchw == 3) {
+        // swapped roles (rows = channels, columns = pixels): boxes of 32 pixels x 32 channels of the
+        // NCHW output {pixels of a plane, channels, images}; images are the batch entries in the
+        // batched form (N = P), else N / P
+        const long long P = q.g.P;
+        const bool ok = q.es == 2 && q.beta == 0.0f && (reinterpret_cast<uintptr_t>(q.d) & 15u) == 0 &&
+                        (P * q.es) % 16 == 0 && P * q.M * q.es < (1ll << 40) && !(g_force_generic.load() & 0x4000);
+        if (!ok) return false;
+        const long long images = q.batch > 1 ? q.batch : q.N / P;
+        cuuint64_t dims[3] = {static_cast<cuuint64_t>(P), static_cast<cuuint64_t>(q.M), static_cast<cuuint64_t>(images)};
+        cuuint64_t strides[2] = {static_cast<cuuint64_t>(P * q.es), static_cast<cuuint64_t>(P * q.M * q.es)};
+        cuuint32_t box[3] = {32, 32, 1};
+        cuuint32_t estr[3] = {1, 1, 1};
+        CUresult r = st.encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, q.d, dims, strides, box, estr,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                               CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        return r == CUDA_SUCCESS;
+    }
     if (q.out_nchw == 2) {
         // NCHW output written row by row: {OW, OH, channels, images}, boxes of 32 outputs of one row
         const long long P = q.g.P, OW = q.g.OW;
@@ -528,7 +545,7 @@ int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
     const long long num_kb_all = (q.K + BK - 1) / BK;
     const int kc_blocks = (q.es == 4 && num_kb_all > 16 && !(g_force_generic.load() & 0x1000)) ? 8 : 0;
     int bn = choose_bn_ts(q, st.num_sms, kc_blocks ? 192 : 256, a_cols, num_kb_all);
-    const int forced = g_force_bn.load();
+    const int forced = g_force_bn.load() & 0xffff;
     if (forced >= 64 && forced <= (kc_blocks ? 192 : 256) && forced % 32 == 0) bn = forced;
     // an MN-major B tile is made of whole groups of BK columns (the UMMA reads all k-rows of the
     // last group it touches): a width that ends inside a group would make it read past the stage
@@ -750,7 +767,7 @@ int launch(const Problem& q, cudaStream_t stream, DeviceState* preset = nullptr)
     const long long tiles_m = (q.M + kBM - 1) / kBM;
     // fp32 here keeps hi and lo copies of both operands per stage: 128 columns leave >= 3 stages
     int bn = choose_bn(q.M, q.N, q.batch, st->num_sms, false, q.es == 4 ? 128 : 256);
-    const int forced = g_force_bn.load();
+    const int forced = g_force_bn.load() & 0xffff;
     if (forced == 64 || forced == 128 || (forced == 256 && q.es == 2)) bn = forced;
 
     // CTA pairs (cta_group::2): 256 x 256 tiles, each CTA stages 128 rows of A and 128 of B, so
@@ -1443,6 +1460,23 @@ int dlf_b200_conv2d_fused(int dtype, size_t batches, size_t channels, size_t hei
         q.d_batch_stride = static_cast<long long>(num_kernels) * P;
         q.bias = static_cast<const char*>(bias);
         q.bias_stride = 0;
+        // With the roles swapped (rows = output channels = lanes, columns = pixels) a lane's 32
+        // columns are 64 consecutive bytes of Y: four 16-byte shared-memory stores fill the staging
+        // block of a TMA store, where the pixel-per-lane form needs 32 two-byte ones. Measured on the
+        // ResNet-50 shapes (batch 256): 128 -> 512 at 28x28 94 -> 86 us, 256 -> 64 at 56x56 98 -> 90 us,
+        // 512 -> 128 at 28x28 56 -> 49 us; with 64 output channels half of the 128 lanes would idle
+        // (64 -> 64: 73 -> 81 us), so those stay unswapped. Bit 19 of the tile-width word: never swap.
+        const uintptr_t ya = reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(residual);
+        if (P % 8 == 0 && P >= 32 && ya % 16 == 0 && num_kernels >= 128 && !((g_force_bn.load() >> 16) & 8)) {
+            std::swap(q.a, q.b);
+            q.M = static_cast<long long>(num_kernels);
+            q.N = P;
+            q.cl_swap = 1;
+            q.out_nchw = 3;
+            q.out_vec = 8;
+            q.g.P = static_cast<int>(P);
+            q.g.out_img_stride = static_cast<long long>(num_kernels) * P;
+        }
         return launch(q, static_cast<cudaStream_t>(stream));
     }
 
@@ -1489,6 +1523,7 @@ int dlf_b200_conv2d_fused(int dtype, size_t batches, size_t channels, size_t hei
     {
         const int tune = g_force_generic.load();
         const int cl_neutral = 0x100 | 0x4000 | 0x10000000 | 0x20000000;
+        const int route = g_force_bn.load() >> 16;
         const long long kb2 = (static_cast<long long>(kernel_h) + 1) / 2;
         const long long rstep = stride_h % 2 == 0 ? 2 : 1;
         const long long jn = ((static_cast<long long>(output_h) - 1) * stride_h + 2 * (kb2 - 1)) / rstep + 1;  // row pairs
@@ -1499,7 +1534,7 @@ int dlf_b200_conv2d_fused(int dtype, size_t batches, size_t channels, size_t hei
         const size_t slack = static_cast<size_t>(ws - static_cast<unsigned char*>(workspace));
         const long long tpr = (static_cast<long long>(output_w) + kBM - 1) / kBM;
         const long long rows = static_cast<long long>(batches) * output_h;
-        if (q.es == 2 && group == 1 && channels <= 4 && (tune & ~cl_neutral) == 0 && workspace != nullptr &&
+        if (q.es == 2 && group == 1 && channels <= 4 && (tune & ~cl_neutral) == 0 && !(route & 1) && workspace != nullptr &&
             workspace_bytes >= slack + w_bytes + x_bytes && kernel_w <= 8 && stride_w <= 64 && stride_h <= 64 &&
             dilation_h == 1 && dilation_w == 1 && rows * tpr < (INT_MAX - 512) / kBM && jn < (1 << 28) && wp < (1 << 27) &&
             pad_top < (1u << 28) && pad_left < (1u << 28)) {
@@ -1581,9 +1616,10 @@ int dlf_b200_conv2d_fused(int dtype, size_t batches, size_t channels, size_t hei
         // ResNet-50 shapes: 256->1024 at 14x14 99 -> 74 us, 1024->256 70 -> 90 us)
         const bool widens = !pointwise || num_kernels >= 2 * channels;
         // every measurement / forcing bit that addresses the other convolution kernels (and the
-        // route's own off switch, 0x40000000) keeps the call on those kernels
+        // route's own off switch, bit 16 of the tile-width word) keeps the call on those kernels
         const int cl_neutral = 0x100 | 0x4000 | 0x10000000 | 0x20000000;
-        if (q.es == 2 && group == 1 && (tune & ~cl_neutral) == 0 && workspace != nullptr &&
+        const int route = g_force_bn.load() >> 16;
+        if (q.es == 2 && group == 1 && (tune & ~cl_neutral) == 0 && !(route & 1) && workspace != nullptr &&
             workspace_bytes >= slack + w_bytes + x_bytes && dense_k && widens && batches < 65536 && cp < 65536ll * 64 &&
             (pointwise || (dilation_h * (kernel_h - 1) < 256 && dilation_w * (kernel_w - 1) < 256 && stride_h <= 8 &&
                            stride_w <= 8)) &&
@@ -1675,7 +1711,7 @@ int dlf_b200_conv2d_fused(int dtype, size_t batches, size_t channels, size_t hei
                     if (P % 8 == 0 && ya % 16 == 0) vec = 8;
                     else if (P % 4 == 0 && ya % 8 == 0) vec = 4;
                     else if (P % 2 == 0 && ya % 4 == 0) vec = 2;
-                    const bool want = (tune & 0x100) ? vec > 1 : vec == 8;  // 0x100: measurement, swap with any vector
+                    const bool want = (route & 2) ? vec > 1 : vec == 8;  // route bit 1: measurement, swap with any vector
                     if (want && P >= 32) {
                         std::swap(r.a, r.b);
                         r.M = static_cast<long long>(num_kernels);
@@ -1717,7 +1753,7 @@ int dlf_b200_conv2d_fused(int dtype, size_t batches, size_t channels, size_t hei
         const int n_tiles = static_cast<int>((ng + cpt_max - 1) / cpt_max);
         int cpt = static_cast<int>(((ng + n_tiles - 1) / n_tiles + 15) / 16 * 16);
         if (cpt > cpt_max) cpt = cpt_max;
-        const int forced_bn = g_force_bn.load();  // experiments: tile width -> channels per tile
+        const int forced_bn = g_force_bn.load() & 0xffff;  // experiments: tile width -> channels per tile
         if (forced_bn >= 16 * taps && forced_bn / taps / 16 * 16 <= cpt_max) cpt = static_cast<int>(forced_bn / taps / 16 * 16);
         Problem r = q;
         r.rc_kw = static_cast<int>(taps);
@@ -2202,6 +2238,17 @@ int dlf_b200_device_status(int* device_status) {
     if (device_status) *device_status = v;
     return kSuccess;
 }
+
+#ifdef DLF_ROLE_CLOCKS
+// measurement build only: reads (and clears) the role clock table of contraction.cuh
+int dlf_b200_debug_role_clocks(unsigned long long* out16) {
+    CUDA_TRY(cudaDeviceSynchronize());
+    CUDA_TRY(cudaMemcpyFromSymbol(out16, g_role_clocks, 16 * sizeof(unsigned long long)));
+    unsigned long long zero[16] = {};
+    CUDA_TRY(cudaMemcpyToSymbol(g_role_clocks, zero, sizeof(zero)));
+    return 0;
+}
+#endif
 
 void dlf_b200_set_tuning(int force_bn, int force_generic_loader) {
     g_force_bn.store(force_bn);

@@ -41,6 +41,24 @@
 
 namespace dlfb200 {
 
+// Measurement build (-DDLF_ROLE_CLOCKS): one thread per role and CTA adds the SM clocks it spent
+// waiting and working to a global table; compiled out otherwise.
+#ifdef DLF_ROLE_CLOCKS
+__device__ unsigned long long g_role_clocks[16];
+#define DLF_CLK_DECL(cond) const bool clk_on = (cond); long long clk_t = clock64();
+#define DLF_CLK_ADD(slot)                                                                         \
+    do {                                                                                          \
+        if (clk_on) {                                                                             \
+            const long long now__ = clock64();                                                    \
+            atomicAdd(&g_role_clocks[slot], static_cast<unsigned long long>(now__ - clk_t));      \
+            clk_t = now__;                                                                        \
+        }                                                                                         \
+    } while (0)
+#else
+#define DLF_CLK_DECL(cond)
+#define DLF_CLK_ADD(slot)
+#endif
+
 constexpr int kBM = 128;
 constexpr int kMmaWarp = 4;
 constexpr int kTmaWarp = 5;
@@ -159,8 +177,19 @@ __device__ __forceinline__ uint4 load_chunk_dense(const GenOperand& op, long lon
     if (line_coord >= line_lim || cont0 >= cont_lim) return v;
     const char* ptr =
         op.base + (boff + static_cast<long long>(line_coord) * op.ld + cont0) * ES;
-    if (cont0 + CPE <= cont_lim && (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0u) {
-        return *reinterpret_cast<const uint4*>(ptr);
+    if (cont0 + CPE <= cont_lim) {
+        // a whole chunk inside the operand: the widest loads its address allows
+        const uint32_t mis = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(ptr)) & 15u;
+        if (mis == 0u) return *reinterpret_cast<const uint4*>(ptr);
+        if ((mis & 7u) == 0u) {
+            const uint2 lo = *reinterpret_cast<const uint2*>(ptr);
+            const uint2 hi = *reinterpret_cast<const uint2*>(ptr + 8);
+            return make_uint4(lo.x, lo.y, hi.x, hi.y);
+        }
+        if ((mis & 3u) == 0u) {
+            const uint32_t* q = reinterpret_cast<const uint32_t*>(ptr);
+            return make_uint4(q[0], q[1], q[2], q[3]);
+        }
     }
     if constexpr (ES == 2) {
         unsigned short e[8];
@@ -345,16 +374,19 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
         const int chalf = (USE_TMA && warp >= 6) ? 1 : 0;
         uint32_t it = 0;
         uint32_t chunk_no = 0;  // TMA-store epilogue: 32-column blocks written so far by this warp
+        DLF_CLK_DECL(warp == 0 && lane == 0)
         for (int t = tile0; t < p.total_tiles; t += tile_step, ++it) {
             int b, m0, n0;
             decode_tile(p, t, b, m0, n0, tile_rows);
             m0 += row_off;
             const uint32_t buf = it & 1u;
             const uint32_t tphase = (it >> 1) & 1u;
+            DLF_CLK_ADD(1);  // epilogue work of the previous tile
             // tcgen05.ld is warp-collective: the warp leaves together or not at all
             const bool w = ptx::mbar_wait_bounded(ptx::smem_u32(&tfull_bar[buf]), tphase, abort_p, wait_limit);
             if (!__all_sync(0xffffffffu, w)) break;
             ptx::tc_fence_after();
+            DLF_CLK_ADD(0);  // waiting for an accumulator
 
             if constexpr (USE_TMA && !PAIR && ES == 2) {
                 if (p.out_nchw == 3) {
@@ -368,19 +400,93 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
                         bv3 = p.fmt == FMT_F16 ? out_load<OUT_F16>(p.bias + co * 2) : out_load<OUT_BF16>(p.bias + co * 2);
                     const uint32_t trow3 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN + cb3;
                     const long long rowoff = static_cast<long long>(co) * p.g.P;
+                    const long long boff3 = static_cast<long long>(b) * p.d_batch_stride * 2;  // batched form: one image per batch entry
                     const bool relu3 = p.relu != 0;
                     for (int c0 = 0; c0 < ncols3; c0 += 32) {
                         uint32_t v[32];
+                        DLF_CLK_ADD(1);
                         ptx::tmem_ld_32x32(trow3 + c0, v);
                         ptx::tmem_ld_wait();
+                        DLF_CLK_ADD(12);  // accumulator columns in registers
                         const int j0 = n0 + cb3 + c0;
                         const int img = j0 / p.g.P;
                         const int pp = j0 - img * p.g.P;
                         const int nc = min(32, ncols3 - c0);
+                        if (p.d_tma && nc == 32 && (pp + 32 <= p.g.P || p.batch > 1)) {
+                            // the warp's 32 channels x 32 pixels are one box of the {pixels, channels,
+                            // images} map: each lane lays its 32 pixels (64 bytes) into the staging
+                            // block, which is then the box's own [channel][pixel] image. In the batched
+                            // form a box that overhangs the plane is clipped by the hardware.
+                            const uint32_t half = chunk_no & 1u;
+                            if (chunk_no >= 2) {
+                                if (lane == 0) ptx::bulk_wait_group_read<1>();
+                                __syncwarp();
+                            }
+                            const uint32_t sblk = ptx::smem_u32(d_stage) + (ewarp * 2 + half) * 2048u;
+                            const char* rp = p.resid ? p.resid + boff3 +
+                                                           (static_cast<long long>(img) * p.g.out_img_stride + rowoff + pp) * 2
+                                                     : nullptr;
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                float r[8];
+#pragma unroll
+                                for (int g = 0; g < 8; ++g) r[g] = fmaf(p.alpha, __uint_as_float(v[8 * k + g]), bv3);
+                                if (rp != nullptr && co_ok) {
+                                    const uint4 u = *reinterpret_cast<const uint4*>(rp + 16 * k);
+                                    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                                    for (int g = 0; g < 4; ++g) {
+                                        const float2 f = p.fmt == FMT_F16
+                                                             ? __half22float2(*reinterpret_cast<const __half2*>(&w[g]))
+                                                             : __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[g]));
+                                        r[2 * g] += f.x;
+                                        r[2 * g + 1] += f.y;
+                                    }
+                                }
+                                uint4 o;
+                                uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+                                for (int g = 0; g < 4; ++g) {
+                                    const float a = relu3 ? fmaxf(r[2 * g], 0.0f) : r[2 * g];
+                                    const float c = relu3 ? fmaxf(r[2 * g + 1], 0.0f) : r[2 * g + 1];
+                                    if (p.fmt == FMT_F16) {
+                                        const __half2 h = __floats2half2_rn(a, c);
+                                        ow[g] = *reinterpret_cast<const uint32_t*>(&h);
+                                    } else {
+                                        const __nv_bfloat162 h = __floats2bfloat162_rn(a, c);
+                                        ow[g] = *reinterpret_cast<const uint32_t*>(&h);
+                                    }
+                                }
+                                st_shared_v4(sblk + lane * 64u + k * 16u, o);
+                            }
+                            ptx::fence_proxy_async_smem();
+                            __syncwarp();
+                            if (lane == 0) {
+                                ptx::tma_store_3d(&tmD, sblk, pp, m0 + q * 32, p.batch > 1 ? b : img);
+                                ptx::bulk_commit_group();
+                            }
+                            ++chunk_no;
+                            continue;
+                        }
 #define DLF_SWAPPED(OUT, G)                                                                                   \
-    epilogue_swapped_chunk<OUT, G>(v, nc, p.d, p.resid, rowoff, p.g.out_img_stride, p.g.P, img, pp, p.alpha, bv3, \
-                                   relu3, co_ok)
-                        if (p.fmt == FMT_F16) {
+    epilogue_swapped_chunk<OUT, G>(v, nc, p.d + boff3, p.resid ? p.resid + boff3 : nullptr, rowoff, p.g.out_img_stride, \
+                                   p.g.P, img, pp, p.alpha, bv3, relu3, co_ok, rowoff, p.g.out_img_stride, img)
+#define DLF_SWAPPED_FAST(OUT, G)                                                                              \
+    epilogue_swapped_chunk_fast<OUT, G>(v, nc, p.d + boff3 + e0 * 2, p.resid ? p.resid + boff3 + e0 * 2 : nullptr, \
+                                        p.g.P - pp, jump, jump, p.alpha, bv3, relu3, co_ok)
+                        if (p.g.P >= 32 && p.out_vec > 1) {
+                            const long long e0 = static_cast<long long>(img) * p.g.out_img_stride + rowoff + pp;
+                            const long long jump = (p.g.out_img_stride - p.g.P) * 2;
+                            if (p.fmt == FMT_F16) {
+                                if (p.out_vec == 8) DLF_SWAPPED_FAST(OUT_F16, 8);
+                                else if (p.out_vec == 4) DLF_SWAPPED_FAST(OUT_F16, 4);
+                                else DLF_SWAPPED_FAST(OUT_F16, 2);
+                            } else {
+                                if (p.out_vec == 8) DLF_SWAPPED_FAST(OUT_BF16, 8);
+                                else if (p.out_vec == 4) DLF_SWAPPED_FAST(OUT_BF16, 4);
+                                else DLF_SWAPPED_FAST(OUT_BF16, 2);
+                            }
+                        } else if (p.fmt == FMT_F16) {
                             if (p.out_vec == 8) DLF_SWAPPED(OUT_F16, 8);
                             else if (p.out_vec == 4) DLF_SWAPPED(OUT_F16, 4);
                             else if (p.out_vec == 2) DLF_SWAPPED(OUT_F16, 2);
@@ -392,6 +498,7 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
                             else DLF_SWAPPED(OUT_BF16, 1);
                         }
 #undef DLF_SWAPPED
+#undef DLF_SWAPPED_FAST
                     }
                     ptx::tc_fence_before();
                     ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));
@@ -449,8 +556,10 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
                     const bool wide = p.d_tma == 64;
                     for (int c0 = 0; c0 < ncols && blk_ok; c0 += 32, ++chunk_no) {
                         uint32_t v[32];
+                        DLF_CLK_ADD(1);
                         ptx::tmem_ld_32x32(trow + c0, v);
                         ptx::tmem_ld_wait();
+                        DLF_CLK_ADD(12);
                         float bv = 0.0f;
                         if (bias != nullptr && c0 + lane < ncols)
                             bv = p.fmt == FMT_F16 ? out_load<OUT_F16>(bias + (c0 + lane) * 2)
@@ -591,21 +700,26 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
             uint32_t stage = 0, phase = 0;
             uint32_t it = 0;
             bool ok = true;
+            DLF_CLK_DECL(true)
             for (int t = tile0; ok && t < p.total_tiles; t += tile_step, ++it) {
                 const uint32_t buf = it & 1u;
                 const uint32_t tphase = (it >> 1) & 1u;
+                DLF_CLK_ADD(4);  // issue
                 if (!ptx::mbar_wait_bounded(ptx::smem_u32(&tempty_bar[buf]), tphase ^ 1u, abort_p, wait_limit)) {
                     ok = false;
                     break;
                 }
                 ptx::tc_fence_after();
+                DLF_CLK_ADD(2);  // waiting for the epilogue to free an accumulator
                 const uint32_t d_tmem = tmem_base + buf * BN;
                 for (int kb = 0; kb < num_kb; ++kb) {
+                    DLF_CLK_ADD(4);
                     if (!ptx::mbar_wait_bounded(ptx::smem_u32(&full_bar[stage]), phase, abort_p, wait_limit)) {
                         ok = false;
                         break;
                     }
                     ptx::tc_fence_after();
+                    DLF_CLK_ADD(3);  // waiting for operands
                     const uint32_t st_units = (stage * stage_bytes) >> 4;
 #pragma unroll
                     for (int ks = 0; ks < BK / UMMA_K; ++ks) {
@@ -648,6 +762,7 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
+            DLF_CLK_DECL(true)
             for (int t = tile0; ok && t < p.total_tiles; t += tile_step) {
                 int b, m0, n0;
                 decode_tile(p, t, b, m0, n0, tile_rows);
@@ -667,21 +782,26 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
                 }
                 int cl_cb = 0, cl_kh = 0, cl_kw = 0;  // channel block and filter tap of kb
                 for (int kb = 0; kb < num_kb; ++kb) {
+                    DLF_CLK_ADD(6);  // issue
                     if (!ptx::mbar_wait_bounded(ptx::smem_u32(&empty_bar[stage]), phase ^ 1u,
                                                 abort_p, wait_limit)) {
                         ok = false;
                         break;
                     }
+                    DLF_CLK_ADD(5);  // waiting for a free stage
                     const uint32_t sA = smem0 + stage * stage_bytes;
                     const uint32_t sB = sA + A_TILE;
                     if (!PAIR && p.cl_swap && p.a_cl == 1) {
                         // swapped roles: A = filter bank (tiled), B = activations (im2col mode, BN windows)
                         const uint32_t bar = ptx::smem_u32(&full_bar[stage]);
                         ptx::mbar_arrive_expect_tx(bar, A_TILE + b_tile);
+                        DLF_CLK_ADD(6);
                         ptx::tma_load_3d(sA, &tmA, bar, kb * BK, m0, 0);
+                        DLF_CLK_ADD(7);  // first copy of the stage handed over
                         ptx::tma_load_im2col_4d(sB, &tmB, bar, cl_cb * BK, cl_w, cl_h, cl_n,
                                                 static_cast<unsigned short>(cl_kw * p.g.dw),
                                                 static_cast<unsigned short>(cl_kh * p.g.dh));
+                        DLF_CLK_ADD(8);  // second copy handed over
                         if (++cl_cb == p.cl_cblocks) {
                             cl_cb = 0;
                             if (++cl_kw == p.g.KW) {
@@ -701,9 +821,12 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
                         const int mt = m0 / kBM;
                         const int rowid = mt / p.cl_tpr;
                         const int n = rowid / p.g.OH;
+                        DLF_CLK_ADD(6);
                         ptx::tma_load_4d(sA, &tmA, bar, 0, (mt - rowid * p.cl_tpr) * kBM,
                                          ((rowid - n * p.g.OH) * p.g.sh + 2 * kb) / p.cl_rstep, n);
+                        DLF_CLK_ADD(7);
                         ptx::tma_load_3d(sB, &tmB, bar, kb * BK, n0, bb);
+                        DLF_CLK_ADD(8);
                         if (++stage == static_cast<uint32_t>(S)) {
                             stage = 0;
                             phase ^= 1u;
@@ -713,10 +836,13 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
                     if (!PAIR && p.a_cl == 1) {
                         const uint32_t bar = ptx::smem_u32(&full_bar[stage]);
                         ptx::mbar_arrive_expect_tx(bar, A_TILE + b_tile);
+                        DLF_CLK_ADD(6);
                         ptx::tma_load_im2col_4d(sA, &tmA, bar, cl_cb * BK, cl_w, cl_h, cl_n,
                                                 static_cast<unsigned short>(cl_kw * p.g.dw),
                                                 static_cast<unsigned short>(cl_kh * p.g.dh));
+                        DLF_CLK_ADD(7);
                         ptx::tma_load_3d(sB, &tmB, bar, kb * BK, n0, bb);
+                        DLF_CLK_ADD(8);
                         if (++cl_cb == p.cl_cblocks) {
                             cl_cb = 0;
                             if (++cl_kw == p.g.KW) {
@@ -750,18 +876,21 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
                     } else {
                         const uint32_t bar = ptx::smem_u32(&full_bar[stage]);
                         ptx::mbar_arrive_expect_tx(bar, A_TILE + b_tile);
+                        DLF_CLK_ADD(6);
                         if (p.a.k_major) {
                             ptx::tma_load_3d(sA, &tmA, bar, kb * BK, m0, ba);
                         } else {
                             for (int g = 0; g < kBM / E; ++g)
                                 ptx::tma_load_3d(sA + g * BK * 128, &tmA, bar, m0 + g * E, kb * BK, ba);
                         }
+                        DLF_CLK_ADD(7);
                         if (p.b.k_major) {
                             ptx::tma_load_3d(sB, &tmB, bar, kb * BK, n0, bb);
                         } else {
                             for (int g = 0; g < BN / E; ++g)
                                 ptx::tma_load_3d(sB + g * BK * 128, &tmB, bar, n0 + g * E, kb * BK, bb);
                         }
+                        DLF_CLK_ADD(8);
                     }
                     if (++stage == static_cast<uint32_t>(S)) {
                         stage = 0;

@@ -137,10 +137,13 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&v)[32], char* pt
 // first pixel and its column count are multiples of G, so a vector never crosses an image).
 // `v`: 32 accumulator columns; `ncols` of them exist; (img, pp): image and pixel of column 0
 // (warp-uniform); `rowoff` = channel * P for this lane; `img_stride` = channels * P (elements).
+// The residual may be addressed differently from the destination (a destination staged in shared
+// memory): element (img_r + images passed, rrowoff, pp) with image stride rimg_stride.
 template <int OUT, int G>
 __device__ __forceinline__ void epilogue_swapped_chunk(const uint32_t (&v)[32], int ncols, char* d, const char* resid,
                                                        long long rowoff, long long img_stride, int P, int img, int pp,
-                                                       float alpha, float bv, bool relu, bool row_ok) {
+                                                       float alpha, float bv, bool relu, bool row_ok,
+                                                       long long rrowoff, long long rimg_stride, int img_r) {
     static_assert(OUT == OUT_F16 || OUT == OUT_BF16, "16-bit outputs");
 #pragma unroll
     for (int k = 0; k < 32 / G; ++k) {
@@ -148,24 +151,26 @@ __device__ __forceinline__ void epilogue_swapped_chunk(const uint32_t (&v)[32], 
             while (pp >= P) {  // next image (warp-uniform)
                 pp -= P;
                 ++img;
+                ++img_r;
             }
             const long long e = static_cast<long long>(img) * img_stride + rowoff + pp;
+            const long long er = static_cast<long long>(img_r) * rimg_stride + rrowoff + pp;
             float r[G];
 #pragma unroll
             for (int g = 0; g < G; ++g) r[g] = alpha * __uint_as_float(v[G * k + g]) + bv;
             if (resid != nullptr && row_ok) {
                 if constexpr (G == 1) {
-                    r[0] += out_load<OUT>(resid + e * 2);
+                    r[0] += out_load<OUT>(resid + er * 2);
                 } else {
                     uint32_t w[G / 2];
                     if constexpr (G == 8) {
-                        const uint4 u = *reinterpret_cast<const uint4*>(resid + e * 2);
+                        const uint4 u = *reinterpret_cast<const uint4*>(resid + er * 2);
                         w[0] = u.x; w[1] = u.y; w[2] = u.z; w[3] = u.w;
                     } else if constexpr (G == 4) {
-                        const uint2 u = *reinterpret_cast<const uint2*>(resid + e * 2);
+                        const uint2 u = *reinterpret_cast<const uint2*>(resid + er * 2);
                         w[0] = u.x; w[1] = u.y;
                     } else {
-                        w[0] = *reinterpret_cast<const uint32_t*>(resid + e * 2);
+                        w[0] = *reinterpret_cast<const uint32_t*>(resid + er * 2);
                     }
 #pragma unroll
                     for (int g = 0; g < G / 2; ++g) {
@@ -209,6 +214,76 @@ __device__ __forceinline__ void epilogue_swapped_chunk(const uint32_t (&v)[32], 
                 }
             }
             pp += G;
+        }
+    }
+}
+
+// The same for planes of at least 32 pixels, where a chunk of 32 columns crosses at most one
+// image boundary: no loop-carried state between the vectors, so the unrolled body is one
+// independent multiply-add / convert / store group per vector. `d0` / `r0` address the element of
+// column 0 in the destination / residual; columns from `split` on (a multiple of G, 32 or more when
+// the chunk stays inside one image) belong to the next image, `d_jump` / `r_jump` bytes further.
+template <int OUT, int G>
+__device__ __forceinline__ void epilogue_swapped_chunk_fast(const uint32_t (&v)[32], int ncols, char* d0, const char* r0,
+                                                            int split, long long d_jump, long long r_jump, float alpha,
+                                                            float bv, bool relu, bool row_ok) {
+    static_assert(OUT == OUT_F16 || OUT == OUT_BF16, "16-bit outputs");
+    static_assert(G == 8 || G == 4 || G == 2, "vector stores");
+#pragma unroll
+    for (int k = 0; k < 32 / G; ++k) {
+        const int c = G * k;
+        if (c < ncols) {
+            const bool next = c >= split;
+            float r[G];
+#pragma unroll
+            for (int g = 0; g < G; ++g) r[g] = fmaf(alpha, __uint_as_float(v[c + g]), bv);
+            if (r0 != nullptr && row_ok) {
+                const char* rp = r0 + c * 2 + (next ? r_jump : 0);
+                uint32_t w[G / 2];
+                if constexpr (G == 8) {
+                    const uint4 u = *reinterpret_cast<const uint4*>(rp);
+                    w[0] = u.x; w[1] = u.y; w[2] = u.z; w[3] = u.w;
+                } else if constexpr (G == 4) {
+                    const uint2 u = *reinterpret_cast<const uint2*>(rp);
+                    w[0] = u.x; w[1] = u.y;
+                } else {
+                    w[0] = *reinterpret_cast<const uint32_t*>(rp);
+                }
+#pragma unroll
+                for (int g = 0; g < G / 2; ++g) {
+                    if constexpr (OUT == OUT_F16) {
+                        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[g]));
+                        r[2 * g] += f.x;
+                        r[2 * g + 1] += f.y;
+                    } else {
+                        const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[g]));
+                        r[2 * g] += f.x;
+                        r[2 * g + 1] += f.y;
+                    }
+                }
+            }
+            uint32_t w[G / 2];
+#pragma unroll
+            for (int g = 0; g < G / 2; ++g) {
+                const float a = relu ? fmaxf(r[2 * g], 0.0f) : r[2 * g];
+                const float b = relu ? fmaxf(r[2 * g + 1], 0.0f) : r[2 * g + 1];
+                if constexpr (OUT == OUT_F16) {
+                    const __half2 h = __floats2half2_rn(a, b);
+                    w[g] = *reinterpret_cast<const uint32_t*>(&h);
+                } else {
+                    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+                    w[g] = *reinterpret_cast<const uint32_t*>(&h);
+                }
+            }
+            if (row_ok) {
+                char* dp = d0 + c * 2 + (next ? d_jump : 0);
+                if constexpr (G == 8)
+                    *reinterpret_cast<uint4*>(dp) = make_uint4(w[0], w[1], w[2], w[3]);
+                else if constexpr (G == 4)
+                    *reinterpret_cast<uint2*>(dp) = make_uint2(w[0], w[1]);
+                else
+                    *reinterpret_cast<uint32_t*>(dp) = w[0];
+            }
         }
     }
 }

@@ -6,6 +6,10 @@
 #include <cstdint>
 #include <cuda.h>
 
+#ifndef DLF_MBAR_HINT_NS
+#define DLF_MBAR_HINT_NS 4000
+#endif
+
 namespace dlfb200 {
 namespace ptx {
 
@@ -39,7 +43,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         "selp.u32 %0, 1, 0, p;\n\t"
         "}"
         : "=r"(ok)
-        : "r"(bar), "r"(parity), "r"(4000u)
+        : "r"(bar), "r"(parity), "r"(static_cast<uint32_t>(DLF_MBAR_HINT_NS))
         : "memory");
     return ok != 0;
 }

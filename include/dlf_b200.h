@@ -227,7 +227,13 @@ int dlf_b200_device_status(int* device_status);
  * filter-packing grid) keep results valid. 0x10000000 is a test aid for the device-side time-out
  * path: a launch that consists of one tile leaves out the commit that hands its accumulator to the
  * epilogue and waits at most 2^21 clocks (about a millisecond): the call returns, the output is
- * not written and dlf_b200_device_status() reports bit 0 once. */
+ * not written and dlf_b200_device_status() reports bit 0 once.
+ * Bits 16 and up of force_bn steer the channels-last route of 16-bit convolutions (transposing
+ * copy into the caller's scratch + tensor-map-fed operand): 0x10000 never take it (the kernels
+ * that gather the activations themselves serve the call, as they do for callers without scratch),
+ * 0x20000 swap the operand roles (lanes = output channels) for every even plane size, not only
+ * for planes of a multiple of 8 pixels, 0x80000 never swap the roles of a 1x1 stride-1 convolution
+ * that runs as a batched GEMM. */
 void dlf_b200_set_tuning(int force_bn, int force_generic_loader);
 
 /* Counts kernel launches made by this library in this process (all threads). */

@@ -636,10 +636,11 @@ CONV_CASES = [
 
 
 # 16-bit convolutions of one group take the channels-last route (transposing copy + tensor-map-fed
-# operand) when the caller passes scratch; tuning bit 0x40000000 keeps them on the kernels that
-# gather the operand themselves. Both are the product (the second serves callers without scratch).
-ROUTES = [(torch.float32, 0), (torch.float16, 0), (torch.float16, 0x40000000), (torch.bfloat16, 0),
-          (torch.bfloat16, 0x40000000)]
+# operand) when the caller passes scratch; bit 16 of the tile-width word keeps them on the kernels
+# that gather the operand themselves. Both are the product (the second serves callers without scratch).
+NO_CL = 0x10000
+ROUTES = [(torch.float32, 0), (torch.float16, 0), (torch.float16, NO_CL), (torch.bfloat16, 0),
+          (torch.bfloat16, NO_CL)]
 ROUTE_IDS = ["f32", "f16-channels-last", "f16-gather", "bf16-channels-last", "bf16-gather"]
 
 
@@ -658,7 +659,7 @@ def test_conv2d_random_parity(lib, case, dtype, route):
     filt = gdnn.Filter2D(X.shape, Wt.shape, group).pads(*pads).strides(*strides).dilations(*dil)
     assert tuple(filt.output_shape()) == ref.shape
     Y = torch.full(ref.shape, float("nan"), dtype=dtype, device="cuda")
-    lib.set_tuning(0, route)
+    lib.set_tuning(route, 0)
     try:
         gdnn.conv2d_filter(torch.from_numpy(X).to(dtype).cuda(), torch.from_numpy(Wt).to(dtype).cuda(),
                            Y, filt, bias=torch.from_numpy(bias).to(dtype).cuda())
@@ -676,7 +677,7 @@ def _resnet_shapes():
     return RESNET50_SHAPES
 
 
-@pytest.mark.parametrize("route", [0, 0x40000000], ids=["channels-last", "gather"])
+@pytest.mark.parametrize("route", [0, NO_CL], ids=["channels-last", "gather"])
 @pytest.mark.parametrize("shape", _resnet_shapes(), ids=lambda c: "x".join(map(str, c[:6])))
 def test_conv2d_resnet50_layer_shapes_vs_oracle(lib, shape, route):
     """BASELINE config 3 at its real layer shapes: every one of the 20 distinct ResNet-50 v1
@@ -692,7 +693,7 @@ def test_conv2d_resnet50_layer_shapes_vs_oracle(lib, shape, route):
     ref = oracle.conv2d(X, Wt, pads=(p,) * 4, strides=(s, s), bias=bias, wide=True)
     filt = gdnn.Filter2D(X.shape, Wt.shape).pads(p, p).strides(s, s)
     Y = torch.full(ref.shape, float("nan"), dtype=torch.float16, device="cuda")
-    lib.set_tuning(0, route)
+    lib.set_tuning(route, 0)
     try:
         gdnn.conv2d_filter(torch.from_numpy(X).half().cuda(), torch.from_numpy(Wt).half().cuda(), Y, filt,
                            bias=torch.from_numpy(bias).half().cuda())
@@ -788,10 +789,10 @@ def test_conv2d_output_store_modes_agree(lib, case, dtype):
     R = torch.from_numpy(_rand(rng, f.output_shape(), "normal")).to(dtype).cuda()
     for fused in (False, True):
         outs = []
-        for flags in (0x40000000, 128 << 16):  # both on the row-form kernel (0x40000000: not the channels-last route)
+        for flags in (0, 128 << 16):
             buf = torch.full((n_out + 64,), 3.0, dtype=dtype, device="cuda")  # guard band on both sides
             Y = buf[32:32 + n_out].view(f.output_shape())
-            lib.set_tuning(0, flags)
+            lib.set_tuning(NO_CL, flags)  # both on the row-form kernel
             try:
                 if fused:
                     gdnn.conv2d_filter(X, Wt, Y, f, bias=bias, residual=R, activation="relu")
@@ -827,8 +828,8 @@ def test_conv2d_pointwise_table_lookup_matches_affine(lib, dtype):
         Wt = torch.from_numpy((0.1 * rng.normal(size=(Co, C // group, KH, KW))).astype(np.float32)).to(dtype).cuda()
         filt = gdnn.Filter2D(X.shape, Wt.shape, group).pads(*pads).strides(*strides).dilations(*dil)
         outs = []
-        for flags in (0x40000000, 0x2000):  # both on the gathering kernel
-            lib.set_tuning(0, flags)
+        for flags in (0, 0x2000):
+            lib.set_tuning(NO_CL, flags)  # both on the gathering kernel
             try:
                 Y = torch.full(filt.output_shape(), float("nan"), dtype=dtype, device="cuda")
                 gdnn.conv2d_filter(X, Wt, Y, filt)
@@ -849,7 +850,7 @@ def test_conv2d_pointwise_table_lookup_matches_affine(lib, dtype):
 def test_conv2d_swapped_roles_every_vector_width(lib, case, dtype):
     """The channels-last route with the roles swapped (lanes = output channels, columns = pixels,
     each lane storing vectors of consecutive pixels) is the default only for planes of a multiple of
-    8 pixels; measurement bit 0x100 turns it on for vectors of 4 and 2 as well. All of them against
+    8 pixels; bit 17 of the tile-width word turns it on for vectors of 4 and 2 as well. All of them against
     the oracle, with a residual and ReLU, and nothing outside Y touched."""
     from dlf_b200 import gdnn
     N, C, H, W, Co, k, s, p = case
@@ -863,10 +864,44 @@ def test_conv2d_swapped_roles_every_vector_width(lib, case, dtype):
     R = torch.from_numpy(Rh).to(dtype).cuda()
     n_out = int(np.prod(f.output_shape()))
     ref = oracle.conv2d_fused(Xh, Wh, residual=Rh, relu=True, bias=bh, pads=(p,) * 4, strides=(s, s), wide=True)
-    for flags in (0, 0x100):
+    for route in (0, 0x20000):
         buf = torch.full((n_out + 64,), 3.0, dtype=dtype, device="cuda")
         Y = buf[32:32 + n_out].view(f.output_shape())
-        lib.set_tuning(0, flags)
+        lib.set_tuning(route, 0)
+        try:
+            gdnn.conv2d_filter(X, Wt, Y, f, bias=b, residual=R, activation="relu")
+            torch.cuda.synchronize()
+        finally:
+            lib.set_tuning(0, 0)
+        assert bool((buf[:32] == 3.0).all()) and bool((buf[32 + n_out:] == 3.0).all())
+        assert max_rel(Y.float().cpu().numpy(), ref) <= HALF_TOL
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("case", [(3, 64, 8, 16, 136), (2, 72, 28, 28, 520), (5, 128, 5, 8, 128), (2, 64, 12, 12, 200)],
+                         ids=lambda c: "x".join(map(str, c)))
+def test_conv2d_pointwise_batched_gemm_both_orientations(lib, case, dtype):
+    """A 1x1 stride-1 convolution on 16-byte-aligned planes is a batched GEMM over the images; with
+    128 output channels or more it runs with the roles swapped (lanes = output channels, TMA stores
+    of [channel][pixel] boxes; planes that are not a multiple of 32 pixels end in a box clipped by
+    the hardware or in per-lane stores). Both orientations against the oracle, with residual and
+    ReLU, nothing outside Y touched."""
+    from dlf_b200 import gdnn
+    N, C, H, W, Co = case
+    rng = np.random.default_rng(sum(case))
+    Xh = _round_to(rng.normal(size=(N, C, H, W)).astype(np.float32), dtype)
+    Wh = _round_to((np.sqrt(2.0 / C) * rng.normal(size=(Co, C, 1, 1))).astype(np.float32), dtype)
+    bh = _round_to(rng.uniform(-0.1, 0.1, Co).astype(np.float32), dtype)
+    X, Wt, b = (torch.from_numpy(a).to(dtype).cuda() for a in (Xh, Wh, bh))
+    f = gdnn.Filter2D(X.shape, Wt.shape)
+    Rh = _round_to(rng.normal(size=tuple(f.output_shape())).astype(np.float32), dtype)
+    R = torch.from_numpy(Rh).to(dtype).cuda()
+    n_out = int(np.prod(f.output_shape()))
+    ref = oracle.conv2d_fused(Xh, Wh, residual=Rh, relu=True, bias=bh, wide=True)
+    for route in (0, 0x80000):
+        buf = torch.full((n_out + 64,), 3.0, dtype=dtype, device="cuda")
+        Y = buf[32:32 + n_out].view(f.output_shape())
+        lib.set_tuning(route, 0)
         try:
             gdnn.conv2d_filter(X, Wt, Y, f, bias=b, residual=R, activation="relu")
             torch.cuda.synchronize()
@@ -889,7 +924,7 @@ FUSED_CASES = [
 
 @pytest.fixture
 def _route(lib, request):
-    lib.set_tuning(0, request.param)
+    lib.set_tuning(request.param, 0)
     yield request.param
     lib.set_tuning(0, 0)
 
@@ -1233,7 +1268,7 @@ def test_conv2d_workspace_bound_covers_the_packed_filter_bank(lib, shape, dtype)
     W = (torch.randn(cout, cin, k, k, device="cuda") * 0.05).to(dtype)
     f = gdnn.Filter2D(X.shape, W.shape).pads(p, p).strides(s, s)
     Y = torch.empty(f.output_shape(), device="cuda", dtype=dtype)
-    lib.set_tuning(0, 0x40000000)  # the kernels that gather the activations themselves
+    lib.set_tuning(NO_CL, 0)  # the kernels that gather the activations themselves
     try:
         n0 = lib.launch_count()
         gdnn.conv2d_filter(X, W, Y, f)
