@@ -299,6 +299,32 @@ class GemmWorkload(Workload):
         self.C = [torch.randn(self.batch * self.m * self.n, generator=g, device=device, dtype=torch.float32).to(td)
                   for _ in range(sets)]
 
+    def step_abi(self, i):
+        """The same step straight through the C ABI with arguments converted once (a single GEMM
+        only): for products of a few microseconds, where the Python mirror's argument checks would
+        set the rate. Scratch for the K-split comes from the workload, as a dlf caller's pool would."""
+        import ctypes
+        import dlf_b200
+        L = dlf_b200.lib()
+        if not hasattr(self, "_abi"):
+            dt = {"f32": 32, "f16": 16, "bf16": 1600}[self.dtype]
+            td = self.torch_dtype()
+            self._al = torch.tensor([self.alpha], dtype=td).numpy().tobytes() if td == torch.float32 else \
+                torch.tensor([self.alpha], dtype=td).view(torch.int16).numpy().tobytes()
+            self._be = torch.tensor([self.beta], dtype=td).numpy().tobytes() if td == torch.float32 else \
+                torch.tensor([self.beta], dtype=td).view(torch.int16).numpy().tobytes()
+            need = L.dlf_b200_gemm_workspace_bytes(dt, self.m, self.n, self.k)
+            self._ws = torch.empty(max(int(need), 1), dtype=torch.uint8, device=self.A[0].device)
+            lda = self.m if self.ta else self.k
+            ldb = self.k if self.tb else self.n
+            P = lambda t: ctypes.c_void_p(t.data_ptr())
+            self._abi = [(dt, 101, 112 if self.ta else 111, 112 if self.tb else 111, self.m, self.n, self.k,
+                          ctypes.c_char_p(self._al), P(self.A[j]), lda, P(self.B[j]), ldb, ctypes.c_char_p(self._be),
+                          P(self.C[j]), self.n, P(self._ws) if need else None, int(need)) for j in range(self.sets)]
+        rc = L.dlf_b200_gemm_ex(*self._abi[i % self.sets], ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+        if rc != 0:
+            raise RuntimeError("dlf_b200_gemm_ex: %d" % rc)
+
     def step_sharded(self, i, world, rank):
         """One large GEMM over `world` GPUs: rank r computes its block of rows of C, then the row
         blocks are all-gathered (NCCL) so that every rank holds all of C. Operands are replicated."""
@@ -514,10 +540,12 @@ def time_steps_graph(fn, steps, warmup, per_graph=20):
 def run_extra(w, device, peaks, steps, warmup, graph=False):
     """Kernel-only numbers for a further BASELINE configuration (reported under "workloads")."""
     w.setup(device, 0, w.sets_needed())
-    ms = time_steps_graph(w.step, steps, warmup) if graph else None
-    timed = "cuda graph replay (20 steps per graph)" if ms is not None else "stream launches"
+    step = w.step_abi if (graph and hasattr(w, "step_abi") and w.batch == 1) else w.step
+    ms = time_steps_graph(step, steps, warmup) if graph else None
+    timed = "cuda graph replay (20 steps per graph)" if ms is not None else \
+        ("stream launches through the C ABI" if step is not w.step else "stream launches")
     if ms is None:
-        ms, _, _ = time_steps(w.step, steps, warmup, 1)
+        ms, _, _ = time_steps(step, steps, warmup, 1)
     sec = ms / 1e3 / steps
     tf = w.flops / sec / 1e12
     return {"tflops": round(tf, 2), "us_per_step": round(sec * 1e6, 2), "dtype": w.dtype,

@@ -22,6 +22,7 @@
 #include "channels_last.cuh"
 #include "contraction.cuh"
 #include "contraction_ts.cuh"
+#include "conv_small.cuh"
 #include "level3.cuh"
 #include "pooling.cuh"
 
@@ -60,6 +61,7 @@ struct DeviceState {
     int static_smem_ts2 = 0;
     int static_smem_ts4 = 0;
     int static_smem_pair = 0;
+    int static_smem_small = 0;
     int max_pair_clusters = 0;  // co-resident CTA pairs of the pair kernel (0 = not usable)
     PFN_cuTensorMapEncodeTiled_v12000 encode = nullptr;
     PFN_cuTensorMapEncodeIm2col_v12000 encode_im2col = nullptr;  // null: the driver has none
@@ -176,6 +178,10 @@ int ensure_device(DeviceState** out) {
         CUDA_TRY(cudaFuncSetAttribute(contraction_kernel<4, false>,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       kSmemPerBlockOptin - st.static_smem_gen4));
+        CUDA_TRY(cudaFuncGetAttributes(&fa, conv_small_kernel));
+        st.static_smem_small = static_cast<int>(fa.sharedSizeBytes);
+        CUDA_TRY(cudaFuncSetAttribute(conv_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      kSmemPerBlockOptin - st.static_smem_small));
         {
             int rc2 = setup_ts_kernels<2>(&st.static_smem_ts2);
             if (rc2 != kSuccess) return rc2;
@@ -276,10 +282,7 @@ struct Problem {
     // channels-last route of a convolution (channels_last.cuh): a.base is the channels-last copy.
     // a_cl == 1: operand A comes through an im2col-mode tensor map over (cl_n, cl_h, cl_w, cl_cp);
     // out_nchw: rows are output pixels of an NCHW tensor (g.P, g.out_img_stride)
-    // a_cl == 2: filters over <= 4 channels; a.base is the bordered row-pair copy (cl_n, cl_h, cl_w
-    // = images, row pairs, bordered row length; cl_rstep rows between pairs), tiles are 128 outputs
-    // of one output row
-    int a_cl = 0, cl_cblocks = 0, cl_tpr = 0, cl_rstep = 1;
+    int a_cl = 0, cl_cblocks = 0;
     // cl_swap: rows of the problem are output channels (a = filter bank), columns are output pixels
     // (b = the channels-last copy; with a_cl == 1 through the im2col-mode map); out_nchw == 3 and
     // out_vec = elements per store of one lane
@@ -363,25 +366,6 @@ int encode_im2col_map(const DeviceState& st, CUtensorMap* map, const Problem& q,
     return r == CUDA_SUCCESS ? kSuccess : kNotImplemented;
 }
 
-// Tiled map over the bordered row-pair copy X'' (N, J, Wp, 2, 4) of an input with <= 4 channels:
-// {64 elements = 8 pixels x 2 rows x 4 channels, outputs of a row (one step = stride_w pixels =
-// stride_w * 16 bytes, so windows of neighbouring outputs overlap), row pairs, images}; a box is
-// [128 outputs][64 elements], one 128-byte k-block line per output.
-int encode_small_map(const DeviceState& st, CUtensorMap* map, const Problem& q) {
-    cuuint64_t dims[4] = {64, static_cast<cuuint64_t>(q.g.OW), static_cast<cuuint64_t>(q.cl_h),
-                          static_cast<cuuint64_t>(q.cl_n)};
-    cuuint64_t strides[3] = {static_cast<cuuint64_t>(q.g.sw * 16), static_cast<cuuint64_t>(q.cl_w * 16),
-                             static_cast<cuuint64_t>(q.cl_h * q.cl_w * 16)};
-    cuuint32_t box[4] = {64, kBM, 1, 1};
-    cuuint32_t estr[4] = {1, 1, 1, 1};
-    CUresult r = st.encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, const_cast<char*>(q.a.base), dims, strides, box, estr,
-                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS && std::getenv("DLF_B200_DEBUG"))
-        std::fprintf(stderr, "dlf_b200: small-channel tensor map refused (%d)\n", static_cast<int>(r));
-    return r == CUDA_SUCCESS ? kSuccess : kNotImplemented;
-}
-
 // Tensor map for TMA stores of the output (blocks of 32 rows x 32 or 64 columns, no swizzle): only when nothing of C has
 // to be read (beta == 0, no per-batch tables) and D's base and strides are 16-byte multiples.
 bool encode_output_map(const DeviceState& st, CUtensorMap* map, const Problem& q, unsigned box_cols) {
@@ -399,23 +383,6 @@ bool encode_output_map(const DeviceState& st, CUtensorMap* map, const Problem& q
         cuuint32_t box[3] = {32, 32, 1};
         cuuint32_t estr[3] = {1, 1, 1};
         CUresult r = st.encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, q.d, dims, strides, box, estr,
-                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
-                               CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        return r == CUDA_SUCCESS;
-    }
-    if (q.out_nchw == 2) {
-        // NCHW output written row by row: {OW, OH, channels, images}, boxes of 32 outputs of one row
-        const long long P = q.g.P, OW = q.g.OW;
-        const bool ok = q.es == 2 && q.beta == 0.0f && (reinterpret_cast<uintptr_t>(q.d) & 15u) == 0 &&
-                        (OW * q.es) % 16 == 0 && P * q.N * q.es < (1ll << 40) && !(g_force_generic.load() & 0x4000);
-        if (!ok) return false;
-        cuuint64_t dims[4] = {static_cast<cuuint64_t>(OW), static_cast<cuuint64_t>(q.g.OH), static_cast<cuuint64_t>(q.N),
-                              static_cast<cuuint64_t>(q.cl_n)};
-        cuuint64_t strides[3] = {static_cast<cuuint64_t>(OW * q.es), static_cast<cuuint64_t>(P * q.es),
-                                 static_cast<cuuint64_t>(P * q.N * q.es)};
-        cuuint32_t box[4] = {32, 1, box_cols, 1};
-        cuuint32_t estr[4] = {1, 1, 1, 1};
-        CUresult r = st.encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, q.d, dims, strides, box, estr,
                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
                                CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         return r == CUDA_SUCCESS;
@@ -876,8 +843,6 @@ int launch(const Problem& q, cudaStream_t stream, DeviceState* preset = nullptr)
     p.a_cl = q.a_cl;
     p.cl_cblocks = q.cl_cblocks;
     p.out_nchw = q.out_nchw;
-    p.cl_tpr = q.cl_tpr;
-    p.cl_rstep = q.cl_rstep;
     p.cl_swap = q.cl_swap;
     p.out_vec = q.out_vec;
     set_wait_policy(p, total);
@@ -894,9 +859,8 @@ int launch(const Problem& q, cudaStream_t stream, DeviceState* preset = nullptr)
             rc = q.a_cl == 1 ? encode_im2col_map(*st, &tm_b, q, q.b.base, bn)
                              : encode_map(*st, &tm_b, q.b, q.es, q.N, q.K, q.batch, bn);
         } else {
-            rc = q.a_cl == 1   ? encode_im2col_map(*st, &tm_a, q, q.a.base, kBM)
-                 : q.a_cl == 2 ? encode_small_map(*st, &tm_a, q)
-                               : encode_map(*st, &tm_a, q.a, q.es, q.M, q.K, q.batch, kBM);
+            rc = q.a_cl == 1 ? encode_im2col_map(*st, &tm_a, q, q.a.base, kBM)
+                             : encode_map(*st, &tm_a, q.a, q.es, q.M, q.K, q.batch, kBM);
             if (rc != kSuccess) return rc;
             rc = encode_map(*st, &tm_b, q.b, q.es, q.N, q.K, q.batch, bn);
         }
@@ -1382,8 +1346,9 @@ size_t dlf_b200_conv2d_workspace_bytes(int dtype, size_t batches, size_t channel
         const size_t cl = batches * height * width * cp * 2 + num_kernels * kernel_h * kernel_w * ck * 2 + 4096;
         if (cl > need) need = cl;
         if (channels <= 4) {
-            // bordered row-pair copy: at most (H + 2*KH + 2) row pairs of (W + 2*KW + 10) pixels of 16 bytes per image
-            const size_t small = batches * (height + 2 * kernel_h + 2) * (width + 2 * kernel_w + 10) * 16 +
+            // bordered row-pair copy: at most (H + 2*KH + 2) row pairs of (W + 2*KW + 80) pixels of 16 bytes per image
+            // (all phases of a row together; every phase rounded up to the tile's columns per row)
+            const size_t small = batches * (height + 2 * kernel_h + 2) * (width + 2 * kernel_w + 80) * 16 +
                                  num_kernels * (kernel_h + 1) / 2 * 128 + 4096;
             if (small > need) need = small;
         }
@@ -1517,9 +1482,9 @@ int dlf_b200_conv2d_fused(int dtype, size_t batches, size_t channels, size_t hei
     q.g.out_img_stride = static_cast<long long>(num_kernels) * P;
     if (P > INT_MAX) return kInvalidDimension;
 
-    // Filters over at most 4 input channels and at most 8 taps per row (the 7x7 stride-2 RGB stem
-    // of a ResNet): bordered row-pair copy + tiled tensor map whose windows overlap, see
-    // channels_last.cuh. One M-tile is 128 outputs of one output row.
+    // Filters over at most 4 input channels, at most 8 taps per row, horizontal stride 1, 2 or 4 and
+    // at most 128 output channels (the 7x7 stride-2 RGB stem of a ResNet): bordered, phase-split
+    // row-pair copy (channels_last.cuh) + the dedicated kernel of conv_small.cuh.
     {
         const int tune = g_force_generic.load();
         const int cl_neutral = 0x100 | 0x4000 | 0x10000000 | 0x20000000;
@@ -1527,65 +1492,113 @@ int dlf_b200_conv2d_fused(int dtype, size_t batches, size_t channels, size_t hei
         const long long kb2 = (static_cast<long long>(kernel_h) + 1) / 2;
         const long long rstep = stride_h % 2 == 0 ? 2 : 1;
         const long long jn = ((static_cast<long long>(output_h) - 1) * stride_h + 2 * (kb2 - 1)) / rstep + 1;  // row pairs
-        const long long wp = (static_cast<long long>(output_w) - 1) * stride_w + 8;
+        const bool sw_ok = stride_w == 1 || stride_w == 2 || stride_w == 4;
+        const long long swl = sw_ok ? static_cast<long long>(stride_w) : 1;
+        const long long wph = static_cast<long long>(output_w) - 1 + 8 / swl;  // pixels per phase of a bordered row
+        const long long owp = (wph + 7) / 8 * 8;                               // tile columns per output row
         const size_t w_bytes = (static_cast<size_t>(num_kernels) * kb2 * 128 + 1023) / 1024 * 1024;
-        const size_t x_bytes = static_cast<size_t>(batches) * jn * wp * 16;
+        const size_t x_bytes = static_cast<size_t>(batches) * jn * swl * (owp + 8) * 16;  // rows of up to owp + 8 pixels
         unsigned char* ws = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(workspace) + 255u) & ~uintptr_t(255));
         const size_t slack = static_cast<size_t>(ws - static_cast<unsigned char*>(workspace));
-        const long long tpr = (static_cast<long long>(output_w) + kBM - 1) / kBM;
-        const long long rows = static_cast<long long>(batches) * output_h;
         if (q.es == 2 && group == 1 && channels <= 4 && (tune & ~cl_neutral) == 0 && !(route & 1) && workspace != nullptr &&
-            workspace_bytes >= slack + w_bytes + x_bytes && kernel_w <= 8 && stride_w <= 64 && stride_h <= 64 &&
-            dilation_h == 1 && dilation_w == 1 && rows * tpr < (INT_MAX - 512) / kBM && jn < (1 << 28) && wp < (1 << 27) &&
-            pad_top < (1u << 28) && pad_left < (1u << 28)) {
+            workspace_bytes >= slack + w_bytes + x_bytes && kernel_w <= 8 && sw_ok && stride_h <= 2 &&
+            dilation_h == 1 && dilation_w == 1 && num_kernels <= 128 && owp <= 240 && jn < (1 << 28) &&
+            pad_top < (1u << 28) && pad_left < (1u << 28) && P * static_cast<long long>(num_kernels) < (1ll << 38)) {
             DeviceState* st = nullptr;
             int rc = ensure_device(&st);
             if (rc != kSuccess) return rc;
-            clear_stale_error();
-            cudaStream_t cs = static_cast<cudaStream_t>(stream);
-            uint16_t* wpk = reinterpret_cast<uint16_t*>(ws);
-            uint4* xp = reinterpret_cast<uint4*>(ws + w_bytes);
-            const long long total = static_cast<long long>(batches) * jn * wp;
-            const unsigned xblocks = static_cast<unsigned>(std::min<long long>((total + 255) / 256, 32ll * st->num_sms));
-            cl_pack_small_activations_kernel<<<xblocks, 256, 0, cs>>>(
-                static_cast<const uint16_t*>(x), xp, static_cast<int>(channels), static_cast<int>(height),
-                static_cast<int>(width), static_cast<int>(jn), static_cast<int>(wp), static_cast<int>(rstep),
-                static_cast<int>(pad_top), static_cast<int>(pad_left), total);
-            g_launches.fetch_add(1);
-            CUDA_TRY(cudaGetLastError());
-            const long long wtotal = static_cast<long long>(num_kernels) * kb2 * 64;
-            cl_pack_small_filters_kernel<<<static_cast<unsigned>(std::min<long long>((wtotal + 255) / 256, 8ll * st->num_sms)), 256, 0, cs>>>(
-                static_cast<const uint16_t*>(w), wpk, static_cast<int>(num_kernels), static_cast<int>(channels),
-                static_cast<int>(kernel_h), static_cast<int>(kernel_w), static_cast<int>(kb2));
-            g_launches.fetch_add(1);
-            CUDA_TRY(cudaGetLastError());
-            Problem r = q;
-            r.batch = 1;
-            r.M = rows * tpr * kBM;  // tiles x 128 rows; rows beyond OW of a tile are not outputs
-            r.N = static_cast<long long>(num_kernels);
-            r.K = kb2 * 64;
-            r.a.base = reinterpret_cast<const char*>(xp);
-            r.a.im2col = 0;
-            r.a.k_major = 1;
-            r.a.ld = 0;
-            r.a.batch_stride = 0;
-            r.b.base = reinterpret_cast<const char*>(wpk);
-            r.b.k_major = 1;
-            r.b.ld = r.K;
-            r.b.batch_stride = 0;
-            r.d_batch_stride = 0;
-            r.bias_stride = 0;
-            r.out_nchw = 2;
-            r.a_cl = 2;
-            r.cl_tpr = static_cast<int>(tpr);
-            r.cl_n = static_cast<long long>(batches);
-            r.cl_h = jn;
-            r.cl_w = wp;
-            r.cl_rstep = static_cast<int>(rstep);
-            r.pack_ws = nullptr;
-            r.pack_ws_bytes = 0;
-            rc = launch(r, cs, st);
-            if (rc != kNotImplemented) return rc;
+            SmallParams sp{};
+            // rows per tile: as many as 240 columns hold (two accumulators and the 32-column loads of
+            // the epilogue must stay inside the 512 columns of tensor memory), an even count when the
+            // width per row is an odd multiple of 8, so that the tile width is a multiple of 16
+            int rr = static_cast<int>(240 / owp);
+            if (rr > static_cast<int>(output_h)) rr = static_cast<int>(output_h);
+            long long owp_t = owp;
+            if ((rr * owp_t) % 16 != 0) {
+                if (rr > 1) --rr;
+                else owp_t += 8;
+            }
+            sp.R = rr;
+            sp.OWp = static_cast<int>(owp_t);
+            sp.BN = static_cast<int>(rr * owp_t);
+            sp.kb_rows = static_cast<int>(2 / rstep);
+            sp.span = rr + sp.kb_rows * static_cast<int>(kb2 - 1);
+            sp.phase_bytes = static_cast<unsigned>((sp.span * owp_t + 8) * 16);
+            sp.stage_bytes = static_cast<unsigned>((swl * sp.phase_bytes + 127) / 128 * 128);
+            const long long a_bytes = kb2 * kBM * 128;
+            long long stages = (kSmemPerBlockOptin - st->static_smem_small - 1024 - a_bytes - kSmallStageOut) / sp.stage_bytes;
+            if (stages > kSmallMaxStages) stages = kSmallMaxStages;
+            const long long tiles_per_image = (static_cast<long long>(output_h) + rr - 1) / rr;
+            const long long total_tiles = static_cast<long long>(batches) * tiles_per_image;
+            if (stages >= 2 && total_tiles < INT_MAX && sp.BN <= 240 && sp.BN % 16 == 0) {
+                clear_stale_error();
+                cudaStream_t cs = static_cast<cudaStream_t>(stream);
+                uint16_t* wpk = reinterpret_cast<uint16_t*>(ws);
+                uint4* xp = reinterpret_cast<uint4*>(ws + w_bytes);
+                const long long total = static_cast<long long>(batches) * swl * jn * owp_t;
+                const unsigned xblocks = static_cast<unsigned>(std::min<long long>((total + 255) / 256, 32ll * st->num_sms));
+                cl_pack_small_activations_kernel<<<xblocks, 256, 0, cs>>>(
+                    static_cast<const uint16_t*>(x), xp, static_cast<int>(channels), static_cast<int>(height),
+                    static_cast<int>(width), static_cast<int>(jn), static_cast<int>(owp_t), static_cast<int>(swl),
+                    static_cast<int>(rstep), static_cast<int>(pad_top), static_cast<int>(pad_left), total);
+                g_launches.fetch_add(1);
+                CUDA_TRY(cudaGetLastError());
+                const long long wtotal = static_cast<long long>(num_kernels) * kb2 * 64;
+                cl_pack_small_filters_kernel<<<static_cast<unsigned>(std::min<long long>((wtotal + 255) / 256, 8ll * st->num_sms)), 256, 0, cs>>>(
+                    static_cast<const uint16_t*>(w), wpk, static_cast<int>(num_kernels), static_cast<int>(channels),
+                    static_cast<int>(kernel_h), static_cast<int>(kernel_w), static_cast<int>(kb2), static_cast<int>(swl));
+                g_launches.fetch_add(1);
+                CUDA_TRY(cudaGetLastError());
+                sp.xp = reinterpret_cast<const char*>(xp);
+                sp.y = static_cast<char*>(y);
+                sp.bias = static_cast<const char*>(bias);
+                sp.resid = q.resid;
+                sp.relu = q.relu;
+                sp.fmt = q.fmt;
+                sp.Cout = static_cast<int>(num_kernels);
+                sp.OH = static_cast<int>(output_h);
+                sp.OW = static_cast<int>(output_w);
+                sp.P = static_cast<int>(P);
+                sp.J = static_cast<int>(jn);
+                sp.sh = static_cast<int>(stride_h);
+                sp.sw = static_cast<int>(swl);
+                sp.rstep = static_cast<int>(rstep);
+                sp.KB = static_cast<int>(kb2);
+                sp.images = static_cast<int>(batches);
+                sp.tiles_per_image = static_cast<int>(tiles_per_image);
+                sp.total_tiles = static_cast<int>(total_tiles);
+                sp.out_img_stride = static_cast<long long>(num_kernels) * P;
+                sp.stages = static_cast<int>(stages);
+                sp.status = st->status;
+                sp.wait_limit = 1ll << 32;
+                CUtensorMap tm_w, tm_d;
+                std::memset(&tm_d, 0, sizeof(tm_d));
+                GenOperand wop{};
+                wop.base = reinterpret_cast<const char*>(wpk);
+                wop.ld = kb2 * 64;
+                wop.k_major = 1;
+                rc = encode_map(*st, &tm_w, wop, 2, static_cast<long long>(num_kernels), kb2 * 64, 1, kBM);
+                if (rc != kSuccess) return rc;
+                const uintptr_t ya = reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(residual);
+                if (P % 8 == 0 && output_w % 8 == 0 && ya % 16 == 0 && !(tune & 0x4000)) {
+                    cuuint64_t dims[3] = {static_cast<cuuint64_t>(P), static_cast<cuuint64_t>(num_kernels),
+                                          static_cast<cuuint64_t>(batches)};
+                    cuuint64_t strides[2] = {static_cast<cuuint64_t>(P * 2), static_cast<cuuint64_t>(P * num_kernels * 2)};
+                    cuuint32_t box[3] = {32, 32, 1};
+                    cuuint32_t estr[3] = {1, 1, 1};
+                    sp.d_tma = st->encode(&tm_d, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, y, dims, strides, box, estr,
+                                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                          CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS
+                                   ? 1
+                                   : 0;
+                }
+                const unsigned grid = static_cast<unsigned>(total_tiles < st->num_sms ? total_tiles : st->num_sms);
+                const size_t dyn = static_cast<size_t>(a_bytes) + kSmallStageOut + static_cast<size_t>(stages) * sp.stage_bytes + 1024;
+                conv_small_kernel<<<grid, kSmallThreads, dyn, cs>>>(sp, tm_w, tm_d);
+                g_launches.fetch_add(1);
+                CUDA_TRY(cudaGetLastError());
+                return kSuccess;
+            }
         }
     }
 

@@ -178,25 +178,32 @@ __global__ void cl_pack_filters_kernel(const uint16_t* __restrict__ w, uint16_t*
 
 // Filters over at most 4 input channels (an RGB stem). With so few channels a filter tap is 8
 // bytes and the tap-by-tap loads above would spend a 64-channel k-block on 4 of them. Instead the
-// copy interleaves two image rows and carries a zero border wide enough for every filter window:
-//     X'' (N, J, Wp, 2, 4),  X''[n][j][q][rr][c] = X[n][c][j*rstep + rr - pad_top][q - pad_left]
-// (zero outside the image or for c >= C), so that the 8 pixels a window covers in the filter rows
-// kh = 2*kb, 2*kb + 1 are 128 contiguous bytes of X''. A tiled tensor map whose "pixel" dimension
-// advances by the horizontal stride (windows of neighbouring outputs overlap) then fetches
-// [128 outputs][64 elements] boxes: one 128-byte line of the K-major operand per output,
-// k = kw * 8 + (kh & 1) * 4 + c within k-block kb. Row pairs start at rows j*rstep: every row when
-// the vertical stride is odd, every second row when it is even (only those are ever read).
-// The filters are laid out to match (zero for kw >= KW, c >= C, kh >= KH).
+// copy interleaves two image rows, carries a zero border wide enough for every filter window and
+// splits the pixels of a row into sw phases:
+//     X'' (N, sw, J, OWp, 2, 4),
+//     X''[n][ph][j][i][rr][c] = X[n][c][j*rstep + rr - pad_top][i*sw + ph - pad_left]
+// (zero outside the image or for c >= C): 16 bytes per pixel, the pixels i*sw + ph that
+// consecutive outputs i need for one filter tap are consecutive in memory, and so are the row
+// pairs of one phase that a tile of output rows needs (OWp pixels per row, the tile's column count
+// per output row). conv_small.cuh reads the overlapping filter windows straight out of a copy of
+// such rows. Row pairs start at rows j*rstep:
+// every row when the vertical stride is odd, every second row when it is even (only those are
+// ever read). The filters are laid out to match: k-block kb covers filter rows 2*kb, 2*kb+1; its
+// four 16-element k-steps are taps (m, m+1) of phase ph in the order ph = 0: m = 0, 2, ..; ph = 1:
+// ..., i.e. filter columns kw = sw*(m + c) + ph for the step's chunk c, each chunk holding
+// (kh & 1) * 4 + channel (zero for kw >= KW, channel >= C, kh >= KH).
 __global__ void __launch_bounds__(256)
     cl_pack_small_activations_kernel(const uint16_t* __restrict__ x, uint4* __restrict__ xp, int C, int H, int W,
-                                     int J, int Wp, int rstep, int pad_t, int pad_l, long long total) {
+                                     int J, int OWp, int sw, int rstep, int pad_t, int pad_l, long long total) {
     for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
          i += static_cast<long long>(gridDim.x) * blockDim.x) {
-        const int q = static_cast<int>(i % Wp);
-        const long long r0 = i / Wp;
+        const int ii = static_cast<int>(i % OWp);
+        long long r0 = i / OWp;
         const int j = static_cast<int>(r0 % J);
-        const long long n = r0 / J;
-        const int iw = q - pad_l;
+        r0 /= J;
+        const int ph = static_cast<int>(r0 % sw);
+        const long long n = r0 / sw;
+        const int iw = ii * sw + ph - pad_l;
         uint32_t v[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
         if (static_cast<unsigned>(iw) < static_cast<unsigned>(W)) {
 #pragma unroll
@@ -216,17 +223,20 @@ __global__ void __launch_bounds__(256)
 
 // one thread per element of W'' (Cout, KB, 64)
 __global__ void cl_pack_small_filters_kernel(const uint16_t* __restrict__ w, uint16_t* __restrict__ wp, int Cout,
-                                             int C, int KH, int KW, int KB) {
+                                             int C, int KH, int KW, int KB, int sw) {
     const long long total = static_cast<long long>(Cout) * KB * 64;
+    const int tpp = 8 / sw;  // taps per phase
     for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
          i += static_cast<long long>(gridDim.x) * blockDim.x) {
-        const int e = static_cast<int>(i & 63);
+        const int k = static_cast<int>(i & 63);
         const long long r = i >> 6;
         const int kb = static_cast<int>(r % KB);
         const long long co = r / KB;
-        const int kw = e >> 3, kh = 2 * kb + ((e >> 2) & 1), c = e & 3;
+        const int ks = k >> 4, c = (k >> 3) & 1, e = k & 7;
+        const int ph = (2 * ks) / tpp, m = (2 * ks) % tpp;
+        const int kw = sw * (m + c) + ph, kh = 2 * kb + (e >> 2), ch = e & 3;
         uint16_t v = 0;
-        if (kh < KH && kw < KW && c < C) v = w[((co * C + c) * KH + kh) * KW + kw];
+        if (kh < KH && kw < KW && ch < C) v = w[((co * C + ch) * KH + kh) * KW + kw];
         wp[i] = v;
     }
 }

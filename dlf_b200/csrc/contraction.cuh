@@ -126,12 +126,7 @@ struct Params {
     // kb % cl_cblocks of filter tap kb / cl_cblocks and one load brings the tile's 128 windows.
     // out_nchw: row i of the problem is output pixel img * P + pp and lands in an NCHW tensor
     // (the output mapping of the implicit-im2col operand, whatever A is).
-    // a_cl == 2 (filters over <= 4 channels, see channels_last.cuh): tmA is a tiled map over the
-    // bordered row-pair copy; an M-tile is 128 consecutive outputs of one output row (cl_tpr tiles
-    // per row, rows (image, oh)), k-block kb covers filter rows 2*kb, 2*kb+1, i.e. row pair
-    // (oh*sh + 2*kb) / cl_rstep of the copy; out_nchw == 2 is the matching output mapping (tmD is
-    // then the 4-D map {OW, OH, channels, images}).
-    int a_cl, cl_cblocks, out_nchw, cl_tpr, cl_rstep;
+    int a_cl, cl_cblocks, out_nchw;
     // cl_swap: the roles are swapped - operand A (rows, tensor-memory lanes) is the filter bank,
     // operand B (columns) the channels-last activations (tmB is then the im2col-mode map when
     // a_cl == 1), and the output mapping is out_nchw == 3: row = output channel, column = output
@@ -506,21 +501,10 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
                 }
             }
             const int i = m0 + q * 32 + lane;
-            bool row_ok = i < p.M;
+            const bool row_ok = i < p.M;
             long long rowbase;
             long long colstride;
-            int rt_n = 0, rt_oh = 0, rt_ow0 = 0;  // out_nchw == 2: image, output row, first column of the tile
-            if (p.out_nchw == 2) {
-                const int mt = m0 / kBM;
-                const int rowid = mt / p.cl_tpr;
-                rt_ow0 = (mt - rowid * p.cl_tpr) * kBM;
-                rt_n = rowid / p.g.OH;
-                rt_oh = rowid - rt_n * p.g.OH;
-                const int ow = rt_ow0 + q * 32 + lane;
-                row_ok = ow < p.g.OW;
-                rowbase = static_cast<long long>(rt_n) * p.g.out_img_stride + static_cast<long long>(rt_oh) * p.g.OW + ow;
-                colstride = p.g.P;
-            } else if (p.a.im2col || p.out_nchw) {
+            if (p.a.im2col || p.out_nchw) {
                 const int img = i / p.g.P;
                 const int pp = i - img * p.g.P;
                 rowbase = static_cast<long long>(img) * p.g.out_img_stride +
@@ -547,7 +531,7 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
                     const int img0 = p.out_nchw == 1 ? i0 / p.g.P : 0;
                     const int pp0 = p.out_nchw == 1 ? i0 - img0 * p.g.P : i0;
                     const bool direct = p.out_nchw == 1 && pp0 + 32 > p.g.P;
-                    const bool blk_ok = p.out_nchw == 2 ? (rt_ow0 + q * 32 < p.g.OW) : (i0 < p.M);
+                    const bool blk_ok = i0 < p.M;
                     // Blocks of 32 rows x 32 columns go to one of the warp's two staging buffers
                     // (2 KB each, adjacent). With 32-column boxes the buffers alternate and every
                     // block is one TMA store; with 64-column boxes (tiles of 128 columns or more)
@@ -630,10 +614,7 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
                         if (lane == 0) {
                             const uint32_t ssrc = ptx::smem_u32(d_stage) + (ewarp * 2 + (wide ? 0u : half)) * 2048u;
                             const int col = n0 + cb + (wide ? (c0 & ~63) : c0);
-                            if (p.out_nchw == 2)
-                                ptx::tma_store_4d(&tmD, ssrc, rt_ow0 + q * 32, rt_oh, col, rt_n);
-                            else
-                                ptx::tma_store_3d(&tmD, ssrc, pp0, col, p.out_nchw == 1 ? img0 : (p.d_batch_stride ? b : 0));
+                            ptx::tma_store_3d(&tmD, ssrc, pp0, col, p.out_nchw == 1 ? img0 : (p.d_batch_stride ? b : 0));
                             ptx::bulk_commit_group();
                         }
                     }
@@ -809,24 +790,6 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
                                 ++cl_kh;
                             }
                         }
-                        if (++stage == static_cast<uint32_t>(S)) {
-                            stage = 0;
-                            phase ^= 1u;
-                        }
-                        continue;
-                    }
-                    if (!PAIR && p.a_cl == 2) {
-                        const uint32_t bar = ptx::smem_u32(&full_bar[stage]);
-                        ptx::mbar_arrive_expect_tx(bar, A_TILE + b_tile);
-                        const int mt = m0 / kBM;
-                        const int rowid = mt / p.cl_tpr;
-                        const int n = rowid / p.g.OH;
-                        DLF_CLK_ADD(6);
-                        ptx::tma_load_4d(sA, &tmA, bar, 0, (mt - rowid * p.cl_tpr) * kBM,
-                                         ((rowid - n * p.g.OH) * p.g.sh + 2 * kb) / p.cl_rstep, n);
-                        DLF_CLK_ADD(7);
-                        ptx::tma_load_3d(sB, &tmB, bar, kb * BK, n0, bb);
-                        DLF_CLK_ADD(8);
                         if (++stage == static_cast<uint32_t>(S)) {
                             stage = 0;
                             phase ^= 1u;
