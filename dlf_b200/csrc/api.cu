@@ -56,6 +56,7 @@ struct DeviceState {
     int num_sms = 0;
     int* status = nullptr;
     int static_smem_tma = 0;
+    int static_smem_tma4 = 0;  // the instantiation with four sets of epilogue warps
     int static_smem_gen2 = 0;
     int static_smem_gen4 = 0;
     int static_smem_ts2 = 0;
@@ -165,6 +166,13 @@ int ensure_device(DeviceState** out) {
         cudaFuncAttributes fa;
         CUDA_TRY(cudaFuncGetAttributes(&fa, contraction_kernel<2, true>));
         st.static_smem_tma = static_cast<int>(fa.sharedSizeBytes);
+        {
+            auto k4 = contraction_kernel<2, true, false, 4>;
+            CUDA_TRY(cudaFuncGetAttributes(&fa, k4));
+            st.static_smem_tma4 = static_cast<int>(fa.sharedSizeBytes);
+            CUDA_TRY(cudaFuncSetAttribute(k4, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          kSmemPerBlockOptin - st.static_smem_tma4));
+        }
         CUDA_TRY(cudaFuncGetAttributes(&fa, contraction_kernel<2, false>));
         st.static_smem_gen2 = static_cast<int>(fa.sharedSizeBytes);
         CUDA_TRY(cudaFuncGetAttributes(&fa, contraction_kernel<4, false>));
@@ -196,7 +204,7 @@ int ensure_device(DeviceState** out) {
             CUDA_TRY(cudaFuncSetAttribute(pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn));
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = dim3(2 * st.num_sms, 1, 1);
-            cfg.blockDim = dim3(kThreadsTma, 1, 1);
+            cfg.blockDim = dim3(kThreadsPair, 1, 1);
             cfg.dynamicSmemBytes = static_cast<size_t>(dyn);
             cudaLaunchAttribute attr;
             attr.id = cudaLaunchAttributeClusterDimension;
@@ -783,7 +791,7 @@ int launch(const Problem& q, cudaStream_t stream, DeviceState* preset = nullptr)
         const long long clusters = ptotal < st->max_pair_clusters ? ptotal : st->max_pair_clusters;
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(static_cast<unsigned>(2 * clusters), 1, 1);
-        cfg.blockDim = dim3(kThreadsTma, 1, 1);
+        cfg.blockDim = dim3(kThreadsPair, 1, 1);
         cfg.dynamicSmemBytes = static_cast<size_t>(pstages) * pstage + 1024;
         cfg.stream = stream;
         cudaLaunchAttribute attr;
@@ -802,13 +810,25 @@ int launch(const Problem& q, cudaStream_t stream, DeviceState* preset = nullptr)
     const long long total = q.batch * tiles_m * tiles_n;
     if (total >= INT_MAX) return kInvalidDimension;
 
-    const int static_smem =
-        use_tma ? st->static_smem_tma : (q.es == 2 ? st->static_smem_gen2 : st->static_smem_gen4);
+    // Epilogue warps of the TMA variant: four sets when the main loop of a tile is short against its
+    // epilogue (K <= 512 and K <= twice the output channels, tiles of 128 columns or more), where the
+    // epilogue is the longest stage (64 -> 256 1x1 at 56x56, batch 256: 149 -> 127 us; 128 -> 512 at
+    // 28x28: 87 -> 77 us; 512 -> 2048 at 7x7: 79 -> 62 us); two sets otherwise - a long main loop
+    // wants the registers and the fourth 48 KB stage (512 -> 128 at 28x28: 49 vs 54 us), and so does
+    // the paired-store epilogue of even planes that cannot have TMA stores (256 -> 1024 at 14x14).
+    const long long num_kb_l = (q.K + 63) / 64;
+    const bool paired_plain = q.out_nchw == 1 && q.g.P % 2 == 0 && q.g.P % 8 != 0;
+    const long long out_ch = q.cl_swap ? q.M : q.N;
+    const bool four_sets = use_tma && num_kb_l <= 8 && q.K <= 2 * out_ch && bn >= 128 && !paired_plain &&
+                           !((g_force_bn.load() >> 16) & 32);
+    const int static_smem = use_tma ? (four_sets ? st->static_smem_tma4 : st->static_smem_tma)
+                                    : (q.es == 2 ? st->static_smem_gen2 : st->static_smem_gen4);
     const int stage_bytes = (kBM + bn) * 128 * (q.es == 4 ? 2 : 1);
-    int stages = (kSmemPerBlockOptin - static_smem - 1024) / stage_bytes;
+    const int epi_stage = use_tma ? epi_stage_bytes(four_sets ? 4 : 2) : 0;  // output staging blocks of the epilogue warps
+    int stages = (kSmemPerBlockOptin - static_smem - 1024 - epi_stage) / stage_bytes;
     if (stages > kMaxStages) stages = kMaxStages;
     if (stages < 2) return kUnexpectedError;
-    const size_t dyn_smem = static_cast<size_t>(stages) * stage_bytes + 1024;
+    const size_t dyn_smem = static_cast<size_t>(stages) * stage_bytes + 1024 + epi_stage;
 
     Params p{};
     p.M = static_cast<int>(q.M);
@@ -865,13 +885,17 @@ int launch(const Problem& q, cudaStream_t stream, DeviceState* preset = nullptr)
             rc = encode_map(*st, &tm_b, q.b, q.es, q.N, q.K, q.batch, bn);
         }
         if (rc != kSuccess) return rc;
-        const unsigned box_cols = (bn >= 128 && !(g_force_generic.load() & 0x100)) ? 64 : 32;
+        // 64-column boxes need 64 columns per epilogue warp
+        const unsigned box_cols = (bn >= (four_sets ? 256 : 128) && !(g_force_generic.load() & 0x100)) ? 64 : 32;
         p.d_tma = (!q.d_f32 && encode_output_map(*st, &tm_d, q, box_cols)) ? static_cast<int>(box_cols) : 0;
     }
 
     const unsigned grid = static_cast<unsigned>(total < st->num_sms ? total : st->num_sms);
     if (use_tma) {
-        contraction_kernel<2, true><<<grid, kThreadsTma, dyn_smem, stream>>>(p, tm_a, tm_b, tm_d);
+        if (four_sets)
+            contraction_kernel<2, true, false, 4><<<grid, tma_threads(4), dyn_smem, stream>>>(p, tm_a, tm_b, tm_d);
+        else
+            contraction_kernel<2, true><<<grid, kThreadsTma, dyn_smem, stream>>>(p, tm_a, tm_b, tm_d);
     } else if (q.es == 2) {
         contraction_kernel<2, false><<<grid, kThreadsGen, dyn_smem, stream>>>(p, tm_a, tm_b, tm_d);
     } else {

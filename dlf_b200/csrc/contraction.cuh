@@ -65,7 +65,14 @@ constexpr int kTmaWarp = 5;
 constexpr int kFirstLoaderWarp = 6;
 constexpr int kLoaderWarps = 8;
 constexpr int kLoaderThreads = kLoaderWarps * 32;
-constexpr int kThreadsTma = 10 * 32;  // warps 6-9: a second set of epilogue warps (other half of the columns)
+// TMA variant: ESETS sets of four epilogue warps (warps 0-3, then 6 upwards), each set taking a share
+// of the tile's columns. Two sets leave the registers and the shared memory a long main loop wants
+// (168 registers, four 48 KB stages); four sets (96 registers, three stages) halve the time of the
+// epilogue, which is what bounds tiles with a short K.
+constexpr int tma_threads(int esets) { return (2 + 4 * esets) * 32; }
+constexpr int epi_stage_bytes(int esets) { return esets * 4 * 2 * 2048; }  // two 2 KB output staging blocks per warp (dynamic)
+constexpr int kThreadsTma = tma_threads(2);
+constexpr int kThreadsPair = tma_threads(2);
 constexpr int kThreadsGen = (kFirstLoaderWarp + kLoaderWarps) * 32;
 constexpr int kMaxStages = 8;
 constexpr int kGroupM = 8;  // tile rasterisation: kGroupM row-tiles share their column sweep
@@ -284,8 +291,8 @@ __device__ __forceinline__ void store_chunk(uint32_t tile, uint32_t lo_tile, int
 // PAIR: the CTA is one of a cluster of two that share 256 x BN tiles through cta_group::2 UMMAs
 // (only with USE_TMA). Each CTA loads its own 128 rows of A and BN/2 rows of B with plain
 // per-CTA TMA loads. Rank 0 issues the UMMAs and signals both CTAs' barriers.
-template <int ES, bool USE_TMA, bool PAIR = false>
-__global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
+template <int ES, bool USE_TMA, bool PAIR = false, int ESETS = 2>
+__global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(ESETS) : kThreadsGen), 1)
     contraction_kernel(const __grid_constant__ Params p, const __grid_constant__ CUtensorMap tmA,
                        const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmD) {
     static_assert(!(USE_TMA && ES == 4), "fp32 operands need the split done by loader warps");
@@ -308,7 +315,7 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
     __shared__ __align__(16) PixelEntry pix_table[USE_TMA ? 1 : kLoaderWarps * kBM];
     // output staging of the TMA-store epilogue: per epilogue warp two 32 x 32 blocks of 16-bit
     // values, [column][row] with rows contiguous (64-byte lines)
-    __shared__ __align__(128) uint8_t d_stage[USE_TMA ? 8 * 2 * 2048 : 16];
+    __shared__ __align__(128) uint8_t d_stage_pair[PAIR ? 8 * 2 * 2048 : 16];  // CTA pairs keep their staging static
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -335,7 +342,7 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
         for (int i = 0; i < 2; ++i) {
             ptx::mbar_init(ptx::smem_u32(&tfull_bar[i]), 1u);
             // PAIR: one arrival per epilogue warp of both CTAs (8 + 8), all on rank 0's barrier
-            ptx::mbar_init(ptx::smem_u32(&tempty_bar[i]), PAIR ? 16u : (USE_TMA ? 256u : 128u));
+            ptx::mbar_init(ptx::smem_u32(&tempty_bar[i]), PAIR ? 16u : (USE_TMA ? ESETS * 128u : 128u));
         }
         ptx::fence_mbar_init();
     }
@@ -366,7 +373,12 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
         // TMA variant: warps 0-3 take the first half of the tile's columns, warps 6-9 the second
         const int q = warp & 3;                       // TMEM lane quadrant (warp index mod 4)
         const int ewarp = warp < 4 ? warp : warp - 2;  // 0..7: staging buffer index
-        const int chalf = (USE_TMA && warp >= 6) ? 1 : 0;
+        // column sets: the tile's columns are shared out among min(sets, BN / 32) sets of four warps
+        const int cset = (USE_TMA && warp >= 6) ? (warp - 6) / 4 + 1 : 0;
+        const int nset = USE_TMA ? min(PAIR ? 2 : ESETS, BN / 32) : 1;
+        const int cols_per = BN / nset;
+        const int cbase = cset < nset ? cset * cols_per : BN;  // idle sets start past the tile
+        const uint32_t d_stage = PAIR ? ptx::smem_u32(d_stage_pair) : smem0 + static_cast<uint32_t>(S) * stage_bytes;
         uint32_t it = 0;
         uint32_t chunk_no = 0;  // TMA-store epilogue: 32-column blocks written so far by this warp
         DLF_CLK_DECL(warp == 0 && lane == 0)
@@ -388,8 +400,8 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
                     // swapped roles: lanes are output channels, columns are output pixels
                     const int co = m0 + q * 32 + lane;
                     const bool co_ok = co < p.M;
-                    const int cb3 = chalf * (BN / 2);
-                    const int ncols3 = max(0, min(BN / 2, p.N - n0 - cb3));
+                    const int cb3 = cbase;
+                    const int ncols3 = max(0, min(cols_per, min(BN, p.N - n0) - cb3));
                     float bv3 = 0.0f;
                     if (p.bias != nullptr && co_ok)
                         bv3 = p.fmt == FMT_F16 ? out_load<OUT_F16>(p.bias + co * 2) : out_load<OUT_BF16>(p.bias + co * 2);
@@ -417,7 +429,7 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
                                 if (lane == 0) ptx::bulk_wait_group_read<1>();
                                 __syncwarp();
                             }
-                            const uint32_t sblk = ptx::smem_u32(d_stage) + (ewarp * 2 + half) * 2048u;
+                            const uint32_t sblk = d_stage + (ewarp * 2 + half) * 2048u;
                             const char* rp = p.resid ? p.resid + boff3 +
                                                            (static_cast<long long>(img) * p.g.out_img_stride + rowoff + pp) * 2
                                                      : nullptr;
@@ -517,11 +529,11 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
             const float alpha = p.alphas ? p.alphas[b] : p.alpha;
             const float beta = p.betas ? p.betas[b] : p.beta;
             const char* bias =
-                p.bias ? p.bias + (static_cast<long long>(b) * p.bias_stride + n0 + (USE_TMA ? chalf * (BN / 2) : 0)) * ES : nullptr;
-            const int cb = USE_TMA ? chalf * (BN / 2) : 0;  // first column of this warp's share
+                p.bias ? p.bias + (static_cast<long long>(b) * p.bias_stride + n0 + (USE_TMA ? cbase : 0)) * ES : nullptr;
+            const int cb = USE_TMA ? cbase : 0;  // first column of this warp's share
             const uint32_t trow = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN + cb;
             char* optr = p.d + (rowbase + static_cast<long long>(n0 + cb) * colstride) * ES;
-            const int ncols = max(0, min(USE_TMA ? BN / 2 : BN, p.N - n0 - cb));
+            const int ncols = max(0, min(USE_TMA ? cols_per : BN, min(BN, p.N - n0) - cb));
             if constexpr (USE_TMA) {
                 if (p.d_tma) {
                     const int i0 = m0 + q * 32;
@@ -557,7 +569,7 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
                             }
                             __syncwarp();
                         }
-                        const uint32_t sbuf = ptx::smem_u32(d_stage) + (ewarp * 2 + half) * 2048u + lane * 2u;
+                        const uint32_t sbuf = d_stage + (ewarp * 2 + half) * 2048u + lane * 2u;
                         if (p.resid != nullptr) {
                             // residual values first (loads must not sit between the stores)
                             const char* rp = p.resid + (optr - p.d) + static_cast<long long>(c0) * colstride * 2;
@@ -612,7 +624,7 @@ __global__ void __launch_bounds__(USE_TMA ? kThreadsTma : kThreadsGen, 1)
                         ptx::fence_proxy_async_smem();
                         __syncwarp();
                         if (lane == 0) {
-                            const uint32_t ssrc = ptx::smem_u32(d_stage) + (ewarp * 2 + (wide ? 0u : half)) * 2048u;
+                            const uint32_t ssrc = d_stage + (ewarp * 2 + (wide ? 0u : half)) * 2048u;
                             const int col = n0 + cb + (wide ? (c0 & ~63) : c0);
                             ptx::tma_store_3d(&tmD, ssrc, pp0, col, p.out_nchw == 1 ? img0 : (p.d_batch_stride ? b : 0));
                             ptx::bulk_commit_group();
