@@ -540,10 +540,11 @@ def time_steps_graph(fn, steps, warmup, per_graph=20):
 def run_extra(w, device, peaks, steps, warmup, graph=False):
     """Kernel-only numbers for a further BASELINE configuration (reported under "workloads")."""
     w.setup(device, 0, w.sets_needed())
-    step = w.step_abi if (graph and hasattr(w, "step_abi") and w.batch == 1) else w.step
+    direct = bool(graph and hasattr(w, "step_abi") and w.batch == 1)
+    step = w.step_abi if direct else w.step
     ms = time_steps_graph(step, steps, warmup) if graph else None
     timed = "cuda graph replay (20 steps per graph)" if ms is not None else \
-        ("stream launches through the C ABI" if step is not w.step else "stream launches")
+        ("stream launches through the C ABI" if direct else "stream launches")
     if ms is None:
         ms, _, _ = time_steps(step, steps, warmup, 1)
     sec = ms / 1e3 / steps

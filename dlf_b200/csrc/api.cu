@@ -810,16 +810,17 @@ int launch(const Problem& q, cudaStream_t stream, DeviceState* preset = nullptr)
     const long long total = q.batch * tiles_m * tiles_n;
     if (total >= INT_MAX) return kInvalidDimension;
 
-    // Epilogue warps of the TMA variant: four sets when the main loop of a tile is short against its
-    // epilogue (K <= 512 and K <= twice the output channels, tiles of 128 columns or more), where the
+    // Epilogue warps of the TMA variant: four sets for convolutions whose main loop is short against
+    // the epilogue (K <= 512 and K <= twice the output channels, tiles of 128 columns or more), where the
     // epilogue is the longest stage (64 -> 256 1x1 at 56x56, batch 256: 149 -> 127 us; 128 -> 512 at
     // 28x28: 87 -> 77 us; 512 -> 2048 at 7x7: 79 -> 62 us); two sets otherwise - a long main loop
     // wants the registers and the fourth 48 KB stage (512 -> 128 at 28x28: 49 vs 54 us), and so does
     // the paired-store epilogue of even planes that cannot have TMA stores (256 -> 1024 at 14x14).
+    // Plain GEMM calls keep two sets (1024 x 512x64x512, bound by its reads: 105 vs 111 us).
     const long long num_kb_l = (q.K + 63) / 64;
     const bool paired_plain = q.out_nchw == 1 && q.g.P % 2 == 0 && q.g.P % 8 != 0;
     const long long out_ch = q.cl_swap ? q.M : q.N;
-    const bool four_sets = use_tma && num_kb_l <= 8 && q.K <= 2 * out_ch && bn >= 128 && !paired_plain &&
+    const bool four_sets = use_tma && q.out_nchw != 0 && num_kb_l <= 8 && q.K <= 2 * out_ch && bn >= 128 && !paired_plain &&
                            !((g_force_bn.load() >> 16) & 32);
     const int static_smem = use_tma ? (four_sets ? st->static_smem_tma4 : st->static_smem_tma)
                                     : (q.es == 2 ? st->static_smem_gen2 : st->static_smem_gen4);

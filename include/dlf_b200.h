@@ -118,7 +118,11 @@ int dlf_b200_gemm_batched_noalloc(int dtype, int layout, int trans_a, int trans_
  * Replaces gpgpu::dnn::conv2d<T> (gpgpu/include/gdnn.h:201-213; gpgpu/src/gdnn.cpp:1577-1630).
  * `bias` (num_kernels entries, storage type) may be NULL; when given it is added in the
  * epilogue, replacing the separate transformChannel pass of ConvOp
- * (dlf/include/predict.h:1272-1281). workspace may be NULL: the kernel needs none. */
+ * (dlf/include/predict.h:1272-1281). `workspace` is optional caller-owned device scratch
+ * (dlf_b200_conv2d_workspace_bytes: about the size of X for 16-bit convolutions of one group,
+ * whose activations are copied there channels-last and then fetched by tensor-map loads; a few MB
+ * for the packed filter bank otherwise). With NULL the kernels gather their operands themselves:
+ * same results within the tolerance, slower. */
 int dlf_b200_conv2d(int dtype, size_t batches, size_t channels, size_t height, size_t width,
                     size_t output_h, size_t output_w, size_t num_kernels, size_t group,
                     size_t kernel_h, size_t kernel_w, size_t pad_top, size_t pad_left,
