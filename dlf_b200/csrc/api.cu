@@ -57,6 +57,7 @@ struct DeviceState {
     int* status = nullptr;
     int static_smem_tma = 0;
     int static_smem_tma4 = 0;  // the instantiation with four sets of epilogue warps
+    int static_smem_tma3 = 0;  // ... with three
     int static_smem_gen2 = 0;
     int static_smem_gen4 = 0;
     int static_smem_ts2 = 0;
@@ -172,6 +173,13 @@ int ensure_device(DeviceState** out) {
             st.static_smem_tma4 = static_cast<int>(fa.sharedSizeBytes);
             CUDA_TRY(cudaFuncSetAttribute(k4, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           kSmemPerBlockOptin - st.static_smem_tma4));
+        }
+        {
+            auto k3 = contraction_kernel<2, true, false, 3>;
+            CUDA_TRY(cudaFuncGetAttributes(&fa, k3));
+            st.static_smem_tma3 = static_cast<int>(fa.sharedSizeBytes);
+            CUDA_TRY(cudaFuncSetAttribute(k3, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          kSmemPerBlockOptin - st.static_smem_tma3));
         }
         CUDA_TRY(cudaFuncGetAttributes(&fa, contraction_kernel<2, false>));
         st.static_smem_gen2 = static_cast<int>(fa.sharedSizeBytes);
@@ -822,10 +830,16 @@ int launch(const Problem& q, cudaStream_t stream, DeviceState* preset = nullptr)
     const long long out_ch = q.cl_swap ? q.M : q.N;
     const bool four_sets = use_tma && q.out_nchw != 0 && num_kb_l <= 8 && q.K <= 2 * out_ch && bn >= 128 && !paired_plain &&
                            !((g_force_bn.load() >> 16) & 32);
-    const int static_smem = use_tma ? (four_sets ? st->static_smem_tma4 : st->static_smem_tma)
+    // Three sets (448 threads, 128 registers, no spills) for the widening pixel-per-lane layers the
+    // four-set form leaves out (256 -> 1024 at 14x14: 77 -> 73 us; 1024 -> 2048 stride 2: 110 -> 98 us;
+    // 3x3 layers lose 4-6 % with it). Bit 22 of the tile-width word: never.
+    const bool three_sets = use_tma && !four_sets && q.out_nchw == 1 && bn >= 128 && q.N >= 2 * q.K &&
+                            !((g_force_bn.load() >> 16) & 64);
+    const int esets = four_sets ? 4 : (three_sets ? 3 : 2);
+    const int static_smem = use_tma ? (four_sets ? st->static_smem_tma4 : three_sets ? st->static_smem_tma3 : st->static_smem_tma)
                                     : (q.es == 2 ? st->static_smem_gen2 : st->static_smem_gen4);
     const int stage_bytes = (kBM + bn) * 128 * (q.es == 4 ? 2 : 1);
-    const int epi_stage = use_tma ? epi_stage_bytes(four_sets ? 4 : 2) : 0;  // output staging blocks of the epilogue warps
+    const int epi_stage = use_tma ? epi_stage_bytes(esets) : 0;  // output staging blocks of the epilogue warps
     int stages = (kSmemPerBlockOptin - static_smem - 1024 - epi_stage) / stage_bytes;
     if (stages > kMaxStages) stages = kMaxStages;
     if (stages < 2) return kUnexpectedError;
@@ -887,7 +901,7 @@ int launch(const Problem& q, cudaStream_t stream, DeviceState* preset = nullptr)
         }
         if (rc != kSuccess) return rc;
         // 64-column boxes need 64 columns per epilogue warp
-        const unsigned box_cols = (bn >= (four_sets ? 256 : 128) && !(g_force_generic.load() & 0x100)) ? 64 : 32;
+        const unsigned box_cols = (esets == 2 ? bn >= 128 : (esets == 4 && bn >= 256)) && !(g_force_generic.load() & 0x100) ? 64 : 32;
         p.d_tma = (!q.d_f32 && encode_output_map(*st, &tm_d, q, box_cols)) ? static_cast<int>(box_cols) : 0;
     }
 
@@ -895,6 +909,8 @@ int launch(const Problem& q, cudaStream_t stream, DeviceState* preset = nullptr)
     if (use_tma) {
         if (four_sets)
             contraction_kernel<2, true, false, 4><<<grid, tma_threads(4), dyn_smem, stream>>>(p, tm_a, tm_b, tm_d);
+        else if (three_sets)
+            contraction_kernel<2, true, false, 3><<<grid, tma_threads(3), dyn_smem, stream>>>(p, tm_a, tm_b, tm_d);
         else
             contraction_kernel<2, true><<<grid, kThreadsTma, dyn_smem, stream>>>(p, tm_a, tm_b, tm_d);
     } else if (q.es == 2) {

@@ -376,8 +376,8 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
         // column sets: the tile's columns are shared out among min(sets, BN / 32) sets of four warps
         const int cset = (USE_TMA && warp >= 6) ? (warp - 6) / 4 + 1 : 0;
         const int nset = USE_TMA ? min(PAIR ? 2 : ESETS, BN / 32) : 1;
-        const int cols_per = BN / nset;
-        const int cbase = cset < nset ? cset * cols_per : BN;  // idle sets start past the tile
+        const int cols_per = ((BN / 32 + nset - 1) / nset) * 32;  // whole blocks of 32 columns; the last set may get fewer
+        const int cbase = cset < nset ? min(cset * cols_per, BN) : BN;  // idle sets start past the tile
         const uint32_t d_stage = PAIR ? ptx::smem_u32(d_stage_pair) : smem0 + static_cast<uint32_t>(S) * stage_bytes;
         uint32_t it = 0;
         uint32_t chunk_no = 0;  // TMA-store epilogue: 32-column blocks written so far by this warp

@@ -238,7 +238,8 @@ int dlf_b200_device_status(int* device_status);
  * 0x20000 swap the operand roles (lanes = output channels) for every even plane size, not only
  * for planes of a multiple of 8 pixels, 0x80000 never swap the roles of a 1x1 stride-1 convolution
  * that runs as a batched GEMM, 0x200000 never use the instantiation of the TMA-fed kernel with four
- * sets of epilogue warps (default for tiles of 128 or more columns with K <= 512). */
+ * sets of epilogue warps (default for tiles of 128 or more columns with K <= 512), 0x400000 never
+ * the one with three sets. */
 void dlf_b200_set_tuning(int force_bn, int force_generic_loader);
 
 /* Counts kernel launches made by this library in this process (all threads). */
