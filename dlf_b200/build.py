@@ -11,7 +11,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libdlf_b200.so")
 SOURCES = ["api.cu"]
-HEADERS = ["channels_last.cuh", "conv_small.cuh", "contraction.cuh", "contraction_ts.cuh", "epilogue.cuh", "level3.cuh", "pooling.cuh", "ptx.cuh", os.path.join("..", "..", "include", "dlf_b200.h")]
+HEADERS = ["channels_last.cuh", "conv_halo.cuh", "conv_small.cuh", "contraction.cuh", "contraction_ts.cuh", "epilogue.cuh", "level3.cuh", "pooling.cuh", "ptx.cuh", os.path.join("..", "..", "include", "dlf_b200.h")]
 
 
 def _stale():

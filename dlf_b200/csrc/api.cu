@@ -23,6 +23,7 @@
 #include "contraction.cuh"
 #include "contraction_ts.cuh"
 #include "conv_small.cuh"
+#include "conv_halo.cuh"
 #include "level3.cuh"
 #include "pooling.cuh"
 
@@ -64,6 +65,7 @@ struct DeviceState {
     int static_smem_ts4 = 0;
     int static_smem_pair = 0;
     int static_smem_small = 0;
+    int static_smem_halo = 0;
     int max_pair_clusters = 0;  // co-resident CTA pairs of the pair kernel (0 = not usable)
     PFN_cuTensorMapEncodeTiled_v12000 encode = nullptr;
     PFN_cuTensorMapEncodeIm2col_v12000 encode_im2col = nullptr;  // null: the driver has none
@@ -194,6 +196,10 @@ int ensure_device(DeviceState** out) {
         CUDA_TRY(cudaFuncSetAttribute(contraction_kernel<4, false>,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       kSmemPerBlockOptin - st.static_smem_gen4));
+        CUDA_TRY(cudaFuncGetAttributes(&fa, conv_halo_kernel));
+        st.static_smem_halo = static_cast<int>(fa.sharedSizeBytes);
+        CUDA_TRY(cudaFuncSetAttribute(conv_halo_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      kSmemPerBlockOptin - st.static_smem_halo));
         CUDA_TRY(cudaFuncGetAttributes(&fa, conv_small_kernel));
         st.static_smem_small = static_cast<int>(fa.sharedSizeBytes);
         CUDA_TRY(cudaFuncSetAttribute(conv_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -1386,6 +1392,10 @@ size_t dlf_b200_conv2d_workspace_bytes(int dtype, size_t batches, size_t channel
         const size_t cp = (channels + 7) / 8 * 8, ck = (channels + 63) / 64 * 64;
         const size_t cl = batches * height * width * cp * 2 + num_kernels * kernel_h * kernel_w * ck * 2 + 4096;
         if (cl > need) need = cl;
+        // halo-tile kernel: bordered channel-group-major copy (at most (H + KH) x (W + KW) pixels per plane)
+        const size_t halo = batches * ((channels + 7) / 8) * (height + kernel_h) * (width + kernel_w) * 16 +
+                            num_kernels * kernel_h * kernel_w * ck * 2 + 4096;
+        if (halo > need) need = halo;
         if (channels <= 4) {
             // bordered row-pair copy: at most (H + 2*KH + 2) row pairs of (W + 2*KW + 80) pixels of 16 bytes per image
             // (all phases of a row together; every phase rounded up to the tile's columns per row)
@@ -1636,6 +1646,122 @@ int dlf_b200_conv2d_fused(int dtype, size_t batches, size_t channels, size_t hei
                 const unsigned grid = static_cast<unsigned>(total_tiles < st->num_sms ? total_tiles : st->num_sms);
                 const size_t dyn = static_cast<size_t>(a_bytes) + kSmallStageOut + static_cast<size_t>(stages) * sp.stage_bytes + 1024;
                 conv_small_kernel<<<grid, kSmallThreads, dyn, cs>>>(sp, tm_w, tm_d);
+                g_launches.fetch_add(1);
+                CUDA_TRY(cudaGetLastError());
+                return kSuccess;
+            }
+        }
+    }
+
+    // Stride-1 filters larger than 1x1 over a multiple of 64 channels with at most 64 output channels
+    // and rows of a multiple of 8 outputs (64 -> 64 3x3 at 56x56): the halo-tile kernel (conv_halo.cuh)
+    // - bordered channel-group-major copy, every tile's activations fetched once, filter taps as
+    // descriptor offsets. With few output channels the activations are most of the operand traffic
+    // (210 -> 186 us at batch 256, main kernel 165 -> 126 us); with 128 and more the filter bank is,
+    // and the im2col-mode route with its 256-pixel tiles is faster (128 -> 128 at 28x28: 87 vs 105 us).
+    // Bit 24 of the tile-width word takes this kernel for every layer it can serve, bit 23 for none.
+    {
+        const int tune = g_force_generic.load();
+        const int cl_neutral = 0x100 | 0x4000 | 0x10000000 | 0x20000000;
+        const int route = g_force_bn.load() >> 16;
+        const long long taps = static_cast<long long>(kernel_h) * kernel_w;
+        const long long hp = static_cast<long long>(output_h) + kernel_h - 1;
+        const long long wp = static_cast<long long>(output_w) + kernel_w - 1;
+        const long long cg = static_cast<long long>(channels) / 8;
+        const size_t w_bytes = (static_cast<size_t>(num_kernels) * taps * channels * 2 + 1023) / 1024 * 1024;
+        const size_t x_bytes = static_cast<size_t>(batches) * cg * hp * wp * 16;
+        unsigned char* ws = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(workspace) + 255u) & ~uintptr_t(255));
+        const size_t slack = static_cast<size_t>(ws - static_cast<unsigned char*>(workspace));
+        if (q.es == 2 && group == 1 && channels % 64 == 0 && taps > 1 && stride_h == 1 && stride_w == 1 &&
+            dilation_h == 1 && dilation_w == 1 && (tune & ~cl_neutral) == 0 && !(route & 1) && !(route & 128) &&
+            workspace != nullptr && workspace_bytes >= slack + w_bytes + x_bytes && wp <= 240 && output_w % 2 == 0 &&
+            ((num_kernels <= 64 && output_w % 8 == 0) || (route & 256)) &&
+            kernel_h <= 16 && kernel_w <= 16 && pad_top < (1u << 20) && pad_left < (1u << 20) &&
+            P * static_cast<long long>(num_kernels) < (1ll << 38) && taps * static_cast<long long>(channels) < INT_MAX - 512) {
+            DeviceState* st = nullptr;
+            int rc = ensure_device(&st);
+            if (rc != kSuccess) return rc;
+            HaloParams hp_{};
+            int rr = static_cast<int>(240 / wp);
+            if (rr > static_cast<int>(output_h)) rr = static_cast<int>(output_h);
+            hp_.R = rr;
+            hp_.BN = static_cast<int>((rr * wp + 15) / 16 * 16);
+            hp_.group_units = static_cast<unsigned>((hp_.BN + (kernel_h - 1) * wp + kernel_w + 7) / 8 * 8);
+            hp_.stage_bytes = 8u * hp_.group_units * 16u;
+            const long long budget = kSmemPerBlockOptin - st->static_smem_halo - 1024 - kHaloStageOut;
+            int hs = 2;
+            long long sa = (budget - static_cast<long long>(hs) * hp_.stage_bytes) / (kBM * 128);
+            if (sa > kHaloMaxA) sa = kHaloMaxA;
+            const long long tiles_per_image = (static_cast<long long>(output_h) + rr - 1) / rr;
+            const long long co_tiles = (static_cast<long long>(num_kernels) + kBM - 1) / kBM;
+            const long long total_tiles = static_cast<long long>(batches) * tiles_per_image * co_tiles;
+            if (sa >= 3 && total_tiles < INT_MAX) {
+                clear_stale_error();
+                cudaStream_t cs = static_cast<cudaStream_t>(stream);
+                uint16_t* wpk = reinterpret_cast<uint16_t*>(ws);
+                uint4* xh = reinterpret_cast<uint4*>(ws + w_bytes);
+                const long long total = static_cast<long long>(batches) * cg * hp * wp;
+                halo_pack_activations_kernel<<<static_cast<unsigned>(std::min<long long>((total + 255) / 256, 32ll * st->num_sms)), 256, 0, cs>>>(
+                    static_cast<const uint16_t*>(x), xh, static_cast<int>(channels), static_cast<int>(height),
+                    static_cast<int>(width), static_cast<int>(hp), static_cast<int>(wp), static_cast<int>(pad_top),
+                    static_cast<int>(pad_left), total);
+                g_launches.fetch_add(1);
+                CUDA_TRY(cudaGetLastError());
+                const long long wtotal = static_cast<long long>(num_kernels) * channels;
+                cl_pack_filters_kernel<<<static_cast<unsigned>(std::min<long long>((wtotal + 255) / 256, 8ll * st->num_sms)), 256, 0, cs>>>(
+                    static_cast<const uint16_t*>(w), wpk, static_cast<int>(num_kernels), static_cast<int>(channels),
+                    static_cast<int>(taps), static_cast<int>(channels));
+                g_launches.fetch_add(1);
+                CUDA_TRY(cudaGetLastError());
+                hp_.xh = reinterpret_cast<const char*>(xh);
+                hp_.y = static_cast<char*>(y);
+                hp_.bias = static_cast<const char*>(bias);
+                hp_.resid = q.resid;
+                hp_.relu = q.relu;
+                hp_.fmt = q.fmt;
+                hp_.Cout = static_cast<int>(num_kernels);
+                hp_.CB = static_cast<int>(channels / 64);
+                hp_.OH = static_cast<int>(output_h);
+                hp_.OW = static_cast<int>(output_w);
+                hp_.P = static_cast<int>(P);
+                hp_.Hp = static_cast<int>(hp);
+                hp_.Wp = static_cast<int>(wp);
+                hp_.KH = static_cast<int>(kernel_h);
+                hp_.KW = static_cast<int>(kernel_w);
+                hp_.images = static_cast<int>(batches);
+                hp_.tiles_per_image = static_cast<int>(tiles_per_image);
+                hp_.co_tiles = static_cast<int>(co_tiles);
+                hp_.total_tiles = static_cast<int>(total_tiles);
+                hp_.out_img_stride = static_cast<long long>(num_kernels) * P;
+                hp_.a_stages = static_cast<int>(sa);
+                hp_.h_stages = hs;
+                hp_.status = st->status;
+                hp_.wait_limit = 1ll << 32;
+                const uintptr_t ya = reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(residual);
+                hp_.out_vec = (output_w % 8 == 0 && ya % 16 == 0) ? 8 : (output_w % 4 == 0 && ya % 8 == 0) ? 4 : (ya % 4 == 0 ? 2 : 1);
+                CUtensorMap tm_w, tm_d;
+                std::memset(&tm_d, 0, sizeof(tm_d));
+                GenOperand wop{};
+                wop.base = reinterpret_cast<const char*>(wpk);
+                wop.ld = taps * static_cast<long long>(channels);
+                wop.k_major = 1;
+                rc = encode_map(*st, &tm_w, wop, 2, static_cast<long long>(num_kernels), taps * static_cast<long long>(channels), 1, kBM);
+                if (rc != kSuccess) return rc;
+                if (hp_.out_vec == 8 && !(tune & 0x4000)) {
+                    cuuint64_t dims[3] = {static_cast<cuuint64_t>(P), static_cast<cuuint64_t>(num_kernels),
+                                          static_cast<cuuint64_t>(batches)};
+                    cuuint64_t strides[2] = {static_cast<cuuint64_t>(P * 2), static_cast<cuuint64_t>(P * num_kernels * 2)};
+                    cuuint32_t box[3] = {32, 32, 1};
+                    cuuint32_t estr[3] = {1, 1, 1};
+                    hp_.d_tma = st->encode(&tm_d, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, y, dims, strides, box, estr,
+                                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                           CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS
+                                    ? 1
+                                    : 0;
+                }
+                const unsigned grid = static_cast<unsigned>(total_tiles < st->num_sms ? total_tiles : st->num_sms);
+                const size_t dyn = static_cast<size_t>(sa) * kBM * 128 + kHaloStageOut + static_cast<size_t>(hs) * hp_.stage_bytes + 1024;
+                conv_halo_kernel<<<grid, kHaloThreads, dyn, cs>>>(hp_, tm_w, tm_d);
                 g_launches.fetch_add(1);
                 CUDA_TRY(cudaGetLastError());
                 return kSuccess;

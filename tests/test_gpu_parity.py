@@ -911,6 +911,50 @@ def test_conv2d_pointwise_batched_gemm_both_orientations(lib, case, dtype):
         assert max_rel(Y.float().cpu().numpy(), ref) <= HALF_TOL
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("case", [
+    (2, 64, 16, 16, 64, 3, 3, 1),     # the default case of this kernel: <= 64 output channels, rows of 8k outputs
+    (2, 64, 56, 56, 48, 3, 3, 1),     # 56x56: tiles of 4 rows, two tiles of weights unused
+    (3, 128, 28, 28, 128, 3, 3, 1),   # two 64-channel blocks per tile, 7 rows per tile
+    (5, 256, 14, 14, 300, 3, 3, 1),   # four blocks, three tiles of output channels, the last one ragged
+    (2, 64, 18, 18, 200, 3, 3, 1),    # rows of 18 outputs: per-lane vector stores instead of TMA boxes
+    (3, 64, 10, 10, 72, 3, 3, 0),     # no padding: 8x8 outputs, the bordered copy has no border
+    (2, 64, 30, 30, 64, 5, 5, 2),     # 5x5
+    (1, 64, 70, 70, 136, 7, 7, 3),    # 7x7, 70 outputs per row: 3 rows per tile, ragged last tile
+    (2, 128, 9, 12, 40, 3, 5, 1),     # KH != KW, output narrower than the input
+], ids=lambda c: "x".join(map(str, c)))
+def test_conv2d_halo_tile_kernel(lib, case, dtype):
+    """Stride-1 filters larger than 1x1 over a multiple of 64 channels can run on the halo-tile kernel
+    (bordered channel-group-major copy, a tile's rows fetched once, the filter taps as descriptor
+    offsets into them). It is the default with at most 64 output channels and rows of a multiple of 8
+    outputs; bit 24 of the tile-width word takes it wherever it can serve, bit 23 never. Both against
+    the oracle with bias, residual and ReLU; nothing outside Y touched; the two routes agree to
+    rounding of the 16-bit output."""
+    from dlf_b200 import gdnn
+    N, C, H, W, Co, kh, kw, p = case
+    rng = np.random.default_rng(sum(case))
+    Xh = _round_to(rng.normal(size=(N, C, H, W)).astype(np.float32), dtype)
+    Wh = _round_to((np.sqrt(2.0 / (C * kh * kw)) * rng.normal(size=(Co, C, kh, kw))).astype(np.float32), dtype)
+    bh = _round_to(rng.uniform(-0.1, 0.1, Co).astype(np.float32), dtype)
+    X, Wt, b = (torch.from_numpy(a).to(dtype).cuda() for a in (Xh, Wh, bh))
+    f = gdnn.Filter2D(X.shape, Wt.shape).pads(p, p)
+    Rh = _round_to(rng.normal(size=tuple(f.output_shape())).astype(np.float32), dtype)
+    R = torch.from_numpy(Rh).to(dtype).cuda()
+    n_out = int(np.prod(f.output_shape()))
+    ref = oracle.conv2d_fused(Xh, Wh, residual=Rh, relu=True, bias=bh, pads=(p,) * 4, wide=True)
+    for route in (0x1000000, 0x800000):
+        buf = torch.full((n_out + 64,), 3.0, dtype=dtype, device="cuda")
+        Y = buf[32:32 + n_out].view(f.output_shape())
+        lib.set_tuning(route, 0)
+        try:
+            gdnn.conv2d_filter(X, Wt, Y, f, bias=b, residual=R, activation="relu")
+            torch.cuda.synchronize()
+        finally:
+            lib.set_tuning(0, 0)
+        assert bool((buf[:32] == 3.0).all()) and bool((buf[32 + n_out:] == 3.0).all())
+        assert max_rel(Y.float().cpu().numpy(), ref) <= HALF_TOL
+
+
 FUSED_CASES = [
     CONV_CASES[0],    # row form 3x3
     CONV_CASES[3],    # 1x1 with aligned planes: TMA-fed GEMM route, TMA-store epilogue
