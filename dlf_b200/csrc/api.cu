@@ -98,6 +98,15 @@ struct StreamDevice {
             return;
         }
         if (s != nullptr && s != cudaStreamLegacy && s != cudaStreamPerThread) {
+            // a stream that is being captured into a CUDA graph may not be queried (the query fails and
+            // invalidates the capture): such a call works on the current device, which a capture
+            // requires to be the stream's anyway
+            cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+            if (cudaStreamIsCapturing(s, &cap) != cudaSuccess) {
+                (void)cudaGetLastError();
+                cap = cudaStreamCaptureStatusNone;
+            }
+            if (cap != cudaStreamCaptureStatusNone) return;
             int sd = dev;
             e = cudaStreamGetDevice(s, &sd);
             if (e != cudaSuccess) {
