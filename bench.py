@@ -598,6 +598,123 @@ def resnet_sweep(device, peaks, batch, reps):
     return summary, rows
 
 
+def resnet50_graph(batch, size=224, classes=1000, seed=0):
+    """ResNet-50 v1 (stride on the first 1x1 of a stage) as a graph for dlf_b200.predict: the 53
+    convolutions of RESNET50_SHAPES with a bias each (batch normalisation already folded), ReLU and
+    residual Add nodes as an exporter writes them, 3x3 max pool, global average pool, Flatten and
+    the 2048 -> classes Gemm. Weights are seeded He-normal draws - no checkpoint is involved."""
+    from dlf_b200 import predict as P
+    rng = np.random.default_rng(seed)
+    g = P.Graph()
+
+    def conv(x, cin, cout, k, stride, pad, name):
+        n = g.append("Conv", kernel_shape=[k, k], strides=[stride, stride], pads=[pad] * 4)
+        n.addInput(x)
+        n.addInput(g.addInitializer(name + ".W", (math.sqrt(2.0 / (cin * k * k)) *
+                                    rng.standard_normal((cout, cin, k, k), dtype=np.float32))))
+        n.addInput(g.addInitializer(name + ".B", rng.uniform(-0.1, 0.1, cout).astype(np.float32)))
+        return n.addOutput(name)
+
+    def relu(x, name):
+        n = g.append("Relu")
+        n.addInput(x)
+        return n.addOutput(name)
+
+    t = relu(conv(g.addInput("image", P.DataType.FLOAT, (batch, 3, size, size)), 3, 64, 7, 2, 3, "conv1"), "relu1")
+    mp = g.append("MaxPool", kernel_shape=[3, 3], strides=[2, 2], pads=[1, 1, 1, 1])
+    mp.addInput(t)
+    t, cin = mp.addOutput("pool1"), 64
+    for stage, (blocks, width, stride) in enumerate(((3, 64, 1), (4, 128, 2), (6, 256, 2), (3, 512, 2))):
+        for b in range(blocks):
+            nm = "s%db%d" % (stage + 1, b)
+            st = stride if b == 0 else 1
+            a = relu(conv(t, cin, width, 1, st, 0, nm + ".c1"), nm + ".r1")
+            a = relu(conv(a, width, width, 3, 1, 1, nm + ".c2"), nm + ".r2")
+            a = conv(a, width, 4 * width, 1, 1, 0, nm + ".c3")
+            sc = conv(t, cin, 4 * width, 1, st, 0, nm + ".down") if b == 0 else t
+            add = g.append("Add")
+            add.addInput(a).addInput(sc)
+            t, cin = relu(add.addOutput(nm + ".add"), nm + ".out"), 4 * width
+    gap = g.append("GlobalAveragePool")
+    gap.addInput(t)
+    fl = g.append("Flatten", axis=1)
+    fl.addInput(gap.addOutput("gap"))
+    fc = g.append("Gemm", transB=1)
+    fc.addInput(fl.addOutput("flat"))
+    fc.addInput(g.addInitializer("fc.W", rng.standard_normal((classes, cin), dtype=np.float32) / math.sqrt(cin)))
+    fc.addInput(g.addInitializer("fc.B", rng.uniform(-0.1, 0.1, classes).astype(np.float32)))
+    g.addOutput(fc.addOutput("logits"))
+    return g
+
+
+def oracle_forward(graph, image, rnd):
+    """An optimized graph (convolutions carrying their residual / ReLU marks) evaluated operator by
+    operator with the CPU oracle on one batch; ``rnd`` rounds every operator's result to the
+    storage type, as the device does when it stores it."""
+    import oracle
+    env = {}
+    for v in graph.inputs:
+        env[id(v)] = rnd(np.asarray(v.initializer, dtype=np.float32)) if v.has_initializer() else rnd(image)
+    for n in graph.nodes:
+        a = [env.get(id(v)) if v is not None else None for v in n.inputs]
+        if n.kind == "Conv":
+            res = env[id(n.get("residual"))] if n.get("residual") is not None else None
+            y = oracle.conv2d_fused(a[0], a[1], residual=res, relu=bool(n.get("relu")), bias=a[2] if len(a) > 2 else None,
+                                    pads=tuple(n.get("pads", (0,) * 4)), strides=tuple(n.get("strides", (1, 1))), wide=True)
+        elif n.kind == "MaxPool":
+            y = oracle.pool2d(a[0], tuple(n.get("kernel_shape")), "max", tuple(n.get("pads", (0,) * 4)),
+                              tuple(n.get("strides", (1, 1))))
+        elif n.kind == "GlobalAveragePool":
+            y = oracle.global_pool(a[0], "avg", wide=True)
+        elif n.kind == "Flatten":
+            y = a[0].reshape(a[0].shape[0], -1)
+        elif n.kind == "Gemm":
+            B = a[1].T if n.get("transB", 0) else a[1]
+            y = (a[0].astype(np.float64) @ B.astype(np.float64) + a[2].astype(np.float64)).astype(np.float32)
+        else:
+            raise RuntimeError("oracle_forward: " + n.kind)
+        env[id(n.output(0))] = rnd(y)
+    return env[id(graph.outputs[0])]
+
+
+def resnet_forward(device, peaks, batch, reps):
+    """A whole ResNet-50 v1 forward (fp16, 224x224) as an operator list of this library
+    (dlf_b200.predict): 53 fused convolutions, max pool, global average pool, the FC Gemm - timed
+    launch by launch and as a CUDA-graph replay. The logits of one image are compared with the
+    oracle evaluating the same operator list on the CPU (relative Frobenius error)."""
+    from dlf_b200 import predict as P
+    pred = P.Predictor(resnet50_graph(batch), dtype=torch.float16, device=device, cuda_graph=False)
+    g = torch.Generator(device=device).manual_seed(7)
+    pred.input(0).copy_(torch.randn(pred.input(0).shape, generator=g, device=device).half())
+    flops = sum(2.0 * batch * co * (h // s) ** 2 * ci * k * k * cnt for ci, h, co, k, s, _, cnt in RESNET50_SHAPES)
+    flops += 2.0 * batch * 1000 * 2048
+    step = lambda i: pred.predict()
+    ms_stream, _, _ = time_steps(step, reps, 3, 1)
+    out = {"batch": batch, "dtype": "f16", "operators": len(pred.operators), "launching_operators": pred.launches_per_predict(),
+           "stream_launches": {"ms_per_forward": round(ms_stream / reps, 3),
+                               "images_per_s": round(batch * reps / (ms_stream / 1e3), 1)}}
+    pred._want_graph = True  # the next predict() captures the list, later ones replay it
+    pred.predict()
+    if pred._cuda_graph is not None:
+        ms_graph, _, _ = time_steps(step, reps, 3, 1)
+        sec = ms_graph / 1e3 / reps
+        out["cuda_graph_replay"] = {"ms_per_forward": round(sec * 1e3, 3), "images_per_s": round(batch / sec, 1),
+                                    "tflops": round(flops / sec / 1e12, 1),
+                                    "frac_of_measured_tensor_peak": round(flops / sec / 1e12 / peaks["bf16_tflops"], 4)}
+    # parity of the whole chain on one image: a batch-1 predictor with the same weights
+    small = P.Predictor(resnet50_graph(1), dtype=torch.float16, device=device, cuda_graph=False)
+    image = pred.input(0)[:1].float().cpu().numpy()
+    small.set(0, image)
+    small.predict()
+    rnd = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).half().float().numpy()
+    want = oracle_forward(small.graph, image, rnd)
+    got = small.get(0)
+    out["logits_rel_fro_err_vs_oracle"] = float("%.3g" % (np.linalg.norm(got - want) / np.linalg.norm(want)))
+    out["logits_batch_vs_single_image_max_abs_diff"] = float(
+        "%.3g" % np.abs(pred.output(0)[:1].float().cpu().numpy() - got).max())
+    return out
+
+
 def multi_gpu_workloads(table, device, peaks, world, rank):
     """The two other ways the path shards, measured on every rank (max over ranks):
     * config 5, one large fp32 GEMM: rows of C per rank, then the NCCL all-gather of the row
@@ -781,6 +898,11 @@ def main():
                           "us_per_step": sec * 1e6, "tflops": w.flops / sec / 1e12,
                           "algorithmic_bytes": w.bytes, "device_status": dlf_b200.device_status()}), flush=True)
         return
+    if args.workload == "resnet_forward":  # the whole network as an operator list
+        print(json.dumps({"resnet50_v1_forward_f16": resnet_forward(device, peaks, args.batch or 256,
+                                                                   steps if args.steps is not None else 10),
+                          "device_status": dlf_b200.device_status()}), flush=True)
+        return
     if args.workload == "resnet_sweep":  # development aid: config 3 alone, per layer
         summary, rows = resnet_sweep(device, peaks, args.batch or 256, steps if args.steps is not None else 10)
         print(json.dumps({"resnet50_v1_convs_f16": summary, "layers": rows, "device_status": dlf_b200.device_status()}), flush=True)
@@ -919,6 +1041,11 @@ def main():
             extras["resnet50_v1_convs_f16_b256_layers"] = rows
         except Exception as e:
             resnet_summary = {"error": repr(e)[:200]}
+        try:
+            extras["resnet50_v1_forward_f16_b256"] = resnet_forward(device, peaks, 256, 10)
+        except Exception as e:
+            extras["resnet50_v1_forward_f16_b256"] = {"error": repr(e)[:200]}
+        torch.cuda.empty_cache()
         try:  # write-only HBM rate (memset of 1 GiB): the roof of the output-dominated workloads
             z = torch.empty(1 << 30, dtype=torch.uint8, device=device)
             ms, _, _ = time_steps(lambda i: z.zero_(), 10, 3, 1)

@@ -176,22 +176,27 @@ int ensure_device(DeviceState** out) {
         CUDA_TRY(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
         if (major != 10) return kNotImplemented;  // tcgen05 kernels: sm_100a only
         cudaFuncAttributes fa;
-        CUDA_TRY(cudaFuncGetAttributes(&fa, contraction_kernel<2, true>));
-        st.static_smem_tma = static_cast<int>(fa.sharedSizeBytes);
-        {
-            auto k4 = contraction_kernel<2, true, false, 4>;
-            CUDA_TRY(cudaFuncGetAttributes(&fa, k4));
-            st.static_smem_tma4 = static_cast<int>(fa.sharedSizeBytes);
-            CUDA_TRY(cudaFuncSetAttribute(k4, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          kSmemPerBlockOptin - st.static_smem_tma4));
+        // the TMA-fed kernel exists with two, three and four sets of epilogue warps, each with and
+        // without residual boxes fetched by TMA; a pair shares the launch arithmetic, which counts
+        // with the larger static shared-memory use of the two
+#define DLF_TMA_SETUP(ESETS, FIELD)                                                                       \
+        {                                                                                                 \
+            auto k0 = contraction_kernel<2, true, false, ESETS, false>;                                   \
+            auto k1 = contraction_kernel<2, true, false, ESETS, true>;                                    \
+            CUDA_TRY(cudaFuncGetAttributes(&fa, k0));                                                     \
+            int worst = static_cast<int>(fa.sharedSizeBytes);                                             \
+            CUDA_TRY(cudaFuncGetAttributes(&fa, k1));                                                     \
+            worst = std::max(worst, static_cast<int>(fa.sharedSizeBytes));                                \
+            st.FIELD = worst;                                                                             \
+            if (ESETS != 2) {                                                                             \
+                CUDA_TRY(cudaFuncSetAttribute(k0, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemPerBlockOptin - worst)); \
+            }                                                                                             \
+            CUDA_TRY(cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemPerBlockOptin - worst));     \
         }
-        {
-            auto k3 = contraction_kernel<2, true, false, 3>;
-            CUDA_TRY(cudaFuncGetAttributes(&fa, k3));
-            st.static_smem_tma3 = static_cast<int>(fa.sharedSizeBytes);
-            CUDA_TRY(cudaFuncSetAttribute(k3, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          kSmemPerBlockOptin - st.static_smem_tma3));
-        }
+        DLF_TMA_SETUP(2, static_smem_tma)
+        DLF_TMA_SETUP(4, static_smem_tma4)
+        DLF_TMA_SETUP(3, static_smem_tma3)
+#undef DLF_TMA_SETUP
         CUDA_TRY(cudaFuncGetAttributes(&fa, contraction_kernel<2, false>));
         st.static_smem_gen2 = static_cast<int>(fa.sharedSizeBytes);
         CUDA_TRY(cudaFuncGetAttributes(&fa, contraction_kernel<4, false>));
@@ -824,7 +829,7 @@ int launch(const Problem& q, cudaStream_t stream, DeviceState* preset = nullptr)
         attr.val.clusterDim.z = 1;
         cfg.attrs = &attr;
         cfg.numAttrs = 1;
-        CUDA_TRY(cudaLaunchKernelEx(&cfg, contraction_kernel<2, true, true>, p, tm_a, tm_b, tm_d));
+        CUDA_TRY(cudaLaunchKernelEx(&cfg, contraction_kernel<2, true, true>, p, tm_a, tm_b, tm_d, tm_d));
         g_launches.fetch_add(1);
         CUDA_TRY(cudaGetLastError());
         return kSuccess;
@@ -897,11 +902,13 @@ int launch(const Problem& q, cudaStream_t stream, DeviceState* preset = nullptr)
     p.out_vec = q.out_vec;
     set_wait_policy(p, total);
 
-    CUtensorMap tm_a, tm_b, tm_d;
+    CUtensorMap tm_a, tm_b, tm_d, tm_r;
     std::memset(&tm_a, 0, sizeof(tm_a));
     std::memset(&tm_b, 0, sizeof(tm_b));
     std::memset(&tm_d, 0, sizeof(tm_d));
+    std::memset(&tm_r, 0, sizeof(tm_r));
     p.d_tma = 0;
+    p.r_tma = 0;
     if (use_tma) {
         if (q.cl_swap) {
             rc = encode_map(*st, &tm_a, q.a, q.es, q.M, q.K, q.batch, kBM);
@@ -916,22 +923,37 @@ int launch(const Problem& q, cudaStream_t stream, DeviceState* preset = nullptr)
         }
         if (rc != kSuccess) return rc;
         // 64-column boxes need 64 columns per epilogue warp
-        const unsigned box_cols = (esets == 2 ? bn >= 128 : (esets == 4 && bn >= 256)) && !(g_force_generic.load() & 0x100) ? 64 : 32;
+        // (a residual is fetched box by box into single staging blocks: 32-column boxes then)
+        const unsigned box_cols = (esets == 2 ? bn >= 128 : (esets == 4 && bn >= 256)) && !(g_force_generic.load() & 0x100) &&
+                                          q.resid == nullptr ? 64 : 32;
         p.d_tma = (!q.d_f32 && encode_output_map(*st, &tm_d, q, box_cols)) ? static_cast<int>(box_cols) : 0;
+        // the residual tensor is laid out like D: the same boxes of it, fetched by TMA loads
+        if (p.d_tma && q.resid != nullptr && (reinterpret_cast<uintptr_t>(q.resid) & 15u) == 0 && !((g_force_bn.load() >> 16) & 512)) {
+            Problem qr = q;
+            qr.d = const_cast<char*>(q.resid);
+            p.r_tma = encode_output_map(*st, &tm_r, qr, box_cols) ? 1 : 0;
+        }
     }
 
     const unsigned grid = static_cast<unsigned>(total < st->num_sms ? total : st->num_sms);
     if (use_tma) {
-        if (four_sets)
-            contraction_kernel<2, true, false, 4><<<grid, tma_threads(4), dyn_smem, stream>>>(p, tm_a, tm_b, tm_d);
-        else if (three_sets)
-            contraction_kernel<2, true, false, 3><<<grid, tma_threads(3), dyn_smem, stream>>>(p, tm_a, tm_b, tm_d);
-        else
-            contraction_kernel<2, true><<<grid, kThreadsTma, dyn_smem, stream>>>(p, tm_a, tm_b, tm_d);
+#define DLF_TMA_LAUNCH(ESETS)                                                                                      \
+        if (p.r_tma)                                                                                               \
+            contraction_kernel<2, true, false, ESETS, true><<<grid, tma_threads(ESETS), dyn_smem, stream>>>(p, tm_a, tm_b, tm_d, tm_r); \
+        else                                                                                                       \
+            contraction_kernel<2, true, false, ESETS, false><<<grid, tma_threads(ESETS), dyn_smem, stream>>>(p, tm_a, tm_b, tm_d, tm_r)
+        if (four_sets) {
+            DLF_TMA_LAUNCH(4);
+        } else if (three_sets) {
+            DLF_TMA_LAUNCH(3);
+        } else {
+            DLF_TMA_LAUNCH(2);
+        }
+#undef DLF_TMA_LAUNCH
     } else if (q.es == 2) {
-        contraction_kernel<2, false><<<grid, kThreadsGen, dyn_smem, stream>>>(p, tm_a, tm_b, tm_d);
+        contraction_kernel<2, false><<<grid, kThreadsGen, dyn_smem, stream>>>(p, tm_a, tm_b, tm_d, tm_r);
     } else {
-        contraction_kernel<4, false><<<grid, kThreadsGen, dyn_smem, stream>>>(p, tm_a, tm_b, tm_d);
+        contraction_kernel<4, false><<<grid, kThreadsGen, dyn_smem, stream>>>(p, tm_a, tm_b, tm_d, tm_r);
     }
     g_launches.fetch_add(1);
     CUDA_TRY(cudaGetLastError());

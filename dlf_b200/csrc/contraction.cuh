@@ -128,6 +128,9 @@ struct Params {
                  // beta == 0 and TMA-compatible strides: the epilogue stages
                  // 32 x 32 blocks in shared memory and writes them with TMA stores
     int d_f32;   // 16-bit operands, but D is written as fp32 (partial products of a K-split GEMM)
+    int r_tma;   // the launch uses the RES instantiation: the residual's 32 x 32 boxes are fetched by TMA
+                 // loads (map tmR, laid out like tmD) into the staging block their results leave from,
+                 // one block ahead of the accumulator
     // Channels-last route of a convolution: operand A is a channels-last (N, H, W, C) copy of the
     // activations. a_cl == 1: tmA is an im2col-mode tensor map; k-block kb is channel block
     // kb % cl_cblocks of filter tap kb / cl_cblocks and one load brings the tile's 128 windows.
@@ -263,6 +266,11 @@ __device__ __forceinline__ void split_tf32(uint32_t x, uint32_t& hi, uint32_t& l
     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo) : "f"(rest));
 }
 
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+    return v;
+}
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, const uint4& v) {
     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y),
                  "r"(v.z), "r"(v.w)
@@ -291,12 +299,14 @@ __device__ __forceinline__ void store_chunk(uint32_t tile, uint32_t lo_tile, int
 // PAIR: the CTA is one of a cluster of two that share 256 x BN tiles through cta_group::2 UMMAs
 // (only with USE_TMA). Each CTA loads its own 128 rows of A and BN/2 rows of B with plain
 // per-CTA TMA loads. Rank 0 issues the UMMAs and signals both CTAs' barriers.
-template <int ES, bool USE_TMA, bool PAIR = false, int ESETS = 2>
+template <int ES, bool USE_TMA, bool PAIR = false, int ESETS = 2, bool RES = false>
 __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(ESETS) : kThreadsGen), 1)
     contraction_kernel(const __grid_constant__ Params p, const __grid_constant__ CUtensorMap tmA,
-                       const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmD) {
+                       const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmD,
+                       const __grid_constant__ CUtensorMap tmR) {
     static_assert(!(USE_TMA && ES == 4), "fp32 operands need the split done by loader warps");
     static_assert(!PAIR || USE_TMA, "CTA pairs are fed by TMA");
+    static_assert(!RES || (USE_TMA && !PAIR && ES == 2), "residual boxes belong to the TMA-store epilogue");
     constexpr int BK = 128 / ES;               // k-values per stage (one 128-byte line)
     constexpr int E = BK;                      // rows per MN-major row group
     constexpr int CPE = 16 / ES;               // elements per 16-byte chunk
@@ -310,6 +320,7 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
     __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
     __shared__ __align__(8) uint64_t tfull_bar[2];
     __shared__ __align__(8) uint64_t tempty_bar[2];
+    __shared__ __align__(8) uint64_t res_bar[RES ? 4 * ESETS : 1][2];  // residual boxes, per epilogue warp and staging block
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
     __shared__ __align__(16) PixelEntry pix_table[USE_TMA ? 1 : kLoaderWarps * kBM];
@@ -338,6 +349,12 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
         for (int s = 0; s < S; ++s) {
             ptx::mbar_init(ptx::smem_u32(&full_bar[s]), USE_TMA ? 1u : kLoaderThreads);
             ptx::mbar_init(ptx::smem_u32(&empty_bar[s]), 1u);
+        }
+        if constexpr (RES) {
+            for (int i = 0; i < 4 * ESETS; ++i) {
+                ptx::mbar_init(ptx::smem_u32(&res_bar[i][0]), 1u);
+                ptx::mbar_init(ptx::smem_u32(&res_bar[i][1]), 1u);
+            }
         }
         for (int i = 0; i < 2; ++i) {
             ptx::mbar_init(ptx::smem_u32(&tfull_bar[i]), 1u);
@@ -381,6 +398,69 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
         const uint32_t d_stage = PAIR ? ptx::smem_u32(d_stage_pair) : smem0 + static_cast<uint32_t>(S) * stage_bytes;
         uint32_t it = 0;
         uint32_t chunk_no = 0;  // TMA-store epilogue: 32-column blocks written so far by this warp
+        // Residual boxes (p.r_tma): a block's residual is the box of the residual tensor that its
+        // result is the box of in D, so one TMA load lands it in the block's own staging buffer, at
+        // the addresses each lane is going to overwrite with its results. The load is issued when
+        // the previous block's store has been handed over - a block ahead of the accumulator, across
+        // tile boundaries too - because loads issued after the accumulator has arrived would add
+        // their whole latency to every block (64 -> 256 channels at 56x56: 128 -> 414 us that way).
+        uint32_t res_pending = 0;  // bit h: a residual load into staging block h is in flight or has landed
+        uint32_t res_parity = 0;   // bit h: phase of res_bar[.][h] to wait for
+        // box coordinates of block c0 of tile tt for this warp; false when that block does not leave
+        // through a TMA store (the conditions of the store paths below)
+        auto res_box = [&](int tt, int c0, int& x, int& y, int& z) -> bool {
+            if (tt >= p.total_tiles) return false;
+            int bb, mm, nn;
+            decode_tile(p, tt, bb, mm, nn, tile_rows);
+            mm += row_off;
+            const int ncols_t = max(0, min(cols_per, min(BN, p.N - nn) - cbase));
+            if (p.out_nchw == 3) {
+                if (c0 + 32 > ncols_t) return false;
+                const int j0 = nn + cbase + c0;
+                const int img = j0 / p.g.P;
+                const int pp = j0 - img * p.g.P;
+                if (pp + 32 > p.g.P && p.batch == 1) return false;
+                x = pp;
+                y = mm + q * 32;
+                z = p.batch > 1 ? bb : img;
+                return true;
+            }
+            const int i0 = mm + q * 32;
+            if (i0 >= p.M || c0 >= ncols_t) return false;
+            const int img0 = p.out_nchw == 1 ? i0 / p.g.P : 0;
+            const int pp0 = p.out_nchw == 1 ? i0 - img0 * p.g.P : i0;
+            if (p.out_nchw == 1 && pp0 + 32 > p.g.P) return false;
+            x = pp0;
+            y = nn + cbase + c0;
+            z = p.out_nchw == 1 ? img0 : (p.d_batch_stride ? bb : 0);
+            return true;
+        };
+        auto res_fetch = [&](int tt, int c0, uint32_t h) {
+            int x = 0, y = 0, z = 0;
+            if (!res_box(tt, c0, x, y, z)) return;
+            if (lane == 0) {
+                const uint32_t bar = ptx::smem_u32(&res_bar[RES ? ewarp : 0][h]);
+                ptx::mbar_arrive_expect_tx(bar, 2048u);
+                ptx::tma_load_3d(d_stage + (ewarp * 2 + h) * 2048u, &tmR, bar, x, y, z);
+            }
+            res_pending |= 1u << h;
+        };
+        // the residual of block (tt, c0) is in staging block h (waits for it), or was never fetched
+        auto res_landed = [&](uint32_t h) -> bool {
+            if (!((res_pending >> h) & 1u)) return false;
+            (void)ptx::mbar_wait_bounded(ptx::smem_u32(&res_bar[RES ? ewarp : 0][h]), (res_parity >> h) & 1u,
+                                         abort_p, wait_limit);
+            res_parity ^= 1u << h;
+            res_pending &= ~(1u << h);
+            return true;
+        };
+        // after block c0 of tile tt (ncols_t columns for this warp) has been handed to its store: the
+        // other staging block is free once the store before that one has read it
+        auto res_ahead = [&](int tt, int c0, int ncols_t, uint32_t h) {
+            if (lane == 0) ptx::bulk_wait_group_read<1>();
+            if (c0 + 32 < ncols_t) res_fetch(tt, c0 + 32, h);
+            else res_fetch(tt + tile_step, 0, h);
+        };
         DLF_CLK_DECL(warp == 0 && lane == 0)
         for (int t = tile0; t < p.total_tiles; t += tile_step, ++it) {
             int b, m0, n0;
@@ -430,16 +510,23 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
                                 __syncwarp();
                             }
                             const uint32_t sblk = d_stage + (ewarp * 2 + half) * 2048u;
-                            const char* rp = p.resid ? p.resid + boff3 +
-                                                           (static_cast<long long>(img) * p.g.out_img_stride + rowoff + pp) * 2
-                                                     : nullptr;
+                            bool res_smem = false;
+                            if constexpr (RES) {
+                                if (!((res_pending >> half) & 1u)) res_fetch(t, c0, half);  // nothing was fetched ahead
+                                res_smem = res_landed(half);
+                            }
+                            const char* rp = (p.resid && !res_smem)
+                                                 ? p.resid + boff3 +
+                                                       (static_cast<long long>(img) * p.g.out_img_stride + rowoff + pp) * 2
+                                                 : nullptr;
 #pragma unroll
                             for (int k = 0; k < 4; ++k) {
                                 float r[8];
 #pragma unroll
                                 for (int g = 0; g < 8; ++g) r[g] = fmaf(p.alpha, __uint_as_float(v[8 * k + g]), bv3);
-                                if (rp != nullptr && co_ok) {
-                                    const uint4 u = *reinterpret_cast<const uint4*>(rp + 16 * k);
+                                if (res_smem || (rp != nullptr && co_ok)) {
+                                    const uint4 u = res_smem ? ld_shared_v4(sblk + lane * 64u + k * 16u)
+                                                             : *reinterpret_cast<const uint4*>(rp + 16 * k);
                                     const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
                                     for (int g = 0; g < 4; ++g) {
@@ -473,6 +560,7 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
                                 ptx::bulk_commit_group();
                             }
                             ++chunk_no;
+                            if constexpr (RES) res_ahead(t, c0, ncols3, half ^ 1u);
                             continue;
                         }
 #define DLF_SWAPPED(OUT, G)                                                                                   \
@@ -570,7 +658,24 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
                             __syncwarp();
                         }
                         const uint32_t sbuf = d_stage + (ewarp * 2 + half) * 2048u + lane * 2u;
-                        if (p.resid != nullptr) {
+                        bool res_smem = false;
+                        if constexpr (RES) {
+                            if (!direct) {
+                                if (!((res_pending >> half) & 1u)) res_fetch(t, c0, half);
+                                res_smem = res_landed(half);
+                            }
+                        }
+                        if (res_smem) {
+                            // the block's residual lies in the staging block, [column][row] like the results
+#pragma unroll
+                            for (int jj = 0; jj < 32; ++jj) {
+                                unsigned short h16;
+                                asm volatile("ld.shared.u16 %0, [%1];" : "=h"(h16) : "r"(sbuf + jj * 64u) : "memory");
+                                const float rv = p.fmt == FMT_F16 ? __half2float(__ushort_as_half(h16))
+                                                                  : __bfloat162float(__ushort_as_bfloat16(h16));
+                                v[jj] = __float_as_uint(alpha * __uint_as_float(v[jj]) + rv);
+                            }
+                        } else if (p.resid != nullptr) {
                             // residual values first (loads must not sit between the stores)
                             const char* rp = p.resid + (optr - p.d) + static_cast<long long>(c0) * colstride * 2;
 #pragma unroll
@@ -629,6 +734,7 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
                             ptx::tma_store_3d(&tmD, ssrc, pp0, col, p.out_nchw == 1 ? img0 : (p.d_batch_stride ? b : 0));
                             ptx::bulk_commit_group();
                         }
+                        if constexpr (RES) res_ahead(t, c0, ncols, half ^ 1u);
                     }
                     ptx::tc_fence_before();
                     if constexpr (PAIR) {
@@ -669,6 +775,12 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
             }
         }
         if constexpr (USE_TMA) {
+            // a residual box fetched ahead of a block that never came (the loop was left early): its
+            // bytes must have landed before the CTA's shared memory is given back
+            if constexpr (RES) {
+                if (res_pending & 1u) (void)res_landed(0u);
+                if (res_pending & 2u) (void)res_landed(1u);
+            }
             if (p.d_tma && lane == 0) ptx::bulk_wait_group<0>();  // all staged blocks are in global memory
         }
     } else if (warp == kMmaWarp) {

@@ -10,6 +10,7 @@ reference's ``StatusCode`` value. Every call goes through the C-ABI of libdlf_b2
 """
 import ctypes
 import enum
+import threading
 
 import torch
 
@@ -111,11 +112,44 @@ def _stream(queue):
 
 
 _GEMM_WORKSPACES = {}
+_SCRATCH = threading.local()
+
+
+class scratch:
+    """``with scratch(buffer):`` makes the calls of this thread take their device scratch (K-split
+    partial sums, packed filter banks, channels-last copies) from ``buffer`` (a uint8 device tensor
+    the caller owns) instead of the per-stream buffers that grow on demand: nothing is allocated
+    inside, which a CUDA-graph capture of a sequence of calls needs. A call that needs more than
+    the buffer holds raises."""
+
+    def __init__(self, buffer):
+        self.buffer = buffer
+
+    def __enter__(self):
+        self.previous = getattr(_SCRATCH, "buffer", None)
+        _SCRATCH.buffer = self.buffer
+        return self
+
+    def __exit__(self, *exc):
+        _SCRATCH.buffer = self.previous
+        return False
+
+
+def _caller_scratch(device, nbytes):
+    buf = getattr(_SCRATCH, "buffer", None)
+    if buf is None:
+        return None
+    if buf.device != device or buf.numel() < nbytes:
+        raise BLASError(StatusCode.kInsufficientMemoryTemp)
+    return buf
 
 
 def _gemm_workspace(device, stream, nbytes):
     """One scratch buffer per (device, stream), grown on demand; calls on a stream are ordered, so
     they can share it."""
+    own = _caller_scratch(device, nbytes)
+    if own is not None:
+        return own
     key = (device.index, stream.cuda_stream)
     buf = _GEMM_WORKSPACES.get(key)
     if buf is None or buf.numel() < nbytes:

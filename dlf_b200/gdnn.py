@@ -11,7 +11,7 @@ import ctypes
 import torch
 
 from . import lib
-from .gblas import BLASError, StatusCode, _check, _ptr, _stream, precision_of
+from .gblas import BLASError, StatusCode, _caller_scratch, _check, _ptr, _stream, precision_of
 
 
 class Filter2D:
@@ -88,6 +88,9 @@ def _workspace(device, stream, nbytes):
     """Scratch for the packed filter bank, one buffer per (device, stream), grown on demand - the
     role the context's temporary-buffer pool plays in the reference (gpgpu/src/gpgpu.cpp:189-214).
     Calls on one stream are ordered, so they can share it."""
+    own = _caller_scratch(device, nbytes)
+    if own is not None:
+        return own
     key = (device.index, stream.cuda_stream)
     buf = _WORKSPACES.get(key)
     if buf is None or buf.numel() < nbytes:
