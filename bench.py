@@ -135,6 +135,17 @@ class ConvC2(Workload):
         j = i % self.sets
         gdnn.conv2d_filter(self.X[j], self.W, self.Y[j], self.filt, bias=self.b)
 
+    def step_fused(self, i):
+        """The same convolution followed by the residual Add and ReLU of a bottleneck's last layer,
+        in one launch (profiling aid: --workload conv --residual)."""
+        from dlf_b200 import gdnn
+        j = i % self.sets
+        if not hasattr(self, "R"):
+            g = torch.Generator(device=self.Y[0].device).manual_seed(3)
+            self.R = [torch.randn(self.Y[0].shape, generator=g, device=self.Y[0].device).to(self.Y[0].dtype)
+                      for _ in range(self.sets)]
+        gdnn.conv2d_filter(self.X[j], self.W, self.Y[j], self.filt, bias=self.b, residual=self.R[j], activation="relu")
+
     def step_no_workspace(self, i):
         """The same convolution through the C ABI with workspace = NULL (the filter bank is then
         gathered inside the main loop instead of being packed first)."""
@@ -842,6 +853,7 @@ def main():
     ap.add_argument("--batch", type=int, default=None, help="images per GPU for conv_c2 (profiling: a small case)")
     ap.add_argument("--shape", default="64,56,64,3,1,1", help="--workload conv: Cin,H,Cout,k,stride,pad")
     ap.add_argument("--dtype", default="f16", help="--workload conv: f16, bf16 or f32")
+    ap.add_argument("--residual", action="store_true", help="--workload conv: fuse a residual Add and ReLU")
     ap.add_argument("--tuning", type=lambda x: int(x, 0), default=0,
                     help="experiments: second argument of dlf_b200_set_tuning for the whole run")
     ap.add_argument("--overlap-gather", action="store_true",
@@ -892,9 +904,10 @@ def main():
                    dtype=args.dtype)
         w.setup(device, 0, w.sets_needed())
         n = steps if args.steps is not None else 20
-        ms, _, _ = time_steps(w.step, n, warmup, 1)
+        ms, _, _ = time_steps(w.step_fused if args.residual else w.step, n, warmup, 1)
         sec = ms / 1e3 / n
         print(json.dumps({"workload": "conv", "shape": args.shape, "batch": w.shape["N"], "dtype": args.dtype,
+                          "residual_relu": bool(args.residual),
                           "us_per_step": sec * 1e6, "tflops": w.flops / sec / 1e12,
                           "algorithmic_bytes": w.bytes, "device_status": dlf_b200.device_status()}), flush=True)
         return

@@ -408,7 +408,9 @@ bool encode_output_map(const DeviceState& st, CUtensorMap* map, const Problem& q
     if (q.out_nchw == 3) {
         // swapped roles (rows = channels, columns = pixels): boxes of 32 pixels x 32 channels of the
         // NCHW output {pixels of a plane, channels, images}; images are the batch entries in the
-        // batched form (N = P), else N / P
+        // batched form (N = P), else N / P. The staging block is 64-byte swizzled: its rows are 64
+        // bytes, and lanes that write 16 bytes each at a 64-byte stride would otherwise use two of
+        // the eight 16-byte bank groups (four times the shared-memory wavefronts)
         const long long P = q.g.P;
         const bool ok = q.es == 2 && q.beta == 0.0f && (reinterpret_cast<uintptr_t>(q.d) & 15u) == 0 &&
                         (P * q.es) % 16 == 0 && P * q.M * q.es < (1ll << 40) && !(g_force_generic.load() & 0x4000);
@@ -419,7 +421,7 @@ bool encode_output_map(const DeviceState& st, CUtensorMap* map, const Problem& q
         cuuint32_t box[3] = {32, 32, 1};
         cuuint32_t estr[3] = {1, 1, 1};
         CUresult r = st.encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, q.d, dims, strides, box, estr,
-                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
                                CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         return r == CUDA_SUCCESS;
     }
@@ -1669,7 +1671,7 @@ int dlf_b200_conv2d_fused(int dtype, size_t batches, size_t channels, size_t hei
                     cuuint32_t box[3] = {32, 32, 1};
                     cuuint32_t estr[3] = {1, 1, 1};
                     sp.d_tma = st->encode(&tm_d, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, y, dims, strides, box, estr,
-                                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
                                           CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS
                                    ? 1
                                    : 0;
@@ -1785,7 +1787,7 @@ int dlf_b200_conv2d_fused(int dtype, size_t batches, size_t channels, size_t hei
                     cuuint32_t box[3] = {32, 32, 1};
                     cuuint32_t estr[3] = {1, 1, 1};
                     hp_.d_tma = st->encode(&tm_d, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, y, dims, strides, box, estr,
-                                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
                                            CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS
                                     ? 1
                                     : 0;

@@ -525,7 +525,7 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
 #pragma unroll
                                 for (int g = 0; g < 8; ++g) r[g] = fmaf(p.alpha, __uint_as_float(v[8 * k + g]), bv3);
                                 if (res_smem || (rp != nullptr && co_ok)) {
-                                    const uint4 u = res_smem ? ld_shared_v4(sblk + lane * 64u + k * 16u)
+                                    const uint4 u = res_smem ? ld_shared_v4(sblk + lane * 64u + ((static_cast<uint32_t>(k) ^ ((lane >> 1) & 3u)) << 4))
                                                              : *reinterpret_cast<const uint4*>(rp + 16 * k);
                                     const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
@@ -551,7 +551,8 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
                                         ow[g] = *reinterpret_cast<const uint32_t*>(&h);
                                     }
                                 }
-                                st_shared_v4(sblk + lane * 64u + k * 16u, o);
+                                // 64-byte swizzle of the box: 16-byte unit k of row r lies at unit k ^ ((r >> 1) & 3)
+                                st_shared_v4(sblk + lane * 64u + ((static_cast<uint32_t>(k) ^ ((lane >> 1) & 3u)) << 4), o);
                             }
                             ptx::fence_proxy_async_smem();
                             __syncwarp();

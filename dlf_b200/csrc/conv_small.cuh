@@ -66,7 +66,8 @@ struct SmallParams {
 };
 
 // One lane's 32 consecutive output pixels: bias, residual, ReLU, conversion, and 64 bytes into the
-// staging block of a TMA store (row = this lane's channel).
+// staging block of a TMA store (row = this lane's channel; `srow` = its 64 bytes in a block aligned
+// to 512 bytes).
 template <int OUT>
 __device__ __forceinline__ void small_stage_block(const uint32_t (&v)[32], uint32_t srow, const char* rp, bool row_ok,
                                                   float bv, bool relu) {
@@ -103,7 +104,9 @@ __device__ __forceinline__ void small_stage_block(const uint32_t (&v)[32], uint3
                 ow[g] = *reinterpret_cast<const uint32_t*>(&h);
             }
         }
-        st_shared_v4(srow + k * 16u, o);
+        // the staging block is 64-byte swizzled (the box of the TMA store says so): 16-byte unit k of
+        // row r lies at unit k ^ ((r >> 1) & 3), which spreads the lanes' stores over all bank groups
+        st_shared_v4(srow + ((static_cast<uint32_t>(k) ^ ((srow >> 7) & 3u)) << 4), o);
     }
 }
 
