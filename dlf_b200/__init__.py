@@ -68,6 +68,17 @@ def _declare(L):
     L.dlf_b200_maxpool.argtypes = [c_int] + [c_size] * 16 + [c_void, c_void, c_void]
     L.dlf_b200_avgpool.restype = c_int
     L.dlf_b200_avgpool.argtypes = [c_int] + [c_size] * 16 + [c_int, c_void, c_void, c_void]
+    L.dlf_b200_nhwc_filter_elems.restype = c_size
+    L.dlf_b200_nhwc_filter_elems.argtypes = [c_size] * 4
+    L.dlf_b200_pack_filters_nhwc.restype = c_int
+    L.dlf_b200_pack_filters_nhwc.argtypes = [c_int] + [c_size] * 4 + [c_void, c_void, c_void]
+    L.dlf_b200_nchw_to_nhwc.restype = c_int
+    L.dlf_b200_nchw_to_nhwc.argtypes = [c_int] + [c_size] * 4 + [c_void, c_void, c_void]
+    L.dlf_b200_conv2d_nhwc.restype = c_int
+    L.dlf_b200_conv2d_nhwc.argtypes = [c_int] + [c_size] * 17 + [c_void, c_void, c_void, c_void, c_int, c_void, c_int,
+                                                               c_void]
+    L.dlf_b200_pool_nhwc.restype = c_int
+    L.dlf_b200_pool_nhwc.argtypes = [c_int, c_int, c_int] + [c_size] * 12 + [c_void, c_void, c_void]
     L.dlf_b200_conv2d_workspace_bytes.restype = c_size
     L.dlf_b200_conv2d_workspace_bytes.argtypes = [c_int] + [c_size] * 10
     L.dlf_b200_level3_workspace_bytes.restype = c_size
@@ -102,6 +113,11 @@ EXPORTED_SYMBOLS = (
     "dlf_b200_conv2d",
     "dlf_b200_conv2d_fused",
     "dlf_b200_conv2d_workspace_bytes",
+    "dlf_b200_nhwc_filter_elems",
+    "dlf_b200_pack_filters_nhwc",
+    "dlf_b200_nchw_to_nhwc",
+    "dlf_b200_conv2d_nhwc",
+    "dlf_b200_pool_nhwc",
     "dlf_b200_level3_workspace_bytes",
     "dlf_b200_symm",
     "dlf_b200_syrk",

@@ -425,6 +425,21 @@ bool encode_output_map(const DeviceState& st, CUtensorMap* map, const Problem& q
                                CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         return r == CUDA_SUCCESS;
     }
+    if (q.out_nchw == 5) {
+        // channels-last output D[pixel][channel] (rows = pixels of all images): boxes of 32 channels x 32
+        // pixels of {channels, pixels}, 64-byte swizzled like the swapped form's
+        const bool ok = q.es == 2 && q.beta == 0.0f && (reinterpret_cast<uintptr_t>(q.d) & 15u) == 0 &&
+                        (q.N * q.es) % 16 == 0 && q.N * q.es < (1ll << 40) && !(g_force_generic.load() & 0x4000);
+        if (!ok) return false;
+        cuuint64_t dims[3] = {static_cast<cuuint64_t>(q.N), static_cast<cuuint64_t>(q.M), 1};
+        cuuint64_t strides[2] = {static_cast<cuuint64_t>(q.N * q.es), static_cast<cuuint64_t>(q.N * q.M * q.es)};
+        cuuint32_t box[3] = {32, 32, 1};
+        cuuint32_t estr[3] = {1, 1, 1};
+        CUresult r = st.encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, q.d, dims, strides, box, estr,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+                               CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        return r == CUDA_SUCCESS;
+    }
     if (q.out_nchw) {
         // NCHW output of a convolution: {pixels of a plane, channels, images}
         const long long P = q.g.P;
@@ -855,7 +870,7 @@ int launch(const Problem& q, cudaStream_t stream, DeviceState* preset = nullptr)
     // Three sets (448 threads, 128 registers, no spills) for the widening pixel-per-lane layers the
     // four-set form leaves out (256 -> 1024 at 14x14: 77 -> 73 us; 1024 -> 2048 stride 2: 110 -> 98 us;
     // 3x3 layers lose 4-6 % with it). Bit 22 of the tile-width word: never.
-    const bool three_sets = use_tma && !four_sets && q.out_nchw == 1 && bn >= 128 && q.N >= 2 * q.K &&
+    const bool three_sets = use_tma && !four_sets && (q.out_nchw == 1 || q.out_nchw == 5) && bn >= 128 && q.N >= 2 * q.K &&
                             !((g_force_bn.load() >> 16) & 64);
     const int esets = four_sets ? 4 : (three_sets ? 3 : 2);
     const int static_smem = use_tma ? (four_sets ? st->static_smem_tma4 : three_sets ? st->static_smem_tma3 : st->static_smem_tma)
@@ -929,12 +944,14 @@ int launch(const Problem& q, cudaStream_t stream, DeviceState* preset = nullptr)
         const unsigned box_cols = (esets == 2 ? bn >= 128 : (esets == 4 && bn >= 256)) && !(g_force_generic.load() & 0x100) &&
                                           q.resid == nullptr ? 64 : 32;
         p.d_tma = (!q.d_f32 && encode_output_map(*st, &tm_d, q, box_cols)) ? static_cast<int>(box_cols) : 0;
+        if (q.out_nchw == 5 && !p.d_tma) return kNotImplemented;  // the channels-last form only leaves through TMA stores
         // the residual tensor is laid out like D: the same boxes of it, fetched by TMA loads
         if (p.d_tma && q.resid != nullptr && (reinterpret_cast<uintptr_t>(q.resid) & 15u) == 0 && !((g_force_bn.load() >> 16) & 512)) {
             Problem qr = q;
             qr.d = const_cast<char*>(q.resid);
             p.r_tma = encode_output_map(*st, &tm_r, qr, box_cols) ? 1 : 0;
         }
+        if (q.out_nchw == 5 && q.resid != nullptr && !p.r_tma) return kNotImplemented;
     }
 
     const unsigned grid = static_cast<unsigned>(total < st->num_sms ? total : st->num_sms);
@@ -1513,10 +1530,12 @@ int dlf_b200_conv2d_fused(int dtype, size_t batches, size_t channels, size_t hei
         // columns are 64 consecutive bytes of Y: four 16-byte shared-memory stores fill the staging
         // block of a TMA store, where the pixel-per-lane form needs 32 two-byte ones. Measured on the
         // ResNet-50 shapes (batch 256): 128 -> 512 at 28x28 94 -> 86 us, 256 -> 64 at 56x56 98 -> 90 us,
-        // 512 -> 128 at 28x28 56 -> 49 us; with 64 output channels half of the 128 lanes would idle
-        // (64 -> 64: 73 -> 81 us), so those stay unswapped. Bit 19 of the tile-width word: never swap.
+        // 512 -> 128 at 28x28 56 -> 49 us. With 64 output channels half of the 128 lanes idle, but the
+        // epilogue warps of the idle quadrants skip their blocks and the staged stores are still the
+        // cheaper ones (64 -> 64 at 56x56: 69 -> 63 us; 256 -> 64: 93 -> 92 us). Bit 19 of the
+        // tile-width word: never swap.
         const uintptr_t ya = reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(residual);
-        if (P % 8 == 0 && P >= 32 && ya % 16 == 0 && num_kernels >= 128 && !((g_force_bn.load() >> 16) & 8)) {
+        if (P % 8 == 0 && P >= 32 && ya % 16 == 0 && num_kernels >= 64 && !((g_force_bn.load() >> 16) & 8)) {
             std::swap(q.a, q.b);
             q.M = static_cast<long long>(num_kernels);
             q.N = P;
@@ -2386,6 +2405,231 @@ int launch_pool(int dtype, int mode, int count_include_pad, size_t batches, size
 }
 
 }  // namespace
+
+size_t dlf_b200_nhwc_filter_elems(size_t channels, size_t num_kernels, size_t kernel_h, size_t kernel_w) {
+    return num_kernels * kernel_h * kernel_w * ((channels + 63) / 64 * 64);
+}
+
+int dlf_b200_pack_filters_nhwc(int dtype, size_t channels, size_t num_kernels, size_t kernel_h, size_t kernel_w,
+                               const void* w, void* w_packed, void* stream) {
+    int fmt = 0, es = 0;
+    if (!dtype_info(dtype, fmt, es) || es != 2) return kNotImplemented;
+    if (channels == 0 || num_kernels == 0 || kernel_h == 0 || kernel_w == 0) return kInvalidDimension;
+    if (w == nullptr) return kInvalidMatrixB;
+    if (w_packed == nullptr || (reinterpret_cast<uintptr_t>(w_packed) & 15u)) return kInvalidMatrixC;
+    const long long taps = static_cast<long long>(kernel_h) * kernel_w;
+    const long long ck = (static_cast<long long>(channels) + 63) / 64 * 64;
+    if (taps * ck >= INT_MAX - 512 || static_cast<long long>(num_kernels) * ck >= (1ll << 40)) return kInvalidDimension;
+    StreamDevice sd(static_cast<cudaStream_t>(stream));
+    if (sd.rc != kSuccess) return sd.rc;
+    DeviceState* st = nullptr;
+    int rc = ensure_device(&st);
+    if (rc != kSuccess) return rc;
+    clear_stale_error();
+    const long long total = static_cast<long long>(num_kernels) * ck;
+    const unsigned blocks = static_cast<unsigned>(std::min<long long>((total + 255) / 256, 8ll * st->num_sms));
+    cl_pack_filters_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint16_t*>(w), static_cast<uint16_t*>(w_packed), static_cast<int>(num_kernels),
+        static_cast<int>(channels), static_cast<int>(taps), static_cast<int>(ck));
+    g_launches.fetch_add(1);
+    CUDA_TRY(cudaGetLastError());
+    return kSuccess;
+}
+
+int dlf_b200_nchw_to_nhwc(int dtype, size_t batches, size_t channels, size_t height, size_t width, const void* x,
+                          void* y, void* stream) {
+    int fmt = 0, es = 0;
+    if (!dtype_info(dtype, fmt, es) || es != 2) return kNotImplemented;
+    if (batches == 0 || channels == 0 || height == 0 || width == 0) return kInvalidDimension;
+    if (x == nullptr) return kInvalidMatrixA;
+    if (y == nullptr || (reinterpret_cast<uintptr_t>(y) & 15u)) return kInvalidMatrixC;
+    const long long plane = static_cast<long long>(height) * width;
+    const long long cp = (static_cast<long long>(channels) + 7) / 8 * 8;
+    if (plane >= INT_MAX || batches >= 65536 || cp >= 65536ll * 64) return kInvalidDimension;
+    StreamDevice sd(static_cast<cudaStream_t>(stream));
+    if (sd.rc != kSuccess) return sd.rc;
+    DeviceState* st = nullptr;
+    int rc = ensure_device(&st);
+    if (rc != kSuccess) return rc;
+    clear_stale_error();
+    cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    dim3 grid(static_cast<unsigned>((plane + kClTile - 1) / kClTile), static_cast<unsigned>((cp + kClTile - 1) / kClTile),
+              static_cast<unsigned>(batches));
+    const uint16_t* xs = static_cast<const uint16_t*>(x);
+    uint16_t* xp = static_cast<uint16_t*>(y);
+    const long long total = static_cast<long long>(batches) * channels * plane;
+    const uintptr_t xa = reinterpret_cast<uintptr_t>(x);
+    const int ci = static_cast<int>(channels), cpi = static_cast<int>(cp), pl = static_cast<int>(plane);
+    if (plane % 8 == 0 && xa % 16 == 0)
+        cl_pack_activations_kernel<CL_VEC8><<<grid, 256, 0, cs>>>(xs, xp, ci, plane, pl, 1, pl, 1, 1, cpi, total);
+    else if (plane % 4 == 0 && xa % 8 == 0)
+        cl_pack_activations_kernel<CL_VEC4><<<grid, 256, 0, cs>>>(xs, xp, ci, plane, pl, 1, pl, 1, 1, cpi, total);
+    else if (plane % 2 == 0 && xa % 4 == 0)
+        cl_pack_activations_kernel<CL_VEC2><<<grid, 256, 0, cs>>>(xs, xp, ci, plane, pl, 1, pl, 1, 1, cpi, total);
+    else
+        cl_pack_activations_kernel<CL_FUNNEL><<<grid, 256, 0, cs>>>(xs, xp, ci, plane, pl, 1, pl, 1, 1, cpi, total);
+    g_launches.fetch_add(1);
+    CUDA_TRY(cudaGetLastError());
+    return kSuccess;
+}
+
+int dlf_b200_conv2d_nhwc(int dtype, size_t batches, size_t channels, size_t height, size_t width, size_t output_h,
+                         size_t output_w, size_t num_kernels, size_t kernel_h, size_t kernel_w, size_t pad_top,
+                         size_t pad_left, size_t pad_bottom, size_t pad_right, size_t stride_h, size_t stride_w,
+                         size_t dilation_h, size_t dilation_w, const void* x, const void* w_packed, const void* bias,
+                         const void* residual, int activation, void* y, int y_layout, void* stream) {
+    (void)pad_bottom;
+    (void)pad_right;
+    Problem q;
+    if (activation != DLF_B200_ACT_NONE && activation != DLF_B200_ACT_RELU) return kInvalidValue;
+    if (y_layout != DLF_B200_LAYOUT_NHWC && y_layout != DLF_B200_LAYOUT_NCHW) return kInvalidValue;
+    if (!dtype_info(dtype, q.fmt, q.es)) return kNotImplemented;
+    if (q.es != 2) return kNotImplemented;
+    if (batches == 0 || channels == 0 || height == 0 || width == 0 || output_h == 0 || output_w == 0 ||
+        num_kernels == 0 || kernel_h == 0 || kernel_w == 0)
+        return kInvalidDimension;
+    if (stride_h == 0 || stride_w == 0 || dilation_h == 0 || dilation_w == 0) return kInvalidValue;
+    if (x == nullptr) return kInvalidMatrixA;
+    if (w_packed == nullptr) return kInvalidMatrixB;
+    if (y == nullptr) return kInvalidMatrixC;
+    const size_t lim = 1u << 20;
+    if (height >= lim || width >= lim || kernel_h > 16 || kernel_w > 16 || pad_top >= 128 || pad_left >= 128 ||
+        stride_h > 8 || stride_w > 8 || dilation_h * (kernel_h - 1) >= 256 || dilation_w * (kernel_w - 1) >= 256 ||
+        batches >= 65536)
+        return kNotImplemented;
+    // the tensor-map unit wants 16-byte pixels and rows; the stores 16-byte rows of D
+    if (channels % 8 != 0 || (y_layout == DLF_B200_LAYOUT_NHWC && num_kernels % 8 != 0)) return kNotImplemented;
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w_packed) | reinterpret_cast<uintptr_t>(y) |
+         reinterpret_cast<uintptr_t>(residual)) & 15u)
+        return kNotImplemented;
+    const long long P = static_cast<long long>(output_h) * output_w;
+    const long long taps = static_cast<long long>(kernel_h) * kernel_w;
+    const long long ck = (static_cast<long long>(channels) + 63) / 64 * 64;
+    if (P >= INT_MAX || static_cast<long long>(batches) * P >= INT_MAX - 512 || taps * ck >= INT_MAX - 512)
+        return kInvalidDimension;
+    StreamDevice sd(static_cast<cudaStream_t>(stream));
+    if (sd.rc != kSuccess) return sd.rc;
+    DeviceState* st = nullptr;
+    int rc = ensure_device(&st);
+    if (rc != kSuccess) return rc;
+    if (st->encode_im2col == nullptr) return kNotImplemented;
+    clear_stale_error();
+    q.resid = static_cast<const char*>(residual);
+    q.relu = activation == DLF_B200_ACT_RELU ? 1 : 0;
+    q.alpha = 1.f;
+    q.beta = 0.f;
+    q.bias = static_cast<const char*>(bias);
+    q.bias_stride = 0;
+    q.batch = 1;
+    q.M = static_cast<long long>(batches) * P;  // output pixels of all images
+    q.N = static_cast<long long>(num_kernels);
+    q.K = taps * ck;
+    q.g.H = static_cast<int>(height);
+    q.g.W = static_cast<int>(width);
+    q.g.OH = static_cast<int>(output_h);
+    q.g.OW = static_cast<int>(output_w);
+    q.g.KH = static_cast<int>(kernel_h);
+    q.g.KW = static_cast<int>(kernel_w);
+    q.g.pad_t = static_cast<int>(pad_top);
+    q.g.pad_l = static_cast<int>(pad_left);
+    q.g.sh = static_cast<int>(stride_h);
+    q.g.sw = static_cast<int>(stride_w);
+    q.g.dh = static_cast<int>(dilation_h);
+    q.g.dw = static_cast<int>(dilation_w);
+    q.g.P = static_cast<int>(P);
+    q.g.img_stride = static_cast<long long>(channels) * height * width;
+    q.g.out_img_stride = static_cast<long long>(num_kernels) * P;
+    // operand A: filter windows of the channels-last activations, fetched by im2col-mode loads (one
+    // load = 128 windows x 64 channels of one tap); operand B: the packed filter bank (Cout, tap, Ck)
+    q.a.base = static_cast<const char*>(x);
+    q.a.im2col = 0;
+    q.a.k_major = 1;
+    q.a.ld = static_cast<long long>(channels);
+    q.a.batch_stride = 0;
+    q.b.base = static_cast<const char*>(w_packed);
+    q.b.k_major = 1;
+    q.b.ld = q.K;
+    q.b.batch_stride = 0;
+    q.d = static_cast<char*>(y);
+    q.d_batch_stride = 0;
+    q.a_cl = 1;
+    q.cl_cblocks = static_cast<int>(ck / 64);
+    q.cl_n = static_cast<long long>(batches);
+    q.cl_h = static_cast<long long>(height);
+    q.cl_w = static_cast<long long>(width);
+    q.cl_cp = static_cast<long long>(channels);
+    q.pack_ws = nullptr;
+    q.pack_ws_bytes = 0;
+    if (y_layout == DLF_B200_LAYOUT_NHWC) {
+        q.ldd = static_cast<long long>(num_kernels);
+        q.out_nchw = 5;
+    } else {
+        // NCHW output: the forms of the channels-last route of dlf_b200_conv2d_fused
+        q.ldd = P;
+        q.out_nchw = 1;
+        if (P % 8 == 0 && P >= 32) {
+            std::swap(q.a, q.b);
+            q.M = static_cast<long long>(num_kernels);
+            q.N = static_cast<long long>(batches) * P;
+            q.cl_swap = 1;
+            q.out_nchw = 3;
+            q.out_vec = 8;
+        } else {
+            q.out_vec = P % 4 == 0 ? 4 : (P % 2 == 0 ? 2 : 1);
+        }
+    }
+    return launch(q, static_cast<cudaStream_t>(stream), st);
+}
+
+int dlf_b200_pool_nhwc(int dtype, int average, int count_include_pad, size_t batches, size_t channels, size_t height,
+                       size_t width, size_t output_h, size_t output_w, size_t kernel_h, size_t kernel_w, size_t pad_top,
+                       size_t pad_left, size_t stride_h, size_t stride_w, const void* x, void* y, void* stream) {
+    int fmt = 0, es = 0;
+    if (!dtype_info(dtype, fmt, es) || es != 2) return kNotImplemented;
+    if (batches == 0 || channels == 0 || height == 0 || width == 0 || output_h == 0 || output_w == 0 || kernel_h == 0 ||
+        kernel_w == 0)
+        return kInvalidDimension;
+    if (stride_h == 0 || stride_w == 0) return kInvalidValue;
+    if (x == nullptr) return kInvalidMatrixA;
+    if (y == nullptr) return kInvalidMatrixC;
+    if (channels % 8 != 0 || ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15u)) return kNotImplemented;
+    const size_t lim = 1u << 20;
+    if (height >= lim || width >= lim || kernel_h >= lim || kernel_w >= lim || pad_top >= lim || pad_left >= lim ||
+        stride_h >= lim || stride_w >= lim)
+        return kInvalidDimension;
+    const long long total = static_cast<long long>(batches) * output_h * output_w * (channels / 8);
+    if (total >= (1ll << 40)) return kInvalidDimension;
+    StreamDevice sd(static_cast<cudaStream_t>(stream));
+    if (sd.rc != kSuccess) return sd.rc;
+    DeviceState* st = nullptr;
+    int rc = ensure_device(&st);
+    if (rc != kSuccess) return rc;
+    clear_stale_error();
+    const unsigned blocks = static_cast<unsigned>(std::min<long long>((total + 255) / 256, 32ll * st->num_sms));
+    PoolNhwc g;
+    g.C8 = static_cast<int>(channels / 8);
+    g.H = static_cast<int>(height);
+    g.W = static_cast<int>(width);
+    g.OH = static_cast<int>(output_h);
+    g.OW = static_cast<int>(output_w);
+    g.KH = static_cast<int>(kernel_h);
+    g.KW = static_cast<int>(kernel_w);
+    g.pad_t = static_cast<int>(pad_top);
+    g.pad_l = static_cast<int>(pad_left);
+    g.sh = static_cast<int>(stride_h);
+    g.sw = static_cast<int>(stride_w);
+    g.average = average ? 1 : 0;
+    g.count_include_pad = count_include_pad ? 1 : 0;
+    g.total = total;
+    cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    if (fmt == FMT_F16)
+        pool_nhwc_kernel<OUT_F16><<<blocks, 256, 0, cs>>>(static_cast<const uint4*>(x), static_cast<uint4*>(y), g);
+    else
+        pool_nhwc_kernel<OUT_BF16><<<blocks, 256, 0, cs>>>(static_cast<const uint4*>(x), static_cast<uint4*>(y), g);
+    g_launches.fetch_add(1);
+    CUDA_TRY(cudaGetLastError());
+    return kSuccess;
+}
 
 int dlf_b200_maxpool(int dtype, size_t batches, size_t channels, size_t height, size_t width, size_t output_h,
                      size_t output_w, size_t kernel_h, size_t kernel_w, size_t pad_top, size_t pad_left,

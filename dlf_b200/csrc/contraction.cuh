@@ -415,7 +415,7 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
             mm += row_off;
             const int ncols_t = max(0, min(cols_per, min(BN, p.N - nn) - cbase));
             if (p.out_nchw == 3) {
-                if (c0 + 32 > ncols_t) return false;
+                if (c0 + 32 > ncols_t || mm + q * 32 >= p.M) return false;
                 const int j0 = nn + cbase + c0;
                 const int img = j0 / p.g.P;
                 const int pp = j0 - img * p.g.P;
@@ -427,6 +427,12 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
             }
             const int i0 = mm + q * 32;
             if (i0 >= p.M || c0 >= ncols_t) return false;
+            if (p.out_nchw == 5) {  // channels-last: {channels, pixels}
+                x = nn + cbase + c0;
+                y = i0;
+                z = 0;
+                return true;
+            }
             const int img0 = p.out_nchw == 1 ? i0 / p.g.P : 0;
             const int pp0 = p.out_nchw == 1 ? i0 - img0 * p.g.P : i0;
             if (p.out_nchw == 1 && pp0 + 32 > p.g.P) return false;
@@ -481,7 +487,8 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
                     const int co = m0 + q * 32 + lane;
                     const bool co_ok = co < p.M;
                     const int cb3 = cbase;
-                    const int ncols3 = max(0, min(cols_per, min(BN, p.N - n0) - cb3));
+                    // a quadrant whose 32 channels all lie beyond M (64 output channels on 128 lanes) has nothing to write
+                    const int ncols3 = m0 + q * 32 < p.M ? max(0, min(cols_per, min(BN, p.N - n0) - cb3)) : 0;
                     float bv3 = 0.0f;
                     if (p.bias != nullptr && co_ok)
                         bv3 = p.fmt == FMT_F16 ? out_load<OUT_F16>(p.bias + co * 2) : out_load<OUT_BF16>(p.bias + co * 2);
@@ -595,6 +602,85 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
                         }
 #undef DLF_SWAPPED
 #undef DLF_SWAPPED_FAST
+                    }
+                    ptx::tc_fence_before();
+                    ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));
+                    continue;
+                }
+                if (p.out_nchw == 5) {
+                    // Channels-last output D[pixel][channel]: the lanes are pixels, the columns output
+                    // channels, so a lane's 32 columns are 64 consecutive bytes of D and the warp's
+                    // block is one [32 pixels][32 channels] box of the {channels, pixels} map (clipped
+                    // by the hardware at the last channel and the last pixel). Staging, swizzle,
+                    // residual boxes and the store are those of the swapped NCHW form above.
+                    const int i0 = m0 + q * 32;
+                    const int ncols5 = i0 < p.M ? max(0, min(cols_per, min(BN, p.N - n0) - cbase)) : 0;
+                    const uint32_t trow5 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN + cbase;
+                    const bool relu5 = p.relu != 0;
+                    const uint32_t sw5 = (static_cast<uint32_t>(lane) >> 1) & 3u;
+                    for (int c0 = 0; c0 < ncols5; c0 += 32) {
+                        uint32_t v[32];
+                        ptx::tmem_ld_32x32(trow5 + c0, v);
+                        ptx::tmem_ld_wait();
+                        const int col = n0 + cbase + c0;
+                        float bv = 0.0f;
+                        if (p.bias != nullptr && col + lane < p.N)
+                            bv = p.fmt == FMT_F16 ? out_load<OUT_F16>(p.bias + (col + lane) * 2)
+                                                  : out_load<OUT_BF16>(p.bias + (col + lane) * 2);
+                        const uint32_t half = chunk_no & 1u;
+                        if (chunk_no >= 2) {
+                            if (lane == 0) ptx::bulk_wait_group_read<1>();
+                            __syncwarp();
+                        }
+                        const uint32_t sblk = d_stage + (ewarp * 2 + half) * 2048u;
+                        bool res_smem = false;
+                        if constexpr (RES) {
+                            if (!((res_pending >> half) & 1u)) res_fetch(t, c0, half);
+                            res_smem = res_landed(half);
+                        }
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            float r[8];
+#pragma unroll
+                            for (int g = 0; g < 8; ++g)
+                                r[g] = fmaf(p.alpha, __uint_as_float(v[8 * k + g]), __shfl_sync(0xffffffffu, bv, 8 * k + g));
+                            const uint32_t saddr = sblk + lane * 64u + ((static_cast<uint32_t>(k) ^ sw5) << 4);
+                            if (res_smem) {
+                                const uint4 u = ld_shared_v4(saddr);
+                                const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                                for (int g = 0; g < 4; ++g) {
+                                    const float2 f = p.fmt == FMT_F16
+                                                         ? __half22float2(*reinterpret_cast<const __half2*>(&w[g]))
+                                                         : __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[g]));
+                                    r[2 * g] += f.x;
+                                    r[2 * g + 1] += f.y;
+                                }
+                            }
+                            uint4 o;
+                            uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+                            for (int g = 0; g < 4; ++g) {
+                                const float a = relu5 ? fmaxf(r[2 * g], 0.0f) : r[2 * g];
+                                const float c = relu5 ? fmaxf(r[2 * g + 1], 0.0f) : r[2 * g + 1];
+                                if (p.fmt == FMT_F16) {
+                                    const __half2 h = __floats2half2_rn(a, c);
+                                    ow[g] = *reinterpret_cast<const uint32_t*>(&h);
+                                } else {
+                                    const __nv_bfloat162 h = __floats2bfloat162_rn(a, c);
+                                    ow[g] = *reinterpret_cast<const uint32_t*>(&h);
+                                }
+                            }
+                            st_shared_v4(saddr, o);
+                        }
+                        ptx::fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            ptx::tma_store_3d(&tmD, sblk, col, i0, 0);
+                            ptx::bulk_commit_group();
+                        }
+                        ++chunk_no;
+                        if constexpr (RES) res_ahead(t, c0, ncols5, half ^ 1u);
                     }
                     ptx::tc_fence_before();
                     ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));

@@ -14,6 +14,9 @@
 
 #include <cfloat>
 #include <cstdint>
+#include <type_traits>
+
+#include "epilogue.cuh"
 
 namespace dlfb200 {
 
@@ -351,6 +354,77 @@ __global__ void __launch_bounds__(256) pool_plane_kernel(const PoolParams p) {
             acc = p.mode == 0 ? fmaxf(acc, o) : acc + o;
         }
         if (lane == 0) PoolType<T>::store(p.y, plane, p.mode == 0 ? acc : acc / static_cast<float>(n));
+    }
+}
+
+// Channels-last pooling: x (N, H, W, C), y (N, OH, OW, C), C a multiple of 8. One thread produces 8
+// channels of one output pixel: every tap is one 16-byte load, consecutive threads take consecutive
+// channel groups and then consecutive pixels, so a warp's loads of a tap are contiguous runs. Same
+// arithmetic as the NCHW kernels above: fp32 accumulation in (kh, kw) order, max from the type's
+// lowest value, the average divided by the taps inside the image or by KH * KW. A global pool is the
+// window KH = H, KW = W.
+struct PoolNhwc {
+    int C8, H, W, OH, OW, KH, KW, pad_t, pad_l, sh, sw;
+    int average, count_include_pad;
+    long long total;  // N * OH * OW * C8
+};
+
+template <int OUT>
+__global__ void __launch_bounds__(256) pool_nhwc_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, const PoolNhwc p) {
+    static_assert(OUT == OUT_F16 || OUT == OUT_BF16, "16-bit types");
+    using T = typename std::conditional<OUT == OUT_F16, __half, __nv_bfloat16>::type;
+    for (long long o = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; o < p.total;
+         o += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int cg = static_cast<int>(o % p.C8);
+        long long r = o / p.C8;
+        const int ow = static_cast<int>(r % p.OW);
+        r /= p.OW;
+        const int oh = static_cast<int>(r % p.OH);
+        const long long img = r / p.OH;
+        const int ih0 = oh * p.sh - p.pad_t;
+        const int iw0 = ow * p.sw - p.pad_l;
+        float acc[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = p.average ? 0.0f : PoolType<T>::lowest();
+        int count = 0;
+        for (int kh = 0; kh < p.KH; ++kh) {
+            const int ih = ih0 + kh;
+            if (static_cast<unsigned>(ih) >= static_cast<unsigned>(p.H)) continue;
+            for (int kw = 0; kw < p.KW; ++kw) {
+                const int iw = iw0 + kw;
+                if (static_cast<unsigned>(iw) >= static_cast<unsigned>(p.W)) continue;
+                const uint4 u = x[((img * p.H + ih) * p.W + iw) * p.C8 + cg];
+                const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    float2 f;
+                    if constexpr (OUT == OUT_F16) f = __half22float2(*reinterpret_cast<const __half2*>(&w[g]));
+                    else f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[g]));
+                    acc[2 * g] = p.average ? acc[2 * g] + f.x : fmaxf(acc[2 * g], f.x);
+                    acc[2 * g + 1] = p.average ? acc[2 * g + 1] + f.y : fmaxf(acc[2 * g + 1], f.y);
+                }
+                ++count;
+            }
+        }
+        if (p.average) {
+            if (p.count_include_pad) count = p.KH * p.KW;
+            const float d = static_cast<float>(count);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[e] = acc[e] / d;
+        }
+        uint4 out;
+        uint32_t* ow4 = reinterpret_cast<uint32_t*>(&out);
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            if constexpr (OUT == OUT_F16) {
+                const __half2 h = __floats2half2_rn(acc[2 * g], acc[2 * g + 1]);
+                ow4[g] = *reinterpret_cast<const uint32_t*>(&h);
+            } else {
+                const __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * g], acc[2 * g + 1]);
+                ow4[g] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+        }
+        y[o] = out;
     }
 }
 

@@ -229,3 +229,93 @@ def global_average_pooling(X, Y, queue=None, event=None):
     """dlf::dnn::global_average_pooling for device tensors (dnn.h:361-375)."""
     h, w = int(X.shape[2]), int(X.shape[3])
     average_pooling(X, Y, Filter2D(X.shape, h, w).strides(h, w), False, queue=queue, event=event)
+
+
+# ---------------------------------------------------------------------------------------------
+# Channels-last operators (16-bit, (N, H, W, C) with C a multiple of 8): what an operator-list
+# runtime that owns its intermediate tensors uses between its operators. The reference's operators
+# are NCHW; these compute the same functions on the permuted tensors.
+
+NHWC, NCHW = 0, 1
+
+
+def nhwc_supported(filt, dtype, y_layout=NHWC):
+    """Whether conv2d_nhwc serves this convolution (the limits of the tensor-map unit's im2col mode;
+    the C entry returns kNotImplemented otherwise and launches nothing)."""
+    f = filt
+    return (dtype in (torch.float16, torch.bfloat16) and f.group == 1 and f.channels % 8 == 0 and
+            (y_layout == NCHW or f.num_kernels % 8 == 0) and f.kernel_h <= 16 and f.kernel_w <= 16 and
+            f.pad_top < 128 and f.pad_left < 128 and f.stride_h <= 8 and f.stride_w <= 8 and
+            f.dilation_h * (f.kernel_h - 1) < 256 and f.dilation_w * (f.kernel_w - 1) < 256 and f.batches < 65536 and
+            (f.output_w - 1) * f.stride_w + 1 - f.width - f.pad_left <= 127 and
+            (f.output_h - 1) * f.stride_h + 1 - f.height - f.pad_top <= 127)
+
+
+def pack_filters_nhwc(W, queue=None):
+    """OIHW filter bank -> (Cout, KH*KW, Ck), Ck = C rounded up to 64 (zero-filled): the K-major operand
+    conv2d_nhwc reads."""
+    prec = precision_of(W)
+    co, c, kh, kw = (int(d) for d in W.shape)
+    n = lib().dlf_b200_nhwc_filter_elems(c, co, kh, kw)
+    out = torch.empty(n, dtype=W.dtype, device=W.device)
+    _, sp = _stream(queue)
+    _check(lib().dlf_b200_pack_filters_nhwc(int(prec), c, co, kh, kw, _ptr(W.contiguous()), _ptr(out), sp))
+    return out
+
+
+def nchw_to_nhwc(X, Y=None, queue=None):
+    """(N, C, H, W) -> (N, H, W, C') with C' = C rounded up to 8 (the added channels zero)."""
+    prec = precision_of(X)
+    n, c, h, w = (int(d) for d in X.shape)
+    cp = (c + 7) // 8 * 8
+    if Y is None:
+        Y = torch.empty((n, h, w, cp), dtype=X.dtype, device=X.device)
+    elif Y.numel() < n * h * w * cp or Y.dtype != X.dtype:
+        raise BLASError(StatusCode.kInsufficientMemoryC)
+    _, sp = _stream(queue)
+    _check(lib().dlf_b200_nchw_to_nhwc(int(prec), n, c, h, w, _ptr(X), _ptr(Y), sp))
+    return Y
+
+
+def conv2d_nhwc(X, W_packed, Y, filt, bias=None, residual=None, activation=None, y_layout=NHWC, queue=None):
+    """Y = act(conv2d(X, W) + bias + residual) with X (N, H, W, C), the filter bank as
+    pack_filters_nhwc writes it, and Y / residual in ``y_layout``. One launch, no scratch."""
+    f = filt
+    prec = precision_of(Y)
+    if X.dtype != Y.dtype or W_packed.dtype != Y.dtype or (bias is not None and bias.dtype != Y.dtype) or \
+            (residual is not None and residual.dtype != Y.dtype):
+        raise BLASError(StatusCode.kInvalidValue)
+    if X.numel() < f.batches * f.channels * f.height * f.width:
+        raise BLASError(StatusCode.kInsufficientMemoryA)
+    if W_packed.numel() < lib().dlf_b200_nhwc_filter_elems(f.channels, f.num_kernels, f.kernel_h, f.kernel_w):
+        raise BLASError(StatusCode.kInsufficientMemoryB)
+    n_out = f.batches * f.num_kernels * f.output_h * f.output_w
+    if Y.numel() < n_out or (residual is not None and residual.numel() < n_out):
+        raise BLASError(StatusCode.kInsufficientMemoryC)
+    if activation not in (None, "relu"):
+        raise BLASError(StatusCode.kInvalidValue)
+    _, sp = _stream(queue)
+    null = ctypes.c_void_p(0)
+    _check(lib().dlf_b200_conv2d_nhwc(
+        int(prec), f.batches, f.channels, f.height, f.width, f.output_h, f.output_w, f.num_kernels, f.kernel_h,
+        f.kernel_w, f.pad_top, f.pad_left, f.pad_bottom, f.pad_right, f.stride_h, f.stride_w, f.dilation_h,
+        f.dilation_w, _ptr(X), _ptr(W_packed), _ptr(bias) if bias is not None else null,
+        _ptr(residual) if residual is not None else null, 1 if activation == "relu" else 0, _ptr(Y), int(y_layout), sp))
+
+
+def pool_nhwc(X, Y, filt, average=False, count_include_pad=False, queue=None):
+    """max / average pooling on (N, H, W, C) tensors; ``filt`` is the pooling Filter2D of the NCHW shape."""
+    f = filt
+    prec = precision_of(Y)
+    if f.dilation_h != 1 or f.dilation_w != 1:
+        raise BLASError(StatusCode.kNotImplemented)
+    if X.dtype != Y.dtype:
+        raise BLASError(StatusCode.kInvalidValue)
+    if X.numel() < f.batches * f.channels * f.height * f.width:
+        raise BLASError(StatusCode.kInsufficientMemoryA)
+    if Y.numel() < f.batches * f.channels * f.output_h * f.output_w:
+        raise BLASError(StatusCode.kInsufficientMemoryC)
+    _, sp = _stream(queue)
+    _check(lib().dlf_b200_pool_nhwc(int(prec), 1 if average else 0, 1 if count_include_pad else 0, f.batches, f.channels,
+                                    f.height, f.width, f.output_h, f.output_w, f.kernel_h, f.kernel_w, f.pad_top,
+                                    f.pad_left, f.stride_h, f.stride_w, _ptr(X), _ptr(Y), sp))

@@ -152,6 +152,41 @@ size_t dlf_b200_conv2d_workspace_bytes(int dtype, size_t batches, size_t channel
                                        size_t num_kernels, size_t group, size_t kernel_h,
                                        size_t kernel_w);
 
+/* Channels-last operators for an operator-list runtime (dlf's Predictor, dlf/include/predict.h:
+ * 2048-2070) that owns the tensors between its operators and may therefore keep them in the
+ * layout the tensor-map unit reads: (N, H, W, C), 16-bit, C a multiple of 8, 16-byte aligned.
+ * The reference's own operators are NCHW (gpgpu/include/gdnn.h:201-251); these entries compute
+ * the same functions on the permuted tensors.
+ *
+ * dlf_b200_conv2d_nhwc: Y = act(conv2d(X, W) + bias + residual), one group. X is (N, H, W, C);
+ * `w_packed` is the filter bank as dlf_b200_pack_filters_nhwc writes it - (Cout, KH*KW, Ck), Ck = C
+ * rounded up to 64, dlf_b200_nhwc_filter_elems elements; for a 1x1 filter over a multiple of 64
+ * channels that is the OIHW bank itself. `y_layout` says how Y (and `residual`, which has Y's shape
+ * and layout) is stored: DLF_B200_LAYOUT_NHWC (Cout a multiple of 8) or DLF_B200_LAYOUT_NCHW. The
+ * activations are fetched by im2col-mode tensor-map loads straight from X: no scratch, no copy, one
+ * launch. kNotImplemented (nothing launched) for what the tensor-map unit cannot address: channel
+ * counts that are not a multiple of 8, unaligned bases, pads of 128 or more, strides above 8,
+ * filters above 16 x 16, (k - 1) * dilation of 256 or more.
+ * dlf_b200_nchw_to_nhwc: (N, C, H, W) -> (N, H, W, C') with C' = C rounded up to 8, the added
+ * channels zero. dlf_b200_pool_nhwc: max (average == 0) or average pooling on (N, H, W, C), C a
+ * multiple of 8, with the arithmetic of dlf_b200_maxpool / dlf_b200_avgpool; a global pool is the
+ * window kernel = (H, W). */
+#define DLF_B200_LAYOUT_NHWC 0
+#define DLF_B200_LAYOUT_NCHW 1
+size_t dlf_b200_nhwc_filter_elems(size_t channels, size_t num_kernels, size_t kernel_h, size_t kernel_w);
+int dlf_b200_pack_filters_nhwc(int dtype, size_t channels, size_t num_kernels, size_t kernel_h, size_t kernel_w,
+                               const void* w, void* w_packed, void* stream);
+int dlf_b200_nchw_to_nhwc(int dtype, size_t batches, size_t channels, size_t height, size_t width, const void* x,
+                          void* y, void* stream);
+int dlf_b200_conv2d_nhwc(int dtype, size_t batches, size_t channels, size_t height, size_t width, size_t output_h,
+                         size_t output_w, size_t num_kernels, size_t kernel_h, size_t kernel_w, size_t pad_top,
+                         size_t pad_left, size_t pad_bottom, size_t pad_right, size_t stride_h, size_t stride_w,
+                         size_t dilation_h, size_t dilation_w, const void* x, const void* w_packed, const void* bias,
+                         const void* residual, int activation, void* y, int y_layout, void* stream);
+int dlf_b200_pool_nhwc(int dtype, int average, int count_include_pad, size_t batches, size_t channels, size_t height,
+                       size_t width, size_t output_h, size_t output_w, size_t kernel_h, size_t kernel_w, size_t pad_top,
+                       size_t pad_left, size_t stride_h, size_t stride_w, const void* x, void* y, void* stream);
+
 /* Level-3 routines that run on the GEMM main loop. Each replaces the gpgpu::blas template of the
  * same name (gpgpu/include/gblas.h:506-586; instantiations gpgpu/src/gblas.cpp; the OpenCL
  * routines expand the symmetric / triangular operand into a general square and call Xgemm, which
