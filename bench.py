@@ -690,39 +690,51 @@ def oracle_forward(graph, image, rnd):
 
 def resnet_forward(device, peaks, batch, reps):
     """A whole ResNet-50 v1 forward (fp16, 224x224) as an operator list of this library
-    (dlf_b200.predict): 53 fused convolutions, max pool, global average pool, the FC Gemm - timed
-    launch by launch and as a CUDA-graph replay. The logits of one image are compared with the
-    oracle evaluating the same operator list on the CPU (relative Frobenius error)."""
+    (dlf_b200.predict): 53 fused convolutions, max pool, global average pool, the FC Gemm - with the
+    tensors between the operators kept channels-last (the default) and with every tensor NCHW as the
+    reference's operators have them, each timed launch by launch and as a CUDA-graph replay. The
+    logits of one image are compared with the oracle evaluating the same operator list on the CPU
+    (relative Frobenius error)."""
     from dlf_b200 import predict as P
-    pred = P.Predictor(resnet50_graph(batch), dtype=torch.float16, device=device, cuda_graph=False)
-    g = torch.Generator(device=device).manual_seed(7)
-    pred.input(0).copy_(torch.randn(pred.input(0).shape, generator=g, device=device).half())
     flops = sum(2.0 * batch * co * (h // s) ** 2 * ci * k * k * cnt for ci, h, co, k, s, _, cnt in RESNET50_SHAPES)
     flops += 2.0 * batch * 1000 * 2048
-    step = lambda i: pred.predict()
-    ms_stream, _, _ = time_steps(step, reps, 3, 1)
-    out = {"batch": batch, "dtype": "f16", "operators": len(pred.operators), "launching_operators": pred.launches_per_predict(),
-           "stream_launches": {"ms_per_forward": round(ms_stream / reps, 3),
-                               "images_per_s": round(batch * reps / (ms_stream / 1e3), 1)}}
-    pred._want_graph = True  # the next predict() captures the list, later ones replay it
-    pred.predict()
-    if pred._cuda_graph is not None:
-        ms_graph, _, _ = time_steps(step, reps, 3, 1)
-        sec = ms_graph / 1e3 / reps
-        out["cuda_graph_replay"] = {"ms_per_forward": round(sec * 1e3, 3), "images_per_s": round(batch / sec, 1),
-                                    "tflops": round(flops / sec / 1e12, 1),
-                                    "frac_of_measured_tensor_peak": round(flops / sec / 1e12 / peaks["bf16_tflops"], 4)}
-    # parity of the whole chain on one image: a batch-1 predictor with the same weights
-    small = P.Predictor(resnet50_graph(1), dtype=torch.float16, device=device, cuda_graph=False)
-    image = pred.input(0)[:1].float().cpu().numpy()
-    small.set(0, image)
-    small.predict()
+    out = {"batch": batch, "dtype": "f16"}
     rnd = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).half().float().numpy()
-    want = oracle_forward(small.graph, image, rnd)
-    got = small.get(0)
-    out["logits_rel_fro_err_vs_oracle"] = float("%.3g" % (np.linalg.norm(got - want) / np.linalg.norm(want)))
-    out["logits_batch_vs_single_image_max_abs_diff"] = float(
-        "%.3g" % np.abs(pred.output(0)[:1].float().cpu().numpy() - got).max())
+    g = torch.Generator(device=device).manual_seed(7)
+    images = torch.randn((batch, 3, 224, 224), generator=g, device=device).half()
+    want = None
+    for key, channels_last in (("nchw", False), ("channels_last", True)):
+        pred = P.Predictor(resnet50_graph(batch), dtype=torch.float16, device=device, cuda_graph=False,
+                           channels_last=channels_last)
+        pred.input(0).copy_(images)
+        step = lambda i: pred.predict()
+        ms_stream, _, _ = time_steps(step, reps, 3, 1)
+        row = {"operators": len(pred.operators), "launching_operators": pred.launches_per_predict(),
+               "stream_launches": {"ms_per_forward": round(ms_stream / reps, 3),
+                                   "images_per_s": round(batch * reps / (ms_stream / 1e3), 1)}}
+        pred._want_graph = True  # the next predict() captures the list, later ones replay it
+        pred.predict()
+        if pred._cuda_graph is not None:
+            ms_graph, _, _ = time_steps(step, reps, 3, 1)
+            sec = ms_graph / 1e3 / reps
+            row["cuda_graph_replay"] = {"ms_per_forward": round(sec * 1e3, 3), "images_per_s": round(batch / sec, 1),
+                                        "tflops": round(flops / sec / 1e12, 1),
+                                        "frac_of_measured_tensor_peak": round(flops / sec / 1e12 / peaks["bf16_tflops"], 4)}
+        # parity of the whole chain on one image: a batch-1 predictor with the same weights
+        small = P.Predictor(resnet50_graph(1), dtype=torch.float16, device=device, cuda_graph=False,
+                            channels_last=channels_last)
+        image = images[:1].float().cpu().numpy()
+        small.set(0, image)
+        small.predict()
+        if want is None:
+            want = oracle_forward(small.graph, image, rnd)
+        got = small.get(0)
+        row["logits_rel_fro_err_vs_oracle"] = float("%.3g" % (np.linalg.norm(got - want) / np.linalg.norm(want)))
+        row["logits_batch_vs_single_image_max_abs_diff"] = float(
+            "%.3g" % np.abs(pred.output(0)[:1].float().cpu().numpy() - got).max())
+        out[key] = row
+        del pred, small
+        torch.cuda.empty_cache()
     return out
 
 

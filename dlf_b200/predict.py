@@ -532,6 +532,39 @@ class GlobalPoolOp(Operator):
         (gdnn.global_average_pooling if self.average else gdnn.global_max_pooling)(self.X, self.Y)
 
 
+class NhwcConvOp(Operator):
+    """A convolution between channels-last tensors: X (N, H, W, C), the filter bank packed once when
+    the predictor is built, Y (and the residual) channels-last or NCHW. One launch, no scratch."""
+
+    def __init__(self, X, Wp, B, Y, filt, residual, relu, y_layout):
+        self.X, self.Wp, self.B, self.Y, self.filter = X, Wp, B, Y, filt
+        self.residual, self.relu, self.y_layout = residual, relu, y_layout
+
+    def evaluate(self):
+        gdnn.conv2d_nhwc(self.X, self.Wp, self.Y, self.filter, bias=self.B, residual=self.residual,
+                         activation="relu" if self.relu else None, y_layout=self.y_layout)
+
+
+class NhwcPoolOp(Operator):
+    """Max / average / global pooling between channels-last tensors."""
+
+    def __init__(self, X, Y, filt, average, count_include_pad):
+        self.X, self.Y, self.filter, self.average, self.count_include_pad = X, Y, filt, average, count_include_pad
+
+    def evaluate(self):
+        gdnn.pool_nhwc(self.X, self.Y, self.filter, average=self.average, count_include_pad=self.count_include_pad)
+
+
+class ToNhwcOp(Operator):
+    """The transposing copy that brings an NCHW value into the channels-last part of the list."""
+
+    def __init__(self, X, Y):
+        self.X, self.Y = X, Y
+
+    def evaluate(self):
+        gdnn.nchw_to_nhwc(self.X, self.Y)
+
+
 class ViewOp(Operator):
     """Flatten / Reshape: the output shares the input's storage (the reference's ReshapeOp aliases
     its datum the same way), so there is nothing to launch."""
@@ -553,9 +586,16 @@ class Predictor:
 
     ``dtype`` is T: every floating-point value of the graph is held in it. With ``cuda_graph``
     (the default) the second ``predict()`` captures the operator list into a CUDA graph and replays
-    it from then on; the first one runs the launches one by one, which also loads the kernels."""
+    it from then on; the first one runs the launches one by one, which also loads the kernels.
 
-    def __init__(self, graph, dtype=torch.float32, device=None, cuda_graph=True):
+    ``channels_last`` (16-bit T only): the predictor owns the tensors between its operators, so it
+    keeps those that only convolutions and poolings read as (N, H, W, C) - the layout the tensor-map
+    unit fetches filter windows from - and runs those operators through the channels-last entries:
+    no transposing copy in front of a convolution, TMA-fed operands and TMA stores whatever the
+    plane size. Graph inputs and outputs stay NCHW; a copy is inserted where an NCHW value enters the
+    channels-last part."""
+
+    def __init__(self, graph, dtype=torch.float32, device=None, cuda_graph=True, channels_last=True):
         if dtype not in _TORCH_TYPES:
             raise TypeError("Predictor: T must be float32, float16 or bfloat16")
         self.dtype = dtype
@@ -569,7 +609,15 @@ class Predictor:
         self.graph = graph
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self._data = {}
-        self.operators = [self._create(n) for n in graph.nodes]
+        self._nhwc_copy = {}
+        self._pre_ops = []
+        self._nhwc = self._assign_layouts(graph) if channels_last and dtype != torch.float32 else set()
+        self.operators = []
+        for n in graph.nodes:
+            op = self._create(n)
+            self.operators.extend(self._pre_ops)
+            self._pre_ops = []
+            self.operators.append(op)
         self._inputs = [self._alloc(v) for v in graph.inputs if not v.has_initializer()]
         self._outputs = [self._alloc(v) for v in graph.outputs]
         need = max([op.scratch_bytes() for op in self.operators] + [0])
@@ -577,6 +625,76 @@ class Predictor:
         self._want_graph = bool(cuda_graph)
         self._cuda_graph = None
         self._warm = False
+
+    # -- layouts --------------------------------------------------------------------------
+
+    _POOLS = ("MaxPool", "AveragePool")
+    _GLOBAL_POOLS = ("GlobalAveragePool", "GlobalMaxPool")
+
+    def _native(self, n):
+        """A convolution the channels-last entry serves (weights known when the list is built)."""
+        return (n.kind == "Conv" and n.input(1).has_initializer() and
+                (n.input(2) is None or n.input(2).has_initializer()) and
+                gdnn.nhwc_supported(_conv_filter(n, n.input(0).dims, n.input(1).dims), self.dtype, gdnn.NCHW))
+
+    def _assign_layouts(self, graph):
+        """ids of the values kept channels-last. Optimistic start: every output of a convolution the
+        channels-last entry serves (a multiple of 8 output channels) and of a windowed pooling over
+        such a value; then values are taken back until nothing contradicts: a graph output, a value
+        read by an operator that needs NCHW, a residual whose convolution writes NCHW, a pooling
+        whose input is NCHW."""
+        native = {id(n): self._native(n) for n in graph.nodes if n.kind == "Conv"}
+        cand = set()
+        for n in graph.nodes:
+            out = n.output(0)
+            if out.dims is None or len(out.dims) != 4 or out.dims[1] % 8:
+                continue
+            if (n.kind == "Conv" and native[id(n)]) or n.kind in self._POOLS:
+                cand.add(id(out))
+        outputs = {id(v) for v in graph.outputs}
+        changed = True
+        while changed:
+            changed = False
+            for n in graph.nodes:
+                out = n.output(0)
+                if id(out) not in cand:
+                    continue
+                drop = id(out) in outputs or (n.kind in self._POOLS and id(n.input(0)) not in cand)
+                for c in graph.nodes:
+                    if drop:
+                        break
+                    reads = any(v is out for v in c.inputs)
+                    as_residual = c.attrs.get("residual") is out
+                    if not reads and not as_residual:
+                        continue
+                    if c.kind == "Conv":
+                        drop = (c.input(0) is out and not native[id(c)]) or \
+                               (as_residual and id(c.output(0)) not in cand) or \
+                               any(v is out for v in c.inputs[1:])
+                    elif c.kind in self._POOLS:
+                        drop = id(c.output(0)) not in cand
+                    elif c.kind in self._GLOBAL_POOLS:
+                        drop = False
+                    else:
+                        drop = True
+                if drop:
+                    cand.discard(id(out))
+                    changed = True
+        return cand
+
+    def _as_nhwc(self, value):
+        """The channels-last tensor of a 4-D value: its own storage, or a copy made by an inserted
+        operator (once per value)."""
+        t = self._alloc(value)
+        if id(value) in self._nhwc:
+            return t
+        c = self._nhwc_copy.get(id(value))
+        if c is None:
+            n, ch, h, w = value.dims
+            c = torch.zeros((n, h, w, (ch + 7) // 8 * 8), dtype=self.dtype, device=self.device)
+            self._nhwc_copy[id(value)] = c
+            self._pre_ops.append(ToNhwcOp(t, c))
+        return c
 
     # -- datums ---------------------------------------------------------------------------
 
@@ -594,6 +712,9 @@ class Predictor:
                                      value.dtype == DataType.DOUBLE else np.float32))).to(self.dtype).to(self.device)
             elif like is not None:
                 t = like.view(value.dims)
+            elif id(value) in self._nhwc:
+                n, ch, h, w = value.dims
+                t = torch.zeros((n, h, w, ch), dtype=self.dtype, device=self.device)
             else:
                 t = torch.zeros(value.dims, dtype=self.dtype, device=self.device)
             self._data[id(value)] = t
@@ -603,6 +724,23 @@ class Predictor:
 
     def _create(self, n):
         k = n.kind
+        if k == "Conv" and self._nhwc is not None and (id(n.output(0)) in self._nhwc or
+                                                        (id(n.input(0)) in self._nhwc and self._native(n))):
+            filt = _conv_filter(n, n.input(0).dims, n.input(1).dims)
+            X = self._as_nhwc(n.input(0))
+            Wp = gdnn.pack_filters_nhwc(self._alloc(n.input(1)))
+            nhwc_out = id(n.output(0)) in self._nhwc
+            res = n.get("residual")
+            R = None if res is None else (self._as_nhwc(res) if nhwc_out else self._alloc(res))
+            return NhwcConvOp(X, Wp, self._alloc(n.input(2)), self._alloc(n.output(0)), filt, R, bool(n.get("relu")),
+                              gdnn.NHWC if nhwc_out else gdnn.NCHW)
+        if k in self._POOLS and id(n.output(0)) in self._nhwc:
+            return NhwcPoolOp(self._alloc(n.input(0)), self._alloc(n.output(0)), _pool_filter(n, n.input(0).dims),
+                              k == "AveragePool", bool(n.get("count_include_pad", 0)))
+        if k in self._GLOBAL_POOLS and id(n.input(0)) in self._nhwc:
+            d = n.input(0).dims
+            return NhwcPoolOp(self._alloc(n.input(0)), self._alloc(n.output(0)),
+                              gdnn.Filter2D(d, d[2], d[3]).strides(d[2], d[3]), k == "GlobalAveragePool", False)
         if k == "Conv":
             X, W = self._alloc(n.input(0)), self._alloc(n.input(1))
             B = self._alloc(n.input(2))

@@ -279,15 +279,23 @@ def _round_fn(dtype):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16], ids=["f32", "f16", "bf16"])
-def test_small_residual_network_against_the_oracle(device_lib, dtype):
+@pytest.mark.parametrize("dtype,channels_last", [(torch.float32, False), (torch.float16, False), (torch.float16, True),
+                                                 (torch.bfloat16, False), (torch.bfloat16, True)],
+                         ids=["f32", "f16-nchw", "f16-channels-last", "bf16-nchw", "bf16-channels-last"])
+def test_small_residual_network_against_the_oracle(device_lib, dtype, channels_last):
     """Every predict() - the first launch by launch, the second captured into a CUDA graph, the
     later ones replays - on fresh inputs against the unoptimized graph evaluated node by node on
     the CPU. Eleven operators launch work (Flatten does not)."""
     rng = np.random.default_rng(11)
     reference_graph = small_resnet(3, 40, np.random.default_rng(5))
-    pred = P.Predictor(small_resnet(3, 40, np.random.default_rng(5)), dtype=dtype)
-    assert pred.launches_per_predict() == 11
+    pred = P.Predictor(small_resnet(3, 40, np.random.default_rng(5)), dtype=dtype, channels_last=channels_last)
+    kinds = [type(op).__name__ for op in pred.operators]
+    if channels_last:
+        # the stem (3 channels) and its pool stay NCHW, one copy brings the pool's output into the
+        # channels-last part, the last block writes NCHW again (its output is a graph output)
+        assert kinds.count("ToNhwcOp") >= 1 and kinds.count("NhwcConvOp") >= 4 and kinds.count("NhwcPoolOp") == 0
+    else:
+        assert pred.launches_per_predict() == 11 and "NhwcConvOp" not in kinds
     rnd = _round_fn(dtype)
     deltas = []
     for step in range(4):
@@ -309,7 +317,7 @@ def test_small_residual_network_against_the_oracle(device_lib, dtype):
                 assert rel_fro(a, b) <= (4e-3 if dtype == torch.float16 else 3e-2)
     # kernel launches of the library: at least one per operator launch by launch, the same number
     # again while the list is captured, none when the graph is replayed
-    assert deltas[0] >= 11 and deltas[1] == deltas[0] and deltas[2] == 0 and deltas[3] == 0
+    assert deltas[0] >= pred.launches_per_predict() and deltas[1] == deltas[0] and deltas[2] == 0 and deltas[3] == 0
 
 
 @pytest.mark.gpu
@@ -335,14 +343,20 @@ def test_graph_replay_equals_launch_by_launch(device_lib):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("dtype", [torch.float32, torch.float16], ids=["f32", "f16"])
-def test_resnet50_operator_list_against_the_oracle(device_lib, dtype):
+@pytest.mark.parametrize("dtype,channels_last", [(torch.float32, False), (torch.float16, False), (torch.float16, True)],
+                         ids=["f32", "f16-nchw", "f16-channels-last"])
+def test_resnet50_operator_list_against_the_oracle(device_lib, dtype, channels_last):
     """All 53 convolutions of ResNet-50 v1 chained with their residual connections, the pools and
     the FC layer, at 64x64 so that the CPU evaluation takes seconds: launch by launch, captured
     and replayed, against the unoptimized graph on the CPU."""
     from bench import resnet50_graph
-    pred = P.Predictor(resnet50_graph(2, size=64, classes=100, seed=3), dtype=dtype)
-    assert pred.launches_per_predict() == 56
+    pred = P.Predictor(resnet50_graph(2, size=64, classes=100, seed=3), dtype=dtype, channels_last=channels_last)
+    kinds = [type(op).__name__ for op in pred.operators]
+    if channels_last:
+        # everything after the stem's pool is channels-last: 52 convolutions and the global pool, one copy
+        assert kinds.count("NhwcConvOp") == 52 and kinds.count("ToNhwcOp") == 1 and kinds.count("NhwcPoolOp") == 1
+    else:
+        assert pred.launches_per_predict() == 56
     reference_graph = resnet50_graph(2, size=64, classes=100, seed=3)
     rnd = _round_fn(dtype)
     rng = np.random.default_rng(8)
