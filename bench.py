@@ -688,7 +688,7 @@ def oracle_forward(graph, image, rnd):
     return env[id(graph.outputs[0])]
 
 
-def resnet_forward(device, peaks, batch, reps):
+def resnet_forward(device, peaks, batch, reps, layouts="both"):
     """A whole ResNet-50 v1 forward (fp16, 224x224) as an operator list of this library
     (dlf_b200.predict): 53 fused convolutions, max pool, global average pool, the FC Gemm - with the
     tensors between the operators kept channels-last (the default) and with every tensor NCHW as the
@@ -704,6 +704,8 @@ def resnet_forward(device, peaks, batch, reps):
     images = torch.randn((batch, 3, 224, 224), generator=g, device=device).half()
     want = None
     for key, channels_last in (("nchw", False), ("channels_last", True)):
+        if layouts != "both" and layouts != key:
+            continue
         pred = P.Predictor(resnet50_graph(batch), dtype=torch.float16, device=device, cuda_graph=False,
                            channels_last=channels_last)
         pred.input(0).copy_(images)
@@ -865,6 +867,8 @@ def main():
     ap.add_argument("--batch", type=int, default=None, help="images per GPU for conv_c2 (profiling: a small case)")
     ap.add_argument("--shape", default="64,56,64,3,1,1", help="--workload conv: Cin,H,Cout,k,stride,pad")
     ap.add_argument("--dtype", default="f16", help="--workload conv: f16, bf16 or f32")
+    ap.add_argument("--layout", default="both", choices=["both", "nchw", "channels_last"],
+                    help="--workload resnet_forward: which tensor layout between the operators to run")
     ap.add_argument("--residual", action="store_true", help="--workload conv: fuse a residual Add and ReLU")
     ap.add_argument("--tuning", type=lambda x: int(x, 0), default=0,
                     help="experiments: second argument of dlf_b200_set_tuning for the whole run")
@@ -925,7 +929,7 @@ def main():
         return
     if args.workload == "resnet_forward":  # the whole network as an operator list
         print(json.dumps({"resnet50_v1_forward_f16": resnet_forward(device, peaks, args.batch or 256,
-                                                                   steps if args.steps is not None else 10),
+                                                                   steps if args.steps is not None else 10, args.layout),
                           "device_status": dlf_b200.device_status()}), flush=True)
         return
     if args.workload == "resnet_sweep":  # development aid: config 3 alone, per layer

@@ -418,10 +418,10 @@ bool encode_output_map(const DeviceState& st, CUtensorMap* map, const Problem& q
         const long long images = q.batch > 1 ? q.batch : q.N / P;
         cuuint64_t dims[3] = {static_cast<cuuint64_t>(P), static_cast<cuuint64_t>(q.M), static_cast<cuuint64_t>(images)};
         cuuint64_t strides[2] = {static_cast<cuuint64_t>(P * q.es), static_cast<cuuint64_t>(P * q.M * q.es)};
-        cuuint32_t box[3] = {32, 32, 1};
+        cuuint32_t box[3] = {box_cols, 32, 1};
         cuuint32_t estr[3] = {1, 1, 1};
         CUresult r = st.encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, q.d, dims, strides, box, estr,
-                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, box_cols == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
                                CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         return r == CUDA_SUCCESS;
     }
@@ -433,10 +433,10 @@ bool encode_output_map(const DeviceState& st, CUtensorMap* map, const Problem& q
         if (!ok) return false;
         cuuint64_t dims[3] = {static_cast<cuuint64_t>(q.N), static_cast<cuuint64_t>(q.M), 1};
         cuuint64_t strides[2] = {static_cast<cuuint64_t>(q.N * q.es), static_cast<cuuint64_t>(q.N * q.M * q.es)};
-        cuuint32_t box[3] = {32, 32, 1};
+        cuuint32_t box[3] = {box_cols, 32, 1};
         cuuint32_t estr[3] = {1, 1, 1};
         CUresult r = st.encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, q.d, dims, strides, box, estr,
-                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, box_cols == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
                                CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         return r == CUDA_SUCCESS;
     }
@@ -941,8 +941,15 @@ int launch(const Problem& q, cudaStream_t stream, DeviceState* preset = nullptr)
         if (rc != kSuccess) return rc;
         // 64-column boxes need 64 columns per epilogue warp
         // (a residual is fetched box by box into single staging blocks: 32-column boxes then)
+        // (the forms that prefetch a residual box a block ahead need the two single staging blocks:
+        // 32-column boxes; the swapped NCHW form fetches it into the wide box itself. Measured at batch
+        // 256: 64 -> 256 at 56x56 120 -> 92 us, with a residual 220 -> 185 us; 128 -> 512 at 28x28 with
+        // a residual 135 -> 105 us. The channels-last form loses with wide boxes - 105 -> 130 us and
+        // 197 -> 228 us on the same layer - and keeps the double-buffered 32-column ones.)
+        const bool boxes_are_rows = q.out_nchw == 3;
         const unsigned box_cols = (esets == 2 ? bn >= 128 : (esets == 4 && bn >= 256)) && !(g_force_generic.load() & 0x100) &&
-                                          q.resid == nullptr ? 64 : 32;
+                                          (q.resid == nullptr || boxes_are_rows) && q.out_nchw != 5 &&
+                                          !(boxes_are_rows && ((g_force_bn.load() >> 16) & 2048)) ? 64 : 32;
         p.d_tma = (!q.d_f32 && encode_output_map(*st, &tm_d, q, box_cols)) ? static_cast<int>(box_cols) : 0;
         if (q.out_nchw == 5 && !p.d_tma) return kNotImplemented;  // the channels-last form only leaves through TMA stores
         // the residual tensor is laid out like D: the same boxes of it, fetched by TMA loads

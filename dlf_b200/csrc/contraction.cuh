@@ -467,6 +467,92 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
             if (c0 + 32 < ncols_t) res_fetch(tt, c0 + 32, h);
             else res_fetch(tt + tile_step, 0, h);
         };
+        // A block of 64 accumulator columns of this warp's 32 rows as ONE box of 64 x 32 elements (4 KB,
+        // rows of 128 bytes, 128-byte swizzle) - p.d_tma == 64 in the forms whose boxes are [row][column]
+        // images of the accumulator (out_nchw 3 and 5). TMA copies cost the SM's copy unit ~150 clocks
+        // apiece whatever their size, and a layer that writes 411 MB in 2 KB boxes (plus as many residual
+        // boxes) is bound by exactly that (64 -> 256 at 56x56: 102 us, 210 us with a residual; the bytes
+        // alone would take 80 and 140). The warp's two 2 KB staging blocks form the one 4 KB block, so
+        // there is no second buffer: the block's previous store must have read it before it is refilled,
+        // and the residual box is fetched into it at the start of the block rather than a block ahead.
+        // `trow`: tensor-memory address of column 0; (x, y, z): box coordinates; bias: per lane (`brow`)
+        // or per column (`bias_cols` != null: entry of column 0). Warp-uniform arguments throughout.
+        auto wide_block = [&](uint32_t trow, int x, int y, int z, int ncols_valid, float brow, const char* bias_cols,
+                              int cols_left_in_tensor, bool relu_on) {
+            if (chunk_no >= 1) {
+                if (lane == 0) ptx::bulk_wait_group_read<0>();
+                __syncwarp();
+            }
+            const uint32_t sblk = d_stage + ewarp * 4096u;
+            bool res_smem = false;
+            if constexpr (RES) {
+                if (lane == 0) {
+                    const uint32_t bar = ptx::smem_u32(&res_bar[RES ? ewarp : 0][0]);
+                    ptx::mbar_arrive_expect_tx(bar, 4096u);
+                    ptx::tma_load_3d(sblk, &tmR, bar, x, y, z);
+                }
+                res_pending |= 1u;
+            }
+            const uint32_t srow = sblk + lane * 128u;
+            const uint32_t sx = static_cast<uint32_t>(lane) & 7u;
+#pragma unroll 1
+            for (int h = 0; h < 2; ++h) {
+                if (32 * h >= ncols_valid) break;
+                uint32_t v[32];
+                ptx::tmem_ld_32x32(trow + 32 * h, v);
+                ptx::tmem_ld_wait();
+                float bcol = 0.0f;
+                if (bias_cols != nullptr && 32 * h + lane < cols_left_in_tensor)
+                    bcol = p.fmt == FMT_F16 ? out_load<OUT_F16>(bias_cols + (32 * h + lane) * 2)
+                                            : out_load<OUT_BF16>(bias_cols + (32 * h + lane) * 2);
+                if constexpr (RES) {
+                    if (h == 0) res_smem = res_landed(0u);
+                }
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    float r[8];
+#pragma unroll
+                    for (int g = 0; g < 8; ++g)
+                        r[g] = fmaf(p.alpha, __uint_as_float(v[8 * k + g]),
+                                    bias_cols != nullptr ? __shfl_sync(0xffffffffu, bcol, 8 * k + g) : brow);
+                    const uint32_t saddr = srow + ((static_cast<uint32_t>(4 * h + k) ^ sx) << 4);
+                    if (res_smem) {
+                        const uint4 u = ld_shared_v4(saddr);
+                        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) {
+                            const float2 f = p.fmt == FMT_F16
+                                                 ? __half22float2(*reinterpret_cast<const __half2*>(&w[g]))
+                                                 : __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[g]));
+                            r[2 * g] += f.x;
+                            r[2 * g + 1] += f.y;
+                        }
+                    }
+                    uint4 o;
+                    uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        const float a = relu_on ? fmaxf(r[2 * g], 0.0f) : r[2 * g];
+                        const float c = relu_on ? fmaxf(r[2 * g + 1], 0.0f) : r[2 * g + 1];
+                        if (p.fmt == FMT_F16) {
+                            const __half2 hh = __floats2half2_rn(a, c);
+                            ow[g] = *reinterpret_cast<const uint32_t*>(&hh);
+                        } else {
+                            const __nv_bfloat162 hh = __floats2bfloat162_rn(a, c);
+                            ow[g] = *reinterpret_cast<const uint32_t*>(&hh);
+                        }
+                    }
+                    st_shared_v4(saddr, o);
+                }
+            }
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                ptx::tma_store_3d(&tmD, sblk, x, y, z);
+                ptx::bulk_commit_group();
+            }
+            ++chunk_no;
+        };
         DLF_CLK_DECL(warp == 0 && lane == 0)
         for (int t = tile0; t < p.total_tiles; t += tile_step, ++it) {
             int b, m0, n0;
@@ -497,16 +583,22 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
                     const long long boff3 = static_cast<long long>(b) * p.d_batch_stride * 2;  // batched form: one image per batch entry
                     const bool relu3 = p.relu != 0;
                     for (int c0 = 0; c0 < ncols3; c0 += 32) {
+                        const int j0 = n0 + cb3 + c0;
+                        const int img = j0 / p.g.P;
+                        const int pp = j0 - img * p.g.P;
+                        const int nc = min(32, ncols3 - c0);
+                        if (p.d_tma == 64 && (c0 & 63) == 0 && ncols3 - c0 >= 64 && (pp + 64 <= p.g.P || p.batch > 1)) {
+                            // 64 pixels x 32 channels in one box (clipped at the plane's end in the batched form)
+                            wide_block(trow3 + c0, pp, m0 + q * 32, p.batch > 1 ? b : img, 64, bv3, nullptr, 0, relu3);
+                            c0 += 32;
+                            continue;
+                        }
                         uint32_t v[32];
                         DLF_CLK_ADD(1);
                         ptx::tmem_ld_32x32(trow3 + c0, v);
                         ptx::tmem_ld_wait();
                         DLF_CLK_ADD(12);  // accumulator columns in registers
-                        const int j0 = n0 + cb3 + c0;
-                        const int img = j0 / p.g.P;
-                        const int pp = j0 - img * p.g.P;
-                        const int nc = min(32, ncols3 - c0);
-                        if (p.d_tma && nc == 32 && (pp + 32 <= p.g.P || p.batch > 1)) {
+                        if (p.d_tma == 32 && nc == 32 && (pp + 32 <= p.g.P || p.batch > 1)) {
                             // the warp's 32 channels x 32 pixels are one box of the {pixels, channels,
                             // images} map: each lane lays its 32 pixels (64 bytes) into the staging
                             // block, which is then the box's own [channel][pixel] image. In the batched
@@ -619,6 +711,14 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
                     const bool relu5 = p.relu != 0;
                     const uint32_t sw5 = (static_cast<uint32_t>(lane) >> 1) & 3u;
                     for (int c0 = 0; c0 < ncols5; c0 += 32) {
+                        if (p.d_tma == 64) {
+                            // 64 channels x 32 pixels in one box (clipped at the last channel and pixel)
+                            const int colw = n0 + cbase + c0;
+                            wide_block(trow5 + c0, colw, i0, 0, ncols5 - c0, 0.0f, p.bias ? p.bias + colw * 2 : nullptr,
+                                       p.N - colw, relu5);
+                            c0 += 32;
+                            continue;
+                        }
                         uint32_t v[32];
                         ptx::tmem_ld_32x32(trow5 + c0, v);
                         ptx::tmem_ld_wait();
