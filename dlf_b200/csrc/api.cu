@@ -306,6 +306,7 @@ struct Problem {
     const float* betas = nullptr;
     const char* bias = nullptr;
     long long bias_stride = 0;
+    int bias_rows = 0;  // bias per row of D (channels-last convolution with the filter bank as operand A)
     const char* resid = nullptr;
     int relu = 0;
     Im2colGeom g{};
@@ -865,7 +866,7 @@ int launch(const Problem& q, cudaStream_t stream, DeviceState* preset = nullptr)
     const long long num_kb_l = (q.K + 63) / 64;
     const bool paired_plain = q.out_nchw == 1 && q.g.P % 2 == 0 && q.g.P % 8 != 0;
     const long long out_ch = q.cl_swap ? q.M : q.N;
-    const bool four_sets = use_tma && q.out_nchw != 0 && num_kb_l <= 8 && q.K <= 2 * out_ch && bn >= 128 && !paired_plain &&
+    const bool four_sets = use_tma && (q.out_nchw != 0 || q.bias_rows) && num_kb_l <= 8 && q.K <= 2 * out_ch && bn >= 128 && !paired_plain &&
                            !((g_force_bn.load() >> 16) & 32);
     // Three sets (448 threads, 128 registers, no spills) for the widening pixel-per-lane layers the
     // four-set form leaves out (256 -> 1024 at 14x14: 77 -> 73 us; 1024 -> 2048 stride 2: 110 -> 98 us;
@@ -907,6 +908,7 @@ int launch(const Problem& q, cudaStream_t stream, DeviceState* preset = nullptr)
     p.betas = q.betas;
     p.bias = q.bias;
     p.bias_stride = q.bias_stride;
+    p.bias_rows = q.bias_rows;
     p.resid = q.resid;
     p.relu = q.relu;
     p.g = q.g;
@@ -951,14 +953,14 @@ int launch(const Problem& q, cudaStream_t stream, DeviceState* preset = nullptr)
                                           (q.resid == nullptr || boxes_are_rows) && q.out_nchw != 5 &&
                                           !(boxes_are_rows && ((g_force_bn.load() >> 16) & 2048)) ? 64 : 32;
         p.d_tma = (!q.d_f32 && encode_output_map(*st, &tm_d, q, box_cols)) ? static_cast<int>(box_cols) : 0;
-        if (q.out_nchw == 5 && !p.d_tma) return kNotImplemented;  // the channels-last form only leaves through TMA stores
+        if ((q.out_nchw == 5 || q.bias_rows) && !p.d_tma) return kNotImplemented;  // the channels-last forms only leave through TMA stores
         // the residual tensor is laid out like D: the same boxes of it, fetched by TMA loads
         if (p.d_tma && q.resid != nullptr && (reinterpret_cast<uintptr_t>(q.resid) & 15u) == 0 && !((g_force_bn.load() >> 16) & 512)) {
             Problem qr = q;
             qr.d = const_cast<char*>(q.resid);
             p.r_tma = encode_output_map(*st, &tm_r, qr, box_cols) ? 1 : 0;
         }
-        if (q.out_nchw == 5 && q.resid != nullptr && !p.r_tma) return kNotImplemented;
+        if ((q.out_nchw == 5 || q.bias_rows) && q.resid != nullptr && !p.r_tma) return kNotImplemented;
     }
 
     const unsigned grid = static_cast<unsigned>(total < st->num_sms ? total : st->num_sms);
@@ -2570,6 +2572,22 @@ int dlf_b200_conv2d_nhwc(int dtype, size_t batches, size_t channels, size_t heig
     if (y_layout == DLF_B200_LAYOUT_NHWC) {
         q.ldd = static_cast<long long>(num_kernels);
         q.out_nchw = 5;
+        // With 65 to 128 output channels and a filter larger than 1x1 the pixel-per-lane form runs UMMAs
+        // of 128 columns and fetches the filter bank once per 128 pixels. With the filter bank as
+        // operand A (lanes = output channels) a tile is 256 pixels wide: D[pixel][channel] is then the
+        // plain column-major output of that product, written through the GEMM epilogue's boxes with
+        // the bias taken per row. Measured at batch 256: 128 -> 128 3x3 at 28x28 77 -> 61 us; not for
+        // 64 output channels, where half of the lanes idle (64 -> 64 3x3 at 56x56: 146 -> 156 us;
+        // 256 -> 64 1x1: 81 -> 108 us), nor for 1x1 filters (512 -> 128 at 28x28: 48 -> 50 us).
+        // Bit 28 of the tile-width word: never.
+        if (num_kernels > 64 && num_kernels <= 128 && taps > 1 && !((g_force_bn.load() >> 16) & 4096)) {
+            std::swap(q.a, q.b);
+            q.M = static_cast<long long>(num_kernels);
+            q.N = static_cast<long long>(batches) * P;
+            q.cl_swap = 1;
+            q.out_nchw = 0;
+            q.bias_rows = 1;
+        }
     } else {
         // NCHW output: the forms of the channels-last route of dlf_b200_conv2d_fused
         q.ldd = P;

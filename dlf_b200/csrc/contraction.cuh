@@ -118,6 +118,8 @@ struct Params {
     const float* betas;
     const char* bias;  // bias[batch*bias_stride + j] in the storage type, or null
     long long bias_stride;
+    int bias_rows;     // the bias belongs to the rows of D (bias[i], one value per lane) instead of the columns:
+                       // a channels-last convolution computed with the filter bank as operand A
     // fused convolution epilogue: resid (null or a tensor laid out like D) is added to the result,
     // relu clamps it at zero before the store
     const char* resid;
@@ -832,9 +834,13 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
                         ptx::tmem_ld_wait();
                         DLF_CLK_ADD(12);
                         float bv = 0.0f;
-                        if (bias != nullptr && c0 + lane < ncols)
+                        if (p.bias_rows) {
+                            if (p.bias != nullptr && row_ok)  // every lane gets its own row's value from any source lane
+                                bv = p.fmt == FMT_F16 ? out_load<OUT_F16>(p.bias + i * 2) : out_load<OUT_BF16>(p.bias + i * 2);
+                        } else if (bias != nullptr && c0 + lane < ncols) {
                             bv = p.fmt == FMT_F16 ? out_load<OUT_F16>(bias + (c0 + lane) * 2)
                                                   : out_load<OUT_BF16>(bias + (c0 + lane) * 2);
+                        }
                         const uint32_t half = wide ? static_cast<uint32_t>((c0 >> 5) & 1) : (chunk_no & 1u);
                         // the store that last read this buffer must have drained it
                         if (wide ? (half == 0 && chunk_no >= 1) : (chunk_no >= 2)) {
@@ -884,7 +890,7 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
                             char* op = optr + static_cast<long long>(c0) * colstride * 2;
 #pragma unroll
                             for (int jj = 0; jj < 32; ++jj) {
-                                float r = __uint_as_float(v[jj]) + __shfl_sync(0xffffffffu, bv, jj);
+                                float r = __uint_as_float(v[jj]) + (p.bias_rows ? bv : __shfl_sync(0xffffffffu, bv, jj));
                                 r = relu ? fmaxf(r, 0.0f) : r;
                                 if (row_ok && c0 + jj < ncols) {
                                     if (p.fmt == FMT_F16) out_store<OUT_F16>(op + jj * colstride * 2, r);
@@ -896,7 +902,7 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
                         if (p.fmt == FMT_F16) {
 #pragma unroll
                             for (int jj = 0; jj < 32; ++jj) {
-                                float r = __uint_as_float(v[jj]) + __shfl_sync(0xffffffffu, bv, jj);
+                                float r = __uint_as_float(v[jj]) + (p.bias_rows ? bv : __shfl_sync(0xffffffffu, bv, jj));
                                 r = relu ? fmaxf(r, 0.0f) : r;
                                 const unsigned short h = __half_as_ushort(__float2half_rn(r));
                                 asm volatile("st.shared.u16 [%0], %1;" ::"r"(sbuf + jj * 64u), "h"(h) : "memory");
@@ -904,7 +910,7 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
                         } else {
 #pragma unroll
                             for (int jj = 0; jj < 32; ++jj) {
-                                float r = __uint_as_float(v[jj]) + __shfl_sync(0xffffffffu, bv, jj);
+                                float r = __uint_as_float(v[jj]) + (p.bias_rows ? bv : __shfl_sync(0xffffffffu, bv, jj));
                                 r = relu ? fmaxf(r, 0.0f) : r;
                                 const unsigned short h = __bfloat16_as_ushort(__float2bfloat16_rn(r));
                                 asm volatile("st.shared.u16 [%0], %1;" ::"r"(sbuf + jj * 64u), "h"(h) : "memory");

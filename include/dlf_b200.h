@@ -277,7 +277,9 @@ int dlf_b200_device_status(int* device_status);
  * the one with three sets, 0x800000 never the halo-tile kernel (stride-1 filters larger than 1x1
  * over a multiple of 64 channels; default with at most 64 output channels and rows of a multiple
  * of 8 outputs), 0x1000000 that kernel for every convolution it can serve, 0x8000000 32-column
- * boxes only in the swapped NCHW epilogue (default: 64-column boxes where a warp owns 64 columns). */
+ * boxes only in the swapped NCHW epilogue (default: 64-column boxes where a warp owns 64 columns),
+ * 0x10000000 never compute a channels-last convolution with the filter bank as operand A (default
+ * for filters larger than 1x1 with 65 to 128 output channels). */
 void dlf_b200_set_tuning(int force_bn, int force_generic_loader);
 
 /* Counts kernel launches made by this library in this process (all threads). */

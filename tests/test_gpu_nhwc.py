@@ -41,6 +41,8 @@ NHWC_CASES = [
     (5, 64, 5, 5, 64, 3, 3, (1, 1, 1, 1), (1, 1), (1, 1)),        # tiles straddle images
     (2, 64, 20, 20, 64, 7, 7, (3, 3, 3, 3), (2, 2), (1, 1)),      # 7x7 stride 2
     (3, 512, 7, 7, 2048, 1, 1, (0, 0, 0, 0), (1, 1), (1, 1)),     # ResNet-50's last widening layer
+    (3, 64, 9, 9, 96, 3, 3, (1, 1, 1, 1), (1, 1), (1, 1)),        # 96 output channels, 3x3: filter bank as operand A, bias per row, idle lanes
+    (2, 128, 14, 14, 128, 3, 3, (1, 1, 1, 1), (2, 2), (1, 1)),    # the same form with stride 2
 ]
 
 
