@@ -429,11 +429,17 @@ bool encode_output_map(const DeviceState& st, CUtensorMap* map, const Problem& q
     if (q.out_nchw == 5) {
         // channels-last output D[pixel][channel] (rows = pixels of all images): boxes of 32 channels x 32
         // pixels of {channels, pixels}, 64-byte swizzled like the swapped form's
+        const bool batched = q.batch > 1 && q.d_batch_stride != 0;
         const bool ok = q.es == 2 && q.beta == 0.0f && (reinterpret_cast<uintptr_t>(q.d) & 15u) == 0 &&
-                        (q.N * q.es) % 16 == 0 && q.N * q.es < (1ll << 40) && !(g_force_generic.load() & 0x4000);
+                        (q.N * q.es) % 16 == 0 && (q.ldd * q.es) % 16 == 0 && q.ldd * q.es < (1ll << 40) &&
+                        (!batched || ((q.d_batch_stride * q.es) % 16 == 0 && q.d_batch_stride * q.es < (1ll << 40))) &&
+                        !(g_force_generic.load() & 0x4000);
         if (!ok) return false;
-        cuuint64_t dims[3] = {static_cast<cuuint64_t>(q.N), static_cast<cuuint64_t>(q.M), 1};
-        cuuint64_t strides[2] = {static_cast<cuuint64_t>(q.N * q.es), static_cast<cuuint64_t>(q.N * q.M * q.es)};
+        cuuint64_t dims[3] = {static_cast<cuuint64_t>(q.N), static_cast<cuuint64_t>(q.M),
+                              static_cast<cuuint64_t>(batched ? q.batch : 1)};
+        cuuint64_t strides[2] = {static_cast<cuuint64_t>(q.ldd * q.es),
+                                 static_cast<cuuint64_t>(batched ? q.d_batch_stride * q.es : q.ldd * q.es * (q.M > 0 ? q.M : 1))};
+        if (strides[1] >= (1ull << 40)) strides[1] = strides[0];
         cuuint32_t box[3] = {box_cols, 32, 1};
         cuuint32_t estr[3] = {1, 1, 1};
         CUresult r = st.encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, q.d, dims, strides, box, estr,
@@ -763,7 +769,7 @@ int launch_ts(const DeviceState& st, const Problem& q, cudaStream_t stream) {
     return kSuccess;
 }
 
-int launch(const Problem& q, cudaStream_t stream, DeviceState* preset = nullptr) {
+int launch(const Problem& q_in, cudaStream_t stream, DeviceState* preset = nullptr) {
     DeviceState* st = preset;
     int rc = kSuccess;
     if (st == nullptr) {
@@ -771,8 +777,31 @@ int launch(const Problem& q, cudaStream_t stream, DeviceState* preset = nullptr)
         if (rc != kSuccess) return rc;
     }
     clear_stale_error();
-    if (q.M > INT_MAX - 512 || q.N > INT_MAX - 512 || q.K > INT_MAX - 512 || q.batch > INT_MAX)
+    if (q_in.M > INT_MAX - 512 || q_in.N > INT_MAX - 512 || q_in.K > INT_MAX - 512 || q_in.batch > INT_MAX)
         return kInvalidDimension;
+
+    // A plain 16-bit product whose result can leave through TMA stores is computed transposed: with
+    // the operands exchanged the lanes hold the columns j of D and the accumulator columns run along
+    // i, the contiguous index of D, so a lane's 32 columns are 64 consecutive bytes - four 16-byte
+    // shared-memory stores into the [row][column] staging block of the channels-last convolution
+    // (out_nchw == 5) instead of 32 two-byte ones, and no shuffles. The product itself is the same
+    // (D^T = Bu * Au^T; both operands are K-major or MN-major either way). Only for products whose
+    // epilogue sets the pace - a short K - and whose N fills the 128 lanes. Measured: the batched
+    // product 1024 x (512 x 512 x 64) 187 -> 125 us (a library bmm: 105 us); 1024 x (512 x 64 x 512)
+    // would lose (106 -> 111 us, half of the lanes idle) and so would 4096^3 (118 -> 137 us: twice the
+    // TMA stores beside a main loop that needs the copy unit itself). Bit 30 of the tile-width word: never.
+    Problem q = q_in;
+    if (q.es == 2 && q.out_nchw == 0 && q.a_cl == 0 && !q.a.im2col && q.beta == 0.0f && q.betas == nullptr &&
+        q.alphas == nullptr && q.a_offs == nullptr && q.b_offs == nullptr && q.d_offs == nullptr && q.bias == nullptr &&
+        q.resid == nullptr && !q.d_f32 && !(g_force_generic.load() & (0xff | 0x4000 | 0x200)) && q.K <= 256 && q.N >= 128 &&
+        (reinterpret_cast<uintptr_t>(q.d) & 15u) == 0 && (q.ldd * q.es) % 16 == 0 && (q.M * q.es) % 16 == 0 &&
+        (q.batch == 1 || q.d_batch_stride == 0 || (q.d_batch_stride * q.es) % 16 == 0) &&
+        tma_ok(q.a, q.es, q.M, q.K, q.batch) && tma_ok(q.b, q.es, q.N, q.K, q.batch) &&
+        !((g_force_bn.load() >> 16) & 16384)) {
+        std::swap(q.a, q.b);
+        std::swap(q.M, q.N);
+        q.out_nchw = 5;
+    }
 
     const bool use_tma = q.es == 2 && !(g_force_generic.load() & 0xff) && q.a_offs == nullptr &&
                          ((q.a_cl != 0 && !q.cl_swap) || tma_ok(q.a, q.es, q.M, q.K, q.batch)) &&

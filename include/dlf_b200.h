@@ -279,7 +279,9 @@ int dlf_b200_device_status(int* device_status);
  * of 8 outputs), 0x1000000 that kernel for every convolution it can serve, 0x8000000 32-column
  * boxes only in the swapped NCHW epilogue (default: 64-column boxes where a warp owns 64 columns),
  * 0x10000000 never compute a channels-last convolution with the filter bank as operand A (default
- * for filters larger than 1x1 with 65 to 128 output channels). */
+ * for filters larger than 1x1 with 65 to 128 output channels), 0x40000000 never compute a plain
+ * 16-bit product transposed (default for K <= 256 and N >= 128 when the result can leave through
+ * TMA stores: the epilogue then writes 16-byte pieces of D's contiguous direction). */
 void dlf_b200_set_tuning(int force_bn, int force_generic_loader);
 
 /* Counts kernel launches made by this library in this process (all threads). */

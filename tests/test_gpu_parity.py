@@ -542,6 +542,53 @@ def test_strided_batched_including_shared_operand(dtype):
             assert max_rel(got, ref) <= HALF_TOL
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(256, 384, 64, 3), (136, 200, 72, 2), (128, 128, 256, 1), (520, 136, 40, 2)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_short_k_products_computed_transposed(lib, shape, dtype):
+    """A 16-bit product with K <= 256 and N >= 128 whose result can leave through TMA stores is
+    computed as D^T = Bu * Au^T (the lanes hold D's columns, the epilogue writes 16-byte pieces of
+    D's contiguous direction); bit 30 of the tile-width word turns that off. Both ways against the
+    oracle for every transpose combination in both layouts, padded leading dimension and batch
+    stride of C, beta = 0 with C pre-filled (it must not be read), nothing outside the m x n windows
+    touched, and the two ways bit-identical (the same products summed in the same order)."""
+    gb = _gb()
+    m, n, k, batch = shape
+    rng = np.random.default_rng(sum(shape))
+    for layout in (gb.Layout.RowMajor, gb.Layout.ColMajor):
+        for ta in (gb.Transpose.NoTrans, gb.Transpose.Trans):
+            for tb in (gb.Transpose.NoTrans, gb.Transpose.Trans):
+                a_one, a_two, b_one, b_two, c_one, c_two = gb._dims(layout, ta, tb, m, n, k)
+                lda, ldb, ldc = a_one, b_one, c_one + 8
+                a_stride, b_stride, c_stride = lda * a_two, ldb * b_two + 16, ldc * c_two + 24
+                A = _round_to(_rand(rng, a_stride * batch), dtype)
+                B = _round_to(_rand(rng, b_stride * batch), dtype)
+                C = np.full(c_stride * batch, 7.0, dtype=np.float32)
+                ref = C.copy()
+                oracle.gblas_sgemm_strided_batched(int(layout), int(ta), int(tb), m, n, k, 0.5, A, 0, lda, a_stride,
+                                                   B, 0, ldb, b_stride, 0.0, ref, 0, ldc, c_stride, batch, wide=True)
+                dA, dB = torch.from_numpy(A).to(dtype).cuda(), torch.from_numpy(B).to(dtype).cuda()
+                outs = []
+                for route in (0, 0x40000000):
+                    dC = torch.full((c_stride * batch,), float("nan"), dtype=dtype, device="cuda")
+                    lib.set_tuning(route, 0)
+                    try:
+                        gb.gemmStridedBatched(layout, ta, tb, m, n, k, 0.5, dA, 0, lda, a_stride, dB, 0, ldb, b_stride,
+                                              0.0, dC, 0, ldc, c_stride, batch)
+                        torch.cuda.synchronize()
+                    finally:
+                        lib.set_tuning(0, 0)
+                    got = dC.float().cpu().numpy()
+                    win = np.zeros(c_stride * batch, dtype=bool)  # the elements of the m x n windows
+                    for bb in range(batch):
+                        for line in range(c_two):
+                            win[bb * c_stride + line * ldc: bb * c_stride + line * ldc + c_one] = True
+                    assert np.isnan(got[~win]).all(), "padding touched"
+                    assert max_rel(got[win], ref[win]) <= HALF_TOL
+                    outs.append(dC)
+                assert torch.equal(outs[0][torch.from_numpy(win).cuda()], outs[1][torch.from_numpy(win).cuda()])
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_gemm_batched_offset_tables(dtype):
     gb = _gb()
