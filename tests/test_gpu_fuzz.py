@@ -61,6 +61,60 @@ def test_random_convolutions(seed):
         assert _close(Y.float().cpu().numpy(), ref, dt), cfg
 
 
+def _aligned_case(rng):
+    """Shapes that reach the tensor-map-fed routes: channel counts in multiples of 8, 16-bit types,
+    planes that are often multiples of 8 pixels."""
+    dt = [torch.float16, torch.bfloat16][rng.integers(0, 2)]
+    C = int(rng.choice([8, 16, 24, 32, 64, 64, 72, 128, 192]))
+    Co = int(rng.choice([8, 16, 40, 64, 64, 72, 96, 128, 136, 256, 320]))
+    k = int(rng.choice([1, 1, 3, 3, 5, 7]))
+    H = int(rng.integers(max(1, k - 2), 34))
+    W = int(rng.choice([4, 7, 8, 12, 14, 16, 20, 28, 30, 32, 33]))
+    pad = int(rng.integers(0, k // 2 + 1))
+    stride = int(rng.choice([1, 1, 1, 2]))
+    if H + 2 * pad < k or W + 2 * pad < k:
+        H, W = H + k, W + k
+    N = int(rng.integers(1, 6))
+    relu, use_res, use_b = (bool(rng.integers(0, 2)) for _ in range(3))
+    return dt, N, C, H, W, Co, k, pad, stride, relu, use_res, use_b
+
+
+@pytest.mark.parametrize("seed", range(3))
+def test_random_aligned_convolutions_on_both_entries(seed):
+    """The NCHW entry (whichever route it takes: channels-last copy + im2col-mode loads, swapped or
+    pixel-per-lane, halo tiles, batched-GEMM form, residual boxes, wide boxes) and the channels-last
+    entry with both output layouts, on the same random problems against the oracle."""
+    from dlf_b200 import gdnn
+    rng = np.random.default_rng(500 + seed)
+    for _ in range(50):
+        dt, N, C, H, W, Co, k, pad, stride, relu, use_res, use_b = _aligned_case(rng)
+        cfg = dict(dt=str(dt), N=N, C=C, H=H, W=W, Co=Co, k=k, pad=pad, stride=stride, relu=relu, res=use_res, bias=use_b)
+        X = _rt(rng.normal(size=(N, C, H, W)).astype(np.float32), dt)
+        Wt = _rt((rng.normal(size=(Co, C, k, k)) / np.sqrt(C * k * k)).astype(np.float32), dt)
+        b = _rt(rng.uniform(-0.1, 0.1, Co).astype(np.float32), dt)
+        f = gdnn.Filter2D(X.shape, Wt.shape).pads(pad, pad).strides(stride, stride)
+        osh = tuple(f.output_shape())
+        R = _rt(rng.normal(size=osh).astype(np.float32), dt)
+        ref = oracle.conv2d_fused(X, Wt, residual=R if use_res else None, relu=relu, bias=b if use_b else None,
+                                  pads=(pad,) * 4, strides=(stride, stride), wide=True)
+        dX, dW = torch.from_numpy(X).to(dt).cuda(), torch.from_numpy(Wt).to(dt).cuda()
+        db = torch.from_numpy(b).to(dt).cuda() if use_b else None
+        dR = torch.from_numpy(R).to(dt).cuda() if use_res else None
+        act = "relu" if relu else None
+        Y = torch.full(osh, float("nan"), dtype=dt, device="cuda")
+        gdnn.conv2d_filter(dX, dW, Y, f, bias=db, residual=dR, activation=act)
+        assert _close(Y.float().cpu().numpy(), ref, dt), ("nchw entry", cfg)
+        assert gdnn.nhwc_supported(f, dt), cfg
+        Xn, Wp = gdnn.nchw_to_nhwc(dX), gdnn.pack_filters_nhwc(dW)
+        Yn = torch.full((osh[0], osh[2], osh[3], osh[1]), float("nan"), dtype=dt, device="cuda")
+        gdnn.conv2d_nhwc(Xn, Wp, Yn, f, bias=db, residual=dR.permute(0, 2, 3, 1).contiguous() if use_res else None,
+                         activation=act)
+        assert _close(Yn.permute(0, 3, 1, 2).float().cpu().numpy(), ref, dt), ("channels-last entry", cfg)
+        Y2 = torch.full(osh, float("nan"), dtype=dt, device="cuda")
+        gdnn.conv2d_nhwc(Xn, Wp, Y2, f, bias=db, residual=dR, activation=act, y_layout=gdnn.NCHW)
+        assert _close(Y2.float().cpu().numpy(), ref, dt), ("channels-last entry, NCHW output", cfg)
+
+
 @pytest.mark.parametrize("seed", range(2))
 def test_random_pooling(seed):
     from dlf_b200 import gdnn
