@@ -307,6 +307,7 @@ struct Problem {
     const char* bias = nullptr;
     long long bias_stride = 0;
     int bias_rows = 0;  // bias per row of D (channels-last convolution with the filter bank as operand A)
+    bool narrow_boxes = false;  // row-staged epilogue with 32-column boxes even where 64-column ones are possible
     const char* resid = nullptr;
     int relu = 0;
     Im2colGeom g{};
@@ -801,6 +802,7 @@ int launch(const Problem& q_in, cudaStream_t stream, DeviceState* preset = nullp
         std::swap(q.a, q.b);
         std::swap(q.M, q.N);
         q.out_nchw = 5;
+        q.narrow_boxes = true;  // measured on the batched product above: 125-128 us with 2 KB boxes, 136 us with 4 KB ones
     }
 
     const bool use_tma = q.es == 2 && !(g_force_generic.load() & 0xff) && q.a_offs == nullptr &&
@@ -973,13 +975,13 @@ int launch(const Problem& q_in, cudaStream_t stream, DeviceState* preset = nullp
         // 64-column boxes need 64 columns per epilogue warp
         // (a residual is fetched box by box into single staging blocks: 32-column boxes then)
         // (the forms that prefetch a residual box a block ahead need the two single staging blocks:
-        // 32-column boxes; the swapped NCHW form fetches it into the wide box itself. Measured at batch
-        // 256: 64 -> 256 at 56x56 120 -> 92 us, with a residual 220 -> 185 us; 128 -> 512 at 28x28 with
-        // a residual 135 -> 105 us. The channels-last form loses with wide boxes - 105 -> 130 us and
-        // 197 -> 228 us on the same layer - and keeps the double-buffered 32-column ones.)
-        const bool boxes_are_rows = q.out_nchw == 3;
+        // 32-column boxes; the row-staged forms fetch it into the wide box itself. Measured at batch
+        // 256, NCHW swapped form: 64 -> 256 at 56x56 120 -> 92 us, with a residual 220 -> 185 us;
+        // 128 -> 512 at 28x28 with a residual 135 -> 105 us. Channels-last form: 105 -> 97 us and
+        // 199 -> 180 us on the first layer, 108 -> 99 us on the second.)
+        const bool boxes_are_rows = q.out_nchw == 3 || q.out_nchw == 5;
         const unsigned box_cols = (esets == 2 ? bn >= 128 : (esets == 4 && bn >= 256)) && !(g_force_generic.load() & 0x100) &&
-                                          (q.resid == nullptr || boxes_are_rows) && q.out_nchw != 5 &&
+                                          (q.resid == nullptr || boxes_are_rows) && !q.narrow_boxes &&
                                           !(boxes_are_rows && ((g_force_bn.load() >> 16) & 2048)) ? 64 : 32;
         p.d_tma = (!q.d_f32 && encode_output_map(*st, &tm_d, q, box_cols)) ? static_cast<int>(box_cols) : 0;
         if ((q.out_nchw == 5 || q.bias_rows) && !p.d_tma) return kNotImplemented;  // the channels-last forms only leave through TMA stores

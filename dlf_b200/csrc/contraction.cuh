@@ -510,13 +510,21 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
                 if constexpr (RES) {
                     if (h == 0) res_smem = res_landed(0u);
                 }
+                // alpha and the bias in a pass of their own: a select between the two kinds of bias
+                // around the shuffle inside the loop below costs far more than it looks
+                if (bias_cols != nullptr) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        v[j] = __float_as_uint(fmaf(p.alpha, __uint_as_float(v[j]), __shfl_sync(0xffffffffu, bcol, j)));
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(fmaf(p.alpha, __uint_as_float(v[j]), brow));
+                }
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
                     float r[8];
 #pragma unroll
-                    for (int g = 0; g < 8; ++g)
-                        r[g] = fmaf(p.alpha, __uint_as_float(v[8 * k + g]),
-                                    bias_cols != nullptr ? __shfl_sync(0xffffffffu, bcol, 8 * k + g) : brow);
+                    for (int g = 0; g < 8; ++g) r[g] = __uint_as_float(v[8 * k + g]);
                     const uint32_t saddr = srow + ((static_cast<uint32_t>(4 * h + k) ^ sx) << 4);
                     if (res_smem) {
                         const uint4 u = ld_shared_v4(saddr);
