@@ -307,6 +307,10 @@ struct Problem {
     const char* bias = nullptr;
     long long bias_stride = 0;
     int bias_rows = 0;  // bias per row of D (channels-last convolution with the filter bank as operand A)
+    const int* a_idx = nullptr;  // per batch entry: index into the strided sequence of A / B / D matrices (device)
+    const int* b_idx = nullptr;
+    const int* d_idx = nullptr;
+    long long a_count = 0, b_count = 0, d_count = 0;  // matrices the index tables reach (batch extents of the tensor maps)
     bool narrow_boxes = false;  // row-staged epilogue with 32-column boxes even where 64-column ones are possible
     const char* resid = nullptr;
     int relu = 0;
@@ -430,14 +434,15 @@ bool encode_output_map(const DeviceState& st, CUtensorMap* map, const Problem& q
     if (q.out_nchw == 5) {
         // channels-last output D[pixel][channel] (rows = pixels of all images): boxes of 32 channels x 32
         // pixels of {channels, pixels}, 64-byte swizzled like the swapped form's
-        const bool batched = q.batch > 1 && q.d_batch_stride != 0;
+        const long long dcount = q.d_idx ? q.d_count : q.batch;
+        const bool batched = dcount > 1 && q.d_batch_stride != 0;
         const bool ok = q.es == 2 && q.beta == 0.0f && (reinterpret_cast<uintptr_t>(q.d) & 15u) == 0 &&
                         (q.N * q.es) % 16 == 0 && (q.ldd * q.es) % 16 == 0 && q.ldd * q.es < (1ll << 40) &&
                         (!batched || ((q.d_batch_stride * q.es) % 16 == 0 && q.d_batch_stride * q.es < (1ll << 40))) &&
                         !(g_force_generic.load() & 0x4000);
         if (!ok) return false;
         cuuint64_t dims[3] = {static_cast<cuuint64_t>(q.N), static_cast<cuuint64_t>(q.M),
-                              static_cast<cuuint64_t>(batched ? q.batch : 1)};
+                              static_cast<cuuint64_t>(batched ? dcount : 1)};
         cuuint64_t strides[2] = {static_cast<cuuint64_t>(q.ldd * q.es),
                                  static_cast<cuuint64_t>(batched ? q.d_batch_stride * q.es : q.ldd * q.es * (q.M > 0 ? q.M : 1))};
         if (strides[1] >= (1ull << 40)) strides[1] = strides[0];
@@ -474,9 +479,10 @@ bool encode_output_map(const DeviceState& st, CUtensorMap* map, const Problem& q
                       q.ldd * q.es < (1ll << 40) && q.d_batch_stride * q.es < (1ll << 40) &&
                       !(g_force_generic.load() & 0x4000);
     if (!d_ok) return false;
-    const bool batched = q.batch > 1 && q.d_batch_stride != 0;
+    const long long dcount = q.d_idx ? q.d_count : q.batch;
+    const bool batched = dcount > 1 && q.d_batch_stride != 0;
     cuuint64_t dims[3] = {static_cast<cuuint64_t>(q.M), static_cast<cuuint64_t>(q.N),
-                          static_cast<cuuint64_t>(batched ? q.batch : 1)};
+                          static_cast<cuuint64_t>(batched ? dcount : 1)};
     cuuint64_t strides[2] = {static_cast<cuuint64_t>(q.ldd * q.es),
                              static_cast<cuuint64_t>(batched ? q.d_batch_stride * q.es
                                                              : q.ldd * q.es * (q.N > 0 ? q.N : 1))};
@@ -801,6 +807,8 @@ int launch(const Problem& q_in, cudaStream_t stream, DeviceState* preset = nullp
         !((g_force_bn.load() >> 16) & 16384)) {
         std::swap(q.a, q.b);
         std::swap(q.M, q.N);
+        std::swap(q.a_idx, q.b_idx);
+        std::swap(q.a_count, q.b_count);
         q.out_nchw = 5;
         q.narrow_boxes = true;  // measured on the batched product above: 125-128 us with 2 KB boxes, 136 us with 4 KB ones
     }
@@ -825,7 +833,7 @@ int launch(const Problem& q_in, cudaStream_t stream, DeviceState* preset = nullp
     // CTA pairs (cta_group::2): 256 x 256 tiles, each CTA stages 128 rows of A and 128 of B, so
     // a third less shared-memory fill per flop than a lone 128 x 256 tile.
     if (use_tma && bn == 256 && q.M > kBM && st->max_pair_clusters > 0 && (g_force_generic.load() & 0x200) &&
-        q.a_cl == 0 && q.out_nchw == 0) {
+        q.a_cl == 0 && q.out_nchw == 0 && q.a_idx == nullptr && q.b_idx == nullptr && q.d_idx == nullptr) {
         const long long ptiles_m = (q.M + 2 * kBM - 1) / (2 * kBM);
         const long long ptiles_n = (q.N + bn - 1) / bn;
         const long long ptotal = q.batch * ptiles_m * ptiles_n;
@@ -940,6 +948,9 @@ int launch(const Problem& q_in, cudaStream_t stream, DeviceState* preset = nullp
     p.bias = q.bias;
     p.bias_stride = q.bias_stride;
     p.bias_rows = q.bias_rows;
+    p.a_idx = q.a_idx;
+    p.b_idx = q.b_idx;
+    p.d_idx = q.d_idx;
     p.resid = q.resid;
     p.relu = q.relu;
     p.g = q.g;
@@ -961,15 +972,15 @@ int launch(const Problem& q_in, cudaStream_t stream, DeviceState* preset = nullp
     p.r_tma = 0;
     if (use_tma) {
         if (q.cl_swap) {
-            rc = encode_map(*st, &tm_a, q.a, q.es, q.M, q.K, q.batch, kBM);
+            rc = encode_map(*st, &tm_a, q.a, q.es, q.M, q.K, q.a_idx ? q.a_count : q.batch, kBM);
             if (rc != kSuccess) return rc;
             rc = q.a_cl == 1 ? encode_im2col_map(*st, &tm_b, q, q.b.base, bn)
-                             : encode_map(*st, &tm_b, q.b, q.es, q.N, q.K, q.batch, bn);
+                             : encode_map(*st, &tm_b, q.b, q.es, q.N, q.K, q.b_idx ? q.b_count : q.batch, bn);
         } else {
             rc = q.a_cl == 1 ? encode_im2col_map(*st, &tm_a, q, q.a.base, kBM)
-                             : encode_map(*st, &tm_a, q.a, q.es, q.M, q.K, q.batch, kBM);
+                             : encode_map(*st, &tm_a, q.a, q.es, q.M, q.K, q.a_idx ? q.a_count : q.batch, kBM);
             if (rc != kSuccess) return rc;
-            rc = encode_map(*st, &tm_b, q.b, q.es, q.N, q.K, q.batch, bn);
+            rc = encode_map(*st, &tm_b, q.b, q.es, q.N, q.K, q.b_idx ? q.b_count : q.batch, bn);
         }
         if (rc != kSuccess) return rc;
         // 64-column boxes need 64 columns per epilogue warp
@@ -1362,8 +1373,8 @@ int dlf_b200_gemm_strided_batched(int dtype, int layout, int trans_a, int trans_
 }
 
 size_t dlf_b200_gemm_batched_workspace_bytes(size_t batch_count) {
-    // three int64 offset tables + two float scalar tables
-    return batch_count * (3 * sizeof(long long) + 2 * sizeof(float));
+    // three int64 offset tables + two float scalar tables + three int32 index tables
+    return batch_count * (3 * sizeof(long long) + 2 * sizeof(float) + 3 * sizeof(int));
 }
 
 int dlf_b200_gemm_batched(int dtype, int layout, int trans_a, int trans_b, size_t m, size_t n,
@@ -1400,6 +1411,98 @@ int dlf_b200_gemm_batched(int dtype, int layout, int trans_a, int trans_b, size_
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     StreamDevice sd(s);
     if (sd.rc != kSuccess) return sd.rc;
+    // Tables that are affine in the batch index (offset_i = offset_0 + i * stride with stride >= 0
+    // for all three matrices, one alpha and one beta) describe a strided batch: the product then
+    // takes the strided path - tensor-map-fed operands, no tables on the device, nothing copied
+    // from the host. (dlf's matmul reaches gemmBatched with such tables whenever its operands
+    // broadcast in a way its own stride test, linalg_detail.h:1430-1478, does not recognise.)
+    {
+        bool affine = true;
+        const long long sa = batch_count > 1 ? h_a[1] - h_a[0] : 0, sb = batch_count > 1 ? h_b[1] - h_b[0] : 0,
+                        sd_ = batch_count > 1 ? h_d[1] - h_d[0] : 0;
+        if (sa < 0 || sb < 0 || sd_ < 0) affine = false;
+        for (size_t i = 1; affine && i < batch_count; ++i)
+            affine = h_a[i] - h_a[0] == static_cast<long long>(i) * sa && h_b[i] - h_b[0] == static_cast<long long>(i) * sb &&
+                     h_d[i] - h_d[0] == static_cast<long long>(i) * sd_ && h_alpha[i] == h_alpha[0] && h_beta[i] == h_beta[0];
+        if (affine && !((g_force_bn.load() >> 16) & 4)) {  // bit 18 of the tile-width word: always through the tables
+            q.a.base += h_a[0] * q.es;
+            q.b.base += h_b[0] * q.es;
+            q.d += h_d[0] * q.es;
+            q.a.batch_stride = sa;
+            q.b.batch_stride = sb;
+            q.d_batch_stride = sd_;
+            q.alpha = h_alpha[0];
+            q.beta = h_beta[0];
+            q.batch = static_cast<long long>(batch_count);
+            return launch(q, s);
+        }
+    }
+    // Tables whose offsets are base + idx * stride with 16-byte aligned base and stride (matrices of a
+    // packed array visited in any order, an operand shared by several products, ...) keep the
+    // tensor-map-fed kernel: idx becomes the batch coordinate of the operand's tensor map, read from
+    // a small table. Needs 16-bit operands that satisfy the TMA rules and, for D, beta == 0 everywhere.
+    int* h_ai = reinterpret_cast<int*>(h_beta + batch_count);
+    int* h_bi = h_ai + batch_count;
+    int* h_di = h_bi + batch_count;
+    bool indexed = q.es == 2 && !(g_force_generic.load() & 0xff) && !((g_force_bn.load() >> 16) & 4);
+    long long base3[3] = {0, 0, 0}, stride3[3] = {0, 0, 0}, count3[3] = {1, 1, 1};
+    {
+        const long long* tabs[3] = {h_a, h_b, h_d};
+        int* idxs[3] = {h_ai, h_bi, h_di};
+        for (int t = 0; indexed && t < 3; ++t) {
+            long long lo = tabs[t][0], g = 0;
+            for (size_t i = 1; i < batch_count; ++i) lo = std::min(lo, tabs[t][i]);
+            for (size_t i = 0; i < batch_count; ++i) {
+                long long d = tabs[t][i] - lo;
+                while (d != 0) {  // g = gcd(g, d)
+                    const long long r = g % d;
+                    g = d;
+                    d = r;
+                }
+            }
+            long long hi = 0;
+            for (size_t i = 0; i < batch_count; ++i) {
+                const long long v = g ? (tabs[t][i] - lo) / g : 0;
+                hi = std::max(hi, v);
+                idxs[t][i] = static_cast<int>(v);
+            }
+            indexed = (lo * q.es) % 16 == 0 && (g * q.es) % 16 == 0 && g * q.es < (1ll << 40) && hi < INT_MAX - 1;
+            base3[t] = lo;
+            stride3[t] = g;
+            count3[t] = hi + 1;
+        }
+        for (size_t i = 0; indexed && i < batch_count; ++i) indexed = h_beta[i] == 0.0f;
+    }
+    if (indexed) {
+        Problem r = q;
+        r.a.base += base3[0] * q.es;
+        r.b.base += base3[1] * q.es;
+        r.d += base3[2] * q.es;
+        r.a.batch_stride = stride3[0];
+        r.b.batch_stride = stride3[1];
+        r.d_batch_stride = stride3[2];
+        r.batch = static_cast<long long>(batch_count);
+        indexed = tma_ok(r.a, r.es, r.M, r.K, count3[0]) && tma_ok(r.b, r.es, r.N, r.K, count3[1]) &&
+                  (reinterpret_cast<uintptr_t>(r.d) & 15u) == 0 && (r.ldd * r.es) % 16 == 0 && (r.M * r.es) % 16 == 0;
+        if (indexed) {
+            CUDA_TRY(cudaMemcpyAsync(workspace, host.data(), need, cudaMemcpyHostToDevice, s));
+            char* w = static_cast<char*>(workspace);
+            const float* d_alpha = reinterpret_cast<const float*>(w + 3 * sizeof(long long) * batch_count);
+            const int* d_idx0 = reinterpret_cast<const int*>(d_alpha + 2 * batch_count);
+            r.a_idx = d_idx0;
+            r.b_idx = d_idx0 + batch_count;
+            r.d_idx = d_idx0 + 2 * batch_count;
+            r.a_count = count3[0];
+            r.b_count = count3[1];
+            r.d_count = count3[2];
+            bool one_alpha = true;
+            for (size_t i = 1; i < batch_count; ++i) one_alpha = one_alpha && h_alpha[i] == h_alpha[0];
+            if (one_alpha) r.alpha = h_alpha[0];
+            else r.alphas = d_alpha;
+            r.beta = 0.0f;
+            return launch(r, s);
+        }
+    }
     // pageable source: the runtime stages it before returning, so `host` may go out of scope
     CUDA_TRY(cudaMemcpyAsync(workspace, host.data(), need, cudaMemcpyHostToDevice, s));
     char* w = static_cast<char*>(workspace);

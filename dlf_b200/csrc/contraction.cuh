@@ -110,6 +110,12 @@ struct Params {
     GenOperand a, b;
     char* d;
     long long ldd, d_batch_stride;
+    // Batched products whose matrices lie at offsets off_b = base + idx_b * stride (the offset tables of
+    // gemmBatched, when they have that form): per operand the index of batch entry b, or null for
+    // idx_b = b. The index is the batch coordinate of the tensor maps.
+    const int* a_idx;
+    const int* b_idx;
+    const int* d_idx;
     // gemmBatched tables (device memory, entries per batch); null for the other calls
     const long long* a_offs;
     const long long* b_offs;
@@ -568,6 +574,7 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
             int b, m0, n0;
             decode_tile(p, t, b, m0, n0, tile_rows);
             m0 += row_off;
+            const int bd = p.d_idx ? p.d_idx[b] : b;  // where batch entry b of D lies
             const uint32_t buf = it & 1u;
             const uint32_t tphase = (it >> 1) & 1u;
             DLF_CLK_ADD(1);  // epilogue work of the previous tile
@@ -724,7 +731,7 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
                         if (p.d_tma == 64) {
                             // 64 channels x 32 pixels in one box (clipped at the last channel and pixel)
                             const int colw = n0 + cbase + c0;
-                            wide_block(trow5 + c0, colw, i0, p.d_batch_stride ? b : 0, ncols5 - c0, 0.0f, p.bias ? p.bias + colw * 2 : nullptr,
+                            wide_block(trow5 + c0, colw, i0, p.d_batch_stride ? bd : 0, ncols5 - c0, 0.0f, p.bias ? p.bias + colw * 2 : nullptr,
                                        p.N - colw, relu5);
                             c0 += 32;
                             continue;
@@ -786,7 +793,7 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
                         ptx::fence_proxy_async_smem();
                         __syncwarp();
                         if (lane == 0) {
-                            ptx::tma_store_3d(&tmD, sblk, col, i0, p.d_batch_stride ? b : 0);
+                            ptx::tma_store_3d(&tmD, sblk, col, i0, p.d_batch_stride ? bd : 0);
                             ptx::bulk_commit_group();
                         }
                         ++chunk_no;
@@ -808,7 +815,7 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
                           static_cast<long long>(b) * p.d_batch_stride + pp;
                 colstride = p.g.P;
             } else {
-                rowbase = (p.d_offs ? p.d_offs[b] : static_cast<long long>(b) * p.d_batch_stride) + i;
+                rowbase = (p.d_offs ? p.d_offs[b] : static_cast<long long>(bd) * p.d_batch_stride) + i;
                 colstride = p.ldd;
             }
             const float alpha = p.alphas ? p.alphas[b] : p.alpha;
@@ -937,7 +944,7 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
                         if (lane == 0) {
                             const uint32_t ssrc = d_stage + (ewarp * 2 + (wide ? 0u : half)) * 2048u;
                             const int col = n0 + cb + (wide ? (c0 & ~63) : c0);
-                            ptx::tma_store_3d(&tmD, ssrc, pp0, col, p.out_nchw == 1 ? img0 : (p.d_batch_stride ? b : 0));
+                            ptx::tma_store_3d(&tmD, ssrc, pp0, col, p.out_nchw == 1 ? img0 : (p.d_batch_stride ? bd : 0));
                             ptx::bulk_commit_group();
                         }
                         if constexpr (RES) res_ahead(t, c0, ncols, half ^ 1u);
@@ -1079,8 +1086,8 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
                 decode_tile(p, t, b, m0, n0, tile_rows);
                 m0 += row_off;
                 n0 += PAIR ? static_cast<int>(rank) * b_rows : 0;  // this CTA's share of the Bu rows
-                const int ba = p.a.batch_stride ? b : 0;
-                const int bb = p.b.batch_stride ? b : 0;
+                const int ba = p.a.batch_stride ? (p.a_idx ? p.a_idx[b] : b) : 0;
+                const int bb = p.b.batch_stride ? (p.b_idx ? p.b_idx[b] : b) : 0;
                 // im2col-mode loads: base pixel of the tile's first filter window
                 int cl_n = 0, cl_h = 0, cl_w = 0;
                 if (!PAIR && p.a_cl == 1) {

@@ -79,7 +79,9 @@ int dlf_b200_gemm_strided_batched(int dtype, int layout, int trans_a, int trans_
  * gblas.cpp:2928-3012; routines/levelx/xgemmbatched.cpp:51-118). a, b, c are the buffer bases.
  * The tables are copied into `workspace` (device memory, at least
  * dlf_b200_gemm_batched_workspace_bytes(batch_count) bytes, owned by the caller, e.g. taken from
- * gpgpu's TemporaryBuffer pool) on the given stream before the kernel runs. */
+ * gpgpu's TemporaryBuffer pool) on the given stream before the kernel runs. Tables that are affine
+ * in the batch index (offset_i = offset_0 + i * stride, stride >= 0, one alpha and one beta) are
+ * recognised on the host and run as dlf_b200_gemm_strided_batched: nothing is copied then. */
 int dlf_b200_gemm_batched(int dtype, int layout, int trans_a, int trans_b, size_t m, size_t n,
                           size_t k, const void* alphas, const void* a, const size_t* a_offsets,
                           size_t a_ld, const void* b, const size_t* b_offsets, size_t b_ld,
@@ -270,7 +272,8 @@ int dlf_b200_device_status(int* device_status);
  * Bits 16 and up of force_bn steer the channels-last route of 16-bit convolutions (transposing
  * copy into the caller's scratch + tensor-map-fed operand): 0x10000 never take it (the kernels
  * that gather the activations themselves serve the call, as they do for callers without scratch),
- * 0x20000 swap the operand roles (lanes = output channels) for every even plane size, not only
+ * 0x40000 dlf_b200_gemm_batched always through its offset tables (default: tables that are affine in
+ * the batch index take the strided path), 0x20000 swap the operand roles (lanes = output channels) for every even plane size, not only
  * for planes of a multiple of 8 pixels, 0x80000 never swap the roles of a 1x1 stride-1 convolution
  * that runs as a batched GEMM, 0x200000 never use the instantiation of the TMA-fed kernel with four
  * sets of epilogue warps (default for tiles of 128 or more columns with K <= 512), 0x400000 never

@@ -589,6 +589,48 @@ def test_short_k_products_computed_transposed(lib, shape, dtype):
                 assert torch.equal(outs[0][torch.from_numpy(win).cuda()], outs[1][torch.from_numpy(win).cuda()])
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_gemm_batched_affine_tables_take_the_strided_path(lib, dtype):
+    """Offset tables that are affine in the batch index (one alpha, one beta) run as a strided batch;
+    16-bit tables of the form base + idx * stride with 16-byte aligned base and stride (one entry out
+    of line by 8 elements; the same matrices in a shuffled order) and beta == 0 keep the
+    tensor-map-fed kernel with idx as the batch coordinate; bit 18 of the tile-width word sends
+    everything through the offset tables. All against the oracle and equal to each other."""
+    gb = _gb()
+    rng = np.random.default_rng(77)
+    m, n, k, batch = 64, 136, 72, 5
+    a_offs = [8 + i * (m * k + 16) for i in range(batch)]
+    b_offs = [0] * batch                                    # stride 0: one B for every product
+    c_offs = [16 + i * (m * n + 8) for i in range(batch)]
+    A = _round_to(_rand(rng, a_offs[-1] + m * k + 64), dtype)
+    B = _round_to(_rand(rng, k * n), dtype)
+    C = _round_to(_rand(rng, c_offs[-1] + m * n + 40), dtype)
+    shuffled = [a_offs[i] for i in (3, 0, 4, 1, 2)]
+    dA, dB = torch.from_numpy(A).to(dtype).cuda(), torch.from_numpy(B).to(dtype).cuda()
+    for offs_a in (a_offs, a_offs[:3] + [a_offs[3] + 8] + a_offs[4:], shuffled):
+        for beta in (0.25, 0.0):
+            ref = C.copy()
+            oracle.gblas_sgemm_batched(oracle.ROW_MAJOR, oracle.NO_TRANS, oracle.NO_TRANS, m, n, k, [0.5] * batch, A,
+                                       offs_a, k, B, b_offs, n, [beta] * batch, ref, c_offs, n, batch, wide=True)
+            outs = []
+            for route in (0, 0x40000):
+                dC = torch.from_numpy(C).to(dtype).cuda()
+                lib.set_tuning(route, 0)
+                try:
+                    gb.gemmBatched(gb.Layout.RowMajor, gb.Transpose.NoTrans, gb.Transpose.NoTrans, m, n, k,
+                                   [0.5] * batch, dA, offs_a, k, dB, b_offs, n, [beta] * batch, dC, c_offs, n, batch)
+                    torch.cuda.synchronize()
+                finally:
+                    lib.set_tuning(0, 0)
+                got = dC.float().cpu().numpy()
+                assert (rel_fro(got, ref) <= FP32_TOL) if dtype == torch.float32 else (max_rel(got, ref) <= HALF_TOL)
+                outs.append(got)
+            if dtype == torch.float32:
+                assert rel_fro(outs[0], outs[1]) <= FP32_TOL
+            else:
+                assert max_rel(outs[0], outs[1]) <= HALF_TOL
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_gemm_batched_offset_tables(dtype):
     gb = _gb()
