@@ -494,12 +494,14 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
             const uint32_t sblk = d_stage + ewarp * 4096u;
             bool res_smem = false;
             if constexpr (RES) {
-                if (lane == 0) {
-                    const uint32_t bar = ptx::smem_u32(&res_bar[RES ? ewarp : 0][0]);
-                    ptx::mbar_arrive_expect_tx(bar, 4096u);
-                    ptx::tma_load_3d(sblk, &tmR, bar, x, y, z);
+                if (!(res_pending & 1u)) {  // not fetched ahead (see the channels-last call site)
+                    if (lane == 0) {
+                        const uint32_t bar = ptx::smem_u32(&res_bar[RES ? ewarp : 0][0]);
+                        ptx::mbar_arrive_expect_tx(bar, 4096u);
+                        ptx::tma_load_3d(sblk, &tmR, bar, x, y, z);
+                    }
+                    res_pending |= 1u;
                 }
-                res_pending |= 1u;
             }
             const uint32_t srow = sblk + lane * 128u;
             const uint32_t sx = static_cast<uint32_t>(lane) & 7u;
@@ -733,6 +735,23 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
                             const int colw = n0 + cbase + c0;
                             wide_block(trow5 + c0, colw, i0, p.d_batch_stride ? bd : 0, ncols5 - c0, 0.0f, p.bias ? p.bias + colw * 2 : nullptr,
                                        p.N - colw, relu5);
+                            if constexpr (RES) {
+                                // The block's store has been handed over: once it has read the staging block,
+                                // the residual box of this warp's block of the NEXT tile is fetched into it, so
+                                // that its latency runs beside the wait for that tile's accumulator.
+                                if (c0 + 64 >= ncols5) {
+                                    int rx = 0, ry = 0, rz = 0;
+                                    if (res_box(t + tile_step, 0, rx, ry, rz)) {
+                                        if (lane == 0) {
+                                            ptx::bulk_wait_group_read<0>();
+                                            const uint32_t bar = ptx::smem_u32(&res_bar[RES ? ewarp : 0][0]);
+                                            ptx::mbar_arrive_expect_tx(bar, 4096u);
+                                            ptx::tma_load_3d(d_stage + ewarp * 4096u, &tmR, bar, rx, ry, rz);
+                                        }
+                                        res_pending |= 1u;
+                                    }
+                                }
+                            }
                             c0 += 32;
                             continue;
                         }
