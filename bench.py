@@ -146,6 +146,22 @@ class ConvC2(Workload):
                       for _ in range(self.sets)]
         gdnn.conv2d_filter(self.X[j], self.W, self.Y[j], self.filt, bias=self.b, residual=self.R[j], activation="relu")
 
+    def step_nhwc(self, i, residual=False):
+        """The same convolution between channels-last tensors (profiling aid: --workload conv --layout
+        channels_last [--residual]); the copies and the filter packing are made once, outside the step."""
+        from dlf_b200 import gdnn
+        j = i % self.sets
+        if not hasattr(self, "Xn"):
+            self.Xn = [gdnn.nchw_to_nhwc(x) for x in self.X]
+            self.Wp = gdnn.pack_filters_nhwc(self.W)
+            o = self.filt.output_shape()
+            self.Yn = [torch.empty((o[0], o[2], o[3], o[1]), dtype=self.Y[0].dtype, device=self.Y[0].device) for _ in range(self.sets)]
+            g = torch.Generator(device=self.Y[0].device).manual_seed(3)
+            self.Rn = [torch.randn(self.Yn[0].shape, generator=g, device=self.Y[0].device).to(self.Y[0].dtype)
+                       for _ in range(self.sets)]
+        gdnn.conv2d_nhwc(self.Xn[j], self.Wp, self.Yn[j], self.filt, bias=self.b,
+                         residual=self.Rn[j] if residual else None, activation="relu" if residual else None)
+
     def step_no_workspace(self, i):
         """The same convolution through the C ABI with workspace = NULL (the filter bank is then
         gathered inside the main loop instead of being packed first)."""
@@ -868,7 +884,8 @@ def main():
     ap.add_argument("--shape", default="64,56,64,3,1,1", help="--workload conv: Cin,H,Cout,k,stride,pad")
     ap.add_argument("--dtype", default="f16", help="--workload conv: f16, bf16 or f32")
     ap.add_argument("--layout", default="both", choices=["both", "nchw", "channels_last"],
-                    help="--workload resnet_forward: which tensor layout between the operators to run")
+                    help="--workload resnet_forward: which tensor layout between the operators to run; --workload conv: "
+                         "channels_last times the channels-last entry")
     ap.add_argument("--residual", action="store_true", help="--workload conv: fuse a residual Add and ReLU")
     ap.add_argument("--tuning", type=lambda x: int(x, 0), default=0,
                     help="experiments: second argument of dlf_b200_set_tuning for the whole run")
@@ -920,10 +937,14 @@ def main():
                    dtype=args.dtype)
         w.setup(device, 0, w.sets_needed())
         n = steps if args.steps is not None else 20
-        ms, _, _ = time_steps(w.step_fused if args.residual else w.step, n, warmup, 1)
+        if args.layout == "channels_last":
+            fn = lambda i: w.step_nhwc(i, args.residual)
+        else:
+            fn = w.step_fused if args.residual else w.step
+        ms, _, _ = time_steps(fn, n, warmup, 1)
         sec = ms / 1e3 / n
         print(json.dumps({"workload": "conv", "shape": args.shape, "batch": w.shape["N"], "dtype": args.dtype,
-                          "residual_relu": bool(args.residual),
+                          "residual_relu": bool(args.residual), "layout": args.layout if args.layout != "both" else "nchw",
                           "us_per_step": sec * 1e6, "tflops": w.flops / sec / 1e12,
                           "algorithmic_bytes": w.bytes, "device_status": dlf_b200.device_status()}), flush=True)
         return
