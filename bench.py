@@ -484,6 +484,44 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
+NUMA_INFO = {}
+ORIGINAL_AFFINITY = set()
+
+
+def bind_to_gpu_numa_node(local):
+    """Runs this rank on the CPUs of the NUMA node its GPU hangs off, before any pinned host buffer
+    exists: pinned pages are placed where the allocating thread runs, and the end-to-end leg moves
+    100 MB per step and rank between them and the GPU - through the socket interconnect when they
+    sit on the other node. Only reads sysfs and sets this process's CPU affinity; any failure leaves
+    the process as it was. What was done is reported in the JSON line (`numa`)."""
+    info = {"bound": False}
+    try:
+        prop = torch.cuda.get_device_properties(local)
+        bus = "%04x:%02x:%02x.0" % (prop.pci_domain_id, prop.pci_bus_id, prop.pci_device_id)
+        info["pci"] = bus
+        with open("/sys/bus/pci/devices/%s/numa_node" % bus) as f:
+            node = int(f.read().strip())
+        info["gpu_node"] = node
+        if node < 0:
+            return info
+        with open("/sys/devices/system/node/node%d/cpulist" % node) as f:
+            cpus = set()
+            for part in f.read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = os.sched_getaffinity(0)
+        use = cpus & allowed
+        info["node_cpus"], info["allowed_cpus"] = len(cpus), len(allowed)
+        if use and use != allowed:
+            ORIGINAL_AFFINITY.update(allowed)  # the CPU baseline's own process gets all of them back
+            os.sched_setaffinity(0, use)
+            info["bound"] = True
+        info["cpus_used"] = len(use or allowed)
+    except Exception as e:  # no sysfs entry, no permission, an older torch: run unbound
+        info["error"] = repr(e)[:120]
+    return info
+
+
 def dist_setup(n_gpus):
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -492,9 +530,11 @@ def dist_setup(n_gpus):
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         torch.cuda.set_device(local)
+        NUMA_INFO.update(bind_to_gpu_numa_node(local))
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     else:
         torch.cuda.set_device(0)
+        NUMA_INFO.update(bind_to_gpu_numa_node(0))
     return rank, world, local
 
 
@@ -863,8 +903,10 @@ def cpu_baseline_subprocess():
     its OpenMP / BLAS thread pools are sized by its own environment (this process has long loaded
     its OpenMP runtime with whatever the launcher exported)."""
     env = {k: v for k, v in os.environ.items() if k not in ("OMP_NUM_THREADS", "DLF_B200_BENCH_ENV")}
+    orig = set(ORIGINAL_AFFINITY)
     res = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "reference", "--steps", "1",
-                          "--warmup", "0"], capture_output=True, text=True, env=env, timeout=600)
+                          "--warmup", "0"], capture_output=True, text=True, env=env, timeout=600,
+                         preexec_fn=(lambda: os.sched_setaffinity(0, orig)) if orig else None)
     for ln in reversed(res.stdout.splitlines()):
         if ln.startswith("{"):
             return json.loads(ln)["cpu_baseline"]
@@ -1005,6 +1047,12 @@ def main():
     if world > 1 and args.workload == "conv_c2" and not args.headline_only and not args.kernel_only:
         multi_gpu_extras = multi_gpu_workloads(table, device, peaks, world, rank)
 
+    numa_ranks = None
+    if world > 1:  # every rank's GPU node and whether it was bound, for the line rank 0 prints
+        import torch.distributed as dist
+        numa_ranks = [None] * world
+        dist.all_gather_object(numa_ranks, [NUMA_INFO.get("gpu_node"), NUMA_INFO.get("bound")])
+
     if rank != 0:
         if world > 1:
             import torch.distributed as dist
@@ -1049,6 +1097,9 @@ def main():
             "device_status": status, "clocks": sampler.summary(t0, t1), "parity_rel_fro_vs_oracle": parity}
     if e2e:
         line["e2e"] = e2e
+    line["numa"] = dict(NUMA_INFO)
+    if numa_ranks is not None:
+        line["numa"]["ranks"] = numa_ranks
 
     if world == 1 and not args.no_cpu_baseline and not args.kernel_only and hasattr(w, "cpu_reference"):
         try:
