@@ -62,7 +62,7 @@ def test_c_abi_argument_errors_without_a_device(built_lib):
     rc = L.dlf_b200_gemm_batched(32, 101, 111, 111, 4, 4, 4, al, p, offs, 4, p, offs, 4, al, p, offs,
                                  4, 2, None, 0, None)
     assert rc == -2050                                   # kInsufficientMemoryTemp
-    assert L.dlf_b200_gemm_batched_workspace_bytes(10) == 10 * 32
+    assert L.dlf_b200_gemm_batched_workspace_bytes(10) == 10 * 44    # 3 offset, 2 scalar and 3 index tables
     rc = L.dlf_b200_conv2d(32, 1, 3, 5, 5, 5, 5, 4, 2, 3, 3, 1, 1, 1, 1, 1, 1, 1, 1, p, p, None, p,
                            None, 0, None)
     assert rc == -1017                                   # channels not divisible by group
