@@ -530,6 +530,98 @@ void avgpool(const size_t batches, const size_t channels,
                         "dlf_b200_avgpool");
 }
 
+// Channels-last operators for an operator-list runtime that owns the tensors between its operators
+// (no counterpart in gpgpu::dnn, whose operators are NCHW): the same argument order as the NCHW
+// functions above, buffers (N, H, W, C), 16-bit T.
+enum class Layout4D { NHWC = DLF_B200_LAYOUT_NHWC, NCHW = DLF_B200_LAYOUT_NCHW };
+
+template <typename T>
+void nchw_to_nhwc(const size_t batches, const size_t channels, const size_t height, const size_t width,
+                  const Buffer<T>& x_buffer, Buffer<T>& y_buffer,
+                  const Queue& queue = current::queue(), Event* event = nullptr) {
+    using blas::BLASError;
+    using blas::StatusCode;
+    if (x_buffer.size() < batches * channels * height * width) throw BLASError(StatusCode::kInsufficientMemoryA);
+    if (y_buffer.size() < batches * height * width * ((channels + 7) / 8 * 8)) throw BLASError(StatusCode::kInsufficientMemoryC);
+    blas::detail::EventScope scope(queue, event);
+    blas::detail::raise(dlf_b200_nchw_to_nhwc(blas::PrecisionOf<T>::value, batches, channels, height, width,
+                                              x_buffer.unwrap(), y_buffer.unwrap(), queue.unwrap()),
+                        "dlf_b200_nchw_to_nhwc");
+}
+
+// OIHW filter bank -> the K-major operand conv2d_nhwc reads; `packed` holds at least
+// dlf_b200_nhwc_filter_elems(channels, num_kernels, kernel_h, kernel_w) elements. Done once per layer.
+template <typename T>
+void pack_filters_nhwc(const size_t channels, const size_t num_kernels, const size_t kernel_h, const size_t kernel_w,
+                       const Buffer<T>& kernel_buffer, Buffer<T>& packed,
+                       const Queue& queue = current::queue(), Event* event = nullptr) {
+    using blas::BLASError;
+    using blas::StatusCode;
+    if (kernel_buffer.size() < num_kernels * channels * kernel_h * kernel_w) throw BLASError(StatusCode::kInsufficientMemoryB);
+    if (packed.size() < dlf_b200_nhwc_filter_elems(channels, num_kernels, kernel_h, kernel_w))
+        throw BLASError(StatusCode::kInsufficientMemoryC);
+    blas::detail::EventScope scope(queue, event);
+    blas::detail::raise(dlf_b200_pack_filters_nhwc(blas::PrecisionOf<T>::value, channels, num_kernels, kernel_h, kernel_w,
+                                                   kernel_buffer.unwrap(), packed.unwrap(), queue.unwrap()),
+                        "dlf_b200_pack_filters_nhwc");
+}
+
+template <typename T>
+void conv2d_nhwc(const size_t batches, const size_t channels,
+                 const size_t height, const size_t width,
+                 const size_t output_h, const size_t output_w,
+                 const size_t num_kernels,
+                 const size_t kernel_h, const size_t kernel_w,
+                 const size_t pad_top, const size_t pad_left,
+                 const size_t pad_bottom, const size_t pad_right,
+                 const size_t stride_h, const size_t stride_w,
+                 const size_t dilation_h, const size_t dilation_w,
+                 const Buffer<T>& im_buffer, const Buffer<T>& packed_kernel_buffer,
+                 Buffer<T>& result_buffer,
+                 const Queue& queue = current::queue(), Event* event = nullptr,
+                 const Buffer<T>* bias = nullptr, const Buffer<T>* residual = nullptr,
+                 const int activation = DLF_B200_ACT_NONE, const Layout4D result_layout = Layout4D::NHWC) {
+    using blas::BLASError;
+    using blas::StatusCode;
+    if (im_buffer.size() < batches * channels * height * width) throw BLASError(StatusCode::kInsufficientMemoryA);
+    if (packed_kernel_buffer.size() < dlf_b200_nhwc_filter_elems(channels, num_kernels, kernel_h, kernel_w))
+        throw BLASError(StatusCode::kInsufficientMemoryB);
+    if (result_buffer.size() < batches * num_kernels * output_h * output_w) throw BLASError(StatusCode::kInsufficientMemoryC);
+    if (bias && bias->size() < num_kernels) throw BLASError(StatusCode::kInvalidValue);
+    if (residual && residual->size() < batches * num_kernels * output_h * output_w) throw BLASError(StatusCode::kInvalidValue);
+    blas::detail::EventScope scope(queue, event);
+    blas::detail::raise(dlf_b200_conv2d_nhwc(blas::PrecisionOf<T>::value, batches, channels, height, width, output_h,
+                                             output_w, num_kernels, kernel_h, kernel_w, pad_top, pad_left, pad_bottom,
+                                             pad_right, stride_h, stride_w, dilation_h, dilation_w, im_buffer.unwrap(),
+                                             packed_kernel_buffer.unwrap(), bias ? bias->unwrap() : nullptr,
+                                             residual ? residual->unwrap() : nullptr, activation, result_buffer.unwrap(),
+                                             static_cast<int>(result_layout), queue.unwrap()),
+                        "dlf_b200_conv2d_nhwc");
+}
+
+// max (average == false) or average pooling between channels-last buffers
+template <typename T>
+void pool_nhwc(const bool average, const bool count_include_pad,
+               const size_t batches, const size_t channels,
+               const size_t height, const size_t width,
+               const size_t output_h, const size_t output_w,
+               const size_t kernel_h, const size_t kernel_w,
+               const size_t pad_top, const size_t pad_left,
+               const size_t stride_h, const size_t stride_w,
+               const Buffer<T>& x_buffer, Buffer<T>& y_buffer,
+               const Queue& queue = current::queue(), Event* event = nullptr) {
+    using blas::BLASError;
+    using blas::StatusCode;
+    if (x_buffer.size() < batches * channels * height * width) throw BLASError(StatusCode::kInsufficientMemoryA);
+    if (y_buffer.size() < batches * channels * output_h * output_w) throw BLASError(StatusCode::kInsufficientMemoryC);
+    blas::detail::EventScope scope(queue, event);
+    blas::detail::raise(dlf_b200_pool_nhwc(blas::PrecisionOf<T>::value, average ? 1 : 0, count_include_pad ? 1 : 0, batches,
+                                           channels, height, width, output_h, output_w, kernel_h, kernel_w, pad_top,
+                                           pad_left, stride_h, stride_w, x_buffer.unwrap(), y_buffer.unwrap(),
+                                           queue.unwrap()),
+                        "dlf_b200_pool_nhwc");
+}
+
 }  // namespace dnn
 }  // namespace gpgpu
 }  // namespace dlf_b200

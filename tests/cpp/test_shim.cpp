@@ -95,6 +95,38 @@ static void conv_bias_golden() {
     CHECK(host(dY2) == Yf);
 }
 
+static void channels_last_chain() {
+    // 8 channels of ones, 3x3 filter bank of ones over 8 channels, pad 1 on a 4 x 4 image: every output
+    // is 8 x (taps inside the image) + bias, exactly representable in fp16. Through the channels-last
+    // entries: copy, packed filters, convolution with both output layouts, then a 2 x 2 max pool.
+    const size_t N = 1, C = 8, H = 4, W = 4, Co = 8;
+    std::vector<__half> X(N * C * H * W, __float2half(1.0f)), Wt(Co * C * 9, __float2half(1.0f)), b(Co);
+    for (size_t i = 0; i < Co; ++i) b[i] = __float2half(static_cast<float>(i));
+    auto dX = dev(X), dW = dev(Wt), dB = dev(b);
+    Buffer<__half> dXn(N * H * W * C), dWp(dlf_b200_nhwc_filter_elems(C, Co, 3, 3)), dYn(N * H * W * Co), dYc(N * Co * H * W);
+    dnn::nchw_to_nhwc<__half>(N, C, H, W, dX, dXn);
+    dnn::pack_filters_nhwc<__half>(C, Co, 3, 3, dW, dWp);
+    const unsigned long long launches0 = dlf_b200_launch_count();
+    dnn::conv2d_nhwc<__half>(N, C, H, W, H, W, Co, 3, 3, 1, 1, 1, 1, 1, 1, 1, 1, dXn, dWp, dYn, current::queue(), nullptr, &dB);
+    CHECK(dlf_b200_launch_count() - launches0 == 1);  // no scratch, no copy: one launch
+    dnn::conv2d_nhwc<__half>(N, C, H, W, H, W, Co, 3, 3, 1, 1, 1, 1, 1, 1, 1, 1, dXn, dWp, dYc, current::queue(), nullptr, &dB,
+                             nullptr, DLF_B200_ACT_NONE, dnn::Layout4D::NCHW);
+    const auto yn = host(dYn), yc = host(dYc);
+    for (size_t h = 0; h < H; ++h)
+        for (size_t w = 0; w < W; ++w) {
+            const int th = 3 - (h == 0) - (h == H - 1), tw = 3 - (w == 0) - (w == W - 1);
+            for (size_t co = 0; co < Co; ++co) {
+                const float want = 8.0f * th * tw + static_cast<float>(co);
+                CHECK(__half2float(yn[(h * W + w) * Co + co]) == want);
+                CHECK(__half2float(yc[(co * H + h) * W + w]) == want);
+            }
+        }
+    Buffer<__half> dP(N * 2 * 2 * Co);
+    dnn::pool_nhwc<__half>(false, false, N, Co, H, W, 2, 2, 2, 2, 0, 0, 2, 2, dYn, dP);
+    const auto pooled = host(dP);
+    for (size_t co = 0; co < Co; ++co) CHECK(__half2float(pooled[co]) == 72.0f + static_cast<float>(co));  // max of the top-left 2 x 2: the interior 9-tap pixel
+}
+
 static void maxpool_golden() {
     // TEST(MaxPool, basic_2d_with_padding), dlf/test/DNNTest.cpp:625-644
     std::vector<float> X(25);
@@ -213,6 +245,7 @@ static void errors() {
 int main() {
     gemm_golden();
     conv_bias_golden();
+    channels_last_chain();
     maxpool_golden();
     batched();
     temporary_pool_is_lifo();
