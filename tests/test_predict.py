@@ -216,6 +216,53 @@ def test_shape_inference_rules_and_refusals():
         P.infer_shapes(bad)
 
 
+def _layout_names(graph, dtype=torch.float16):
+    """Names of the values a predictor of ``dtype`` would keep channels-last (no device needed: the
+    assignment only looks at the graph)."""
+    P.infer_shapes(graph)
+    P.optimize(graph)
+    pred = object.__new__(P.Predictor)
+    pred.dtype = dtype
+    ids = pred._assign_layouts(graph)
+    names = {}
+    for n in graph.nodes:
+        names[id(n.output(0))] = n.output(0).name
+    return {names[i] for i in ids}
+
+
+def test_channels_last_assignment_follows_the_readers():
+    # every operator of the residual network after the stem's pool reads and writes channels-last,
+    # except what ends in the NCHW graph output: the last block's residual chain
+    got = _layout_names(small_resnet(2, 32, np.random.default_rng(0)))
+    assert got == {"b1.c1", "b1.c2", "b2.c1", "b2.c2"}
+    # with only the logits as output, the whole trunk is channels-last; the 3-channel stem is not
+    # (its input has 3 channels) and neither is its pool (a pooling follows its input's layout)
+    g = small_resnet(2, 32, np.random.default_rng(0))
+    g.outputs = g.outputs[:1]
+    got = _layout_names(g)
+    assert got == {"b1.c1", "b1.c2", "b1.c3", "b1.down", "b2.c1", "b2.c2", "b2.c3"}
+    # fp32 predictors never use the channels-last entries: decided before the assignment runs
+    rng = np.random.default_rng(1)
+    g = P.Graph()
+    x = g.addInput("x", P.DataType.FLOAT, (1, 16, 8, 8))
+    a = _conv(g, x, "a", 16, 3, 1, 1, rng, bn=False, cin=16)          # channels-last: read by b and by the pool
+    b = _conv(g, a, "b", 12, 1, 1, 0, rng, bn=False, cin=16)          # 12 output channels: not a multiple of 8 -> NCHW
+    mp = g.append("MaxPool", kernel_shape=[2, 2], strides=[2, 2])
+    mp.addInput(a)
+    c = _conv(g, mp.addOutput("p"), "c", 8, 1, 1, 0, rng, bn=False, cin=16)
+    g.addOutput(b)
+    g.addOutput(c)
+    assert _layout_names(g) == {"a", "p"}
+    # a value that a non-native convolution reads (grouped) must stay NCHW, and so must what feeds its pool
+    g = P.Graph()
+    x = g.addInput("x", P.DataType.FLOAT, (1, 16, 8, 8))
+    a = _conv(g, x, "a", 16, 3, 1, 1, rng, bn=False, cin=16)
+    n = g.append("Conv", group=2, kernel_shape=[1, 1])
+    n.addInput(a).addInput(g.addInitializer("gw", np.ones((8, 8, 1, 1), np.float32)))
+    g.addOutput(n.addOutput("grouped"))
+    assert _layout_names(g) == set()
+
+
 def test_a_relu_that_follows_no_convolution_is_refused():
     g = P.Graph()
     x = g.addInput("x", P.DataType.FLOAT, (1, 2, 4, 4))
