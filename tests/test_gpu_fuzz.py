@@ -177,3 +177,43 @@ def test_random_strided_batched_gemm(seed):
         if not row:
             got = got.transpose(0, 2, 1)
         assert _close(got, ref, dt), cfg
+
+
+@pytest.mark.parametrize("seed", range(2))
+def test_random_aligned_batched_gemm_strided_and_through_tables(seed):
+    """16-bit batched products whose bases, leading dimensions and strides are 16-byte multiples - the
+    shapes that reach the tensor-map-fed kernel, its transposed form for short K, and, through
+    gemmBatched with the batch entries in a shuffled order, the indexed batch coordinate."""
+    from dlf_b200 import gblas as gb
+    rng = np.random.default_rng(900 + seed)
+    for _ in range(40):
+        dt = [torch.float16, torch.bfloat16][rng.integers(0, 2)]
+        m, n = int(rng.integers(1, 60)) * 8, int(rng.integers(1, 60)) * 8
+        k = int(rng.choice([8, 16, 40, 64, 72, 128, 200, 256, 264, 512]))
+        batch = int(rng.integers(1, 6))
+        layout = [gb.Layout.RowMajor, gb.Layout.ColMajor][rng.integers(0, 2)]
+        ta = [gb.Transpose.NoTrans, gb.Transpose.Trans][rng.integers(0, 2)]
+        tb = [gb.Transpose.NoTrans, gb.Transpose.Trans][rng.integers(0, 2)]
+        a1, a2, b1, b2, c1, c2 = gb._dims(layout, ta, tb, m, n, k)
+        lda, ldb, ldc = (d + 8 * int(rng.integers(0, 2)) for d in (a1, b1, c1))
+        sa = lda * a2 + 8 * int(rng.integers(0, 3))
+        sb = 0 if rng.integers(0, 4) == 0 else ldb * b2 + 8 * int(rng.integers(0, 3))  # 0: one B for every product
+        sc = ldc * c2 + 8 * int(rng.integers(0, 3))
+        alpha, beta = float(rng.choice([1.0, 0.5, -2.0])), float(rng.choice([0.0, 0.0, 0.5]))
+        tables = bool(rng.integers(0, 2))
+        cfg = dict(dt=str(dt), m=m, n=n, k=k, batch=batch, layout=int(layout), ta=int(ta), tb=int(tb), lda=lda, ldb=ldb,
+                   ldc=ldc, sa=sa, sb=sb, sc=sc, alpha=alpha, beta=beta, tables=tables)
+        A = _rt(rng.uniform(-1, 1, sa * batch).astype(np.float32), dt)
+        B = _rt(rng.uniform(-1, 1, max(sb, ldb * b2) * batch).astype(np.float32), dt)
+        C = _rt(rng.normal(size=sc * batch).astype(np.float32), dt)
+        ref = C.copy()
+        oracle.gblas_sgemm_strided_batched(int(layout), int(ta), int(tb), m, n, k, alpha, A, 0, lda, sa, B, 0, ldb, sb,
+                                           beta, ref, 0, ldc, sc, batch, wide=True)
+        dA, dB, dC = (torch.from_numpy(x).to(dt).cuda() for x in (A, B, C))
+        if tables:
+            perm = [int(p) for p in rng.permutation(batch)]
+            gb.gemmBatched(layout, ta, tb, m, n, k, [alpha] * batch, dA, [p * sa for p in perm], lda, dB,
+                           [p * sb for p in perm], ldb, [beta] * batch, dC, [p * sc for p in perm], ldc, batch)
+        else:
+            gb.gemmStridedBatched(layout, ta, tb, m, n, k, alpha, dA, 0, lda, sa, dB, 0, ldb, sb, beta, dC, 0, ldc, sc, batch)
+        assert _close(dC.float().cpu().numpy(), ref, dt), cfg
