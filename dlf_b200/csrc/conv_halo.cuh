@@ -163,7 +163,9 @@ __global__ void __launch_bounds__(kHaloThreads, 1)
             const uint32_t tacc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
             const long long e_img = static_cast<long long>(img) * p.out_img_stride + static_cast<long long>(co) * p.P;
             // blocks (row r, columns c0 .. c0+31 of that row): the warp sets take them in turn
-            for (int idx = eset; idx < rows * cpr; idx += kHaloEpiSets) {
+            // (a lane quadrant whose 32 channels all lie beyond Cout has nothing to write)
+            const int nblocks = co0 + q * 32 < p.Cout ? rows * cpr : 0;
+            for (int idx = eset; idx < nblocks; idx += kHaloEpiSets) {
                 const int r = idx / cpr;
                 const int c0 = (idx - r * cpr) * 32;
                 uint32_t v[32];

@@ -184,7 +184,10 @@ __global__ void __launch_bounds__(kSmallThreads, 1)
             const uint32_t tacc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
             const long long e_img = static_cast<long long>(img) * p.out_img_stride + static_cast<long long>(co) * p.P;
             // blocks (row r, columns c0 .. c0+31 of that row): the warp sets take them in turn
-            for (int idx = eset; idx < rows * cpr; idx += kSmallEpiSets) {
+            // (a lane quadrant whose 32 channels all lie beyond Cout - two of the four with 64 output
+            // channels - has nothing to write: its blocks would only occupy the copy unit)
+            const int nblocks = q * 32 < p.Cout ? rows * cpr : 0;
+            for (int idx = eset; idx < nblocks; idx += kSmallEpiSets) {
                 const int r = idx / cpr;
                 const int c0 = (idx - r * cpr) * 32;
                 uint32_t v[32];
