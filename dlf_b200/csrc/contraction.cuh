@@ -336,7 +336,10 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
     // values, [column][row] with rows contiguous (64-byte lines)
     __shared__ __align__(128) uint8_t d_stage_pair[PAIR ? 8 * 2 * 2048 : 16];  // CTA pairs keep their staging static
 
-    const int warp = threadIdx.x >> 5;
+    // the warp index through a shuffle: the compiler then knows that it is the same in every lane,
+    // keeps the role branches and what they compute on the uniform datapath, and the descriptors of
+    // the UMMA issuer never pass through per-lane registers
+    const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
     const int lane = threadIdx.x & 31;
     const int BN = p.BN;
     const int S = p.stages;
@@ -1017,7 +1020,11 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
         }
     } else if (warp == kMmaWarp) {
         // ------------------------------------------------------------ UMMA issuer
-        if (lane == 0 && rank == 0) {
+        // The whole warp runs the loop, converged, and one elected lane issues: loop state and
+        // descriptors then live in uniform registers. (Issued from inside an `if (lane == 0)` region
+        // every UMMA paid for moving its operands over from per-lane registers: a 64-column UMMA
+        // cost as much issue time as a 256-column one.)
+        if (rank == 0) {
             const uint32_t idesc =
                 ptx::make_idesc(p.fmt == FMT_F32 ? 2u : static_cast<uint32_t>(p.fmt),
                                 p.a.k_major ? 0u : 1u, p.b.k_major ? 0u : 1u, PAIR ? 2 * kBM : kBM, BN);
@@ -1037,12 +1044,12 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
             uint32_t stage = 0, phase = 0;
             uint32_t it = 0;
             bool ok = true;
-            DLF_CLK_DECL(true)
+            DLF_CLK_DECL(lane == 0)
             for (int t = tile0; ok && t < p.total_tiles; t += tile_step, ++it) {
                 const uint32_t buf = it & 1u;
                 const uint32_t tphase = (it >> 1) & 1u;
                 DLF_CLK_ADD(4);  // issue
-                if (!ptx::mbar_wait_bounded(ptx::smem_u32(&tempty_bar[buf]), tphase ^ 1u, abort_p, wait_limit)) {
+                if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(ptx::smem_u32(&tempty_bar[buf]), tphase ^ 1u, abort_p, wait_limit))) {
                     ok = false;
                     break;
                 }
@@ -1051,13 +1058,14 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
                 const uint32_t d_tmem = tmem_base + buf * BN;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     DLF_CLK_ADD(4);
-                    if (!ptx::mbar_wait_bounded(ptx::smem_u32(&full_bar[stage]), phase, abort_p, wait_limit)) {
+                    if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(ptx::smem_u32(&full_bar[stage]), phase, abort_p, wait_limit))) {
                         ok = false;
                         break;
                     }
                     ptx::tc_fence_after();
                     DLF_CLK_ADD(3);  // waiting for operands
                     const uint32_t st_units = (stage * stage_bytes) >> 4;
+                    if (ptx::elect_one()) {
 #pragma unroll
                     for (int ks = 0; ks < BK / UMMA_K; ++ks) {
                         const uint64_t da = da0 + (st_units + ((ks * a_step) >> 4));
@@ -1079,12 +1087,14 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
                     } else {
                         ptx::umma_commit(ptx::smem_u32(&empty_bar[stage]));
                     }
+                    }
+                    __syncwarp();
                     if (++stage == static_cast<uint32_t>(S)) {
                         stage = 0;
                         phase ^= 1u;
                     }
                 }
-                if (ok && !p.skip_tile_commit) {
+                if (ok && !p.skip_tile_commit && ptx::elect_one()) {
                     if constexpr (PAIR) {  // both CTAs' epilogue warps read their half of the tile
                         ptx::umma_commit_pair(ptx::smem_u32(&tfull_bar[buf]));
                         ptx::umma_commit_pair(ptx::map_to_cta(ptx::smem_u32(&tfull_bar[buf]), 1u));
@@ -1096,17 +1106,22 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
         }
     } else if (USE_TMA && warp == kTmaWarp) {
         // ------------------------------------------------------------ TMA producer
-        if (lane == 0) {
+        // The whole warp runs the loop, converged, and one lane issues the copies: coordinates,
+        // addresses and loop state then stay in uniform registers, which is where the copy
+        // instructions take them from (see the UMMA issuer).
+        {
+            const bool leader = ptx::elect_one();
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            DLF_CLK_DECL(true)
+            DLF_CLK_DECL(lane == 0)
             for (int t = tile0; ok && t < p.total_tiles; t += tile_step) {
                 int b, m0, n0;
                 decode_tile(p, t, b, m0, n0, tile_rows);
                 m0 += row_off;
                 n0 += PAIR ? static_cast<int>(rank) * b_rows : 0;  // this CTA's share of the Bu rows
-                const int ba = p.a.batch_stride ? (p.a_idx ? p.a_idx[b] : b) : 0;
-                const int bb = p.b.batch_stride ? (p.b_idx ? p.b_idx[b] : b) : 0;
+                // (table entries come from memory: the shuffle tells the compiler that they are uniform)
+                const int ba = p.a.batch_stride ? (p.a_idx ? __shfl_sync(0xffffffffu, p.a_idx[b], 0) : b) : 0;
+                const int bb = p.b.batch_stride ? (p.b_idx ? __shfl_sync(0xffffffffu, p.b_idx[b], 0) : b) : 0;
                 // im2col-mode loads: base pixel of the tile's first filter window
                 int cl_n = 0, cl_h = 0, cl_w = 0;
                 if (!PAIR && p.a_cl == 1) {
@@ -1120,8 +1135,8 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
                 int cl_cb = 0, cl_kh = 0, cl_kw = 0;  // channel block and filter tap of kb
                 for (int kb = 0; kb < num_kb; ++kb) {
                     DLF_CLK_ADD(6);  // issue
-                    if (!ptx::mbar_wait_bounded(ptx::smem_u32(&empty_bar[stage]), phase ^ 1u,
-                                                abort_p, wait_limit)) {
+                    if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(ptx::smem_u32(&empty_bar[stage]), phase ^ 1u,
+                                                                        abort_p, wait_limit))) {
                         ok = false;
                         break;
                     }
@@ -1131,11 +1146,11 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
                     if (!PAIR && p.cl_swap && p.a_cl == 1) {
                         // swapped roles: A = filter bank (tiled), B = activations (im2col mode, BN windows)
                         const uint32_t bar = ptx::smem_u32(&full_bar[stage]);
-                        ptx::mbar_arrive_expect_tx(bar, A_TILE + b_tile);
+                        if (leader) ptx::mbar_arrive_expect_tx(bar, A_TILE + b_tile);
                         DLF_CLK_ADD(6);
-                        ptx::tma_load_3d(sA, &tmA, bar, kb * BK, m0, 0);
+                        if (leader) ptx::tma_load_3d(sA, &tmA, bar, kb * BK, m0, 0);
                         DLF_CLK_ADD(7);  // first copy of the stage handed over
-                        ptx::tma_load_im2col_4d(sB, &tmB, bar, cl_cb * BK, cl_w, cl_h, cl_n,
+                        if (leader) ptx::tma_load_im2col_4d(sB, &tmB, bar, cl_cb * BK, cl_w, cl_h, cl_n,
                                                 static_cast<unsigned short>(cl_kw * p.g.dw),
                                                 static_cast<unsigned short>(cl_kh * p.g.dh));
                         DLF_CLK_ADD(8);  // second copy handed over
@@ -1154,13 +1169,13 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
                     }
                     if (!PAIR && p.a_cl == 1) {
                         const uint32_t bar = ptx::smem_u32(&full_bar[stage]);
-                        ptx::mbar_arrive_expect_tx(bar, A_TILE + b_tile);
+                        if (leader) ptx::mbar_arrive_expect_tx(bar, A_TILE + b_tile);
                         DLF_CLK_ADD(6);
-                        ptx::tma_load_im2col_4d(sA, &tmA, bar, cl_cb * BK, cl_w, cl_h, cl_n,
+                        if (leader) ptx::tma_load_im2col_4d(sA, &tmA, bar, cl_cb * BK, cl_w, cl_h, cl_n,
                                                 static_cast<unsigned short>(cl_kw * p.g.dw),
                                                 static_cast<unsigned short>(cl_kh * p.g.dh));
                         DLF_CLK_ADD(7);
-                        ptx::tma_load_3d(sB, &tmB, bar, kb * BK, n0, bb);
+                        if (leader) ptx::tma_load_3d(sB, &tmB, bar, kb * BK, n0, bb);
                         DLF_CLK_ADD(8);
                         if (++cl_cb == p.cl_cblocks) {
                             cl_cb = 0;
@@ -1179,35 +1194,35 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
                         // both CTAs' copies are counted on rank 0's barrier, which rank 0 arms
                         // with the bytes of the two CTAs together
                         const uint32_t bar = ptx::map_to_cta(ptx::smem_u32(&full_bar[stage]), 0u);
-                        if (rank == 0) ptx::mbar_arrive_expect_tx(ptx::smem_u32(&full_bar[stage]), 2u * (A_TILE + b_tile));
+                        if (leader && rank == 0) ptx::mbar_arrive_expect_tx(ptx::smem_u32(&full_bar[stage]), 2u * (A_TILE + b_tile));
                         if (p.a.k_major) {
-                            ptx::tma_load_3d_pair(sA, &tmA, bar, kb * BK, m0, ba);
+                            if (leader) ptx::tma_load_3d_pair(sA, &tmA, bar, kb * BK, m0, ba);
                         } else {
                             for (int g = 0; g < kBM / E; ++g)
-                                ptx::tma_load_3d_pair(sA + g * BK * 128, &tmA, bar, m0 + g * E, kb * BK, ba);
+                                if (leader) ptx::tma_load_3d_pair(sA + g * BK * 128, &tmA, bar, m0 + g * E, kb * BK, ba);
                         }
                         if (p.b.k_major) {
-                            ptx::tma_load_3d_pair(sB, &tmB, bar, kb * BK, n0, bb);
+                            if (leader) ptx::tma_load_3d_pair(sB, &tmB, bar, kb * BK, n0, bb);
                         } else {
                             for (int g = 0; g < b_rows / E; ++g)
-                                ptx::tma_load_3d_pair(sB + g * BK * 128, &tmB, bar, n0 + g * E, kb * BK, bb);
+                                if (leader) ptx::tma_load_3d_pair(sB + g * BK * 128, &tmB, bar, n0 + g * E, kb * BK, bb);
                         }
                     } else {
                         const uint32_t bar = ptx::smem_u32(&full_bar[stage]);
-                        ptx::mbar_arrive_expect_tx(bar, A_TILE + b_tile);
+                        if (leader) ptx::mbar_arrive_expect_tx(bar, A_TILE + b_tile);
                         DLF_CLK_ADD(6);
                         if (p.a.k_major) {
-                            ptx::tma_load_3d(sA, &tmA, bar, kb * BK, m0, ba);
+                            if (leader) ptx::tma_load_3d(sA, &tmA, bar, kb * BK, m0, ba);
                         } else {
                             for (int g = 0; g < kBM / E; ++g)
-                                ptx::tma_load_3d(sA + g * BK * 128, &tmA, bar, m0 + g * E, kb * BK, ba);
+                                if (leader) ptx::tma_load_3d(sA + g * BK * 128, &tmA, bar, m0 + g * E, kb * BK, ba);
                         }
                         DLF_CLK_ADD(7);
                         if (p.b.k_major) {
-                            ptx::tma_load_3d(sB, &tmB, bar, kb * BK, n0, bb);
+                            if (leader) ptx::tma_load_3d(sB, &tmB, bar, kb * BK, n0, bb);
                         } else {
                             for (int g = 0; g < BN / E; ++g)
-                                ptx::tma_load_3d(sB + g * BK * 128, &tmB, bar, n0 + g * E, kb * BK, bb);
+                                if (leader) ptx::tma_load_3d(sB + g * BK * 128, &tmB, bar, n0 + g * E, kb * BK, bb);
                         }
                         DLF_CLK_ADD(8);
                     }
