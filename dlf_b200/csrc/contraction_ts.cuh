@@ -289,7 +289,8 @@ __global__ void __launch_bounds__(kTsThreads, 1)
     __shared__ int abort_flag;
     __shared__ int epi_ok[2][4];  // TMA-store epilogue: outcome of each epilogue warp's wait for the tile
 
-    const int warp = threadIdx.x >> 5;
+    // (through a shuffle: the compiler then knows that the warp index is uniform)
+    const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
     const int lane = threadIdx.x & 31;
     const int BN = p.BN;
     // The A slots live in tensor memory and the B stages in shared memory: the two rings have their
@@ -851,25 +852,27 @@ __global__ void __launch_bounds__(kTsThreads, 1)
         if (tp.b_tma) {
             if (warp == kTsLoaderWarp0) {
                 // TMA producer: raw fp32 tile of Bu into the hi image of the stage
-                if (lane == 0) {
-                    ptx::tma_prefetch_desc(&tmB);
+                // (the whole warp runs the loop, converged; one lane issues: see the UMMA issuer)
+                {
+                    const bool leader = ptx::elect_one();
+                    if (leader) ptx::tma_prefetch_desc(&tmB);
                     for (int t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x) {
                         int b, m0, n0;
                         decode_tile(p, t, b, m0, n0);
                         const int bb = p.b.batch_stride ? b : 0;
                         for (int kb = 0; kb < num_kb; ++kb) {
-                            if (!ptx::mbar_wait_bounded(ptx::smem_u32(&empty_b[s]), ph ^ 1u, abort_p, wait_limit)) {
+                            if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(ptx::smem_u32(&empty_b[s]), ph ^ 1u, abort_p, wait_limit))) {
                                 ok = false;
                                 break;
                             }
                             const uint32_t bar = ptx::smem_u32(&raw_b[s]);
                             const uint32_t sB = smem0 + s * stage_bytes;
-                            ptx::mbar_arrive_expect_tx(bar, b_tile);
+                            if (leader) ptx::mbar_arrive_expect_tx(bar, b_tile);
                             if (p.b.k_major) {
-                                ptx::tma_load_3d(sB, &tmB, bar, kb * BK, n0, bb);
+                                if (leader) ptx::tma_load_3d(sB, &tmB, bar, kb * BK, n0, bb);
                             } else {
                                 for (int g = 0; g < BN / BK; ++g)
-                                    ptx::tma_load_3d(sB + g * BK * 128, &tmB, bar, n0 + g * BK, kb * BK, bb);
+                                    if (leader) ptx::tma_load_3d(sB + g * BK * 128, &tmB, bar, n0 + g * BK, kb * BK, bb);
                             }
                             if (++s == static_cast<uint32_t>(SB)) {
                                 s = 0;
@@ -997,7 +1000,9 @@ __global__ void __launch_bounds__(kTsThreads, 1)
         }
     } else if (warp == kTsMmaWarp) {
         // ------------------------------------------------------------ UMMA issuer
-        if (lane == 0) {
+        // The whole warp runs the loop, converged, and one elected lane issues, so that loop state
+        // and descriptors stay in uniform registers (see contraction.cuh).
+        {
             const uint32_t idesc =
                 ptx::make_idesc(p.fmt == FMT_F32 ? 2u : static_cast<uint32_t>(p.fmt), 0u,
                                 p.b.k_major ? 0u : 1u, kBM, BN);
@@ -1012,7 +1017,7 @@ __global__ void __launch_bounds__(kTsThreads, 1)
             const int kc = tp.kc_blocks > 0 ? tp.kc_blocks : num_kb;
             for (int t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x) {
                 for (int kb0 = 0; ok && kb0 < num_kb; kb0 += kc) {  // one accumulator per K-chunk
-                    if (!ptx::mbar_wait_bounded(ptx::smem_u32(&tempty_bar[buf]), tphase ^ 1u, abort_p, wait_limit)) {
+                    if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(ptx::smem_u32(&tempty_bar[buf]), tphase ^ 1u, abort_p, wait_limit))) {
                         ok = false;
                         break;
                     }
@@ -1022,14 +1027,15 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                     for (int kb = kb0; kb < kb1; ++kb) {
                         // (a resident filter bank arrives once: only the first tile waits for it)
                         const bool wait_b = !tp.b_resident || t == static_cast<int>(blockIdx.x);
-                        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&full_a[s]), ph, abort_p, wait_limit) ||
-                            (wait_b && !ptx::mbar_wait_bounded(ptx::smem_u32(&full_b[sb]), phb, abort_p, wait_limit))) {
+                        if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(ptx::smem_u32(&full_a[s]), ph, abort_p, wait_limit) &&
+                                                         (!wait_b || ptx::mbar_wait_bounded(ptx::smem_u32(&full_b[sb]), phb, abort_p, wait_limit)))) {
                             ok = false;
                             break;
                         }
                         ptx::tc_fence_after();
                         const uint32_t st_units = (sb * stage_bytes) >> 4;
                         const uint32_t a_slot = tmem_base + a_col0 + s * A_COLS;
+                        if (ptx::elect_one()) {
 #pragma unroll
                         for (int ks = 0; ks < BK / UMMA_K; ++ks) {
                             const uint64_t db = db0 + (st_units + ((ks * b_step) >> 4));
@@ -1045,6 +1051,8 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                         }
                         ptx::umma_commit(ptx::smem_u32(&empty_a[s]));
                         if (!tp.b_resident) ptx::umma_commit(ptx::smem_u32(&empty_b[sb]));
+                        }
+                        __syncwarp();
                         if (++s == static_cast<uint32_t>(SA)) {
                             s = 0;
                             ph ^= 1u;
@@ -1054,7 +1062,8 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                             phb ^= 1u;
                         }
                     }
-                    if (ok && !p.skip_tile_commit) ptx::umma_commit(ptx::smem_u32(&tfull_bar[buf]));
+                    if (ok && !p.skip_tile_commit && ptx::elect_one()) ptx::umma_commit(ptx::smem_u32(&tfull_bar[buf]));
+                    __syncwarp();
                     if (++buf == static_cast<uint32_t>(nbuf)) {
                         buf = 0;
                         tphase ^= 1u;

@@ -95,7 +95,8 @@ __global__ void __launch_bounds__(kHaloThreads, 1)
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
 
-    const int warp = threadIdx.x >> 5;
+    // (through a shuffle: the compiler then knows that the warp index is uniform)
+    const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
     const int lane = threadIdx.x & 31;
     const int BN = p.BN;
     const int SA = p.a_stages, SH = p.h_stages;
@@ -219,7 +220,9 @@ __global__ void __launch_bounds__(kHaloThreads, 1)
         if (p.d_tma && lane == 0) ptx::bulk_wait_group<0>();
     } else if (warp == 4) {
         // ------------------------------------------------------------ UMMA issuer
-        if (lane == 0) {
+        // (the whole warp runs the loop, converged, and one elected lane issues: loop state and
+        // descriptors stay in uniform registers)
+        {
             const uint32_t idesc = ptx::make_idesc(static_cast<uint32_t>(p.fmt), 0u, 0u, kBM, BN);
             const uint64_t da0 = ptx::make_smem_desc(sA, 16u, 1024u, 2u);
             // operand B: unswizzled K-major; rows (halo positions) 16 bytes apart, the two 8-channel
@@ -230,29 +233,32 @@ __global__ void __launch_bounds__(kHaloThreads, 1)
             for (int t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x, ++it) {
                 const uint32_t buf = it & 1u;
                 const uint32_t tphase = (it >> 1) & 1u;
-                if (!ptx::mbar_wait_bounded(ptx::smem_u32(&tempty_bar[buf]), tphase ^ 1u, abort_p, wait_limit)) break;
+                if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(ptx::smem_u32(&tempty_bar[buf]), tphase ^ 1u, abort_p, wait_limit))) break;
                 ptx::tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BN;
                 for (int cb = 0; ok && cb < p.CB; ++cb) {
-                    if (!ptx::mbar_wait_bounded(ptx::smem_u32(&h_full[hs]), hph, abort_p, wait_limit)) {
+                    if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(ptx::smem_u32(&h_full[hs]), hph, abort_p, wait_limit))) {
                         ok = false;
                         break;
                     }
                     const uint32_t h_units = (hs * p.stage_bytes) >> 4;
                     int kh = 0, kw = 0;
                     for (int tap = 0; tap < taps; ++tap) {
-                        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&a_full[as]), aph, abort_p, wait_limit)) {
+                        if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(ptx::smem_u32(&a_full[as]), aph, abort_p, wait_limit))) {
                             ok = false;
                             break;
                         }
                         ptx::tc_fence_after();
                         const uint32_t a_units = (as * A_TILE) >> 4;
                         const uint32_t shift = static_cast<uint32_t>(kh * p.Wp + kw);
+                        if (ptx::elect_one()) {
 #pragma unroll
-                        for (int ks = 0; ks < 4; ++ks)
-                            ptx::umma_f16(d_tmem, da0 + (a_units + ks * 2), db0 + (h_units + 2 * ks * p.group_units + shift),
-                                          idesc, (cb | tap | ks) ? 1u : 0u);
-                        ptx::umma_commit(ptx::smem_u32(&a_empty[as]));
+                            for (int ks = 0; ks < 4; ++ks)
+                                ptx::umma_f16(d_tmem, da0 + (a_units + ks * 2), db0 + (h_units + 2 * ks * p.group_units + shift),
+                                              idesc, (cb | tap | ks) ? 1u : 0u);
+                            ptx::umma_commit(ptx::smem_u32(&a_empty[as]));
+                        }
+                        __syncwarp();
                         if (++as == static_cast<uint32_t>(SA)) {
                             as = 0;
                             aph ^= 1u;
@@ -263,18 +269,22 @@ __global__ void __launch_bounds__(kHaloThreads, 1)
                         }
                     }
                     if (!ok) break;
-                    ptx::umma_commit(ptx::smem_u32(&h_empty[hs]));
+                    if (ptx::elect_one()) ptx::umma_commit(ptx::smem_u32(&h_empty[hs]));
+                    __syncwarp();
                     if (++hs == static_cast<uint32_t>(SH)) {
                         hs = 0;
                         hph ^= 1u;
                     }
                 }
-                if (ok) ptx::umma_commit(ptx::smem_u32(&tfull_bar[buf]));
+                if (ok && ptx::elect_one()) ptx::umma_commit(ptx::smem_u32(&tfull_bar[buf]));
+                __syncwarp();
             }
         }
     } else if (warp == 5) {
         // ------------------------------------------------------------ copy producer
-        if (lane == 0) {
+        // (converged warp, one issuing lane, as the UMMA issuer)
+        {
+            const bool leader = ptx::elect_one();
             uint32_t as = 0, aph = 0, hs = 0, hph = 0;
             bool ok = true;
             const int CG = p.CB * 8;
@@ -285,7 +295,7 @@ __global__ void __launch_bounds__(kHaloThreads, 1)
                 const int oh0 = (rem / p.co_tiles) * p.R;
                 const int nrows = min(p.R + p.KH - 1, p.Hp - oh0);  // halo rows that exist
                 for (int cb = 0; ok && cb < p.CB; ++cb) {
-                    if (!ptx::mbar_wait_bounded(ptx::smem_u32(&h_empty[hs]), hph ^ 1u, abort_p, wait_limit)) {
+                    if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(ptx::smem_u32(&h_empty[hs]), hph ^ 1u, abort_p, wait_limit))) {
                         ok = false;
                         break;
                     }
@@ -295,23 +305,23 @@ __global__ void __launch_bounds__(kHaloThreads, 1)
                     // (64 -> 64 at 56x56: 207 vs 186 us)
                     const uint32_t hbar = ptx::smem_u32(&h_full[hs]);
                     const uint32_t bytes = static_cast<uint32_t>(nrows * p.Wp) * 16u;
-                    ptx::mbar_arrive_expect_tx(hbar, 8u * bytes);
+                    if (leader) ptx::mbar_arrive_expect_tx(hbar, 8u * bytes);
                     const uint32_t dst0 = sHalo + hs * p.stage_bytes;
                     for (int g = 0; g < 8; ++g)
-                        ptx::bulk_load(dst0 + g * p.group_units * 16u,
+                        if (leader) ptx::bulk_load(dst0 + g * p.group_units * 16u,
                                        p.xh + ((static_cast<long long>(img) * CG + cb * 8 + g) * p.Hp + oh0) * p.Wp * 16, bytes, hbar);
                     if (++hs == static_cast<uint32_t>(SH)) {
                         hs = 0;
                         hph ^= 1u;
                     }
                     for (int tap = 0; tap < taps; ++tap) {
-                        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&a_empty[as]), aph ^ 1u, abort_p, wait_limit)) {
+                        if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(ptx::smem_u32(&a_empty[as]), aph ^ 1u, abort_p, wait_limit))) {
                             ok = false;
                             break;
                         }
                         const uint32_t abar = ptx::smem_u32(&a_full[as]);
-                        ptx::mbar_arrive_expect_tx(abar, A_TILE);
-                        ptx::tma_load_3d(sA + as * A_TILE, &tmW, abar, (tap * p.CB + cb) * 64, co0, 0);
+                        if (leader) ptx::mbar_arrive_expect_tx(abar, A_TILE);
+                        if (leader) ptx::tma_load_3d(sA + as * A_TILE, &tmW, abar, (tap * p.CB + cb) * 64, co0, 0);
                         if (++as == static_cast<uint32_t>(SA)) {
                             as = 0;
                             aph ^= 1u;

@@ -123,7 +123,8 @@ __global__ void __launch_bounds__(kSmallThreads, 1)
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
 
-    const int warp = threadIdx.x >> 5;
+    // (through a shuffle: the compiler then knows that the warp index is uniform)
+    const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
     const int lane = threadIdx.x & 31;
     const int BN = p.BN;
     const int S = p.stages;
@@ -241,7 +242,9 @@ __global__ void __launch_bounds__(kSmallThreads, 1)
         if (p.d_tma && lane == 0) ptx::bulk_wait_group<0>();
     } else if (warp == 4) {
         // ------------------------------------------------------------ UMMA issuer
-        if (lane == 0) {
+        // (the whole warp runs the loop, converged, and one elected lane issues: loop state and
+        // descriptors stay in uniform registers)
+        {
             const uint32_t idesc = ptx::make_idesc(static_cast<uint32_t>(p.fmt), 0u, 0u, kBM, BN);
             const uint64_t da0 = ptx::make_smem_desc(sA, 16u, 1024u, 2u);
             // operand B: unswizzled K-major, rows 16 bytes apart, the two k-chunks of a UMMA 16 bytes apart too
@@ -249,19 +252,20 @@ __global__ void __launch_bounds__(kSmallThreads, 1)
             const int taps_per_phase = 8 / p.sw;                 // 16-byte pixels of a window in one phase
             const uint32_t phase_units = p.phase_bytes >> 4;     // 16-byte units between the phases of a stage
             const uint32_t kb_units = static_cast<uint32_t>(p.kb_rows * p.OWp);  // ... between the row pairs of k-blocks
-            bool ok = ptx::mbar_wait_bounded(ptx::smem_u32(&a_full), 0u, abort_p, wait_limit);
+            bool ok = __all_sync(0xffffffffu, ptx::mbar_wait_bounded(ptx::smem_u32(&a_full), 0u, abort_p, wait_limit));
             uint32_t stage = 0, phase = 0, it = 0;
             for (int t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x, ++it) {
                 const uint32_t buf = it & 1u;
                 const uint32_t tphase = (it >> 1) & 1u;
-                if (!ptx::mbar_wait_bounded(ptx::smem_u32(&tempty_bar[buf]), tphase ^ 1u, abort_p, wait_limit) ||
-                    !ptx::mbar_wait_bounded(ptx::smem_u32(&raw_full[stage]), phase, abort_p, wait_limit)) {
+                if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(ptx::smem_u32(&tempty_bar[buf]), tphase ^ 1u, abort_p, wait_limit) &&
+                                                 ptx::mbar_wait_bounded(ptx::smem_u32(&raw_full[stage]), phase, abort_p, wait_limit))) {
                     ok = false;
                     break;
                 }
                 ptx::tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BN;
                 const uint32_t b_units = (stage * p.stage_bytes) >> 4;
+                if (ptx::elect_one()) {
                 for (int kb = 0; kb < p.KB; ++kb) {
                     const uint32_t a_units = (static_cast<uint32_t>(kb) * A_KB) >> 4;
                     // k-step ks = taps (m, m+1) of phase ph: ks = ph * taps_per_phase / 2 + m / 2
@@ -278,34 +282,38 @@ __global__ void __launch_bounds__(kSmallThreads, 1)
                     }
                 }
                 ptx::umma_commit(ptx::smem_u32(&empty_bar[stage]));
+                ptx::umma_commit(ptx::smem_u32(&tfull_bar[buf]));
+                }
+                __syncwarp();
                 if (++stage == static_cast<uint32_t>(S)) {
                     stage = 0;
                     phase ^= 1u;
                 }
-                if (ok) ptx::umma_commit(ptx::smem_u32(&tfull_bar[buf]));
             }
         }
     } else if (warp == 5) {
         // ------------------------------------------------------------ copy producer
-        if (lane == 0) {
-            ptx::mbar_arrive_expect_tx(ptx::smem_u32(&a_full), static_cast<uint32_t>(p.KB) * A_KB);
-            for (int kb = 0; kb < p.KB; ++kb) ptx::tma_load_3d(sA + kb * A_KB, &tmW, ptx::smem_u32(&a_full), kb * 64, 0, 0);
+        // (converged warp, one issuing lane, as the UMMA issuer)
+        {
+            const bool leader = ptx::elect_one();
+            if (leader) ptx::mbar_arrive_expect_tx(ptx::smem_u32(&a_full), static_cast<uint32_t>(p.KB) * A_KB);
+            for (int kb = 0; kb < p.KB; ++kb) if (leader) ptx::tma_load_3d(sA + kb * A_KB, &tmW, ptx::smem_u32(&a_full), kb * 64, 0, 0);
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             for (int t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x) {
                 const int img = t / p.tiles_per_image;
                 const int oh0 = (t - img * p.tiles_per_image) * p.R;
-                if (!ptx::mbar_wait_bounded(ptx::smem_u32(&empty_bar[stage]), phase ^ 1u, abort_p, wait_limit)) break;
+                if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(ptx::smem_u32(&empty_bar[stage]), phase ^ 1u, abort_p, wait_limit))) break;
                 // row pairs j0 .. j0 + span - 1 of every phase (fewer at the bottom of the image: the
                 // rows left out only feed output rows that do not exist)
                 const int j0 = (oh0 * p.sh) / p.rstep;
                 const int nrows = min(p.span, p.J - j0);
                 const uint32_t bytes = static_cast<uint32_t>(nrows * p.OWp) * 16u;
                 const uint32_t bar = ptx::smem_u32(&raw_full[stage]);
-                ptx::mbar_arrive_expect_tx(bar, static_cast<uint32_t>(p.sw) * bytes);
+                if (leader) ptx::mbar_arrive_expect_tx(bar, static_cast<uint32_t>(p.sw) * bytes);
                 const uint32_t dst0 = sStage + stage * p.stage_bytes;
                 for (int ph = 0; ph < p.sw; ++ph)
-                    ptx::bulk_load(dst0 + ph * p.phase_bytes,
+                    if (leader) ptx::bulk_load(dst0 + ph * p.phase_bytes,
                                    p.xp + ((static_cast<long long>(img) * p.sw + ph) * p.J + j0) * p.OWp * 16, bytes, bar);
                 if (++stage == static_cast<uint32_t>(S)) {
                     stage = 0;
