@@ -369,8 +369,9 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
         }
         for (int i = 0; i < 2; ++i) {
             ptx::mbar_init(ptx::smem_u32(&tfull_bar[i]), 1u);
-            // PAIR: one arrival per epilogue warp of both CTAs (8 + 8), all on rank 0's barrier
-            ptx::mbar_init(ptx::smem_u32(&tempty_bar[i]), PAIR ? 16u : (USE_TMA ? ESETS * 128u : 128u));
+            // one arrival per epilogue warp (256 per-thread arrivals on one barrier serialise in shared
+            // memory); PAIR: the warps of both CTAs (8 + 8), all on rank 0's barrier
+            ptx::mbar_init(ptx::smem_u32(&tempty_bar[i]), PAIR ? 16u : (USE_TMA ? ESETS * 4u : 4u));
         }
         ptx::fence_mbar_init();
     }
@@ -718,7 +719,8 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
 #undef DLF_SWAPPED_FAST
                     }
                     ptx::tc_fence_before();
-                    ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));
                     continue;
                 }
                 if (p.out_nchw == 5) {
@@ -822,7 +824,8 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
                         if constexpr (RES) res_ahead(t, c0, ncols5, half ^ 1u);
                     }
                     ptx::tc_fence_before();
-                    ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));
                     continue;
                 }
             }
@@ -976,7 +979,8 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
                         __syncwarp();
                         if (lane == 0) ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_u32(&tempty_bar[buf]), 0u));
                     } else {
-                        ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));
                     }
                     continue;
                 }
@@ -1006,7 +1010,8 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_u32(&tempty_bar[buf]), 0u));
             } else {
-                ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));
             }
         }
         if constexpr (USE_TMA) {

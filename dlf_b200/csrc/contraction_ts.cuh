@@ -310,15 +310,16 @@ __global__ void __launch_bounds__(kTsThreads, 1)
     if (threadIdx.x == 0) {
         abort_flag = 0;
         for (int s = 0; s < kMaxStages; ++s) {
-            ptx::mbar_init(ptx::smem_u32(&full_a[s]), 128u);
-            ptx::mbar_init(ptx::smem_u32(&full_b[s]), tp.b_packed ? 1u : (tp.b_tma ? 64u : kTsLoaderThreads));
+            // (one arrival per warp: per-thread arrivals on one barrier serialise in shared memory)
+            ptx::mbar_init(ptx::smem_u32(&full_a[s]), 4u);
+            ptx::mbar_init(ptx::smem_u32(&full_b[s]), tp.b_packed ? 1u : (tp.b_tma ? 2u : kTsLoaderThreads / 32u));
             ptx::mbar_init(ptx::smem_u32(&raw_b[s]), 1u);
             ptx::mbar_init(ptx::smem_u32(&empty_a[s]), 1u);
             ptx::mbar_init(ptx::smem_u32(&empty_b[s]), 1u);
         }
         for (int i = 0; i < 2; ++i) {
             ptx::mbar_init(ptx::smem_u32(&tfull_bar[i]), 1u);
-            ptx::mbar_init(ptx::smem_u32(&tempty_bar[i]), 128u);
+            ptx::mbar_init(ptx::smem_u32(&tempty_bar[i]), 4u);  // one arrival per epilogue warp
         }
         ptx::fence_mbar_init();
     }
@@ -407,7 +408,8 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                 ptx::tc_fence_after();
                 drain_chunk(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + buf * BN, BN, part_row, kb0 == 0);
                 ptx::tc_fence_before();
-                ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));
                 if (++buf == static_cast<uint32_t>(nbuf)) {
                     buf = 0;
                     tphase ^= 1u;
@@ -546,7 +548,8 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                     }
                 }
                 ptx::tc_fence_before();
-                ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));
                 if constexpr (ES == 2) {
                     if (mode == 2) {
                         // every staging thread makes its writes visible to the async proxy, then
@@ -610,7 +613,8 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                                                 beta_e, bias, lane, part, pair_ok, ex);
             }
             ptx::tc_fence_before();
-            ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));
             if (++buf == static_cast<uint32_t>(nbuf)) {
                 buf = 0;
                 tphase ^= 1u;
@@ -833,7 +837,8 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                     if (acc == 0x12345678u) p.status[1] = 1;  // keeps the loads alive
                 }
                 ptx::tc_fence_before();
-                ptx::mbar_arrive(ptx::smem_u32(&full_a[s]));
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&full_a[s]));
                 gpar ^= 1u;
                 if (++s == static_cast<uint32_t>(SA)) {
                     s = 0;
@@ -909,7 +914,8 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                             st_shared_v4(sB + b_tile + o, lo);
                         }
                         ptx::fence_proxy_async_smem();
-                        ptx::mbar_arrive(ptx::smem_u32(&full_b[s]));
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&full_b[s]));
                         if (++s == static_cast<uint32_t>(SB)) {
                             s = 0;
                             ph ^= 1u;
@@ -920,9 +926,11 @@ __global__ void __launch_bounds__(kTsThreads, 1)
             ok = false;  // skip the gather loop below
         }
         if (tp.b_packed != nullptr) {
-            // stage images were prepared in global memory: one thread streams them in with bulk
-            // copies, the other loader threads have nothing to do
-            if (lt == 0) {
+            // stage images were prepared in global memory: the first loader warp streams them in with
+            // bulk copies (converged, one lane issuing: see the UMMA issuer), the other loader
+            // threads have nothing to do
+            if (warp == kTsLoaderWarp0) {
+                const bool leader = ptx::elect_one();
                 // the packing grid launched just before this one must have completed
                 asm volatile("griddepcontrol.wait;" ::: "memory");
                 for (int t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x) {
@@ -932,15 +940,15 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                     const unsigned char* src =
                         tp.b_packed + (static_cast<long long>(b) * p.tiles_n + n0 / BN) * num_kb * stage_bytes;
                     for (int kb = 0; kb < num_kb; ++kb) {
-                        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&empty_b[s]), ph ^ 1u, abort_p, wait_limit)) {
+                        if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(ptx::smem_u32(&empty_b[s]), ph ^ 1u, abort_p, wait_limit))) {
                             ok = false;
                             break;
                         }
                         const uint32_t bar = ptx::smem_u32(&full_b[s]);
                         const uint32_t sB = smem0 + s * stage_bytes;
-                        ptx::mbar_arrive_expect_tx(bar, stage_bytes);
+                        if (leader) ptx::mbar_arrive_expect_tx(bar, stage_bytes);
                         for (uint32_t o = 0; o < stage_bytes; o += 8192u)
-                            ptx::bulk_load(sB + o, src + static_cast<long long>(kb) * stage_bytes + o,
+                            if (leader) ptx::bulk_load(sB + o, src + static_cast<long long>(kb) * stage_bytes + o,
                                            min(8192u, stage_bytes - o), bar);
                         if (++s == static_cast<uint32_t>(SB)) {
                             s = 0;
@@ -991,7 +999,8 @@ __global__ void __launch_bounds__(kTsThreads, 1)
                     }
                 }
                 ptx::fence_proxy_async_smem();
-                ptx::mbar_arrive(ptx::smem_u32(&full_b[s]));
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&full_b[s]));
                 if (++s == static_cast<uint32_t>(SB)) {
                     s = 0;
                     ph ^= 1u;

@@ -119,7 +119,7 @@ __global__ void __launch_bounds__(kHaloThreads, 1)
         }
         for (int i = 0; i < 2; ++i) {
             ptx::mbar_init(ptx::smem_u32(&tfull_bar[i]), 1u);
-            ptx::mbar_init(ptx::smem_u32(&tempty_bar[i]), kHaloEpiSets * 128u);
+            ptx::mbar_init(ptx::smem_u32(&tempty_bar[i]), kHaloEpiSets * 4u);  // one arrival per epilogue warp
         }
         ptx::fence_mbar_init();
     }
@@ -215,7 +215,8 @@ __global__ void __launch_bounds__(kHaloThreads, 1)
                 }
             }
             ptx::tc_fence_before();
-            ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));
         }
         if (p.d_tma && lane == 0) ptx::bulk_wait_group<0>();
     } else if (warp == 4) {

@@ -143,7 +143,7 @@ __global__ void __launch_bounds__(kSmallThreads, 1)
         ptx::mbar_init(ptx::smem_u32(&a_full), 1u);
         for (int i = 0; i < 2; ++i) {
             ptx::mbar_init(ptx::smem_u32(&tfull_bar[i]), 1u);
-            ptx::mbar_init(ptx::smem_u32(&tempty_bar[i]), kSmallEpiSets * 128u);
+            ptx::mbar_init(ptx::smem_u32(&tempty_bar[i]), kSmallEpiSets * 4u);  // one arrival per epilogue warp
         }
         ptx::fence_mbar_init();
     }
@@ -237,7 +237,8 @@ __global__ void __launch_bounds__(kSmallThreads, 1)
                 }
             }
             ptx::tc_fence_before();
-            ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&tempty_bar[buf]));
         }
         if (p.d_tma && lane == 0) ptx::bulk_wait_group<0>();
     } else if (warp == 4) {
