@@ -1151,14 +1151,14 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
                     if (!PAIR && p.cl_swap && p.a_cl == 1) {
                         // swapped roles: A = filter bank (tiled), B = activations (im2col mode, BN windows)
                         const uint32_t bar = ptx::smem_u32(&full_bar[stage]);
-                        if (leader) ptx::mbar_arrive_expect_tx(bar, A_TILE + b_tile);
-                        DLF_CLK_ADD(6);
-                        if (leader) ptx::tma_load_3d(sA, &tmA, bar, kb * BK, m0, 0);
-                        DLF_CLK_ADD(7);  // first copy of the stage handed over
-                        if (leader) ptx::tma_load_im2col_4d(sB, &tmB, bar, cl_cb * BK, cl_w, cl_h, cl_n,
-                                                static_cast<unsigned short>(cl_kw * p.g.dw),
-                                                static_cast<unsigned short>(cl_kh * p.g.dh));
-                        DLF_CLK_ADD(8);  // second copy handed over
+                        if (leader) {  // one divergent region per k-block
+                            ptx::mbar_arrive_expect_tx(bar, A_TILE + b_tile);
+                            ptx::tma_load_3d(sA, &tmA, bar, kb * BK, m0, 0);
+                            ptx::tma_load_im2col_4d(sB, &tmB, bar, cl_cb * BK, cl_w, cl_h, cl_n,
+                                                    static_cast<unsigned short>(cl_kw * p.g.dw),
+                                                    static_cast<unsigned short>(cl_kh * p.g.dh));
+                        }
+                        DLF_CLK_ADD(8);  // copies handed over
                         if (++cl_cb == p.cl_cblocks) {
                             cl_cb = 0;
                             if (++cl_kw == p.g.KW) {
@@ -1174,13 +1174,13 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
                     }
                     if (!PAIR && p.a_cl == 1) {
                         const uint32_t bar = ptx::smem_u32(&full_bar[stage]);
-                        if (leader) ptx::mbar_arrive_expect_tx(bar, A_TILE + b_tile);
-                        DLF_CLK_ADD(6);
-                        if (leader) ptx::tma_load_im2col_4d(sA, &tmA, bar, cl_cb * BK, cl_w, cl_h, cl_n,
-                                                static_cast<unsigned short>(cl_kw * p.g.dw),
-                                                static_cast<unsigned short>(cl_kh * p.g.dh));
-                        DLF_CLK_ADD(7);
-                        if (leader) ptx::tma_load_3d(sB, &tmB, bar, kb * BK, n0, bb);
+                        if (leader) {  // one divergent region per k-block
+                            ptx::mbar_arrive_expect_tx(bar, A_TILE + b_tile);
+                            ptx::tma_load_im2col_4d(sA, &tmA, bar, cl_cb * BK, cl_w, cl_h, cl_n,
+                                                    static_cast<unsigned short>(cl_kw * p.g.dw),
+                                                    static_cast<unsigned short>(cl_kh * p.g.dh));
+                            ptx::tma_load_3d(sB, &tmB, bar, kb * BK, n0, bb);
+                        }
                         DLF_CLK_ADD(8);
                         if (++cl_cb == p.cl_cblocks) {
                             cl_cb = 0;
@@ -1214,20 +1214,20 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
                         }
                     } else {
                         const uint32_t bar = ptx::smem_u32(&full_bar[stage]);
-                        if (leader) ptx::mbar_arrive_expect_tx(bar, A_TILE + b_tile);
-                        DLF_CLK_ADD(6);
-                        if (p.a.k_major) {
-                            if (leader) ptx::tma_load_3d(sA, &tmA, bar, kb * BK, m0, ba);
-                        } else {
-                            for (int g = 0; g < kBM / E; ++g)
-                                if (leader) ptx::tma_load_3d(sA + g * BK * 128, &tmA, bar, m0 + g * E, kb * BK, ba);
-                        }
-                        DLF_CLK_ADD(7);
-                        if (p.b.k_major) {
-                            if (leader) ptx::tma_load_3d(sB, &tmB, bar, kb * BK, n0, bb);
-                        } else {
-                            for (int g = 0; g < BN / E; ++g)
-                                if (leader) ptx::tma_load_3d(sB + g * BK * 128, &tmB, bar, n0 + g * E, kb * BK, bb);
+                        if (leader) {  // one divergent region per k-block
+                            ptx::mbar_arrive_expect_tx(bar, A_TILE + b_tile);
+                            if (p.a.k_major) {
+                                ptx::tma_load_3d(sA, &tmA, bar, kb * BK, m0, ba);
+                            } else {
+                                for (int g = 0; g < kBM / E; ++g)
+                                    ptx::tma_load_3d(sA + g * BK * 128, &tmA, bar, m0 + g * E, kb * BK, ba);
+                            }
+                            if (p.b.k_major) {
+                                ptx::tma_load_3d(sB, &tmB, bar, kb * BK, n0, bb);
+                            } else {
+                                for (int g = 0; g < BN / E; ++g)
+                                    ptx::tma_load_3d(sB + g * BK * 128, &tmB, bar, n0 + g * E, kb * BK, bb);
+                            }
                         }
                         DLF_CLK_ADD(8);
                     }
