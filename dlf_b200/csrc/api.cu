@@ -556,7 +556,23 @@ int choose_bn_ts(const Problem& q, int num_sms, int max_bn, int a_cols, long lon
 // (about a millisecond) instead of 2^32. The epilogue's wait then runs out, every role drains,
 // tensor memory is freed and the status word reports the time-out; nothing traps or faults, and
 // the next launch runs normally.
+// multiply-shift constants for a divisor (see FastDiv in contraction.cuh); {0, 0} = divide plainly
+FastDiv make_fastdiv(long long d) {
+    FastDiv f{0u, 0u};
+    if (d <= 0 || d >= (1ll << 31)) return f;
+    unsigned shift = 0;
+    while ((1ull << shift) < static_cast<unsigned long long>(d)) ++shift;
+    f.shift = shift;
+    f.mul = static_cast<uint32_t>((((1ull << shift) - static_cast<unsigned long long>(d)) << 32) / static_cast<unsigned long long>(d)) + 1u;
+    return f;
+}
+
+// (also prepares the divisions of the tile decode: tiles_m, tiles_n and g are set by now)
 void set_wait_policy(Params& p, long long total_tiles) {
+    p.fd_per = make_fastdiv(static_cast<long long>(p.tiles_m) * p.tiles_n);
+    p.fd_group = make_fastdiv(static_cast<long long>(kGroupM) * p.tiles_n);
+    p.fd_P = make_fastdiv(p.g.P);
+    p.fd_OW = make_fastdiv(p.g.OW);
     const bool inject = (g_force_generic.load() & 0x10000000) != 0 && total_tiles == 1;
     p.wait_limit = inject ? (1ll << 21) : (1ll << 32);
     p.skip_tile_commit = inject ? 1 : 0;

@@ -101,11 +101,24 @@ struct Im2colGeom {
     long long out_img_stride;  // elements between images of Y (Cout*P)
 };
 
+// Division of a non-negative 32-bit int (< 2^31) by a divisor fixed for the launch, as a multiply
+// and a shift: q = (mulhi(n, mul) + n) >> shift with shift = ceil(log2 d) and
+// mul = floor(2^32 * (2^shift - d) / d) + 1, exact for n < 2^31 (the sum stays below 2^32). The role
+// warps decode a tile index and an image / row position once per tile; the compiler's division
+// sequences were a visible part of the per-tile cost. mul == 0: not prepared, divide plainly.
+struct FastDiv {
+    uint32_t mul, shift;
+};
+__device__ __forceinline__ int fast_div(int n, FastDiv f, int d) {
+    return f.mul ? static_cast<int>((__umulhi(static_cast<uint32_t>(n), f.mul) + static_cast<uint32_t>(n)) >> f.shift) : n / d;
+}
+
 struct Params {
     int M, N, K, batch;
     int BN, stages, fmt;
     int tiles_m, tiles_n;
     int total_tiles;
+    FastDiv fd_per, fd_group, fd_P, fd_OW;  // tiles_m * tiles_n, kGroupM * tiles_n, g.P, g.OW
     float alpha, beta;
     GenOperand a, b;
     char* d;
@@ -170,15 +183,16 @@ struct PixelEntry {  // one output pixel of the current tile (implicit im2col op
 __device__ __forceinline__ void decode_tile(const Params& p, int t, int& b, int& m0, int& n0,
                                             int rows_per_tile = kBM) {
     const int per = p.tiles_m * p.tiles_n;
-    b = t / per;
+    b = fast_div(t, p.fd_per, per);
     const int r = t - b * per;
     const int group = kGroupM * p.tiles_n;
-    const int gi = r / group;
+    const int gi = fast_div(r, p.fd_group, group);
     const int first = gi * kGroupM;
     const int gm = min(p.tiles_m - first, kGroupM);
     const int rr = r - gi * group;
-    m0 = (first + rr % gm) * rows_per_tile;
-    n0 = (rr / gm) * p.BN;
+    const int cq = gm == kGroupM ? rr / kGroupM : rr / gm;  // (a full group: a shift)
+    m0 = (first + rr - cq * gm) * rows_per_tile;
+    n0 = cq * p.BN;
 }
 
 template <int ES>
@@ -1131,9 +1145,9 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
                 int cl_n = 0, cl_h = 0, cl_w = 0;
                 if (!PAIR && p.a_cl == 1) {
                     const int first = p.cl_swap ? n0 : m0;  // first output pixel of the tile
-                    cl_n = first / p.g.P;
+                    cl_n = fast_div(first, p.fd_P, p.g.P);
                     const int pp = first - cl_n * p.g.P;
-                    const int oh = pp / p.g.OW;
+                    const int oh = fast_div(pp, p.fd_OW, p.g.OW);
                     cl_h = oh * p.g.sh - p.g.pad_t;
                     cl_w = (pp - oh * p.g.OW) * p.g.sw - p.g.pad_l;
                 }
