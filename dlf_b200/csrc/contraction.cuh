@@ -443,7 +443,7 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
             if (p.out_nchw == 3) {
                 if (c0 + 32 > ncols_t || mm + q * 32 >= p.M) return false;
                 const int j0 = nn + cbase + c0;
-                const int img = j0 / p.g.P;
+                const int img = fast_div(j0, p.fd_P, p.g.P);
                 const int pp = j0 - img * p.g.P;
                 if (pp + 32 > p.g.P && p.batch == 1) return false;
                 x = pp;
@@ -459,7 +459,7 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
                 z = p.d_batch_stride ? bb : 0;
                 return true;
             }
-            const int img0 = p.out_nchw == 1 ? i0 / p.g.P : 0;
+            const int img0 = p.out_nchw == 1 ? fast_div(i0, p.fd_P, p.g.P) : 0;
             const int pp0 = p.out_nchw == 1 ? i0 - img0 * p.g.P : i0;
             if (p.out_nchw == 1 && pp0 + 32 > p.g.P) return false;
             x = pp0;
@@ -621,7 +621,7 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
                     const bool relu3 = p.relu != 0;
                     for (int c0 = 0; c0 < ncols3; c0 += 32) {
                         const int j0 = n0 + cb3 + c0;
-                        const int img = j0 / p.g.P;
+                        const int img = fast_div(j0, p.fd_P, p.g.P);
                         const int pp = j0 - img * p.g.P;
                         const int nc = min(32, ncols3 - c0);
                         if (p.d_tma == 64 && (c0 & 63) == 0 && ncols3 - c0 >= 64 && (pp + 64 <= p.g.P || p.batch > 1)) {
@@ -848,7 +848,7 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
             long long rowbase;
             long long colstride;
             if (p.a.im2col || p.out_nchw) {
-                const int img = i / p.g.P;
+                const int img = fast_div(i, p.fd_P, p.g.P);
                 const int pp = i - img * p.g.P;
                 rowbase = static_cast<long long>(img) * p.g.out_img_stride +
                           static_cast<long long>(b) * p.d_batch_stride + pp;
@@ -871,7 +871,7 @@ __global__ void __launch_bounds__(PAIR ? kThreadsPair : (USE_TMA ? tma_threads(E
                     // NCHW output: a block of 32 pixels is one box of the {P, channels, images} map
                     // unless it runs over the end of its image; such a block (and only it) is
                     // written by the lanes themselves
-                    const int img0 = p.out_nchw == 1 ? i0 / p.g.P : 0;
+                    const int img0 = p.out_nchw == 1 ? fast_div(i0, p.fd_P, p.g.P) : 0;
                     const int pp0 = p.out_nchw == 1 ? i0 - img0 * p.g.P : i0;
                     const bool direct = p.out_nchw == 1 && pp0 + 32 > p.g.P;
                     const bool blk_ok = i0 < p.M;
